@@ -1,0 +1,591 @@
+/*
+ * CPU oracle for the quantized decode hot path.  TEST INFRASTRUCTURE ONLY.
+ *
+ * This file restates, in plain single-threaded C, the arithmetic of the
+ * reference library's quantized-decode functions so that the CUDA path can
+ * be checked bit-for-bit (integer outputs) or within tolerance (fp32
+ * outputs).  Nothing in the product links or calls it: only the tests, the
+ * smoke check and the benchmark's CPU-baseline leg may load it.
+ *
+ * Parity is pinned: every function here is compared with the reference's own
+ * compiled code (oracle/_ref, built by oracle/Makefile from the reference's
+ * sources) on seeded inputs, and with the fixtures in tests/golden/ that the
+ * same compiled reference produced.
+ *
+ * Build flags matter: compile WITHOUT -ffast-math and WITHOUT -march=native
+ * (no FMA contraction), the same way the reference is built, so that the
+ * float results agree bit-for-bit with the reference.
+ *
+ * Each function names the reference file:line it follows.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#define LHO_API __attribute__((visibility("default")))
+
+/* ------------------------------------------------------------------ */
+/* 16-bit float conversions (reference: src/kernels/dtypes.hpp:87-105) */
+/* ------------------------------------------------------------------ */
+
+/* fp32 -> bf16 bits, round-to-nearest-even, NaN kept quiet.
+ * Reference: src/kernels/dtypes.hpp:87-98. */
+LHO_API uint16_t lho_f32_to_bf16_bits(float v) {
+    uint32_t u;
+    memcpy(&u, &v, 4);
+    if (((u >> 23) & 0xffu) == 0xffu && (u & 0x7fffffu) != 0u)
+        return (uint16_t)((u >> 16) | 0x40u);
+    u += 0x7fffu + ((u >> 16) & 1u);
+    return (uint16_t)(u >> 16);
+}
+
+/* bf16 bits -> fp32.  Reference: src/kernels/dtypes.hpp:100-105. */
+LHO_API float lho_bf16_bits_to_f32(uint16_t b) {
+    uint32_t u = (uint32_t)b << 16;
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+}
+
+/* In-place round of an fp32 array to bf16 precision (stored back as fp32). */
+LHO_API void lho_round_to_bf16(float* x, int64_t n) {
+    for (int64_t i = 0; i < n; ++i)
+        x[i] = lho_bf16_bits_to_f32(lho_f32_to_bf16_bits(x[i]));
+}
+
+/* ------------------------------------------------------------------ */
+/* Symmetric integer rounding helpers                                  */
+/* ------------------------------------------------------------------ */
+
+/* Saturating round-half-even to [-lim, lim].
+ * Reference: src/kernels/quant.cpp:12-19 (int8), :117-124 (int4),
+ * src/kernels/kvcache_quant.cpp:14-23. */
+static inline int sat_rne(float v, int lim) {
+    if (v >= (float)lim) return lim;
+    if (v <= (float)-lim) return -lim;
+    int r = (int)lrintf(v);
+    if (r > lim) r = lim;
+    if (r < -lim) r = -lim;
+    return r;
+}
+
+static inline float absmax_f32(const float* x, int64_t n, int64_t stride) {
+    float m = 0.0f;
+    for (int64_t i = 0; i < n; ++i) {
+        float a = fabsf(x[i * stride]);
+        if (a > m) m = a;
+    }
+    return m;
+}
+
+/* ------------------------------------------------------------------ */
+/* int8 quantisers                                                     */
+/* ------------------------------------------------------------------ */
+
+/* Per-row (per-token) symmetric int8: scale = max|row|/127 (1 when the row
+ * is all zero), q = sat_rne(x * (1/scale)) -- note the reciprocal multiply.
+ * Reference: src/kernels/quant.cpp:52-63. */
+LHO_API void lho_q8_quantize_per_row(const float* src, int8_t* dst,
+                                     float* scales, int rows, int dim) {
+    for (int r = 0; r < rows; ++r) {
+        const float* x = src + (int64_t)r * dim;
+        int8_t* q = dst + (int64_t)r * dim;
+        float m = absmax_f32(x, dim, 1);
+        float s = (m > 0.0f) ? m / 127.0f : 1.0f;
+        float inv = 1.0f / s;
+        for (int i = 0; i < dim; ++i) q[i] = (int8_t)sat_rne(x[i] * inv, 127);
+        scales[r] = s;
+    }
+}
+
+/* Reference: src/kernels/quant.cpp:65-73. */
+LHO_API void lho_q8_dequantize_per_row(const int8_t* src, const float* scales,
+                                       float* dst, int rows, int dim) {
+    for (int r = 0; r < rows; ++r)
+        for (int i = 0; i < dim; ++i)
+            dst[(int64_t)r * dim + i] = src[(int64_t)r * dim + i] * scales[r];
+}
+
+/* Per-column (per-output-channel) symmetric int8 of a [rows, cols] matrix:
+ * scale[c] = max|col c|/127 (1 when zero), q = sat_rne(x / scale[c]) -- a
+ * true division here, unlike the per-row quantiser.
+ * Reference: src/kernels/quant.cpp:75-96. */
+LHO_API void lho_q8_quantize_per_col(const float* src, int8_t* dst,
+                                     float* scales, int rows, int cols) {
+    for (int c = 0; c < cols; ++c) {
+        float m = absmax_f32(src + c, rows, cols);
+        scales[c] = (m > 0.0f) ? m / 127.0f : 1.0f;
+    }
+    for (int r = 0; r < rows; ++r)
+        for (int c = 0; c < cols; ++c)
+            dst[(int64_t)r * cols + c] =
+                (int8_t)sat_rne(src[(int64_t)r * cols + c] / scales[c], 127);
+}
+
+/* Reference: src/kernels/quant.cpp:98-105. */
+LHO_API void lho_q8_dequantize_per_col(const int8_t* src, const float* scales,
+                                       float* dst, int rows, int cols) {
+    for (int r = 0; r < rows; ++r)
+        for (int c = 0; c < cols; ++c)
+            dst[(int64_t)r * cols + c] = src[(int64_t)r * cols + c] * scales[c];
+}
+
+/* ------------------------------------------------------------------ */
+/* int4 group-wise                                                     */
+/* ------------------------------------------------------------------ */
+
+/* Sign-extend the int4 stored for logical row k, column n of a [K, N] weight
+ * packed two-per-byte along K (byte (k/2, n); low nibble = even k).
+ * Reference: src/kernels/quant.hpp:68-75. */
+static inline int q4_at(const uint8_t* packed, int k, int n, int N) {
+    uint8_t b = packed[(int64_t)(k >> 1) * N + n];
+    int nib = (k & 1) ? (b >> 4) : (b & 0xf);
+    return (nib & 8) ? nib - 16 : nib;
+}
+
+LHO_API int lho_q4_get(const uint8_t* packed, int k, int n, int N) {
+    return q4_at(packed, k, n, N);
+}
+
+/* Group-wise symmetric int4 along K: scale[g, n] = max|w[gG..gG+G, n]|/7
+ * (1 when zero); q = sat_rne(w / scale) in [-7, 7] (true division); two's
+ * complement nibbles, even k in the low nibble.
+ * Reference: src/kernels/quant.cpp:128-160. */
+LHO_API void lho_q4_quantize_groupwise(const float* src, uint8_t* packed,
+                                       float* scales, int K, int N, int G) {
+    int groups = K / G;
+    for (int g = 0; g < groups; ++g)
+        for (int n = 0; n < N; ++n) {
+            float m = absmax_f32(src + (int64_t)g * G * N + n, G, N);
+            scales[(int64_t)g * N + n] = (m > 0.0f) ? m / 7.0f : 1.0f;
+        }
+    for (int k = 0; k < K; k += 2)
+        for (int n = 0; n < N; ++n) {
+            float s0 = scales[(int64_t)(k / G) * N + n];
+            float s1 = scales[(int64_t)((k + 1) / G) * N + n];
+            int lo = sat_rne(src[(int64_t)k * N + n] / s0, 7);
+            int hi = sat_rne(src[(int64_t)(k + 1) * N + n] / s1, 7);
+            packed[(int64_t)(k >> 1) * N + n] =
+                (uint8_t)((lo & 0xf) | ((hi & 0xf) << 4));
+        }
+}
+
+/* Reference: src/kernels/quant.cpp:162-171. */
+LHO_API void lho_q4_dequantize_groupwise(const uint8_t* packed,
+                                         const float* scales, float* dst,
+                                         int K, int N, int G) {
+    for (int k = 0; k < K; ++k)
+        for (int n = 0; n < N; ++n)
+            dst[(int64_t)k * N + n] =
+                (float)q4_at(packed, k, n, N) * scales[(int64_t)(k / G) * N + n];
+}
+
+/* ------------------------------------------------------------------ */
+/* GEMMs                                                               */
+/* ------------------------------------------------------------------ */
+
+/* C <- beta*C with the reference's special cases (beta==0 stores zeros even
+ * over NaN, beta==1 leaves C alone).
+ * Reference: src/kernels/gemm_quant.cpp:12-21, src/kernels/gemm.cpp:28-35. */
+static void scale_c(float* C, int M, int N, float beta) {
+    int64_t n = (int64_t)M * N;
+    if (beta == 0.0f) {
+        for (int64_t i = 0; i < n; ++i) C[i] = 0.0f;
+    } else if (beta != 1.0f) {
+        for (int64_t i = 0; i < n; ++i) C[i] *= beta;
+    }
+}
+
+/* fp32 GEMM C = alpha*A@B + beta*C, row-major, accumulating into C in
+ * ascending k for every (i, j) with the term (alpha*A[i,k])*B[k,j].  The
+ * reference's 64^3 blocking visits k in the same ascending order for a given
+ * (i, j), so the sums are bit-identical.
+ * Reference: src/kernels/gemm.cpp:21-57. */
+LHO_API void lho_gemm_f32(const float* A, const float* B, float* C, int M,
+                          int N, int K, float alpha, float beta) {
+    scale_c(C, M, N, beta);
+    for (int i = 0; i < M; ++i) {
+        float* c = C + (int64_t)i * N;
+        for (int k = 0; k < K; ++k) {
+            float a = alpha * A[(int64_t)i * K + k];
+            const float* b = B + (int64_t)k * N;
+            for (int j = 0; j < N; ++j) c[j] += a * b[j];
+        }
+    }
+}
+
+/* W8A8: int8 x int8 -> int32 exact, then C += alpha*a_s[m]*b_s[n]*float(acc)
+ * evaluated left to right.  B is [K, N] with N contiguous.  The k loop is
+ * interchanged with the j loop here (row-streaming B); int32 sums are exact,
+ * so the result is identical to the reference's column walk.
+ * Reference: src/kernels/gemm_quant.cpp:29-49. */
+LHO_API void lho_gemm_w8a8(const int8_t* Aq, const int8_t* Bq,
+                           const float* a_scales, const float* b_scales,
+                           float* C, int M, int N, int K, float alpha,
+                           float beta) {
+    scale_c(C, M, N, beta);
+    int32_t* acc = (int32_t*)malloc(sizeof(int32_t) * (size_t)N);
+    for (int i = 0; i < M; ++i) {
+        memset(acc, 0, sizeof(int32_t) * (size_t)N);
+        for (int k = 0; k < K; ++k) {
+            int32_t a = Aq[(int64_t)i * K + k];
+            const int8_t* b = Bq + (int64_t)k * N;
+            for (int j = 0; j < N; ++j) acc[j] += a * (int32_t)b[j];
+        }
+        float as = a_scales[i];
+        float* c = C + (int64_t)i * N;
+        for (int j = 0; j < N; ++j)
+            c[j] += alpha * as * b_scales[j] * (float)acc[j];
+    }
+    free(acc);
+}
+
+/* W4A16 group-wise: for each K-group, dequantise q*scale into an fp32 panel
+ * and accumulate C[i,:] += (alpha*A[i,k]) * panel[k,:] in ascending k.
+ * Reference: src/kernels/gemm_quant.cpp:54-82. */
+LHO_API void lho_gemm_w4a16_groupwise(const float* A, const uint8_t* Bp,
+                                      const float* b_scales, float* C, int M,
+                                      int N, int K, int G, float alpha,
+                                      float beta) {
+    scale_c(C, M, N, beta);
+    float* panel = (float*)malloc(sizeof(float) * (size_t)G * (size_t)N);
+    for (int k0 = 0; k0 < K; k0 += G) {
+        const float* s = b_scales + (int64_t)(k0 / G) * N;
+        for (int kk = 0; kk < G; ++kk)
+            for (int n = 0; n < N; ++n)
+                panel[(int64_t)kk * N + n] =
+                    (float)q4_at(Bp, k0 + kk, n, N) * s[n];
+        for (int i = 0; i < M; ++i) {
+            float* c = C + (int64_t)i * N;
+            for (int kk = 0; kk < G; ++kk) {
+                float a = alpha * A[(int64_t)i * K + k0 + kk];
+                const float* b = panel + (int64_t)kk * N;
+                for (int j = 0; j < N; ++j) c[j] += a * b[j];
+            }
+        }
+    }
+    free(panel);
+}
+
+/* Weight-only int8 per-channel GEMM.  The reference has no single function
+ * for it: it is the composition "dequantise per column, then fp32 GEMM".
+ * Reference: src/kernels/quant.cpp:98-105 followed by
+ * src/kernels/gemm.cpp:21-57. */
+LHO_API void lho_gemm_w8a16_perchannel(const float* A, const int8_t* Bq,
+                                       const float* b_scales, float* C, int M,
+                                       int N, int K, float alpha, float beta) {
+    float* Bd = (float*)malloc(sizeof(float) * (size_t)K * (size_t)N);
+    lho_q8_dequantize_per_col(Bq, b_scales, Bd, K, N);
+    lho_gemm_f32(A, Bd, C, M, N, K, alpha, beta);
+    free(Bd);
+}
+
+/* ------------------------------------------------------------------ */
+/* Paged KV cache                                                      */
+/* ------------------------------------------------------------------ */
+
+/* Mirrors PagedCacheLayout (src/kernels/kvcache.hpp:26-31). */
+typedef struct {
+    int num_blocks;
+    int block_size;
+    int n_kv_heads;
+    int head_dim;
+} lho_layout;
+
+/* Mirrors PagedAttnConfig (src/kernels/paged_attention.hpp:28-37); `causal`
+ * is an int here (0/1). */
+typedef struct {
+    int n_q_heads;
+    int n_kv_heads;
+    int seq_q;
+    int head_dim;
+    int causal;
+    float scale;
+    int window;
+    int chunk;
+} lho_attn_cfg;
+
+/* Element offset of (block, head, slot, 0) in a [num_blocks, heads,
+ * block_size, head_dim] pool.  Reference: src/kernels/kvcache.hpp:34-41. */
+static inline int64_t row_off(const lho_layout* L, int block, int head,
+                              int slot) {
+    return (((int64_t)block * L->n_kv_heads + head) * L->block_size + slot) *
+           L->head_dim;
+}
+
+/* Offset of the per-row scale in [num_blocks, heads, block_size].
+ * Reference: src/kernels/kvcache_quant.hpp:31-36. */
+static inline int64_t scale_off(const lho_layout* L, int block, int head,
+                                int slot) {
+    return ((int64_t)block * L->n_kv_heads + head) * L->block_size + slot;
+}
+
+/* fp32 append: copy each new (token, head) row into its page slot.  New rows
+ * arrive head-major: [n_kv_heads, seq_new, head_dim].
+ * Reference: src/kernels/kvcache.cpp:7-32. */
+LHO_API void lho_paged_kv_append_f32(float* k_pool, float* v_pool,
+                                     const float* k_new, const float* v_new,
+                                     const int32_t* table, const lho_layout* L,
+                                     int past_len, int seq_new) {
+    for (int s = 0; s < seq_new; ++s) {
+        int pos = past_len + s;
+        int blk = table[pos / L->block_size];
+        int slot = pos % L->block_size;
+        for (int h = 0; h < L->n_kv_heads; ++h) {
+            int64_t d = row_off(L, blk, h, slot);
+            int64_t f = ((int64_t)h * seq_new + s) * L->head_dim;
+            memcpy(k_pool + d, k_new + f, sizeof(float) * (size_t)L->head_dim);
+            memcpy(v_pool + d, v_new + f, sizeof(float) * (size_t)L->head_dim);
+        }
+    }
+}
+
+/* One head_dim row -> int8 + fp32 scale, reciprocal-multiply idiom.
+ * Reference: src/kernels/kvcache_quant.cpp:24-35. */
+static void q8_row(const float* x, int8_t* q, float* scale, int d) {
+    float m = absmax_f32(x, d, 1);
+    float s = (m > 0.0f) ? m / 127.0f : 1.0f;
+    float inv = 1.0f / s;
+    for (int i = 0; i < d; ++i) q[i] = (int8_t)sat_rne(x[i] * inv, 127);
+    *scale = s;
+}
+
+/* int8 append.  Reference: src/kernels/kvcache_quant.cpp:58-80. */
+LHO_API void lho_paged_kv_append_q8(int8_t* k_pool, int8_t* v_pool,
+                                    float* k_scales, float* v_scales,
+                                    const float* k_new, const float* v_new,
+                                    const int32_t* table, const lho_layout* L,
+                                    int past_len, int seq_new) {
+    for (int s = 0; s < seq_new; ++s) {
+        int pos = past_len + s;
+        int blk = table[pos / L->block_size];
+        int slot = pos % L->block_size;
+        for (int h = 0; h < L->n_kv_heads; ++h) {
+            int64_t d = row_off(L, blk, h, slot);
+            int64_t so = scale_off(L, blk, h, slot);
+            int64_t f = ((int64_t)h * seq_new + s) * L->head_dim;
+            q8_row(k_new + f, k_pool + d, k_scales + so, L->head_dim);
+            q8_row(v_new + f, v_pool + d, v_scales + so, L->head_dim);
+        }
+    }
+}
+
+/* Key j visible to query row i?  Causal aligns the LAST query row with cache
+ * position seq_len-1 (shift = seq_len - seq_q); window keeps the trailing
+ * `window` keys; chunk keeps keys in the query's chunk.
+ * Reference: src/kernels/kvcache_quant.cpp:42-54,
+ * src/kernels/paged_attention.cpp:18-30. */
+static inline int visible(const lho_attn_cfg* c, int i, int j, int shift) {
+    if (c->causal && j > shift + i) return 0;
+    if (c->window > 0 && j < shift + i - c->window + 1) return 0;
+    if (c->chunk > 0 && (shift + i) / c->chunk != j / c->chunk) return 0;
+    return 1;
+}
+
+static inline float softmax_scale(const lho_attn_cfg* c) {
+    return (c->scale > 0.0f) ? c->scale : 1.0f / sqrtf((float)c->head_dim);
+}
+
+/* Shared three-pass attention over a paged pool; `q8` selects int8 pools with
+ * per-row scales (dequantised element-by-element as k*ks, v*vs) or fp32
+ * pools.  Pass 1 scores + max, pass 2 exp + sum, pass 3 weighted V sum with
+ * p = e * (1/sum).  Rows with no visible key produce zeros.
+ * Reference: src/kernels/kvcache_quant.cpp:82-161 (int8),
+ * src/kernels/paged_attention.cpp:36-108 (fp32). */
+static void attend(const float* Q, const void* Kp, const void* Vp,
+                   const float* Ks, const float* Vs, const int32_t* table,
+                   int seq_len, float* O, const lho_attn_cfg* c,
+                   const lho_layout* L, int q8) {
+    const float sc = softmax_scale(c);
+    const int group = c->n_q_heads / c->n_kv_heads;
+    const int d = c->head_dim;
+    const int B = L->block_size;
+    const int shift = seq_len - c->seq_q;
+    float* w = (float*)calloc((size_t)(seq_len > 0 ? seq_len : 1), sizeof(float));
+
+    for (int h = 0; h < c->n_q_heads; ++h) {
+        const int kvh = h / group;
+        for (int i = 0; i < c->seq_q; ++i) {
+            const float* q = Q + ((int64_t)h * c->seq_q + i) * d;
+            float* o = O + ((int64_t)h * c->seq_q + i) * d;
+            int last = seq_len - 1;
+            if (c->causal && shift + i < last) last = shift + i;
+            int first = 0;
+            if (c->window > 0 && shift + i - c->window + 1 > 0)
+                first = shift + i - c->window + 1;
+            for (int t = 0; t < d; ++t) o[t] = 0.0f;
+            if (last < first) continue;
+
+            float mx = -INFINITY;
+            int any = 0;
+            for (int j = first; j <= last; ++j) {
+                if (!visible(c, i, j, shift)) continue;
+                int blk = table[j / B], slot = j % B;
+                float dot = 0.0f;
+                if (q8) {
+                    const int8_t* k = (const int8_t*)Kp + row_off(L, blk, kvh, slot);
+                    float ks = Ks[scale_off(L, blk, kvh, slot)];
+                    for (int t = 0; t < d; ++t) dot += q[t] * (k[t] * ks);
+                } else {
+                    const float* k = (const float*)Kp + row_off(L, blk, kvh, slot);
+                    for (int t = 0; t < d; ++t) dot += q[t] * k[t];
+                }
+                dot *= sc;
+                w[j] = dot;
+                if (dot > mx) mx = dot;
+                any = 1;
+            }
+            if (!any) continue;
+
+            float sum = 0.0f;
+            for (int j = first; j <= last; ++j) {
+                if (!visible(c, i, j, shift)) continue;
+                w[j] = expf(w[j] - mx);
+                sum += w[j];
+            }
+            const float inv = 1.0f / sum;
+            for (int j = first; j <= last; ++j) {
+                if (!visible(c, i, j, shift)) continue;
+                const float p = w[j] * inv;
+                int blk = table[j / B], slot = j % B;
+                if (q8) {
+                    const int8_t* v = (const int8_t*)Vp + row_off(L, blk, kvh, slot);
+                    float vs = Vs[scale_off(L, blk, kvh, slot)];
+                    for (int t = 0; t < d; ++t) o[t] += p * (v[t] * vs);
+                } else {
+                    const float* v = (const float*)Vp + row_off(L, blk, kvh, slot);
+                    for (int t = 0; t < d; ++t) o[t] += p * v[t];
+                }
+            }
+        }
+    }
+    free(w);
+}
+
+/* Single-request int8 paged attention.
+ * Reference: src/kernels/kvcache_quant.cpp:82-161. */
+LHO_API void lho_paged_attention_q8(const float* Q, const int8_t* Kp,
+                                    const int8_t* Vp, const float* Ks,
+                                    const float* Vs, const int32_t* table,
+                                    int seq_len, float* O,
+                                    const lho_attn_cfg* c, const lho_layout* L) {
+    attend(Q, Kp, Vp, Ks, Vs, table, seq_len, O, c, L, 1);
+}
+
+/* Single-request fp32 paged attention.
+ * Reference: src/kernels/paged_attention.cpp:112-123. */
+LHO_API void lho_paged_attention_f32(const float* Q, const float* Kp,
+                                     const float* Vp, const int32_t* table,
+                                     int seq_len, float* O,
+                                     const lho_attn_cfg* c, const lho_layout* L) {
+    attend(Q, Kp, Vp, NULL, NULL, table, seq_len, O, c, L, 0);
+}
+
+/* Batched calling convention: Q/O [n_req, n_q_heads, seq_q, head_dim], tables
+ * [n_req, max_blocks] row-major, seq_lens [n_req].  The reference offers it
+ * for fp32 pools only; the int8 form is the same loop over requests.
+ * Reference: src/kernels/paged_attention.cpp:125-148. */
+LHO_API void lho_paged_attention_q8_batched(
+    const float* Q, const int8_t* Kp, const int8_t* Vp, const float* Ks,
+    const float* Vs, const int32_t* tables, int max_blocks,
+    const int32_t* seq_lens, int n_req, float* O, const lho_attn_cfg* c,
+    const lho_layout* L) {
+    int64_t per = (int64_t)c->n_q_heads * c->seq_q * c->head_dim;
+    for (int r = 0; r < n_req; ++r)
+        attend(Q + r * per, Kp, Vp, Ks, Vs, tables + (int64_t)r * max_blocks,
+               seq_lens[r], O + r * per, c, L, 1);
+}
+
+LHO_API void lho_paged_attention_f32_batched(
+    const float* Q, const float* Kp, const float* Vp, const int32_t* tables,
+    int max_blocks, const int32_t* seq_lens, int n_req, float* O,
+    const lho_attn_cfg* c, const lho_layout* L) {
+    int64_t per = (int64_t)c->n_q_heads * c->seq_q * c->head_dim;
+    for (int r = 0; r < n_req; ++r)
+        attend(Q + r * per, Kp, Vp, NULL, NULL, tables + (int64_t)r * max_blocks,
+               seq_lens[r], O + r * per, c, L, 0);
+}
+
+/* ------------------------------------------------------------------ */
+/* Bench harness: independent calls of the functions above spread over */
+/* host threads (the functions themselves stay single-threaded, as in  */
+/* the reference).  Compiled with -fopenmp.                            */
+/* ------------------------------------------------------------------ */
+
+/* N-sharded W4A16: shard s holds a compact [K/2, n_shard] packed slab, its
+ * [K/G, n_shard] scales and its own [M, n_shard] output. */
+LHO_API void lho_par_gemm_w4a16_shards(const float* A,
+                                       const uint8_t* const* Bp,
+                                       const float* const* Bs, float* const* C,
+                                       int M, int n_shard, int K, int G,
+                                       float alpha, float beta, int shards) {
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int s = 0; s < shards; ++s)
+        lho_gemm_w4a16_groupwise(A, Bp[s], Bs[s], C[s], M, n_shard, K, G, alpha,
+                                 beta);
+}
+
+LHO_API void lho_par_gemm_w8a16_shards(const float* A, const int8_t* const* Bq,
+                                       const float* const* Bs, float* const* C,
+                                       int M, int n_shard, int K, float alpha,
+                                       float beta, int shards) {
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int s = 0; s < shards; ++s)
+        lho_gemm_w8a16_perchannel(A, Bq[s], Bs[s], C[s], M, n_shard, K, alpha,
+                                  beta);
+}
+
+/* W8A8 over slabs of `slab` rows of M. */
+LHO_API void lho_par_gemm_w8a8_mslabs(const int8_t* Aq, const int8_t* Bq,
+                                      const float* a_scales,
+                                      const float* b_scales, float* C, int M,
+                                      int N, int K, float alpha, float beta,
+                                      int slab) {
+    int n_slabs = (M + slab - 1) / slab;
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int s = 0; s < n_slabs; ++s) {
+        int m0 = s * slab;
+        int m = (M - m0 < slab) ? M - m0 : slab;
+        lho_gemm_w8a8(Aq + (int64_t)m0 * K, Bq, a_scales + m0, b_scales,
+                      C + (int64_t)m0 * N, m, N, K, alpha, beta);
+    }
+}
+
+/* One request per task. */
+LHO_API void lho_par_paged_attention_q8_batched(
+    const float* Q, const int8_t* Kp, const int8_t* Vp, const float* Ks,
+    const float* Vs, const int32_t* tables, int max_blocks,
+    const int32_t* seq_lens, int n_req, float* O, const lho_attn_cfg* c,
+    const lho_layout* L) {
+    int64_t per = (int64_t)c->n_q_heads * c->seq_q * c->head_dim;
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int r = 0; r < n_req; ++r)
+        lho_paged_attention_q8(Q + r * per, Kp, Vp, Ks, Vs,
+                               tables + (int64_t)r * max_blocks, seq_lens[r],
+                               O + r * per, c, L);
+}
+
+/* Append for many requests: request r appends seq_new[r] rows at past[r];
+ * k_new/v_new of request r start at element offset new_off[r]. */
+LHO_API void lho_par_paged_kv_append_q8_batched(
+    int8_t* k_pool, int8_t* v_pool, float* k_scales, float* v_scales,
+    const float* k_new, const float* v_new, const int64_t* new_off,
+    const int32_t* tables, int max_blocks, const int32_t* past,
+    const int32_t* seq_new, int n_req, const lho_layout* L) {
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int r = 0; r < n_req; ++r)
+        lho_paged_kv_append_q8(k_pool, v_pool, k_scales, v_scales,
+                               k_new + new_off[r], v_new + new_off[r],
+                               tables + (int64_t)r * max_blocks, L, past[r],
+                               seq_new[r]);
+}
+
+LHO_API int lho_max_threads(void) {
+#ifdef _OPENMP
+    extern int omp_get_max_threads(void);
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}

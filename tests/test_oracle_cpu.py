@@ -1,0 +1,150 @@
+"""CPU suite: the C restatement against the golden fixtures (produced by the
+reference's own compiled code) and, where the compiled reference is present,
+against it directly on larger seeded inputs.  Integer outputs and scales must
+be bit-identical; float outputs are bit-identical too because the restatement
+keeps the reference's accumulation order."""
+import numpy as np
+import pytest
+
+import golden_io as gio
+from cpu_checker import AttnCfg, Checker, Layout, PagedPools, ref_available
+
+port = Checker("lho")
+
+
+def same(a, b):
+    assert a.shape == b.shape and a.dtype == b.dtype
+    assert np.array_equal(a.view(np.uint8), b.view(np.uint8))
+
+
+def test_bf16_rounding_matches_reference_bits():
+    g = gio.load("bf16_round")
+    same(port.round_to_bf16(g["x"]), g["y"])
+
+
+def test_q8_per_row_golden():
+    g = gio.load("q8_per_row")
+    q, s = port.q8_quantize_per_row(g["x"])
+    same(q, g["q"]); same(s, g["s"])
+    same(port.q8_dequantize_per_row(q, s), g["d"])
+    assert s[3] == 1.0 and not q[3].any()          # zero row keeps scale 1
+    assert np.abs(q).max() <= 127
+    # reference invariant (tests/test_quant.cpp:24-47): |dq - x| < scale
+    assert np.all(np.abs(g["d"] - g["x"]) < s[:, None] + 1e-6)
+
+
+def test_q8_per_col_golden():
+    g = gio.load("q8_per_col")
+    q, s = port.q8_quantize_per_col(g["x"])
+    same(q, g["q"]); same(s, g["s"])
+    same(port.q8_dequantize_per_col(q, s), g["d"])
+    assert s[5] == 1.0
+
+
+@pytest.mark.parametrize("name", gio.names("q4_"))
+def test_q4_groupwise_golden(name):
+    g = gio.load(name)
+    G = int(g["G"])
+    p, s = port.q4_quantize_groupwise(g["w"], G)
+    same(p, g["p"]); same(s, g["s"])
+    same(port.q4_dequantize_groupwise(p, s, G), g["d"])
+    K, N = g["w"].shape
+    vals = np.array([[port.q4_get(p, k, n) for n in range(N)] for k in range(K)])
+    assert vals.min() >= -7 and vals.max() <= 7     # tests/test_quant.cpp:85-99
+    assert np.all(np.abs(g["d"] - g["w"]) < np.repeat(s, G, axis=0) + 1e-6)
+
+
+def test_w8a8_golden():
+    g = gio.load("w8a8_m32n48k64")
+    C = port.gemm_w8a8(g["Aq"], g["Bq"], g["a_s"], g["b_s"])
+    same(C, g["C"])
+    rel = np.sqrt(np.mean((C - g["C_fp32"]) ** 2)) / np.sqrt(np.mean(g["C_fp32"] ** 2))
+    assert rel < 0.05                                # tests/test_gemm_quant.cpp:31-53
+    g = gio.load("w8a8_beta")
+    same(port.gemm_w8a8(g["Aq"], g["Bq"], g["a_s"], g["b_s"], g["C0"], alpha=0.5, beta=2.0), g["C"])
+
+
+@pytest.mark.parametrize("name", gio.names("w4a16_"))
+def test_w4a16_golden(name):
+    g = gio.load(name)
+    G = int(g["G"])
+    same(port.gemm_w4a16_groupwise(g["A"], g["p"], g["s"], G), g["C"])
+    same(port.gemm_w4a16_groupwise(g["A"], g["p"], g["s"], G, g["C0"], alpha=0.5, beta=2.0), g["C_ab"])
+
+
+def test_w8a16_golden():
+    g = gio.load("w8a16_m16n64k128")
+    same(port.gemm_w8a16_perchannel(g["A"], g["Bq"], g["b_s"]), g["C"])
+
+
+def test_w4a16_packed_bytes_beat_fp16_by_3x():
+    # tests/test_gemm_quant.cpp:126-138
+    K = N = 4096
+    for G in (32, 64, 128):
+        assert (K * N * 2) / (K * N // 2 + K // G * N * 4) > 3.0
+
+
+def test_append_q8_golden():
+    g = gio.load("append_q8")
+    L = Layout(*[int(v) for v in g["layout"]])
+    pools = port.empty_pools_q8(L)
+    kn, vn = g["k_new"], g["v_new"]
+    port.paged_kv_append_q8(pools, kn[:, :5].copy(), vn[:, :5].copy(), g["table"], L, 0, 5)
+    port.paged_kv_append_q8(pools, kn[:, 5:].copy(), vn[:, 5:].copy(), g["table"], L, 5, 4)
+    same(pools.k, g["k"]); same(pools.v, g["v"]); same(pools.ks, g["ks"]); same(pools.vs, g["vs"])
+
+
+@pytest.mark.parametrize("name", gio.names("attn_"))
+def test_attention_golden(name):
+    g = gio.load(name)
+    L, cfg = gio.attn_structs(g)
+    pools = PagedPools(g["k"], g["v"], g["ks"], g["vs"])
+    O = port.paged_attention_q8_batched(g["Q"], pools, g["tables"], g["seq_lens"], cfg, L)
+    same(O, g["O"])
+    Of = port.paged_attention_f32_batched(g["Q"], g["kf"], g["vf"], g["tables"], g["seq_lens"], cfg, L)
+    same(Of, g["O_f32"])
+    # reference invariant (tests/test_kvcache_quant.cpp:71-127): q8 close to fp32
+    assert np.mean((O - Of) ** 2) < 1e-3 and np.abs(O - Of).max() < 5e-2
+
+
+@pytest.mark.skipif(not ref_available(), reason="compiled reference not present")
+def test_port_matches_compiled_reference_on_larger_inputs():
+    ref = Checker("lhr")
+    rng = np.random.default_rng(7)
+    # quantisers
+    x = rng.standard_normal((37, 200)).astype(np.float32)
+    for f in ("q8_quantize_per_row", "q8_quantize_per_col"):
+        a, b = getattr(port, f)(x), getattr(ref, f)(x)
+        same(a[0], b[0]); same(a[1], b[1])
+    w = (rng.standard_normal((512, 96)) * 0.02).astype(np.float32)
+    (p, s), (p2, s2) = port.q4_quantize_groupwise(w, 128), ref.q4_quantize_groupwise(w, 128)
+    same(p, p2); same(s, s2)
+    # GEMMs
+    A = rng.standard_normal((3, 512)).astype(np.float32)
+    same(port.gemm_w4a16_groupwise(A, p, s, 128), ref.gemm_w4a16_groupwise(A, p, s, 128))
+    Bq, bs = ref.q8_quantize_per_col(w)
+    same(port.gemm_w8a16_perchannel(A, Bq, bs), ref.gemm_w8a16_perchannel(A, Bq, bs))
+    Aq, a_s = ref.q8_quantize_per_row(A)
+    same(port.gemm_w8a8(Aq, Bq, a_s, bs), ref.gemm_w8a8(Aq, Bq, a_s, bs))
+    # paged decode at the benchmark's geometry, small batch
+    L = Layout(64, 16, 2, 128)
+    cfg = AttnCfg(8, 2, 1, 128, 1, 0.0, 0, 0)
+    lens = [200, 37, 129]
+    tables = np.full((3, 13), -1, np.int32)
+    perm = rng.permutation(64).astype(np.int32)
+    pa, pb = port.empty_pools_q8(L), ref.empty_pools_q8(L)
+    used = 0
+    for r, l in enumerate(lens):
+        nb = (l + 15) // 16
+        tables[r, :nb] = perm[used:used + nb]; used += nb
+        kn = rng.standard_normal((2, l, 128)).astype(np.float32)
+        vn = rng.standard_normal((2, l, 128)).astype(np.float32)
+        port.paged_kv_append_q8(pa, kn, vn, tables[r], L, 0, l)
+        ref.paged_kv_append_q8(pb, kn, vn, tables[r], L, 0, l)
+    same(pa.k, pb.k); same(pa.vs, pb.vs)
+    Q = rng.standard_normal((3, 8, 1, 128)).astype(np.float32)
+    sl = np.array(lens, np.int32)
+    same(port.paged_attention_q8_batched(Q, pa, tables, sl, cfg, L),
+         ref.paged_attention_q8_batched(Q, pb, tables, sl, cfg, L))
+    same(port.paged_attention_q8_batched(Q, pa, tables, sl, cfg, L, parallel=True),
+         ref.paged_attention_q8_batched(Q, pb, tables, sl, cfg, L))
