@@ -1,0 +1,436 @@
+"""Benchmark of the quantized decode hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Headline workload (N=1): int4 group-128 decode GEMV at the Llama-3-8B MLP
+up-projection shape (A 1x4096 bf16-stored, W 4096x14336), the second BASELINE
+config.  One step = one pass of the GEMV over LAYERS distinct quantised weight
+matrices (a 32-layer model's worth, 1 GB of packed weights, so the 126 MB L2
+cannot serve the traffic).  value = algorithmic bytes moved per second, summed
+over ranks.  At N>1 every weight is sharded along N (output columns), each
+rank computes its column slab, and the slabs of a step are reassembled with one
+NCCL all-gather (strong scaling).
+
+The same JSON line carries: the roofline of the dominant kernel against the
+measured HBM copy bandwidth, the end-to-end number through the host-buffer API
+(activations in from pinned host memory, outputs back out, every call), the
+reference's CPU implementation timed on this box's host cores on a bounded
+sample, clocks sampled during the timed region, and the other BASELINE
+workloads (M=8/32, weight-only int8 M=16, paged int8-KV decode attention,
+W8A8) as `extra`.  All inputs are seeded synthetic data of the stated shapes
+and distributions.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+K_DIM, N_DIM, GROUP = 4096, 14336, 128
+LAYERS = 32
+METRIC = "int4 group-128 decode GEMV effective HBM bandwidth"
+UNIT = "TB/s"
+
+
+def gemv_bytes(M, K, N, G, wbits=4):
+    """Algorithmic bytes of one call: packed weights + group/channel scales + A (fp32) + C (fp32)."""
+    w = K * N // 2 if wbits == 4 else K * N
+    sc = (K // G) * N * 4 if wbits == 4 else N * 4
+    return w + sc + 4 * M * K + 4 * M * N
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 1590.0)), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) while a region runs."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thr = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.02)
+
+    def __enter__(self):
+        if self.nv:
+            self._thr = threading.Thread(target=self._run, daemon=True)
+            self._thr.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thr:
+            self._thr.join()
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+def physical_gpu_index(local):
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local])
+        except Exception:
+            return local
+    return local
+
+
+# ----------------------------------------------------------------------------- reference arm
+
+def cpu_gemv_baseline(budget_s=12.0, M=1):
+    """The reference's gemm_w4a16_groupwise on the host cores: the unmodified
+    single-threaded function called on one compact N-shard per thread."""
+    import numpy as np
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from cpu_checker import best_checker
+    chk = best_checker()
+    threads = chk.max_threads()
+    rng = np.random.default_rng(20242)
+    W = (rng.standard_normal((K_DIM, N_DIM)) * 0.02).astype(np.float32)
+    p, s = chk.q4_quantize_groupwise(W, GROUP)
+    A = chk.round_to_bf16(rng.standard_normal((M, K_DIM)).astype(np.float32))
+    shards = threads
+    while N_DIM % shards:
+        shards -= 1
+    ns = N_DIM // shards
+    Bp = [np.ascontiguousarray(p[:, i * ns:(i + 1) * ns]) for i in range(shards)]
+    Bs = [np.ascontiguousarray(s[:, i * ns:(i + 1) * ns]) for i in range(shards)]
+    Cs = [np.zeros((M, ns), np.float32) for _ in range(shards)]
+    chk.par_gemm_w4a16_shards(A, Bp, Bs, Cs, GROUP)          # warm-up
+    times = []
+    t_end = time.perf_counter() + budget_s
+    while len(times) < 3 or (time.perf_counter() < t_end and len(times) < 200):
+        t0 = time.perf_counter()
+        chk.par_gemm_w4a16_shards(A, Bp, Bs, Cs, GROUP)
+        times.append(time.perf_counter() - t0)
+    times.sort()
+    p50 = times[len(times) // 2]
+    return {"value": gemv_bytes(M, K_DIM, N_DIM, GROUP) / p50 / 1e12, "unit": UNIT, "cores": threads,
+            "kind": chk.kind, "ms_per_call": p50 * 1e3,
+            "sample": f"{len(times)} calls of one {K_DIM}x{N_DIM} GEMV (M={M}), N split into "
+                      f"{shards} compact shards, one per host thread; p50"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    budget = max(4.0, min(20.0, 2.0 * (args.steps + args.warmup)))
+    cb = cpu_gemv_baseline(budget_s=budget)
+    line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": UNIT,
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": cb["ms_per_call"] * LAYERS, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"cfg2: W4A16 GEMV M=1 K={K_DIM} N={N_DIM} G={GROUP}; "
+                                   f"CPU sample = one weight matrix, step time scaled to {LAYERS}"},
+            "cpu_baseline": cb,
+            "e2e": {"value": cb["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- our arm
+
+def timed(fn, steps, warmup, dist, torch, sampler=None):
+    """W untimed steps, then exactly `steps` steps between CUDA events on the
+    launching stream, bracketed by barrier + synchronize; max over ranks."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ctx = sampler if sampler is not None else _Null()
+    with ctx:
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if dist is not None:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
+
+
+class _Null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False
+
+
+def make_w4_layers(torch, lb, layers, K, n_local, G, seed):
+    packed, scales = [], []
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+    for _ in range(layers):
+        W = torch.randn(K, n_local, device="cuda", generator=gen) * 0.02
+        p, s = lb.q4_quantize_groupwise(W, G)
+        packed.append(p)
+        scales.append(s)
+        del W
+    return packed, scales
+
+
+def bench_extra(torch, lb, steps, warmup, hbm_peak):
+    """The other BASELINE workloads on one GPU (kernel-only, inputs resident)."""
+    out = {}
+    gen = torch.Generator(device="cuda").manual_seed(20241)
+    packed, scales = make_w4_layers(torch, lb, 8, K_DIM, N_DIM, GROUP, 20243)
+    for M in (8, 32):
+        A = torch.randn(M, K_DIM, device="cuda", generator=gen).bfloat16().float()
+        C = torch.empty(M, N_DIM, device="cuda")
+
+        def step():
+            for p, s in zip(packed, scales):
+                lb.gemm_w4a16_groupwise(A, p, s, GROUP, C=C)
+        ms = timed(step, steps, warmup, None, torch)
+        per = ms / (steps * len(packed)) * 1e-3
+        b = gemv_bytes(M, K_DIM, N_DIM, GROUP)
+        out[f"w4a16_m{M}"] = {"us_per_call": per * 1e6, "GBps": b / per / 1e9,
+                              "hbm_frac": b / per / 1e9 / hbm_peak, "bytes": b}
+    del packed, scales
+    # weight-only int8, M=16, K=N=4096 (first BASELINE config), 16 weight sets = 268 MB
+    ws = []
+    for _ in range(16):
+        W = torch.randn(4096, 4096, device="cuda", generator=gen) * 0.02
+        ws.append(lb.q8_quantize_per_col(W))
+    A = torch.randn(16, 4096, device="cuda", generator=gen)
+    C = torch.empty(16, 4096, device="cuda")
+
+    def step8():
+        for q, s in ws:
+            lb.gemm_w8a16_perchannel(A, q, s, C=C)
+    ms = timed(step8, steps, warmup, None, torch)
+    per = ms / (steps * len(ws)) * 1e-3
+    b = gemv_bytes(16, 4096, 4096, 0, wbits=8)
+    out["w8a16_m16"] = {"us_per_call": per * 1e6, "GBps": b / per / 1e9, "hbm_frac": b / per / 1e9 / hbm_peak,
+                        "bytes": b}
+    del ws
+    out["paged_decode_q8"] = bench_paged_decode(torch, lb, steps, warmup, hbm_peak)
+    return out
+
+
+def bench_paged_decode(torch, lb, steps, warmup, hbm_peak, n_req=64, hq=32, hkv=8, d=128, bs=16,
+                       pool_pages=65536, seed=20243):
+    """Third BASELINE config: 64 sequences, lengths U[512,4096], page 16, random
+    block tables over a 64k-page pool, int8 KV with per-row fp32 scales."""
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    lens = rng.integers(512, 4097, size=n_req).astype(np.int32)
+    perm = rng.permutation(pool_pages).astype(np.int32)
+    max_blocks = 4096 // bs
+    tables = np.full((n_req, max_blocks), -1, np.int32)
+    used = 0
+    for r, l in enumerate(lens):
+        nb = (int(l) + bs - 1) // bs
+        tables[r, :nb] = perm[used:used + nb]
+        used += nb
+    L = lb.PagedLayout(pool_pages, bs, hkv, d)
+    shp = (pool_pages, hkv, bs, d)
+    k = torch.zeros(shp, dtype=torch.int8, device="cuda")
+    v = torch.zeros_like(k)
+    ks = torch.zeros(shp[:3], device="cuda")
+    vs = torch.zeros_like(ks)
+    td = torch.from_numpy(tables).cuda()
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+    for r, l in enumerate(lens):
+        kn = torch.randn(hkv, int(l), d, device="cuda", generator=gen)
+        vn = torch.randn(hkv, int(l), d, device="cuda", generator=gen)
+        lb.paged_kv_append_q8(k, v, ks, vs, kn, vn, td[r], L, 0, int(l))
+    Q = torch.randn(n_req, hq, 1, d, device="cuda", generator=gen)
+    O = torch.empty_like(Q)
+    sl = torch.from_numpy(lens).cuda()
+    cfg = lb.PagedAttnCfg(hq, hkv, 1, d, 1, 0.0, 0, 0)
+
+    def step():
+        lb.paged_attention_q8_batched(Q, k, v, ks, vs, td, sl, cfg, L, O=O)
+    ms = timed(step, steps, warmup, None, torch)
+    per = ms / steps * 1e-3
+    total = int(lens.sum())
+    pages = int(sum((int(l) + bs - 1) // bs for l in lens))
+    b = total * hkv * (2 * d + 8) + 2 * Q.numel() * 4 + 4 * pages + 4 * n_req
+    import ctypes as C
+    fast = lb._cabi.load().lhb_paged_attention_q8_fast_path(C.byref(cfg), C.byref(L))
+    return {"tok_per_s": n_req / per, "us_per_step": per * 1e6, "GBps": b / per / 1e9,
+            "hbm_frac": b / per / 1e9 / hbm_peak, "bytes": b, "sum_len": total, "fast_path": int(fast),
+            "note": "KV working set 313 MB > L2; one kernel launch per step"}
+
+
+def run_ours(args):
+    import torch
+    import longhornai_b200 as lb
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
+        dist = dist_mod
+    g = world
+    if N_DIM % (g * 16):
+        raise SystemExit("N must divide into 16-column-aligned shards")
+    n_local = N_DIM // g
+    hbm_peak, _, peak_kind = measured_peaks()
+    M = 1
+
+    packed, scales = make_w4_layers(torch, lb, LAYERS, K_DIM, n_local, GROUP, 20242 + rank)
+    gen = torch.Generator(device="cuda").manual_seed(7)
+    acts = [torch.randn(M, K_DIM, device="cuda", generator=gen).bfloat16().float() for _ in range(LAYERS)]
+    outs = torch.empty(LAYERS, M, n_local, device="cuda")
+    gathered = torch.empty(g, LAYERS, M, n_local, device="cuda") if g > 1 else None
+
+    def step():
+        for i in range(LAYERS):
+            lb.gemm_w4a16_groupwise(acts[i], packed[i], scales[i], GROUP, C=outs[i])
+        if g > 1:
+            dist.all_gather_into_tensor(gathered, outs)
+
+    sampler = ClockSampler(physical_gpu_index(local)) if rank == 0 else None
+    ms = timed(step, args.steps, args.warmup, dist, torch, sampler)
+    launches = args.steps * LAYERS
+    bytes_call_local = gemv_bytes(M, K_DIM, n_local, GROUP)
+    bytes_step_total = LAYERS * (g * (bytes_call_local - 4 * M * K_DIM) + 4 * M * K_DIM)
+    value = bytes_step_total * args.steps / (ms * 1e-3) / 1e12
+
+    # end to end through the host-buffer path: activations come from pinned host
+    # memory and results go back to pinned host memory on every call
+    h_act = [a.cpu().pin_memory() for a in acts]
+    h_out = torch.empty(LAYERS, M, n_local).pin_memory()
+    d_act = torch.empty(M, K_DIM, device="cuda")
+
+    def step_e2e():
+        for i in range(LAYERS):
+            d_act.copy_(h_act[i], non_blocking=True)
+            lb.gemm_w4a16_groupwise(d_act, packed[i], scales[i], GROUP, C=outs[i])
+            h_out[i].copy_(outs[i], non_blocking=True)
+        if g > 1:
+            dist.all_gather_into_tensor(gathered, outs)
+        torch.cuda.current_stream().synchronize()
+    ms_e2e = timed(step_e2e, args.steps, args.warmup, dist, torch)
+    e2e_value = bytes_step_total * args.steps / (ms_e2e * 1e-3) / 1e12
+
+    status = lb.default_context().poll()
+    if status != 0:
+        raise SystemExit(f"device status word = {status}")
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    per_launch_s = ms * 1e-3 / launches
+    achieved = bytes_call_local / per_launch_s / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": g, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"cfg2: W4A16 group-{GROUP} decode GEMV, A {M}x{K_DIM} (bf16-stored, fp32 in the API), "
+                               f"W {K_DIM}x{N_DIM} int4 packed [K/2,N] + fp32 scales; {LAYERS} distinct weight "
+                               f"matrices per step",
+                   "M": M, "K": K_DIM, "N": N_DIM, "group": GROUP, "layers_per_step": LAYERS,
+                   "sharding": f"N/{g} columns per rank" + (", one all-gather of the outputs per step" if g > 1 else ""),
+                   "l2": f"inputs larger than L2: {LAYERS * bytes_call_local / 1e6:.0f} MB of weights per rank "
+                         f"cycled every step" + ("" if LAYERS * bytes_call_local > 2 * 126e6 else
+                                                 " (NOT larger than L2 at this shard size)"),
+                   "fast_path": int(lb._cabi.load().lhb_gemm_w4a16_fast_path(M, n_local, K_DIM, GROUP))},
+        "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
+                "h2d_bytes_per_step": LAYERS * M * K_DIM * 4, "d2h_bytes_per_step": LAYERS * M * n_local * 4,
+                "note": "activations H2D from pinned memory and outputs D2H every call; weights resident"},
+        "gpu_launches": launches,
+        "roofline": {"bound": "hbm", "kernel": "gemv_mma_kernel<4,1>", "achieved": achieved, "peak": hbm_peak,
+                     "unit": "GB/s", "frac": achieved / hbm_peak, "peak_kind": f"of {peak_kind}",
+                     "frac_of_nominal_8TBps": achieved / 8000.0, "bytes_per_launch": bytes_call_local,
+                     "us_per_launch": per_launch_s * 1e6, "traffic": None},
+        "clocks": sampler.summary() if sampler else None,
+    }
+    if g == 1 and not args.no_extra:
+        try:
+            line["extra"] = bench_extra(torch, lb, args.steps, args.warmup, hbm_peak)
+        except Exception as e:      # the headline must still be printed
+            line["extra"] = {"error": repr(e)}
+    if g == 1 and not args.no_cpu:
+        try:
+            line["cpu_baseline"] = cpu_gemv_baseline()
+        except Exception as e:
+            line["cpu_baseline"] = {"error": repr(e)}
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extra", action="store_true", help="skip the secondary workloads")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

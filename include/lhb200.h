@@ -1,0 +1,241 @@
+/*
+ * lhb200 -- C ABI of the B200 (sm_100a) implementation of LonghornAI's
+ * quantized decode hot path.
+ *
+ * Every entry point mirrors one free function of the reference's
+ * `namespace lh` kernel layer (the citation above each declaration gives the
+ * reference header it replaces).  Differences that the GPU imposes, and that
+ * are the same for every call:
+ *
+ *   - all data pointers are DEVICE pointers on the context's device;
+ *   - the call only ENQUEUES work on `stream` (a cudaStream_t passed as
+ *     void*; NULL = the legacy default stream) and never synchronises;
+ *   - the first argument is a context created once per device, which owns the
+ *     scratch arena the split kernels use, so no call allocates device memory;
+ *   - the return value is 0 or a negative lhb_status; nothing throws.  The
+ *     reference validates nothing and returns void; here shape and alignment
+ *     preconditions are checked and reported.
+ *
+ * Alignment contract: base pointers 16-byte aligned.  Any shape is accepted;
+ * shapes that meet the fast-path conditions documented per call run the
+ * tensor-core kernels, others run a generic kernel with identical results
+ * within the stated tolerance.
+ *
+ * There is no CPU fallback: without a CUDA device every compute call returns
+ * LHB_ERR_CUDA.
+ */
+#ifndef LHB200_H
+#define LHB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LHB_API __attribute__((visibility("default")))
+
+typedef enum lhb_status {
+    LHB_OK = 0,
+    LHB_ERR_BAD_SHAPE = -1,    /* a dimension is non-positive or violates a precondition */
+    LHB_ERR_MISALIGNED = -2,   /* a pointer misses the 16-byte alignment contract */
+    LHB_ERR_UNSUPPORTED = -3,  /* valid in the reference, not implemented here */
+    LHB_ERR_CUDA = -4,         /* a CUDA runtime/driver call failed (see lhb_last_error) */
+    LHB_ERR_NULL = -5,         /* a required pointer (or the context) is NULL */
+    LHB_ERR_SCRATCH = -6,      /* the context's scratch arena is too small for this call */
+    LHB_ERR_TIMEOUT = -7       /* a bounded device-side wait gave up (read via lhb_ctx_poll) */
+} lhb_status;
+
+typedef struct lhb_ctx lhb_ctx;
+
+/* Mirrors lh::PagedCacheLayout (src/kernels/kvcache.hpp:26-31): pools are
+ * [num_blocks, n_kv_heads, block_size, head_dim], scale pools
+ * [num_blocks, n_kv_heads, block_size]. */
+typedef struct lhb_paged_layout {
+    int num_blocks;
+    int block_size;
+    int n_kv_heads;
+    int head_dim;
+} lhb_paged_layout;
+
+/* Mirrors lh::PagedAttnConfig (src/kernels/paged_attention.hpp:28-37);
+ * `causal` is an int (0/1); scale <= 0 means 1/sqrt(head_dim). */
+typedef struct lhb_paged_attn_cfg {
+    int n_q_heads;
+    int n_kv_heads;
+    int seq_q;
+    int head_dim;
+    int causal;
+    float scale;
+    int window;
+    int chunk;
+} lhb_paged_attn_cfg;
+
+/* ---- context ------------------------------------------------------------ */
+
+/* Create the per-device context: a scratch arena of `scratch_bytes` (0 = the
+ * 64 MiB default) and a device status word.  No counterpart in the reference
+ * (its kernels use std::vector scratch: src/kernels/gemm_quant.cpp:59,
+ * src/kernels/kvcache_quant.cpp:93). */
+LHB_API int lhb_ctx_create(int device, size_t scratch_bytes, lhb_ctx** out);
+LHB_API int lhb_ctx_destroy(lhb_ctx* ctx);
+/* Synchronise `stream` and return the device status word (0, or
+ * LHB_ERR_TIMEOUT if a kernel's bounded wait expired); clears it. */
+LHB_API int lhb_ctx_poll(lhb_ctx* ctx, void* stream);
+LHB_API const char* lhb_status_string(int status);
+/* Text of the last failing CUDA call on this thread ("" if none). */
+LHB_API const char* lhb_last_error(void);
+/* 1 when a W4/W8 GEMM or paged-attention call with these arguments takes the
+ * tensor-core fast path, 0 when it takes the generic kernel (for tests and
+ * benchmarks to state which path they timed). */
+LHB_API int lhb_gemm_w4a16_fast_path(int M, int N, int K, int group_size);
+LHB_API int lhb_gemm_w8a16_fast_path(int M, int N, int K);
+LHB_API int lhb_gemm_w8a8_fast_path(int M, int N, int K);
+LHB_API int lhb_paged_attention_q8_fast_path(const lhb_paged_attn_cfg* cfg,
+                                             const lhb_paged_layout* layout);
+
+/* ---- quantisers (bit-exact with the reference) ---------------------------- */
+
+/* lh::q8_quantize_per_row / q8_dequantize_per_row (src/kernels/quant.hpp:38-41). */
+LHB_API int lhb_q8_quantize_per_row(lhb_ctx* ctx, const float* src, int8_t* dst,
+                                    float* scales_out, int rows, int dim, void* stream);
+LHB_API int lhb_q8_dequantize_per_row(lhb_ctx* ctx, const int8_t* src, const float* scales,
+                                      float* dst, int rows, int dim, void* stream);
+/* lh::q8_quantize_per_col / q8_dequantize_per_col (src/kernels/quant.hpp:45-48). */
+LHB_API int lhb_q8_quantize_per_col(lhb_ctx* ctx, const float* src, int8_t* dst,
+                                    float* scales_out, int rows, int cols, void* stream);
+LHB_API int lhb_q8_dequantize_per_col(lhb_ctx* ctx, const int8_t* src, const float* scales,
+                                      float* dst, int rows, int cols, void* stream);
+/* lh::q4_quantize_groupwise / q4_dequantize_groupwise (src/kernels/quant.hpp:60-63).
+ * K even, group_size divides K. */
+LHB_API int lhb_q4_quantize_groupwise(lhb_ctx* ctx, const float* src, uint8_t* packed,
+                                      float* scales_out, int K, int N, int group_size,
+                                      void* stream);
+LHB_API int lhb_q4_dequantize_groupwise(lhb_ctx* ctx, const uint8_t* packed, const float* scales,
+                                        float* dst, int K, int N, int group_size, void* stream);
+
+/* ---- quantized GEMMs ------------------------------------------------------- */
+
+/* lh::gemm_w8a8 (src/kernels/gemm_quant.hpp:42-45): int8 A [M,K] x int8 B [K,N]
+ * (N contiguous), int32 accumulate, C = beta*C + alpha*A_scales[m]*B_scales[n]*acc.
+ * With beta == 0 the result is bit-identical to the reference. */
+LHB_API int lhb_gemm_w8a8(lhb_ctx* ctx, const int8_t* A_q, const int8_t* B_q,
+                          const float* A_scales, const float* B_scales, float* C, int M, int N,
+                          int K, float alpha, float beta, void* stream);
+/* lh::gemm_w4a16_groupwise (src/kernels/gemm_quant.hpp:54-57): fp32 A [M,K],
+ * packed int4 B [K/2,N] with fp32 scales [K/G,N], fp32 C [M,N]. */
+LHB_API int lhb_gemm_w4a16_groupwise(lhb_ctx* ctx, const float* A, const uint8_t* B_packed,
+                                     const float* B_scales, float* C, int M, int N, int K,
+                                     int group_size, float alpha, float beta, void* stream);
+/* Weight-only int8 per-output-channel GEMM.  The reference has no single
+ * function: it is q8_dequantize_per_col (src/kernels/quant.hpp:47) followed by
+ * gemm (src/kernels/gemm.hpp:18); this call fuses the two. */
+LHB_API int lhb_gemm_w8a16_perchannel(lhb_ctx* ctx, const float* A, const int8_t* B_q,
+                                      const float* B_scales, float* C, int M, int N, int K,
+                                      float alpha, float beta, void* stream);
+
+/* ---- paged int8 KV cache ---------------------------------------------------- */
+
+/* lh::paged_kv_append_q8 (src/kernels/kvcache_quant.hpp:41-46): one request;
+ * k_new/v_new fp32 [n_kv_heads, seq_new, head_dim]; block_table device int32. */
+LHB_API int lhb_paged_kv_append_q8(lhb_ctx* ctx, int8_t* k_pool, int8_t* v_pool, float* k_scales,
+                                   float* v_scales, const float* k_new, const float* v_new,
+                                   const int32_t* block_table, const lhb_paged_layout* layout,
+                                   int past_len, int seq_new, void* stream);
+/* Batched form of the same append for a decode step: request r appends
+ * `seq_new` rows at position past_lens[r] (device array) through row r of
+ * block_tables [n_requests, max_blocks_per_req]; k_new/v_new are
+ * [n_requests, n_kv_heads, seq_new, head_dim].  The reference appends one
+ * request per call (src/kernels/kvcache_quant.cpp:58-80); this is that loop
+ * in one launch. */
+LHB_API int lhb_paged_kv_append_q8_batched(lhb_ctx* ctx, int8_t* k_pool, int8_t* v_pool,
+                                           float* k_scales, float* v_scales, const float* k_new,
+                                           const float* v_new, const int32_t* block_tables,
+                                           int max_blocks_per_req, const int32_t* past_lens,
+                                           int n_requests, const lhb_paged_layout* layout,
+                                           int seq_new, void* stream);
+/* lh::paged_kv_append (src/kernels/kvcache.hpp:50-55): fp32 pools. */
+LHB_API int lhb_paged_kv_append_f32(lhb_ctx* ctx, float* k_pool, float* v_pool,
+                                    const float* k_new, const float* v_new,
+                                    const int32_t* block_table, const lhb_paged_layout* layout,
+                                    int past_len, int seq_new, void* stream);
+
+/* ---- paged attention ---------------------------------------------------------- */
+
+/* lh::paged_attention_q8 (src/kernels/kvcache_quant.hpp:51-57): one request. */
+LHB_API int lhb_paged_attention_q8(lhb_ctx* ctx, const float* Q, const int8_t* K_pool,
+                                   const int8_t* V_pool, const float* K_scales,
+                                   const float* V_scales, const int32_t* block_table, int seq_len,
+                                   float* O, const lhb_paged_attn_cfg* cfg,
+                                   const lhb_paged_layout* layout, void* stream);
+/* Batched int8 paged attention with the calling convention of
+ * lh::paged_attention_batched (src/kernels/paged_attention.hpp:50-63) plus the
+ * two scale pools: Q/O [n_requests, n_q_heads, seq_q, head_dim], block_tables
+ * int32 [n_requests, max_blocks_per_req] (padding value ignored), seq_lens
+ * int32 [n_requests], all in device memory. */
+LHB_API int lhb_paged_attention_q8_batched(lhb_ctx* ctx, const float* Q, const int8_t* K_pool,
+                                           const int8_t* V_pool, const float* K_scales,
+                                           const float* V_scales, const int32_t* block_tables,
+                                           int max_blocks_per_req, const int32_t* seq_lens,
+                                           int n_requests, float* O,
+                                           const lhb_paged_attn_cfg* cfg,
+                                           const lhb_paged_layout* layout, void* stream);
+/* lh::paged_attention / lh::paged_attention_batched on fp32 pools
+ * (src/kernels/paged_attention.hpp:42-63). */
+LHB_API int lhb_paged_attention_f32_batched(lhb_ctx* ctx, const float* Q, const float* K_pool,
+                                            const float* V_pool, const int32_t* block_tables,
+                                            int max_blocks_per_req, const int32_t* seq_lens,
+                                            int n_requests, float* O,
+                                            const lhb_paged_attn_cfg* cfg,
+                                            const lhb_paged_layout* layout, void* stream);
+
+/* ---- device-resident cache manager ---------------------------------------------- */
+
+/* Host bookkeeping of lh::CacheManager (src/runtime/cache_manager.hpp:34-110:
+ * LIFO free list popping ascending ids, refcounts, all-or-nothing
+ * ensure_capacity) with the storage moved to the GPU: int8 K/V pools + fp32
+ * scale pools in the layout above, and the batched block tables
+ * int32 [max_requests, max_blocks_per_req] (padded with -1) and seq_lens
+ * int32 [max_requests] of lh::Scheduler::prepare_step
+ * (src/runtime/scheduler.cpp:41-58) kept in device memory and patched
+ * incrementally (row = request id) instead of rebuilt every step.  With
+ * ctx == NULL the manager is "detached": the same bookkeeping with no device
+ * storage (every device pointer getter returns NULL). */
+typedef struct lhb_cache_manager lhb_cache_manager;
+
+LHB_API int lhb_cm_create(lhb_ctx* ctx, const lhb_paged_layout* layout, int max_requests,
+                          int max_blocks_per_req, lhb_cache_manager** out);
+LHB_API int lhb_cm_destroy(lhb_cache_manager* cm);
+LHB_API int lhb_cm_num_free_blocks(const lhb_cache_manager* cm);
+LHB_API int lhb_cm_num_total_blocks(const lhb_cache_manager* cm);
+/* Returns the new request id (dense, reused after release) or -1 when
+ * max_requests are live. */
+LHB_API int lhb_cm_create_request(lhb_cache_manager* cm);
+LHB_API int lhb_cm_release_request(lhb_cache_manager* cm, int id, void* stream);
+/* 1 on success, 0 on out-of-blocks (table unchanged), negative on error. */
+LHB_API int lhb_cm_ensure_capacity(lhb_cache_manager* cm, int id, int seq_len, void* stream);
+LHB_API int lhb_cm_set_seq_len(lhb_cache_manager* cm, int id, int seq_len, void* stream);
+LHB_API int lhb_cm_reference_block(lhb_cache_manager* cm, int id, int logical_idx, int physical,
+                                   void* stream);
+LHB_API int lhb_cm_allocate_block(lhb_cache_manager* cm);
+LHB_API int lhb_cm_release_block(lhb_cache_manager* cm, int physical);
+LHB_API int lhb_cm_retain_block(lhb_cache_manager* cm, int physical);
+LHB_API int lhb_cm_refcount(const lhb_cache_manager* cm, int physical);
+LHB_API int lhb_cm_seq_len(const lhb_cache_manager* cm, int id);
+/* Copies the host copy of request `id`'s block table into out[0..cap) and
+ * returns its length. */
+LHB_API int lhb_cm_block_table(const lhb_cache_manager* cm, int id, int32_t* out, int cap);
+/* Device pointers (valid until lhb_cm_destroy). */
+LHB_API int8_t* lhb_cm_k_pool(lhb_cache_manager* cm);
+LHB_API int8_t* lhb_cm_v_pool(lhb_cache_manager* cm);
+LHB_API float* lhb_cm_k_scales(lhb_cache_manager* cm);
+LHB_API float* lhb_cm_v_scales(lhb_cache_manager* cm);
+LHB_API int32_t* lhb_cm_block_tables(lhb_cache_manager* cm);
+LHB_API int32_t* lhb_cm_seq_lens(lhb_cache_manager* cm);
+LHB_API int lhb_cm_max_blocks_per_req(const lhb_cache_manager* cm);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LHB200_H */

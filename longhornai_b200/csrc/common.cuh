@@ -1,0 +1,97 @@
+// Shared declarations of the lhb200 library: the context object, error
+// plumbing and small device helpers used by every kernel file.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <mutex>
+#include <string>
+#include <unordered_map>
+
+#include "lhb200.h"
+
+namespace lhb {
+
+// Per-thread text of the last failing CUDA call (read by lhb_last_error).
+void set_last_error(const char* what, cudaError_t err);
+void set_last_error_text(const std::string& text);
+
+#define LHB_CUDA(call)                                   \
+    do {                                                 \
+        cudaError_t _e = (call);                         \
+        if (_e != cudaSuccess) {                         \
+            ::lhb::set_last_error(#call, _e);            \
+            return LHB_ERR_CUDA;                         \
+        }                                                \
+    } while (0)
+
+#define LHB_LAUNCH_CHECK()                               \
+    do {                                                 \
+        cudaError_t _e = cudaGetLastError();             \
+        if (_e != cudaSuccess) {                         \
+            ::lhb::set_last_error("kernel launch", _e);  \
+            return LHB_ERR_CUDA;                         \
+        }                                                \
+    } while (0)
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
+inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// 128-byte opaque tensor-map blob (layout-compatible with CUtensorMap).
+struct alignas(64) TensorMap { unsigned char bytes[128]; };
+
+}  // namespace lhb
+
+// The context: one per device.  Scratch is carved out linearly per call (calls
+// on one context are expected on one stream at a time; concurrent calls that
+// use scratch must use separate contexts).
+struct lhb_ctx {
+    int device = 0;
+    int sm_count = 0;
+    size_t scratch_bytes = 0;
+    unsigned char* scratch = nullptr;   // device
+    int* status_word = nullptr;         // device, 0 = ok
+    int* counters = nullptr;            // device, zero-initialised, self-resetting
+    size_t counters_len = 0;
+    std::mutex mu;
+    // tensor maps keyed by (pointer, dims, box) -- encoding costs microseconds
+    std::unordered_map<std::string, lhb::TensorMap> tmaps;
+};
+
+namespace lhb {
+
+// ---------------------------------------------------------------------------
+// device helpers
+// ---------------------------------------------------------------------------
+
+// Saturating round-half-even to [-lim, lim]; the reference's sat_round_i8 /
+// sat_round_i4 / saturate_round (src/kernels/quant.cpp:12-19, :117-124,
+// src/kernels/kvcache_quant.cpp:14-23).  NaN maps to -lim, which is what
+// lrintf + clamp gives on x86-64.
+__device__ __forceinline__ int sat_rne(float v, int lim) {
+    const float l = static_cast<float>(lim);
+    if (v >= l) return lim;
+    if (v <= -l) return -lim;
+    if (v != v) return -lim;
+    int r = __float2int_rn(v);
+    r = r > lim ? lim : r;
+    r = r < -lim ? -lim : r;
+    return r;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+}  // namespace lhb

@@ -1,0 +1,53 @@
+// Internal launch functions shared between the kernel files and api.cu.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "lhb200.h"
+
+namespace lhb {
+
+// generic kernels (gemm_generic.cu, paged_attention_generic.cu)
+int launch_w4a16_generic(const float* A, const uint8_t* Bp, const float* Bs, float* C, int M, int N,
+                         int K, int G, float alpha, float beta, cudaStream_t st);
+int launch_w8a16_generic(const float* A, const int8_t* Bq, const float* Bs, float* C, int M, int N,
+                         int K, float alpha, float beta, cudaStream_t st);
+int launch_w8a8_generic(const int8_t* Aq, const int8_t* Bq, const float* as, const float* bs,
+                        float* C, int M, int N, int K, float alpha, float beta, cudaStream_t st);
+int launch_paged_attention_generic(lhb_ctx* ctx, bool q8, const float* Q, const void* Kp,
+                                   const void* Vp, const float* Ks, const float* Vs,
+                                   const int32_t* tables, int max_blocks, const int32_t* seq_lens,
+                                   int seq_len_scalar, int n_req, float* O,
+                                   const lhb_paged_attn_cfg& cfg, const lhb_paged_layout& L,
+                                   cudaStream_t st);
+
+// tensor-core skinny GEMMs (gemv_mma.cu)
+bool w4a16_fast_ok(int M, int N, int K, int G);
+bool w8a16_fast_ok(int M, int N, int K);
+int launch_w4a16_fast(lhb_ctx* ctx, const float* A, const uint8_t* Bp, const float* Bs, float* C,
+                      int M, int N, int K, int G, float alpha, float beta, cudaStream_t st);
+int launch_w8a16_fast(lhb_ctx* ctx, const float* A, const int8_t* Bq, const float* Bs, float* C,
+                      int M, int N, int K, float alpha, float beta, cudaStream_t st);
+
+// tcgen05 W8A8 (gemm_w8a8_tc.cu)
+bool w8a8_fast_ok(int M, int N, int K);
+int launch_w8a8_fast(lhb_ctx* ctx, const int8_t* Aq, const int8_t* Bq, const float* as,
+                     const float* bs, float* C, int M, int N, int K, float alpha, float beta,
+                     cudaStream_t st);
+
+// split-KV decode attention (paged_attention_decode.cu)
+bool decode_fast_ok(const lhb_paged_attn_cfg& cfg, const lhb_paged_layout& L);
+int launch_decode_fast(lhb_ctx* ctx, const float* Q, const int8_t* Kp, const int8_t* Vp,
+                       const float* Ks, const float* Vs, const int32_t* tables, int max_blocks,
+                       const int32_t* seq_lens, int n_req, float* O, const lhb_paged_attn_cfg& cfg,
+                       const lhb_paged_layout& L, cudaStream_t st);
+
+// TMA tensor maps (tensor_map.cu): 2-D uint8 tensor [rows, cols] (cols
+// contiguous, row pitch in bytes), box [box_rows, box_cols], 128-byte swizzle
+// when swizzle128 is set.  Cached per context.
+struct TensorMap;
+int get_tensor_map_2d_u8(lhb_ctx* ctx, const void* base, uint64_t rows, uint64_t cols,
+                         uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols,
+                         bool swizzle128, TensorMap* out);
+
+}  // namespace lhb

@@ -1,0 +1,504 @@
+// Skinny weight-only GEMMs (decode GEMV, M <= 16 per launch) for int4-group
+// and int8-per-channel weights in the reference's own layouts:
+//   W4: packed uint8 [K/2, N], byte (k/2, n), low nibble = even k
+//       (src/kernels/quant.hpp:52-57), fp32 scales [K/G, N];
+//   W8: int8 [K, N], fp32 scales [N] (src/kernels/quant.hpp:45-48).
+// Both layouts are N-contiguous, i.e. the reduction axis is the slow axis.
+//
+// The path is HBM-bound: the weight bytes are read exactly once.  To keep the
+// instruction count per weight well under what the memory system can feed,
+// the dot products run on the tensor cores with the weights dequantised in
+// registers:
+//
+//   TMA (2-D, 128-byte swizzle)  global -> shared, 64 rows x 128 columns per
+//       stage, the whole K-chunk of a CTA in flight at once (4-deep ring);
+//   ldmatrix.trans on the raw bytes: one 8x8 b16 matrix = 8 byte-rows x 16
+//       columns; the transposed fragment hands every thread bytes of ONE
+//       column at two consecutive rows, which is exactly the "two adjacent k
+//       of one output column" pairing an m16n8k16 A-fragment register needs;
+//   nibble/byte -> fp16 with mask+xor against 0x6400 (1024 + x) and one
+//       HSUB2/HFMA2, exact for |q| <= 128;
+//   mma.sync m16n8k16 f16 x f16 -> f32 with the weights as the 16-row operand
+//       (16 output columns) and the activations as the 8-column operand.
+//
+// Activations are fp32 in the API.  They are split on the fly into two fp16
+// terms hi + lo (after an exact power-of-two scaling of each row chunk into
+// fp16 range), which occupy two MMA columns per row of A; products and sums
+// stay in fp32, so the result differs from the reference's fp32 loop only by
+// summation order (~1e-6 relative).
+//
+// K is split over a thread-block cluster (1..8 CTAs along K); the partial
+// [M, 128] tiles are reduced in fixed order through distributed shared memory,
+// so the result is deterministic and no global scratch is used.
+#include <cooperative_groups.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+#include "dispatch.h"
+
+namespace cg = cooperative_groups;
+
+namespace lhb {
+
+constexpr int GV_COLS = 128;        // columns per CTA (TMA box inner extent, bytes)
+constexpr int GV_ROWS = 64;         // byte-rows per stage
+constexpr int GV_STAGE_BYTES = GV_COLS * GV_ROWS;
+constexpr int GV_NSTAGE = 4;
+constexpr int GV_CONSUMER_WARPS = 8;
+constexpr int GV_THREADS = (GV_CONSUMER_WARPS + 1) * 32;   // + one producer warp
+constexpr int GV_MAX_CLUSTER = 8;
+
+// ---- PTX wrappers -----------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded wait: gives up after about one second, records LHB_ERR_TIMEOUT in the
+// status word and lets the caller carry on (its results are then garbage, but
+// every barrier of the kernel is still reached and the kernel ends).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status) {
+    for (int i = 0; i < 64; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    while (!mbar_try_wait(bar, parity)) {
+        if (global_timer_ns() - t0 > 1000000000ull) {
+            atomicExch(status, static_cast<int>(LHB_ERR_TIMEOUT));
+            return false;
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int x, int y,
+                                            uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                          uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+
+// Two int4 nibbles (bits 0-3 of each 16-bit half of `w`, two's complement) ->
+// exact fp16 pair: (nib ^ 8) | 0x6400 is the fp16 number 1032 + q.
+__device__ __forceinline__ uint32_t nib_lo_to_h2(uint32_t w) {
+    const uint32_t t = (w & 0x000f000fu) ^ 0x64086408u;
+    return h2_as_u32(__hsub2(u32_as_h2(t), u32_as_h2(0x64086408u)));
+}
+// Nibbles in bits 4-7 of each half: ((w & 0xf0) ^ 0x80) | 0x6400 = 1152 + 16 q;
+// one fused multiply-add (x/16 - 72) gives q exactly.
+__device__ __forceinline__ uint32_t nib_hi_to_h2(uint32_t w) {
+    const uint32_t t = (w & 0x00f000f0u) ^ 0x64806480u;
+    return h2_as_u32(__hfma2(u32_as_h2(t), u32_as_h2(0x2c002c00u) /* 1/16 */,
+                             u32_as_h2(0xd480d480u) /* -72 */));
+}
+// Two int8 values in bytes `sel` of w (already xor 0x80) -> exact fp16 pair:
+// byte | 0x6400 is 1024 + (q + 128).
+template <uint32_t SEL>
+__device__ __forceinline__ uint32_t i8pair_to_h2(uint32_t w_biased) {
+    const uint32_t t = __byte_perm(w_biased, 0x64646464u, SEL);
+    return h2_as_u32(__hsub2(u32_as_h2(t), u32_as_h2(0x64806480u)));
+}
+
+// ---- the kernel ----------------------------------------------------------------
+
+struct GemvParams {
+    const float* A;        // [M, K]
+    const float* scales;   // W4: [K/G, N]   W8: [N]
+    float* C;              // [M, N]
+    int M, N, K, G;        // G unused for W8
+    float alpha, beta;
+    int stages_total;      // ceil(rows / 64)
+    int stages_per_cta;
+    int* status;
+};
+
+// WBITS: 4 or 8.  JB: number of 8-column activation blocks (M <= 4*JB).
+template <int WBITS, int JB>
+__global__ void __launch_bounds__(GV_THREADS, 1)
+gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
+    constexpr int K_PER_ROW = (WBITS == 4) ? 2 : 1;
+    constexpr int K_PER_STAGE = GV_ROWS * K_PER_ROW;
+    constexpr int KB_PER_STAGE = K_PER_STAGE / 16;        // k16 blocks per stage: 8 (W4), 4 (W8)
+    constexpr int NJ = 8 * JB;                            // activation columns (2 per row of A)
+    constexpr int MROWS = 4 * JB;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* tiles = smem;                                             // GV_NSTAGE * 8 KiB
+    float* part = reinterpret_cast<float*>(smem + GV_NSTAGE * GV_STAGE_BYTES);   // [MROWS][128]
+    float* inv_s = part + MROWS * GV_COLS;                             // [MROWS]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(inv_s + 16);          // full[4], empty[4]
+    __half* bfrag = reinterpret_cast<__half*>(bars + 2 * GV_NSTAGE);   // [kb][NJ][4][4]
+
+    cg::cluster_group cluster = cg::this_cluster();
+    const int S = static_cast<int>(cluster.num_blocks());
+    const int ks = static_cast<int>(cluster.block_rank());
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int col0 = blockIdx.x * GV_COLS;
+
+    const int stage_begin = min(ks * p.stages_per_cta, p.stages_total);
+    const int stage_end = min(stage_begin + p.stages_per_cta, p.stages_total);
+    const int n_stages = stage_end - stage_begin;
+    const int k_begin = stage_begin * K_PER_STAGE;
+    const int k_count = n_stages * K_PER_STAGE;            // multiple of 16; may run past K
+
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + GV_NSTAGE);
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < GV_NSTAGE; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, GV_CONSUMER_WARPS);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    // Producer: put the first GV_NSTAGE stages in flight before anything else.
+    if (warp == GV_CONSUMER_WARPS && lane == 0) {
+        const int first = min(n_stages, GV_NSTAGE);
+        for (int s = 0; s < first; ++s) {
+            mbar_expect_tx(full0 + 8 * s, GV_STAGE_BYTES);
+            tma_load_2d(smem_u32(tiles + s * GV_STAGE_BYTES), &tmB, col0, (stage_begin + s) * GV_ROWS,
+                        full0 + 8 * s);
+        }
+    }
+
+    // Activation prologue (all warps, overlapped with the loads in flight):
+    // row m of this CTA's K-chunk -> scale by a power of two into fp16 range,
+    // split into hi + lo, store in B-fragment order.
+    for (int m = warp; m < MROWS; m += GV_THREADS / 32) {
+        const bool live = m < p.M;
+        const float* a = p.A + static_cast<int64_t>(m) * p.K + k_begin;
+        float mx = 0.0f;
+        if (live)
+            for (int k = lane; k < k_count; k += 32)
+                if (k_begin + k < p.K) mx = fmaxf(mx, fabsf(a[k]));
+        mx = warp_max(mx);
+        // power-of-two factor taking max|a| into [2^13, 2^14); exponent clamped
+        int e = static_cast<int>((__float_as_uint(mx) >> 23) & 0xff);
+        int se = (mx > 0.0f) ? 267 - e : 127;
+        se = max(1, min(253, se));
+        const float s = __uint_as_float(static_cast<uint32_t>(se) << 23);
+        if (lane == 0) inv_s[m] = __uint_as_float(static_cast<uint32_t>(254 - se) << 23);
+        for (int k = lane; k < k_count; k += 32) {
+            float v = 0.0f;
+            if (live && k_begin + k < p.K) v = a[k] * s;
+            const __half hi = __float2half_rn(v);
+            const __half lo = __float2half_rn(v - __half2float(hi));
+            const int kb = k >> 4, kin = k & 15;
+            int t, e4;
+            if (WBITS == 4) {            // thread t holds k0+4t+{0,2,1,3}
+                t = kin >> 2;
+                const int r = kin & 3;
+                e4 = ((r & 1) << 1) | (r >> 1);
+            } else {                     // thread t holds k0+{2t, 2t+1, 8+2t, 9+2t}
+                t = (kin & 7) >> 1;
+                e4 = ((kin >> 3) << 1) | (kin & 1);
+            }
+            const int base = ((kb * NJ + 2 * m) * 4 + t) * 4 + e4;
+            bfrag[base] = hi;
+            bfrag[base + 16] = lo;       // column 2m+1
+        }
+    }
+    __syncthreads();
+
+    float out[JB][4];
+#pragma unroll
+    for (int jb = 0; jb < JB; ++jb)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) out[jb][i] = 0.0f;
+
+    if (warp < GV_CONSUMER_WARPS) {
+        const int g = lane >> 2, t = lane & 3;
+        const int n_a = col0 + warp * 16 + 2 * g;           // this thread's two output columns
+        float acc[JB][4];
+#pragma unroll
+        for (int jb = 0; jb < JB; ++jb)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[jb][i] = 0.0f;
+        const int kb_per_group = (WBITS == 4) ? p.G / 16 : 0x7fffffff;
+        int kb_in_group = (WBITS == 4) ? (k_begin / 16) % kb_per_group : 0;
+        // ldmatrix row address: matrix (lane / 8), row (lane % 8); 16-byte chunk = warp, swizzled
+        const int lrow = lane & 7, lmat = lane >> 3;
+        // end of a quantisation group (or of this CTA's chunk): fold the scale
+        // of the group that k16-block `kb` belongs to into the running output
+        auto flush_group = [&](int kb) {
+            float s0 = 0.0f, s1 = 0.0f;
+            const int k = k_begin + kb * 16;
+            if (k < p.K) {
+                const float* sp = p.scales + static_cast<int64_t>(k / p.G) * p.N + n_a;
+                if (n_a < p.N) s0 = sp[0];
+                if (n_a + 1 < p.N) s1 = sp[1];
+            }
+#pragma unroll
+            for (int jb = 0; jb < JB; ++jb) {
+                out[jb][0] = fmaf(s0, acc[jb][0], out[jb][0]);
+                out[jb][1] = fmaf(s0, acc[jb][1], out[jb][1]);
+                out[jb][2] = fmaf(s1, acc[jb][2], out[jb][2]);
+                out[jb][3] = fmaf(s1, acc[jb][3], out[jb][3]);
+                acc[jb][0] = acc[jb][1] = acc[jb][2] = acc[jb][3] = 0.0f;
+            }
+        };
+
+        for (int ls = 0; ls < n_stages; ++ls) {
+            const int slot = ls % GV_NSTAGE;
+            mbar_wait(full0 + 8 * slot, (ls / GV_NSTAGE) & 1, p.status);
+            const uint32_t tile = smem_u32(tiles + slot * GV_STAGE_BYTES);
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                uint32_t x[4];
+                const int row = half * 32 + lmat * 8 + lrow;
+                ldmatrix_x4_trans(tile + row * 128 + ((warp ^ (row & 7)) << 4), x);
+                if (half == 1) {           // stage fully read by this warp
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(empty0 + 8 * slot);
+                }
+                if (WBITS == 4) {
+#pragma unroll
+                    for (int mat = 0; mat < 4; ++mat) {
+                        const int kb = ls * KB_PER_STAGE + half * 4 + mat;
+                        const uint32_t a0 = nib_lo_to_h2(x[mat]);
+                        const uint32_t a2 = nib_hi_to_h2(x[mat]);
+                        const uint32_t a1 = nib_lo_to_h2(x[mat] >> 8);
+                        const uint32_t a3 = nib_hi_to_h2(x[mat] >> 8);
+#pragma unroll
+                        for (int jb = 0; jb < JB; ++jb) {
+                            const uint2 b = *reinterpret_cast<const uint2*>(
+                                bfrag + ((kb * NJ + jb * 8 + g) * 4 + t) * 4);
+                            mma_16816(acc[jb], a0, a1, a2, a3, b.x, b.y);
+                        }
+                        if (++kb_in_group == kb_per_group) {
+                            kb_in_group = 0;
+                            flush_group(kb);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int pr = 0; pr < 2; ++pr) {
+                        const int kb = ls * KB_PER_STAGE + half * 2 + pr;
+                        const uint32_t w0 = x[2 * pr] ^ 0x80808080u;
+                        const uint32_t w1 = x[2 * pr + 1] ^ 0x80808080u;
+                        const uint32_t a0 = i8pair_to_h2<0x4240>(w0);
+                        const uint32_t a1 = i8pair_to_h2<0x4341>(w0);
+                        const uint32_t a2 = i8pair_to_h2<0x4240>(w1);
+                        const uint32_t a3 = i8pair_to_h2<0x4341>(w1);
+#pragma unroll
+                        for (int jb = 0; jb < JB; ++jb) {
+                            const uint2 b = *reinterpret_cast<const uint2*>(
+                                bfrag + ((kb * NJ + jb * 8 + g) * 4 + t) * 4);
+                            mma_16816(acc[jb], a0, a1, a2, a3, b.x, b.y);
+                        }
+                    }
+                }
+            }
+        }
+        if (WBITS == 4 && kb_in_group != 0 && n_stages > 0) flush_group(n_stages * KB_PER_STAGE - 1);
+        if (WBITS == 8) {
+            float s0 = 0.0f, s1 = 0.0f;
+            if (n_a < p.N) s0 = p.scales[n_a];
+            if (n_a + 1 < p.N) s1 = p.scales[n_a + 1];
+#pragma unroll
+            for (int jb = 0; jb < JB; ++jb) {
+                out[jb][0] = s0 * acc[jb][0]; out[jb][1] = s0 * acc[jb][1];
+                out[jb][2] = s1 * acc[jb][2]; out[jb][3] = s1 * acc[jb][3];
+            }
+        }
+        // hi + lo columns of row m = 4*jb + t, undo the activation scaling
+#pragma unroll
+        for (int jb = 0; jb < JB; ++jb) {
+            const int m = 4 * jb + t;
+            const float is = inv_s[m];
+            float2 v;
+            v.x = is * (out[jb][0] + out[jb][1]);
+            v.y = is * (out[jb][2] + out[jb][3]);
+            *reinterpret_cast<float2*>(part + m * GV_COLS + warp * 16 + 2 * g) = v;
+        }
+    } else if (lane == 0) {
+        // producer: refill ring slots as the consumers release them
+        for (int ls = GV_NSTAGE; ls < n_stages; ++ls) {
+            const int slot = ls % GV_NSTAGE;
+            mbar_wait(empty0 + 8 * slot, ((ls / GV_NSTAGE) - 1) & 1, p.status);
+            mbar_expect_tx(full0 + 8 * slot, GV_STAGE_BYTES);
+            tma_load_2d(smem_u32(tiles + slot * GV_STAGE_BYTES), &tmB, col0,
+                        (stage_begin + ls) * GV_ROWS, full0 + 8 * slot);
+        }
+    }
+
+    // Cluster reduction over the K split, fixed order, through distributed
+    // shared memory.  CTA `ks` finishes columns [ks*128/S, (ks+1)*128/S).
+    cluster.sync();
+    const int cols_per = GV_COLS / S;
+    for (int i = threadIdx.x; i < p.M * cols_per; i += GV_THREADS) {
+        const int m = i / cols_per, c = ks * cols_per + i % cols_per;
+        const int n = col0 + c;
+        if (n >= p.N) continue;
+        float sum = 0.0f;
+        for (int r = 0; r < S; ++r) {
+            const float* rp = cluster.map_shared_rank(part, r);
+            sum += rp[m * GV_COLS + c];
+        }
+        float* cp = p.C + static_cast<int64_t>(m) * p.N + n;
+        *cp = (p.beta == 0.0f) ? p.alpha * sum : fmaf(p.beta, *cp, p.alpha * sum);
+    }
+    cluster.sync();   // keep every CTA's shared memory alive until all peers have read it
+}
+
+// ---- host side --------------------------------------------------------------------
+
+static size_t gemv_smem_bytes(int jb, int k_per_cta) {
+    const size_t nj = 8 * jb, mrows = 4 * jb;
+    return 1024 + GV_NSTAGE * GV_STAGE_BYTES + mrows * GV_COLS * 4 + 16 * 4 + 2 * GV_NSTAGE * 8 +
+           static_cast<size_t>(k_per_cta) * nj * 2;
+}
+
+struct GemvPlan { int cluster; int stages_total; int stages_per_cta; size_t smem; bool ok; };
+
+// Pick the K split: as many cluster CTAs (power of two, <= 8) as needed to
+// put >= ~4 CTAs on every SM, without making a CTA's chunk shorter than one
+// stage, and subject to the shared-memory budget.
+static GemvPlan plan_gemv(int wbits, int jb, int N, int K, int sm_count) {
+    GemvPlan pl{};
+    const int k_per_stage = GV_ROWS * (wbits == 4 ? 2 : 1);
+    pl.stages_total = ceil_div(K, k_per_stage);
+    const int col_tiles = ceil_div(N, GV_COLS);
+    int S = 1;
+    while (S < GV_MAX_CLUSTER && col_tiles * S < 4 * sm_count && pl.stages_total >= 2 * S) S *= 2;
+    for (;; S *= 2) {
+        pl.cluster = S;
+        pl.stages_per_cta = ceil_div(pl.stages_total, S);
+        pl.smem = gemv_smem_bytes(jb, pl.stages_per_cta * k_per_stage);
+        if (pl.smem <= 200 * 1024) { pl.ok = true; return pl; }
+        if (S >= GV_MAX_CLUSTER) { pl.ok = false; return pl; }
+    }
+}
+
+static int jb_for(int M) { return M <= 4 ? 1 : (M <= 8 ? 2 : 4); }
+
+bool w4a16_fast_ok(int M, int N, int K, int G) {
+    if (M < 1 || (N % 16) != 0 || (K % 16) != 0 || (G % 16) != 0 || (K % G) != 0) return false;
+    if (M > 64) return false;                     // larger M: generic path (dense GEMM territory)
+    return plan_gemv(4, jb_for(M > 16 ? 16 : M), N, K, 148).ok;
+}
+
+bool w8a16_fast_ok(int M, int N, int K) {
+    if (M < 1 || (N % 16) != 0 || (K % 16) != 0) return false;
+    if (M > 64) return false;
+    return plan_gemv(8, jb_for(M > 16 ? 16 : M), N, K, 148).ok;
+}
+
+template <int WBITS, int JB>
+static int launch_gemv_t(lhb_ctx* ctx, const TensorMap& tm, GemvParams p, const GemvPlan& pl,
+                         cudaStream_t st) {
+    auto kern = gemv_mma_kernel<WBITS, JB>;
+    static bool attr_set[64] = {};                // per instantiation and device
+    if (!attr_set[ctx->device & 63]) {
+        LHB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        attr_set[ctx->device & 63] = true;
+    }
+    p.stages_total = pl.stages_total;
+    p.stages_per_cta = pl.stages_per_cta;
+    p.status = ctx->status_word;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ceil_div(p.N, GV_COLS), pl.cluster, 1);
+    cfg.blockDim = dim3(GV_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = pl.smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = pl.cluster;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    LHB_CUDA(cudaLaunchKernelEx(&cfg, kern, tm, p));
+    return LHB_OK;
+}
+
+template <int WBITS>
+static int launch_gemv(lhb_ctx* ctx, const float* A, const void* B, const float* scales, float* C,
+                       int M, int N, int K, int G, float alpha, float beta, cudaStream_t st) {
+    const uint64_t rows = (WBITS == 4) ? K / 2 : K;
+    TensorMap tm;
+    if (int e = get_tensor_map_2d_u8(ctx, B, rows, N, N, GV_ROWS, GV_COLS, true, &tm)) return e;
+    // rows of A are independent: M > 16 is served in slabs of 16 rows
+    for (int m0 = 0; m0 < M; m0 += 16) {
+        const int m = std::min(16, M - m0);
+        const int jb = jb_for(m);
+        const GemvPlan pl = plan_gemv(WBITS, jb, N, K, ctx->sm_count);
+        if (!pl.ok) return LHB_ERR_UNSUPPORTED;
+        GemvParams p{};
+        p.A = A + static_cast<int64_t>(m0) * K;
+        p.scales = scales;
+        p.C = C + static_cast<int64_t>(m0) * N;
+        p.M = m; p.N = N; p.K = K; p.G = G; p.alpha = alpha; p.beta = beta;
+        int e;
+        if (jb == 1) e = launch_gemv_t<WBITS, 1>(ctx, tm, p, pl, st);
+        else if (jb == 2) e = launch_gemv_t<WBITS, 2>(ctx, tm, p, pl, st);
+        else e = launch_gemv_t<WBITS, 4>(ctx, tm, p, pl, st);
+        if (e) return e;
+    }
+    return LHB_OK;
+}
+
+int launch_w4a16_fast(lhb_ctx* ctx, const float* A, const uint8_t* Bp, const float* Bs, float* C,
+                      int M, int N, int K, int G, float alpha, float beta, cudaStream_t st) {
+    return launch_gemv<4>(ctx, A, Bp, Bs, C, M, N, K, G, alpha, beta, st);
+}
+
+int launch_w8a16_fast(lhb_ctx* ctx, const float* A, const int8_t* Bq, const float* Bs, float* C,
+                      int M, int N, int K, float alpha, float beta, cudaStream_t st) {
+    return launch_gemv<8>(ctx, A, Bq, Bs, C, M, N, K, 0, alpha, beta, st);
+}
+
+}  // namespace lhb

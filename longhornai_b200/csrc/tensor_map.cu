@@ -1,0 +1,72 @@
+// TMA tensor-map construction.  cuTensorMapEncodeTiled is resolved at run time
+// through the CUDA runtime's driver entry-point query, so the library carries
+// no link-time dependency on libcuda and still loads on a machine without a
+// driver (where every compute call reports LHB_ERR_CUDA).
+#include <cuda.h>
+
+#include <cstring>
+#include <string>
+
+#include "common.cuh"
+#include "dispatch.h"
+
+namespace lhb {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn resolve_encode() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+        else
+            cudaGetLastError();
+    });
+    return fn;
+}
+
+static_assert(sizeof(TensorMap) == sizeof(CUtensorMap), "tensor map blob size");
+
+int get_tensor_map_2d_u8(lhb_ctx* ctx, const void* base, uint64_t rows, uint64_t cols,
+                         uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols,
+                         bool swizzle128, TensorMap* out) {
+    char key[160];
+    snprintf(key, sizeof(key), "%p/%llu/%llu/%llu/%u/%u/%d", base, (unsigned long long)rows,
+             (unsigned long long)cols, (unsigned long long)pitch_bytes, box_rows, box_cols,
+             swizzle128 ? 1 : 0);
+    {
+        std::lock_guard<std::mutex> lk(ctx->mu);
+        auto it = ctx->tmaps.find(key);
+        if (it != ctx->tmaps.end()) { *out = it->second; return LHB_OK; }
+    }
+    EncodeTiledFn enc = resolve_encode();
+    if (!enc) { set_last_error_text("cuTensorMapEncodeTiled unavailable"); return LHB_ERR_CUDA; }
+    if ((reinterpret_cast<uintptr_t>(base) & 15) || (pitch_bytes & 15)) return LHB_ERR_MISALIGNED;
+    CUtensorMap tm;
+    const cuuint64_t gdim[2] = {cols, rows};
+    const cuuint64_t gstride[1] = {pitch_bytes};
+    const cuuint32_t box[2] = {box_cols, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), gdim,
+                           gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_last_error_text("cuTensorMapEncodeTiled failed with CUresult " + std::to_string((int)r));
+        return LHB_ERR_CUDA;
+    }
+    memcpy(out->bytes, &tm, sizeof(tm));
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    if (ctx->tmaps.size() > 4096) ctx->tmaps.clear();
+    ctx->tmaps[key] = *out;
+    return LHB_OK;
+}
+
+}  // namespace lhb

@@ -1,0 +1,360 @@
+"""GPU parity: the CUDA path, called through the C ABI, against
+  (1) the committed golden fixtures (outputs of the reference's compiled code),
+  (2) the CPU checker on seeded inputs, up to the full benchmark shapes,
+  (3) size-independent properties (linearity, shard composition, round trips).
+Integer outputs and scales must be bit-identical; fp32 outputs must satisfy
+|x - y| <= 1e-4 + 1e-3 |y| (the library tolerance)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import golden_io as gio
+import longhornai_b200 as lb
+from cpu_checker import AttnCfg, Layout, PagedPools, best_checker
+from gpu_util import assert_close, assert_same_bits, dev, host, lb_cfg, lb_layout
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def chk():
+    return best_checker()
+
+
+@pytest.fixture(scope="module")
+def lib():
+    return lb._cabi.load()
+
+
+def poll_ok():
+    assert lb.default_context().poll() == 0
+
+
+# --------------------------------------------------------------------------- quantisers
+
+def test_q8_per_row_golden_bits():
+    g = gio.load("q8_per_row")
+    q, s = lb.q8_quantize_per_row(dev(g["x"]))
+    assert_same_bits(host(q), g["q"], "q"); assert_same_bits(host(s), g["s"], "scales")
+    assert_same_bits(host(lb.q8_dequantize_per_row(q, s)), g["d"], "dequant")
+
+
+def test_q8_per_col_golden_bits():
+    g = gio.load("q8_per_col")
+    q, s = lb.q8_quantize_per_col(dev(g["x"]))
+    assert_same_bits(host(q), g["q"], "q"); assert_same_bits(host(s), g["s"], "scales")
+    assert_same_bits(host(lb.q8_dequantize_per_col(q, s)), g["d"], "dequant")
+
+
+@pytest.mark.parametrize("name", gio.names("q4_"))
+def test_q4_groupwise_golden_bits(name):
+    g = gio.load(name)
+    G = int(g["G"])
+    p, s = lb.q4_quantize_groupwise(dev(g["w"]), G)
+    assert_same_bits(host(p), g["p"], "packed"); assert_same_bits(host(s), g["s"], "scales")
+    assert_same_bits(host(lb.q4_dequantize_groupwise(p, s, G)), g["d"], "dequant")
+
+
+def test_quantisers_bit_exact_on_seeded_matrices(chk):
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal((300, 1000)).astype(np.float32)
+    x[17] = 0.0
+    x[:, 33] = 0.0
+    q, s = lb.q8_quantize_per_row(dev(x)); q0, s0 = chk.q8_quantize_per_row(x)
+    assert_same_bits(host(q), q0, "row q"); assert_same_bits(host(s), s0, "row s")
+    q, s = lb.q8_quantize_per_col(dev(x)); q0, s0 = chk.q8_quantize_per_col(x)
+    assert_same_bits(host(q), q0, "col q"); assert_same_bits(host(s), s0, "col s")
+    w = (rng.standard_normal((512, 1000)) * 0.02).astype(np.float32)
+    for G in (32, 128):
+        p, s = lb.q4_quantize_groupwise(dev(w), G); p0, s0 = chk.q4_quantize_groupwise(w, G)
+        assert_same_bits(host(p), p0, f"q4 packed G={G}"); assert_same_bits(host(s), s0, f"q4 scales G={G}")
+    poll_ok()
+
+
+# --------------------------------------------------------------------------- W8A8
+
+def test_w8a8_golden_bits():
+    g = gio.load("w8a8_m32n48k64")
+    C_ = lb.gemm_w8a8(dev(g["Aq"]), dev(g["Bq"]), dev(g["a_s"]), dev(g["b_s"]))
+    assert_same_bits(host(C_), g["C"], "w8a8 beta=0")
+    g = gio.load("w8a8_beta")
+    C_ = lb.gemm_w8a8(dev(g["Aq"]), dev(g["Bq"]), dev(g["a_s"]), dev(g["b_s"]), C=dev(g["C0"]),
+                      alpha=0.5, beta=2.0)
+    assert_same_bits(host(C_), g["C"], "w8a8 alpha/beta")
+
+
+@pytest.mark.parametrize("M,N,K", [(8, 96, 200), (128, 256, 512), (300, 1040, 768), (256, 2048, 1024)])
+def test_w8a8_bit_exact_against_checker(chk, lib, M, N, K):
+    rng = np.random.default_rng(M + N + K)
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    W = (rng.standard_normal((K, N)) * 0.02).astype(np.float32)
+    Aq, a_s = chk.q8_quantize_per_row(A)
+    Bq, b_s = chk.q8_quantize_per_col(W)
+    want = chk.gemm_w8a8(Aq, Bq, a_s, b_s, alpha=1.25)
+    got = lb.gemm_w8a8(dev(Aq), dev(Bq), dev(a_s), dev(b_s), alpha=1.25)
+    assert_same_bits(host(got), want, f"w8a8 {M}x{N}x{K} fast={lib.lhb_gemm_w8a8_fast_path(M, N, K)}")
+    C0 = rng.standard_normal((M, N)).astype(np.float32)
+    want = chk.gemm_w8a8(Aq, Bq, a_s, b_s, C0, alpha=0.5, beta=2.0)
+    got = lb.gemm_w8a8(dev(Aq), dev(Bq), dev(a_s), dev(b_s), C=dev(C0), alpha=0.5, beta=2.0)
+    assert_same_bits(host(got), want, "w8a8 alpha/beta")
+    poll_ok()
+
+
+# --------------------------------------------------------------------------- W4A16
+
+@pytest.mark.parametrize("name", gio.names("w4a16_"))
+def test_w4a16_golden(name):
+    g = gio.load(name)
+    G = int(g["G"])
+    A, p, s = dev(g["A"]), dev(g["p"]), dev(g["s"])
+    assert_close(host(lb.gemm_w4a16_groupwise(A, p, s, G)), g["C"], what=name)
+    got = lb.gemm_w4a16_groupwise(A, p, s, G, C=dev(g["C0"]), alpha=0.5, beta=2.0)
+    assert_close(host(got), g["C_ab"], what=name + " alpha/beta")
+    poll_ok()
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 5, 8, 13, 16, 17, 32, 40])
+@pytest.mark.parametrize("N,K,G", [(1040, 1024, 128), (256, 384, 64), (4096, 2048, 32)])
+def test_w4a16_against_checker(chk, lib, M, N, K, G):
+    rng = np.random.default_rng(1000 * M + N + K + G)
+    A = (rng.standard_normal((M, K)) * rng.choice([1e-3, 1.0, 300.0])).astype(np.float32)
+    W = (rng.standard_normal((K, N)) * 0.02).astype(np.float32)
+    p, s = chk.q4_quantize_groupwise(W, G)
+    want = chk.gemm_w4a16_groupwise(A, p, s, G)
+    got = lb.gemm_w4a16_groupwise(dev(A), dev(p), dev(s), G)
+    # tolerance scaled by the magnitude of the activations (the absolute term of
+    # the library tolerance is stated for unit-variance activations)
+    scale = max(1.0, float(np.abs(A).max()))
+    assert_close(host(got) / scale, want / scale,
+                 what=f"w4a16 M={M} N={N} K={K} G={G} fast={lib.lhb_gemm_w4a16_fast_path(M, N, K, G)}")
+    poll_ok()
+
+
+def test_w4a16_full_shape_cfg2(chk, lib):
+    """Llama-3-8B up-projection shape, M = 1, 8, 32; bf16-stored activations."""
+    K, N, G = 4096, 14336, 128
+    rng = np.random.default_rng(20242)
+    W = (rng.standard_normal((K, N)) * 0.02).astype(np.float32)
+    p, s = lb.q4_quantize_groupwise(dev(W), G)
+    p0, s0 = chk.q4_quantize_groupwise(W, G)
+    assert_same_bits(host(p), p0, "packed"); assert_same_bits(host(s), s0, "scales")
+    for M in (1, 8, 32):
+        assert lib.lhb_gemm_w4a16_fast_path(M, N, K, G) == 1
+        A = chk.round_to_bf16(rng.standard_normal((M, K)).astype(np.float32))
+        got = host(lb.gemm_w4a16_groupwise(dev(A), p, s, G))
+        assert_close(got, chk.gemm_w4a16_groupwise(A, p0, s0, G), what=f"cfg2 M={M}")
+        # N-shard composition: two compact column shards give the same columns
+        h = N // 2
+        left = lb.gemm_w4a16_groupwise(dev(A), p[:, :h].contiguous(), s[:, :h].contiguous(), G)
+        assert_close(host(left), got[:, :h], rtol=1e-5, atol=1e-6, what="shard composition")
+    poll_ok()
+
+
+def test_w4a16_linearity_and_determinism():
+    K, N, G = 2048, 2048, 128
+    g = torch.Generator(device="cuda").manual_seed(5)
+    W = torch.randn(K, N, device="cuda", generator=g) * 0.02
+    p, s = lb.q4_quantize_groupwise(W, G)
+    a = torch.randn(4, K, device="cuda", generator=g)
+    b = torch.randn(4, K, device="cuda", generator=g)
+    ya, yb = lb.gemm_w4a16_groupwise(a, p, s, G), lb.gemm_w4a16_groupwise(b, p, s, G)
+    yab = lb.gemm_w4a16_groupwise(a + b, p, s, G)
+    assert_close(host(yab), host(ya + yb), what="linearity")
+    assert torch.equal(ya, lb.gemm_w4a16_groupwise(a, p, s, G)), "run-to-run determinism"
+    # against the dequantised weights in fp64
+    ref = (a.double() @ lb.q4_dequantize_groupwise(p, s, G).double()).float()
+    assert_close(host(ya), host(ref), what="dequant + fp64 matmul")
+    poll_ok()
+
+
+# --------------------------------------------------------------------------- W8A16
+
+def test_w8a16_golden():
+    g = gio.load("w8a16_m16n64k128")
+    got = lb.gemm_w8a16_perchannel(dev(g["A"]), dev(g["Bq"]), dev(g["b_s"]))
+    assert_close(host(got), g["C"], what="w8a16 golden")
+
+
+@pytest.mark.parametrize("M,N,K", [(16, 4096, 4096), (1, 1040, 1024), (7, 33, 100), (40, 512, 768)])
+def test_w8a16_against_checker(chk, lib, M, N, K):
+    rng = np.random.default_rng(M * 7 + N + K)
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    W = (rng.standard_normal((K, N)) * 0.02).astype(np.float32)
+    q, s = lb.q8_quantize_per_col(dev(W))
+    q0, s0 = chk.q8_quantize_per_col(W)
+    assert_same_bits(host(q), q0, "q"); assert_same_bits(host(s), s0, "s")
+    got = lb.gemm_w8a16_perchannel(dev(A), q, s)
+    assert_close(host(got), chk.gemm_w8a16_perchannel(A, q0, s0),
+                 what=f"w8a16 {M}x{N}x{K} fast={lib.lhb_gemm_w8a16_fast_path(M, N, K)}")
+    C0 = rng.standard_normal((M, N)).astype(np.float32)
+    got = lb.gemm_w8a16_perchannel(dev(A), q, s, C=dev(C0), alpha=0.5, beta=2.0)
+    assert_close(host(got), chk.gemm_w8a16_perchannel(A, q0, s0, C0, alpha=0.5, beta=2.0), what="alpha/beta")
+    poll_ok()
+
+
+# --------------------------------------------------------------------------- append
+
+def test_append_q8_golden_bits():
+    g = gio.load("append_q8")
+    L = Layout(*[int(v) for v in g["layout"]])
+    shp = (L.num_blocks, L.n_kv_heads, L.block_size, L.head_dim)
+    k = torch.zeros(shp, dtype=torch.int8, device="cuda"); v = torch.zeros_like(k)
+    ks = torch.zeros(shp[:3], device="cuda"); vs = torch.zeros_like(ks)
+    table = dev(g["table"])
+    kn, vn = g["k_new"], g["v_new"]
+    lb.paged_kv_append_q8(k, v, ks, vs, dev(kn[:, :5]), dev(vn[:, :5]), table, lb_layout(L), 0, 5)
+    lb.paged_kv_append_q8(k, v, ks, vs, dev(kn[:, 5:]), dev(vn[:, 5:]), table, lb_layout(L), 5, 4)
+    assert_same_bits(host(k), g["k"], "k pool"); assert_same_bits(host(v), g["v"], "v pool")
+    assert_same_bits(host(ks), g["ks"], "k scales"); assert_same_bits(host(vs), g["vs"], "v scales")
+
+
+# --------------------------------------------------------------------------- attention
+
+@pytest.mark.parametrize("name", gio.names("attn_"))
+def test_attention_golden(name, lib):
+    g = gio.load(name)
+    L, cfg = gio.attn_structs(g)
+    got = lb.paged_attention_q8_batched(dev(g["Q"]), dev(g["k"]), dev(g["v"]), dev(g["ks"]),
+                                        dev(g["vs"]), dev(g["tables"]), dev(g["seq_lens"]),
+                                        lb_cfg(cfg), lb_layout(L))
+    fast = lib.lhb_paged_attention_q8_fast_path(C.byref(lb_cfg(cfg)), C.byref(lb_layout(L)))
+    assert_close(host(got), g["O"], what=f"{name} (fast={fast})")
+    # single-request entry point, request by request
+    for r in range(g["Q"].shape[0]):
+        o = lb.paged_attention_q8(dev(g["Q"][r]), dev(g["k"]), dev(g["v"]), dev(g["ks"]), dev(g["vs"]),
+                                  dev(g["tables"][r]), int(g["seq_lens"][r]), lb_cfg(cfg), lb_layout(L))
+        assert_close(host(o), g["O"][r], what=f"{name} request {r}")
+    gotf = lb.paged_attention_batched_f32(dev(g["Q"]), dev(g["kf"]), dev(g["vf"]), dev(g["tables"]),
+                                          dev(g["seq_lens"]), lb_cfg(cfg), lb_layout(L))
+    assert_close(host(gotf), g["O_f32"], what=name + " fp32 pools")
+    poll_ok()
+
+
+def build_paged_case(chk, rng, n_req, lens, qh, kvh, d, bs, nblk, batched_append=True):
+    """Fill int8 pools on the GPU (library append) and on the CPU (checker) from the same rows."""
+    L = Layout(nblk, bs, kvh, d)
+    max_blocks = max(1, max((l + bs - 1) // bs for l in lens))
+    perm = rng.permutation(nblk).astype(np.int32)
+    tables = np.full((n_req, max_blocks), -1, np.int32)
+    used = 0
+    for r, l in enumerate(lens):
+        nb = (l + bs - 1) // bs
+        tables[r, :nb] = perm[used:used + nb]; used += nb
+    assert used <= nblk
+    pools = chk.empty_pools_q8(L)
+    shp = (nblk, kvh, bs, d)
+    k = torch.zeros(shp, dtype=torch.int8, device="cuda"); v = torch.zeros_like(k)
+    ks = torch.zeros(shp[:3], device="cuda"); vs = torch.zeros_like(ks)
+    tables_d = dev(tables)
+    offs, kn_all, vn_all = [], [], []
+    off = 0
+    for r, l in enumerate(lens):
+        kn = rng.standard_normal((kvh, l, d)).astype(np.float32)
+        vn = rng.standard_normal((kvh, l, d)).astype(np.float32)
+        offs.append(off); off += kn.size
+        kn_all.append(kn.ravel()); vn_all.append(vn.ravel())
+        if l:
+            lb.paged_kv_append_q8(k, v, ks, vs, dev(kn), dev(vn), tables_d[r], lb_layout(L), 0, l)
+    kn_all = np.concatenate(kn_all) if off else np.zeros(1, np.float32)
+    vn_all = np.concatenate(vn_all) if off else np.zeros(1, np.float32)
+    chk.paged_kv_append_q8_batched(pools, kn_all, vn_all, np.array(offs, np.int64), tables,
+                                   np.zeros(n_req, np.int32), np.array(lens, np.int32), L)
+    return L, tables, pools, (k, v, ks, vs)
+
+
+@pytest.mark.parametrize("lens", [[513, 16, 1, 257, 4096, 33], [100] * 8, [0, 5, 0]])
+def test_decode_attention_against_checker(chk, lib, lens):
+    rng = np.random.default_rng(sum(lens) + len(lens))
+    qh, kvh, d, bs = 32, 8, 128, 16
+    nblk = sum((l + bs - 1) // bs for l in lens) + 7
+    L, tables, pools, (k, v, ks, vs) = build_paged_case(chk, rng, len(lens), lens, qh, kvh, d, bs, nblk)
+    assert_same_bits(host(k), pools.k, "k pool"); assert_same_bits(host(vs), pools.vs, "v scales")
+    cfg = AttnCfg(qh, kvh, 1, d, 1, 0.0, 0, 0)
+    Q = rng.standard_normal((len(lens), qh, 1, d)).astype(np.float32)
+    sl = np.array(lens, np.int32)
+    want = chk.paged_attention_q8_batched(Q, pools, tables, sl, cfg, L, parallel=True)
+    got = lb.paged_attention_q8_batched(dev(Q), k, v, ks, vs, dev(tables), dev(sl), lb_cfg(cfg), lb_layout(L))
+    fast = lib.lhb_paged_attention_q8_fast_path(C.byref(lb_cfg(cfg)), C.byref(lb_layout(L)))
+    assert_close(host(got), want, what=f"decode lens={lens} fast={fast}")
+    poll_ok()
+
+
+def test_decode_step_append_then_attend(chk):
+    """One decode step for a batch: batched append of one token per request at
+    positions taken from the device seq_lens, then attention over len+1 keys."""
+    rng = np.random.default_rng(77)
+    qh, kvh, d, bs = 8, 2, 128, 16
+    lens = [31, 16, 47, 1]
+    nblk = 24
+    L, tables, pools, (k, v, ks, vs) = build_paged_case(chk, rng, len(lens), [l + 1 for l in lens], qh, kvh, d, bs, nblk)
+    # overwrite the last token of every request through the batched append
+    kn = rng.standard_normal((len(lens), kvh, 1, d)).astype(np.float32)
+    vn = rng.standard_normal((len(lens), kvh, 1, d)).astype(np.float32)
+    past = np.array(lens, np.int32)
+    lb.paged_kv_append_q8_batched(k, v, ks, vs, dev(kn), dev(vn), dev(tables), dev(past), lb_layout(L), 1)
+    for r, l in enumerate(lens):
+        chk.paged_kv_append_q8(pools, kn[r].copy(), vn[r].copy(), tables[r], L, l, 1)
+    assert_same_bits(host(k), pools.k, "k after decode append"); assert_same_bits(host(ks), pools.ks, "ks")
+    cfg = AttnCfg(qh, kvh, 1, d, 1, 0.0, 0, 0)
+    Q = rng.standard_normal((len(lens), qh, 1, d)).astype(np.float32)
+    sl = past + 1
+    want = chk.paged_attention_q8_batched(Q, pools, tables, sl, cfg, L)
+    got = lb.paged_attention_q8_batched(dev(Q), k, v, ks, vs, dev(tables), dev(sl), lb_cfg(cfg), lb_layout(L))
+    assert_close(host(got), want, what="decode step")
+    poll_ok()
+
+
+def test_attention_ignores_table_padding_and_is_deterministic(chk):
+    rng = np.random.default_rng(3)
+    lens = [300, 40]
+    L, tables, pools, (k, v, ks, vs) = build_paged_case(chk, rng, 2, lens, 8, 2, 128, 16, 40)
+    cfg = lb_cfg(AttnCfg(8, 2, 1, 128, 1, 0.0, 0, 0))
+    Q = dev(rng.standard_normal((2, 8, 1, 128)).astype(np.float32))
+    sl = dev(np.array(lens, np.int32))
+    a = lb.paged_attention_q8_batched(Q, k, v, ks, vs, dev(tables), sl, cfg, lb_layout(L))
+    t2 = tables.copy(); t2[t2 < 0] = 12345678      # padding must never be dereferenced
+    wide = np.full((2, tables.shape[1] + 9), -1, np.int32); wide[:, :tables.shape[1]] = t2
+    b = lb.paged_attention_q8_batched(Q, k, v, ks, vs, dev(wide), sl, cfg, lb_layout(L))
+    assert torch.equal(a, b)
+    poll_ok()
+
+
+# --------------------------------------------------------------------------- cache manager on the device
+
+def test_device_cache_manager_end_to_end(chk):
+    """tests/test_cache_manager.cpp:96-141 of the reference with int8 pools:
+    create request -> allocate -> append -> attend, all through the manager's
+    device-resident tables."""
+    rng = np.random.default_rng(1400)
+    qh, kvh, d, bs = 4, 2, 128, 16
+    L = lb.PagedLayout(32, bs, kvh, d)
+    cm = lb.DeviceCacheManager(L, max_requests=4, max_blocks_per_req=8)
+    lens = [45, 7, 100]
+    ids = [cm.create_request() for _ in lens]
+    for rid, l in zip(ids, lens):
+        assert cm.ensure_capacity(rid, l + 1)
+        cm.set_seq_len(rid, l)
+    assert not cm.ensure_capacity(ids[0], 8 * bs + 1)       # beyond max_blocks_per_req
+    k, v, ks, vs, tables, seq_lens = cm.tensors()
+    cl = Layout(32, bs, kvh, d)
+    pools = chk.empty_pools_q8(cl)
+    htab = np.full((4, 8), -1, np.int32)
+    for rid, l in zip(ids, lens):
+        htab[rid, :len(cm.block_table(rid))] = cm.block_table(rid)
+        kn = rng.standard_normal((kvh, l, d)).astype(np.float32)
+        vn = rng.standard_normal((kvh, l, d)).astype(np.float32)
+        lb.paged_kv_append_q8(k, v, ks, vs, dev(kn), dev(vn), tables[rid], L, 0, l)
+        chk.paged_kv_append_q8(pools, kn, vn, htab[rid], cl, 0, l)
+    assert np.array_equal(host(tables), htab)
+    assert host(seq_lens).tolist() == [45, 7, 100, 0]
+    Q = rng.standard_normal((4, qh, 1, d)).astype(np.float32)
+    cfg = AttnCfg(qh, kvh, 1, d, 1, 0.0, 0, 0)
+    got = lb.paged_attention_q8_batched(dev(Q), k, v, ks, vs, tables, seq_lens, lb_cfg(cfg), L)
+    want = chk.paged_attention_q8_batched(Q, pools, htab, np.array([45, 7, 100, 0], np.int32), cfg, cl)
+    assert_close(host(got), want, what="managed blocks")
+    cm.release_request(ids[1])
+    torch.cuda.synchronize()
+    assert (host(tables)[ids[1]] == -1).all() and host(seq_lens)[ids[1]] == 0
+    cm.close()
