@@ -32,6 +32,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+GRAPHS = os.environ.get("LHB_BENCH_GRAPHS", "1") != "0"
 K_DIM, N_DIM, GROUP = 4096, 14336, 128
 LAYERS = 32
 METRIC = "int4 group-128 decode GEMV effective HBM bandwidth"
@@ -203,6 +204,26 @@ def timed(fn, steps, warmup, dist, torch, sampler=None):
     return ms
 
 
+def graphed(fn, torch, enabled=True):
+    """Capture `fn` (a fixed sequence of launches on the current stream) into a
+    CUDA graph and return its replay; the launches were already run once by the
+    caller so that one-time set-up (function attributes, tensor maps) is done."""
+    if not enabled:
+        return fn, False
+    try:
+        fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        torch.cuda.synchronize()
+        return g.replay, True
+    except Exception as e:          # stay measurable without graphs
+        print(f"[bench] graph capture failed ({e!r}); timing eager launches", file=sys.stderr)
+        torch.cuda.synchronize()
+        return fn, False
+
+
 class _Null:
     def __enter__(self):
         return self
@@ -235,7 +256,8 @@ def bench_extra(torch, lb, steps, warmup, hbm_peak):
         def step():
             for p, s in zip(packed, scales):
                 lb.gemm_w4a16_groupwise(A, p, s, GROUP, C=C)
-        ms = timed(step, steps, warmup, None, torch)
+        run, _ = graphed(step, torch, GRAPHS)
+        ms = timed(run, steps, warmup, None, torch)
         per = ms / (steps * len(packed)) * 1e-3
         b = gemv_bytes(M, K_DIM, N_DIM, GROUP)
         out[f"w4a16_m{M}"] = {"us_per_call": per * 1e6, "GBps": b / per / 1e9,
@@ -252,7 +274,8 @@ def bench_extra(torch, lb, steps, warmup, hbm_peak):
     def step8():
         for q, s in ws:
             lb.gemm_w8a16_perchannel(A, q, s, C=C)
-    ms = timed(step8, steps, warmup, None, torch)
+    run8, _ = graphed(step8, torch, GRAPHS)
+    ms = timed(run8, steps, warmup, None, torch)
     per = ms / (steps * len(ws)) * 1e-3
     b = gemv_bytes(16, 4096, 4096, 0, wbits=8)
     out["w8a16_m16"] = {"us_per_call": per * 1e6, "GBps": b / per / 1e9, "hbm_frac": b / per / 1e9 / hbm_peak,
@@ -296,7 +319,8 @@ def bench_paged_decode(torch, lb, steps, warmup, hbm_peak, n_req=64, hq=32, hkv=
 
     def step():
         lb.paged_attention_q8_batched(Q, k, v, ks, vs, td, sl, cfg, L, O=O)
-    ms = timed(step, steps, warmup, None, torch)
+    run, _ = graphed(step, torch, GRAPHS)
+    ms = timed(run, steps, warmup, None, torch)
     per = ms / steps * 1e-3
     total = int(lens.sum())
     pages = int(sum((int(l) + bs - 1) // bs for l in lens))
@@ -336,9 +360,13 @@ def run_ours(args):
     outs = torch.empty(LAYERS, M, n_local, device="cuda")
     gathered = torch.empty(g, LAYERS, M, n_local, device="cuda") if g > 1 else None
 
-    def step():
+    def gemvs():
         for i in range(LAYERS):
             lb.gemm_w4a16_groupwise(acts[i], packed[i], scales[i], GROUP, C=outs[i])
+    run_gemvs, is_graph = graphed(gemvs, torch, GRAPHS)
+
+    def step():
+        run_gemvs()
         if g > 1:
             dist.all_gather_into_tensor(gathered, outs)
 
@@ -355,14 +383,18 @@ def run_ours(args):
     h_out = torch.empty(LAYERS, M, n_local).pin_memory()
     d_act = torch.empty(M, K_DIM, device="cuda")
 
-    def step_e2e():
+    def e2e_body():
         for i in range(LAYERS):
             d_act.copy_(h_act[i], non_blocking=True)
             lb.gemm_w4a16_groupwise(d_act, packed[i], scales[i], GROUP, C=outs[i])
             h_out[i].copy_(outs[i], non_blocking=True)
+    run_e2e, e2e_graph = graphed(e2e_body, torch, GRAPHS)
+
+    def step_e2e():
+        run_e2e()
         if g > 1:
             dist.all_gather_into_tensor(gathered, outs)
-        torch.cuda.current_stream().synchronize()
+        torch.cuda.current_stream().synchronize()      # the caller reads the results on the host
     ms_e2e = timed(step_e2e, args.steps, args.warmup, dist, torch)
     e2e_value = bytes_step_total * args.steps / (ms_e2e * 1e-3) / 1e12
 
@@ -389,10 +421,12 @@ def run_ours(args):
                    "l2": f"inputs larger than L2: {LAYERS * bytes_call_local / 1e6:.0f} MB of weights per rank "
                          f"cycled every step" + ("" if LAYERS * bytes_call_local > 2 * 126e6 else
                                                  " (NOT larger than L2 at this shard size)"),
+                   "launch": "CUDA graph replay of the step" if is_graph else "eager launches",
                    "fast_path": int(lb._cabi.load().lhb_gemm_w4a16_fast_path(M, n_local, K_DIM, GROUP))},
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": LAYERS * M * K_DIM * 4, "d2h_bytes_per_step": LAYERS * M * n_local * 4,
-                "note": "activations H2D from pinned memory and outputs D2H every call; weights resident"},
+                "note": "activations H2D from pinned memory and outputs D2H every call, host sync every step; "
+                        "weights resident" + ("; copies+kernels of a step replayed as one CUDA graph" if e2e_graph else "")},
         "gpu_launches": launches,
         "roofline": {"bound": "hbm", "kernel": "gemv_mma_kernel<4,1>", "achieved": achieved, "peak": hbm_peak,
                      "unit": "GB/s", "frac": achieved / hbm_peak, "peak_kind": f"of {peak_kind}",

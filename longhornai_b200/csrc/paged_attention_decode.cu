@@ -1,9 +1,449 @@
-// placeholder: filled in below
+// Split-KV paged decode attention over int8 pages (seq_q == 1).
+//
+// Pool layout is the reference's: K/V int8 [num_blocks, n_kv_heads, 16, 128]
+// with one fp32 scale per (block, head, slot) row
+// (src/kernels/kvcache.hpp:34-41, src/kernels/kvcache_quant.hpp:31-36), so a
+// page of one head is 2 KiB contiguous for K, 2 KiB for V and 64 B for each
+// scale row.  The path is HBM-bound: every page is read once for the whole GQA
+// group (up to 4 query heads share a KV head).
+//
+// Work split: grid = (splits, kv heads, requests).  A CTA owns a contiguous
+// range of the request's visible pages; its 4 warps take pages round-robin and
+// run independent cp.async rings (4 stages x 4.1 KiB per warp, 128-bit copies,
+// XOR-swizzled 16-byte chunks) -- no block-level barrier inside the main loop.
+// Per page a warp does
+//   S = K Q^T  : mma.sync m16n8k16, tokens as the 16 rows, head_dim as k,
+//                int8 -> fp16 by byte-permute against 0x64 (1024 + x), exact;
+//                Q is split into fp16 hi + lo terms (two MMA columns per head),
+//   online softmax in base 2 with the V row scale folded into the exponent:
+//                w = 2^(s*c + log2(vs) - m), so w is in (0, 1] whatever the
+//                magnitude of the scales; the denominator is tracked in the
+//                same frame,
+//   O += V^T W : mma.sync with head_dim as the 16 rows and tokens as k; W is
+//                again split into fp16 hi + lo columns.
+// The four warps merge (m, l, O) in shared memory; with more than one split the
+// CTA writes its partial to the context's scratch arena and the last CTA to
+// arrive for a (request, kv head) merges the partials in fixed order
+// (the (m, l, O) merge rule of flash decoding,
+// src/kernels/attention.cpp:255-280 in the reference).
+//
+// Results differ from the reference's three-pass softmax
+// (src/kernels/kvcache_quant.cpp:82-161) only by fp32 summation order and the
+// 2^-22 relative error of the split terms.
+#include <cuda_fp16.h>
+
+#include <cstdlib>
+
 #include "common.cuh"
 #include "dispatch.h"
+
 namespace lhb {
-bool decode_fast_ok(const lhb_paged_attn_cfg&, const lhb_paged_layout&) { return false; }
-int launch_decode_fast(lhb_ctx*, const float*, const int8_t*, const int8_t*, const float*, const float*,
-                       const int32_t*, int, const int32_t*, int, float*, const lhb_paged_attn_cfg&,
-                       const lhb_paged_layout&, cudaStream_t) { return LHB_ERR_UNSUPPORTED; }
+
+constexpr int PD_WARPS = 4;
+constexpr int PD_THREADS = PD_WARPS * 32;
+constexpr int PD_STAGES = 4;
+constexpr int PD_D = 128;
+constexpr int PD_BS = 16;
+constexpr int PD_STAGE_BYTES = 2048 + 2048 + 64 + 64;          // K, V, ks, vs
+constexpr int PD_WARP_BYTES = PD_STAGES * PD_STAGE_BYTES;
+constexpr int PD_MAX_GROUP = 4;
+constexpr int PD_PART = PD_D + 2;                               // floats per (split, head): m, l, O[128]
+constexpr float PD_WSHIFT = 10.0f;                              // w is scaled by 2^10 into fp16's normal range
+constexpr float PD_MIN_LOG2_VS = -100.0f;
+
+__device__ __forceinline__ uint32_t pd_smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void pd_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                       uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pd_h2u(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+__device__ __forceinline__ __half2 pd_u2h(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+
+// (byte | 0x6400) read as fp16 is 1024 + byte; with the byte pre-biased by 128
+// that is 1152 + q, and one subtraction gives q exactly.
+__device__ __forceinline__ uint32_t pd_unbias(uint32_t t) {
+    return pd_h2u(__hsub2(pd_u2h(t), pd_u2h(0x64806480u)));
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float fast_log2(float x) {
+    float y;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// fp32 -> (hi, lo) fp16 pair packed in one register (hi in the low half)
+__device__ __forceinline__ uint32_t split_h2(float v) {
+    const __half hi = __float2half_rn(v);
+    const __half lo = __float2half_rn(v - __half2float(hi));
+    return static_cast<uint32_t>(__half_as_ushort(hi)) | (static_cast<uint32_t>(__half_as_ushort(lo)) << 16);
+}
+
+struct DecodeParams {
+    const float* Q;          // [n_req, n_q_heads, 1, 128]
+    const int8_t* Kp;
+    const int8_t* Vp;
+    const float* Ks;
+    const float* Vs;
+    const int32_t* tables;   // [n_req, max_blocks]
+    const int32_t* seq_lens; // [n_req]
+    float* O;
+    float* part;             // scratch: [n_req, n_kv, splits, group, PD_PART]
+    int* counters;           // [n_req * n_kv], zero between calls
+    int* status;
+    int max_blocks, n_q_heads, n_kv_heads, group, num_blocks, splits;
+    int window, chunk;
+    float scale_log2e;
+};
+
+__global__ void __launch_bounds__(PD_THREADS)
+paged_decode_q8_kernel(const DecodeParams p) {
+    extern __shared__ __align__(128) uint8_t pd_smem[];
+    __shared__ int s_last;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int split = blockIdx.x, kvh = blockIdx.y, req = blockIdx.z;
+    const int G = p.group;
+
+    // ---- visible key range of the single query row (seq_q == 1) -------------
+    int len = p.seq_lens[req];
+    len = max(0, min(len, p.max_blocks * PD_BS));
+    const int last = len - 1;
+    int first = 0;
+    if (p.window > 0) first = max(0, len - p.window);
+    if (p.chunk > 0 && len > 0) first = max(first, (last / p.chunk) * p.chunk);
+    const int page_f = first / PD_BS;
+    const int n_pages = (len > 0 && last >= first) ? last / PD_BS - page_f + 1 : 0;
+    const int per_split = (n_pages + p.splits - 1) / p.splits;
+    const int pg_lo = page_f + split * per_split;
+    const int pg_hi = min(page_f + n_pages, pg_lo + per_split);   // exclusive
+    const int32_t* table = p.tables + static_cast<int64_t>(req) * p.max_blocks;
+
+    // ---- Q fragments: per head a power-of-two scale into fp16 range, hi/lo split
+    // column j = 2*h + term of the 8-column operand; thread (g, t) holds column g
+    // at head_dim positions 32t + 4i .. 32t + 4i + 3 for k-step i.
+    const int hq = g >> 1, term = g & 1;
+    uint32_t qf[8][2];
+    float qinv[PD_MAX_GROUP];
+    {
+        const float* qbase = p.Q + (static_cast<int64_t>(req) * p.n_q_heads + kvh * G) * PD_D;
+#pragma unroll
+        for (int h = 0; h < PD_MAX_GROUP; ++h) {
+            float mx = 0.0f;
+            if (h < G) {
+                const float4 v = *reinterpret_cast<const float4*>(qbase + h * PD_D + lane * 4);
+                mx = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+            }
+            mx = warp_max(mx);
+            const int e = static_cast<int>((__float_as_uint(mx) >> 23) & 0xff);
+            int se = (mx > 0.0f) ? 267 - e : 127;
+            se = max(1, min(253, se));
+            qinv[h] = __uint_as_float(static_cast<uint32_t>(254 - se) << 23);
+        }
+        float qs = 0.0f;
+#pragma unroll
+        for (int h = 0; h < PD_MAX_GROUP; ++h)
+            if (h == hq) qs = 1.0f / qinv[h];          // exact: powers of two
+        const bool live = hq < G;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (live) v = *reinterpret_cast<const float4*>(qbase + hq * PD_D + 32 * t + 4 * i);
+            const uint32_t s0 = split_h2(v.x * qs), s1 = split_h2(v.y * qs);
+            const uint32_t s2 = split_h2(v.z * qs), s3 = split_h2(v.w * qs);
+            const uint32_t sel = term ? 0x7632u : 0x5410u;
+            qf[i][0] = __byte_perm(s0, s1, sel);
+            qf[i][1] = __byte_perm(s2, s3, sel);
+        }
+    }
+
+    // ---- per-warp state ---------------------------------------------------------
+    uint8_t* ring = pd_smem + warp * PD_WARP_BYTES;
+    const uint32_t ring_u32 = pd_smem_u32(ring);
+    float oacc[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.0f;
+    float m_run = -INFINITY;      // running max of head t (identical on the 8 lanes that share t)
+    float l_run = 0.0f;           // this lane's share of the denominator
+    const float sc = p.scale_log2e * (t == 0 ? qinv[0] : t == 1 ? qinv[1] : t == 2 ? qinv[2] : qinv[3]);
+
+    const int my_first = pg_lo + warp;                 // this warp's pages: my_first, +4, +8, ...
+    const int n_iter = (pg_hi > my_first) ? (pg_hi - my_first + PD_WARPS - 1) / PD_WARPS : 0;
+
+    // lane l of ids_a / ids_b holds the page id of iteration 32*batch + l for
+    // the batch being consumed / the next one (prefetches run 3 iterations ahead)
+    int32_t ids_a = 0, ids_b = 0;
+    auto fetch_ids = [&](int batch) -> int32_t {
+        const int it = batch * 32 + lane;
+        return (it < n_iter) ? table[my_first + it * PD_WARPS] : 0;
+    };
+    auto page_id = [&](int it, int cur_batch) -> int {
+        const int a = __shfl_sync(0xffffffffu, ids_a, it & 31);
+        const int b = __shfl_sync(0xffffffffu, ids_b, it & 31);
+        return ((it >> 5) == cur_batch) ? a : b;
+    };
+    auto issue = [&](int it, int cur_batch) {
+        if (it < n_iter) {
+            int blk = page_id(it, cur_batch);
+            if (blk < 0 || blk >= p.num_blocks) blk = 0;           // masked below; never dereference a bad id
+            const int64_t row0 = (static_cast<int64_t>(blk) * p.n_kv_heads + kvh) * PD_BS;
+            const uint32_t st = ring_u32 + (it % PD_STAGES) * PD_STAGE_BYTES;
+            const int8_t* kp = p.Kp + row0 * PD_D;
+            const int8_t* vp = p.Vp + row0 * PD_D;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int idx = c * 32 + lane;                     // 16-byte chunk 0..127 of the page
+                const int tok = idx >> 3, ch = idx & 7;
+                const uint32_t off = tok * 128 + ((ch ^ (tok & 7)) << 4);
+                cp_async16(st + off, kp + idx * 16);
+                cp_async16(st + 2048 + off, vp + idx * 16);
+            }
+            if (lane < 4) cp_async16(st + 4096 + lane * 16, p.Ks + row0 + lane * 4);
+            else if (lane < 8) cp_async16(st + 4160 + (lane - 4) * 16, p.Vs + row0 + (lane - 4) * 4);
+        }
+        cp_async_commit();
+    };
+
+    ids_a = fetch_ids(0);
+    ids_b = fetch_ids(1);
+#pragma unroll
+    for (int s = 0; s < PD_STAGES - 1; ++s) issue(s, 0);
+
+    for (int it = 0; it < n_iter; ++it) {
+        const int batch = it >> 5;
+        if ((it & 31) == 0 && it > 0) { ids_a = ids_b; ids_b = fetch_ids(batch + 1); }
+        cp_async_wait<PD_STAGES - 2>();
+        __syncwarp();                                   // every lane is done with iteration it - 1
+        issue(it + PD_STAGES - 1, batch);               // refills the stage iteration it - 1 used
+        const uint8_t* st = ring + (it % PD_STAGES) * PD_STAGE_BYTES;
+        const int page = my_first + it * PD_WARPS;
+        const int tok0 = page * PD_BS;
+        const int blk_id = page_id(it, batch);
+        const bool page_ok = blk_id >= 0 && blk_id < p.num_blocks;
+
+        // ---- S = K Q^T over 8 k-steps ------------------------------------------
+        float sacc[4] = {0.f, 0.f, 0.f, 0.f};
+        {
+            const uint8_t* r0 = st + g * 128;           // token g
+            const uint8_t* r1 = st + (g + 8) * 128;     // token g + 8 (same swizzle: (g+8)&7 == g)
+            const int sw = g & 7;
+            const uint4 a0 = *reinterpret_cast<const uint4*>(r0 + (((2 * t) ^ sw) << 4));
+            const uint4 a1 = *reinterpret_cast<const uint4*>(r0 + (((2 * t + 1) ^ sw) << 4));
+            const uint4 b0 = *reinterpret_cast<const uint4*>(r1 + (((2 * t) ^ sw) << 4));
+            const uint4 b1 = *reinterpret_cast<const uint4*>(r1 + (((2 * t + 1) ^ sw) << 4));
+            const uint32_t wa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            const uint32_t wb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint32_t xa = wa[i] ^ 0x80808080u, xb = wb[i] ^ 0x80808080u;
+                const uint32_t f0 = pd_unbias(__byte_perm(xa, 0x64646464u, 0x4140));   // token g,   d+0,1
+                const uint32_t f2 = pd_unbias(__byte_perm(xa, 0x64646464u, 0x4342));   // token g,   d+2,3
+                const uint32_t f1 = pd_unbias(__byte_perm(xb, 0x64646464u, 0x4140));   // token g+8
+                const uint32_t f3 = pd_unbias(__byte_perm(xb, 0x64646464u, 0x4342));
+                pd_mma(sacc, f0, f1, f2, f3, qf[i][0], qf[i][1]);
+            }
+        }
+        // ---- online softmax (base 2), V scale folded into the exponent -------------
+        const float* ksr = reinterpret_cast<const float*>(st + 4096);
+        const float* vsr = reinterpret_cast<const float*>(st + 4160);
+        float x0 = (sacc[0] + sacc[1]) * ksr[g] * sc;          // token g,   head t
+        float x1 = (sacc[2] + sacc[3]) * ksr[g + 8] * sc;      // token g+8, head t
+        const int p0 = tok0 + g, p1 = tok0 + g + 8;
+        const bool ok0 = page_ok && p0 >= first && p0 <= last;
+        const bool ok1 = page_ok && p1 >= first && p1 <= last;
+        const float lv0 = fmaxf(fast_log2(vsr[g]), PD_MIN_LOG2_VS);
+        const float lv1 = fmaxf(fast_log2(vsr[g + 8]), PD_MIN_LOG2_VS);
+        x0 = ok0 ? x0 : -INFINITY;
+        x1 = ok1 ? x1 : -INFINITY;
+        const float y0 = x0 + lv0, y1 = x1 + lv1;              // -inf stays -inf
+        float mp = fmaxf(y0, y1);
+        mp = fmaxf(mp, __shfl_xor_sync(0xffffffffu, mp, 4));
+        mp = fmaxf(mp, __shfl_xor_sync(0xffffffffu, mp, 8));
+        mp = fmaxf(mp, __shfl_xor_sync(0xffffffffu, mp, 16));
+        const float m_new = fmaxf(m_run, mp);
+        const float alpha = (m_new == -INFINITY || m_new == m_run) ? 1.0f : fast_exp2(m_run - m_new);
+        m_run = m_new;
+        const float mb = (m_new == -INFINITY) ? 0.0f : m_new;
+        const float w0 = fast_exp2(y0 - mb + PD_WSHIFT);       // 2^10 * p * vs (relative to the frame)
+        const float w1 = fast_exp2(y1 - mb + PD_WSHIFT);
+        l_run = l_run * alpha + fast_exp2(x0 - mb) + fast_exp2(x1 - mb);
+        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                oacc[i][0] *= alpha; oacc[i][1] *= alpha; oacc[i][2] *= alpha; oacc[i][3] *= alpha;
+            }
+        }
+        // ---- W operand: column g' = 2*head + term needs tokens 2t, 2t+1, 2t+8, 2t+9
+        const uint32_t W0 = split_h2(w0), W1 = split_h2(w1);
+        const int srcA = (2 * t) * 4 + hq, srcB = (2 * t + 1) * 4 + hq;
+        const uint32_t xA0 = __shfl_sync(0xffffffffu, W0, srcA), xB0 = __shfl_sync(0xffffffffu, W0, srcB);
+        const uint32_t xA1 = __shfl_sync(0xffffffffu, W1, srcA), xB1 = __shfl_sync(0xffffffffu, W1, srcB);
+        const uint32_t psel = term ? 0x7632u : 0x5410u;
+        const uint32_t pb0 = __byte_perm(xA0, xB0, psel);      // tokens 2t, 2t+1
+        const uint32_t pb1 = __byte_perm(xA1, xB1, psel);      // tokens 2t+8, 2t+9
+        // ---- O += V^T W over 8 blocks of 16 head_dim rows -----------------------------
+        {
+            const uint8_t* vb = st + 2048;
+            const int r = 2 * t;
+            const uint4 v0 = *reinterpret_cast<const uint4*>(vb + r * 128 + ((g ^ (r & 7)) << 4));
+            const uint4 v1 = *reinterpret_cast<const uint4*>(vb + (r + 1) * 128 + ((g ^ ((r + 1) & 7)) << 4));
+            const uint4 v2 = *reinterpret_cast<const uint4*>(vb + (r + 8) * 128 + ((g ^ (r & 7)) << 4));
+            const uint4 v3 = *reinterpret_cast<const uint4*>(vb + (r + 9) * 128 + ((g ^ ((r + 1) & 7)) << 4));
+            const uint32_t r0w[4] = {v0.x, v0.y, v0.z, v0.w}, r1w[4] = {v1.x, v1.y, v1.z, v1.w};
+            const uint32_t r2w[4] = {v2.x, v2.y, v2.z, v2.w}, r3w[4] = {v3.x, v3.y, v3.z, v3.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                // rows of the operand: head_dim 16g + i (slot g) and 16g + 8 + i (slot g + 8);
+                // byte (i & 3) of the two token rows goes to bytes 0 and 2, then
+                // (byte ^ 0x80) | 0x6400 per half
+                const int wlo = i >> 2, whi = 2 + (i >> 2);
+                const uint32_t bsel = (i & 3) | (((i & 3) + 4) << 8);
+                const uint32_t f0 = pd_unbias((__byte_perm(r0w[wlo], r1w[wlo], bsel) & 0x00ff00ffu) ^ 0x64806480u);
+                const uint32_t f1 = pd_unbias((__byte_perm(r0w[whi], r1w[whi], bsel) & 0x00ff00ffu) ^ 0x64806480u);
+                const uint32_t f2 = pd_unbias((__byte_perm(r2w[wlo], r3w[wlo], bsel) & 0x00ff00ffu) ^ 0x64806480u);
+                const uint32_t f3 = pd_unbias((__byte_perm(r2w[whi], r3w[whi], bsel) & 0x00ff00ffu) ^ 0x64806480u);
+                pd_mma(oacc[i], f0, f1, f2, f3, pb0, pb1);
+            }
+        }
+    }
+    cp_async_wait<0>();
+
+    // ---- merge the four warps in shared memory -------------------------------------------
+    __syncthreads();                                   // rings are dead from here on
+    float* sm_m = reinterpret_cast<float*>(pd_smem);                   // [4 warps][4 heads]
+    float* sm_l = sm_m + PD_WARPS * PD_MAX_GROUP;                      // [4][4]
+    float* sm_o = sm_l + PD_WARPS * PD_MAX_GROUP;                      // [4 warps][4 heads][128]
+    {
+        float l = l_run;
+        l += __shfl_xor_sync(0xffffffffu, l, 4);
+        l += __shfl_xor_sync(0xffffffffu, l, 8);
+        l += __shfl_xor_sync(0xffffffffu, l, 16);
+        if (g == 0) { sm_m[warp * PD_MAX_GROUP + t] = m_run; sm_l[warp * PD_MAX_GROUP + t] = l; }
+        float* od = sm_o + (warp * PD_MAX_GROUP + t) * PD_D + 16 * g;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            od[i] = oacc[i][0] + oacc[i][1];           // hi + lo columns of head t
+            od[8 + i] = oacc[i][2] + oacc[i][3];
+        }
+    }
+    __syncthreads();
+    const int d = threadIdx.x;                          // 128 threads <-> 128 head_dim elements
+    const int64_t pbase = ((static_cast<int64_t>(req) * p.n_kv_heads + kvh) * p.splits + split) * G;
+    for (int h = 0; h < G; ++h) {
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < PD_WARPS; ++w) M = fmaxf(M, sm_m[w * PD_MAX_GROUP + h]);
+        float L = 0.0f, o = 0.0f;
+#pragma unroll
+        for (int w = 0; w < PD_WARPS; ++w) {
+            const float mw = sm_m[w * PD_MAX_GROUP + h];
+            const float f = (mw == -INFINITY) ? 0.0f : fast_exp2(mw - M);
+            L += f * sm_l[w * PD_MAX_GROUP + h];
+            o += f * sm_o[(w * PD_MAX_GROUP + h) * PD_D + d];
+        }
+        if (p.splits == 1) {
+            float* out = p.O + (static_cast<int64_t>(req) * p.n_q_heads + kvh * G + h) * PD_D;
+            out[d] = (L > 0.0f) ? o * (1.0f / L) * exp2f(-PD_WSHIFT) : 0.0f;
+        } else {
+            float* pp = p.part + (pbase + h) * PD_PART;
+            if (d == 0) { pp[0] = M; pp[1] = L; }
+            pp[2 + d] = o;
+        }
+    }
+    if (p.splits == 1) return;
+
+    // ---- cross-CTA merge: the last split to arrive combines all partials ------------------
+    __threadfence();
+    __syncthreads();
+    const int cidx = req * p.n_kv_heads + kvh;
+    if (threadIdx.x == 0) {
+        const int old = atomicAdd(p.counters + cidx, 1);
+        s_last = (old == p.splits - 1);
+        if (s_last) p.counters[cidx] = 0;              // ready for the next call
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const int64_t b0 = (static_cast<int64_t>(req) * p.n_kv_heads + kvh) * p.splits * G;
+    for (int h = 0; h < G; ++h) {
+        float M = -INFINITY;
+        for (int s = 0; s < p.splits; ++s) M = fmaxf(M, __ldcg(p.part + (b0 + s * G + h) * PD_PART));
+        float L = 0.0f, o = 0.0f;
+        for (int s = 0; s < p.splits; ++s) {
+            const float* pp = p.part + (b0 + s * G + h) * PD_PART;
+            const float ms = __ldcg(pp);
+            const float f = (ms == -INFINITY) ? 0.0f : fast_exp2(ms - M);
+            L += f * __ldcg(pp + 1);
+            o += f * __ldcg(pp + 2 + d);
+        }
+        float* out = p.O + (static_cast<int64_t>(req) * p.n_q_heads + kvh * G + h) * PD_D;
+        out[d] = (L > 0.0f) ? o * (1.0f / L) * exp2f(-PD_WSHIFT) : 0.0f;
+    }
+}
+
+bool decode_fast_ok(const lhb_paged_attn_cfg& cfg, const lhb_paged_layout& L) {
+    if (cfg.seq_q != 1 || cfg.head_dim != PD_D || L.head_dim != PD_D || L.block_size != PD_BS) return false;
+    if (cfg.n_kv_heads <= 0 || cfg.n_q_heads % cfg.n_kv_heads) return false;
+    const int group = cfg.n_q_heads / cfg.n_kv_heads;
+    return group >= 1 && group <= PD_MAX_GROUP && cfg.n_kv_heads <= 65535;
+}
+
+int launch_decode_fast(lhb_ctx* ctx, const float* Q, const int8_t* Kp, const int8_t* Vp,
+                       const float* Ks, const float* Vs, const int32_t* tables, int max_blocks,
+                       const int32_t* seq_lens, int n_req, float* O, const lhb_paged_attn_cfg& cfg,
+                       const lhb_paged_layout& L, cudaStream_t st) {
+    const int group = cfg.n_q_heads / cfg.n_kv_heads;
+    const int64_t items = static_cast<int64_t>(n_req) * cfg.n_kv_heads;
+    // enough CTAs to keep ~8 per SM, at least ~8 pages per CTA
+    int splits = static_cast<int>(ceil_div64(8LL * ctx->sm_count, items));
+    splits = std::max(1, std::min(splits, std::max(1, max_blocks / 8)));
+    splits = std::min(splits, 32);
+    if (const char* e = getenv("LHB_DECODE_SPLITS")) splits = std::max(1, std::min(64, atoi(e)));
+    if (items > static_cast<int64_t>(ctx->counters_len)) splits = 1;
+    const size_t need = static_cast<size_t>(items) * splits * group * PD_PART * sizeof(float);
+    if (splits > 1 && need > ctx->scratch_bytes) {
+        splits = static_cast<int>(ctx->scratch_bytes / (static_cast<size_t>(items) * group * PD_PART * sizeof(float)));
+        if (splits < 1) splits = 1;
+    }
+    DecodeParams p{};
+    p.Q = Q; p.Kp = Kp; p.Vp = Vp; p.Ks = Ks; p.Vs = Vs; p.tables = tables; p.seq_lens = seq_lens;
+    p.O = O; p.part = reinterpret_cast<float*>(ctx->scratch); p.counters = ctx->counters;
+    p.status = ctx->status_word;
+    p.max_blocks = max_blocks; p.n_q_heads = cfg.n_q_heads; p.n_kv_heads = cfg.n_kv_heads;
+    p.group = group; p.num_blocks = L.num_blocks; p.splits = splits;
+    p.window = cfg.window; p.chunk = cfg.chunk;
+    const float scale = cfg.scale > 0.0f ? cfg.scale : 1.0f / sqrtf(static_cast<float>(cfg.head_dim));
+    p.scale_log2e = scale * 1.4426950408889634f;
+    const size_t smem = PD_WARPS * PD_WARP_BYTES;
+    static bool attr_set[64] = {};
+    if (!attr_set[ctx->device & 63]) {
+        LHB_CUDA(cudaFuncSetAttribute(paged_decode_q8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(smem)));
+        attr_set[ctx->device & 63] = true;
+    }
+    dim3 grid(splits, cfg.n_kv_heads, n_req);
+    paged_decode_q8_kernel<<<grid, PD_THREADS, smem, st>>>(p);
+    LHB_LAUNCH_CHECK();
+    return LHB_OK;
+}
+
+}  // namespace lhb
