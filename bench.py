@@ -282,7 +282,35 @@ def bench_extra(torch, lb, steps, warmup, hbm_peak):
                         "bytes": b}
     del ws
     out["paged_decode_q8"] = bench_paged_decode(torch, lb, steps, warmup, hbm_peak)
+    torch.cuda.empty_cache()
+    out["w8a8_prefill"] = bench_w8a8(torch, lb, min(steps, 5), 3)
     return out
+
+
+def bench_w8a8(torch, lb, steps, warmup, M=8192, K=8192, N=28672):
+    """Fifth BASELINE config: per-token int8 activations x per-channel int8 weights,
+    int32 accumulate, fp32 rescale (Llama-3-70B MLP shape)."""
+    import ctypes as C
+    gen = torch.Generator(device="cuda").manual_seed(20245)
+    X = torch.randn(M, K, device="cuda", generator=gen)
+    Aq, a_s = lb.q8_quantize_per_row(X)
+    del X
+    Wt = torch.randn(K, N, device="cuda", generator=gen) * 0.02
+    Bq, b_s = lb.q8_quantize_per_col(Wt)
+    del Wt
+    Cout = torch.empty(M, N, device="cuda")
+
+    def step():
+        lb.gemm_w8a8(Aq, Bq, a_s, b_s, C=Cout)
+    ms = timed(step, steps, warmup, None, torch)
+    per = ms / steps * 1e-3
+    ops = 2.0 * M * N * K
+    _, bf16_peak, kind = measured_peaks()
+    return {"ms_per_call": per * 1e3, "TOPs": ops / per / 1e12,
+            "frac_of_2x_bf16_" + kind: ops / per / 1e12 / (2 * bf16_peak),
+            "frac_of_nominal_4500": ops / per / 1e12 / 4500.0,
+            "fast_path": int(lb._cabi.load().lhb_gemm_w8a8_fast_path(M, N, K)),
+            "bytes": M * K + K * N + 4 * M * N + 4 * (M + N)}
 
 
 def bench_paged_decode(torch, lb, steps, warmup, hbm_peak, n_req=64, hq=32, hkv=8, d=128, bs=16,
@@ -457,10 +485,18 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary workloads")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--only", default=None, choices=["paged_decode"],
+                    help="run one secondary workload alone on one GPU (for profiling) and print its numbers")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
-    if args.impl == "reference":
+    if args.only == "paged_decode":
+        import torch
+        import longhornai_b200 as lb
+        torch.cuda.set_device(0)
+        print(json.dumps({"paged_decode_q8": bench_paged_decode(torch, lb, args.steps, args.warmup,
+                                                                 measured_peaks()[0])}), flush=True)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -133,7 +133,7 @@ int lhb_gemm_w8a8(lhb_ctx* ctx, const int8_t* Aq, const int8_t* Bq, const float*
     if (M < 0 || N <= 0 || K <= 0) return LHB_ERR_BAD_SHAPE;
     if (M == 0) return LHB_OK;
     cudaStream_t st = as_stream(stream);
-    if (w8a8_fast_ok(M, N, K) && aligned16(Aq) && aligned16(Bq) && aligned16(C))
+    if (w8a8_fast_ok(M, N, K) && aligned16(Aq) && aligned16(Bq) && aligned16(bs) && aligned16(C))
         return launch_w8a8_fast(ctx, Aq, Bq, as, bs, C, M, N, K, alpha, beta, st);
     return launch_w8a8_generic(Aq, Bq, as, bs, C, M, N, K, alpha, beta, st);
 }

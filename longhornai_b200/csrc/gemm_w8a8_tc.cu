@@ -1,8 +1,245 @@
-// placeholder: filled in below
+// W8A8 GEMM on the 5th-generation tensor cores: int8 x int8 -> int32 in TMEM,
+// fp32 rescale in the epilogue.
+//
+// Operand layouts are the reference's (src/kernels/gemm_quant.hpp:35-45):
+// A_q int8 [M, K] with K contiguous, B_q int8 [K, N] with N contiguous, i.e. B
+// is "MN-major" for the tensor core.  Both are consumed as they lie: TMA brings
+// 128-byte-swizzled tiles into shared memory and the tcgen05 shared-memory
+// descriptors describe A as K-major and B as MN-major, so there is no weight
+// transpose.
+//
+// One persistent CTA per SM walks 128 x 256 output tiles (M fastest, so the CTAs
+// running together share A/B panels in L2).  Warp roles:
+//   warp 0   TMA producer   4-stage ring, 48 KiB per stage (A 128x128, B 128x256)
+//   warp 1   MMA issuer     one thread issues 4 tcgen05.mma (K = 32 each) per stage
+//                           and commits the stage's "empty" barrier
+//   warp 2   TMEM allocator 512 columns = two 128 x 256 int32 accumulators, so the
+//                           epilogue of tile i overlaps the main loop of tile i+1
+//   warps 4-7 epilogue      tcgen05.ld 32 lanes x 32 columns, then
+//                           C = beta*C + ((alpha*a_s[m])*b_s[n])*float(acc)
+// The int32 sums are exact and the epilogue multiplies in the reference's order
+// with single roundings (src/kernels/gemm_quant.cpp:44-46), so the output is
+// bit-identical to the reference.
+//
+// Every wait is bounded (ptx::mbar_wait); a timeout sets the context's status
+// word, all roles fall through to the common exit and TMEM is freed.
+#include <algorithm>
+
 #include "common.cuh"
 #include "dispatch.h"
+#include "ptx.cuh"
+
 namespace lhb {
-bool w8a8_fast_ok(int, int, int) { return false; }
-int launch_w8a8_fast(lhb_ctx*, const int8_t*, const int8_t*, const float*, const float*, float*, int,
-                     int, int, float, float, cudaStream_t) { return LHB_ERR_UNSUPPORTED; }
+
+constexpr int W8_BM = 128, W8_BN = 256, W8_BK = 128;
+constexpr int W8_STAGES = 4;
+constexpr int W8_A_BYTES = W8_BM * W8_BK;            // 16 KiB
+constexpr int W8_B_BYTES = W8_BK * W8_BN;            // 32 KiB, two 128-column boxes
+constexpr int W8_STAGE_BYTES = W8_A_BYTES + W8_B_BYTES;
+constexpr int W8_THREADS = 256;
+constexpr int W8_TMEM_COLS = 512;
+constexpr size_t W8_SMEM = 1024 + static_cast<size_t>(W8_STAGES) * W8_STAGE_BYTES + 256;
+
+// instruction descriptor: D = s32 (bits 4-5 = 2), A = B = signed int8 (bits 7-9,
+// 10-12 = 1), A K-major (bit 15 = 0), B MN-major (bit 16 = 1), N >> 3 at bit 17,
+// M >> 4 at bit 24
+constexpr uint32_t W8_IDESC = (2u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
+                              (static_cast<uint32_t>(W8_BN >> 3) << 17) |
+                              (static_cast<uint32_t>(W8_BM >> 4) << 24);
+
+struct W8Params {
+    const float* a_scales;
+    const float* b_scales;
+    float* C;
+    int M, N, K;
+    float alpha, beta;
+    int tiles_m, tiles_n;
+    int* status;
+};
+
+__global__ void __launch_bounds__(W8_THREADS, 1)
+gemm_w8a8_tc_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ TensorMap tmB,
+                    const W8Params p) {
+    extern __shared__ uint8_t w8_smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(w8_smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + W8_STAGES * W8_STAGE_BYTES);
+    // bars[0..3] full, [4..7] empty, [8..9] tmem_full, [10..11] tmem_empty
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t bar0 = ptx::smem_u32(bars);
+    auto full_bar = [&](int s) { return bar0 + 8 * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8 * (W8_STAGES + s); };
+    auto tfull_bar = [&](int b) { return bar0 + 8 * (2 * W8_STAGES + b); };
+    auto tempty_bar = [&](int b) { return bar0 + 8 * (2 * W8_STAGES + 2 + b); };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < W8_STAGES; ++s) { ptx::mbar_init(full_bar(s), 1); ptx::mbar_init(empty_bar(s), 1); }
+        for (int b = 0; b < 2; ++b) { ptx::mbar_init(tfull_bar(b), 1); ptx::mbar_init(tempty_bar(b), 128); }
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+        ptx::prefetch_tmap(&tmA);
+        ptx::prefetch_tmap(&tmB);
+    }
+    if (warp == 2) {
+        ptx::tmem_alloc(ptx::smem_u32(tmem_slot), W8_TMEM_COLS);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int n_tiles = p.tiles_m * p.tiles_n;
+    const int num_kb = (p.K + W8_BK - 1) / W8_BK;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            for (int tile = blockIdx.x; tile < n_tiles && !*abort_flag; tile += gridDim.x) {
+                const int m0 = (tile % p.tiles_m) * W8_BM, n0 = (tile / p.tiles_m) * W8_BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % W8_STAGES;
+                    if (!ptx::mbar_wait(empty_bar(s), ((it / W8_STAGES) & 1) ^ 1, abort_flag, p.status)) break;
+                    ptx::mbar_expect_tx(full_bar(s), W8_STAGE_BYTES);
+                    const uint32_t sa = ptx::smem_u32(smem + s * W8_STAGE_BYTES);
+                    ptx::tma_load_2d(sa, &tmA, kb * W8_BK, m0, full_bar(s));
+                    ptx::tma_load_2d(sa + W8_A_BYTES, &tmB, n0, kb * W8_BK, full_bar(s));
+                    ptx::tma_load_2d(sa + W8_A_BYTES + W8_BK * 128, &tmB, n0 + 128, kb * W8_BK, full_bar(s));
+                }
+            }
+            // drain: every stage this thread armed completes before the CTA may exit
+            const int armed = it < W8_STAGES ? it : W8_STAGES;
+            for (int j = 0; j < armed; ++j) {
+                const int jt = it - 1 - j;
+                const int s = jt % W8_STAGES;
+                const uint64_t t0 = ptx::global_timer_ns();
+                while (!ptx::mbar_try_wait(full_bar(s), (jt / W8_STAGES) & 1))
+                    if (ptx::global_timer_ns() - t0 > 200000000ull) break;
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            int it = 0, ti = 0;
+            for (int tile = blockIdx.x; tile < n_tiles && !*abort_flag; tile += gridDim.x, ++ti) {
+                const int buf = ti & 1;
+                if (!ptx::mbar_wait(tempty_bar(buf), ((ti >> 1) & 1) ^ 1, abort_flag, p.status)) break;
+                ptx::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * W8_BN;
+                bool ok = true;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % W8_STAGES;
+                    if (!ptx::mbar_wait(full_bar(s), (it / W8_STAGES) & 1, abort_flag, p.status)) { ok = false; break; }
+                    ptx::tc_fence_after();
+                    const uint32_t sa = ptx::smem_u32(smem + s * W8_STAGE_BYTES);
+                    const uint32_t sb = sa + W8_A_BYTES;
+#pragma unroll
+                    for (int k4 = 0; k4 < W8_BK / 32; ++k4) {
+                        // A: K-major, rows of 128 B, 8-row groups 1024 B apart; K advances 32 B inside the row
+                        const uint64_t da = ptx::smem_desc_sw128(sa + k4 * 32, 16, 1024);
+                        // B: MN-major, 128 columns per atom row, 8 k-rows = 1024 B, the second
+                        // 128-column box lies W8_BK*128 bytes further; K advances 32 rows
+                        const uint64_t db = ptx::smem_desc_sw128(sb + k4 * 32 * 128, W8_BK * 128, 1024);
+                        ptx::mma_i8_ss(d_tmem, da, db, W8_IDESC, (kb | k4) != 0 ? 1u : 0u);
+                    }
+                    ptx::tc_commit(empty_bar(s));
+                }
+                if (!ok) break;
+                ptx::tc_commit(tfull_bar(buf));
+            }
+        }
+    } else if (warp >= 4) {
+        const int q = warp - 4;                            // TMEM lane quarter this warp may read
+        int ti = 0;
+        for (int tile = blockIdx.x; tile < n_tiles && !*abort_flag; tile += gridDim.x, ++ti) {
+            const int buf = ti & 1;
+            const int m0 = (tile % p.tiles_m) * W8_BM, n0 = (tile / p.tiles_m) * W8_BN;
+            if (!ptx::mbar_wait(tfull_bar(buf), (ti >> 1) & 1, abort_flag, p.status)) break;
+            ptx::tc_fence_after();
+            const int row = m0 + 32 * q + lane;
+            const bool row_ok = row < p.M;
+            const float sa = row_ok ? __fmul_rn(p.alpha, p.a_scales[row]) : 0.0f;
+            float* crow = p.C + static_cast<int64_t>(row_ok ? row : 0) * p.N;
+#pragma unroll 1
+            for (int c = 0; c < W8_BN / 32; ++c) {
+                uint32_t r[32];
+                ptx::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(32 * q) << 16) + buf * W8_BN + c * 32, r);
+                ptx::tmem_ld_wait();
+                if (c == W8_BN / 32 - 1) {                 // accumulator fully read: hand it back
+                    ptx::tc_fence_before();
+                    ptx::mbar_arrive(tempty_bar(buf));
+                }
+                const int nb = n0 + c * 32;
+                if (!row_ok || nb >= p.N) continue;
+                if (nb + 32 <= p.N) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        const float4 bs = __ldg(reinterpret_cast<const float4*>(p.b_scales + nb + j));
+                        float4 v;
+                        v.x = __fmul_rn(__fmul_rn(sa, bs.x), static_cast<float>(static_cast<int>(r[j])));
+                        v.y = __fmul_rn(__fmul_rn(sa, bs.y), static_cast<float>(static_cast<int>(r[j + 1])));
+                        v.z = __fmul_rn(__fmul_rn(sa, bs.z), static_cast<float>(static_cast<int>(r[j + 2])));
+                        v.w = __fmul_rn(__fmul_rn(sa, bs.w), static_cast<float>(static_cast<int>(r[j + 3])));
+                        float4* dst = reinterpret_cast<float4*>(crow + nb + j);
+                        if (p.beta != 0.0f) {
+                            const float4 o = *dst;
+                            if (p.beta == 1.0f) {
+                                v.x = __fadd_rn(o.x, v.x); v.y = __fadd_rn(o.y, v.y);
+                                v.z = __fadd_rn(o.z, v.z); v.w = __fadd_rn(o.w, v.w);
+                            } else {
+                                v.x = __fadd_rn(__fmul_rn(o.x, p.beta), v.x); v.y = __fadd_rn(__fmul_rn(o.y, p.beta), v.y);
+                                v.z = __fadd_rn(__fmul_rn(o.z, p.beta), v.z); v.w = __fadd_rn(__fmul_rn(o.w, p.beta), v.w);
+                            }
+                        }
+                        *dst = v;
+                    }
+                } else {
+                    for (int j = 0; j < 32 && nb + j < p.N; ++j) {
+                        float v = __fmul_rn(__fmul_rn(sa, p.b_scales[nb + j]), static_cast<float>(static_cast<int>(r[j])));
+                        float* dst = crow + nb + j;
+                        if (p.beta == 1.0f) v = __fadd_rn(*dst, v);
+                        else if (p.beta != 0.0f) v = __fadd_rn(__fmul_rn(*dst, p.beta), v);
+                        *dst = v;
+                    }
+                }
+            }
+        }
+    }
+
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 2) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, W8_TMEM_COLS);
+    }
 }
+
+bool w8a8_fast_ok(int M, int N, int K) {
+    return M >= 64 && N >= 128 && K >= 128 && (N % 16) == 0 && (K % 16) == 0;
+}
+
+int launch_w8a8_fast(lhb_ctx* ctx, const int8_t* Aq, const int8_t* Bq, const float* as,
+                     const float* bs, float* C, int M, int N, int K, float alpha, float beta,
+                     cudaStream_t st) {
+    TensorMap tmA, tmB;
+    if (int e = get_tensor_map_2d_u8(ctx, Aq, M, K, K, W8_BM, W8_BK, true, &tmA)) return e;
+    if (int e = get_tensor_map_2d_u8(ctx, Bq, K, N, N, W8_BK, 128, true, &tmB)) return e;
+    static bool attr_set[64] = {};
+    if (!attr_set[ctx->device & 63]) {
+        LHB_CUDA(cudaFuncSetAttribute(gemm_w8a8_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(W8_SMEM)));
+        attr_set[ctx->device & 63] = true;
+    }
+    W8Params p{};
+    p.a_scales = as; p.b_scales = bs; p.C = C; p.M = M; p.N = N; p.K = K;
+    p.alpha = alpha; p.beta = beta;
+    p.tiles_m = ceil_div(M, W8_BM); p.tiles_n = ceil_div(N, W8_BN);
+    p.status = ctx->status_word;
+    const int grid = std::min(ctx->sm_count, p.tiles_m * p.tiles_n);
+    gemm_w8a8_tc_kernel<<<grid, W8_THREADS, W8_SMEM, st>>>(tmA, tmB, p);
+    LHB_LAUNCH_CHECK();
+    return LHB_OK;
+}
+
+}  // namespace lhb

@@ -27,16 +27,18 @@
 // stay in fp32, so the result differs from the reference's fp32 loop only by
 // summation order (~1e-6 relative).
 //
-// K is split over a thread-block cluster (1..8 CTAs along K); the partial
-// [M, 128] tiles are reduced in fixed order through distributed shared memory,
-// so the result is deterministic and no global scratch is used.
-#include <cooperative_groups.h>
+// K is split over blockIdx.y so that every SM holds 3-4 CTAs with their whole
+// K-chunk in flight.  Each split writes its partial [M, 128] tile to the
+// context's scratch arena; the last split to arrive for a column tile (a
+// self-resetting counter) sums the partials in fixed order and applies
+// alpha/beta, so the result is deterministic and C is written once.
 #include <cuda_fp16.h>
+
+#include <cstdlib>
 
 #include "common.cuh"
 #include "dispatch.h"
-
-namespace cg = cooperative_groups;
+#include "ptx.cuh"
 
 namespace lhb {
 
@@ -46,71 +48,11 @@ constexpr int GV_STAGE_BYTES = GV_COLS * GV_ROWS;
 constexpr int GV_NSTAGE = 4;
 constexpr int GV_CONSUMER_WARPS = 8;
 constexpr int GV_THREADS = (GV_CONSUMER_WARPS + 1) * 32;   // + one producer warp
-constexpr int GV_MAX_CLUSTER = 8;
+constexpr int GV_MAX_SPLIT = 32;
 
-// ---- PTX wrappers -----------------------------------------------------------
+// ---- PTX wrappers (mbarrier / TMA live in ptx.cuh) --------------------------------
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-                 : "memory");
-}
-
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-
-__device__ __forceinline__ uint64_t global_timer_ns() {
-    uint64_t t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-
-// Bounded wait: gives up after about one second, records LHB_ERR_TIMEOUT in the
-// status word and lets the caller carry on (its results are then garbage, but
-// every barrier of the kernel is still reached and the kernel ends).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status) {
-    for (int i = 0; i < 64; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = global_timer_ns();
-    while (!mbar_try_wait(bar, parity)) {
-        if (global_timer_ns() - t0 > 1000000000ull) {
-            atomicExch(status, static_cast<int>(LHB_ERR_TIMEOUT));
-            return false;
-        }
-    }
-    return true;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int x, int y,
-                                            uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
-        "[%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar)
-        : "memory");
-}
+using ptx::smem_u32;
 
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -161,12 +103,15 @@ struct GemvParams {
     float alpha, beta;
     int stages_total;      // ceil(rows / 64)
     int stages_per_cta;
+    int splits;            // gridDim.y
+    float* partial;        // scratch [splits, M, N] (unused when splits == 1)
+    int* counters;         // one per column tile, zero between calls
     int* status;
 };
 
 // WBITS: 4 or 8.  JB: number of 8-column activation blocks (M <= 4*JB).
 template <int WBITS, int JB>
-__global__ void __launch_bounds__(GV_THREADS, 1)
+__global__ void __launch_bounds__(GV_THREADS, (JB == 4) ? 3 : 4)
 gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
     constexpr int K_PER_ROW = (WBITS == 4) ? 2 : 1;
     constexpr int K_PER_STAGE = GV_ROWS * K_PER_ROW;
@@ -178,13 +123,14 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* tiles = smem;                                             // GV_NSTAGE * 8 KiB
     float* part = reinterpret_cast<float*>(smem + GV_NSTAGE * GV_STAGE_BYTES);   // [MROWS][128]
-    float* inv_s = part + MROWS * GV_COLS;                             // [MROWS]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(inv_s + 16);          // full[4], empty[4]
-    __half* bfrag = reinterpret_cast<__half*>(bars + 2 * GV_NSTAGE);   // [kb][NJ][4][4]
+    float* inv_s = part + MROWS * GV_COLS;                             // [16]
+    unsigned* rowmax = reinterpret_cast<unsigned*>(inv_s + 16);        // [16] max|a| bits per row
+    uint64_t* bars = reinterpret_cast<uint64_t*>(rowmax + 16);         // full[4], empty[4]
+    int* flags = reinterpret_cast<int*>(bars + 2 * GV_NSTAGE);         // [0] abort, [1] is-last
+    __half* bfrag = reinterpret_cast<__half*>(flags + 4);              // [kb][NJ][4][4]
+    volatile int* abort_flag = flags;
 
-    cg::cluster_group cluster = cg::this_cluster();
-    const int S = static_cast<int>(cluster.num_blocks());
-    const int ks = static_cast<int>(cluster.block_rank());
+    const int ks = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int col0 = blockIdx.x * GV_COLS;
 
@@ -195,60 +141,78 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
     const int k_count = n_stages * K_PER_STAGE;            // multiple of 16; may run past K
 
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + GV_NSTAGE);
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < GV_NSTAGE; ++s) {
-            mbar_init(full0 + 8 * s, 1);
-            mbar_init(empty0 + 8 * s, GV_CONSUMER_WARPS);
-        }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-
-    // Producer: put the first GV_NSTAGE stages in flight before anything else.
+    // The producer thread sets the barriers up and puts the first GV_NSTAGE stages
+    // in flight before anything else happens in the CTA.
     if (warp == GV_CONSUMER_WARPS && lane == 0) {
+        for (int s = 0; s < GV_NSTAGE; ++s) {
+            ptx::mbar_init(full0 + 8 * s, 1);
+            ptx::mbar_init(empty0 + 8 * s, GV_CONSUMER_WARPS);
+        }
+        flags[0] = 0;
+        flags[1] = 0;
+        ptx::fence_mbar_init();
         const int first = min(n_stages, GV_NSTAGE);
         for (int s = 0; s < first; ++s) {
-            mbar_expect_tx(full0 + 8 * s, GV_STAGE_BYTES);
-            tma_load_2d(smem_u32(tiles + s * GV_STAGE_BYTES), &tmB, col0, (stage_begin + s) * GV_ROWS,
-                        full0 + 8 * s);
+            ptx::mbar_expect_tx(full0 + 8 * s, GV_STAGE_BYTES);
+            ptx::tma_load_2d(smem_u32(tiles + s * GV_STAGE_BYTES), &tmB, col0, (stage_begin + s) * GV_ROWS,
+                             full0 + 8 * s);
         }
     }
+    if (threadIdx.x < 16) rowmax[threadIdx.x] = 0u;
+    __syncthreads();
 
-    // Activation prologue (all warps, overlapped with the loads in flight):
-    // row m of this CTA's K-chunk -> scale by a power of two into fp16 range,
-    // split into hi + lo, store in B-fragment order.
-    for (int m = warp; m < MROWS; m += GV_THREADS / 32) {
-        const bool live = m < p.M;
-        const float* a = p.A + static_cast<int64_t>(m) * p.K + k_begin;
+    // Activation prologue (all threads, overlapped with the loads in flight):
+    // every live row of this CTA's K-chunk is scaled by a power of two into fp16
+    // range, split into hi + lo and stored in B-fragment order.  Columns of rows
+    // m >= M are left as they are: an MMA column only feeds its own output
+    // column, and those are never read.
+    const int q4 = k_count >> 2;                           // float4 per row
+    const int n4 = p.M * q4;
+    for (int i = threadIdx.x; i < n4; i += GV_THREADS) {
+        const int m = i / q4, k = (i - m * q4) * 4;
         float mx = 0.0f;
-        if (live)
-            for (int k = lane; k < k_count; k += 32)
-                if (k_begin + k < p.K) mx = fmaxf(mx, fabsf(a[k]));
-        mx = warp_max(mx);
+        if (k_begin + k < p.K) {
+            const float4 v = *reinterpret_cast<const float4*>(p.A + static_cast<int64_t>(m) * p.K + k_begin + k);
+            mx = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+        }
+        if (mx > 0.0f) atomicMax(rowmax + m, __float_as_uint(mx));
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n4; i += GV_THREADS) {
+        const int m = i / q4, k = (i - m * q4) * 4;
         // power-of-two factor taking max|a| into [2^13, 2^14); exponent clamped
-        int e = static_cast<int>((__float_as_uint(mx) >> 23) & 0xff);
-        int se = (mx > 0.0f) ? 267 - e : 127;
+        const unsigned mb = rowmax[m];
+        int se = mb ? 267 - static_cast<int>((mb >> 23) & 0xff) : 127;
         se = max(1, min(253, se));
-        const float s = __uint_as_float(static_cast<uint32_t>(se) << 23);
-        if (lane == 0) inv_s[m] = __uint_as_float(static_cast<uint32_t>(254 - se) << 23);
-        for (int k = lane; k < k_count; k += 32) {
-            float v = 0.0f;
-            if (live && k_begin + k < p.K) v = a[k] * s;
-            const __half hi = __float2half_rn(v);
-            const __half lo = __float2half_rn(v - __half2float(hi));
-            const int kb = k >> 4, kin = k & 15;
-            int t, e4;
-            if (WBITS == 4) {            // thread t holds k0+4t+{0,2,1,3}
-                t = kin >> 2;
-                const int r = kin & 3;
-                e4 = ((r & 1) << 1) | (r >> 1);
-            } else {                     // thread t holds k0+{2t, 2t+1, 8+2t, 9+2t}
-                t = (kin & 7) >> 1;
-                e4 = ((kin >> 3) << 1) | (kin & 1);
-            }
-            const int base = ((kb * NJ + 2 * m) * 4 + t) * 4 + e4;
-            bfrag[base] = hi;
-            bfrag[base + 16] = lo;       // column 2m+1
+        const float sc = __uint_as_float(static_cast<uint32_t>(se) << 23);
+        if (k == 0) inv_s[m] = __uint_as_float(static_cast<uint32_t>(254 - se) << 23);
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (k_begin + k < p.K)
+            v = *reinterpret_cast<const float4*>(p.A + static_cast<int64_t>(m) * p.K + k_begin + k);
+        const float x[4] = {v.x * sc, v.y * sc, v.z * sc, v.w * sc};
+        unsigned short hi[4], lo[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const __half h = __float2half_rn(x[j]);
+            hi[j] = __half_as_ushort(h);
+            lo[j] = __half_as_ushort(__float2half_rn(x[j] - __half2float(h)));
+        }
+        const int kb = k >> 4, kin = k & 15;
+        if (WBITS == 4) {
+            // fragment slot t = kin/4 holds k+{0,2,1,3}: one 8-byte store per column
+            __half* d = bfrag + ((kb * NJ + 2 * m) * 4 + (kin >> 2)) * 4;
+            *reinterpret_cast<uint2*>(d) = make_uint2(hi[0] | (static_cast<uint32_t>(hi[2]) << 16),
+                                                      hi[1] | (static_cast<uint32_t>(hi[3]) << 16));
+            *reinterpret_cast<uint2*>(d + 16) = make_uint2(lo[0] | (static_cast<uint32_t>(lo[2]) << 16),
+                                                           lo[1] | (static_cast<uint32_t>(lo[3]) << 16));
+        } else {
+            // slot t holds k0+{2t, 2t+1, 8+2t, 9+2t}: (k, k+1) and (k+2, k+3) go to slots t, t+1
+            const int t0 = (kin & 7) >> 1, e = (kin >> 3) << 1;
+            __half* d = bfrag + ((kb * NJ + 2 * m) * 4 + t0) * 4 + e;
+            *reinterpret_cast<uint32_t*>(d) = hi[0] | (static_cast<uint32_t>(hi[1]) << 16);
+            *reinterpret_cast<uint32_t*>(d + 4) = hi[2] | (static_cast<uint32_t>(hi[3]) << 16);
+            *reinterpret_cast<uint32_t*>(d + 16) = lo[0] | (static_cast<uint32_t>(lo[1]) << 16);
+            *reinterpret_cast<uint32_t*>(d + 20) = lo[2] | (static_cast<uint32_t>(lo[3]) << 16);
         }
     }
     __syncthreads();
@@ -293,7 +257,7 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
 
         for (int ls = 0; ls < n_stages; ++ls) {
             const int slot = ls % GV_NSTAGE;
-            mbar_wait(full0 + 8 * slot, (ls / GV_NSTAGE) & 1, p.status);
+            ptx::mbar_wait(full0 + 8 * slot, (ls / GV_NSTAGE) & 1, abort_flag, p.status);
             const uint32_t tile = smem_u32(tiles + slot * GV_STAGE_BYTES);
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
@@ -302,7 +266,7 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
                 ldmatrix_x4_trans(tile + row * 128 + ((warp ^ (row & 7)) << 4), x);
                 if (half == 1) {           // stage fully read by this warp
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(empty0 + 8 * slot);
+                    if (lane == 0) ptx::mbar_arrive(empty0 + 8 * slot);
                 }
                 if (WBITS == 4) {
 #pragma unroll
@@ -354,73 +318,119 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
                 out[jb][2] = s1 * acc[jb][2]; out[jb][3] = s1 * acc[jb][3];
             }
         }
-        // hi + lo columns of row m = 4*jb + t, undo the activation scaling
+        // hi + lo columns of row m = 4*jb + t, undo the activation scaling; rows of
+        // this split go straight to C (one split) or to the scratch partials
 #pragma unroll
         for (int jb = 0; jb < JB; ++jb) {
             const int m = 4 * jb + t;
-            const float is = inv_s[m];
-            float2 v;
-            v.x = is * (out[jb][0] + out[jb][1]);
-            v.y = is * (out[jb][2] + out[jb][3]);
-            *reinterpret_cast<float2*>(part + m * GV_COLS + warp * 16 + 2 * g) = v;
+            if (m < p.M && n_a < p.N) {
+                const float is = inv_s[m];
+                float2 v;
+                v.x = is * (out[jb][0] + out[jb][1]);
+                v.y = is * (out[jb][2] + out[jb][3]);
+                if (p.splits == 1) {
+                    float* cp = p.C + static_cast<int64_t>(m) * p.N + n_a;
+                    if (p.beta == 0.0f) { v.x *= p.alpha; v.y *= p.alpha; }
+                    else { v.x = fmaf(p.beta, cp[0], p.alpha * v.x); v.y = fmaf(p.beta, cp[1], p.alpha * v.y); }
+                    *reinterpret_cast<float2*>(cp) = v;       // N % 16 == 0: both columns exist, 8-byte aligned
+                } else {
+                    *reinterpret_cast<float2*>(p.partial + (static_cast<int64_t>(ks) * p.M + m) * p.N + n_a) = v;
+                }
+            }
         }
     } else if (lane == 0) {
         // producer: refill ring slots as the consumers release them
+        int issued = min(n_stages, GV_NSTAGE);
         for (int ls = GV_NSTAGE; ls < n_stages; ++ls) {
             const int slot = ls % GV_NSTAGE;
-            mbar_wait(empty0 + 8 * slot, ((ls / GV_NSTAGE) - 1) & 1, p.status);
-            mbar_expect_tx(full0 + 8 * slot, GV_STAGE_BYTES);
-            tma_load_2d(smem_u32(tiles + slot * GV_STAGE_BYTES), &tmB, col0,
-                        (stage_begin + ls) * GV_ROWS, full0 + 8 * slot);
+            if (!ptx::mbar_wait(empty0 + 8 * slot, ((ls / GV_NSTAGE) - 1) & 1, abort_flag, p.status)) break;
+            ptx::mbar_expect_tx(full0 + 8 * slot, GV_STAGE_BYTES);
+            ptx::tma_load_2d(smem_u32(tiles + slot * GV_STAGE_BYTES), &tmB, col0,
+                             (stage_begin + ls) * GV_ROWS, full0 + 8 * slot);
+            issued = ls + 1;
+        }
+        if (*abort_flag) {
+            // a wait ran out: let the copies still in flight land before the CTA exits
+            for (int ls = max(0, issued - GV_NSTAGE); ls < issued; ++ls) {
+                const uint64_t t0 = ptx::global_timer_ns();
+                while (!ptx::mbar_try_wait(full0 + 8 * (ls % GV_NSTAGE), (ls / GV_NSTAGE) & 1))
+                    if (ptx::global_timer_ns() - t0 > 200000000ull) break;
+            }
         }
     }
+    if (p.splits == 1) return;
 
-    // Cluster reduction over the K split, fixed order, through distributed
-    // shared memory.  CTA `ks` finishes columns [ks*128/S, (ks+1)*128/S).
-    cluster.sync();
-    const int cols_per = GV_COLS / S;
-    for (int i = threadIdx.x; i < p.M * cols_per; i += GV_THREADS) {
-        const int m = i / cols_per, c = ks * cols_per + i % cols_per;
-        const int n = col0 + c;
-        if (n >= p.N) continue;
-        float sum = 0.0f;
-        for (int r = 0; r < S; ++r) {
-            const float* rp = cluster.map_shared_rank(part, r);
-            sum += rp[m * GV_COLS + c];
-        }
-        float* cp = p.C + static_cast<int64_t>(m) * p.N + n;
-        *cp = (p.beta == 0.0f) ? p.alpha * sum : fmaf(p.beta, *cp, p.alpha * sum);
+    // Split-K epilogue: the last split to arrive for this column tile sums the
+    // partials in split order and writes C.
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int old = atomicAdd(p.counters + blockIdx.x, 1);
+        flags[1] = (old == p.splits - 1);
+        if (old == p.splits - 1) p.counters[blockIdx.x] = 0;   // ready for the next call
     }
-    cluster.sync();   // keep every CTA's shared memory alive until all peers have read it
+    __syncthreads();
+    if (!flags[1]) return;
+    __threadfence();
+    const int ncol = min(GV_COLS, p.N - col0);
+    for (int i = threadIdx.x; i < p.M * (ncol >> 2); i += GV_THREADS) {
+        const int m = i / (ncol >> 2), c = (i % (ncol >> 2)) * 4;
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r = 0; r < p.splits; ++r) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(
+                p.partial + (static_cast<int64_t>(r) * p.M + m) * p.N + col0 + c));
+            sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+        }
+        float4* cp = reinterpret_cast<float4*>(p.C + static_cast<int64_t>(m) * p.N + col0 + c);
+        if (p.beta == 0.0f) {
+            sum.x *= p.alpha; sum.y *= p.alpha; sum.z *= p.alpha; sum.w *= p.alpha;
+        } else {
+            const float4 o = *cp;
+            sum.x = fmaf(p.beta, o.x, p.alpha * sum.x); sum.y = fmaf(p.beta, o.y, p.alpha * sum.y);
+            sum.z = fmaf(p.beta, o.z, p.alpha * sum.z); sum.w = fmaf(p.beta, o.w, p.alpha * sum.w);
+        }
+        *cp = sum;
+    }
 }
 
 // ---- host side --------------------------------------------------------------------
 
 static size_t gemv_smem_bytes(int jb, int k_per_cta) {
     const size_t nj = 8 * jb, mrows = 4 * jb;
-    return 1024 + GV_NSTAGE * GV_STAGE_BYTES + mrows * GV_COLS * 4 + 16 * 4 + 2 * GV_NSTAGE * 8 +
+    return 1024 + GV_NSTAGE * GV_STAGE_BYTES + mrows * GV_COLS * 4 + 16 * 4 + 16 * 4 + 2 * GV_NSTAGE * 8 + 16 +
            static_cast<size_t>(k_per_cta) * nj * 2;
 }
 
-struct GemvPlan { int cluster; int stages_total; int stages_per_cta; size_t smem; bool ok; };
+struct GemvPlan { int splits; int stages_total; int stages_per_cta; size_t smem; bool ok; };
 
-// Pick the K split: as many cluster CTAs (power of two, <= 8) as needed to
-// put >= ~4 CTAs on every SM, without making a CTA's chunk shorter than one
-// stage, and subject to the shared-memory budget.
+// Pick the K split.  A CTA costs its stage count plus a fixed overhead (launch,
+// activation prologue, partial write-out, about three stages' worth); the grid
+// should fit in one wave of ~4 CTAs per SM.  The shared-memory budget (the
+// activation fragments grow with the chunk length) bounds the chunk from above.
 static GemvPlan plan_gemv(int wbits, int jb, int N, int K, int sm_count) {
-    GemvPlan pl{};
+    GemvPlan best{};
     const int k_per_stage = GV_ROWS * (wbits == 4 ? 2 : 1);
-    pl.stages_total = ceil_div(K, k_per_stage);
+    const int stages_total = ceil_div(K, k_per_stage);
     const int col_tiles = ceil_div(N, GV_COLS);
-    int S = 1;
-    while (S < GV_MAX_CLUSTER && col_tiles * S < 4 * sm_count && pl.stages_total >= 2 * S) S *= 2;
-    for (;; S *= 2) {
-        pl.cluster = S;
-        pl.stages_per_cta = ceil_div(pl.stages_total, S);
-        pl.smem = gemv_smem_bytes(jb, pl.stages_per_cta * k_per_stage);
-        if (pl.smem <= 200 * 1024) { pl.ok = true; return pl; }
-        if (S >= GV_MAX_CLUSTER) { pl.ok = false; return pl; }
+    double best_cost = 1e30;
+    int forced = 0;
+    if (const char* e = getenv("LHB_GEMV_SPLITS")) forced = atoi(e);
+    for (int S = 1; S <= std::min(stages_total, GV_MAX_SPLIT); ++S) {
+        if (forced > 0 && S != std::min(forced, std::min(stages_total, GV_MAX_SPLIT))) continue;
+        const int spc = ceil_div(stages_total, S);
+        const int splits = ceil_div(stages_total, spc);
+        const size_t smem = gemv_smem_bytes(jb, spc * k_per_stage);
+        if (smem > 200 * 1024) continue;
+        const int per_sm = std::max(1, std::min(4, static_cast<int>((220 * 1024) / smem)));
+        const int waves = ceil_div(col_tiles * splits, sm_count * per_sm);
+        const double cost = waves * (spc + 3.0) + 0.05 * splits;
+        if (cost < best_cost) {
+            best_cost = cost;
+            best.splits = splits; best.stages_total = stages_total; best.stages_per_cta = spc;
+            best.smem = smem; best.ok = true;
+        }
     }
+    return best;
 }
 
 static int jb_for(int M) { return M <= 4 ? 1 : (M <= 8 ? 2 : 4); }
@@ -448,20 +458,13 @@ static int launch_gemv_t(lhb_ctx* ctx, const TensorMap& tm, GemvParams p, const 
     }
     p.stages_total = pl.stages_total;
     p.stages_per_cta = pl.stages_per_cta;
+    p.splits = pl.splits;
+    p.partial = reinterpret_cast<float*>(ctx->scratch);
+    p.counters = ctx->counters;
     p.status = ctx->status_word;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(ceil_div(p.N, GV_COLS), pl.cluster, 1);
-    cfg.blockDim = dim3(GV_THREADS, 1, 1);
-    cfg.dynamicSmemBytes = pl.smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = pl.cluster;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    LHB_CUDA(cudaLaunchKernelEx(&cfg, kern, tm, p));
+    const dim3 grid(ceil_div(p.N, GV_COLS), pl.splits, 1);
+    kern<<<grid, GV_THREADS, pl.smem, st>>>(tm, p);
+    LHB_LAUNCH_CHECK();
     return LHB_OK;
 }
 
@@ -475,8 +478,11 @@ static int launch_gemv(lhb_ctx* ctx, const float* A, const void* B, const float*
     for (int m0 = 0; m0 < M; m0 += 16) {
         const int m = std::min(16, M - m0);
         const int jb = jb_for(m);
-        const GemvPlan pl = plan_gemv(WBITS, jb, N, K, ctx->sm_count);
+        GemvPlan pl = plan_gemv(WBITS, jb, N, K, ctx->sm_count);
         if (!pl.ok) return LHB_ERR_UNSUPPORTED;
+        if (ceil_div(N, GV_COLS) > static_cast<int>(ctx->counters_len)) return LHB_ERR_UNSUPPORTED;
+        if (pl.splits > 1 && static_cast<size_t>(pl.splits) * m * N * sizeof(float) > ctx->scratch_bytes)
+            return LHB_ERR_SCRATCH;
         GemvParams p{};
         p.A = A + static_cast<int64_t>(m0) * K;
         p.scales = scales;

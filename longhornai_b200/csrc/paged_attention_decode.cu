@@ -9,7 +9,7 @@
 //
 // Work split: grid = (splits, kv heads, requests).  A CTA owns a contiguous
 // range of the request's visible pages; its 4 warps take pages round-robin and
-// run independent cp.async rings (4 stages x 4.1 KiB per warp, 128-bit copies,
+// run independent cp.async rings (3 stages x 4.1 KiB per warp, 128-bit copies,
 // XOR-swizzled 16-byte chunks) -- no block-level barrier inside the main loop.
 // Per page a warp does
 //   S = K Q^T  : mma.sync m16n8k16, tokens as the 16 rows, head_dim as k,
@@ -41,7 +41,7 @@ namespace lhb {
 
 constexpr int PD_WARPS = 4;
 constexpr int PD_THREADS = PD_WARPS * 32;
-constexpr int PD_STAGES = 4;
+constexpr int PD_STAGES = 3;
 constexpr int PD_D = 128;
 constexpr int PD_BS = 16;
 constexpr int PD_STAGE_BYTES = 2048 + 2048 + 64 + 64;          // K, V, ks, vs
@@ -115,7 +115,7 @@ struct DecodeParams {
     float scale_log2e;
 };
 
-__global__ void __launch_bounds__(PD_THREADS)
+__global__ void __launch_bounds__(PD_THREADS, 4)
 paged_decode_q8_kernel(const DecodeParams p) {
     extern __shared__ __align__(128) uint8_t pd_smem[];
     __shared__ int s_last;
@@ -242,6 +242,7 @@ paged_decode_q8_kernel(const DecodeParams p) {
 
         // ---- S = K Q^T over 8 k-steps ------------------------------------------
         float sacc[4] = {0.f, 0.f, 0.f, 0.f};
+        float sacc2[4] = {0.f, 0.f, 0.f, 0.f};     // second chain: even / odd k-steps are independent
         {
             const uint8_t* r0 = st + g * 128;           // token g
             const uint8_t* r1 = st + (g + 8) * 128;     // token g + 8 (same swizzle: (g+8)&7 == g)
@@ -259,8 +260,11 @@ paged_decode_q8_kernel(const DecodeParams p) {
                 const uint32_t f2 = pd_unbias(__byte_perm(xa, 0x64646464u, 0x4342));   // token g,   d+2,3
                 const uint32_t f1 = pd_unbias(__byte_perm(xb, 0x64646464u, 0x4140));   // token g+8
                 const uint32_t f3 = pd_unbias(__byte_perm(xb, 0x64646464u, 0x4342));
-                pd_mma(sacc, f0, f1, f2, f3, qf[i][0], qf[i][1]);
+                if (i & 1) pd_mma(sacc2, f0, f1, f2, f3, qf[i][0], qf[i][1]);
+                else pd_mma(sacc, f0, f1, f2, f3, qf[i][0], qf[i][1]);
             }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) sacc[j] += sacc2[j];
         }
         // ---- online softmax (base 2), V scale folded into the exponent -------------
         const float* ksr = reinterpret_cast<const float*>(st + 4096);

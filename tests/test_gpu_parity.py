@@ -317,7 +317,10 @@ def test_attention_ignores_table_padding_and_is_deterministic(chk):
     t2 = tables.copy(); t2[t2 < 0] = 12345678      # padding must never be dereferenced
     wide = np.full((2, tables.shape[1] + 9), -1, np.int32); wide[:, :tables.shape[1]] = t2
     b = lb.paged_attention_q8_batched(Q, k, v, ks, vs, dev(wide), sl, cfg, lb_layout(L))
-    assert torch.equal(a, b)
+    # a wider table may change the KV split, i.e. the order of the fp32 sums, not the values
+    assert_close(host(b), host(a), rtol=1e-5, atol=1e-6, what="padding")
+    a2 = lb.paged_attention_q8_batched(Q, k, v, ks, vs, dev(tables), sl, cfg, lb_layout(L))
+    assert torch.equal(a, a2), "run-to-run determinism"
     poll_ok()
 
 
