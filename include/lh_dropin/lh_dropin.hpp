@@ -1,0 +1,120 @@
+// Drop-in C++ front end: the reference's `namespace lh` functions for the
+// quantized decode path, with the reference's exact signatures, implemented on
+// the GPU through the lhb200 C ABI (link liblhb200.so).
+//
+// Point the include path at include/lh_dropin instead of the reference's src/
+// and the same `#include "kernels/gemm_quant.hpp"` lines resolve to these
+// declarations (the per-file headers under kernels/ forward here).
+//
+// Pointer arguments may be host or device pointers, independently of each other:
+//   * device pointers are passed straight to the kernels, the call is enqueued
+//     on lh::dropin::stream() and returns without synchronising;
+//   * host pointers are staged (copied to the device, and results copied back)
+//     and the call returns after the results are in host memory, so code written
+//     against the reference (all-host buffers) runs unmodified.
+// Differences from the reference, which validates nothing and returns void: a
+// shape the reference would treat as undefined behaviour, or a CUDA failure,
+// throws std::runtime_error.  There is no CPU fallback.
+#ifndef LH_DROPIN_HPP
+#define LH_DROPIN_HPP
+
+#include <cstdint>
+
+#define LH_DROPIN_API __attribute__((visibility("default")))
+
+namespace lh {
+
+// -- src/kernels/kvcache.hpp:26-41 ------------------------------------------------
+struct PagedCacheLayout {
+    int num_blocks = 0;
+    int block_size = 16;
+    int n_kv_heads = 1;
+    int head_dim = 1;
+};
+
+inline int64_t paged_offset(const PagedCacheLayout& L, int block, int head, int slot, int d) {
+    return (((static_cast<int64_t>(block) * L.n_kv_heads + head) * L.block_size + slot) * L.head_dim) + d;
+}
+
+// -- src/kernels/kvcache_quant.hpp:31-36 ---------------------------------------------
+inline int64_t paged_scale_offset(const PagedCacheLayout& L, int block, int head, int slot) {
+    return (static_cast<int64_t>(block) * L.n_kv_heads + head) * L.block_size + slot;
+}
+
+// -- src/kernels/paged_attention.hpp:28-37 ---------------------------------------------
+struct PagedAttnConfig {
+    int n_q_heads = 1;
+    int n_kv_heads = 1;
+    int seq_q = 1;
+    int head_dim = 1;
+    bool causal = true;
+    float scale = 0.0f;   // <= 0: 1/sqrt(head_dim)
+    int window = 0;
+    int chunk = 0;
+};
+
+// -- src/kernels/quant.hpp:38-75 ----------------------------------------------------------
+LH_DROPIN_API void q8_quantize_per_row(const float* src, int8_t* dst, float* scales_out, int rows, int dim);
+LH_DROPIN_API void q8_dequantize_per_row(const int8_t* src, const float* scales, float* dst, int rows, int dim);
+LH_DROPIN_API void q8_quantize_per_col(const float* src, int8_t* dst, float* scales_out, int rows, int cols);
+LH_DROPIN_API void q8_dequantize_per_col(const int8_t* src, const float* scales, float* dst, int rows, int cols);
+LH_DROPIN_API void q4_quantize_groupwise(const float* src, uint8_t* packed, float* scales_out, int K, int N,
+                                         int group_size);
+LH_DROPIN_API void q4_dequantize_groupwise(const uint8_t* packed, const float* scales, float* dst, int K, int N,
+                                           int group_size);
+// host-side nibble read (packed must be a host pointer)
+inline int8_t q4_get(const uint8_t* packed, int k, int n, int N) {
+    const uint8_t b = packed[static_cast<int64_t>(k / 2) * N + n];
+    const int nib = (k & 1) ? (b >> 4) : (b & 0x0f);
+    return static_cast<int8_t>((nib & 8) ? nib - 16 : nib);
+}
+
+// -- src/kernels/gemm_quant.hpp:42-57 ----------------------------------------------------------
+LH_DROPIN_API void gemm_w8a8(const int8_t* A_q, const int8_t* B_q, const float* A_scales, const float* B_scales,
+                             float* C, int M, int N, int K, float alpha = 1.0f, float beta = 0.0f);
+LH_DROPIN_API void gemm_w4a16_groupwise(const float* A, const uint8_t* B_packed, const float* B_scales, float* C,
+                                        int M, int N, int K, int group_size, float alpha = 1.0f,
+                                        float beta = 0.0f);
+// Weight-only int8 per output channel (the reference composes
+// q8_dequantize_per_col + gemm; this is the fused call).
+LH_DROPIN_API void gemm_w8a16_perchannel(const float* A, const int8_t* B_q, const float* B_scales, float* C,
+                                         int M, int N, int K, float alpha = 1.0f, float beta = 0.0f);
+
+// -- src/kernels/kvcache.hpp:50-55, src/kernels/kvcache_quant.hpp:41-57 --------------------------
+LH_DROPIN_API void paged_kv_append(float* k_pool, float* v_pool, const float* k_new, const float* v_new,
+                                   const int32_t* block_table, const PagedCacheLayout& L, int past_len,
+                                   int seq_new);
+LH_DROPIN_API void paged_kv_append_q8(int8_t* k_pool, int8_t* v_pool, float* k_scales, float* v_scales,
+                                      const float* k_new, const float* v_new, const int32_t* block_table,
+                                      const PagedCacheLayout& L, int past_len, int seq_new);
+LH_DROPIN_API void paged_attention_q8(const float* Q, const int8_t* K_pool, const int8_t* V_pool,
+                                      const float* K_scales, const float* V_scales, const int32_t* block_table,
+                                      int seq_len, float* O, const PagedAttnConfig& cfg,
+                                      const PagedCacheLayout& L);
+// Batched int8 form with the calling convention of paged_attention_batched.
+LH_DROPIN_API void paged_attention_q8_batched(const float* Q, const int8_t* K_pool, const int8_t* V_pool,
+                                              const float* K_scales, const float* V_scales,
+                                              const int32_t* block_tables, int max_blocks_per_req,
+                                              const int32_t* seq_lens, int n_requests, float* O,
+                                              const PagedAttnConfig& cfg, const PagedCacheLayout& L);
+
+// -- src/kernels/paged_attention.hpp:42-63 ----------------------------------------------------------
+LH_DROPIN_API void paged_attention(const float* Q, const float* K_pool, const float* V_pool,
+                                   const int32_t* block_table, int seq_len, float* O,
+                                   const PagedAttnConfig& cfg, const PagedCacheLayout& L);
+LH_DROPIN_API void paged_attention_batched(const float* Q, const float* K_pool, const float* V_pool,
+                                           const int32_t* block_tables, int max_blocks_per_req,
+                                           const int32_t* seq_lens, int n_requests, float* O,
+                                           const PagedAttnConfig& cfg, const PagedCacheLayout& L);
+
+namespace dropin {
+// The CUDA stream device-pointer calls are enqueued on (default: the legacy
+// default stream) and a blocking wait for it.
+LH_DROPIN_API void set_stream(void* cuda_stream);
+LH_DROPIN_API void* stream();
+LH_DROPIN_API void synchronize();
+}  // namespace dropin
+
+}  // namespace lh
+
+#endif  // LH_DROPIN_HPP

@@ -104,6 +104,7 @@ struct GemvParams {
     int stages_total;      // ceil(rows / 64)
     int stages_per_cta;
     int splits;            // gridDim.y
+    int groups_per_cta;    // W4: rows of the shared scale panel (0 for W8)
     float* partial;        // scratch [splits, M, N] (unused when splits == 1)
     int* counters;         // one per column tile, zero between calls
     int* status;
@@ -127,7 +128,8 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
     unsigned* rowmax = reinterpret_cast<unsigned*>(inv_s + 16);        // [16] max|a| bits per row
     uint64_t* bars = reinterpret_cast<uint64_t*>(rowmax + 16);         // full[4], empty[4]
     int* flags = reinterpret_cast<int*>(bars + 2 * GV_NSTAGE);         // [0] abort, [1] is-last
-    __half* bfrag = reinterpret_cast<__half*>(flags + 4);              // [kb][NJ][4][4]
+    float* sscale = reinterpret_cast<float*>(flags + 4);               // W4: [groups_per_cta][128] group scales
+    __half* bfrag = reinterpret_cast<__half*>(sscale + p.groups_per_cta * GV_COLS);   // [kb][NJ][4][4]
     volatile int* abort_flag = flags;
 
     const int ks = blockIdx.y;
@@ -166,6 +168,17 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
     // range, split into hi + lo and stored in B-fragment order.  Columns of rows
     // m >= M are left as they are: an MMA column only feeds its own output
     // column, and those are never read.
+    // W4: this CTA's panel of group scales, [groups][128 columns], coalesced
+    const int g_first = (WBITS == 4) ? k_begin / p.G : 0;
+    if (WBITS == 4) {
+        for (int i = threadIdx.x; i < p.groups_per_cta * (GV_COLS / 4); i += GV_THREADS) {
+            const int gl = i / (GV_COLS / 4), c = (i % (GV_COLS / 4)) * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if ((g_first + gl) * p.G < p.K && col0 + c < p.N)      // N % 16 == 0: whole float4 in range
+                v = *reinterpret_cast<const float4*>(p.scales + static_cast<int64_t>(g_first + gl) * p.N + col0 + c);
+            *reinterpret_cast<float4*>(sscale + gl * GV_COLS + c) = v;
+        }
+    }
     const int q4 = k_count >> 2;                           // float4 per row
     const int n4 = p.M * q4;
     for (int i = threadIdx.x; i < n4; i += GV_THREADS) {
@@ -231,6 +244,11 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
         for (int jb = 0; jb < JB; ++jb)
 #pragma unroll
             for (int i = 0; i < 4; ++i) acc[jb][i] = 0.0f;
+        float ch0 = 0.0f, ch1 = 0.0f;                      // W8: per-channel scales, fetched ahead of the loop
+        if (WBITS == 8) {
+            if (n_a < p.N) ch0 = p.scales[n_a];
+            if (n_a + 1 < p.N) ch1 = p.scales[n_a + 1];
+        }
         const int kb_per_group = (WBITS == 4) ? p.G / 16 : 0x7fffffff;
         int kb_in_group = (WBITS == 4) ? (k_begin / 16) % kb_per_group : 0;
         // ldmatrix row address: matrix (lane / 8), row (lane % 8); 16-byte chunk = warp, swizzled
@@ -238,13 +256,9 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
         // end of a quantisation group (or of this CTA's chunk): fold the scale
         // of the group that k16-block `kb` belongs to into the running output
         auto flush_group = [&](int kb) {
-            float s0 = 0.0f, s1 = 0.0f;
-            const int k = k_begin + kb * 16;
-            if (k < p.K) {
-                const float* sp = p.scales + static_cast<int64_t>(k / p.G) * p.N + n_a;
-                if (n_a < p.N) s0 = sp[0];
-                if (n_a + 1 < p.N) s1 = sp[1];
-            }
+            const int gl = (k_begin + kb * 16) / p.G - g_first;
+            const float2 sv = *reinterpret_cast<const float2*>(sscale + gl * GV_COLS + warp * 16 + 2 * g);
+            const float s0 = sv.x, s1 = sv.y;
 #pragma unroll
             for (int jb = 0; jb < JB; ++jb) {
                 out[jb][0] = fmaf(s0, acc[jb][0], out[jb][0]);
@@ -309,9 +323,7 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
         }
         if (WBITS == 4 && kb_in_group != 0 && n_stages > 0) flush_group(n_stages * KB_PER_STAGE - 1);
         if (WBITS == 8) {
-            float s0 = 0.0f, s1 = 0.0f;
-            if (n_a < p.N) s0 = p.scales[n_a];
-            if (n_a + 1 < p.N) s1 = p.scales[n_a + 1];
+            const float s0 = ch0, s1 = ch1;
 #pragma unroll
             for (int jb = 0; jb < JB; ++jb) {
                 out[jb][0] = s0 * acc[jb][0]; out[jb][1] = s0 * acc[jb][1];
@@ -395,9 +407,14 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
 
 // ---- host side --------------------------------------------------------------------
 
-static size_t gemv_smem_bytes(int jb, int k_per_cta) {
+static int gemv_groups_per_cta(int wbits, int k_per_cta, int G) {
+    return wbits == 4 ? k_per_cta / G + 2 : 0;             // + 2: chunks need not start on a group boundary
+}
+
+static size_t gemv_smem_bytes(int wbits, int jb, int k_per_cta, int G) {
     const size_t nj = 8 * jb, mrows = 4 * jb;
     return 1024 + GV_NSTAGE * GV_STAGE_BYTES + mrows * GV_COLS * 4 + 16 * 4 + 16 * 4 + 2 * GV_NSTAGE * 8 + 16 +
+           static_cast<size_t>(gemv_groups_per_cta(wbits, k_per_cta, G)) * GV_COLS * 4 +
            static_cast<size_t>(k_per_cta) * nj * 2;
 }
 
@@ -407,7 +424,7 @@ struct GemvPlan { int splits; int stages_total; int stages_per_cta; size_t smem;
 // activation prologue, partial write-out, about three stages' worth); the grid
 // should fit in one wave of ~4 CTAs per SM.  The shared-memory budget (the
 // activation fragments grow with the chunk length) bounds the chunk from above.
-static GemvPlan plan_gemv(int wbits, int jb, int N, int K, int sm_count) {
+static GemvPlan plan_gemv(int wbits, int jb, int N, int K, int G, int sm_count) {
     GemvPlan best{};
     const int k_per_stage = GV_ROWS * (wbits == 4 ? 2 : 1);
     const int stages_total = ceil_div(K, k_per_stage);
@@ -419,7 +436,7 @@ static GemvPlan plan_gemv(int wbits, int jb, int N, int K, int sm_count) {
         if (forced > 0 && S != std::min(forced, std::min(stages_total, GV_MAX_SPLIT))) continue;
         const int spc = ceil_div(stages_total, S);
         const int splits = ceil_div(stages_total, spc);
-        const size_t smem = gemv_smem_bytes(jb, spc * k_per_stage);
+        const size_t smem = gemv_smem_bytes(wbits, jb, spc * k_per_stage, G);
         if (smem > 200 * 1024) continue;
         const int per_sm = std::max(1, std::min(4, static_cast<int>((220 * 1024) / smem)));
         const int waves = ceil_div(col_tiles * splits, sm_count * per_sm);
@@ -438,13 +455,13 @@ static int jb_for(int M) { return M <= 4 ? 1 : (M <= 8 ? 2 : 4); }
 bool w4a16_fast_ok(int M, int N, int K, int G) {
     if (M < 1 || (N % 16) != 0 || (K % 16) != 0 || (G % 16) != 0 || (K % G) != 0) return false;
     if (M > 64) return false;                     // larger M: generic path (dense GEMM territory)
-    return plan_gemv(4, jb_for(M > 16 ? 16 : M), N, K, 148).ok;
+    return plan_gemv(4, jb_for(M > 16 ? 16 : M), N, K, G, 148).ok;
 }
 
 bool w8a16_fast_ok(int M, int N, int K) {
     if (M < 1 || (N % 16) != 0 || (K % 16) != 0) return false;
     if (M > 64) return false;
-    return plan_gemv(8, jb_for(M > 16 ? 16 : M), N, K, 148).ok;
+    return plan_gemv(8, jb_for(M > 16 ? 16 : M), N, K, 1, 148).ok;
 }
 
 template <int WBITS, int JB>
@@ -459,6 +476,7 @@ static int launch_gemv_t(lhb_ctx* ctx, const TensorMap& tm, GemvParams p, const 
     p.stages_total = pl.stages_total;
     p.stages_per_cta = pl.stages_per_cta;
     p.splits = pl.splits;
+    p.groups_per_cta = gemv_groups_per_cta(WBITS, pl.stages_per_cta * GV_ROWS * (WBITS == 4 ? 2 : 1), p.G);
     p.partial = reinterpret_cast<float*>(ctx->scratch);
     p.counters = ctx->counters;
     p.status = ctx->status_word;
@@ -478,7 +496,7 @@ static int launch_gemv(lhb_ctx* ctx, const float* A, const void* B, const float*
     for (int m0 = 0; m0 < M; m0 += 16) {
         const int m = std::min(16, M - m0);
         const int jb = jb_for(m);
-        GemvPlan pl = plan_gemv(WBITS, jb, N, K, ctx->sm_count);
+        GemvPlan pl = plan_gemv(WBITS, jb, N, K, WBITS == 4 ? G : 1, ctx->sm_count);
         if (!pl.ok) return LHB_ERR_UNSUPPORTED;
         if (ceil_div(N, GV_COLS) > static_cast<int>(ctx->counters_len)) return LHB_ERR_UNSUPPORTED;
         if (pl.splits > 1 && static_cast<size_t>(pl.splits) * m * N * sizeof(float) > ctx->scratch_bytes)
