@@ -5,35 +5,37 @@
 //   W8: int8 [K, N], fp32 scales [N] (src/kernels/quant.hpp:45-48).
 // Both layouts are N-contiguous, i.e. the reduction axis is the slow axis.
 //
-// The path is HBM-bound: the weight bytes are read exactly once.  To keep the
-// instruction count per weight well under what the memory system can feed,
-// the dot products run on the tensor cores with the weights dequantised in
-// registers:
+// The path is HBM-bound: the weight bytes are read exactly once, so the kernel
+// is built to spend as few issue slots per weight as possible.
 //
 //   TMA (2-D, 128-byte swizzle)  global -> shared, 64 rows x 128 columns per
-//       stage, the whole K-chunk of a CTA in flight at once (4-deep ring);
+//       stage, 4-deep ring, the first four stages of a CTA in flight at once;
 //   ldmatrix.trans on the raw bytes: one 8x8 b16 matrix = 8 byte-rows x 16
-//       columns; the transposed fragment hands every thread bytes of ONE
-//       column at two consecutive rows, which is exactly the "two adjacent k
-//       of one output column" pairing an m16n8k16 A-fragment register needs;
-//   nibble/byte -> fp16 with mask+xor against 0x6400 (1024 + x) and one
-//       HSUB2/HFMA2, exact for |q| <= 128;
-//   mma.sync m16n8k16 f16 x f16 -> f32 with the weights as the 16-row operand
-//       (16 output columns) and the activations as the 8-column operand.
+//       columns; the transposed fragment hands every thread the bytes of two
+//       adjacent columns at two consecutive rows;
+//   int4 -> int8 without arithmetic: a nibble moved to the top of its byte IS
+//       the two's-complement int8 value 16*q (shift/mask), and one byte-permute
+//       per register gathers four consecutive k of one column, which is the
+//       operand register of the int8 tensor-core MMA (int8 weights need the
+//       permute only);
+//   mma.sync m16n8k32 s8 x s8 -> s32: weights are the 16-row operand (16 output
+//       columns), activations the 8-column operand.
 //
-// Activations are fp32 in the API.  They are split on the fly into two fp16
-// terms hi + lo (after an exact power-of-two scaling of each row chunk into
-// fp16 range), which occupy two MMA columns per row of A; products and sums
-// stay in fp32, so the result differs from the reference's fp32 loop only by
-// summation order (~1e-6 relative).
+// Activations are fp32 in the API.  Each row of a CTA's K-chunk is scaled by a
+// power of two so that max|a| lands in [2^19, 2^20), rounded to an integer and
+// written as three signed 7-bit digits (a = d1*2^14 + d2*2^7 + d3), one MMA
+// column per digit.  Integer products and sums are exact; the only error is
+// the rounding of a to 20 bits relative to the chunk maximum (2^-21), so any
+// fp32 input meets the 1e-3 / 1e-4 tolerance against the reference's fp32 loop
+// (src/kernels/gemm_quant.cpp:54-82).  int32 partial sums are converted to
+// fp32 at every quantisation group (at most every 128 k), multiplied by the
+// group scale and accumulated in fp32.
 //
-// K is split over blockIdx.y so that every SM holds 3-4 CTAs with their whole
-// K-chunk in flight.  Each split writes its partial [M, 128] tile to the
-// context's scratch arena; the last split to arrive for a column tile (a
-// self-resetting counter) sums the partials in fixed order and applies
-// alpha/beta, so the result is deterministic and C is written once.
-#include <cuda_fp16.h>
-
+// K is split over blockIdx.y so that every SM holds 3-4 CTAs.  Each split
+// writes its partial [M, 128] tile to the context's scratch arena; the last
+// split to arrive for a column tile (a self-resetting counter) sums the
+// partials in fixed order and applies alpha/beta, so the result is
+// deterministic and C is written once.
 #include <cstdlib>
 
 #include "common.cuh"
@@ -49,8 +51,7 @@ constexpr int GV_NSTAGE = 4;
 constexpr int GV_CONSUMER_WARPS = 8;
 constexpr int GV_THREADS = (GV_CONSUMER_WARPS + 1) * 32;   // + one producer warp
 constexpr int GV_MAX_SPLIT = 32;
-
-// ---- PTX wrappers (mbarrier / TMA live in ptx.cuh) --------------------------------
+constexpr int GV_MAX_M = 16;
 
 using ptx::smem_u32;
 
@@ -60,40 +61,19 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4
                  : "r"(addr));
 }
 
-__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
-                                          uint32_t a3, uint32_t b0, uint32_t b1) {
+__device__ __forceinline__ void mma_s8_16832(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                             uint32_t b0, uint32_t b1) {
     asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
         "{%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
-__device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
-
-// Two int4 nibbles (bits 0-3 of each 16-bit half of `w`, two's complement) ->
-// exact fp16 pair: (nib ^ 8) | 0x6400 is the fp16 number 1032 + q.
-__device__ __forceinline__ uint32_t nib_lo_to_h2(uint32_t w) {
-    const uint32_t t = (w & 0x000f000fu) ^ 0x64086408u;
-    return h2_as_u32(__hsub2(u32_as_h2(t), u32_as_h2(0x64086408u)));
+// exact int32 -> fp32 for |v| < 2^22 without the conversion pipe
+__device__ __forceinline__ float small_int_to_float(int v) {
+    return __int_as_float(v + 0x4B400000) - 12582912.0f;
 }
-// Nibbles in bits 4-7 of each half: ((w & 0xf0) ^ 0x80) | 0x6400 = 1152 + 16 q;
-// one fused multiply-add (x/16 - 72) gives q exactly.
-__device__ __forceinline__ uint32_t nib_hi_to_h2(uint32_t w) {
-    const uint32_t t = (w & 0x00f000f0u) ^ 0x64806480u;
-    return h2_as_u32(__hfma2(u32_as_h2(t), u32_as_h2(0x2c002c00u) /* 1/16 */,
-                             u32_as_h2(0xd480d480u) /* -72 */));
-}
-// Two int8 values in bytes `sel` of w (already xor 0x80) -> exact fp16 pair:
-// byte | 0x6400 is 1024 + (q + 128).
-template <uint32_t SEL>
-__device__ __forceinline__ uint32_t i8pair_to_h2(uint32_t w_biased) {
-    const uint32_t t = __byte_perm(w_biased, 0x64646464u, SEL);
-    return h2_as_u32(__hsub2(u32_as_h2(t), u32_as_h2(0x64806480u)));
-}
-
-// ---- the kernel ----------------------------------------------------------------
 
 struct GemvParams {
     const float* A;        // [M, K]
@@ -110,26 +90,26 @@ struct GemvParams {
     int* status;
 };
 
-// WBITS: 4 or 8.  JB: number of 8-column activation blocks (M <= 4*JB).
+// WBITS: 4 or 8.  JB: number of 8-column activation blocks; 3 digit columns per
+// row of A, so M <= (8 * JB) / 3.
 template <int WBITS, int JB>
-__global__ void __launch_bounds__(GV_THREADS, (JB == 4) ? 3 : 4)
+__global__ void __launch_bounds__(GV_THREADS, (JB >= 6) ? 2 : 4)
 gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
     constexpr int K_PER_ROW = (WBITS == 4) ? 2 : 1;
     constexpr int K_PER_STAGE = GV_ROWS * K_PER_ROW;
-    constexpr int KB_PER_STAGE = K_PER_STAGE / 16;        // k16 blocks per stage: 8 (W4), 4 (W8)
-    constexpr int NJ = 8 * JB;                            // activation columns (2 per row of A)
-    constexpr int MROWS = 4 * JB;
+    constexpr int KB_PER_STAGE = K_PER_STAGE / 32;        // k32 blocks per stage: 4 (W4), 2 (W8)
+    constexpr int NJ = 8 * JB;                            // digit columns
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* tiles = smem;                                             // GV_NSTAGE * 8 KiB
-    float* part = reinterpret_cast<float*>(smem + GV_NSTAGE * GV_STAGE_BYTES);   // [MROWS][128]
-    float* inv_s = part + MROWS * GV_COLS;                             // [16]
+    float* part = reinterpret_cast<float*>(smem + GV_NSTAGE * GV_STAGE_BYTES);   // [NJ][128]
+    float* inv_s = part + NJ * GV_COLS;                                // [16]
     unsigned* rowmax = reinterpret_cast<unsigned*>(inv_s + 16);        // [16] max|a| bits per row
     uint64_t* bars = reinterpret_cast<uint64_t*>(rowmax + 16);         // full[4], empty[4]
     int* flags = reinterpret_cast<int*>(bars + 2 * GV_NSTAGE);         // [0] abort, [1] is-last
     float* sscale = reinterpret_cast<float*>(flags + 4);               // W4: [groups_per_cta][128] group scales
-    __half* bfrag = reinterpret_cast<__half*>(sscale + p.groups_per_cta * GV_COLS);   // [kb][NJ][4][4]
+    uint8_t* dfrag = reinterpret_cast<uint8_t*>(sscale + p.groups_per_cta * GV_COLS);   // [kb32][NJ][32]
     volatile int* abort_flag = flags;
 
     const int ks = blockIdx.y;
@@ -140,7 +120,7 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
     const int stage_end = min(stage_begin + p.stages_per_cta, p.stages_total);
     const int n_stages = stage_end - stage_begin;
     const int k_begin = stage_begin * K_PER_STAGE;
-    const int k_count = n_stages * K_PER_STAGE;            // multiple of 16; may run past K
+    const int k_count = n_stages * K_PER_STAGE;            // multiple of 32; may run past K
 
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + GV_NSTAGE);
     // The producer thread sets the barriers up and puts the first GV_NSTAGE stages
@@ -163,11 +143,7 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
     if (threadIdx.x < 16) rowmax[threadIdx.x] = 0u;
     __syncthreads();
 
-    // Activation prologue (all threads, overlapped with the loads in flight):
-    // every live row of this CTA's K-chunk is scaled by a power of two into fp16
-    // range, split into hi + lo and stored in B-fragment order.  Columns of rows
-    // m >= M are left as they are: an MMA column only feeds its own output
-    // column, and those are never read.
+    // ---- prologue, overlapped with the loads in flight ---------------------------
     // W4: this CTA's panel of group scales, [groups][128 columns], coalesced
     const int g_first = (WBITS == 4) ? k_begin / p.G : 0;
     if (WBITS == 4) {
@@ -179,6 +155,9 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
             *reinterpret_cast<float4*>(sscale + gl * GV_COLS + c) = v;
         }
     }
+    // Activations: row maxima of this CTA's K-chunk, then three 7-bit digits per
+    // element in MMA-operand order.  Digit columns of rows m >= M are left as
+    // they are: an MMA column only feeds its own output column, never read.
     const int q4 = k_count >> 2;                           // float4 per row
     const int n4 = p.M * q4;
     for (int i = threadIdx.x; i < n4; i += GV_THREADS) {
@@ -193,9 +172,9 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
     __syncthreads();
     for (int i = threadIdx.x; i < n4; i += GV_THREADS) {
         const int m = i / q4, k = (i - m * q4) * 4;
-        // power-of-two factor taking max|a| into [2^13, 2^14); exponent clamped
+        // power-of-two factor taking max|a| into [2^19, 2^20); exponent clamped
         const unsigned mb = rowmax[m];
-        int se = mb ? 267 - static_cast<int>((mb >> 23) & 0xff) : 127;
+        int se = mb ? 273 - static_cast<int>((mb >> 23) & 0xff) : 127;     // 127 + 19 - (e - 127)
         se = max(1, min(253, se));
         const float sc = __uint_as_float(static_cast<uint32_t>(se) << 23);
         if (k == 0) inv_s[m] = __uint_as_float(static_cast<uint32_t>(254 - se) << 23);
@@ -203,70 +182,79 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
         if (k_begin + k < p.K)
             v = *reinterpret_cast<const float4*>(p.A + static_cast<int64_t>(m) * p.K + k_begin + k);
         const float x[4] = {v.x * sc, v.y * sc, v.z * sc, v.w * sc};
-        unsigned short hi[4], lo[4];
+        uint32_t d1 = 0, d2 = 0, d3 = 0;                  // 4 digits each, one byte per element
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const __half h = __float2half_rn(x[j]);
-            hi[j] = __half_as_ushort(h);
-            lo[j] = __half_as_ushort(__float2half_rn(x[j] - __half2float(h)));
+            int iv = __float2int_rn(fminf(fmaxf(x[j], -1048576.0f), 1048576.0f));
+            const int lo = ((iv + 64) & 127) - 64;
+            iv = (iv - lo) >> 7;
+            const int mid = ((iv + 64) & 127) - 64;
+            const int hi = (iv - mid) >> 7;
+            d1 |= static_cast<uint32_t>(hi & 0xff) << (8 * j);
+            d2 |= static_cast<uint32_t>(mid & 0xff) << (8 * j);
+            d3 |= static_cast<uint32_t>(lo & 0xff) << (8 * j);
         }
-        const int kb = k >> 4, kin = k & 15;
+        const int kb = k >> 5, kin = k & 31, half = kin >> 4, r = kin & 15;
+        uint8_t* base = dfrag + (kb * NJ + 3 * m) * 32 + half * 4;
         if (WBITS == 4) {
-            // fragment slot t = kin/4 holds k+{0,2,1,3}: one 8-byte store per column
-            __half* d = bfrag + ((kb * NJ + 2 * m) * 4 + (kin >> 2)) * 4;
-            *reinterpret_cast<uint2*>(d) = make_uint2(hi[0] | (static_cast<uint32_t>(hi[2]) << 16),
-                                                      hi[1] | (static_cast<uint32_t>(hi[3]) << 16));
-            *reinterpret_cast<uint2*>(d + 16) = make_uint2(lo[0] | (static_cast<uint32_t>(lo[2]) << 16),
-                                                           lo[1] | (static_cast<uint32_t>(lo[3]) << 16));
+            // thread slot t = r / 4 holds k0 + 4t .. 4t+3 (and +16 in the second word)
+            uint8_t* d = base + (r >> 2) * 8;
+            *reinterpret_cast<uint32_t*>(d) = d1;
+            *reinterpret_cast<uint32_t*>(d + 32) = d2;
+            *reinterpret_cast<uint32_t*>(d + 64) = d3;
         } else {
-            // slot t holds k0+{2t, 2t+1, 8+2t, 9+2t}: (k, k+1) and (k+2, k+3) go to slots t, t+1
-            const int t0 = (kin & 7) >> 1, e = (kin >> 3) << 1;
-            __half* d = bfrag + ((kb * NJ + 2 * m) * 4 + t0) * 4 + e;
-            *reinterpret_cast<uint32_t*>(d) = hi[0] | (static_cast<uint32_t>(hi[1]) << 16);
-            *reinterpret_cast<uint32_t*>(d + 4) = hi[2] | (static_cast<uint32_t>(hi[3]) << 16);
-            *reinterpret_cast<uint32_t*>(d + 16) = lo[0] | (static_cast<uint32_t>(lo[1]) << 16);
-            *reinterpret_cast<uint32_t*>(d + 20) = lo[2] | (static_cast<uint32_t>(lo[3]) << 16);
+            // slot t holds k0 + {2t, 2t+1, 8+2t, 9+2t}: elements (k, k+1) -> slot t0,
+            // (k+2, k+3) -> slot t0 + 1, bytes 0-1 (r < 8) or 2-3 (r >= 8)
+            uint8_t* d = base + ((r & 7) >> 1) * 8 + ((r >> 3) << 1);
+            *reinterpret_cast<uint16_t*>(d) = static_cast<uint16_t>(d1);
+            *reinterpret_cast<uint16_t*>(d + 8) = static_cast<uint16_t>(d1 >> 16);
+            *reinterpret_cast<uint16_t*>(d + 32) = static_cast<uint16_t>(d2);
+            *reinterpret_cast<uint16_t*>(d + 40) = static_cast<uint16_t>(d2 >> 16);
+            *reinterpret_cast<uint16_t*>(d + 64) = static_cast<uint16_t>(d3);
+            *reinterpret_cast<uint16_t*>(d + 72) = static_cast<uint16_t>(d3 >> 16);
         }
     }
     __syncthreads();
 
-    float out[JB][4];
-#pragma unroll
-    for (int jb = 0; jb < JB; ++jb)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) out[jb][i] = 0.0f;
-
+    // ---- main loop ------------------------------------------------------------------
     if (warp < GV_CONSUMER_WARPS) {
         const int g = lane >> 2, t = lane & 3;
-        const int n_a = col0 + warp * 16 + 2 * g;           // this thread's two output columns
-        float acc[JB][4];
+        float out[JB][4];
+        int acc[JB][4];
 #pragma unroll
         for (int jb = 0; jb < JB; ++jb)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) acc[jb][i] = 0.0f;
-        float ch0 = 0.0f, ch1 = 0.0f;                      // W8: per-channel scales, fetched ahead of the loop
-        if (WBITS == 8) {
-            if (n_a < p.N) ch0 = p.scales[n_a];
-            if (n_a + 1 < p.N) ch1 = p.scales[n_a + 1];
-        }
-        const int kb_per_group = (WBITS == 4) ? p.G / 16 : 0x7fffffff;
-        int kb_in_group = (WBITS == 4) ? (k_begin / 16) % kb_per_group : 0;
-        // ldmatrix row address: matrix (lane / 8), row (lane % 8); 16-byte chunk = warp, swizzled
+            for (int i = 0; i < 4; ++i) { out[jb][i] = 0.0f; acc[jb][i] = 0; }
+        // int32 sums are folded into fp32 every `flush_every` k32-blocks: at the end
+        // of each quantisation group, and at least every 128 k (keeps |acc| < 2^22)
+        const int flush_every = (WBITS == 4) ? min(p.G, 128) / 32 : 4;
+        int since_flush = 0;
         const int lrow = lane & 7, lmat = lane >> 3;
-        // end of a quantisation group (or of this CTA's chunk): fold the scale
-        // of the group that k16-block `kb` belongs to into the running output
-        auto flush_group = [&](int kb) {
-            const int gl = (k_begin + kb * 16) / p.G - g_first;
-            const float2 sv = *reinterpret_cast<const float2*>(sscale + gl * GV_COLS + warp * 16 + 2 * g);
-            const float s0 = sv.x, s1 = sv.y;
+        const uint8_t* dthread = dfrag + g * 32 + t * 8;   // + (kb * NJ + jb * 8) * 32
+
+        auto flush = [&](int kb) {
+            float s0 = 1.0f, s1 = 1.0f;
+            if (WBITS == 4) {
+                const int gl = (k_begin + kb * 32) / p.G - g_first;
+                const float2 sv = *reinterpret_cast<const float2*>(sscale + gl * GV_COLS + warp * 16 + 2 * g);
+                s0 = sv.x; s1 = sv.y;
+            }
 #pragma unroll
             for (int jb = 0; jb < JB; ++jb) {
-                out[jb][0] = fmaf(s0, acc[jb][0], out[jb][0]);
-                out[jb][1] = fmaf(s0, acc[jb][1], out[jb][1]);
-                out[jb][2] = fmaf(s1, acc[jb][2], out[jb][2]);
-                out[jb][3] = fmaf(s1, acc[jb][3], out[jb][3]);
-                acc[jb][0] = acc[jb][1] = acc[jb][2] = acc[jb][3] = 0.0f;
+                out[jb][0] = fmaf(s0, small_int_to_float(acc[jb][0]), out[jb][0]);
+                out[jb][1] = fmaf(s0, small_int_to_float(acc[jb][1]), out[jb][1]);
+                out[jb][2] = fmaf(s1, small_int_to_float(acc[jb][2]), out[jb][2]);
+                out[jb][3] = fmaf(s1, small_int_to_float(acc[jb][3]), out[jb][3]);
+                acc[jb][0] = acc[jb][1] = acc[jb][2] = acc[jb][3] = 0;
             }
+        };
+        auto mma_block = [&](int kb, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3) {
+#pragma unroll
+            for (int jb = 0; jb < JB; ++jb) {
+                const uint2 b = *reinterpret_cast<const uint2*>(dthread + (kb * NJ + jb * 8) * 32);
+                mma_s8_16832(acc[jb], a0, a1, a2, a3, b.x, b.y);
+            }
+            if (++since_flush == flush_every) { since_flush = 0; flush(kb); }
         };
 
         for (int ls = 0; ls < n_stages; ++ls) {
@@ -282,73 +270,42 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive(empty0 + 8 * slot);
                 }
+                // register x[j]: bytes {row 2t: col 2g, col 2g+1; row 2t+1: col 2g, col 2g+1}
+                // of byte-rows 8j .. 8j+7 of this 32-row block
                 if (WBITS == 4) {
+                    uint32_t p0[4], p1[4];     // 4 consecutive k of column 2g / 2g+1, as int8 = 16*q
 #pragma unroll
-                    for (int mat = 0; mat < 4; ++mat) {
-                        const int kb = ls * KB_PER_STAGE + half * 4 + mat;
-                        const uint32_t a0 = nib_lo_to_h2(x[mat]);
-                        const uint32_t a2 = nib_hi_to_h2(x[mat]);
-                        const uint32_t a1 = nib_lo_to_h2(x[mat] >> 8);
-                        const uint32_t a3 = nib_hi_to_h2(x[mat] >> 8);
-#pragma unroll
-                        for (int jb = 0; jb < JB; ++jb) {
-                            const uint2 b = *reinterpret_cast<const uint2*>(
-                                bfrag + ((kb * NJ + jb * 8 + g) * 4 + t) * 4);
-                            mma_16816(acc[jb], a0, a1, a2, a3, b.x, b.y);
-                        }
-                        if (++kb_in_group == kb_per_group) {
-                            kb_in_group = 0;
-                            flush_group(kb);
-                        }
+                    for (int j = 0; j < 4; ++j) {
+                        const uint32_t lo = (x[j] << 4) & 0xf0f0f0f0u;     // even k
+                        const uint32_t hi = x[j] & 0xf0f0f0f0u;            // odd k
+                        p0[j] = __byte_perm(lo, hi, 0x6240);
+                        p1[j] = __byte_perm(lo, hi, 0x7351);
                     }
+                    const int kb = ls * KB_PER_STAGE + half * 2;
+                    mma_block(kb, p0[0], p1[0], p0[1], p1[1]);
+                    mma_block(kb + 1, p0[2], p1[2], p0[3], p1[3]);
                 } else {
-#pragma unroll
-                    for (int pr = 0; pr < 2; ++pr) {
-                        const int kb = ls * KB_PER_STAGE + half * 2 + pr;
-                        const uint32_t w0 = x[2 * pr] ^ 0x80808080u;
-                        const uint32_t w1 = x[2 * pr + 1] ^ 0x80808080u;
-                        const uint32_t a0 = i8pair_to_h2<0x4240>(w0);
-                        const uint32_t a1 = i8pair_to_h2<0x4341>(w0);
-                        const uint32_t a2 = i8pair_to_h2<0x4240>(w1);
-                        const uint32_t a3 = i8pair_to_h2<0x4341>(w1);
-#pragma unroll
-                        for (int jb = 0; jb < JB; ++jb) {
-                            const uint2 b = *reinterpret_cast<const uint2*>(
-                                bfrag + ((kb * NJ + jb * 8 + g) * 4 + t) * 4);
-                            mma_16816(acc[jb], a0, a1, a2, a3, b.x, b.y);
-                        }
-                    }
+                    // k-slots 4t..4t+3 <- rows {2t, 2t+1} of matrices 0 and 1; 16+4t.. <- matrices 2 and 3
+                    const uint32_t a0 = __byte_perm(x[0], x[1], 0x6420), a1 = __byte_perm(x[0], x[1], 0x7531);
+                    const uint32_t a2 = __byte_perm(x[2], x[3], 0x6420), a3 = __byte_perm(x[2], x[3], 0x7531);
+                    mma_block(ls * KB_PER_STAGE + half, a0, a1, a2, a3);
                 }
             }
         }
-        if (WBITS == 4 && kb_in_group != 0 && n_stages > 0) flush_group(n_stages * KB_PER_STAGE - 1);
+        if (since_flush != 0 && n_stages > 0) flush(n_stages * KB_PER_STAGE - 1);
+        // per-column partial sums of this warp's 16 columns: column j of the operand
+        // = digit (j % 3) of row j / 3
+        float c0 = 1.0f, c1 = 1.0f;
         if (WBITS == 8) {
-            const float s0 = ch0, s1 = ch1;
-#pragma unroll
-            for (int jb = 0; jb < JB; ++jb) {
-                out[jb][0] = s0 * acc[jb][0]; out[jb][1] = s0 * acc[jb][1];
-                out[jb][2] = s1 * acc[jb][2]; out[jb][3] = s1 * acc[jb][3];
-            }
+            const int n_a = col0 + warp * 16 + 2 * g;
+            c0 = (n_a < p.N) ? p.scales[n_a] : 0.0f;
+            c1 = (n_a + 1 < p.N) ? p.scales[n_a + 1] : 0.0f;
         }
-        // hi + lo columns of row m = 4*jb + t, undo the activation scaling; rows of
-        // this split go straight to C (one split) or to the scratch partials
 #pragma unroll
         for (int jb = 0; jb < JB; ++jb) {
-            const int m = 4 * jb + t;
-            if (m < p.M && n_a < p.N) {
-                const float is = inv_s[m];
-                float2 v;
-                v.x = is * (out[jb][0] + out[jb][1]);
-                v.y = is * (out[jb][2] + out[jb][3]);
-                if (p.splits == 1) {
-                    float* cp = p.C + static_cast<int64_t>(m) * p.N + n_a;
-                    if (p.beta == 0.0f) { v.x *= p.alpha; v.y *= p.alpha; }
-                    else { v.x = fmaf(p.beta, cp[0], p.alpha * v.x); v.y = fmaf(p.beta, cp[1], p.alpha * v.y); }
-                    *reinterpret_cast<float2*>(cp) = v;       // N % 16 == 0: both columns exist, 8-byte aligned
-                } else {
-                    *reinterpret_cast<float2*>(p.partial + (static_cast<int64_t>(ks) * p.M + m) * p.N + n_a) = v;
-                }
-            }
+            float* d = part + (jb * 8 + 2 * t) * GV_COLS + warp * 16 + 2 * g;
+            *reinterpret_cast<float2*>(d) = make_float2(c0 * out[jb][0], c1 * out[jb][2]);
+            *reinterpret_cast<float2*>(d + GV_COLS) = make_float2(c0 * out[jb][1], c1 * out[jb][3]);
         }
     } else if (lane == 0) {
         // producer: refill ring slots as the consumers release them
@@ -370,6 +327,36 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
             }
         }
     }
+    __syncthreads();
+
+    // ---- combine the three digit columns of every row; write C or the split's partial ----
+    const int ncol = min(GV_COLS, p.N - col0);            // multiple of 16
+    const float digit_unit = (WBITS == 4) ? 0.0625f : 1.0f;    // int4 nibbles were carried as 16*q
+    for (int i = threadIdx.x; i < p.M * (ncol >> 2); i += GV_THREADS) {
+        const int m = i / (ncol >> 2), c = (i % (ncol >> 2)) * 4;
+        const float4 h = *reinterpret_cast<const float4*>(part + (3 * m) * GV_COLS + c);
+        const float4 md = *reinterpret_cast<const float4*>(part + (3 * m + 1) * GV_COLS + c);
+        const float4 l = *reinterpret_cast<const float4*>(part + (3 * m + 2) * GV_COLS + c);
+        const float is = inv_s[m] * digit_unit;
+        float4 v;
+        v.x = is * fmaf(16384.0f, h.x, fmaf(128.0f, md.x, l.x));
+        v.y = is * fmaf(16384.0f, h.y, fmaf(128.0f, md.y, l.y));
+        v.z = is * fmaf(16384.0f, h.z, fmaf(128.0f, md.z, l.z));
+        v.w = is * fmaf(16384.0f, h.w, fmaf(128.0f, md.w, l.w));
+        if (p.splits == 1) {
+            float4* cp = reinterpret_cast<float4*>(p.C + static_cast<int64_t>(m) * p.N + col0 + c);
+            if (p.beta == 0.0f) {
+                v.x *= p.alpha; v.y *= p.alpha; v.z *= p.alpha; v.w *= p.alpha;
+            } else {
+                const float4 o = *cp;
+                v.x = fmaf(p.beta, o.x, p.alpha * v.x); v.y = fmaf(p.beta, o.y, p.alpha * v.y);
+                v.z = fmaf(p.beta, o.z, p.alpha * v.z); v.w = fmaf(p.beta, o.w, p.alpha * v.w);
+            }
+            *cp = v;
+        } else {
+            *reinterpret_cast<float4*>(p.partial + (static_cast<int64_t>(ks) * p.M + m) * p.N + col0 + c) = v;
+        }
+    }
     if (p.splits == 1) return;
 
     // Split-K epilogue: the last split to arrive for this column tile sums the
@@ -384,7 +371,6 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
     __syncthreads();
     if (!flags[1]) return;
     __threadfence();
-    const int ncol = min(GV_COLS, p.N - col0);
     for (int i = threadIdx.x; i < p.M * (ncol >> 2); i += GV_THREADS) {
         const int m = i / (ncol >> 2), c = (i % (ncol >> 2)) * 4;
         float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -412,10 +398,10 @@ static int gemv_groups_per_cta(int wbits, int k_per_cta, int G) {
 }
 
 static size_t gemv_smem_bytes(int wbits, int jb, int k_per_cta, int G) {
-    const size_t nj = 8 * jb, mrows = 4 * jb;
-    return 1024 + GV_NSTAGE * GV_STAGE_BYTES + mrows * GV_COLS * 4 + 16 * 4 + 16 * 4 + 2 * GV_NSTAGE * 8 + 16 +
+    const size_t nj = 8 * jb;
+    return 1024 + GV_NSTAGE * GV_STAGE_BYTES + nj * GV_COLS * 4 + 16 * 4 + 16 * 4 + 2 * GV_NSTAGE * 8 + 16 +
            static_cast<size_t>(gemv_groups_per_cta(wbits, k_per_cta, G)) * GV_COLS * 4 +
-           static_cast<size_t>(k_per_cta) * nj * 2;
+           static_cast<size_t>(k_per_cta) * nj;
 }
 
 struct GemvPlan { int splits; int stages_total; int stages_per_cta; size_t smem; bool ok; };
@@ -423,7 +409,7 @@ struct GemvPlan { int splits; int stages_total; int stages_per_cta; size_t smem;
 // Pick the K split.  A CTA costs its stage count plus a fixed overhead (launch,
 // activation prologue, partial write-out, about three stages' worth); the grid
 // should fit in one wave of ~4 CTAs per SM.  The shared-memory budget (the
-// activation fragments grow with the chunk length) bounds the chunk from above.
+// activation digits grow with the chunk length) bounds the chunk from above.
 static GemvPlan plan_gemv(int wbits, int jb, int N, int K, int G, int sm_count) {
     GemvPlan best{};
     const int k_per_stage = GV_ROWS * (wbits == 4 ? 2 : 1);
@@ -438,7 +424,7 @@ static GemvPlan plan_gemv(int wbits, int jb, int N, int K, int G, int sm_count) 
         const int splits = ceil_div(stages_total, spc);
         const size_t smem = gemv_smem_bytes(wbits, jb, spc * k_per_stage, G);
         if (smem > 200 * 1024) continue;
-        const int per_sm = std::max(1, std::min(4, static_cast<int>((220 * 1024) / smem)));
+        const int per_sm = std::max(1, std::min(jb >= 6 ? 2 : 4, static_cast<int>((220 * 1024) / smem)));
         const int waves = ceil_div(col_tiles * splits, sm_count * per_sm);
         const double cost = waves * (spc + 3.0) + 0.05 * splits;
         if (cost < best_cost) {
@@ -450,18 +436,19 @@ static GemvPlan plan_gemv(int wbits, int jb, int N, int K, int G, int sm_count) 
     return best;
 }
 
-static int jb_for(int M) { return M <= 4 ? 1 : (M <= 8 ? 2 : 4); }
+static int jb_for(int M) { return M <= 2 ? 1 : (M <= 5 ? 2 : (M <= 8 ? 3 : 6)); }
 
 bool w4a16_fast_ok(int M, int N, int K, int G) {
-    if (M < 1 || (N % 16) != 0 || (K % 16) != 0 || (G % 16) != 0 || (K % G) != 0) return false;
+    if (M < 1 || (N % 16) != 0 || (K % 32) != 0 || (G % 32) != 0 || (K % G) != 0) return false;
+    if (G > 128 && (G % 128) != 0) return false;  // int32 sums are folded every 128 k at the latest
     if (M > 64) return false;                     // larger M: generic path (dense GEMM territory)
-    return plan_gemv(4, jb_for(M > 16 ? 16 : M), N, K, G, 148).ok;
+    return plan_gemv(4, jb_for(std::min(M, GV_MAX_M)), N, K, G, 148).ok;
 }
 
 bool w8a16_fast_ok(int M, int N, int K) {
-    if (M < 1 || (N % 16) != 0 || (K % 16) != 0) return false;
+    if (M < 1 || (N % 16) != 0 || (K % 32) != 0) return false;
     if (M > 64) return false;
-    return plan_gemv(8, jb_for(M > 16 ? 16 : M), N, K, 1, 148).ok;
+    return plan_gemv(8, jb_for(std::min(M, GV_MAX_M)), N, K, 1, 148).ok;
 }
 
 template <int WBITS, int JB>
@@ -493,8 +480,8 @@ static int launch_gemv(lhb_ctx* ctx, const float* A, const void* B, const float*
     TensorMap tm;
     if (int e = get_tensor_map_2d_u8(ctx, B, rows, N, N, GV_ROWS, GV_COLS, true, &tm)) return e;
     // rows of A are independent: M > 16 is served in slabs of 16 rows
-    for (int m0 = 0; m0 < M; m0 += 16) {
-        const int m = std::min(16, M - m0);
+    for (int m0 = 0; m0 < M; m0 += GV_MAX_M) {
+        const int m = std::min(GV_MAX_M, M - m0);
         const int jb = jb_for(m);
         GemvPlan pl = plan_gemv(WBITS, jb, N, K, WBITS == 4 ? G : 1, ctx->sm_count);
         if (!pl.ok) return LHB_ERR_UNSUPPORTED;
@@ -509,7 +496,8 @@ static int launch_gemv(lhb_ctx* ctx, const float* A, const void* B, const float*
         int e;
         if (jb == 1) e = launch_gemv_t<WBITS, 1>(ctx, tm, p, pl, st);
         else if (jb == 2) e = launch_gemv_t<WBITS, 2>(ctx, tm, p, pl, st);
-        else e = launch_gemv_t<WBITS, 4>(ctx, tm, p, pl, st);
+        else if (jb == 3) e = launch_gemv_t<WBITS, 3>(ctx, tm, p, pl, st);
+        else e = launch_gemv_t<WBITS, 6>(ctx, tm, p, pl, st);
         if (e) return e;
     }
     return LHB_OK;
