@@ -93,7 +93,7 @@ struct GemvParams {
 // WBITS: 4 or 8.  JB: number of 8-column activation blocks; 3 digit columns per
 // row of A, so M <= (8 * JB) / 3.
 template <int WBITS, int JB>
-__global__ void __launch_bounds__(GV_THREADS, (JB >= 6) ? 2 : 4)
+__global__ void __launch_bounds__(GV_THREADS, (JB >= 6) ? 2 : (JB == 3 ? 3 : 4))
 gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
     constexpr int K_PER_ROW = (WBITS == 4) ? 2 : 1;
     constexpr int K_PER_STAGE = GV_ROWS * K_PER_ROW;
@@ -141,6 +141,12 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
         }
     }
     if (threadIdx.x < 16) rowmax[threadIdx.x] = 0u;
+    // Programmatic dependent launch: the weight loads above depend on nothing an
+    // earlier kernel in the stream writes, so they are already in flight while
+    // that kernel drains; everything below (activations, C, scratch, counters)
+    // waits for it to finish.  The next kernel may be scheduled from here on.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     __syncthreads();
 
     // ---- prologue, overlapped with the loads in flight ---------------------------
@@ -160,18 +166,31 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
     // they are: an MMA column only feeds its own output column, never read.
     const int q4 = k_count >> 2;                           // float4 per row
     const int n4 = p.M * q4;
-    for (int i = threadIdx.x; i < n4; i += GV_THREADS) {
-        const int m = i / q4, k = (i - m * q4) * 4;
+    const int n4_pad = (n4 + 31) & ~31;                    // whole warps take part in the shuffles
+    const float inv_q4 = 1.0f / static_cast<float>(q4 > 0 ? q4 : 1);
+    for (int i = threadIdx.x; i < n4_pad; i += GV_THREADS) {
+        const bool valid = i < n4;
+        // row index without an integer division: (i + 0.5) / q4 is never within
+        // 0.5 / q4 of an integer, far more than the float error at these sizes
+        const int m = valid ? min(p.M - 1, __float2int_rz((static_cast<float>(i) + 0.5f) * inv_q4)) : -1;
+        const int k = (i - m * q4) * 4;
         float mx = 0.0f;
-        if (k_begin + k < p.K) {
+        if (valid && k_begin + k < p.K) {
             const float4 v = *reinterpret_cast<const float4*>(p.A + static_cast<int64_t>(m) * p.K + k_begin + k);
             mx = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
         }
-        if (mx > 0.0f) atomicMax(rowmax + m, __float_as_uint(mx));
+        const int m0 = __shfl_sync(0xffffffffu, m, 0);
+        if (__all_sync(0xffffffffu, m == m0)) {            // the usual case: one row per warp step
+            mx = warp_max(mx);
+            if (lane == 0 && m0 >= 0 && mx > 0.0f) atomicMax(rowmax + m0, __float_as_uint(mx));
+        } else if (valid && mx > 0.0f) {
+            atomicMax(rowmax + m, __float_as_uint(mx));
+        }
     }
     __syncthreads();
     for (int i = threadIdx.x; i < n4; i += GV_THREADS) {
-        const int m = i / q4, k = (i - m * q4) * 4;
+        const int m = min(p.M - 1, __float2int_rz((static_cast<float>(i) + 0.5f) * inv_q4));
+        const int k = (i - m * q4) * 4;
         // power-of-two factor taking max|a| into [2^19, 2^20); exponent clamped
         const unsigned mb = rowmax[m];
         int se = mb ? 273 - static_cast<int>((mb >> 23) & 0xff) : 127;     // 127 + 19 - (e - 127)
@@ -228,14 +247,16 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
         // int32 sums are folded into fp32 every `flush_every` k32-blocks: at the end
         // of each quantisation group, and at least every 128 k (keeps |acc| < 2^22)
         const int flush_every = (WBITS == 4) ? min(p.G, 128) / 32 : 4;
+        const int group_blocks = (WBITS == 4) ? p.G / 32 : 0x7fffffff;     // k32-blocks per group
         int since_flush = 0;
+        int blk_in_group = (WBITS == 4) ? (k_begin / 32) % group_blocks : 0;
+        int gl = 0;                                        // group index relative to g_first
         const int lrow = lane & 7, lmat = lane >> 3;
         const uint8_t* dthread = dfrag + g * 32 + t * 8;   // + (kb * NJ + jb * 8) * 32
 
-        auto flush = [&](int kb) {
+        auto flush = [&]() {
             float s0 = 1.0f, s1 = 1.0f;
             if (WBITS == 4) {
-                const int gl = (k_begin + kb * 32) / p.G - g_first;
                 const float2 sv = *reinterpret_cast<const float2*>(sscale + gl * GV_COLS + warp * 16 + 2 * g);
                 s0 = sv.x; s1 = sv.y;
             }
@@ -254,7 +275,10 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
                 const uint2 b = *reinterpret_cast<const uint2*>(dthread + (kb * NJ + jb * 8) * 32);
                 mma_s8_16832(acc[jb], a0, a1, a2, a3, b.x, b.y);
             }
-            if (++since_flush == flush_every) { since_flush = 0; flush(kb); }
+            ++since_flush;
+            ++blk_in_group;
+            if (since_flush == flush_every || blk_in_group == group_blocks) { since_flush = 0; flush(); }
+            if (blk_in_group == group_blocks) { blk_in_group = 0; ++gl; }
         };
 
         for (int ls = 0; ls < n_stages; ++ls) {
@@ -292,7 +316,7 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
                 }
             }
         }
-        if (since_flush != 0 && n_stages > 0) flush(n_stages * KB_PER_STAGE - 1);
+        if (since_flush != 0) flush();
         // per-column partial sums of this warp's 16 columns: column j of the operand
         // = digit (j % 3) of row j / 3
         float c0 = 1.0f, c1 = 1.0f;
@@ -332,8 +356,9 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
     // ---- combine the three digit columns of every row; write C or the split's partial ----
     const int ncol = min(GV_COLS, p.N - col0);            // multiple of 16
     const float digit_unit = (WBITS == 4) ? 0.0625f : 1.0f;    // int4 nibbles were carried as 16*q
-    for (int i = threadIdx.x; i < p.M * (ncol >> 2); i += GV_THREADS) {
-        const int m = i / (ncol >> 2), c = (i % (ncol >> 2)) * 4;
+    for (int i = threadIdx.x; i < p.M * (GV_COLS / 4); i += GV_THREADS) {
+        const int m = i >> 5, c = (i & 31) * 4;
+        if (c >= ncol) continue;
         const float4 h = *reinterpret_cast<const float4*>(part + (3 * m) * GV_COLS + c);
         const float4 md = *reinterpret_cast<const float4*>(part + (3 * m + 1) * GV_COLS + c);
         const float4 l = *reinterpret_cast<const float4*>(part + (3 * m + 2) * GV_COLS + c);
@@ -371,8 +396,9 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
     __syncthreads();
     if (!flags[1]) return;
     __threadfence();
-    for (int i = threadIdx.x; i < p.M * (ncol >> 2); i += GV_THREADS) {
-        const int m = i / (ncol >> 2), c = (i % (ncol >> 2)) * 4;
+    for (int i = threadIdx.x; i < p.M * (GV_COLS / 4); i += GV_THREADS) {
+        const int m = i >> 5, c = (i & 31) * 4;
+        if (c >= ncol) continue;
         float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int r = 0; r < p.splits; ++r) {
             const float4 v = __ldcg(reinterpret_cast<const float4*>(
@@ -467,9 +493,18 @@ static int launch_gemv_t(lhb_ctx* ctx, const TensorMap& tm, GemvParams p, const 
     p.partial = reinterpret_cast<float*>(ctx->scratch);
     p.counters = ctx->counters;
     p.status = ctx->status_word;
-    const dim3 grid(ceil_div(p.N, GV_COLS), pl.splits, 1);
-    kern<<<grid, GV_THREADS, pl.smem, st>>>(tm, p);
-    LHB_LAUNCH_CHECK();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ceil_div(p.N, GV_COLS), pl.splits, 1);
+    cfg.blockDim = dim3(GV_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = pl.smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    static const bool pdl = !(getenv("LHB_PDL") && atoi(getenv("LHB_PDL")) == 0);
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    LHB_CUDA(cudaLaunchKernelEx(&cfg, kern, tm, p));
     return LHB_OK;
 }
 
