@@ -8,8 +8,8 @@
 // The path is HBM-bound: the weight bytes are read exactly once, so the kernel
 // is built to spend as few issue slots per weight as possible.
 //
-//   TMA (2-D, 128-byte swizzle)  global -> shared, 64 rows x 128 columns per
-//       stage, 4-deep ring, the first four stages of a CTA in flight at once;
+//   TMA (2-D, 128-byte swizzle)  global -> shared, two 64-row x 128-column boxes
+//       per stage (a CTA owns 256 columns), 3-deep ring, all of it in flight at once;
 //   ldmatrix.trans on the raw bytes: one 8x8 b16 matrix = 8 byte-rows x 16
 //       columns; the transposed fragment hands every thread the bytes of two
 //       adjacent columns at two consecutive rows;
@@ -31,7 +31,7 @@
 // fp32 at every quantisation group (at most every 128 k), multiplied by the
 // group scale and accumulated in fp32.
 //
-// K is split over blockIdx.y so that every SM holds 3-4 CTAs.  Each split
+// K is split over blockIdx.y so that every SM holds up to 3 CTAs.  Each split
 // writes its partial [M, 128] tile to the context's scratch arena; the last
 // split to arrive for a column tile (a self-resetting counter) sums the
 // partials in fixed order and applies alpha/beta, so the result is
@@ -44,10 +44,13 @@
 
 namespace lhb {
 
-constexpr int GV_COLS = 128;        // columns per CTA (TMA box inner extent, bytes)
+constexpr int GV_BOX_COLS = 128;    // TMA box inner extent (bytes = columns), one 128-byte swizzle row
+constexpr int GV_BOXES = 2;         // boxes side by side per stage
+constexpr int GV_COLS = GV_BOX_COLS * GV_BOXES;   // columns per CTA
 constexpr int GV_ROWS = 64;         // byte-rows per stage
-constexpr int GV_STAGE_BYTES = GV_COLS * GV_ROWS;
-constexpr int GV_NSTAGE = 4;
+constexpr int GV_BOX_BYTES = GV_BOX_COLS * GV_ROWS;
+constexpr int GV_STAGE_BYTES = GV_BOX_BYTES * GV_BOXES;
+constexpr int GV_NSTAGE = 3;
 constexpr int GV_CONSUMER_WARPS = 8;
 constexpr int GV_THREADS = (GV_CONSUMER_WARPS + 1) * 32;   // + one producer warp
 constexpr int GV_MAX_SPLIT = 32;
@@ -93,7 +96,7 @@ struct GemvParams {
 // WBITS: 4 or 8.  JB: number of 8-column activation blocks; 3 digit columns per
 // row of A, so M <= (8 * JB) / 3.
 template <int WBITS, int JB>
-__global__ void __launch_bounds__(GV_THREADS, (JB >= 6) ? 2 : (JB == 3 ? 3 : 4))
+__global__ void __launch_bounds__(GV_THREADS, (JB >= 6) ? 1 : (JB >= 2 ? 2 : 3))
 gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
     constexpr int K_PER_ROW = (WBITS == 4) ? 2 : 1;
     constexpr int K_PER_STAGE = GV_ROWS * K_PER_ROW;
@@ -102,13 +105,13 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* tiles = smem;                                             // GV_NSTAGE * 8 KiB
-    float* part = reinterpret_cast<float*>(smem + GV_NSTAGE * GV_STAGE_BYTES);   // [NJ][128]
+    uint8_t* tiles = smem;                                             // GV_NSTAGE * 16 KiB
+    float* part = reinterpret_cast<float*>(smem + GV_NSTAGE * GV_STAGE_BYTES);   // [NJ][256]
     float* inv_s = part + NJ * GV_COLS;                                // [16]
     unsigned* rowmax = reinterpret_cast<unsigned*>(inv_s + 16);        // [16] max|a| bits per row
-    uint64_t* bars = reinterpret_cast<uint64_t*>(rowmax + 16);         // full[4], empty[4]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(rowmax + 16);         // full[], empty[]
     int* flags = reinterpret_cast<int*>(bars + 2 * GV_NSTAGE);         // [0] abort, [1] is-last
-    float* sscale = reinterpret_cast<float*>(flags + 4);               // W4: [groups_per_cta][128] group scales
+    float* sscale = reinterpret_cast<float*>(flags + 4);               // W4: [groups_per_cta][256] group scales
     uint8_t* dfrag = reinterpret_cast<uint8_t*>(sscale + p.groups_per_cta * GV_COLS);   // [kb32][NJ][32]
     volatile int* abort_flag = flags;
 
@@ -136,8 +139,10 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
         const int first = min(n_stages, GV_NSTAGE);
         for (int s = 0; s < first; ++s) {
             ptx::mbar_expect_tx(full0 + 8 * s, GV_STAGE_BYTES);
-            ptx::tma_load_2d(smem_u32(tiles + s * GV_STAGE_BYTES), &tmB, col0, (stage_begin + s) * GV_ROWS,
-                             full0 + 8 * s);
+#pragma unroll
+            for (int b = 0; b < GV_BOXES; ++b)
+                ptx::tma_load_2d(smem_u32(tiles + s * GV_STAGE_BYTES + b * GV_BOX_BYTES), &tmB,
+                                 col0 + b * GV_BOX_COLS, (stage_begin + s) * GV_ROWS, full0 + 8 * s);
         }
     }
     if (threadIdx.x < 16) rowmax[threadIdx.x] = 0u;
@@ -237,99 +242,122 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
 
     // ---- main loop ------------------------------------------------------------------
     if (warp < GV_CONSUMER_WARPS) {
+        // A warp owns two 16-column fragments f = 0, 1: columns 32*warp + 16*f .. +15 of
+        // the CTA, i.e. 16-byte chunks 2*(warp%4) + f of box warp/4.
         const int g = lane >> 2, t = lane & 3;
-        float out[JB][4];
-        int acc[JB][4];
+        const int box = warp >> 2, chunk0 = (warp & 3) * 2;
+        const int wcol = warp * 32 + 2 * g;                 // + 16*f: this thread's column pair in the CTA
+        float out[2][JB][4];
+        int acc[2][JB][4];
 #pragma unroll
-        for (int jb = 0; jb < JB; ++jb)
+        for (int f = 0; f < 2; ++f)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) { out[jb][i] = 0.0f; acc[jb][i] = 0; }
+            for (int jb = 0; jb < JB; ++jb)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) { out[f][jb][i] = 0.0f; acc[f][jb][i] = 0; }
         // int32 sums are folded into fp32 every `flush_every` k32-blocks: at the end
         // of each quantisation group, and at least every 128 k (keeps |acc| < 2^22)
         const int flush_every = (WBITS == 4) ? min(p.G, 128) / 32 : 4;
         const int group_blocks = (WBITS == 4) ? p.G / 32 : 0x7fffffff;     // k32-blocks per group
         int since_flush = 0;
         int blk_in_group = (WBITS == 4) ? (k_begin / 32) % group_blocks : 0;
-        int gl = 0;                                        // group index relative to g_first
+        const float* sthread = sscale + wcol;               // + gl * GV_COLS + 16 * f
         const int lrow = lane & 7, lmat = lane >> 3;
         const uint8_t* dthread = dfrag + g * 32 + t * 8;   // + (kb * NJ + jb * 8) * 32
 
         auto flush = [&]() {
-            float s0 = 1.0f, s1 = 1.0f;
-            if (WBITS == 4) {
-                const float2 sv = *reinterpret_cast<const float2*>(sscale + gl * GV_COLS + warp * 16 + 2 * g);
-                s0 = sv.x; s1 = sv.y;
-            }
 #pragma unroll
-            for (int jb = 0; jb < JB; ++jb) {
-                out[jb][0] = fmaf(s0, small_int_to_float(acc[jb][0]), out[jb][0]);
-                out[jb][1] = fmaf(s0, small_int_to_float(acc[jb][1]), out[jb][1]);
-                out[jb][2] = fmaf(s1, small_int_to_float(acc[jb][2]), out[jb][2]);
-                out[jb][3] = fmaf(s1, small_int_to_float(acc[jb][3]), out[jb][3]);
-                acc[jb][0] = acc[jb][1] = acc[jb][2] = acc[jb][3] = 0;
+            for (int f = 0; f < 2; ++f) {
+                float s0 = 1.0f, s1 = 1.0f;
+                if (WBITS == 4) {
+                    const float2 sv = *reinterpret_cast<const float2*>(sthread + 16 * f);
+                    s0 = sv.x; s1 = sv.y;
+                }
+#pragma unroll
+                for (int jb = 0; jb < JB; ++jb) {
+                    out[f][jb][0] = fmaf(s0, small_int_to_float(acc[f][jb][0]), out[f][jb][0]);
+                    out[f][jb][1] = fmaf(s0, small_int_to_float(acc[f][jb][1]), out[f][jb][1]);
+                    out[f][jb][2] = fmaf(s1, small_int_to_float(acc[f][jb][2]), out[f][jb][2]);
+                    out[f][jb][3] = fmaf(s1, small_int_to_float(acc[f][jb][3]), out[f][jb][3]);
+                    acc[f][jb][0] = acc[f][jb][1] = acc[f][jb][2] = acc[f][jb][3] = 0;
+                }
             }
         };
-        auto mma_block = [&](int kb, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3) {
+        // one k32-block: the activation fragment is loaded once and feeds both column fragments
+        auto mma_block = [&](const uint32_t (&a)[2][4]) {
 #pragma unroll
             for (int jb = 0; jb < JB; ++jb) {
-                const uint2 b = *reinterpret_cast<const uint2*>(dthread + (kb * NJ + jb * 8) * 32);
-                mma_s8_16832(acc[jb], a0, a1, a2, a3, b.x, b.y);
+                const uint2 b = *reinterpret_cast<const uint2*>(dthread + jb * 8 * 32);
+                mma_s8_16832(acc[0][jb], a[0][0], a[0][1], a[0][2], a[0][3], b.x, b.y);
+                mma_s8_16832(acc[1][jb], a[1][0], a[1][1], a[1][2], a[1][3], b.x, b.y);
             }
+            dthread += NJ * 32;
             ++since_flush;
             ++blk_in_group;
             if (since_flush == flush_every || blk_in_group == group_blocks) { since_flush = 0; flush(); }
-            if (blk_in_group == group_blocks) { blk_in_group = 0; ++gl; }
+            if (blk_in_group == group_blocks) { blk_in_group = 0; sthread += GV_COLS; }
         };
 
         for (int ls = 0; ls < n_stages; ++ls) {
             const int slot = ls % GV_NSTAGE;
             ptx::mbar_wait(full0 + 8 * slot, (ls / GV_NSTAGE) & 1, abort_flag, p.status);
-            const uint32_t tile = smem_u32(tiles + slot * GV_STAGE_BYTES);
+            const uint32_t tile = smem_u32(tiles + slot * GV_STAGE_BYTES + box * GV_BOX_BYTES);
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
-                uint32_t x[4];
+                // register x[f][j]: bytes {row 2t: col 2g, col 2g+1; row 2t+1: col 2g, col 2g+1}
+                // of byte-rows 8j .. 8j+7 of this 32-row block, fragment f
+                uint32_t x[2][4];
                 const int row = half * 32 + lmat * 8 + lrow;
-                ldmatrix_x4_trans(tile + row * 128 + ((warp ^ (row & 7)) << 4), x);
+                ldmatrix_x4_trans(tile + row * 128 + (((chunk0) ^ (row & 7)) << 4), x[0]);
+                ldmatrix_x4_trans(tile + row * 128 + (((chunk0 + 1) ^ (row & 7)) << 4), x[1]);
                 if (half == 1) {           // stage fully read by this warp
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive(empty0 + 8 * slot);
                 }
-                // register x[j]: bytes {row 2t: col 2g, col 2g+1; row 2t+1: col 2g, col 2g+1}
-                // of byte-rows 8j .. 8j+7 of this 32-row block
                 if (WBITS == 4) {
-                    uint32_t p0[4], p1[4];     // 4 consecutive k of column 2g / 2g+1, as int8 = 16*q
+                    uint32_t a[2][2][4];   // [k32-block][fragment][operand register]
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const uint32_t lo = (x[j] << 4) & 0xf0f0f0f0u;     // even k
-                        const uint32_t hi = x[j] & 0xf0f0f0f0u;            // odd k
-                        p0[j] = __byte_perm(lo, hi, 0x6240);
-                        p1[j] = __byte_perm(lo, hi, 0x7351);
-                    }
-                    const int kb = ls * KB_PER_STAGE + half * 2;
-                    mma_block(kb, p0[0], p1[0], p0[1], p1[1]);
-                    mma_block(kb + 1, p0[2], p1[2], p0[3], p1[3]);
+                    for (int f = 0; f < 2; ++f)
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const uint32_t lo = (x[f][j] << 4) & 0xf0f0f0f0u;     // even k, int8 = 16*q
+                            const uint32_t hi = x[f][j] & 0xf0f0f0f0u;            // odd k
+                            // 4 consecutive k of column 2g (regs 0, 2) / 2g+1 (regs 1, 3)
+                            a[j >> 1][f][(j & 1) * 2] = __byte_perm(lo, hi, 0x6240);
+                            a[j >> 1][f][(j & 1) * 2 + 1] = __byte_perm(lo, hi, 0x7351);
+                        }
+                    mma_block(a[0]);
+                    mma_block(a[1]);
                 } else {
                     // k-slots 4t..4t+3 <- rows {2t, 2t+1} of matrices 0 and 1; 16+4t.. <- matrices 2 and 3
-                    const uint32_t a0 = __byte_perm(x[0], x[1], 0x6420), a1 = __byte_perm(x[0], x[1], 0x7531);
-                    const uint32_t a2 = __byte_perm(x[2], x[3], 0x6420), a3 = __byte_perm(x[2], x[3], 0x7531);
-                    mma_block(ls * KB_PER_STAGE + half, a0, a1, a2, a3);
+                    uint32_t a[2][4];
+#pragma unroll
+                    for (int f = 0; f < 2; ++f) {
+                        a[f][0] = __byte_perm(x[f][0], x[f][1], 0x6420);
+                        a[f][1] = __byte_perm(x[f][0], x[f][1], 0x7531);
+                        a[f][2] = __byte_perm(x[f][2], x[f][3], 0x6420);
+                        a[f][3] = __byte_perm(x[f][2], x[f][3], 0x7531);
+                    }
+                    mma_block(a);
                 }
             }
         }
         if (since_flush != 0) flush();
-        // per-column partial sums of this warp's 16 columns: column j of the operand
-        // = digit (j % 3) of row j / 3
-        float c0 = 1.0f, c1 = 1.0f;
-        if (WBITS == 8) {
-            const int n_a = col0 + warp * 16 + 2 * g;
-            c0 = (n_a < p.N) ? p.scales[n_a] : 0.0f;
-            c1 = (n_a + 1 < p.N) ? p.scales[n_a + 1] : 0.0f;
-        }
+        // per-column partial sums: column j of the operand = digit (j % 3) of row j / 3
 #pragma unroll
-        for (int jb = 0; jb < JB; ++jb) {
-            float* d = part + (jb * 8 + 2 * t) * GV_COLS + warp * 16 + 2 * g;
-            *reinterpret_cast<float2*>(d) = make_float2(c0 * out[jb][0], c1 * out[jb][2]);
-            *reinterpret_cast<float2*>(d + GV_COLS) = make_float2(c0 * out[jb][1], c1 * out[jb][3]);
+        for (int f = 0; f < 2; ++f) {
+            float c0 = 1.0f, c1 = 1.0f;
+            if (WBITS == 8) {
+                const int n_a = col0 + wcol + 16 * f;
+                c0 = (n_a < p.N) ? p.scales[n_a] : 0.0f;
+                c1 = (n_a + 1 < p.N) ? p.scales[n_a + 1] : 0.0f;
+            }
+#pragma unroll
+            for (int jb = 0; jb < JB; ++jb) {
+                float* d = part + (jb * 8 + 2 * t) * GV_COLS + wcol + 16 * f;
+                *reinterpret_cast<float2*>(d) = make_float2(c0 * out[f][jb][0], c1 * out[f][jb][2]);
+                *reinterpret_cast<float2*>(d + GV_COLS) = make_float2(c0 * out[f][jb][1], c1 * out[f][jb][3]);
+            }
         }
     } else if (lane == 0) {
         // producer: refill ring slots as the consumers release them
@@ -338,8 +366,10 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
             const int slot = ls % GV_NSTAGE;
             if (!ptx::mbar_wait(empty0 + 8 * slot, ((ls / GV_NSTAGE) - 1) & 1, abort_flag, p.status)) break;
             ptx::mbar_expect_tx(full0 + 8 * slot, GV_STAGE_BYTES);
-            ptx::tma_load_2d(smem_u32(tiles + slot * GV_STAGE_BYTES), &tmB, col0,
-                             (stage_begin + ls) * GV_ROWS, full0 + 8 * slot);
+#pragma unroll
+            for (int b = 0; b < GV_BOXES; ++b)
+                ptx::tma_load_2d(smem_u32(tiles + slot * GV_STAGE_BYTES + b * GV_BOX_BYTES), &tmB,
+                                 col0 + b * GV_BOX_COLS, (stage_begin + ls) * GV_ROWS, full0 + 8 * slot);
             issued = ls + 1;
         }
         if (*abort_flag) {
@@ -357,7 +387,7 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
     const int ncol = min(GV_COLS, p.N - col0);            // multiple of 16
     const float digit_unit = (WBITS == 4) ? 0.0625f : 1.0f;    // int4 nibbles were carried as 16*q
     for (int i = threadIdx.x; i < p.M * (GV_COLS / 4); i += GV_THREADS) {
-        const int m = i >> 5, c = (i & 31) * 4;
+        const int m = i >> 6, c = (i & 63) * 4;
         if (c >= ncol) continue;
         const float4 h = *reinterpret_cast<const float4*>(part + (3 * m) * GV_COLS + c);
         const float4 md = *reinterpret_cast<const float4*>(part + (3 * m + 1) * GV_COLS + c);
@@ -397,7 +427,7 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
     if (!flags[1]) return;
     __threadfence();
     for (int i = threadIdx.x; i < p.M * (GV_COLS / 4); i += GV_THREADS) {
-        const int m = i >> 5, c = (i & 31) * 4;
+        const int m = i >> 6, c = (i & 63) * 4;
         if (c >= ncol) continue;
         float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int r = 0; r < p.splits; ++r) {
@@ -434,7 +464,7 @@ struct GemvPlan { int splits; int stages_total; int stages_per_cta; size_t smem;
 
 // Pick the K split.  A CTA costs its stage count plus a fixed overhead (launch,
 // activation prologue, partial write-out, about three stages' worth); the grid
-// should fit in one wave of ~4 CTAs per SM.  The shared-memory budget (the
+// should fit in one wave of the CTAs an SM can hold (3 for M <= 2).  The shared-memory budget (the
 // activation digits grow with the chunk length) bounds the chunk from above.
 static GemvPlan plan_gemv(int wbits, int jb, int N, int K, int G, int sm_count) {
     GemvPlan best{};
@@ -450,7 +480,7 @@ static GemvPlan plan_gemv(int wbits, int jb, int N, int K, int G, int sm_count) 
         const int splits = ceil_div(stages_total, spc);
         const size_t smem = gemv_smem_bytes(wbits, jb, spc * k_per_stage, G);
         if (smem > 200 * 1024) continue;
-        const int per_sm = std::max(1, std::min(jb >= 6 ? 2 : 4, static_cast<int>((220 * 1024) / smem)));
+        const int per_sm = std::max(1, std::min(jb >= 6 ? 1 : (jb >= 2 ? 2 : 3), static_cast<int>((224 * 1024) / (smem + 1024))));
         const int waves = ceil_div(col_tiles * splits, sm_count * per_sm);
         const double cost = waves * (spc + 3.0) + 0.05 * splits;
         if (cost < best_cost) {
@@ -513,7 +543,7 @@ static int launch_gemv(lhb_ctx* ctx, const float* A, const void* B, const float*
                        int M, int N, int K, int G, float alpha, float beta, cudaStream_t st) {
     const uint64_t rows = (WBITS == 4) ? K / 2 : K;
     TensorMap tm;
-    if (int e = get_tensor_map_2d_u8(ctx, B, rows, N, N, GV_ROWS, GV_COLS, true, &tm)) return e;
+    if (int e = get_tensor_map_2d_u8(ctx, B, rows, N, N, GV_ROWS, GV_BOX_COLS, true, &tm)) return e;
     // rows of A are independent: M > 16 is served in slabs of 16 rows
     for (int m0 = 0; m0 < M; m0 += GV_MAX_M) {
         const int m = std::min(GV_MAX_M, M - m0);

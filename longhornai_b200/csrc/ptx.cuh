@@ -33,11 +33,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     asm volatile(
         "{\n"
         ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
         "selp.u32 %0, 1, 0, p;\n"
         "}\n"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(20000u)     // suspend-time hint: the warp may sleep in hardware
         : "memory");
     return ok != 0;
 }
@@ -53,7 +53,7 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // runs on to its normal end (results are then undefined, the context is not).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* status) {
-    for (int i = 0; i < 128; ++i)
+    for (int i = 0; i < 16; ++i)
         if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = global_timer_ns();
     while (!mbar_try_wait(bar, parity)) {
