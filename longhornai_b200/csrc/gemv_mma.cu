@@ -482,7 +482,7 @@ static GemvPlan plan_gemv(int wbits, int jb, int N, int K, int G, int sm_count) 
         if (smem > 200 * 1024) continue;
         const int per_sm = std::max(1, std::min(jb >= 6 ? 1 : (jb >= 2 ? 2 : 3), static_cast<int>((224 * 1024) / (smem + 1024))));
         const int waves = ceil_div(col_tiles * splits, sm_count * per_sm);
-        const double cost = waves * (spc + 3.0) + 0.05 * splits;
+        const double cost = waves * (spc + 3.0) + 1.2 * splits;   // every split adds to the fixed-order reduction
         if (cost < best_cost) {
             best_cost = cost;
             best.splits = splits; best.stages_total = stages_total; best.stages_per_cta = spc;
