@@ -181,6 +181,31 @@ LHB_API int lhb_paged_attention_q8_batched(lhb_ctx* ctx, const float* Q, const i
                                            int n_requests, float* O,
                                            const lhb_paged_attn_cfg* cfg,
                                            const lhb_paged_layout* layout, void* stream);
+/* No counterpart in the reference.  The same batched int8 decode attention as
+ * lhb_paged_attention_q8_batched for callers that cannot let this library
+ * allocate device memory and therefore have no context: a process that has
+ * already committed all of HBM to its own pools, a plugin host that forbids
+ * allocation after start-up, a loop that cannot tolerate the device-wide
+ * synchronisation an allocation may cause.  The kernel's scratch (split-KV
+ * partials, arrival counters, status word) lives in fixed arrays inside the
+ * library image (about 8 MiB per GPU that loads the library, held until the
+ * process exits); the call itself performs no cudaMalloc/cudaFree.
+ * Limits: decode shape only (seq_q 1, head_dim 128, block_size 16, at most 4
+ * query heads per KV head; otherwise LHB_ERR_UNSUPPORTED);
+ * n_requests * n_kv_heads <= 4096 and split partials <= 8 MiB, otherwise
+ * LHB_ERR_SCRATCH with a message in lhb_last_error().  The first call on a
+ * device looks the arrays' device addresses up and sets a kernel attribute;
+ * make that first call before any stream capture.  All calls on a device share
+ * the arrays: calls that overlap on the GPU (different streams) race and must
+ * be serialised by the caller. */
+LHB_API int lhb_paged_attention_q8_batched_noalloc(const float* Q, const int8_t* K_pool,
+                                                   const int8_t* V_pool, const float* K_scales,
+                                                   const float* V_scales,
+                                                   const int32_t* block_tables,
+                                                   int max_blocks_per_req, const int32_t* seq_lens,
+                                                   int n_requests, float* O,
+                                                   const lhb_paged_attn_cfg* cfg,
+                                                   const lhb_paged_layout* layout, void* stream);
 /* lh::paged_attention / lh::paged_attention_batched on fp32 pools
  * (src/kernels/paged_attention.hpp:42-63). */
 LHB_API int lhb_paged_attention_f32_batched(lhb_ctx* ctx, const float* Q, const float* K_pool,

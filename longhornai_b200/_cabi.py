@@ -58,6 +58,7 @@ SIGNATURES = {
     "lhb_paged_kv_append_f32": (_i, [_vp] * 6 + [_LP, _i, _i, _vp]),
     "lhb_paged_attention_q8": (_i, [_vp] * 7 + [_i, _vp, _CP, _LP, _vp]),
     "lhb_paged_attention_q8_batched": (_i, [_vp] * 7 + [_i, _vp, _i, _vp, _CP, _LP, _vp]),
+    "lhb_paged_attention_q8_batched_noalloc": (_i, [_vp] * 6 + [_i, _vp, _i, _vp, _CP, _LP, _vp]),
     "lhb_paged_attention_f32_batched": (_i, [_vp] * 5 + [_i, _vp, _i, _vp, _CP, _LP, _vp]),
     "lhb_cm_create": (_i, [_vp, _LP, _i, _i, C.POINTER(_vp)]),
     "lhb_cm_destroy": (_i, [_vp]),

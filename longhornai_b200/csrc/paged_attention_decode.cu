@@ -33,6 +33,8 @@
 #include <cuda_fp16.h>
 
 #include <cstdlib>
+#include <mutex>
+#include <string>
 
 #include "common.cuh"
 #include "dispatch.h"
@@ -450,4 +452,127 @@ int launch_decode_fast(lhb_ctx* ctx, const float* Q, const int8_t* Kp, const int
     return LHB_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Decode attention for callers that must not allocate device memory.
+//
+// Some hosts cannot give this library a context, because creating one calls
+// cudaMalloc: a serving process that has already handed every free byte of HBM
+// to its own KV pools, a plugin loaded into a host whose rules forbid
+// allocation after start-up, or a latency-critical loop that cannot afford the
+// device-wide synchronisation an allocation may imply.  For them the split-KV
+// partials, the arrival counters and the status word of the kernel above live
+// in fixed arrays inside the library image instead of a context's arena.
+//
+// Limits (checked, reported as LHB_ERR_SCRATCH with a message):
+//   n_requests * n_kv_heads                          <= 4096  (one counter each)
+//   n_requests * n_kv_heads * splits * group * 130 floats <= 8 MiB of partials
+// Every GPU that loads the library holds these arrays (about 8 MiB) until the
+// process exits.  All calls on a device share them and they keep the previous
+// call's contents: the counters are cleared on the stream at the start of each
+// call, the partials are always written before they are read.  Two calls that
+// overlap on the GPU (different streams) race on the arrays; serialise them.
+// ---------------------------------------------------------------------------
+
+constexpr size_t NA_PART_FLOATS = (size_t(8) << 20) / sizeof(float);
+constexpr int NA_COUNTERS = 4096;
+
+static __device__ __align__(256) float g_na_partials[NA_PART_FLOATS];
+static __device__ __align__(256) int g_na_counters[NA_COUNTERS];
+static __device__ __align__(256) int g_na_status[64];
+
+namespace {
+
+struct NoAllocDevice {
+    float* partials = nullptr;     // device addresses of the arrays above on this device
+    int* counters = nullptr;
+    int* status = nullptr;
+    int sm_count = 0;
+    bool ready = false;
+};
+
+std::mutex g_na_mu;
+NoAllocDevice g_na_dev[64];
+
+// Once per device, with that device current: in host code the array names are
+// only handles, the addresses a kernel can use come from cudaGetSymbolAddress.
+int na_setup(int dev, NoAllocDevice** out) {
+    std::lock_guard<std::mutex> lk(g_na_mu);
+    NoAllocDevice& d = g_na_dev[dev & 63];
+    if (!d.ready) {
+        LHB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&d.partials), g_na_partials));
+        LHB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&d.counters), g_na_counters));
+        LHB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&d.status), g_na_status));
+        LHB_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
+        LHB_CUDA(cudaFuncSetAttribute(paged_decode_q8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      PD_WARPS * PD_WARP_BYTES));
+        d.ready = true;
+    }
+    *out = &d;
+    return LHB_OK;
+}
+
+}  // namespace
 }  // namespace lhb
+
+extern "C" int lhb_paged_attention_q8_batched_noalloc(
+    const float* Q, const int8_t* K_pool, const int8_t* V_pool, const float* K_scales,
+    const float* V_scales, const int32_t* block_tables, int max_blocks_per_req,
+    const int32_t* seq_lens, int n_requests, float* O, const lhb_paged_attn_cfg* cfg,
+    const lhb_paged_layout* layout, void* stream) {
+    using namespace lhb;
+    if (!Q || !K_pool || !V_pool || !K_scales || !V_scales || !block_tables || !seq_lens || !O || !cfg || !layout)
+        return LHB_ERR_NULL;
+    if (n_requests < 0 || n_requests > 65535 || max_blocks_per_req <= 0 || layout->num_blocks <= 0)
+        return LHB_ERR_BAD_SHAPE;
+    if (cfg->head_dim != layout->head_dim || cfg->n_kv_heads != layout->n_kv_heads || cfg->window < 0 ||
+        cfg->chunk < 0 || cfg->n_q_heads <= 0)
+        return LHB_ERR_BAD_SHAPE;
+    if (!decode_fast_ok(*cfg, *layout)) {
+        set_last_error_text("lhb_paged_attention_q8_batched_noalloc: only the decode shape is served "
+                            "(seq_q 1, head_dim 128, block_size 16, at most 4 query heads per KV head)");
+        return LHB_ERR_UNSUPPORTED;
+    }
+    if (!aligned16(Q) || !aligned16(K_pool) || !aligned16(V_pool) || !aligned16(K_scales) ||
+        !aligned16(V_scales) || !aligned16(O))
+        return LHB_ERR_MISALIGNED;
+    if (n_requests == 0) return LHB_OK;
+    int dev = 0;
+    LHB_CUDA(cudaGetDevice(&dev));
+    NoAllocDevice* d = nullptr;
+    if (int e = na_setup(dev, &d)) return e;
+
+    const int group = cfg->n_q_heads / cfg->n_kv_heads;
+    const int64_t items = static_cast<int64_t>(n_requests) * cfg->n_kv_heads;
+    if (items > NA_COUNTERS) {
+        set_last_error_text("lhb_paged_attention_q8_batched_noalloc: n_requests * n_kv_heads = " +
+                            std::to_string(items) + " exceeds the fixed limit of " + std::to_string(NA_COUNTERS));
+        return LHB_ERR_SCRATCH;
+    }
+    // same split rule as the context-based entry point, so both give the same bits
+    int splits = static_cast<int>(ceil_div64(8LL * d->sm_count, items));
+    splits = std::max(1, std::min(splits, std::max(1, max_blocks_per_req / 8)));
+    splits = std::min(splits, 32);
+    if (const char* e = getenv("LHB_DECODE_SPLITS")) splits = std::max(1, std::min(64, atoi(e)));
+    const size_t need = static_cast<size_t>(items) * splits * group * PD_PART;
+    if (splits > 1 && need > NA_PART_FLOATS) {
+        set_last_error_text("lhb_paged_attention_q8_batched_noalloc: " + std::to_string(need * sizeof(float)) +
+                            " bytes of split partials exceed the fixed 8 MiB array");
+        return LHB_ERR_SCRATCH;
+    }
+    cudaStream_t st = as_stream(stream);
+    LHB_CUDA(cudaMemsetAsync(d->counters, 0, sizeof(int) * static_cast<size_t>(items), st));
+
+    DecodeParams p{};
+    p.Q = Q; p.Kp = K_pool; p.Vp = V_pool; p.Ks = K_scales; p.Vs = V_scales;
+    p.tables = block_tables; p.seq_lens = seq_lens; p.O = O;
+    p.part = d->partials; p.counters = d->counters; p.status = d->status;
+    p.max_blocks = max_blocks_per_req; p.n_q_heads = cfg->n_q_heads; p.n_kv_heads = cfg->n_kv_heads;
+    p.group = group; p.num_blocks = layout->num_blocks; p.splits = splits;
+    p.window = cfg->window; p.chunk = cfg->chunk;
+    const float scale = cfg->scale > 0.0f ? cfg->scale : 1.0f / sqrtf(static_cast<float>(cfg->head_dim));
+    p.scale_log2e = scale * 1.4426950408889634f;
+    dim3 grid(splits, cfg->n_kv_heads, n_requests);
+    paged_decode_q8_kernel<<<grid, PD_THREADS, PD_WARPS * PD_WARP_BYTES, st>>>(p);
+    LHB_LAUNCH_CHECK();
+    return LHB_OK;
+}

@@ -296,3 +296,22 @@ def paged_attention_batched_f32(Q, K_pool, V_pool, block_tables, seq_lens, cfg: 
         max_blocks, _t(seq_lens, torch.int32, "seq_lens"), n_req, _t(O, torch.float32, "O"),
         C.byref(cfg), C.byref(L), _stream(c.device)), "paged_attention_batched_f32")
     return O
+
+
+def paged_attention_q8_batched_noalloc(Q, K_pool, V_pool, K_scales, V_scales, block_tables, seq_lens,
+                                       cfg: PagedAttnCfg, L: PagedLayout, O):
+    """Batched int8 decode attention through the entry point that allocates no
+    device memory and takes no context (its scratch is a fixed array inside the
+    library).  For hosts that must not allocate: every buffer, the output
+    included, is supplied by the caller.  Limits and the sharing rule are stated
+    with the declaration in include/lhb200.h."""
+    lib = _cabi.load()
+    n_req, max_blocks = block_tables.shape
+    dev = Q.device.index
+    check(lib.lhb_paged_attention_q8_batched_noalloc(
+        _t(Q, torch.float32, "Q"), _t(K_pool, torch.int8, "K_pool"), _t(V_pool, torch.int8, "V_pool"),
+        _t(K_scales, torch.float32, "K_scales"), _t(V_scales, torch.float32, "V_scales"),
+        _t(block_tables, torch.int32, "block_tables"), max_blocks, _t(seq_lens, torch.int32, "seq_lens"),
+        n_req, _t(O, torch.float32, "O"), C.byref(cfg), C.byref(L), _stream(dev)),
+        "paged_attention_q8_batched_noalloc")
+    return O
