@@ -91,7 +91,7 @@ class ClockSampler:
                         self.reasons.add(name)
             except Exception:
                 pass
-            time.sleep(0.02)
+            time.sleep(0.001)
 
     def __enter__(self):
         if self.nv:
