@@ -11,16 +11,20 @@
 // range of the request's visible pages; its 4 warps take pages round-robin and
 // run independent cp.async rings (3 stages x 4.1 KiB per warp, 128-bit copies,
 // XOR-swizzled 16-byte chunks) -- no block-level barrier inside the main loop.
-// Per page a warp does
-//   S = K Q^T  : mma.sync m16n8k16, tokens as the 16 rows, head_dim as k,
-//                int8 -> fp16 by byte-permute against 0x64 (1024 + x), exact;
-//                Q is split into fp16 hi + lo terms (two MMA columns per head),
-//   online softmax in base 2 with the V row scale folded into the exponent:
-//                w = 2^(s*c + log2(vs) - m), so w is in (0, 1] whatever the
-//                magnitude of the scales; the denominator is tracked in the
-//                same frame,
-//   O += V^T W : mma.sync with head_dim as the 16 rows and tokens as k; W is
-//                again split into fp16 hi + lo columns.
+// Per page a warp does, entirely on the int8 tensor-core path (mma.sync s8):
+//   S = K Q^T  : m16n8k32, tokens as the 16 rows, head_dim as k; the int8 rows of
+//                K are operand registers as they lie in shared memory (no
+//                conversion at all); Q is three signed 7-bit digits per element
+//                (exact power-of-two scaling per head), one MMA column per digit;
+//   softmax in base 2 with the V row scale folded into the exponent:
+//                P = 2^(s*c + log2(vs) - m_ref) <= 1 whatever the magnitude of the
+//                scales, written as three 7-bit digits of round(2^20 P); the
+//                denominator is tracked in fp32 in the same frame;
+//   O += V^T P : m16n8k16 with head_dim as the 16 rows and the page's 16 tokens as
+//                k; 4x4 byte transposes (byte-permute) turn V rows into operand
+//                registers.  The int32 sums stay in the frame of m_ref and are
+//                folded into fp32 only when a head's maximum rises or every 8
+//                pages, so the usual page costs no rescaling.
 // The four warps merge (m, l, O) in shared memory; with more than one split the
 // CTA writes its partial to the context's scratch arena and the last CTA to
 // arrive for a (request, kv head) merges the partials in fixed order
@@ -29,8 +33,7 @@
 //
 // Results differ from the reference's three-pass softmax
 // (src/kernels/kvcache_quant.cpp:82-161) only by fp32 summation order and the
-// 2^-22 relative error of the split terms.
-#include <cuda_fp16.h>
+// 2^-21 rounding of Q and P to 20-bit integers.
 
 #include <cstdlib>
 #include <mutex>
@@ -47,10 +50,10 @@ constexpr int PD_STAGES = 3;
 constexpr int PD_D = 128;
 constexpr int PD_BS = 16;
 constexpr int PD_STAGE_BYTES = 2048 + 2048 + 64 + 64;          // K, V, ks, vs
-constexpr int PD_WARP_BYTES = PD_STAGES * PD_STAGE_BYTES;
+constexpr int PD_WARP_BYTES = PD_STAGES * PD_STAGE_BYTES + 256;  // + P digit exchange buffer
 constexpr int PD_MAX_GROUP = 4;
 constexpr int PD_PART = PD_D + 2;                               // floats per (split, head): m, l, O[128]
-constexpr float PD_WSHIFT = 10.0f;                              // w is scaled by 2^10 into fp16's normal range
+constexpr float PD_WSHIFT = 20.0f;                              // P weights are integers in [0, 2^20]
 constexpr float PD_MIN_LOG2_VS = -100.0f;
 
 __device__ __forceinline__ uint32_t pd_smem_u32(const void* p) {
@@ -64,22 +67,34 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-__device__ __forceinline__ void pd_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                       uint32_t b0, uint32_t b1) {
+// int8 x int8 -> int32 tensor-core MMAs (weights / pages as the 16-row operand)
+__device__ __forceinline__ void pd_imma32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
     asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
         "{%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ void pd_imma16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(b0));
+}
 
-__device__ __forceinline__ uint32_t pd_h2u(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
-__device__ __forceinline__ __half2 pd_u2h(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+// exact int32 -> fp32 for |v| < 2^22 without the conversion pipe
+__device__ __forceinline__ float pd_i2f(int v) { return __int_as_float(v + 0x4B400000) - 12582912.0f; }
 
-// (byte | 0x6400) read as fp16 is 1024 + byte; with the byte pre-biased by 128
-// that is 1152 + q, and one subtraction gives q exactly.
-__device__ __forceinline__ uint32_t pd_unbias(uint32_t t) {
-    return pd_h2u(__hsub2(pd_u2h(t), pd_u2h(0x64806480u)));
+// 4x4 byte transpose: out[b] = {r0.byte b, r1.byte b, r2.byte b, r3.byte b}
+__device__ __forceinline__ void pd_transpose4(uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3,
+                                              uint32_t (&out)[4]) {
+    const uint32_t lo01 = __byte_perm(r0, r1, 0x5140), hi01 = __byte_perm(r0, r1, 0x7362);
+    const uint32_t lo23 = __byte_perm(r2, r3, 0x5140), hi23 = __byte_perm(r2, r3, 0x7362);
+    out[0] = __byte_perm(lo01, lo23, 0x5410);
+    out[1] = __byte_perm(lo01, lo23, 0x7632);
+    out[2] = __byte_perm(hi01, hi23, 0x5410);
+    out[3] = __byte_perm(hi01, hi23, 0x7632);
 }
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -91,13 +106,6 @@ __device__ __forceinline__ float fast_log2(float x) {
     float y;
     asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
-}
-
-// fp32 -> (hi, lo) fp16 pair packed in one register (hi in the low half)
-__device__ __forceinline__ uint32_t split_h2(float v) {
-    const __half hi = __float2half_rn(v);
-    const __half lo = __float2half_rn(v - __half2float(hi));
-    return static_cast<uint32_t>(__half_as_ushort(hi)) | (static_cast<uint32_t>(__half_as_ushort(lo)) << 16);
 }
 
 struct DecodeParams {
@@ -117,7 +125,7 @@ struct DecodeParams {
     float scale_log2e;
 };
 
-__global__ void __launch_bounds__(PD_THREADS, 4)
+__global__ void __launch_bounds__(PD_THREADS, 3)
 paged_decode_q8_kernel(const DecodeParams p) {
     extern __shared__ __align__(128) uint8_t pd_smem[];
     __shared__ int s_last;
@@ -140,11 +148,14 @@ paged_decode_q8_kernel(const DecodeParams p) {
     const int pg_hi = min(page_f + n_pages, pg_lo + per_split);   // exclusive
     const int32_t* table = p.tables + static_cast<int64_t>(req) * p.max_blocks;
 
-    // ---- Q fragments: per head a power-of-two scale into fp16 range, hi/lo split
-    // column j = 2*h + term of the 8-column operand; thread (g, t) holds column g
-    // at head_dim positions 32t + 4i .. 32t + 4i + 3 for k-step i.
-    const int hq = g >> 1, term = g & 1;
-    uint32_t qf[8][2];
+    // ---- Q as three signed 7-bit digits per element (q*s = d1*2^14 + d2*2^7 + d3, s a
+    // power of two per head putting max|q| in [2^19, 2^20)), one int8 MMA column per
+    // digit.  Column layout of the two 8-column operand blocks: block 0 column 2h = d1,
+    // 2h+1 = d2 of head h; block 1 column 2h = d3 (odd columns zero), so thread (g, t)
+    // of the result fragment owns every digit of head t.  Thread (g, t) of the operand
+    // holds column g at head_dim positions 32t + 8i .. +7 for k-step i.
+    const int hq = g >> 1, odd = g & 1;
+    uint32_t qf[4][2][2];            // [k-step][block][register]
     float qinv[PD_MAX_GROUP];
     {
         const float* qbase = p.Q + (static_cast<int64_t>(req) * p.n_q_heads + kvh * G) * PD_D;
@@ -157,7 +168,7 @@ paged_decode_q8_kernel(const DecodeParams p) {
             }
             mx = warp_max(mx);
             const int e = static_cast<int>((__float_as_uint(mx) >> 23) & 0xff);
-            int se = (mx > 0.0f) ? 267 - e : 127;
+            int se = (mx > 0.0f) ? 273 - e : 127;          // 127 + 19 - (e - 127)
             se = max(1, min(253, se));
             qinv[h] = __uint_as_float(static_cast<uint32_t>(254 - se) << 23);
         }
@@ -167,26 +178,60 @@ paged_decode_q8_kernel(const DecodeParams p) {
             if (h == hq) qs = 1.0f / qinv[h];          // exact: powers of two
         const bool live = hq < G;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (live) v = *reinterpret_cast<const float4*>(qbase + hq * PD_D + 32 * t + 4 * i);
-            const uint32_t s0 = split_h2(v.x * qs), s1 = split_h2(v.y * qs);
-            const uint32_t s2 = split_h2(v.z * qs), s3 = split_h2(v.w * qs);
-            const uint32_t sel = term ? 0x7632u : 0x5410u;
-            qf[i][0] = __byte_perm(s0, s1, sel);
-            qf[i][1] = __byte_perm(s2, s3, sel);
+        for (int i = 0; i < 4; ++i) {
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (live) v = *reinterpret_cast<const float4*>(qbase + hq * PD_D + 32 * t + 8 * i + 4 * r);
+                const float x[4] = {v.x * qs, v.y * qs, v.z * qs, v.w * qs};
+                uint32_t b0 = 0, b1 = 0;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    int iv = __float2int_rn(fminf(fmaxf(x[j], -1048576.0f), 1048576.0f));
+                    const int lo = ((iv + 64) & 127) - 64;
+                    iv = (iv - lo) >> 7;
+                    const int mid = ((iv + 64) & 127) - 64;
+                    const int hi = (iv - mid) >> 7;
+                    b0 |= static_cast<uint32_t>((odd ? mid : hi) & 0xff) << (8 * j);
+                    b1 |= static_cast<uint32_t>((odd ? 0 : lo) & 0xff) << (8 * j);
+                }
+                qf[i][0][r] = b0;
+                qf[i][1][r] = b1;
+            }
         }
     }
 
     // ---- per-warp state ---------------------------------------------------------
     uint8_t* ring = pd_smem + warp * PD_WARP_BYTES;
     const uint32_t ring_u32 = pd_smem_u32(ring);
-    float oacc[8][4];
+    uint8_t* pdig = ring + PD_STAGES * PD_STAGE_BYTES;   // [2 blocks][8 columns][16 tokens] digit bytes of P
+    for (int i = lane; i < 64; i += 32) reinterpret_cast<uint32_t*>(pdig)[i] = 0u;             // odd columns of block 1 stay zero
+    __syncwarp();
+    int oi0[8][4], oi1[8][4];        // int32 sums of V^T P since the last fold: block 0 (d1, d2), block 1 (d3)
+    float of[8][2];                  // folded fp32 output of head t at head_dim 16g + i and 16g + 8 + i
 #pragma unroll
-    for (int i = 0; i < 8; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.0f;
-    float m_run = -INFINITY;      // running max of head t (identical on the 8 lanes that share t)
-    float l_run = 0.0f;           // this lane's share of the denominator
+    for (int i = 0; i < 8; ++i) {
+        oi0[i][0] = oi0[i][1] = oi0[i][2] = oi0[i][3] = 0;
+        oi1[i][0] = oi1[i][1] = oi1[i][2] = oi1[i][3] = 0;
+        of[i][0] = of[i][1] = 0.0f;
+    }
+    float m_ref = -INFINITY;      // reference exponent of head t (identical on the 8 lanes that share t)
+    float l_run = 0.0f;           // this lane's share of the denominator, in the frame of m_ref
+    int pages_since_fold = 0;
     const float sc = p.scale_log2e * (t == 0 ? qinv[0] : t == 1 ? qinv[1] : t == 2 ? qinv[2] : qinv[3]);
+
+    // Fold the int32 sums into the fp32 output (after rescaling it by `alpha`) and clear them.
+    auto fold = [&](float alpha) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float a = fmaf(16384.0f, pd_i2f(oi0[i][0]), fmaf(128.0f, pd_i2f(oi0[i][1]), pd_i2f(oi1[i][0])));
+            const float b = fmaf(16384.0f, pd_i2f(oi0[i][2]), fmaf(128.0f, pd_i2f(oi0[i][3]), pd_i2f(oi1[i][2])));
+            of[i][0] = fmaf(of[i][0], alpha, a);
+            of[i][1] = fmaf(of[i][1], alpha, b);
+            oi0[i][0] = oi0[i][1] = oi0[i][2] = oi0[i][3] = 0;
+            oi1[i][0] = oi1[i][1] = oi1[i][2] = oi1[i][3] = 0;
+        }
+    };
 
     const int my_first = pg_lo + warp;                 // this warp's pages: my_first, +4, +8, ...
     const int n_iter = (pg_hi > my_first) ? (pg_hi - my_first + PD_WARPS - 1) / PD_WARPS : 0;
@@ -242,9 +287,8 @@ paged_decode_q8_kernel(const DecodeParams p) {
         const int blk_id = page_id(it, batch);
         const bool page_ok = blk_id >= 0 && blk_id < p.num_blocks;
 
-        // ---- S = K Q^T over 8 k-steps ------------------------------------------
-        float sacc[4] = {0.f, 0.f, 0.f, 0.f};
-        float sacc2[4] = {0.f, 0.f, 0.f, 0.f};     // second chain: even / odd k-steps are independent
+        // ---- S = K Q^T: int8 rows of K are MMA operand registers as they lie ------------
+        int s0[4] = {0, 0, 0, 0}, s1[4] = {0, 0, 0, 0};     // block 0: (d1, d2) of head t; block 1: d3
         {
             const uint8_t* r0 = st + g * 128;           // token g
             const uint8_t* r1 = st + (g + 8) * 128;     // token g + 8 (same swizzle: (g+8)&7 == g)
@@ -256,23 +300,16 @@ paged_decode_q8_kernel(const DecodeParams p) {
             const uint32_t wa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
             const uint32_t wb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const uint32_t xa = wa[i] ^ 0x80808080u, xb = wb[i] ^ 0x80808080u;
-                const uint32_t f0 = pd_unbias(__byte_perm(xa, 0x64646464u, 0x4140));   // token g,   d+0,1
-                const uint32_t f2 = pd_unbias(__byte_perm(xa, 0x64646464u, 0x4342));   // token g,   d+2,3
-                const uint32_t f1 = pd_unbias(__byte_perm(xb, 0x64646464u, 0x4140));   // token g+8
-                const uint32_t f3 = pd_unbias(__byte_perm(xb, 0x64646464u, 0x4342));
-                if (i & 1) pd_mma(sacc2, f0, f1, f2, f3, qf[i][0], qf[i][1]);
-                else pd_mma(sacc, f0, f1, f2, f3, qf[i][0], qf[i][1]);
+            for (int i = 0; i < 4; ++i) {
+                pd_imma32(s0, wa[2 * i], wb[2 * i], wa[2 * i + 1], wb[2 * i + 1], qf[i][0][0], qf[i][0][1]);
+                pd_imma32(s1, wa[2 * i], wb[2 * i], wa[2 * i + 1], wb[2 * i + 1], qf[i][1][0], qf[i][1][1]);
             }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) sacc[j] += sacc2[j];
         }
-        // ---- online softmax (base 2), V scale folded into the exponent -------------
+        // ---- scores in base 2, V row scale folded into the exponent ------------------------
         const float* ksr = reinterpret_cast<const float*>(st + 4096);
         const float* vsr = reinterpret_cast<const float*>(st + 4160);
-        float x0 = (sacc[0] + sacc[1]) * ksr[g] * sc;          // token g,   head t
-        float x1 = (sacc[2] + sacc[3]) * ksr[g + 8] * sc;      // token g+8, head t
+        float x0 = fmaf(16384.0f, pd_i2f(s0[0]), fmaf(128.0f, pd_i2f(s0[1]), pd_i2f(s1[0]))) * ksr[g] * sc;
+        float x1 = fmaf(16384.0f, pd_i2f(s0[2]), fmaf(128.0f, pd_i2f(s0[3]), pd_i2f(s1[2]))) * ksr[g + 8] * sc;
         const int p0 = tok0 + g, p1 = tok0 + g + 8;
         const bool ok0 = page_ok && p0 >= first && p0 <= last;
         const bool ok1 = page_ok && p1 >= first && p1 <= last;
@@ -285,53 +322,65 @@ paged_decode_q8_kernel(const DecodeParams p) {
         mp = fmaxf(mp, __shfl_xor_sync(0xffffffffu, mp, 4));
         mp = fmaxf(mp, __shfl_xor_sync(0xffffffffu, mp, 8));
         mp = fmaxf(mp, __shfl_xor_sync(0xffffffffu, mp, 16));
-        const float m_new = fmaxf(m_run, mp);
-        const float alpha = (m_new == -INFINITY || m_new == m_run) ? 1.0f : fast_exp2(m_run - m_new);
-        m_run = m_new;
-        const float mb = (m_new == -INFINITY) ? 0.0f : m_new;
-        const float w0 = fast_exp2(y0 - mb + PD_WSHIFT);       // 2^10 * p * vs (relative to the frame)
-        const float w1 = fast_exp2(y1 - mb + PD_WSHIFT);
-        l_run = l_run * alpha + fast_exp2(x0 - mb) + fast_exp2(x1 - mb);
-        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                oacc[i][0] *= alpha; oacc[i][1] *= alpha; oacc[i][2] *= alpha; oacc[i][3] *= alpha;
-            }
+        // The int32 sums are kept in the frame of m_ref.  They are folded into fp32
+        // when a head's maximum rises (new frame) and at the latest every 8 pages
+        // (keeps every sum below 2^22); after the first pages of a sequence the
+        // maximum rarely moves, so the fold is rare.
+        const bool rise = mp > m_ref;
+        if (__any_sync(0xffffffffu, rise) || pages_since_fold == 8) {
+            const float m_new = rise ? mp : m_ref;
+            const float alpha = (m_new == m_ref) ? 1.0f : fast_exp2(m_ref - m_new);   // exp2(-inf) = 0
+            fold(alpha);
+            l_run *= alpha;
+            m_ref = m_new;
+            pages_since_fold = 0;
         }
-        // ---- W operand: column g' = 2*head + term needs tokens 2t, 2t+1, 2t+8, 2t+9
-        const uint32_t W0 = split_h2(w0), W1 = split_h2(w1);
-        const int srcA = (2 * t) * 4 + hq, srcB = (2 * t + 1) * 4 + hq;
-        const uint32_t xA0 = __shfl_sync(0xffffffffu, W0, srcA), xB0 = __shfl_sync(0xffffffffu, W0, srcB);
-        const uint32_t xA1 = __shfl_sync(0xffffffffu, W1, srcA), xB1 = __shfl_sync(0xffffffffu, W1, srcB);
-        const uint32_t psel = term ? 0x7632u : 0x5410u;
-        const uint32_t pb0 = __byte_perm(xA0, xB0, psel);      // tokens 2t, 2t+1
-        const uint32_t pb1 = __byte_perm(xA1, xB1, psel);      // tokens 2t+8, 2t+9
-        // ---- O += V^T W over 8 blocks of 16 head_dim rows -----------------------------
+        ++pages_since_fold;
+        const float mb = (m_ref == -INFINITY) ? 0.0f : m_ref;
+        l_run += fast_exp2(x0 - mb) + fast_exp2(x1 - mb);
+        // ---- P = 2^20 * 2^(y - m_ref) <= 2^20 as three 7-bit digits, through shared memory
+        // into operand order: column c of a block, tokens 4t .. 4t+3 in one register
+        {
+            int w0 = __float2int_rn(fast_exp2(y0 - mb + PD_WSHIFT));
+            int w1 = __float2int_rn(fast_exp2(y1 - mb + PD_WSHIFT));
+            const int l0 = ((w0 + 64) & 127) - 64; w0 = (w0 - l0) >> 7;
+            const int l1 = ((w1 + 64) & 127) - 64; w1 = (w1 - l1) >> 7;
+            const int m0 = ((w0 + 64) & 127) - 64; const int h0 = (w0 - m0) >> 7;
+            const int m1 = ((w1 + 64) & 127) - 64; const int h1 = (w1 - m1) >> 7;
+            uint8_t* c0 = pdig + (2 * t) * 16;          // block 0, column 2t (d1); +16: column 2t+1 (d2)
+            c0[g] = static_cast<uint8_t>(h0); c0[g + 8] = static_cast<uint8_t>(h1);
+            c0[16 + g] = static_cast<uint8_t>(m0); c0[16 + g + 8] = static_cast<uint8_t>(m1);
+            c0[128 + g] = static_cast<uint8_t>(l0); c0[128 + g + 8] = static_cast<uint8_t>(l1);   // block 1, column 2t (d3)
+        }
+        __syncwarp();
+        const uint32_t pb0 = *reinterpret_cast<const uint32_t*>(pdig + g * 16 + 4 * t);
+        const uint32_t pb1 = *reinterpret_cast<const uint32_t*>(pdig + 128 + g * 16 + 4 * t);
+        // ---- O += V^T P: 4x4 byte transposes turn V rows into "4 tokens of one head_dim" registers
         {
             const uint8_t* vb = st + 2048;
-            const int r = 2 * t;
-            const uint4 v0 = *reinterpret_cast<const uint4*>(vb + r * 128 + ((g ^ (r & 7)) << 4));
-            const uint4 v1 = *reinterpret_cast<const uint4*>(vb + (r + 1) * 128 + ((g ^ ((r + 1) & 7)) << 4));
-            const uint4 v2 = *reinterpret_cast<const uint4*>(vb + (r + 8) * 128 + ((g ^ (r & 7)) << 4));
-            const uint4 v3 = *reinterpret_cast<const uint4*>(vb + (r + 9) * 128 + ((g ^ ((r + 1) & 7)) << 4));
-            const uint32_t r0w[4] = {v0.x, v0.y, v0.z, v0.w}, r1w[4] = {v1.x, v1.y, v1.z, v1.w};
-            const uint32_t r2w[4] = {v2.x, v2.y, v2.z, v2.w}, r3w[4] = {v3.x, v3.y, v3.z, v3.w};
+            uint32_t vr[4][4];                          // [token 4t + j][word: head_dim 16g + 4w .. +3]
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                // rows of the operand: head_dim 16g + i (slot g) and 16g + 8 + i (slot g + 8);
-                // byte (i & 3) of the two token rows goes to bytes 0 and 2, then
-                // (byte ^ 0x80) | 0x6400 per half
-                const int wlo = i >> 2, whi = 2 + (i >> 2);
-                const uint32_t bsel = (i & 3) | (((i & 3) + 4) << 8);
-                const uint32_t f0 = pd_unbias((__byte_perm(r0w[wlo], r1w[wlo], bsel) & 0x00ff00ffu) ^ 0x64806480u);
-                const uint32_t f1 = pd_unbias((__byte_perm(r0w[whi], r1w[whi], bsel) & 0x00ff00ffu) ^ 0x64806480u);
-                const uint32_t f2 = pd_unbias((__byte_perm(r2w[wlo], r3w[wlo], bsel) & 0x00ff00ffu) ^ 0x64806480u);
-                const uint32_t f3 = pd_unbias((__byte_perm(r2w[whi], r3w[whi], bsel) & 0x00ff00ffu) ^ 0x64806480u);
-                pd_mma(oacc[i], f0, f1, f2, f3, pb0, pb1);
+            for (int j = 0; j < 4; ++j) {
+                const int r = 4 * t + j;
+                const uint4 v = *reinterpret_cast<const uint4*>(vb + r * 128 + ((g ^ (r & 7)) << 4));
+                vr[j][0] = v.x; vr[j][1] = v.y; vr[j][2] = v.z; vr[j][3] = v.w;
+            }
+#pragma unroll
+            for (int w = 0; w < 2; ++w) {
+                // head_dim 16g + 4w + b (operand row g) and 16g + 8 + 4w + b (row g + 8), b = 0..3
+                uint32_t ta[4], tb[4];
+                pd_transpose4(vr[0][w], vr[1][w], vr[2][w], vr[3][w], ta);
+                pd_transpose4(vr[0][w + 2], vr[1][w + 2], vr[2][w + 2], vr[3][w + 2], tb);
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    pd_imma16(oi0[4 * w + b], ta[b], tb[b], pb0);
+                    pd_imma16(oi1[4 * w + b], ta[b], tb[b], pb1);
+                }
             }
         }
     }
     cp_async_wait<0>();
+    fold(1.0f);
 
     // ---- merge the four warps in shared memory -------------------------------------------
     __syncthreads();                                   // rings are dead from here on
@@ -343,12 +392,12 @@ paged_decode_q8_kernel(const DecodeParams p) {
         l += __shfl_xor_sync(0xffffffffu, l, 4);
         l += __shfl_xor_sync(0xffffffffu, l, 8);
         l += __shfl_xor_sync(0xffffffffu, l, 16);
-        if (g == 0) { sm_m[warp * PD_MAX_GROUP + t] = m_run; sm_l[warp * PD_MAX_GROUP + t] = l; }
+        if (g == 0) { sm_m[warp * PD_MAX_GROUP + t] = m_ref; sm_l[warp * PD_MAX_GROUP + t] = l; }
         float* od = sm_o + (warp * PD_MAX_GROUP + t) * PD_D + 16 * g;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            od[i] = oacc[i][0] + oacc[i][1];           // hi + lo columns of head t
-            od[8 + i] = oacc[i][2] + oacc[i][3];
+            od[i] = of[i][0];
+            od[8 + i] = of[i][1];
         }
     }
     __syncthreads();
