@@ -91,6 +91,7 @@ struct GemvParams {
     float* partial;        // scratch [splits, M, N] (unused when splits == 1)
     int* counters;         // one per column tile, zero between calls
     int* status;
+    int debug;             // timing experiments only (LHB_GEMV_DEBUG): 1 skip split reduction, 2 skip digits, 4 skip MMAs
 };
 
 // WBITS: 4 or 8.  JB: number of 8-column activation blocks; 3 digit columns per
@@ -173,7 +174,7 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
     const int n4 = p.M * q4;
     const int n4_pad = (n4 + 31) & ~31;                    // whole warps take part in the shuffles
     const float inv_q4 = 1.0f / static_cast<float>(q4 > 0 ? q4 : 1);
-    for (int i = threadIdx.x; i < n4_pad; i += GV_THREADS) {
+    for (int i = threadIdx.x; i < ((p.debug & 2) ? 0 : n4_pad); i += GV_THREADS) {
         const bool valid = i < n4;
         // row index without an integer division: (i + 0.5) / q4 is never within
         // 0.5 / q4 of an integer, far more than the float error at these sizes
@@ -193,7 +194,7 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
         }
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < n4; i += GV_THREADS) {
+    for (int i = threadIdx.x; i < ((p.debug & 2) ? 0 : n4); i += GV_THREADS) {
         const int m = min(p.M - 1, __float2int_rz((static_cast<float>(i) + 0.5f) * inv_q4));
         const int k = (i - m * q4) * 4;
         // power-of-two factor taking max|a| into [2^19, 2^20); exponent clamped
@@ -314,6 +315,7 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive(empty0 + 8 * slot);
                 }
+                if (p.debug & 4) continue;
                 if (WBITS == 4) {
                     uint32_t a[2][2][4];   // [k32-block][fragment][operand register]
 #pragma unroll
@@ -412,7 +414,7 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
             *reinterpret_cast<float4*>(p.partial + (static_cast<int64_t>(ks) * p.M + m) * p.N + col0 + c) = v;
         }
     }
-    if (p.splits == 1) return;
+    if (p.splits == 1 || (p.debug & 1)) return;
 
     // Split-K epilogue: the last split to arrive for this column tile sums the
     // partials in split order and writes C.
@@ -523,6 +525,8 @@ static int launch_gemv_t(lhb_ctx* ctx, const TensorMap& tm, GemvParams p, const 
     p.partial = reinterpret_cast<float*>(ctx->scratch);
     p.counters = ctx->counters;
     p.status = ctx->status_word;
+    static const int dbg = getenv("LHB_GEMV_DEBUG") ? atoi(getenv("LHB_GEMV_DEBUG")) : 0;
+    p.debug = dbg;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ceil_div(p.N, GV_COLS), pl.splits, 1);
     cfg.blockDim = dim3(GV_THREADS, 1, 1);
