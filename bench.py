@@ -464,7 +464,10 @@ def run_ours(args):
         "roofline": {"bound": "hbm", "kernel": "gemv_mma_kernel<4,1>", "achieved": achieved, "peak": hbm_peak,
                      "unit": "GB/s", "frac": achieved / hbm_peak, "peak_kind": f"of {peak_kind}",
                      "frac_of_nominal_8TBps": achieved / 8000.0, "bytes_per_launch": bytes_call_local,
-                     "us_per_launch": per_launch_s * 1e6, "traffic": None},
+                     "us_per_launch": per_launch_s * 1e6,
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at the
+                     # full N (profiles/gemv_w4a16_m1_cfg2.md); scales with the shard width
+                     "traffic": int(31_250_432 * (n_local / N_DIM)) if M == 1 else None},
         "clocks": sampler.summary() if sampler else None,
     }
     if g == 1 and not args.no_extra:
@@ -490,7 +493,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary workloads")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--only", default=None, choices=["paged_decode"],
+    ap.add_argument("--only", default=None, choices=["paged_decode", "w8a8"],
                     help="run one secondary workload alone on one GPU (for profiling) and print its numbers")
     args = ap.parse_args()
     if args.warmup < 3:
@@ -501,6 +504,11 @@ def main():
         torch.cuda.set_device(0)
         print(json.dumps({"paged_decode_q8": bench_paged_decode(torch, lb, args.steps, args.warmup,
                                                                  measured_peaks()[0])}), flush=True)
+    elif args.only == "w8a8":
+        import torch
+        import longhornai_b200 as lb
+        torch.cuda.set_device(0)
+        print(json.dumps({"w8a8_prefill": bench_w8a8(torch, lb, args.steps, args.warmup, M=2048)}), flush=True)
     elif args.impl == "reference":
         run_reference(args)
     else:
