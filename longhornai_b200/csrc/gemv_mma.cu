@@ -31,16 +31,21 @@
 // fp32 at every quantisation group (at most every 128 k), multiplied by the
 // group scale and accumulated in fp32.
 //
-// K is split over blockIdx.y so that every SM holds up to 3 CTAs.  Each split
-// writes its partial [M, 128] tile to the context's scratch arena; the last
-// split to arrive for a column tile (a self-resetting counter) sums the
-// partials in fixed order and applies alpha/beta, so the result is
-// deterministic and C is written once.
+// K is split over blockIdx.y.  With 2 or 4 splits the CTAs of a column tile
+// form a thread-block cluster and sum their partial [M, 256] tiles in split
+// order through distributed shared memory; with other split counts each split
+// writes its partial to the context's scratch arena and the last one to arrive
+// (a self-resetting counter) sums them in the same order.  Either way the
+// result is deterministic and C is written once, with alpha/beta applied.
+#include <cooperative_groups.h>
+
 #include <cstdlib>
 
 #include "common.cuh"
 #include "dispatch.h"
 #include "ptx.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace lhb {
 
@@ -91,6 +96,7 @@ struct GemvParams {
     float* partial;        // scratch [splits, M, N] (unused when splits == 1)
     int* counters;         // one per column tile, zero between calls
     int* status;
+    int cluster;           // 1: the splits of a column tile form a thread-block cluster (reduce through DSMEM)
     int debug;             // timing experiments only (LHB_GEMV_DEBUG): 1 skip split reduction, 2 skip digits, 4 skip MMAs
 };
 
@@ -410,11 +416,44 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
                 v.z = fmaf(p.beta, o.z, p.alpha * v.z); v.w = fmaf(p.beta, o.w, p.alpha * v.w);
             }
             *cp = v;
+        } else if (p.cluster) {
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(tiles) + m * GV_COLS + c) = v;   // ring is dead by now
         } else {
             *reinterpret_cast<float4*>(p.partial + (static_cast<int64_t>(ks) * p.M + m) * p.N + col0 + c) = v;
         }
     }
     if (p.splits == 1 || (p.debug & 1)) return;
+
+    if (p.cluster) {
+        // Split-K reduction inside the cluster: every CTA finishes a slice of the
+        // 256 columns, reading the partial tiles of all splits in split order
+        // through distributed shared memory.  No global round trip.
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        const int S = p.splits, rank = static_cast<int>(cluster.block_rank());
+        const int q4s = (GV_COLS / 4) / S;                       // float4 columns per CTA (S divides 64)
+        const float* comb = reinterpret_cast<const float*>(tiles);
+        for (int i = threadIdx.x; i < p.M * q4s; i += GV_THREADS) {
+            const int m = i / q4s, c = (rank * q4s + i % q4s) * 4;
+            if (c >= ncol) continue;
+            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int r = 0; r < S; ++r) {
+                const float4 v = *reinterpret_cast<const float4*>(cluster.map_shared_rank(comb, r) + m * GV_COLS + c);
+                sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+            }
+            float4* cp = reinterpret_cast<float4*>(p.C + static_cast<int64_t>(m) * p.N + col0 + c);
+            if (p.beta == 0.0f) {
+                sum.x *= p.alpha; sum.y *= p.alpha; sum.z *= p.alpha; sum.w *= p.alpha;
+            } else {
+                const float4 o = *cp;
+                sum.x = fmaf(p.beta, o.x, p.alpha * sum.x); sum.y = fmaf(p.beta, o.y, p.alpha * sum.y);
+                sum.z = fmaf(p.beta, o.z, p.alpha * sum.z); sum.w = fmaf(p.beta, o.w, p.alpha * sum.w);
+            }
+            *cp = sum;
+        }
+        cluster.sync();     // keep every CTA's shared memory alive until all peers have read it
+        return;
+    }
 
     // Split-K epilogue: the last split to arrive for this column tile sums the
     // partials in split order and writes C.
@@ -532,12 +571,25 @@ static int launch_gemv_t(lhb_ctx* ctx, const TensorMap& tm, GemvParams p, const 
     cfg.blockDim = dim3(GV_THREADS, 1, 1);
     cfg.dynamicSmemBytes = pl.smem;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
     static const bool pdl = !(getenv("LHB_PDL") && atoi(getenv("LHB_PDL")) == 0);
+    static const bool use_cluster = !(getenv("LHB_GEMV_CLUSTER") && atoi(getenv("LHB_GEMV_CLUSTER")) == 0);
+    p.cluster = (use_cluster && (pl.splits == 2 || pl.splits == 4)) ? 1 : 0;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    if (p.cluster) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = 1;
+        attr[na].val.clusterDim.y = pl.splits;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = pdl ? 1 : 0;
+    cfg.numAttrs = na;
     LHB_CUDA(cudaLaunchKernelEx(&cfg, kern, tm, p));
     return LHB_OK;
 }

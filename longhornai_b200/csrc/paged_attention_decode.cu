@@ -23,8 +23,9 @@
 //   O += V^T P : m16n8k16 with head_dim as the 16 rows and the page's 16 tokens as
 //                k; 4x4 byte transposes (byte-permute) turn V rows into operand
 //                registers.  The int32 sums stay in the frame of m_ref and are
-//                folded into fp32 only when a head's maximum rises or every 8
-//                pages, so the usual page costs no rescaling.
+//                folded into fp32 only when a head's maximum rises above it (the frame is
+//                then set 3 above the new maximum, so this happens about once per
+//                sequence): the usual page costs no rescaling.
 // The four warps merge (m, l, O) in shared memory; with more than one split the
 // CTA writes its partial to the context's scratch arena and the last CTA to
 // arrive for a (request, kv head) merges the partials in fixed order
@@ -55,6 +56,7 @@ constexpr int PD_MAX_GROUP = 4;
 constexpr int PD_PART = PD_D + 2;                               // floats per (split, head): m, l, O[128]
 constexpr float PD_WSHIFT = 20.0f;                              // P weights are integers in [0, 2^20]
 constexpr float PD_MIN_LOG2_VS = -100.0f;
+constexpr float PD_FRAME_MARGIN = 3.0f;                         // head room of the integer frame, in log2 units
 
 __device__ __forceinline__ uint32_t pd_smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -220,14 +222,17 @@ paged_decode_q8_kernel(const DecodeParams p) {
     int pages_since_fold = 0;
     const float sc = p.scale_log2e * (t == 0 ? qinv[0] : t == 1 ? qinv[1] : t == 2 ? qinv[2] : qinv[3]);
 
-    // Fold the int32 sums into the fp32 output (after rescaling it by `alpha`) and clear them.
+    // Fold the int32 sums (taken in the frame of the current m_ref) into the fp32
+    // output, move both to a new frame by `alpha`, and clear the sums.
     auto fold = [&](float alpha) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            const float a = fmaf(16384.0f, pd_i2f(oi0[i][0]), fmaf(128.0f, pd_i2f(oi0[i][1]), pd_i2f(oi1[i][0])));
-            const float b = fmaf(16384.0f, pd_i2f(oi0[i][2]), fmaf(128.0f, pd_i2f(oi0[i][3]), pd_i2f(oi1[i][2])));
-            of[i][0] = fmaf(of[i][0], alpha, a);
-            of[i][1] = fmaf(of[i][1], alpha, b);
+            const float a = fmaf(16384.0f, __int2float_rn(oi0[i][0]),
+                                 fmaf(128.0f, __int2float_rn(oi0[i][1]), __int2float_rn(oi1[i][0])));
+            const float b = fmaf(16384.0f, __int2float_rn(oi0[i][2]),
+                                 fmaf(128.0f, __int2float_rn(oi0[i][3]), __int2float_rn(oi1[i][2])));
+            of[i][0] = (of[i][0] + a) * alpha;
+            of[i][1] = (of[i][1] + b) * alpha;
             oi0[i][0] = oi0[i][1] = oi0[i][2] = oi0[i][3] = 0;
             oi1[i][0] = oi1[i][1] = oi1[i][2] = oi1[i][3] = 0;
         }
@@ -248,6 +253,13 @@ paged_decode_q8_kernel(const DecodeParams p) {
         const int b = __shfl_sync(0xffffffffu, ids_b, it & 31);
         return ((it >> 5) == cur_batch) ? a : b;
     };
+    // lane-constant pieces of the page copy: chunk idx = c*32 + lane of a 2 KiB page
+    uint32_t cp_dst[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const int idx = c * 32 + lane, tok = idx >> 3, ch = idx & 7;
+        cp_dst[c] = tok * 128 + ((ch ^ (tok & 7)) << 4);
+    }
     auto issue = [&](int it, int cur_batch) {
         if (it < n_iter) {
             int blk = page_id(it, cur_batch);
@@ -258,11 +270,8 @@ paged_decode_q8_kernel(const DecodeParams p) {
             const int8_t* vp = p.Vp + row0 * PD_D;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                const int idx = c * 32 + lane;                     // 16-byte chunk 0..127 of the page
-                const int tok = idx >> 3, ch = idx & 7;
-                const uint32_t off = tok * 128 + ((ch ^ (tok & 7)) << 4);
-                cp_async16(st + off, kp + idx * 16);
-                cp_async16(st + 2048 + off, vp + idx * 16);
+                cp_async16(st + cp_dst[c], kp + (c * 32 + lane) * 16);
+                cp_async16(st + 2048 + cp_dst[c], vp + (c * 32 + lane) * 16);
             }
             if (lane < 4) cp_async16(st + 4096 + lane * 16, p.Ks + row0 + lane * 4);
             else if (lane < 8) cp_async16(st + 4160 + (lane - 4) * 16, p.Vs + row0 + (lane - 4) * 4);
@@ -322,13 +331,14 @@ paged_decode_q8_kernel(const DecodeParams p) {
         mp = fmaxf(mp, __shfl_xor_sync(0xffffffffu, mp, 4));
         mp = fmaxf(mp, __shfl_xor_sync(0xffffffffu, mp, 8));
         mp = fmaxf(mp, __shfl_xor_sync(0xffffffffu, mp, 16));
-        // The int32 sums are kept in the frame of m_ref.  They are folded into fp32
-        // when a head's maximum rises (new frame) and at the latest every 8 pages
-        // (keeps every sum below 2^22); after the first pages of a sequence the
-        // maximum rarely moves, so the fold is rare.
+        // The int32 sums are kept in the frame of m_ref.  When a head's maximum rises
+        // above it, the sums are folded into fp32 and the frame moves to the new
+        // maximum plus a margin of 3 (weights then start at <= 2^-3 of full scale,
+        // still 17 bits), so that later, smaller rises need no fold; a sequence
+        // usually folds once.  Every 4096 pages a fold keeps the int32 sums in range.
         const bool rise = mp > m_ref;
-        if (__any_sync(0xffffffffu, rise) || pages_since_fold == 8) {
-            const float m_new = rise ? mp : m_ref;
+        if (__any_sync(0xffffffffu, rise) || pages_since_fold == 4096) {
+            const float m_new = rise ? mp + PD_FRAME_MARGIN : m_ref;
             const float alpha = (m_new == m_ref) ? 1.0f : fast_exp2(m_ref - m_new);   // exp2(-inf) = 0
             fold(alpha);
             l_run *= alpha;
