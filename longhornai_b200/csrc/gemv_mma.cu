@@ -55,7 +55,7 @@ constexpr int GV_COLS = GV_BOX_COLS * GV_BOXES;   // columns per CTA
 constexpr int GV_ROWS = 64;         // byte-rows per stage
 constexpr int GV_BOX_BYTES = GV_BOX_COLS * GV_ROWS;
 constexpr int GV_STAGE_BYTES = GV_BOX_BYTES * GV_BOXES;
-constexpr int GV_NSTAGE = 3;
+constexpr int GV_MAX_STAGE = 8;     // ring depth is chosen per launch (2..8) from the shared-memory budget
 constexpr int GV_CONSUMER_WARPS = 8;
 constexpr int GV_THREADS = (GV_CONSUMER_WARPS + 1) * 32;   // + one producer warp
 constexpr int GV_MAX_SPLIT = 32;
@@ -96,6 +96,7 @@ struct GemvParams {
     float* partial;        // scratch [splits, M, N] (unused when splits == 1)
     int* counters;         // one per column tile, zero between calls
     int* status;
+    int nstage;            // ring depth
     int cluster;           // 1: the splits of a column tile form a thread-block cluster (reduce through DSMEM)
     int debug;             // timing experiments only (LHB_GEMV_DEBUG): 1 skip split reduction, 2 skip digits, 4 skip MMAs
 };
@@ -112,12 +113,13 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* tiles = smem;                                             // GV_NSTAGE * 16 KiB
-    float* part = reinterpret_cast<float*>(smem + GV_NSTAGE * GV_STAGE_BYTES);   // [NJ][256]
+    const int NST = p.nstage;
+    uint8_t* tiles = smem;                                             // NST * 16 KiB
+    float* part = reinterpret_cast<float*>(smem + NST * GV_STAGE_BYTES);         // [NJ][256]
     float* inv_s = part + NJ * GV_COLS;                                // [16]
     unsigned* rowmax = reinterpret_cast<unsigned*>(inv_s + 16);        // [16] max|a| bits per row
     uint64_t* bars = reinterpret_cast<uint64_t*>(rowmax + 16);         // full[], empty[]
-    int* flags = reinterpret_cast<int*>(bars + 2 * GV_NSTAGE);         // [0] abort, [1] is-last
+    int* flags = reinterpret_cast<int*>(bars + 2 * GV_MAX_STAGE);      // [0] abort, [1] is-last
     float* sscale = reinterpret_cast<float*>(flags + 4);               // W4: [groups_per_cta][256] group scales
     uint8_t* dfrag = reinterpret_cast<uint8_t*>(sscale + p.groups_per_cta * GV_COLS);   // [kb32][NJ][32]
     volatile int* abort_flag = flags;
@@ -132,18 +134,18 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
     const int k_begin = stage_begin * K_PER_STAGE;
     const int k_count = n_stages * K_PER_STAGE;            // multiple of 32; may run past K
 
-    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + GV_NSTAGE);
-    // The producer thread sets the barriers up and puts the first GV_NSTAGE stages
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + GV_MAX_STAGE);
+    // The producer thread sets the barriers up and puts the first ring-full of stages
     // in flight before anything else happens in the CTA.
     if (warp == GV_CONSUMER_WARPS && lane == 0) {
-        for (int s = 0; s < GV_NSTAGE; ++s) {
+        for (int s = 0; s < GV_MAX_STAGE; ++s) {
             ptx::mbar_init(full0 + 8 * s, 1);
             ptx::mbar_init(empty0 + 8 * s, GV_CONSUMER_WARPS);
         }
         flags[0] = 0;
         flags[1] = 0;
         ptx::fence_mbar_init();
-        const int first = min(n_stages, GV_NSTAGE);
+        const int first = min(n_stages, NST);
         for (int s = 0; s < first; ++s) {
             ptx::mbar_expect_tx(full0 + 8 * s, GV_STAGE_BYTES);
 #pragma unroll
@@ -305,9 +307,10 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
             if (blk_in_group == group_blocks) { blk_in_group = 0; sthread += GV_COLS; }
         };
 
+        int slot = 0;
+        uint32_t phase = 0;
         for (int ls = 0; ls < n_stages; ++ls) {
-            const int slot = ls % GV_NSTAGE;
-            ptx::mbar_wait(full0 + 8 * slot, (ls / GV_NSTAGE) & 1, abort_flag, p.status);
+            ptx::mbar_wait(full0 + 8 * slot, phase, abort_flag, p.status);
             const uint32_t tile = smem_u32(tiles + slot * GV_STAGE_BYTES + box * GV_BOX_BYTES);
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
@@ -349,6 +352,7 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
                     mma_block(a);
                 }
             }
+            if (++slot == NST) { slot = 0; phase ^= 1; }
         }
         if (since_flush != 0) flush();
         // per-column partial sums: column j of the operand = digit (j % 3) of row j / 3
@@ -369,22 +373,24 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
         }
     } else if (lane == 0) {
         // producer: refill ring slots as the consumers release them
-        int issued = min(n_stages, GV_NSTAGE);
-        for (int ls = GV_NSTAGE; ls < n_stages; ++ls) {
-            const int slot = ls % GV_NSTAGE;
-            if (!ptx::mbar_wait(empty0 + 8 * slot, ((ls / GV_NSTAGE) - 1) & 1, abort_flag, p.status)) break;
+        int issued = min(n_stages, NST);
+        int slot = 0;
+        uint32_t phase = 0;                                // parity of the consumers' release being waited for
+        for (int ls = NST; ls < n_stages; ++ls) {
+            if (!ptx::mbar_wait(empty0 + 8 * slot, phase, abort_flag, p.status)) break;
             ptx::mbar_expect_tx(full0 + 8 * slot, GV_STAGE_BYTES);
 #pragma unroll
             for (int b = 0; b < GV_BOXES; ++b)
                 ptx::tma_load_2d(smem_u32(tiles + slot * GV_STAGE_BYTES + b * GV_BOX_BYTES), &tmB,
                                  col0 + b * GV_BOX_COLS, (stage_begin + ls) * GV_ROWS, full0 + 8 * slot);
             issued = ls + 1;
+            if (++slot == NST) { slot = 0; phase ^= 1; }
         }
         if (*abort_flag) {
             // a wait ran out: let the copies still in flight land before the CTA exits
-            for (int ls = max(0, issued - GV_NSTAGE); ls < issued; ++ls) {
+            for (int ls = max(0, issued - NST); ls < issued; ++ls) {
                 const uint64_t t0 = ptx::global_timer_ns();
-                while (!ptx::mbar_try_wait(full0 + 8 * (ls % GV_NSTAGE), (ls / GV_NSTAGE) & 1))
+                while (!ptx::mbar_try_wait(full0 + 8 * (ls % NST), (ls / NST) & 1))
                     if (ptx::global_timer_ns() - t0 > 200000000ull) break;
             }
         }
@@ -494,14 +500,15 @@ static int gemv_groups_per_cta(int wbits, int k_per_cta, int G) {
     return wbits == 4 ? k_per_cta / G + 2 : 0;             // + 2: chunks need not start on a group boundary
 }
 
+// shared memory of a CTA without its ring
 static size_t gemv_smem_bytes(int wbits, int jb, int k_per_cta, int G) {
     const size_t nj = 8 * jb;
-    return 1024 + GV_NSTAGE * GV_STAGE_BYTES + nj * GV_COLS * 4 + 16 * 4 + 16 * 4 + 2 * GV_NSTAGE * 8 + 16 +
+    return 1024 + nj * GV_COLS * 4 + 16 * 4 + 16 * 4 + 2 * GV_MAX_STAGE * 8 + 16 +
            static_cast<size_t>(gemv_groups_per_cta(wbits, k_per_cta, G)) * GV_COLS * 4 +
            static_cast<size_t>(k_per_cta) * nj;
 }
 
-struct GemvPlan { int splits; int stages_total; int stages_per_cta; size_t smem; bool ok; };
+struct GemvPlan { int splits; int stages_total; int stages_per_cta; int nstage; size_t smem; bool ok; };
 
 // Pick the K split.  A CTA costs its stage count plus a fixed overhead (launch,
 // activation prologue, partial write-out, about three stages' worth); the grid
@@ -519,15 +526,25 @@ static GemvPlan plan_gemv(int wbits, int jb, int N, int K, int G, int sm_count) 
         if (forced > 0 && S != std::min(forced, std::min(stages_total, GV_MAX_SPLIT))) continue;
         const int spc = ceil_div(stages_total, S);
         const int splits = ceil_div(stages_total, spc);
-        const size_t smem = gemv_smem_bytes(wbits, jb, spc * k_per_stage, G);
-        if (smem > 200 * 1024) continue;
-        const int per_sm = std::max(1, std::min(jb >= 6 ? 1 : (jb >= 2 ? 2 : 3), static_cast<int>((224 * 1024) / (smem + 1024))));
+        const size_t fixed = gemv_smem_bytes(wbits, jb, spc * k_per_stage, G);
+        if (fixed + 2 * GV_STAGE_BYTES > 200 * 1024) continue;
+        const int reg_limit = jb >= 6 ? 1 : (jb >= 2 ? 2 : 3);       // CTAs per SM the register file allows
+        // CTAs an SM must hold for the grid to be one wave, then the deepest ring that still fits
+        int per_sm = std::min(reg_limit, std::max(1, ceil_div(col_tiles * splits, sm_count)));
+        while (per_sm > 1 && fixed + 2 * GV_STAGE_BYTES + 1024 > (224 * 1024) / static_cast<size_t>(per_sm)) --per_sm;
+        const size_t budget = std::min<size_t>(200 * 1024, (224 * 1024) / per_sm - 1024);
+        int nstage = static_cast<int>((budget - fixed) / GV_STAGE_BYTES);
+        nstage = std::max(2, std::min(nstage, std::min(spc, GV_MAX_STAGE)));
+        const size_t smem = fixed + static_cast<size_t>(nstage) * GV_STAGE_BYTES;
         const int waves = ceil_div(col_tiles * splits, sm_count * per_sm);
-        const double cost = waves * (spc + 3.0) + 1.2 * splits;   // every split adds to the fixed-order reduction
+        // a shallow ring cannot keep the memory system busy: charge the stages that do not fit
+        // the reduction over 2 or 4 splits stays inside a cluster (cheap); other counts go through scratch
+        const double red = (splits == 2 || splits == 4) ? 0.6 : 1.2;
+        const double cost = waves * (spc + 3.0 + 0.5 * std::max(0, spc - nstage)) + red * splits;
         if (cost < best_cost) {
             best_cost = cost;
             best.splits = splits; best.stages_total = stages_total; best.stages_per_cta = spc;
-            best.smem = smem; best.ok = true;
+            best.nstage = nstage; best.smem = smem; best.ok = true;
         }
     }
     return best;
@@ -560,6 +577,7 @@ static int launch_gemv_t(lhb_ctx* ctx, const TensorMap& tm, GemvParams p, const 
     p.stages_total = pl.stages_total;
     p.stages_per_cta = pl.stages_per_cta;
     p.splits = pl.splits;
+    p.nstage = pl.nstage;
     p.groups_per_cta = gemv_groups_per_cta(WBITS, pl.stages_per_cta * GV_ROWS * (WBITS == 4 ? 2 : 1), p.G);
     p.partial = reinterpret_cast<float*>(ctx->scratch);
     p.counters = ctx->counters;

@@ -72,14 +72,14 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 // int8 x int8 -> int32 tensor-core MMAs (weights / pages as the 16-row operand)
 __device__ __forceinline__ void pd_imma32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                           uint32_t b0, uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
         "{%0,%1,%2,%3};"
         : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ void pd_imma16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
         : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
         : "r"(a0), "r"(a1), "r"(b0));
@@ -127,7 +127,7 @@ struct DecodeParams {
     float scale_log2e;
 };
 
-__global__ void __launch_bounds__(PD_THREADS, 3)
+__global__ void __launch_bounds__(PD_THREADS, 4)
 paged_decode_q8_kernel(const DecodeParams p) {
     extern __shared__ __align__(128) uint8_t pd_smem[];
     __shared__ int s_last;

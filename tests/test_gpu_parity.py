@@ -152,6 +152,24 @@ def test_w4a16_full_shape_cfg2(chk, lib):
     poll_ok()
 
 
+@pytest.mark.parametrize("splits", [1, 2, 3, 4, 8])
+def test_w4a16_every_split_reduction_path(chk, splits, monkeypatch):
+    """The K split is reduced inside a cluster (2 or 4 splits) or through the scratch
+    arena (other counts); force each and compare with the checker."""
+    monkeypatch.setenv("LHB_GEMV_SPLITS", str(splits))
+    rng = np.random.default_rng(splits)
+    M, N, K, G = 3, 1040, 2048, 128
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    W = (rng.standard_normal((K, N)) * 0.02).astype(np.float32)
+    p, s = chk.q4_quantize_groupwise(W, G)
+    C0 = rng.standard_normal((M, N)).astype(np.float32)
+    got = lb.gemm_w4a16_groupwise(dev(A), dev(p), dev(s), G, C=dev(C0), alpha=0.5, beta=2.0)
+    assert_close(host(got), chk.gemm_w4a16_groupwise(A, p, s, G, C0, alpha=0.5, beta=2.0), what=f"splits={splits}")
+    got2 = lb.gemm_w4a16_groupwise(dev(A), dev(p), dev(s), G, C=dev(C0), alpha=0.5, beta=2.0)
+    assert torch.equal(got, got2)
+    poll_ok()
+
+
 def test_w4a16_linearity_and_determinism():
     K, N, G = 2048, 2048, 128
     g = torch.Generator(device="cuda").manual_seed(5)
@@ -318,7 +336,7 @@ def test_attention_ignores_table_padding_and_is_deterministic(chk):
     wide = np.full((2, tables.shape[1] + 9), -1, np.int32); wide[:, :tables.shape[1]] = t2
     b = lb.paged_attention_q8_batched(Q, k, v, ks, vs, dev(wide), sl, cfg, lb_layout(L))
     # a wider table may change the KV split, i.e. the order of the fp32 sums, not the values
-    assert_close(host(b), host(a), rtol=1e-5, atol=1e-6, what="padding")
+    assert_close(host(b), host(a), rtol=1e-4, atol=1e-5, what="padding")
     a2 = lb.paged_attention_q8_batched(Q, k, v, ks, vs, dev(tables), sl, cfg, lb_layout(L))
     assert torch.equal(a, a2), "run-to-run determinism"
     poll_ok()
