@@ -69,6 +69,30 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+// Shared-memory accesses by 32-bit shared-space address (no generic 64-bit address math).
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ float ldsf(uint32_t a) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ void sts8(uint32_t a, int v) {
+    asm volatile("st.shared.u8 [%0], %1;" ::"r"(a), "r"(v) : "memory");
+}
+template <int OFF>
+__device__ __forceinline__ void cp_async16_off(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1 + %2], 16;" ::"r"(dst), "l"(src), "n"(OFF) : "memory");
+}
+
 // int8 x int8 -> int32 tensor-core MMAs (weights / pages as the 16-row operand)
 __device__ __forceinline__ void pd_imma32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                           uint32_t b0, uint32_t b1) {
@@ -241,71 +265,68 @@ paged_decode_q8_kernel(const DecodeParams p) {
     const int my_first = pg_lo + warp;                 // this warp's pages: my_first, +4, +8, ...
     const int n_iter = (pg_hi > my_first) ? (pg_hi - my_first + PD_WARPS - 1) / PD_WARPS : 0;
 
-    // lane l of ids_a / ids_b holds the page id of iteration 32*batch + l for
-    // the batch being consumed / the next one (prefetches run 3 iterations ahead)
-    int32_t ids_a = 0, ids_b = 0;
-    auto fetch_ids = [&](int batch) -> int32_t {
-        const int it = batch * 32 + lane;
-        return (it < n_iter) ? table[my_first + it * PD_WARPS] : 0;
-    };
-    auto page_id = [&](int it, int cur_batch) -> int {
-        const int a = __shfl_sync(0xffffffffu, ids_a, it & 31);
-        const int b = __shfl_sync(0xffffffffu, ids_b, it & 31);
-        return ((it >> 5) == cur_batch) ? a : b;
-    };
-    // lane-constant pieces of the page copy: chunk idx = c*32 + lane of a 2 KiB page
-    uint32_t cp_dst[4];
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-        const int idx = c * 32 + lane, tok = idx >> 3, ch = idx & 7;
-        cp_dst[c] = tok * 128 + ((ch ^ (tok & 7)) << 4);
-    }
-    auto issue = [&](int it, int cur_batch) {
+    // Page ids: lane l of `ids` holds the id of iteration 32*batch + l of the batch the
+    // prefetcher is in; validity of the pages in flight is remembered in `ok_bits`.
+    int32_t ids = 0;
+    int ids_batch = -1;
+    uint32_t ok_bits = 0;                               // bit (it & 31): page of iteration it is valid
+    // lane-constant pieces of the page copy: 16-byte chunk idx = c*32 + lane of a 2 KiB page goes to
+    // token idx/8, chunk (idx%8) ^ (token%8); for c the token is 4c + lane/8
+    const uint32_t cp_d0 = (lane >> 3) * 128 + (((lane & 7) ^ (lane >> 3)) << 4);
+    const uint32_t lane16 = lane * 16;
+    uint32_t issue_off = 0;                             // stage offset of the next copy in the ring
+    auto issue = [&](int it) {
         if (it < n_iter) {
-            int blk = page_id(it, cur_batch);
-            if (blk < 0 || blk >= p.num_blocks) blk = 0;           // masked below; never dereference a bad id
-            const int64_t row0 = (static_cast<int64_t>(blk) * p.n_kv_heads + kvh) * PD_BS;
-            const uint32_t st = ring_u32 + (it % PD_STAGES) * PD_STAGE_BYTES;
-            const int8_t* kp = p.Kp + row0 * PD_D;
-            const int8_t* vp = p.Vp + row0 * PD_D;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                cp_async16(st + cp_dst[c], kp + (c * 32 + lane) * 16);
-                cp_async16(st + 2048 + cp_dst[c], vp + (c * 32 + lane) * 16);
+            if ((it >> 5) != ids_batch) {               // entering a new batch of 32 iterations
+                ids_batch = it >> 5;
+                const int j = ids_batch * 32 + lane;
+                ids = (j < n_iter) ? table[my_first + j * PD_WARPS] : 0;
             }
-            if (lane < 4) cp_async16(st + 4096 + lane * 16, p.Ks + row0 + lane * 4);
-            else if (lane < 8) cp_async16(st + 4160 + (lane - 4) * 16, p.Vs + row0 + (lane - 4) * 4);
+            int blk = __shfl_sync(0xffffffffu, ids, it & 31);
+            const bool okp = blk >= 0 && blk < p.num_blocks;
+            ok_bits = okp ? (ok_bits | (1u << (it & 31))) : (ok_bits & ~(1u << (it & 31)));
+            if (!okp) blk = 0;                          // masked at use; a bad id is never dereferenced
+            const int64_t row0 = (static_cast<int64_t>(blk) * p.n_kv_heads + kvh) * PD_BS;
+            const uint32_t st = ring_u32 + issue_off;
+            const int8_t* kp = p.Kp + row0 * PD_D + lane16;
+            const int8_t* vp = p.Vp + row0 * PD_D + lane16;
+            const uint32_t d0 = st + cp_d0, d1 = st + (cp_d0 ^ 64);
+            cp_async16_off<0>(d0, kp);            cp_async16_off<0>(d0 + 2048, vp);
+            cp_async16_off<512>(d1 + 512, kp);    cp_async16_off<512>(d1 + 2048 + 512, vp);
+            cp_async16_off<1024>(d0 + 1024, kp);  cp_async16_off<1024>(d0 + 2048 + 1024, vp);
+            cp_async16_off<1536>(d1 + 1536, kp);  cp_async16_off<1536>(d1 + 2048 + 1536, vp);
+            if (lane < 4) cp_async16(st + 4096 + lane16, p.Ks + row0 + lane * 4);
+            else if (lane < 8) cp_async16(st + 4160 + lane16 - 64, p.Vs + row0 + (lane - 4) * 4);
         }
+        issue_off = (issue_off == (PD_STAGES - 1) * PD_STAGE_BYTES) ? 0 : issue_off + PD_STAGE_BYTES;
         cp_async_commit();
     };
 
-    ids_a = fetch_ids(0);
-    ids_b = fetch_ids(1);
 #pragma unroll
-    for (int s = 0; s < PD_STAGES - 1; ++s) issue(s, 0);
+    for (int s = 0; s < PD_STAGES - 1; ++s) issue(s);
+
+    // lane-constant shared offsets inside a stage
+    const uint32_t ka = g * 128 + (((2 * t) ^ g) << 4);                 // K: token g, chunk 2t (chunk 2t+1: ^16; token g+8: +1024)
+    const uint32_t vb = 2048 + 4 * t * 128 + ((g ^ (4 * (t & 1))) << 4);  // V: token 4t + j: (vb ^ (j << 4)) + 128 j
+    const uint32_t pdig_u32 = ring_u32 + PD_STAGES * PD_STAGE_BYTES;
+    const uint32_t pst = pdig_u32 + 32 * t + g;                         // digit bytes of this thread's tokens g, g+8
+    const uint32_t pld = pdig_u32 + g * 16 + 4 * t;                     // operand register: column g, tokens 4t..4t+3
+    uint32_t use_off = 0;
 
     for (int it = 0; it < n_iter; ++it) {
-        const int batch = it >> 5;
-        if ((it & 31) == 0 && it > 0) { ids_a = ids_b; ids_b = fetch_ids(batch + 1); }
         cp_async_wait<PD_STAGES - 2>();
         __syncwarp();                                   // every lane is done with iteration it - 1
-        issue(it + PD_STAGES - 1, batch);               // refills the stage iteration it - 1 used
-        const uint8_t* st = ring + (it % PD_STAGES) * PD_STAGE_BYTES;
-        const int page = my_first + it * PD_WARPS;
-        const int tok0 = page * PD_BS;
-        const int blk_id = page_id(it, batch);
-        const bool page_ok = blk_id >= 0 && blk_id < p.num_blocks;
+        issue(it + PD_STAGES - 1);                      // refills the stage iteration it - 1 used
+        const uint32_t st = ring_u32 + use_off;
+        use_off = (use_off == (PD_STAGES - 1) * PD_STAGE_BYTES) ? 0 : use_off + PD_STAGE_BYTES;
+        const int tok0 = (my_first + it * PD_WARPS) * PD_BS;
+        const bool page_ok = (ok_bits >> (it & 31)) & 1u;
 
         // ---- S = K Q^T: int8 rows of K are MMA operand registers as they lie ------------
         int s0[4] = {0, 0, 0, 0}, s1[4] = {0, 0, 0, 0};     // block 0: (d1, d2) of head t; block 1: d3
         {
-            const uint8_t* r0 = st + g * 128;           // token g
-            const uint8_t* r1 = st + (g + 8) * 128;     // token g + 8 (same swizzle: (g+8)&7 == g)
-            const int sw = g & 7;
-            const uint4 a0 = *reinterpret_cast<const uint4*>(r0 + (((2 * t) ^ sw) << 4));
-            const uint4 a1 = *reinterpret_cast<const uint4*>(r0 + (((2 * t + 1) ^ sw) << 4));
-            const uint4 b0 = *reinterpret_cast<const uint4*>(r1 + (((2 * t) ^ sw) << 4));
-            const uint4 b1 = *reinterpret_cast<const uint4*>(r1 + (((2 * t + 1) ^ sw) << 4));
+            const uint4 a0 = lds128(st + ka), a1 = lds128(st + (ka ^ 16));                   // token g
+            const uint4 b0 = lds128(st + ka + 1024), b1 = lds128(st + (ka ^ 16) + 1024);     // token g + 8
             const uint32_t wa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
             const uint32_t wb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
@@ -315,15 +336,14 @@ paged_decode_q8_kernel(const DecodeParams p) {
             }
         }
         // ---- scores in base 2, V row scale folded into the exponent ------------------------
-        const float* ksr = reinterpret_cast<const float*>(st + 4096);
-        const float* vsr = reinterpret_cast<const float*>(st + 4160);
-        float x0 = fmaf(16384.0f, pd_i2f(s0[0]), fmaf(128.0f, pd_i2f(s0[1]), pd_i2f(s1[0]))) * ksr[g] * sc;
-        float x1 = fmaf(16384.0f, pd_i2f(s0[2]), fmaf(128.0f, pd_i2f(s0[3]), pd_i2f(s1[2]))) * ksr[g + 8] * sc;
+        const uint32_t sca = st + 4096 + 4 * g;               // ks[g], +32: ks[g+8], +64: vs[g], +96: vs[g+8]
+        float x0 = fmaf(16384.0f, pd_i2f(s0[0]), fmaf(128.0f, pd_i2f(s0[1]), pd_i2f(s1[0]))) * ldsf(sca) * sc;
+        float x1 = fmaf(16384.0f, pd_i2f(s0[2]), fmaf(128.0f, pd_i2f(s0[3]), pd_i2f(s1[2]))) * ldsf(sca + 32) * sc;
         const int p0 = tok0 + g, p1 = tok0 + g + 8;
         const bool ok0 = page_ok && p0 >= first && p0 <= last;
         const bool ok1 = page_ok && p1 >= first && p1 <= last;
-        const float lv0 = fmaxf(fast_log2(vsr[g]), PD_MIN_LOG2_VS);
-        const float lv1 = fmaxf(fast_log2(vsr[g + 8]), PD_MIN_LOG2_VS);
+        const float lv0 = fmaxf(fast_log2(ldsf(sca + 64)), PD_MIN_LOG2_VS);
+        const float lv1 = fmaxf(fast_log2(ldsf(sca + 96)), PD_MIN_LOG2_VS);
         x0 = ok0 ? x0 : -INFINITY;
         x1 = ok1 ? x1 : -INFINITY;
         const float y0 = x0 + lv0, y1 = x1 + lv1;              // -inf stays -inf
@@ -357,22 +377,20 @@ paged_decode_q8_kernel(const DecodeParams p) {
             const int l1 = ((w1 + 64) & 127) - 64; w1 = (w1 - l1) >> 7;
             const int m0 = ((w0 + 64) & 127) - 64; const int h0 = (w0 - m0) >> 7;
             const int m1 = ((w1 + 64) & 127) - 64; const int h1 = (w1 - m1) >> 7;
-            uint8_t* c0 = pdig + (2 * t) * 16;          // block 0, column 2t (d1); +16: column 2t+1 (d2)
-            c0[g] = static_cast<uint8_t>(h0); c0[g + 8] = static_cast<uint8_t>(h1);
-            c0[16 + g] = static_cast<uint8_t>(m0); c0[16 + g + 8] = static_cast<uint8_t>(m1);
-            c0[128 + g] = static_cast<uint8_t>(l0); c0[128 + g + 8] = static_cast<uint8_t>(l1);   // block 1, column 2t (d3)
+            // block 0 column 2t (d1) at +0, column 2t+1 (d2) at +16, block 1 column 2t (d3) at +128
+            sts8(pst, h0); sts8(pst + 8, h1);
+            sts8(pst + 16, m0); sts8(pst + 24, m1);
+            sts8(pst + 128, l0); sts8(pst + 136, l1);
         }
         __syncwarp();
-        const uint32_t pb0 = *reinterpret_cast<const uint32_t*>(pdig + g * 16 + 4 * t);
-        const uint32_t pb1 = *reinterpret_cast<const uint32_t*>(pdig + 128 + g * 16 + 4 * t);
+        const uint32_t pb0 = lds32(pld);
+        const uint32_t pb1 = lds32(pld + 128);
         // ---- O += V^T P: 4x4 byte transposes turn V rows into "4 tokens of one head_dim" registers
         {
-            const uint8_t* vb = st + 2048;
             uint32_t vr[4][4];                          // [token 4t + j][word: head_dim 16g + 4w .. +3]
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const int r = 4 * t + j;
-                const uint4 v = *reinterpret_cast<const uint4*>(vb + r * 128 + ((g ^ (r & 7)) << 4));
+                const uint4 v = lds128(st + ((vb ^ (j << 4)) + 128 * j));
                 vr[j][0] = v.x; vr[j][1] = v.y; vr[j][2] = v.z; vr[j][3] = v.w;
             }
 #pragma unroll
