@@ -52,6 +52,7 @@ constexpr int PD_D = 128;
 constexpr int PD_BS = 16;
 constexpr int PD_STAGE_BYTES = 2048 + 2048 + 64 + 64;          // K, V, ks, vs
 constexpr int PD_WARP_BYTES = PD_STAGES * PD_STAGE_BYTES + 256;  // + P digit exchange buffer
+constexpr int PD_SMEM_BYTES = PD_WARPS * PD_WARP_BYTES + 2048;  // + the CTA's Q digit fragments
 constexpr int PD_MAX_GROUP = 4;
 constexpr int PD_PART = PD_D + 2;                               // floats per (split, head): m, l, O[128]
 constexpr float PD_WSHIFT = 20.0f;                              // P weights are integers in [0, 2^20]
@@ -146,7 +147,9 @@ struct DecodeParams {
     float* part;             // scratch: [n_req, n_kv, splits, group, PD_PART]
     int* counters;           // [n_req * n_kv], zero between calls
     int* status;
-    int max_blocks, n_q_heads, n_kv_heads, group, num_blocks, splits;
+    int max_blocks, n_q_heads, n_kv_heads, group, num_blocks;
+    int splits;              // grid.x: the most splits any request can use
+    int pages_per_cta;       // a request is cut into ceil(pages / pages_per_cta) splits, at most `splits`
     int window, chunk;
     float scale_log2e;
 };
@@ -169,7 +172,11 @@ paged_decode_q8_kernel(const DecodeParams p) {
     if (p.chunk > 0 && len > 0) first = max(first, (last / p.chunk) * p.chunk);
     const int page_f = first / PD_BS;
     const int n_pages = (len > 0 && last >= first) ? last / PD_BS - page_f + 1 : 0;
-    const int per_split = (n_pages + p.splits - 1) / p.splits;
+    // Long requests are cut into more pieces than short ones, so that every CTA
+    // has about the same number of pages; CTAs beyond a request's piece count leave.
+    const int nsplit = max(1, min(p.splits, (n_pages + p.pages_per_cta - 1) / p.pages_per_cta));
+    if (split >= nsplit) return;
+    const int per_split = (n_pages + nsplit - 1) / nsplit;
     const int pg_lo = page_f + split * per_split;
     const int pg_hi = min(page_f + n_pages, pg_lo + per_split);   // exclusive
     const int32_t* table = p.tables + static_cast<int64_t>(req) * p.max_blocks;
@@ -203,8 +210,10 @@ paged_decode_q8_kernel(const DecodeParams p) {
         for (int h = 0; h < PD_MAX_GROUP; ++h)
             if (h == hq) qs = 1.0f / qinv[h];          // exact: powers of two
         const bool live = hq < G;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        // warp w converts k-step w; the CTA shares the fragments through shared memory
+        uint32_t* qsm = reinterpret_cast<uint32_t*>(pd_smem + PD_WARPS * PD_WARP_BYTES);    // [k-step][block][reg][lane]
+        {
+            const int i = warp;
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
                 float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -221,10 +230,17 @@ paged_decode_q8_kernel(const DecodeParams p) {
                     b0 |= static_cast<uint32_t>((odd ? mid : hi) & 0xff) << (8 * j);
                     b1 |= static_cast<uint32_t>((odd ? 0 : lo) & 0xff) << (8 * j);
                 }
-                qf[i][0][r] = b0;
-                qf[i][1][r] = b1;
+                qsm[((i * 2 + 0) * 2 + r) * 32 + lane] = b0;
+                qsm[((i * 2 + 1) * 2 + r) * 32 + lane] = b1;
             }
         }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int b = 0; b < 2; ++b)
+#pragma unroll
+                for (int r = 0; r < 2; ++r) qf[i][b][r] = qsm[((i * 2 + b) * 2 + r) * 32 + lane];
     }
 
     // ---- per-warp state ---------------------------------------------------------
@@ -290,11 +306,12 @@ paged_decode_q8_kernel(const DecodeParams p) {
             const uint32_t st = ring_u32 + issue_off;
             const int8_t* kp = p.Kp + row0 * PD_D + lane16;
             const int8_t* vp = p.Vp + row0 * PD_D + lane16;
-            const uint32_t d0 = st + cp_d0, d1 = st + (cp_d0 ^ 64);
+            // tokens 4c + lane/8: sw differs from sw(lane/8) by (c & 1) << 2 and (c >> 1) << 1
+            const uint32_t d0 = st + cp_d0, d1 = st + (cp_d0 ^ 64), d2 = st + (cp_d0 ^ 32), d3 = st + (cp_d0 ^ 96);
             cp_async16_off<0>(d0, kp);            cp_async16_off<0>(d0 + 2048, vp);
             cp_async16_off<512>(d1 + 512, kp);    cp_async16_off<512>(d1 + 2048 + 512, vp);
-            cp_async16_off<1024>(d0 + 1024, kp);  cp_async16_off<1024>(d0 + 2048 + 1024, vp);
-            cp_async16_off<1536>(d1 + 1536, kp);  cp_async16_off<1536>(d1 + 2048 + 1536, vp);
+            cp_async16_off<1024>(d2 + 1024, kp);  cp_async16_off<1024>(d2 + 2048 + 1024, vp);
+            cp_async16_off<1536>(d3 + 1536, kp);  cp_async16_off<1536>(d3 + 2048 + 1536, vp);
             if (lane < 4) cp_async16(st + 4096 + lane16, p.Ks + row0 + lane * 4);
             else if (lane < 8) cp_async16(st + 4160 + lane16 - 64, p.Vs + row0 + (lane - 4) * 4);
         }
@@ -306,8 +323,10 @@ paged_decode_q8_kernel(const DecodeParams p) {
     for (int s = 0; s < PD_STAGES - 1; ++s) issue(s);
 
     // lane-constant shared offsets inside a stage
-    const uint32_t ka = g * 128 + (((2 * t) ^ g) << 4);                 // K: token g, chunk 2t (chunk 2t+1: ^16; token g+8: +1024)
-    const uint32_t vb = 2048 + 4 * t * 128 + ((g ^ (4 * (t & 1))) << 4);  // V: token 4t + j: (vb ^ (j << 4)) + 128 j
+    // 16-byte chunk c of token row r sits at chunk c ^ sw(r), sw(r) = (r & 5) | (((r >> 1) ^ (r >> 3)) & 1) << 1:
+    // conflict-free for the K reads (rows g, g+8) and the V reads (rows 4t + j) alike
+    const uint32_t ka = g * 128 + (((2 * t) ^ g) << 4);                 // K: token g, chunk 2t (chunk 2t+1: ^16; token g+8: (^32) + 1024)
+    const uint32_t vb = 2048 + 4 * t * 128 + ((g ^ ((t >> 1) << 1) ^ ((t & 1) << 2)) << 4);  // V: token 4t + j: (vb ^ (j << 4)) + 128 j
     const uint32_t pdig_u32 = ring_u32 + PD_STAGES * PD_STAGE_BYTES;
     const uint32_t pst = pdig_u32 + 32 * t + g;                         // digit bytes of this thread's tokens g, g+8
     const uint32_t pld = pdig_u32 + g * 16 + 4 * t;                     // operand register: column g, tokens 4t..4t+3
@@ -326,7 +345,7 @@ paged_decode_q8_kernel(const DecodeParams p) {
         int s0[4] = {0, 0, 0, 0}, s1[4] = {0, 0, 0, 0};     // block 0: (d1, d2) of head t; block 1: d3
         {
             const uint4 a0 = lds128(st + ka), a1 = lds128(st + (ka ^ 16));                   // token g
-            const uint4 b0 = lds128(st + ka + 1024), b1 = lds128(st + (ka ^ 16) + 1024);     // token g + 8
+            const uint4 b0 = lds128(st + (ka ^ 32) + 1024), b1 = lds128(st + (ka ^ 48) + 1024);   // token g + 8
             const uint32_t wa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
             const uint32_t wb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
@@ -443,7 +462,7 @@ paged_decode_q8_kernel(const DecodeParams p) {
             L += f * sm_l[w * PD_MAX_GROUP + h];
             o += f * sm_o[(w * PD_MAX_GROUP + h) * PD_D + d];
         }
-        if (p.splits == 1) {
+        if (nsplit == 1) {
             float* out = p.O + (static_cast<int64_t>(req) * p.n_q_heads + kvh * G + h) * PD_D;
             out[d] = (L > 0.0f) ? o * (1.0f / L) * exp2f(-PD_WSHIFT) : 0.0f;
         } else {
@@ -452,7 +471,7 @@ paged_decode_q8_kernel(const DecodeParams p) {
             pp[2 + d] = o;
         }
     }
-    if (p.splits == 1) return;
+    if (nsplit == 1) return;
 
     // ---- cross-CTA merge: the last split to arrive combines all partials ------------------
     __threadfence();
@@ -460,7 +479,7 @@ paged_decode_q8_kernel(const DecodeParams p) {
     const int cidx = req * p.n_kv_heads + kvh;
     if (threadIdx.x == 0) {
         const int old = atomicAdd(p.counters + cidx, 1);
-        s_last = (old == p.splits - 1);
+        s_last = (old == nsplit - 1);
         if (s_last) p.counters[cidx] = 0;              // ready for the next call
     }
     __syncthreads();
@@ -469,9 +488,9 @@ paged_decode_q8_kernel(const DecodeParams p) {
     const int64_t b0 = (static_cast<int64_t>(req) * p.n_kv_heads + kvh) * p.splits * G;
     for (int h = 0; h < G; ++h) {
         float M = -INFINITY;
-        for (int s = 0; s < p.splits; ++s) M = fmaxf(M, __ldcg(p.part + (b0 + s * G + h) * PD_PART));
+        for (int s = 0; s < nsplit; ++s) M = fmaxf(M, __ldcg(p.part + (b0 + s * G + h) * PD_PART));
         float L = 0.0f, o = 0.0f;
-        for (int s = 0; s < p.splits; ++s) {
+        for (int s = 0; s < nsplit; ++s) {
             const float* pp = p.part + (b0 + s * G + h) * PD_PART;
             const float ms = __ldcg(pp);
             const float f = (ms == -INFINITY) ? 0.0f : fast_exp2(ms - M);
@@ -481,6 +500,25 @@ paged_decode_q8_kernel(const DecodeParams p) {
         float* out = p.O + (static_cast<int64_t>(req) * p.n_q_heads + kvh * G + h) * PD_D;
         out[d] = (L > 0.0f) ? o * (1.0f / L) * exp2f(-PD_WSHIFT) : 0.0f;
     }
+}
+
+// How a request is cut: `pages` pages (16 tokens each) per CTA, hence at most
+// `splits` pieces for the longest request the table can describe.  Sized so that
+// about six CTAs per SM exist if requests are half as long as the table allows,
+// within 8..40 pages per CTA (fewer pages: the per-CTA set-up dominates; more:
+// the last CTAs to finish leave SMs idle).
+static void decode_split_plan(int sm_count, int64_t items, int max_blocks, size_t part_floats_avail, int group,
+                              int* splits, int* pages) {
+    int64_t pp = items * max_blocks / (12LL * std::max(1, sm_count));
+    int pg = static_cast<int>(std::max<int64_t>(8, std::min<int64_t>(40, pp)));
+    if (const char* e = getenv("LHB_DECODE_PAGES")) pg = std::max(1, atoi(e));
+    int sp = std::max(1, std::min(32, ceil_div(max_blocks, pg)));
+    if (const char* e = getenv("LHB_DECODE_SPLITS")) sp = std::max(1, std::min(sp, atoi(e)));
+    const size_t per_split = static_cast<size_t>(items) * group * PD_PART;
+    if (sp > 1 && per_split * sp > part_floats_avail)
+        sp = static_cast<int>(std::max<size_t>(1, part_floats_avail / per_split));
+    *splits = sp;
+    *pages = std::max(pg, ceil_div(max_blocks, sp));       // every page of the longest request is covered
 }
 
 bool decode_fast_ok(const lhb_paged_attn_cfg& cfg, const lhb_paged_layout& L) {
@@ -496,27 +534,20 @@ int launch_decode_fast(lhb_ctx* ctx, const float* Q, const int8_t* Kp, const int
                        const lhb_paged_layout& L, cudaStream_t st) {
     const int group = cfg.n_q_heads / cfg.n_kv_heads;
     const int64_t items = static_cast<int64_t>(n_req) * cfg.n_kv_heads;
-    // enough CTAs to keep ~8 per SM, at least ~8 pages per CTA
-    int splits = static_cast<int>(ceil_div64(8LL * ctx->sm_count, items));
-    splits = std::max(1, std::min(splits, std::max(1, max_blocks / 8)));
-    splits = std::min(splits, 32);
-    if (const char* e = getenv("LHB_DECODE_SPLITS")) splits = std::max(1, std::min(64, atoi(e)));
-    if (items > static_cast<int64_t>(ctx->counters_len)) splits = 1;
-    const size_t need = static_cast<size_t>(items) * splits * group * PD_PART * sizeof(float);
-    if (splits > 1 && need > ctx->scratch_bytes) {
-        splits = static_cast<int>(ctx->scratch_bytes / (static_cast<size_t>(items) * group * PD_PART * sizeof(float)));
-        if (splits < 1) splits = 1;
-    }
+    int splits = 1, pages = max_blocks;
+    decode_split_plan(ctx->sm_count, items, max_blocks,
+                      items > static_cast<int64_t>(ctx->counters_len) ? 0 : ctx->scratch_bytes / sizeof(float), group,
+                      &splits, &pages);
     DecodeParams p{};
     p.Q = Q; p.Kp = Kp; p.Vp = Vp; p.Ks = Ks; p.Vs = Vs; p.tables = tables; p.seq_lens = seq_lens;
     p.O = O; p.part = reinterpret_cast<float*>(ctx->scratch); p.counters = ctx->counters;
     p.status = ctx->status_word;
     p.max_blocks = max_blocks; p.n_q_heads = cfg.n_q_heads; p.n_kv_heads = cfg.n_kv_heads;
-    p.group = group; p.num_blocks = L.num_blocks; p.splits = splits;
+    p.group = group; p.num_blocks = L.num_blocks; p.splits = splits; p.pages_per_cta = pages;
     p.window = cfg.window; p.chunk = cfg.chunk;
     const float scale = cfg.scale > 0.0f ? cfg.scale : 1.0f / sqrtf(static_cast<float>(cfg.head_dim));
     p.scale_log2e = scale * 1.4426950408889634f;
-    const size_t smem = PD_WARPS * PD_WARP_BYTES;
+    const size_t smem = PD_SMEM_BYTES;
     static bool attr_set[64] = {};
     if (!attr_set[ctx->device & 63]) {
         LHB_CUDA(cudaFuncSetAttribute(paged_decode_q8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -581,7 +612,7 @@ int na_setup(int dev, NoAllocDevice** out) {
         LHB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&d.status), g_na_status));
         LHB_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
         LHB_CUDA(cudaFuncSetAttribute(paged_decode_q8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      PD_WARPS * PD_WARP_BYTES));
+                                      PD_SMEM_BYTES));
         d.ready = true;
     }
     *out = &d;
@@ -625,11 +656,9 @@ extern "C" int lhb_paged_attention_q8_batched_noalloc(
                             std::to_string(items) + " exceeds the fixed limit of " + std::to_string(NA_COUNTERS));
         return LHB_ERR_SCRATCH;
     }
-    // same split rule as the context-based entry point, so both give the same bits
-    int splits = static_cast<int>(ceil_div64(8LL * d->sm_count, items));
-    splits = std::max(1, std::min(splits, std::max(1, max_blocks_per_req / 8)));
-    splits = std::min(splits, 32);
-    if (const char* e = getenv("LHB_DECODE_SPLITS")) splits = std::max(1, std::min(64, atoi(e)));
+    // same split rule as the context-based entry point with its default arena, so both give the same bits
+    int splits = 1, pages = max_blocks_per_req;
+    decode_split_plan(d->sm_count, items, max_blocks_per_req, size_t(64) << 18, group, &splits, &pages);
     const size_t need = static_cast<size_t>(items) * splits * group * PD_PART;
     if (splits > 1 && need > NA_PART_FLOATS) {
         set_last_error_text("lhb_paged_attention_q8_batched_noalloc: " + std::to_string(need * sizeof(float)) +
@@ -644,12 +673,12 @@ extern "C" int lhb_paged_attention_q8_batched_noalloc(
     p.tables = block_tables; p.seq_lens = seq_lens; p.O = O;
     p.part = d->partials; p.counters = d->counters; p.status = d->status;
     p.max_blocks = max_blocks_per_req; p.n_q_heads = cfg->n_q_heads; p.n_kv_heads = cfg->n_kv_heads;
-    p.group = group; p.num_blocks = layout->num_blocks; p.splits = splits;
+    p.group = group; p.num_blocks = layout->num_blocks; p.splits = splits; p.pages_per_cta = pages;
     p.window = cfg->window; p.chunk = cfg->chunk;
     const float scale = cfg->scale > 0.0f ? cfg->scale : 1.0f / sqrtf(static_cast<float>(cfg->head_dim));
     p.scale_log2e = scale * 1.4426950408889634f;
     dim3 grid(splits, cfg->n_kv_heads, n_requests);
-    paged_decode_q8_kernel<<<grid, PD_THREADS, PD_WARPS * PD_WARP_BYTES, st>>>(p);
+    paged_decode_q8_kernel<<<grid, PD_THREADS, PD_SMEM_BYTES, st>>>(p);
     LHB_LAUNCH_CHECK();
     return LHB_OK;
 }
