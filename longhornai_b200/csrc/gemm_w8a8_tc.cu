@@ -21,9 +21,13 @@
 // with single roundings (src/kernels/gemm_quant.cpp:44-46), so the output is
 // bit-identical to the reference.
 //
+// For M >= 256 the CTA-pair variant further down is used instead (two CTAs of a
+// cluster share a 256 x 256 tile; LHB_W8A8_PAIR=0 forces this kernel).
+//
 // Every wait is bounded (ptx::mbar_wait); a timeout sets the context's status
 // word, all roles fall through to the common exit and TMEM is freed.
 #include <algorithm>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "dispatch.h"
@@ -56,6 +60,47 @@ struct W8Params {
     int tiles_m, tiles_n;
     int* status;
 };
+
+
+// One 32-column chunk of one output row: C = beta*C + ((alpha*a_s)*b_s[n])*float(acc),
+// multiplied in the reference's order with single roundings.
+__device__ __forceinline__ void w8_store_chunk(float* crow, int nb, const uint32_t (&r)[32], float sa,
+                                               const W8Params& p) {
+    if (nb + 32 <= p.N) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+            const float4 bs = __ldg(reinterpret_cast<const float4*>(p.b_scales + nb + j));
+            float4 v;
+            v.x = __fmul_rn(__fmul_rn(sa, bs.x), static_cast<float>(static_cast<int>(r[j])));
+            v.y = __fmul_rn(__fmul_rn(sa, bs.y), static_cast<float>(static_cast<int>(r[j + 1])));
+            v.z = __fmul_rn(__fmul_rn(sa, bs.z), static_cast<float>(static_cast<int>(r[j + 2])));
+            v.w = __fmul_rn(__fmul_rn(sa, bs.w), static_cast<float>(static_cast<int>(r[j + 3])));
+            float4* dst = reinterpret_cast<float4*>(crow + nb + j);
+            if (p.beta != 0.0f) {
+                const float4 o = *dst;
+                if (p.beta == 1.0f) {
+                    v.x = __fadd_rn(o.x, v.x); v.y = __fadd_rn(o.y, v.y);
+                    v.z = __fadd_rn(o.z, v.z); v.w = __fadd_rn(o.w, v.w);
+                } else {
+                    v.x = __fadd_rn(__fmul_rn(o.x, p.beta), v.x); v.y = __fadd_rn(__fmul_rn(o.y, p.beta), v.y);
+                    v.z = __fadd_rn(__fmul_rn(o.z, p.beta), v.z); v.w = __fadd_rn(__fmul_rn(o.w, p.beta), v.w);
+                }
+            }
+            *dst = v;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            if (nb + j < p.N) {
+                float v = __fmul_rn(__fmul_rn(sa, p.b_scales[nb + j]), static_cast<float>(static_cast<int>(r[j])));
+                float* dst = crow + nb + j;
+                if (p.beta == 1.0f) v = __fadd_rn(*dst, v);
+                else if (p.beta != 0.0f) v = __fadd_rn(__fmul_rn(*dst, p.beta), v);
+                *dst = v;
+            }
+        }
+    }
+}
 
 __global__ void __launch_bounds__(W8_THREADS, 1)
 gemm_w8a8_tc_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ TensorMap tmB,
@@ -172,37 +217,7 @@ gemm_w8a8_tc_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant
                 }
                 const int nb = n0 + c * 32;
                 if (!row_ok || nb >= p.N) continue;
-                if (nb + 32 <= p.N) {
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        const float4 bs = __ldg(reinterpret_cast<const float4*>(p.b_scales + nb + j));
-                        float4 v;
-                        v.x = __fmul_rn(__fmul_rn(sa, bs.x), static_cast<float>(static_cast<int>(r[j])));
-                        v.y = __fmul_rn(__fmul_rn(sa, bs.y), static_cast<float>(static_cast<int>(r[j + 1])));
-                        v.z = __fmul_rn(__fmul_rn(sa, bs.z), static_cast<float>(static_cast<int>(r[j + 2])));
-                        v.w = __fmul_rn(__fmul_rn(sa, bs.w), static_cast<float>(static_cast<int>(r[j + 3])));
-                        float4* dst = reinterpret_cast<float4*>(crow + nb + j);
-                        if (p.beta != 0.0f) {
-                            const float4 o = *dst;
-                            if (p.beta == 1.0f) {
-                                v.x = __fadd_rn(o.x, v.x); v.y = __fadd_rn(o.y, v.y);
-                                v.z = __fadd_rn(o.z, v.z); v.w = __fadd_rn(o.w, v.w);
-                            } else {
-                                v.x = __fadd_rn(__fmul_rn(o.x, p.beta), v.x); v.y = __fadd_rn(__fmul_rn(o.y, p.beta), v.y);
-                                v.z = __fadd_rn(__fmul_rn(o.z, p.beta), v.z); v.w = __fadd_rn(__fmul_rn(o.w, p.beta), v.w);
-                            }
-                        }
-                        *dst = v;
-                    }
-                } else {
-                    for (int j = 0; j < 32 && nb + j < p.N; ++j) {
-                        float v = __fmul_rn(__fmul_rn(sa, p.b_scales[nb + j]), static_cast<float>(static_cast<int>(r[j])));
-                        float* dst = crow + nb + j;
-                        if (p.beta == 1.0f) v = __fadd_rn(*dst, v);
-                        else if (p.beta != 0.0f) v = __fadd_rn(__fmul_rn(*dst, p.beta), v);
-                        *dst = v;
-                    }
-                }
+                w8_store_chunk(crow, nb, r, sa, p);
             }
         }
     }
@@ -212,6 +227,149 @@ gemm_w8a8_tc_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant
     if (warp == 2) {
         ptx::tc_fence_after();
         ptx::tmem_dealloc(tmem_base, W8_TMEM_COLS);
+    }
+}
+
+
+// ---------------------------------------------------------------------------
+// CTA-pair variant: two CTAs of a cluster share one 256 x 256 output tile.
+// Each CTA loads its 128 rows of A and its 128 columns of B (32 KiB per stage
+// instead of 48), the leader issues tcgen05.mma.cta_group::2 (M = 256) that
+// reads both CTAs' shared memory, and each CTA's TMEM receives its 128 rows.
+// Shared-memory traffic per MMA drops by a third, which is what limits the
+// single-CTA kernel.  Barriers: "full" lives in the leader (both CTAs' loads
+// report there), "empty" and "accumulator full" exist in both CTAs (the leader
+// commits to each), "accumulator empty" lives in the leader (256 arrivals).
+// ---------------------------------------------------------------------------
+constexpr int W8P_STAGES = 6;
+constexpr int W8P_A_BYTES = 128 * W8_BK;             // this CTA's 128 rows
+constexpr int W8P_B_BYTES = W8_BK * 128;             // this CTA's 128 columns
+constexpr int W8P_STAGE_BYTES = W8P_A_BYTES + W8P_B_BYTES;
+constexpr size_t W8P_SMEM = 1024 + static_cast<size_t>(W8P_STAGES) * W8P_STAGE_BYTES + 256;
+constexpr uint32_t W8P_IDESC = (2u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
+                               (static_cast<uint32_t>(256 >> 3) << 17) | (static_cast<uint32_t>(256 >> 4) << 24);
+
+__global__ void __launch_bounds__(W8_THREADS, 1)
+gemm_w8a8_tc_pair_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ TensorMap tmB,
+                         const W8Params p) {
+    extern __shared__ uint8_t w8_smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(w8_smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + W8P_STAGES * W8P_STAGE_BYTES);
+    // bars[0..5] full, [6..11] empty, [12..13] tmem_full, [14..15] tmem_empty
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = ptx::cluster_ctarank();       // 0 = leader
+    const uint32_t bar0 = ptx::smem_u32(bars);
+    auto full_bar = [&](int s) { return bar0 + 8 * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8 * (W8P_STAGES + s); };
+    auto tfull_bar = [&](int b) { return bar0 + 8 * (2 * W8P_STAGES + b); };
+    auto tempty_bar = [&](int b) { return bar0 + 8 * (2 * W8P_STAGES + 2 + b); };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < W8P_STAGES; ++s) { ptx::mbar_init(full_bar(s), 1); ptx::mbar_init(empty_bar(s), 1); }
+        for (int b = 0; b < 2; ++b) { ptx::mbar_init(tfull_bar(b), 1); ptx::mbar_init(tempty_bar(b), 256); }
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+        ptx::prefetch_tmap(&tmA);
+        ptx::prefetch_tmap(&tmB);
+    }
+    if (warp == 2) {
+        ptx::tmem_alloc_pair(ptx::smem_u32(tmem_slot), W8_TMEM_COLS);
+        ptx::tmem_relinquish_pair();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::cluster_sync_all();                            // both CTAs' barriers exist before anyone signals them
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int tiles_m = (p.M + 255) / 256;
+    const int n_tiles = tiles_m * p.tiles_n;
+    const int num_kb = (p.K + W8_BK - 1) / W8_BK;
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            for (int tile = pair; tile < n_tiles && !*abort_flag; tile += n_pairs) {
+                const int m0 = (tile % tiles_m) * 256 + 128 * rank, n0 = (tile / tiles_m) * W8_BN + 128 * rank;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % W8P_STAGES;
+                    if (!ptx::mbar_wait(empty_bar(s), ((it / W8P_STAGES) & 1) ^ 1, abort_flag, p.status)) break;
+                    const uint32_t leader_full = ptx::mapa_shared(full_bar(s), 0);
+                    if (rank == 0) ptx::mbar_expect_tx(full_bar(s), 2 * W8P_STAGE_BYTES);   // both CTAs' bytes
+                    const uint32_t sa = ptx::smem_u32(smem + s * W8P_STAGE_BYTES);
+                    ptx::tma_load_2d_pair(sa, &tmA, kb * W8_BK, m0, leader_full);
+                    ptx::tma_load_2d_pair(sa + W8P_A_BYTES, &tmB, n0, kb * W8_BK, leader_full);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            int it = 0, ti = 0;
+            for (int tile = pair; tile < n_tiles && !*abort_flag; tile += n_pairs, ++ti) {
+                const int buf = ti & 1;
+                if (!ptx::mbar_wait(tempty_bar(buf), ((ti >> 1) & 1) ^ 1, abort_flag, p.status)) break;
+                ptx::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * W8_BN;
+                bool ok = true;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % W8P_STAGES;
+                    if (!ptx::mbar_wait(full_bar(s), (it / W8P_STAGES) & 1, abort_flag, p.status)) { ok = false; break; }
+                    ptx::tc_fence_after();
+                    const uint32_t sa = ptx::smem_u32(smem + s * W8P_STAGE_BYTES);
+                    const uint32_t sb = sa + W8P_A_BYTES;
+#pragma unroll
+                    for (int k4 = 0; k4 < W8_BK / 32; ++k4) {
+                        const uint64_t da = ptx::smem_desc_sw128(sa + k4 * 32, 16, 1024);
+                        const uint64_t db = ptx::smem_desc_sw128(sb + k4 * 32 * 128, 16, 1024);
+                        ptx::mma_i8_ss_pair(d_tmem, da, db, W8P_IDESC, (kb | k4) != 0 ? 1u : 0u);
+                    }
+                    ptx::tc_commit_pair(ptx::mapa_shared(empty_bar(s), 0));     // stage free in both CTAs
+                    ptx::tc_commit_pair(ptx::mapa_shared(empty_bar(s), 1));
+                }
+                if (!ok) break;
+                ptx::tc_commit_pair(ptx::mapa_shared(tfull_bar(buf), 0));
+                ptx::tc_commit_pair(ptx::mapa_shared(tfull_bar(buf), 1));
+            }
+        }
+    } else if (warp >= 4) {
+        const int q = warp - 4;
+        int ti = 0;
+        for (int tile = pair; tile < n_tiles && !*abort_flag; tile += n_pairs, ++ti) {
+            const int buf = ti & 1;
+            const int m0 = (tile % tiles_m) * 256 + 128 * rank, n0 = (tile / tiles_m) * W8_BN;
+            if (!ptx::mbar_wait(tfull_bar(buf), (ti >> 1) & 1, abort_flag, p.status)) break;
+            ptx::tc_fence_after();
+            const int row = m0 + 32 * q + lane;
+            const bool row_ok = row < p.M;
+            const float sa = row_ok ? __fmul_rn(p.alpha, p.a_scales[row]) : 0.0f;
+            float* crow = p.C + static_cast<int64_t>(row_ok ? row : 0) * p.N;
+            const uint32_t leader_tempty = ptx::mapa_shared(tempty_bar(buf), 0);
+#pragma unroll 1
+            for (int c = 0; c < W8_BN / 32; ++c) {
+                uint32_t r[32];
+                ptx::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(32 * q) << 16) + buf * W8_BN + c * 32, r);
+                ptx::tmem_ld_wait();
+                if (c == W8_BN / 32 - 1) {
+                    ptx::tc_fence_before();
+                    ptx::mbar_arrive_cluster(leader_tempty);
+                }
+                const int nb = n0 + c * 32;
+                if (!row_ok || nb >= p.N) continue;
+                w8_store_chunk(crow, nb, r, sa, p);
+            }
+        }
+    }
+
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::cluster_sync_all();                            // neither CTA frees memory the pair may still touch
+    if (warp == 2) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc_pair(tmem_base, W8_TMEM_COLS);
     }
 }
 
@@ -236,6 +394,31 @@ int launch_w8a8_fast(lhb_ctx* ctx, const int8_t* Aq, const int8_t* Bq, const flo
     p.alpha = alpha; p.beta = beta;
     p.tiles_m = ceil_div(M, W8_BM); p.tiles_n = ceil_div(N, W8_BN);
     p.status = ctx->status_word;
+    const char* pair_env = getenv("LHB_W8A8_PAIR");          // 0 forces the single-CTA kernel
+    const int use_pair = pair_env ? atoi(pair_env) : 1;
+    if (use_pair && M >= 256) {
+        static bool attr2[64] = {};
+        if (!attr2[ctx->device & 63]) {
+            LHB_CUDA(cudaFuncSetAttribute(gemm_w8a8_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          static_cast<int>(W8P_SMEM)));
+            attr2[ctx->device & 63] = true;
+        }
+        const int tiles = ceil_div(M, 256) * p.tiles_n;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * std::min(ctx->sm_count / 2, tiles), 1, 1);
+        cfg.blockDim = dim3(W8_THREADS, 1, 1);
+        cfg.dynamicSmemBytes = W8P_SMEM;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        LHB_CUDA(cudaLaunchKernelEx(&cfg, gemm_w8a8_tc_pair_kernel, tmA, tmB, p));
+        return LHB_OK;
+    }
     const int grid = std::min(ctx->sm_count, p.tiles_m * p.tiles_n);
     gemm_w8a8_tc_kernel<<<grid, W8_THREADS, W8_SMEM, st>>>(tmA, tmB, p);
     LHB_LAUNCH_CHECK();

@@ -510,7 +510,7 @@ paged_decode_q8_kernel(const DecodeParams p) {
 static void decode_split_plan(int sm_count, int64_t items, int max_blocks, size_t part_floats_avail, int group,
                               int* splits, int* pages) {
     int64_t pp = items * max_blocks / (12LL * std::max(1, sm_count));
-    int pg = static_cast<int>(std::max<int64_t>(8, std::min<int64_t>(40, pp)));
+    int pg = static_cast<int>(std::max<int64_t>(8, std::min<int64_t>(96, pp)));
     if (const char* e = getenv("LHB_DECODE_PAGES")) pg = std::max(1, atoi(e));
     int sp = std::max(1, std::min(32, ceil_div(max_blocks, pg)));
     if (const char* e = getenv("LHB_DECODE_SPLITS")) sp = std::max(1, std::min(sp, atoi(e)));

@@ -102,6 +102,27 @@ def test_w8a8_bit_exact_against_checker(chk, lib, M, N, K):
     poll_ok()
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 256, 256), (300, 1040, 768), (1024, 2048, 1024), (2048, 4096 + 16, 4096)])
+def test_w8a8_cta_pair_path_bit_exact(chk, lib, monkeypatch, M, N, K):
+    """The CTA-pair kernel (two CTAs share a 256 x 256 tile, used for M >= 256) gives the same bits
+    as the single-CTA kernel and as the reference arithmetic."""
+    rng = np.random.default_rng(7 * M + N + K)
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    W = (rng.standard_normal((K, N)) * 0.02).astype(np.float32)
+    Aq, a_s = chk.q8_quantize_per_row(A)
+    Bq, b_s = chk.q8_quantize_per_col(W)
+    C0 = rng.standard_normal((M, N)).astype(np.float32)
+    dAq, dBq, das, dbs = dev(Aq), dev(Bq), dev(a_s), dev(b_s)
+    monkeypatch.setenv("LHB_W8A8_PAIR", "0")
+    base = host(lb.gemm_w8a8(dAq, dBq, das, dbs, C=dev(C0), alpha=0.5, beta=2.0))
+    monkeypatch.setenv("LHB_W8A8_PAIR", "1")
+    got = host(lb.gemm_w8a8(dAq, dBq, das, dbs, C=dev(C0), alpha=0.5, beta=2.0))
+    poll_ok()
+    assert_same_bits(got, base, f"pair vs single-CTA {M}x{N}x{K}")
+    if M * N * K <= 1024 * 2048 * 1024:
+        assert_same_bits(got, chk.gemm_w8a8(Aq, Bq, a_s, b_s, C0, alpha=0.5, beta=2.0), "pair vs checker")
+
+
 # --------------------------------------------------------------------------- W4A16
 
 @pytest.mark.parametrize("name", gio.names("w4a16_"))
