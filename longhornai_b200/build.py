@@ -26,6 +26,8 @@ SOURCES = ["api.cu", "quant.cu", "gemm_generic.cu", "kvcache.cu", "paged_attenti
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr",
               "-I" + os.path.join(ROOT, "include"), "-I" + CSRC]
+# extra compiler flags for development builds, e.g. LHB_NVCC_EXTRA="-DLHB_GEMV_TRACE"
+NVCC_FLAGS += os.environ.get("LHB_NVCC_EXTRA", "").split()
 
 
 def _deps_mtime():

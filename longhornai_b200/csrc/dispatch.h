@@ -49,5 +49,8 @@ struct TensorMap;
 int get_tensor_map_2d_u8(lhb_ctx* ctx, const void* base, uint64_t rows, uint64_t cols,
                          uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols,
                          bool swizzle128, TensorMap* out);
+// the same for an fp32 tensor (cols and box_cols in elements), no swizzle
+int get_tensor_map_2d_f32(lhb_ctx* ctx, const void* base, uint64_t rows, uint64_t cols,
+                          uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols, TensorMap* out);
 
 }  // namespace lhb

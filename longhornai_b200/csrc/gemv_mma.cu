@@ -6,46 +6,52 @@
 // Both layouts are N-contiguous, i.e. the reduction axis is the slow axis.
 //
 // The path is HBM-bound: the weight bytes are read exactly once, so the kernel
-// is built to spend as few issue slots per weight as possible.
+// is built to spend as few issue slots per weight as possible and to give
+// every SM the same number of bytes.
 //
-//   TMA (2-D, 128-byte swizzle)  global -> shared, two 64-row x 128-column boxes
-//       per stage (a CTA owns 256 columns), 3-deep ring, all of it in flight at once;
+//   Work units.  The weight matrix is cut into units of 64 byte-rows x 256
+//       columns (16 KiB; 128 k of int4 or 64 k of int8).  Units are numbered
+//       column tile by column tile, and CTA c of P takes the contiguous range
+//       [c*U/P, (c+1)*U/P): every CTA streams the same amount (+-1 unit)
+//       whatever N and K are.  With fewer column tiles than CTAs, P is a
+//       multiple of the tile count, so a range is a K-slice of one tile; else a
+//       range crosses a few tiles and each piece ("segment") is handled in turn.
+//   TMA (2-D, 128-byte swizzle) brings a unit into a ring of shared-memory
+//       stages; for W4 a second, unswizzled tensor map brings the unit's rows of
+//       group scales along on the same barrier.  One producer thread runs ahead
+//       of the consumers across segment borders.
 //   ldmatrix.trans on the raw bytes: one 8x8 b16 matrix = 8 byte-rows x 16
 //       columns; the transposed fragment hands every thread the bytes of two
-//       adjacent columns at two consecutive rows;
-//   int4 -> int8 without arithmetic: a nibble moved to the top of its byte IS
-//       the two's-complement int8 value 16*q (shift/mask), and one byte-permute
-//       per register gathers four consecutive k of one column, which is the
-//       operand register of the int8 tensor-core MMA (int8 weights need the
-//       permute only);
+//       adjacent columns at two consecutive rows.
+//   One byte-permute over two such registers gathers four byte-rows of one
+//       column.  For int4 that register holds eight weights: masking keeps the
+//       odd-k nibbles where they are, shift+mask moves the even-k nibbles up,
+//       and a nibble at the top of its byte IS the int8 value 16*q.  These
+//       registers are tensor-core operands as they stand: the k order inside a
+//       32-block is free as long as the activation operand uses the same order.
 //   mma.sync m16n8k32 s8 x s8 -> s32: weights are the 16-row operand (16 output
 //       columns), activations the 8-column operand.
 //
-// Activations are fp32 in the API.  Each row of a CTA's K-chunk is scaled by a
-// power of two so that max|a| lands in [2^19, 2^20), rounded to an integer and
-// written as three signed 7-bit digits (a = d1*2^14 + d2*2^7 + d3), one MMA
-// column per digit.  Integer products and sums are exact; the only error is
-// the rounding of a to 20 bits relative to the chunk maximum (2^-21), so any
+// Activations are fp32 in the API.  Each row of the K-range a CTA touches is
+// scaled by a power of two so that max|a| lands in [2^19, 2^20), rounded to an
+// integer and written as three signed 7-bit digits (a = d1*2^14 + d2*2^7 + d3),
+// one MMA column per digit.  Integer products and sums are exact; the only error
+// is the rounding of a to 20 bits relative to the range maximum (2^-21), so any
 // fp32 input meets the 1e-3 / 1e-4 tolerance against the reference's fp32 loop
 // (src/kernels/gemm_quant.cpp:54-82).  int32 partial sums are converted to
-// fp32 at every quantisation group (at most every 128 k), multiplied by the
-// group scale and accumulated in fp32.
+// fp32 at every quantisation group (at most every 128 k of int4, 256 k of
+// int8), multiplied by the group scale and accumulated in fp32.
 //
-// K is split over blockIdx.y.  With 2 or 4 splits the CTAs of a column tile
-// form a thread-block cluster and sum their partial [M, 256] tiles in split
-// order through distributed shared memory; with other split counts each split
-// writes its partial to the context's scratch arena and the last one to arrive
-// (a self-resetting counter) sums them in the same order.  Either way the
-// result is deterministic and C is written once, with alpha/beta applied.
-#include <cooperative_groups.h>
-
+// A segment that covers all of K writes C directly.  Otherwise it writes its
+// partial [M, 256] tile to the context's scratch arena, and the last
+// contributor to arrive for that column tile (a self-resetting counter) sums
+// the partials in contributor order and writes C: deterministic for a given SM
+// count, and C is written once, with alpha/beta applied.
 #include <cstdlib>
 
 #include "common.cuh"
 #include "dispatch.h"
 #include "ptx.cuh"
-
-namespace cg = cooperative_groups;
 
 namespace lhb {
 
@@ -57,9 +63,10 @@ constexpr int GV_BOX_BYTES = GV_BOX_COLS * GV_ROWS;
 constexpr int GV_STAGE_BYTES = GV_BOX_BYTES * GV_BOXES;
 constexpr int GV_MAX_STAGE = 8;     // ring depth is chosen per launch (2..8) from the shared-memory budget
 constexpr int GV_CONSUMER_WARPS = 8;
-constexpr int GV_THREADS = (GV_CONSUMER_WARPS + 1) * 32;   // + one producer warp
-constexpr int GV_MAX_SPLIT = 32;
+constexpr int GV_CONSUMERS = GV_CONSUMER_WARPS * 32;
+constexpr int GV_THREADS = GV_CONSUMERS + 32;     // + one producer warp
 constexpr int GV_MAX_M = 16;
+constexpr int GV_PB = 8;           // activation float4 loads a thread keeps in flight in the prologue
 
 using ptx::smem_u32;
 
@@ -78,65 +85,98 @@ __device__ __forceinline__ void mma_s8_16832(int (&c)[4], uint32_t a0, uint32_t 
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// barrier among the consumer warps only (the producer warp never joins it)
+__device__ __forceinline__ void consumer_sync() {
+    asm volatile("bar.sync 1, %0;" ::"n"(GV_CONSUMERS) : "memory");
+}
+
 // exact int32 -> fp32 for |v| < 2^22 without the conversion pipe
 __device__ __forceinline__ float small_int_to_float(int v) {
     return __int_as_float(v + 0x4B400000) - 12582912.0f;
 }
 
+// Development aid, compiled only with -DLHB_GEMV_TRACE: thread 0 of every CTA stamps
+// %globaltimer at the phase borders of the last 64 launches.
+#ifdef LHB_GEMV_TRACE
+__device__ unsigned long long g_gv_trace[64][512][8];
+#define GV_STAMP(i)                                                                                  \
+    do {                                                                                             \
+        if (threadIdx.x == 0 && blockIdx.x < 512) g_gv_trace[p.trace_slot][blockIdx.x][i] = ptx::global_timer_ns(); \
+    } while (0)
+#else
+#define GV_STAMP(i) do { } while (0)
+#endif
+
 struct GemvParams {
     const float* A;        // [M, K]
-    const float* scales;   // W4: [K/G, N]   W8: [N]
+    const float* scales;   // W8: [N] (W4 scales arrive through their tensor map)
     float* C;              // [M, N]
     int M, N, K, G;        // G unused for W8
     float alpha, beta;
-    int stages_total;      // ceil(rows / 64)
-    int stages_per_cta;
-    int splits;            // gridDim.y
-    int groups_per_cta;    // W4: rows of the shared scale panel (0 for W8)
-    float* partial;        // scratch [splits, M, N] (unused when splits == 1)
+    int S;                 // stages (units) per column tile = ceil(rows / 64)
+    int units;             // column tiles * S
+    int nstage;            // ring depth
+    int srows;             // W4: scale rows per stage
+    int flush_mask;        // W4: bit b set = fold the int32 sums after k32-block b of a stage
+    int max_contrib;       // partial slots per column tile in scratch
+    float* partial;        // scratch [column tile][max_contrib][M][256]
     int* counters;         // one per column tile, zero between calls
     int* status;
-    int nstage;            // ring depth
-    int cluster;           // 1: the splits of a column tile form a thread-block cluster (reduce through DSMEM)
-    int debug;             // timing experiments only (LHB_GEMV_DEBUG): 1 skip split reduction, 2 skip digits, 4 skip MMAs
+    int trace_slot;        // development builds only
 };
 
 // WBITS: 4 or 8.  JB: number of 8-column activation blocks; 3 digit columns per
 // row of A, so M <= (8 * JB) / 3.
 template <int WBITS, int JB>
-__global__ void __launch_bounds__(GV_THREADS, (JB >= 6) ? 1 : (JB >= 2 ? 2 : 3))
-gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
+__global__ void __launch_bounds__(GV_THREADS, (JB >= 6) ? 1 : (JB == 1 ? 3 : 2))
+gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ TensorMap tmS, const GemvParams p) {
     constexpr int K_PER_ROW = (WBITS == 4) ? 2 : 1;
-    constexpr int K_PER_STAGE = GV_ROWS * K_PER_ROW;
-    constexpr int KB_PER_STAGE = K_PER_STAGE / 32;        // k32 blocks per stage: 4 (W4), 2 (W8)
+    constexpr int KPS = GV_ROWS * K_PER_ROW;              // k per stage: 128 (W4), 64 (W8)
+    constexpr int KPS_SHIFT = (WBITS == 4) ? 7 : 6;
+    constexpr int KB = KPS / 32;                          // k32 blocks per stage: 4 (W4), 2 (W8)
     constexpr int NJ = 8 * JB;                            // digit columns
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int NST = p.nstage;
     uint8_t* tiles = smem;                                             // NST * 16 KiB
-    float* part = reinterpret_cast<float*>(smem + NST * GV_STAGE_BYTES);         // [NJ][256]
+    float* sc = reinterpret_cast<float*>(smem + NST * GV_STAGE_BYTES);            // W4: [NST][srows][256]
+    float* part = sc + NST * p.srows * GV_COLS;                        // [NJ][256]
     float* inv_s = part + NJ * GV_COLS;                                // [16]
     unsigned* rowmax = reinterpret_cast<unsigned*>(inv_s + 16);        // [16] max|a| bits per row
     uint64_t* bars = reinterpret_cast<uint64_t*>(rowmax + 16);         // full[], empty[]
     int* flags = reinterpret_cast<int*>(bars + 2 * GV_MAX_STAGE);      // [0] abort, [1] is-last
-    float* sscale = reinterpret_cast<float*>(flags + 4);               // W4: [groups_per_cta][256] group scales
-    uint8_t* dfrag = reinterpret_cast<uint8_t*>(sscale + p.groups_per_cta * GV_COLS);   // [kb32][NJ][32]
+    uint8_t* dfrag = reinterpret_cast<uint8_t*>(flags + 4);            // [digit stage][kb32][NJ][32]
     volatile int* abort_flag = flags;
 
-    const int ks = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int col0 = blockIdx.x * GV_COLS;
-
-    const int stage_begin = min(ks * p.stages_per_cta, p.stages_total);
-    const int stage_end = min(stage_begin + p.stages_per_cta, p.stages_total);
-    const int n_stages = stage_end - stage_begin;
-    const int k_begin = stage_begin * K_PER_STAGE;
-    const int k_count = n_stages * K_PER_STAGE;            // multiple of 32; may run past K
+    const int S = p.S;
+    GV_STAMP(0);
+    const int u0 = static_cast<int>(static_cast<int64_t>(blockIdx.x) * p.units / gridDim.x);
+    const int u1 = static_cast<int>(static_cast<int64_t>(blockIdx.x + 1) * p.units / gridDim.x);
+    const int n_units = u1 - u0;
+    const int tile_first = u0 / S;
+    const int s_first = u0 - tile_first * S;
+    const int n_dig = min(S, n_units);                     // distinct stages of K this CTA meets
 
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + GV_MAX_STAGE);
-    // The producer thread sets the barriers up and puts the first ring-full of stages
+    const uint32_t stage_tx = GV_STAGE_BYTES + ((WBITS == 4) ? p.srows * GV_COLS * 4 : 0);
+    // one unit into ring slot `slot`: two weight boxes and, for W4, its rows of group scales
+    auto issue = [&](int tile, int stage, int slot) {
+        const uint32_t bar = full0 + 8 * slot;
+        ptx::mbar_expect_tx(bar, stage_tx);
+#pragma unroll
+        for (int b = 0; b < GV_BOXES; ++b)
+            ptx::tma_load_2d(smem_u32(tiles + slot * GV_STAGE_BYTES + b * GV_BOX_BYTES), &tmB,
+                             tile * GV_COLS + b * GV_BOX_COLS, stage * GV_ROWS, bar);
+        if (WBITS == 4) {
+            const int row = (p.G >= KPS) ? (stage * KPS) / p.G : stage * p.srows;
+            ptx::tma_load_2d(smem_u32(sc + slot * p.srows * GV_COLS), &tmS, tile * GV_COLS, row, bar);
+        }
+    };
+    // The producer thread sets the barriers up and puts the first ring-full of units
     // in flight before anything else happens in the CTA.
+    int prod_tile = tile_first, prod_stage = s_first;
     if (warp == GV_CONSUMER_WARPS && lane == 0) {
         for (int s = 0; s < GV_MAX_STAGE; ++s) {
             ptx::mbar_init(full0 + 8 * s, 1);
@@ -145,13 +185,10 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
         flags[0] = 0;
         flags[1] = 0;
         ptx::fence_mbar_init();
-        const int first = min(n_stages, NST);
+        const int first = min(n_units, NST);
         for (int s = 0; s < first; ++s) {
-            ptx::mbar_expect_tx(full0 + 8 * s, GV_STAGE_BYTES);
-#pragma unroll
-            for (int b = 0; b < GV_BOXES; ++b)
-                ptx::tma_load_2d(smem_u32(tiles + s * GV_STAGE_BYTES + b * GV_BOX_BYTES), &tmB,
-                                 col0 + b * GV_BOX_COLS, (stage_begin + s) * GV_ROWS, full0 + 8 * s);
+            issue(prod_tile, prod_stage, s);
+            if (++prod_stage == S) { prod_stage = 0; ++prod_tile; }
         }
     }
     if (threadIdx.x < 16) rowmax[threadIdx.x] = 0u;
@@ -161,84 +198,117 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
     // waits for it to finish.  The next kernel may be scheduled from here on.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    GV_STAMP(1);
     __syncthreads();
 
     // ---- prologue, overlapped with the loads in flight ---------------------------
-    // W4: this CTA's panel of group scales, [groups][128 columns], coalesced
-    const int g_first = (WBITS == 4) ? k_begin / p.G : 0;
-    if (WBITS == 4) {
-        for (int i = threadIdx.x; i < p.groups_per_cta * (GV_COLS / 4); i += GV_THREADS) {
-            const int gl = i / (GV_COLS / 4), c = (i % (GV_COLS / 4)) * 4;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if ((g_first + gl) * p.G < p.K && col0 + c < p.N)      // N % 16 == 0: whole float4 in range
-                v = *reinterpret_cast<const float4*>(p.scales + static_cast<int64_t>(g_first + gl) * p.N + col0 + c);
-            *reinterpret_cast<float4*>(sscale + gl * GV_COLS + c) = v;
-        }
-    }
-    // Activations: row maxima of this CTA's K-chunk, then three 7-bit digits per
-    // element in MMA-operand order.  Digit columns of rows m >= M are left as
-    // they are: an MMA column only feeds its own output column, never read.
-    const int q4 = k_count >> 2;                           // float4 per row
+    // Activations of the K stages this CTA meets (digit stage i = stage
+    // (s_first + i) mod S): row maxima, then three 7-bit digits per element in
+    // MMA-operand order.  Digit columns of rows m >= M are left as they are: an
+    // MMA column only feeds its own output column, never read.
+    const int q4 = n_dig * (KPS / 4);                      // float4 per row
     const int n4 = p.M * q4;
     const int n4_pad = (n4 + 31) & ~31;                    // whole warps take part in the shuffles
     const float inv_q4 = 1.0f / static_cast<float>(q4 > 0 ? q4 : 1);
-    for (int i = threadIdx.x; i < ((p.debug & 2) ? 0 : n4_pad); i += GV_THREADS) {
-        const bool valid = i < n4;
-        // row index without an integer division: (i + 0.5) / q4 is never within
-        // 0.5 / q4 of an integer, far more than the float error at these sizes
-        const int m = valid ? min(p.M - 1, __float2int_rz((static_cast<float>(i) + 0.5f) * inv_q4)) : -1;
-        const int k = (i - m * q4) * 4;
-        float mx = 0.0f;
-        if (valid && k_begin + k < p.K) {
-            const float4 v = *reinterpret_cast<const float4*>(p.A + static_cast<int64_t>(m) * p.K + k_begin + k);
-            mx = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+    // global k of local element kl (a multiple of 4) of the digit stages
+    auto k_of = [&](int kl) {
+        int stage = s_first + (kl >> KPS_SHIFT);
+        if (stage >= S) stage -= S;
+        return stage * KPS + (kl & (KPS - 1));
+    };
+    // Loads are issued GV_PB at a time per thread before any of them is used: the
+    // prologue's cost is a few memory round trips, not one per float4.
+    for (int base = 0; base < n4_pad; base += GV_PB * GV_THREADS) {
+        float4 v[GV_PB];
+        int mrow[GV_PB];
+#pragma unroll
+        for (int j = 0; j < GV_PB; ++j) {
+            const int i = base + j * GV_THREADS + threadIdx.x;
+            // row index without an integer division: (i + 0.5) / q4 is never within
+            // 0.5 / q4 of an integer, far more than the float error at these sizes
+            const int m = (i < n4) ? min(p.M - 1, __float2int_rz((static_cast<float>(i) + 0.5f) * inv_q4)) : -1;
+            mrow[j] = m;
+            v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (m >= 0) {
+                const int k = k_of((i - m * q4) * 4);
+                if (k < p.K) v[j] = *reinterpret_cast<const float4*>(p.A + static_cast<int64_t>(m) * p.K + k);
+            }
         }
-        const int m0 = __shfl_sync(0xffffffffu, m, 0);
-        if (__all_sync(0xffffffffu, m == m0)) {            // the usual case: one row per warp step
-            mx = warp_max(mx);
-            if (lane == 0 && m0 >= 0 && mx > 0.0f) atomicMax(rowmax + m0, __float_as_uint(mx));
-        } else if (valid && mx > 0.0f) {
-            atomicMax(rowmax + m, __float_as_uint(mx));
+#pragma unroll
+        for (int j = 0; j < GV_PB; ++j) {
+            if (base + j * GV_THREADS + (threadIdx.x & ~31) >= n4_pad) break;      // warp-uniform
+            const int m = mrow[j];
+            float mx = fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w)));
+            const int m0 = __shfl_sync(0xffffffffu, m, 0);
+            if (__all_sync(0xffffffffu, m == m0)) {        // the usual case: one row per warp step
+                mx = warp_max(mx);
+                if (lane == 0 && m0 >= 0 && mx > 0.0f) atomicMax(rowmax + m0, __float_as_uint(mx));
+            } else if (m >= 0 && mx > 0.0f) {
+                atomicMax(rowmax + m, __float_as_uint(mx));
+            }
         }
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < ((p.debug & 2) ? 0 : n4); i += GV_THREADS) {
+    for (int base = 0; base < n4; base += GV_PB * GV_THREADS) {
+      float4 vb[GV_PB];
+#pragma unroll
+      for (int j = 0; j < GV_PB; ++j) {
+          const int i = base + j * GV_THREADS + threadIdx.x;
+          vb[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (i < n4) {
+              const int m = min(p.M - 1, __float2int_rz((static_cast<float>(i) + 0.5f) * inv_q4));
+              const int k = k_of((i - m * q4) * 4);
+              if (k < p.K) vb[j] = *reinterpret_cast<const float4*>(p.A + static_cast<int64_t>(m) * p.K + k);
+          }
+      }
+#pragma unroll
+      for (int j = 0; j < GV_PB; ++j) {
+        const int i = base + j * GV_THREADS + threadIdx.x;
+        if (i >= n4) break;
         const int m = min(p.M - 1, __float2int_rz((static_cast<float>(i) + 0.5f) * inv_q4));
-        const int k = (i - m * q4) * 4;
+        const int kl = (i - m * q4) * 4;
         // power-of-two factor taking max|a| into [2^19, 2^20); exponent clamped
         const unsigned mb = rowmax[m];
         int se = mb ? 273 - static_cast<int>((mb >> 23) & 0xff) : 127;     // 127 + 19 - (e - 127)
         se = max(1, min(253, se));
-        const float sc = __uint_as_float(static_cast<uint32_t>(se) << 23);
-        if (k == 0) inv_s[m] = __uint_as_float(static_cast<uint32_t>(254 - se) << 23);
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (k_begin + k < p.K)
-            v = *reinterpret_cast<const float4*>(p.A + static_cast<int64_t>(m) * p.K + k_begin + k);
-        const float x[4] = {v.x * sc, v.y * sc, v.z * sc, v.w * sc};
-        uint32_t d1 = 0, d2 = 0, d3 = 0;                  // 4 digits each, one byte per element
+        const float scl = __uint_as_float(static_cast<uint32_t>(se) << 23);
+        if (kl == 0) inv_s[m] = __uint_as_float(static_cast<uint32_t>(254 - se) << 23);
+        const float4 v = vb[j];
+        // a = rint(v * scl) = d1*2^14 + d2*2^7 + d3 with every digit in [-64, 64], by
+        // exact fp32 arithmetic: adding 1.5*2^23 rounds to an integer and leaves its
+        // two's-complement low bits in the low mantissa bits.
+        const float x[4] = {v.x * scl, v.y * scl, v.z * scl, v.w * scl};
+        uint32_t b1[4], b2[4], b3[4];                     // low byte = digit
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            int iv = __float2int_rn(fminf(fmaxf(x[j], -1048576.0f), 1048576.0f));
-            const int lo = ((iv + 64) & 127) - 64;
-            iv = (iv - lo) >> 7;
-            const int mid = ((iv + 64) & 127) - 64;
-            const int hi = (iv - mid) >> 7;
-            d1 |= static_cast<uint32_t>(hi & 0xff) << (8 * j);
-            d2 |= static_cast<uint32_t>(mid & 0xff) << (8 * j);
-            d3 |= static_cast<uint32_t>(lo & 0xff) << (8 * j);
+            const float MG = 12582912.0f;
+            const float xi = (x[j] + MG) - MG;                         // rint(x), |xi| <= 2^20
+            const float t1 = fmaf(xi, 6.103515625e-05f, MG);           // + xi / 2^14
+            const float r1 = fmaf(t1 - MG, -16384.0f, xi);             // |r1| <= 2^13
+            const float t2 = fmaf(r1, 0.0078125f, MG);                 // + r1 / 2^7
+            const float t3 = fmaf(t2 - MG, -128.0f, r1) + MG;          // |.| <= 64
+            b1[j] = __float_as_uint(t1); b2[j] = __float_as_uint(t2); b3[j] = __float_as_uint(t3);
         }
-        const int kb = k >> 5, kin = k & 31, half = kin >> 4, r = kin & 15;
-        uint8_t* base = dfrag + (kb * NJ + 3 * m) * 32 + half * 4;
+        // d1/d2/d3: 4 digits each, one byte per element
+        const uint32_t d1 = __byte_perm(__byte_perm(b1[0], b1[1], 0x0040), __byte_perm(b1[2], b1[3], 0x0040), 0x5410);
+        const uint32_t d2 = __byte_perm(__byte_perm(b2[0], b2[1], 0x0040), __byte_perm(b2[2], b2[3], 0x0040), 0x5410);
+        const uint32_t d3 = __byte_perm(__byte_perm(b3[0], b3[1], 0x0040), __byte_perm(b3[2], b3[3], 0x0040), 0x5410);
+        const int kb = kl >> 5, kin = kl & 31, half = kin >> 4, r = kin & 15;      // kb counts across digit stages
+        uint8_t* base = dfrag + (kb * NJ + 3 * m) * 32;
         if (WBITS == 4) {
-            // thread slot t = r / 4 holds k0 + 4t .. 4t+3 (and +16 in the second word)
-            uint8_t* d = base + (r >> 2) * 8;
-            *reinterpret_cast<uint32_t*>(d) = d1;
-            *reinterpret_cast<uint32_t*>(d + 32) = d2;
-            *reinterpret_cast<uint32_t*>(d + 64) = d3;
+            // Operand slot order of a k32-block (see the main loop): thread slot t = r / 4,
+            // first word = even k {4t, 4t+2, 16+4t, 16+4t+2}, second word = the odd k beside them.
+            uint8_t* d = base + (r >> 2) * 8 + half * 2;
+            *reinterpret_cast<uint16_t*>(d) = static_cast<uint16_t>(__byte_perm(d1, 0, 0x4420));
+            *reinterpret_cast<uint16_t*>(d + 4) = static_cast<uint16_t>(__byte_perm(d1, 0, 0x4431));
+            *reinterpret_cast<uint16_t*>(d + 32) = static_cast<uint16_t>(__byte_perm(d2, 0, 0x4420));
+            *reinterpret_cast<uint16_t*>(d + 36) = static_cast<uint16_t>(__byte_perm(d2, 0, 0x4431));
+            *reinterpret_cast<uint16_t*>(d + 64) = static_cast<uint16_t>(__byte_perm(d3, 0, 0x4420));
+            *reinterpret_cast<uint16_t*>(d + 68) = static_cast<uint16_t>(__byte_perm(d3, 0, 0x4431));
         } else {
             // slot t holds k0 + {2t, 2t+1, 8+2t, 9+2t}: elements (k, k+1) -> slot t0,
             // (k+2, k+3) -> slot t0 + 1, bytes 0-1 (r < 8) or 2-3 (r >= 8)
-            uint8_t* d = base + ((r & 7) >> 1) * 8 + ((r >> 3) << 1);
+            uint8_t* d = base + half * 4 + ((r & 7) >> 1) * 8 + ((r >> 3) << 1);
             *reinterpret_cast<uint16_t*>(d) = static_cast<uint16_t>(d1);
             *reinterpret_cast<uint16_t*>(d + 8) = static_cast<uint16_t>(d1 >> 16);
             *reinterpret_cast<uint16_t*>(d + 32) = static_cast<uint16_t>(d2);
@@ -246,40 +316,47 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
             *reinterpret_cast<uint16_t*>(d + 64) = static_cast<uint16_t>(d3);
             *reinterpret_cast<uint16_t*>(d + 72) = static_cast<uint16_t>(d3 >> 16);
         }
+      }
     }
     __syncthreads();
+    GV_STAMP(2);
 
-    // ---- main loop ------------------------------------------------------------------
     if (warp < GV_CONSUMER_WARPS) {
         // A warp owns two 16-column fragments f = 0, 1: columns 32*warp + 16*f .. +15 of
-        // the CTA, i.e. 16-byte chunks 2*(warp%4) + f of box warp/4.
+        // the tile, i.e. 16-byte chunks 2*(warp%4) + f of box warp/4.
         const int g = lane >> 2, t = lane & 3;
         const int box = warp >> 2, chunk0 = (warp & 3) * 2;
-        const int wcol = warp * 32 + 2 * g;                 // + 16*f: this thread's column pair in the CTA
+        const int wcol = warp * 32 + 2 * g;                 // + 16*f: this thread's column pair in the tile
+        const int lrow = lane & 7, lmat = lane >> 3;
+        // ldmatrix source of this lane inside a stage, per half (32 byte-rows) and fragment
+        uint32_t ldoff[2][2];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int row = half * 32 + lmat * 8 + lrow;
+#pragma unroll
+            for (int f = 0; f < 2; ++f)
+                ldoff[half][f] = box * GV_BOX_BYTES + row * 128 + (((chunk0 + f) ^ (row & 7)) << 4);
+        }
+        const uint8_t* dlane = dfrag + g * 32 + t * 8;      // + ((digit stage * KB + kb) * NJ + jb * 8) * 32
+        const uint32_t tiles0 = smem_u32(tiles);
+
         float out[2][JB][4];
         int acc[2][JB][4];
+        auto clear = [&]() {
 #pragma unroll
-        for (int f = 0; f < 2; ++f)
+            for (int f = 0; f < 2; ++f)
 #pragma unroll
-            for (int jb = 0; jb < JB; ++jb)
+                for (int jb = 0; jb < JB; ++jb)
 #pragma unroll
-                for (int i = 0; i < 4; ++i) { out[f][jb][i] = 0.0f; acc[f][jb][i] = 0; }
-        // int32 sums are folded into fp32 every `flush_every` k32-blocks: at the end
-        // of each quantisation group, and at least every 128 k (keeps |acc| < 2^22)
-        const int flush_every = (WBITS == 4) ? min(p.G, 128) / 32 : 4;
-        const int group_blocks = (WBITS == 4) ? p.G / 32 : 0x7fffffff;     // k32-blocks per group
-        int since_flush = 0;
-        int blk_in_group = (WBITS == 4) ? (k_begin / 32) % group_blocks : 0;
-        const float* sthread = sscale + wcol;               // + gl * GV_COLS + 16 * f
-        const int lrow = lane & 7, lmat = lane >> 3;
-        const uint8_t* dthread = dfrag + g * 32 + t * 8;   // + (kb * NJ + jb * 8) * 32
-
-        auto flush = [&]() {
+                    for (int i = 0; i < 4; ++i) { out[f][jb][i] = 0.0f; acc[f][jb][i] = 0; }
+        };
+        // fold the int32 sums into fp32, times the scales at `srow` (W4) or 1 (W8)
+        auto flush = [&](const float* srow) {
 #pragma unroll
             for (int f = 0; f < 2; ++f) {
                 float s0 = 1.0f, s1 = 1.0f;
                 if (WBITS == 4) {
-                    const float2 sv = *reinterpret_cast<const float2*>(sthread + 16 * f);
+                    const float2 sv = *reinterpret_cast<const float2*>(srow + wcol + 16 * f);
                     s0 = sv.x; s1 = sv.y;
                 }
 #pragma unroll
@@ -293,268 +370,268 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const GemvParams p) {
             }
         };
         // one k32-block: the activation fragment is loaded once and feeds both column fragments
-        auto mma_block = [&](const uint32_t (&a)[2][4]) {
+        auto mma_block = [&](const uint8_t* dblk, const uint32_t (&a)[2][4]) {
 #pragma unroll
             for (int jb = 0; jb < JB; ++jb) {
-                const uint2 b = *reinterpret_cast<const uint2*>(dthread + jb * 8 * 32);
+                const uint2 b = *reinterpret_cast<const uint2*>(dblk + jb * 8 * 32);
                 mma_s8_16832(acc[0][jb], a[0][0], a[0][1], a[0][2], a[0][3], b.x, b.y);
                 mma_s8_16832(acc[1][jb], a[1][0], a[1][1], a[1][2], a[1][3], b.x, b.y);
             }
-            dthread += NJ * 32;
-            ++since_flush;
-            ++blk_in_group;
-            if (since_flush == flush_every || blk_in_group == group_blocks) { since_flush = 0; flush(); }
-            if (blk_in_group == group_blocks) { blk_in_group = 0; sthread += GV_COLS; }
         };
 
-        int slot = 0;
+        int slot = 0, didx = 0;
         uint32_t phase = 0;
-        for (int ls = 0; ls < n_stages; ++ls) {
-            ptx::mbar_wait(full0 + 8 * slot, phase, abort_flag, p.status);
-            const uint32_t tile = smem_u32(tiles + slot * GV_STAGE_BYTES + box * GV_BOX_BYTES);
+        int u = u0;
+        int tile = tile_first, s_begin = s_first;
+        while (u < u1) {
+            const int s_end = min(S, s_begin + (u1 - u));
+            clear();
+            int unflushed = 0;                              // W8: stages since the last fold
+            for (int s = s_begin; s < s_end; ++s) {
+                const bool ok = ptx::mbar_wait(full0 + 8 * slot, phase, abort_flag, p.status);
+                const uint32_t tile_s = tiles0 + slot * GV_STAGE_BYTES;
+                const uint8_t* dst = dlane + didx * (KB * NJ * 32);
+                const float* sstage = sc + slot * p.srows * GV_COLS;
+                if (ok) {
+                    int srow_i = 0;
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                // register x[f][j]: bytes {row 2t: col 2g, col 2g+1; row 2t+1: col 2g, col 2g+1}
-                // of byte-rows 8j .. 8j+7 of this 32-row block, fragment f
-                uint32_t x[2][4];
-                const int row = half * 32 + lmat * 8 + lrow;
-                ldmatrix_x4_trans(tile + row * 128 + (((chunk0) ^ (row & 7)) << 4), x[0]);
-                ldmatrix_x4_trans(tile + row * 128 + (((chunk0 + 1) ^ (row & 7)) << 4), x[1]);
-                if (half == 1) {           // stage fully read by this warp
-                    __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(empty0 + 8 * slot);
-                }
-                if (p.debug & 4) continue;
-                if (WBITS == 4) {
-                    uint32_t a[2][2][4];   // [k32-block][fragment][operand register]
+                    for (int half = 0; half < 2; ++half) {
+                        // register x[f][j]: bytes {row 2t: col 2g, col 2g+1; row 2t+1: col 2g, col 2g+1}
+                        // of byte-rows 8j .. 8j+7 of this 32-row half, fragment f
+                        uint32_t x[2][4];
+                        ldmatrix_x4_trans(tile_s + ldoff[half][0], x[0]);
+                        ldmatrix_x4_trans(tile_s + ldoff[half][1], x[1]);
+                        if (WBITS == 4) {
 #pragma unroll
-                    for (int f = 0; f < 2; ++f)
+                            for (int q = 0; q < 2; ++q) {           // k32-block 2*half + q: matrices 2q, 2q+1
+                                uint32_t a[2][4];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const uint32_t lo = (x[f][j] << 4) & 0xf0f0f0f0u;     // even k, int8 = 16*q
-                            const uint32_t hi = x[f][j] & 0xf0f0f0f0u;            // odd k
-                            // 4 consecutive k of column 2g (regs 0, 2) / 2g+1 (regs 1, 3)
-                            a[j >> 1][f][(j & 1) * 2] = __byte_perm(lo, hi, 0x6240);
-                            a[j >> 1][f][(j & 1) * 2 + 1] = __byte_perm(lo, hi, 0x7351);
+                                for (int f = 0; f < 2; ++f) {
+                                    // four byte-rows {2t, 2t+1, 8+2t, 9+2t} of column 2g / 2g+1
+                                    const uint32_t e0 = __byte_perm(x[f][2 * q], x[f][2 * q + 1], 0x6420);
+                                    const uint32_t e1 = __byte_perm(x[f][2 * q], x[f][2 * q + 1], 0x7531);
+                                    a[f][0] = (e0 << 4) & 0xf0f0f0f0u;     // even k, int8 = 16*q
+                                    a[f][1] = (e1 << 4) & 0xf0f0f0f0u;
+                                    a[f][2] = e0 & 0xf0f0f0f0u;            // odd k
+                                    a[f][3] = e1 & 0xf0f0f0f0u;
+                                }
+                                const int kb = 2 * half + q;
+                                mma_block(dst + kb * NJ * 32, a);
+                                if (p.flush_mask & (1 << kb)) {
+                                    flush(sstage + srow_i * GV_COLS);
+                                    ++srow_i;
+                                }
+                            }
+                        } else {
+                            // k-slots 4t..4t+3 <- rows {2t, 2t+1} of matrices 0 and 1; 16+4t.. <- matrices 2 and 3
+                            uint32_t a[2][4];
+#pragma unroll
+                            for (int f = 0; f < 2; ++f) {
+                                a[f][0] = __byte_perm(x[f][0], x[f][1], 0x6420);
+                                a[f][1] = __byte_perm(x[f][0], x[f][1], 0x7531);
+                                a[f][2] = __byte_perm(x[f][2], x[f][3], 0x6420);
+                                a[f][3] = __byte_perm(x[f][2], x[f][3], 0x7531);
+                            }
+                            mma_block(dst + half * NJ * 32, a);
                         }
-                    mma_block(a[0]);
-                    mma_block(a[1]);
-                } else {
-                    // k-slots 4t..4t+3 <- rows {2t, 2t+1} of matrices 0 and 1; 16+4t.. <- matrices 2 and 3
-                    uint32_t a[2][4];
-#pragma unroll
-                    for (int f = 0; f < 2; ++f) {
-                        a[f][0] = __byte_perm(x[f][0], x[f][1], 0x6420);
-                        a[f][1] = __byte_perm(x[f][0], x[f][1], 0x7531);
-                        a[f][2] = __byte_perm(x[f][2], x[f][3], 0x6420);
-                        a[f][3] = __byte_perm(x[f][2], x[f][3], 0x7531);
                     }
-                    mma_block(a);
+                    if (WBITS == 8 && ++unflushed == 4) { unflushed = 0; flush(nullptr); }
+                }
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(empty0 + 8 * slot);      // stage (weights and scales) fully read
+                if (++slot == NST) { slot = 0; phase ^= 1; }
+                if (++didx == n_dig) didx = 0;
+            }
+            if (WBITS == 8 && unflushed != 0) flush(nullptr);
+            GV_STAMP(3);
+
+            // ---- end of a segment: digit columns -> shared memory -> [M, 256] tile ----
+            // per-column partial sums: column j of the operand = digit (j % 3) of row j / 3
+#pragma unroll
+            for (int f = 0; f < 2; ++f) {
+                float c0 = 1.0f, c1 = 1.0f;
+                if (WBITS == 8) {
+                    const int n_a = tile * GV_COLS + wcol + 16 * f;
+                    c0 = (n_a < p.N) ? p.scales[n_a] : 0.0f;
+                    c1 = (n_a + 1 < p.N) ? p.scales[n_a + 1] : 0.0f;
+                }
+#pragma unroll
+                for (int jb = 0; jb < JB; ++jb) {
+                    float* d = part + (jb * 8 + 2 * t) * GV_COLS + wcol + 16 * f;
+                    *reinterpret_cast<float2*>(d) = make_float2(c0 * out[f][jb][0], c1 * out[f][jb][2]);
+                    *reinterpret_cast<float2*>(d + GV_COLS) = make_float2(c0 * out[f][jb][1], c1 * out[f][jb][3]);
                 }
             }
-            if (++slot == NST) { slot = 0; phase ^= 1; }
-        }
-        if (since_flush != 0) flush();
-        // per-column partial sums: column j of the operand = digit (j % 3) of row j / 3
-#pragma unroll
-        for (int f = 0; f < 2; ++f) {
-            float c0 = 1.0f, c1 = 1.0f;
-            if (WBITS == 8) {
-                const int n_a = col0 + wcol + 16 * f;
-                c0 = (n_a < p.N) ? p.scales[n_a] : 0.0f;
-                c1 = (n_a + 1 < p.N) ? p.scales[n_a + 1] : 0.0f;
+            consumer_sync();
+
+            const bool whole = (s_begin == 0 && s_end == S);       // this segment is all of K
+            const int col0 = tile * GV_COLS;
+            const int ncol = min(GV_COLS, p.N - col0);             // multiple of 16
+            const float digit_unit = (WBITS == 4) ? 0.0625f : 1.0f;     // int4 nibbles were carried as 16*q
+            // contributors to this column tile are the CTAs cf..cl; contributor i owns partial slot i
+            int cf = 0, n_contrib = 1;
+            if (!whole) {
+                const int64_t P = gridDim.x;
+                cf = static_cast<int>(((static_cast<int64_t>(tile) * S + 1) * P - 1) / p.units);
+                const int cl = static_cast<int>(((static_cast<int64_t>(tile + 1) * S) * P - 1) / p.units);
+                n_contrib = cl - cf + 1;
             }
-#pragma unroll
-            for (int jb = 0; jb < JB; ++jb) {
-                float* d = part + (jb * 8 + 2 * t) * GV_COLS + wcol + 16 * f;
-                *reinterpret_cast<float2*>(d) = make_float2(c0 * out[f][jb][0], c1 * out[f][jb][2]);
-                *reinterpret_cast<float2*>(d + GV_COLS) = make_float2(c0 * out[f][jb][1], c1 * out[f][jb][3]);
+            float* slot_base = p.partial + (static_cast<int64_t>(tile) * p.max_contrib) * p.M * GV_COLS;
+            float* my_slot = slot_base + static_cast<int64_t>(blockIdx.x - cf) * p.M * GV_COLS;
+            auto store_c = [&](int m, int c, float4 v) {
+                float4* cp = reinterpret_cast<float4*>(p.C + static_cast<int64_t>(m) * p.N + col0 + c);
+                if (p.beta == 0.0f) {
+                    v.x *= p.alpha; v.y *= p.alpha; v.z *= p.alpha; v.w *= p.alpha;
+                } else {
+                    const float4 o = *cp;
+                    v.x = fmaf(p.beta, o.x, p.alpha * v.x); v.y = fmaf(p.beta, o.y, p.alpha * v.y);
+                    v.z = fmaf(p.beta, o.z, p.alpha * v.z); v.w = fmaf(p.beta, o.w, p.alpha * v.w);
+                }
+                *cp = v;
+            };
+            for (int i = threadIdx.x; i < p.M * (GV_COLS / 4); i += GV_CONSUMERS) {
+                const int m = i >> 6, c = (i & 63) * 4;
+                if (c >= ncol) continue;
+                const float4 h = *reinterpret_cast<const float4*>(part + (3 * m) * GV_COLS + c);
+                const float4 md = *reinterpret_cast<const float4*>(part + (3 * m + 1) * GV_COLS + c);
+                const float4 l = *reinterpret_cast<const float4*>(part + (3 * m + 2) * GV_COLS + c);
+                const float is = inv_s[m] * digit_unit;
+                float4 v;
+                v.x = is * fmaf(16384.0f, h.x, fmaf(128.0f, md.x, l.x));
+                v.y = is * fmaf(16384.0f, h.y, fmaf(128.0f, md.y, l.y));
+                v.z = is * fmaf(16384.0f, h.z, fmaf(128.0f, md.z, l.z));
+                v.w = is * fmaf(16384.0f, h.w, fmaf(128.0f, md.w, l.w));
+                if (whole) store_c(m, c, v);
+                else *reinterpret_cast<float4*>(my_slot + m * GV_COLS + c) = v;
             }
+            if (!whole) {
+                // the last contributor to arrive sums the partials in contributor order and writes C
+                consumer_sync();
+                GV_STAMP(4);
+                // One thread fences for the CTA on either side of the count (a fence per thread
+                // costs microseconds here): the barrier before orders every consumer's partial
+                // stores ahead of it, the barrier after orders the other contributors' stores
+                // ahead of every consumer's loads.
+                if (threadIdx.x == 0) {
+                    __threadfence();
+                    const int old = atomicAdd(p.counters + tile, 1);
+                    flags[1] = (old == n_contrib - 1);
+                    if (old == n_contrib - 1) p.counters[tile] = 0;    // ready for the next call
+                    __threadfence();
+                }
+                consumer_sync();
+                GV_STAMP(5);
+                if (flags[1]) {
+                    for (int i = threadIdx.x; i < p.M * (GV_COLS / 4); i += GV_CONSUMERS) {
+                        const int m = i >> 6, c = (i & 63) * 4;
+                        if (c >= ncol) continue;
+                        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+                        // eight partials in flight at a time: one memory round trip per eight
+                        // contributors, summed in contributor order
+                        for (int r0 = 0; r0 < n_contrib; r0 += 8) {
+                            float4 v[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)         // unconditional (clamped) so that they overlap
+                                v[j] = __ldcg(reinterpret_cast<const float4*>(
+                                    slot_base + (static_cast<int64_t>(min(r0 + j, n_contrib - 1)) * p.M + m) * GV_COLS + c));
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                if (r0 + j < n_contrib) { sum.x += v[j].x; sum.y += v[j].y; sum.z += v[j].z; sum.w += v[j].w; }
+                        }
+                        store_c(m, c, sum);
+                    }
+                }
+            }
+            consumer_sync();                                // `part` and flags[1] are free again
+            GV_STAMP(6);
+            u += s_end - s_begin;
+            s_begin = 0;
+            ++tile;
         }
     } else if (lane == 0) {
         // producer: refill ring slots as the consumers release them
-        int issued = min(n_stages, NST);
+        int issued = min(n_units, NST);
         int slot = 0;
         uint32_t phase = 0;                                // parity of the consumers' release being waited for
-        for (int ls = NST; ls < n_stages; ++ls) {
+        for (int ui = NST; ui < n_units; ++ui) {
             if (!ptx::mbar_wait(empty0 + 8 * slot, phase, abort_flag, p.status)) break;
-            ptx::mbar_expect_tx(full0 + 8 * slot, GV_STAGE_BYTES);
-#pragma unroll
-            for (int b = 0; b < GV_BOXES; ++b)
-                ptx::tma_load_2d(smem_u32(tiles + slot * GV_STAGE_BYTES + b * GV_BOX_BYTES), &tmB,
-                                 col0 + b * GV_BOX_COLS, (stage_begin + ls) * GV_ROWS, full0 + 8 * slot);
-            issued = ls + 1;
+            issue(prod_tile, prod_stage, slot);
+            if (++prod_stage == S) { prod_stage = 0; ++prod_tile; }
+            issued = ui + 1;
             if (++slot == NST) { slot = 0; phase ^= 1; }
         }
         if (*abort_flag) {
             // a wait ran out: let the copies still in flight land before the CTA exits
-            for (int ls = max(0, issued - NST); ls < issued; ++ls) {
+            for (int ui = max(0, issued - NST); ui < issued; ++ui) {
                 const uint64_t t0 = ptx::global_timer_ns();
-                while (!ptx::mbar_try_wait(full0 + 8 * (ls % NST), (ls / NST) & 1))
+                while (!ptx::mbar_try_wait(full0 + 8 * (ui % NST), (ui / NST) & 1))
                     if (ptx::global_timer_ns() - t0 > 200000000ull) break;
             }
         }
-    }
-    __syncthreads();
-
-    // ---- combine the three digit columns of every row; write C or the split's partial ----
-    const int ncol = min(GV_COLS, p.N - col0);            // multiple of 16
-    const float digit_unit = (WBITS == 4) ? 0.0625f : 1.0f;    // int4 nibbles were carried as 16*q
-    for (int i = threadIdx.x; i < p.M * (GV_COLS / 4); i += GV_THREADS) {
-        const int m = i >> 6, c = (i & 63) * 4;
-        if (c >= ncol) continue;
-        const float4 h = *reinterpret_cast<const float4*>(part + (3 * m) * GV_COLS + c);
-        const float4 md = *reinterpret_cast<const float4*>(part + (3 * m + 1) * GV_COLS + c);
-        const float4 l = *reinterpret_cast<const float4*>(part + (3 * m + 2) * GV_COLS + c);
-        const float is = inv_s[m] * digit_unit;
-        float4 v;
-        v.x = is * fmaf(16384.0f, h.x, fmaf(128.0f, md.x, l.x));
-        v.y = is * fmaf(16384.0f, h.y, fmaf(128.0f, md.y, l.y));
-        v.z = is * fmaf(16384.0f, h.z, fmaf(128.0f, md.z, l.z));
-        v.w = is * fmaf(16384.0f, h.w, fmaf(128.0f, md.w, l.w));
-        if (p.splits == 1) {
-            float4* cp = reinterpret_cast<float4*>(p.C + static_cast<int64_t>(m) * p.N + col0 + c);
-            if (p.beta == 0.0f) {
-                v.x *= p.alpha; v.y *= p.alpha; v.z *= p.alpha; v.w *= p.alpha;
-            } else {
-                const float4 o = *cp;
-                v.x = fmaf(p.beta, o.x, p.alpha * v.x); v.y = fmaf(p.beta, o.y, p.alpha * v.y);
-                v.z = fmaf(p.beta, o.z, p.alpha * v.z); v.w = fmaf(p.beta, o.w, p.alpha * v.w);
-            }
-            *cp = v;
-        } else if (p.cluster) {
-            *reinterpret_cast<float4*>(reinterpret_cast<float*>(tiles) + m * GV_COLS + c) = v;   // ring is dead by now
-        } else {
-            *reinterpret_cast<float4*>(p.partial + (static_cast<int64_t>(ks) * p.M + m) * p.N + col0 + c) = v;
-        }
-    }
-    if (p.splits == 1 || (p.debug & 1)) return;
-
-    if (p.cluster) {
-        // Split-K reduction inside the cluster: every CTA finishes a slice of the
-        // 256 columns, reading the partial tiles of all splits in split order
-        // through distributed shared memory.  No global round trip.
-        cg::cluster_group cluster = cg::this_cluster();
-        cluster.sync();
-        const int S = p.splits, rank = static_cast<int>(cluster.block_rank());
-        const int q4s = (GV_COLS / 4) / S;                       // float4 columns per CTA (S divides 64)
-        const float* comb = reinterpret_cast<const float*>(tiles);
-        for (int i = threadIdx.x; i < p.M * q4s; i += GV_THREADS) {
-            const int m = i / q4s, c = (rank * q4s + i % q4s) * 4;
-            if (c >= ncol) continue;
-            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int r = 0; r < S; ++r) {
-                const float4 v = *reinterpret_cast<const float4*>(cluster.map_shared_rank(comb, r) + m * GV_COLS + c);
-                sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
-            }
-            float4* cp = reinterpret_cast<float4*>(p.C + static_cast<int64_t>(m) * p.N + col0 + c);
-            if (p.beta == 0.0f) {
-                sum.x *= p.alpha; sum.y *= p.alpha; sum.z *= p.alpha; sum.w *= p.alpha;
-            } else {
-                const float4 o = *cp;
-                sum.x = fmaf(p.beta, o.x, p.alpha * sum.x); sum.y = fmaf(p.beta, o.y, p.alpha * sum.y);
-                sum.z = fmaf(p.beta, o.z, p.alpha * sum.z); sum.w = fmaf(p.beta, o.w, p.alpha * sum.w);
-            }
-            *cp = sum;
-        }
-        cluster.sync();     // keep every CTA's shared memory alive until all peers have read it
-        return;
-    }
-
-    // Split-K epilogue: the last split to arrive for this column tile sums the
-    // partials in split order and writes C.
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const int old = atomicAdd(p.counters + blockIdx.x, 1);
-        flags[1] = (old == p.splits - 1);
-        if (old == p.splits - 1) p.counters[blockIdx.x] = 0;   // ready for the next call
-    }
-    __syncthreads();
-    if (!flags[1]) return;
-    __threadfence();
-    for (int i = threadIdx.x; i < p.M * (GV_COLS / 4); i += GV_THREADS) {
-        const int m = i >> 6, c = (i & 63) * 4;
-        if (c >= ncol) continue;
-        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int r = 0; r < p.splits; ++r) {
-            const float4 v = __ldcg(reinterpret_cast<const float4*>(
-                p.partial + (static_cast<int64_t>(r) * p.M + m) * p.N + col0 + c));
-            sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
-        }
-        float4* cp = reinterpret_cast<float4*>(p.C + static_cast<int64_t>(m) * p.N + col0 + c);
-        if (p.beta == 0.0f) {
-            sum.x *= p.alpha; sum.y *= p.alpha; sum.z *= p.alpha; sum.w *= p.alpha;
-        } else {
-            const float4 o = *cp;
-            sum.x = fmaf(p.beta, o.x, p.alpha * sum.x); sum.y = fmaf(p.beta, o.y, p.alpha * sum.y);
-            sum.z = fmaf(p.beta, o.z, p.alpha * sum.z); sum.w = fmaf(p.beta, o.w, p.alpha * sum.w);
-        }
-        *cp = sum;
     }
 }
 
 // ---- host side --------------------------------------------------------------------
 
-static int gemv_groups_per_cta(int wbits, int k_per_cta, int G) {
-    return wbits == 4 ? k_per_cta / G + 2 : 0;             // + 2: chunks need not start on a group boundary
-}
+struct GemvPlan {
+    int S, col_tiles, units, ctas, nstage, srows, flush_mask, max_contrib;
+    size_t smem;
+    bool ok;
+};
 
-// shared memory of a CTA without its ring
-static size_t gemv_smem_bytes(int wbits, int jb, int k_per_cta, int G) {
-    const size_t nj = 8 * jb;
-    return 1024 + nj * GV_COLS * 4 + 16 * 4 + 16 * 4 + 2 * GV_MAX_STAGE * 8 + 16 +
-           static_cast<size_t>(gemv_groups_per_cta(wbits, k_per_cta, G)) * GV_COLS * 4 +
-           static_cast<size_t>(k_per_cta) * nj;
-}
+static bool w4_group_ok(int G) { return G == 32 || G == 64 || (G >= 128 && G % 128 == 0); }
 
-struct GemvPlan { int splits; int stages_total; int stages_per_cta; int nstage; size_t smem; bool ok; };
-
-// Pick the K split.  A CTA costs its stage count plus a fixed overhead (launch,
-// activation prologue, partial write-out, about three stages' worth); the grid
-// should fit in one wave of the CTAs an SM can hold (3 for M <= 2).  The shared-memory budget (the
-// activation digits grow with the chunk length) bounds the chunk from above.
+// Split the units over the CTAs.  The grid is one full wave of the CTAs the SMs can
+// hold (two per SM up to M = 8, one for M <= 16) unless a CTA's share of K needs
+// more shared memory for its activation digits than there is; then there are more,
+// smaller CTAs.  The ring takes what shared memory remains, up to GV_MAX_STAGE.
 static GemvPlan plan_gemv(int wbits, int jb, int N, int K, int G, int sm_count) {
-    GemvPlan best{};
-    const int k_per_stage = GV_ROWS * (wbits == 4 ? 2 : 1);
-    const int stages_total = ceil_div(K, k_per_stage);
-    const int col_tiles = ceil_div(N, GV_COLS);
-    double best_cost = 1e30;
-    int forced = 0;
-    if (const char* e = getenv("LHB_GEMV_SPLITS")) forced = atoi(e);
-    for (int S = 1; S <= std::min(stages_total, GV_MAX_SPLIT); ++S) {
-        if (forced > 0 && S != std::min(forced, std::min(stages_total, GV_MAX_SPLIT))) continue;
-        const int spc = ceil_div(stages_total, S);
-        const int splits = ceil_div(stages_total, spc);
-        const size_t fixed = gemv_smem_bytes(wbits, jb, spc * k_per_stage, G);
-        if (fixed + 2 * GV_STAGE_BYTES > 200 * 1024) continue;
-        const int reg_limit = jb >= 6 ? 1 : (jb >= 2 ? 2 : 3);       // CTAs per SM the register file allows
-        // CTAs an SM must hold for the grid to be one wave, then the deepest ring that still fits
-        int per_sm = std::min(reg_limit, std::max(1, ceil_div(col_tiles * splits, sm_count)));
-        while (per_sm > 1 && fixed + 2 * GV_STAGE_BYTES + 1024 > (224 * 1024) / static_cast<size_t>(per_sm)) --per_sm;
-        const size_t budget = std::min<size_t>(200 * 1024, (224 * 1024) / per_sm - 1024);
-        int nstage = static_cast<int>((budget - fixed) / GV_STAGE_BYTES);
-        nstage = std::max(2, std::min(nstage, std::min(spc, GV_MAX_STAGE)));
-        const size_t smem = fixed + static_cast<size_t>(nstage) * GV_STAGE_BYTES;
-        const int waves = ceil_div(col_tiles * splits, sm_count * per_sm);
-        // a shallow ring cannot keep the memory system busy: charge the stages that do not fit
-        // the reduction over 2 or 4 splits stays inside a cluster (cheap); other counts go through scratch
-        const double red = (splits == 2 || splits == 4) ? 0.6 : 1.2;
-        const double cost = waves * (spc + 3.0 + 0.5 * std::max(0, spc - nstage)) + red * splits;
-        if (cost < best_cost) {
-            best_cost = cost;
-            best.splits = splits; best.stages_total = stages_total; best.stages_per_cta = spc;
-            best.nstage = nstage; best.smem = smem; best.ok = true;
-        }
+    GemvPlan pl{};
+    const int kps = GV_ROWS * (wbits == 4 ? 2 : 1);
+    pl.S = ceil_div(K, kps);
+    pl.col_tiles = ceil_div(N, GV_COLS);
+    const int64_t units = static_cast<int64_t>(pl.S) * pl.col_tiles;
+    if (units <= 0 || units > (1 << 30)) return pl;
+    pl.units = static_cast<int>(units);
+    pl.srows = wbits == 4 ? (G < 128 ? 128 / G : 1) : 0;
+    pl.flush_mask = wbits == 4 ? (G == 32 ? 0xF : (G == 64 ? 0xA : 0x8)) : 0;
+    int per_sm = jb >= 6 ? 1 : (jb == 1 ? 3 : 2);          // what the kernel's launch bounds allow
+    if (const char* e = getenv("LHB_GEMV_CTAS_PER_SM")) per_sm = std::max(1, std::min(per_sm, atoi(e)));
+    const size_t nj = 8 * jb;
+    const size_t stage_bytes = GV_STAGE_BYTES + static_cast<size_t>(pl.srows) * GV_COLS * 4;
+    const size_t fixed = 1024 + nj * GV_COLS * 4 + 16 * 4 + 16 * 4 + 2 * GV_MAX_STAGE * 8 + 16;
+    const size_t dig_per_stage = static_cast<size_t>(kps) * nj;
+    size_t budget = per_sm == 1 ? 227 * 1024 : (228 * 1024) / per_sm - 1024 - 512;
+    if (const char* e = getenv("LHB_GEMV_SMEM_KB")) budget = std::min<size_t>(budget, static_cast<size_t>(atoi(e)) * 1024);
+    int ctas = static_cast<int>(std::min<int64_t>(units, static_cast<int64_t>(per_sm) * sm_count));
+    // with fewer column tiles than CTAs, a whole number of CTAs per tile: no CTA then
+    // straddles two tiles and pays for two hand-offs
+    if (pl.col_tiles <= ctas) ctas = pl.col_tiles * std::min(pl.S, ctas / pl.col_tiles);
+    int range = ceil_div(pl.units, ctas);
+    if (fixed + 2 * stage_bytes + dig_per_stage * std::min(pl.S, range) > budget) {
+        // digits of a whole range do not fit: shorter ranges, more CTAs
+        if (fixed + 2 * stage_bytes + dig_per_stage > budget) return pl;
+        const int r_max = static_cast<int>((budget - fixed - 2 * stage_bytes) / dig_per_stage);
+        ctas = ceil_div(pl.units, r_max);
+        if (pl.col_tiles <= ctas) ctas = pl.col_tiles * ceil_div(ctas, pl.col_tiles);
+        range = ceil_div(pl.units, ctas);
     }
-    return best;
+    const size_t dig = dig_per_stage * std::min(pl.S, range);
+    pl.ctas = ctas;
+    pl.nstage = static_cast<int>(std::min<size_t>(GV_MAX_STAGE, (budget - fixed - dig) / stage_bytes));
+    pl.nstage = std::max(2, std::min(pl.nstage, std::max(2, range)));
+    pl.smem = fixed + dig + pl.nstage * stage_bytes;
+    const int r_min = std::max(1, pl.units / ctas);
+    pl.max_contrib = std::min(ctas, pl.S / r_min + 2);
+    pl.ok = true;
+    return pl;
 }
 
 static int jb_for(int M) { return M <= 2 ? 1 : (M <= 5 ? 2 : (M <= 8 ? 3 : 6)); }
 
 bool w4a16_fast_ok(int M, int N, int K, int G) {
-    if (M < 1 || (N % 16) != 0 || (K % 32) != 0 || (G % 32) != 0 || (K % G) != 0) return false;
-    if (G > 128 && (G % 128) != 0) return false;  // int32 sums are folded every 128 k at the latest
+    if (M < 1 || (N % 16) != 0 || (K % 32) != 0 || G <= 0 || (K % G) != 0) return false;
+    if (!w4_group_ok(G)) return false;            // groups must tile a 128-k stage, or be whole stages
     if (M > 64) return false;                     // larger M: generic path (dense GEMM territory)
     return plan_gemv(4, jb_for(std::min(M, GV_MAX_M)), N, K, G, 148).ok;
 }
@@ -566,49 +643,43 @@ bool w8a16_fast_ok(int M, int N, int K) {
 }
 
 template <int WBITS, int JB>
-static int launch_gemv_t(lhb_ctx* ctx, const TensorMap& tm, GemvParams p, const GemvPlan& pl,
-                         cudaStream_t st) {
+static int launch_gemv_t(lhb_ctx* ctx, const TensorMap& tm, const TensorMap& tms, GemvParams p,
+                         const GemvPlan& pl, cudaStream_t st) {
     auto kern = gemv_mma_kernel<WBITS, JB>;
     static bool attr_set[64] = {};                // per instantiation and device
     if (!attr_set[ctx->device & 63]) {
-        LHB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        LHB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         attr_set[ctx->device & 63] = true;
     }
-    p.stages_total = pl.stages_total;
-    p.stages_per_cta = pl.stages_per_cta;
-    p.splits = pl.splits;
+    p.S = pl.S;
+    p.units = pl.units;
     p.nstage = pl.nstage;
-    p.groups_per_cta = gemv_groups_per_cta(WBITS, pl.stages_per_cta * GV_ROWS * (WBITS == 4 ? 2 : 1), p.G);
+    p.srows = pl.srows;
+    p.flush_mask = pl.flush_mask;
+    p.max_contrib = pl.max_contrib;
     p.partial = reinterpret_cast<float*>(ctx->scratch);
     p.counters = ctx->counters;
     p.status = ctx->status_word;
-    static const int dbg = getenv("LHB_GEMV_DEBUG") ? atoi(getenv("LHB_GEMV_DEBUG")) : 0;
-    p.debug = dbg;
+#ifdef LHB_GEMV_TRACE
+    static int trace_calls = 0;
+    p.trace_slot = (trace_calls++) & 63;
+#endif
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(ceil_div(p.N, GV_COLS), pl.splits, 1);
+    cfg.gridDim = dim3(pl.ctas, 1, 1);
     cfg.blockDim = dim3(GV_THREADS, 1, 1);
     cfg.dynamicSmemBytes = pl.smem;
     cfg.stream = st;
     static const bool pdl = !(getenv("LHB_PDL") && atoi(getenv("LHB_PDL")) == 0);
-    static const bool use_cluster = !(getenv("LHB_GEMV_CLUSTER") && atoi(getenv("LHB_GEMV_CLUSTER")) == 0);
-    p.cluster = (use_cluster && (pl.splits == 2 || pl.splits == 4)) ? 1 : 0;
-    cudaLaunchAttribute attr[2];
+    cudaLaunchAttribute attr[1];
     int na = 0;
     if (pdl) {
         attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[na].val.programmaticStreamSerializationAllowed = 1;
         ++na;
     }
-    if (p.cluster) {
-        attr[na].id = cudaLaunchAttributeClusterDimension;
-        attr[na].val.clusterDim.x = 1;
-        attr[na].val.clusterDim.y = pl.splits;
-        attr[na].val.clusterDim.z = 1;
-        ++na;
-    }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    LHB_CUDA(cudaLaunchKernelEx(&cfg, kern, tm, p));
+    LHB_CUDA(cudaLaunchKernelEx(&cfg, kern, tm, tms, p));
     return LHB_OK;
 }
 
@@ -616,27 +687,32 @@ template <int WBITS>
 static int launch_gemv(lhb_ctx* ctx, const float* A, const void* B, const float* scales, float* C,
                        int M, int N, int K, int G, float alpha, float beta, cudaStream_t st) {
     const uint64_t rows = (WBITS == 4) ? K / 2 : K;
-    TensorMap tm;
+    TensorMap tm, tms;
     if (int e = get_tensor_map_2d_u8(ctx, B, rows, N, N, GV_ROWS, GV_BOX_COLS, true, &tm)) return e;
+    tms = tm;                                     // W8 has no scale tiles; the kernel never uses the map
     // rows of A are independent: M > 16 is served in slabs of 16 rows
     for (int m0 = 0; m0 < M; m0 += GV_MAX_M) {
         const int m = std::min(GV_MAX_M, M - m0);
         const int jb = jb_for(m);
         GemvPlan pl = plan_gemv(WBITS, jb, N, K, WBITS == 4 ? G : 1, ctx->sm_count);
         if (!pl.ok) return LHB_ERR_UNSUPPORTED;
-        if (ceil_div(N, GV_COLS) > static_cast<int>(ctx->counters_len)) return LHB_ERR_UNSUPPORTED;
-        if (pl.splits > 1 && static_cast<size_t>(pl.splits) * m * N * sizeof(float) > ctx->scratch_bytes)
+        if (pl.col_tiles > static_cast<int>(ctx->counters_len)) return LHB_ERR_UNSUPPORTED;
+        if (static_cast<size_t>(pl.col_tiles) * pl.max_contrib * m * GV_COLS * sizeof(float) > ctx->scratch_bytes)
             return LHB_ERR_SCRATCH;
+        if (WBITS == 4 && m0 == 0)
+            if (int e = get_tensor_map_2d_f32(ctx, scales, K / G, N, static_cast<uint64_t>(N) * 4, pl.srows,
+                                              GV_COLS, &tms))
+                return e;
         GemvParams p{};
         p.A = A + static_cast<int64_t>(m0) * K;
         p.scales = scales;
         p.C = C + static_cast<int64_t>(m0) * N;
         p.M = m; p.N = N; p.K = K; p.G = G; p.alpha = alpha; p.beta = beta;
         int e;
-        if (jb == 1) e = launch_gemv_t<WBITS, 1>(ctx, tm, p, pl, st);
-        else if (jb == 2) e = launch_gemv_t<WBITS, 2>(ctx, tm, p, pl, st);
-        else if (jb == 3) e = launch_gemv_t<WBITS, 3>(ctx, tm, p, pl, st);
-        else e = launch_gemv_t<WBITS, 6>(ctx, tm, p, pl, st);
+        if (jb == 1) e = launch_gemv_t<WBITS, 1>(ctx, tm, tms, p, pl, st);
+        else if (jb == 2) e = launch_gemv_t<WBITS, 2>(ctx, tm, tms, p, pl, st);
+        else if (jb == 3) e = launch_gemv_t<WBITS, 3>(ctx, tm, tms, p, pl, st);
+        else e = launch_gemv_t<WBITS, 6>(ctx, tm, tms, p, pl, st);
         if (e) return e;
     }
     return LHB_OK;
@@ -653,3 +729,9 @@ int launch_w8a16_fast(lhb_ctx* ctx, const float* A, const int8_t* Bq, const floa
 }
 
 }  // namespace lhb
+
+#ifdef LHB_GEMV_TRACE
+extern "C" __attribute__((visibility("default"))) int lhb_debug_gemv_trace(void* host_out) {
+    return static_cast<int>(cudaMemcpyFromSymbol(host_out, lhb::g_gv_trace, sizeof(lhb::g_gv_trace)));
+}
+#endif

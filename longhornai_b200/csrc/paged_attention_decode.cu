@@ -474,31 +474,62 @@ paged_decode_q8_kernel(const DecodeParams p) {
     if (nsplit == 1) return;
 
     // ---- cross-CTA merge: the last split to arrive combines all partials ------------------
-    __threadfence();
+    // One thread fences for the CTA on either side of the count: the barrier before it
+    // orders every thread's partial stores ahead of the fence, the barrier after it orders
+    // the other splits' stores ahead of every thread's loads.
     __syncthreads();
     const int cidx = req * p.n_kv_heads + kvh;
     if (threadIdx.x == 0) {
+        __threadfence();
         const int old = atomicAdd(p.counters + cidx, 1);
         s_last = (old == nsplit - 1);
         if (s_last) p.counters[cidx] = 0;              // ready for the next call
+        __threadfence();
     }
     __syncthreads();
     if (!s_last) return;
-    __threadfence();
+    // One warp per query head, a lane per four output dimensions; the partials of up to
+    // eight splits are in flight together, so the merge costs one memory round trip per
+    // eight splits instead of one per partial.  Splits are folded in split order with a
+    // running maximum (deterministic).
     const int64_t b0 = (static_cast<int64_t>(req) * p.n_kv_heads + kvh) * p.splits * G;
-    for (int h = 0; h < G; ++h) {
-        float M = -INFINITY;
-        for (int s = 0; s < nsplit; ++s) M = fmaxf(M, __ldcg(p.part + (b0 + s * G + h) * PD_PART));
-        float L = 0.0f, o = 0.0f;
-        for (int s = 0; s < nsplit; ++s) {
-            const float* pp = p.part + (b0 + s * G + h) * PD_PART;
-            const float ms = __ldcg(pp);
-            const float f = (ms == -INFINITY) ? 0.0f : fast_exp2(ms - M);
-            L += f * __ldcg(pp + 1);
-            o += f * __ldcg(pp + 2 + d);
+    const int mw = threadIdx.x >> 5, ml = threadIdx.x & 31;
+    for (int h = mw; h < G; h += PD_WARPS) {
+        float M = -INFINITY, L = 0.0f;
+        float2 oa = make_float2(0.f, 0.f), ob = make_float2(0.f, 0.f);   // dims 2*ml.. and 64 + 2*ml..
+        for (int s0 = 0; s0 < nsplit; s0 += 8) {
+            float ms[8], ls[8];
+            float2 va[8], vb[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                ms[j] = -INFINITY; ls[j] = 0.0f;
+                va[j] = make_float2(0.f, 0.f); vb[j] = make_float2(0.f, 0.f);
+                if (s0 + j < nsplit) {
+                    const float* pp = p.part + (b0 + (s0 + j) * G + h) * PD_PART;
+                    ms[j] = __ldcg(pp);
+                    ls[j] = __ldcg(pp + 1);
+                    va[j] = __ldcg(reinterpret_cast<const float2*>(pp + 2 + 2 * ml));
+                    vb[j] = __ldcg(reinterpret_cast<const float2*>(pp + 2 + 64 + 2 * ml));
+                }
+            }
+            float Mb = M;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) Mb = fmaxf(Mb, ms[j]);
+            const float keep = (M == -INFINITY) ? 0.0f : fast_exp2(M - Mb);
+            L *= keep; oa.x *= keep; oa.y *= keep; ob.x *= keep; ob.y *= keep;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float f = (ms[j] == -INFINITY) ? 0.0f : fast_exp2(ms[j] - Mb);
+                L += f * ls[j];
+                oa.x += f * va[j].x; oa.y += f * va[j].y;
+                ob.x += f * vb[j].x; ob.y += f * vb[j].y;
+            }
+            M = Mb;
         }
         float* out = p.O + (static_cast<int64_t>(req) * p.n_q_heads + kvh * G + h) * PD_D;
-        out[d] = (L > 0.0f) ? o * (1.0f / L) * exp2f(-PD_WSHIFT) : 0.0f;
+        const float r = (L > 0.0f) ? (1.0f / L) * exp2f(-PD_WSHIFT) : 0.0f;
+        *reinterpret_cast<float2*>(out + 2 * ml) = make_float2(oa.x * r, oa.y * r);
+        *reinterpret_cast<float2*>(out + 64 + 2 * ml) = make_float2(ob.x * r, ob.y * r);
     }
 }
 

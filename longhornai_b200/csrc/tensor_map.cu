@@ -34,11 +34,11 @@ static EncodeTiledFn resolve_encode() {
 
 static_assert(sizeof(TensorMap) == sizeof(CUtensorMap), "tensor map blob size");
 
-int get_tensor_map_2d_u8(lhb_ctx* ctx, const void* base, uint64_t rows, uint64_t cols,
-                         uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols,
-                         bool swizzle128, TensorMap* out) {
+static int get_tensor_map_2d(lhb_ctx* ctx, CUtensorMapDataType dtype, const void* base, uint64_t rows,
+                             uint64_t cols, uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols,
+                             bool swizzle128, TensorMap* out) {
     char key[160];
-    snprintf(key, sizeof(key), "%p/%llu/%llu/%llu/%u/%u/%d", base, (unsigned long long)rows,
+    snprintf(key, sizeof(key), "%d/%p/%llu/%llu/%llu/%u/%u/%d", (int)dtype, base, (unsigned long long)rows,
              (unsigned long long)cols, (unsigned long long)pitch_bytes, box_rows, box_cols,
              swizzle128 ? 1 : 0);
     {
@@ -54,7 +54,7 @@ int get_tensor_map_2d_u8(lhb_ctx* ctx, const void* base, uint64_t rows, uint64_t
     const cuuint64_t gstride[1] = {pitch_bytes};
     const cuuint32_t box[2] = {box_cols, box_rows};
     const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = enc(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), gdim,
+    const CUresult r = enc(&tm, dtype, 2, const_cast<void*>(base), gdim,
                            gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                            swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -67,6 +67,19 @@ int get_tensor_map_2d_u8(lhb_ctx* ctx, const void* base, uint64_t rows, uint64_t
     if (ctx->tmaps.size() > 4096) ctx->tmaps.clear();
     ctx->tmaps[key] = *out;
     return LHB_OK;
+}
+
+int get_tensor_map_2d_u8(lhb_ctx* ctx, const void* base, uint64_t rows, uint64_t cols,
+                         uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols,
+                         bool swizzle128, TensorMap* out) {
+    return get_tensor_map_2d(ctx, CU_TENSOR_MAP_DATA_TYPE_UINT8, base, rows, cols, pitch_bytes, box_rows,
+                             box_cols, swizzle128, out);
+}
+
+int get_tensor_map_2d_f32(lhb_ctx* ctx, const void* base, uint64_t rows, uint64_t cols,
+                          uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols, TensorMap* out) {
+    return get_tensor_map_2d(ctx, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, base, rows, cols, pitch_bytes, box_rows,
+                             box_cols, false, out);
 }
 
 }  // namespace lhb

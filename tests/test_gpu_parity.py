@@ -173,20 +173,28 @@ def test_w4a16_full_shape_cfg2(chk, lib):
     poll_ok()
 
 
-@pytest.mark.parametrize("splits", [1, 2, 3, 4, 8])
-def test_w4a16_every_split_reduction_path(chk, splits, monkeypatch):
-    """The K split is reduced inside a cluster (2 or 4 splits) or through the scratch
-    arena (other counts); force each and compare with the checker."""
-    monkeypatch.setenv("LHB_GEMV_SPLITS", str(splits))
-    rng = np.random.default_rng(splits)
-    M, N, K, G = 3, 1040, 2048, 128
+@pytest.mark.parametrize("M,N,K,G", [
+    (3, 1040, 2048, 128),       # few units: one per CTA, every column tile summed from 16 partials
+    (1, 256 * 300, 128, 128),   # K is one unit: every segment is a whole tile, no partials
+    (2, 256 * 700, 256, 64),    # ranges of several units: whole tiles in the middle, partial at the ends
+    (5, 16 * 37, 4096 + 640, 32),   # ragged N, K not a multiple of the 128-k unit
+    (16, 4096, 4096, 256),      # group longer than a unit
+    (1, 14336, 4096, 128),      # headline shape: 5 CTAs per column tile
+])
+def test_w4a16_unit_ranges_and_partial_sums(chk, M, N, K, G):
+    """A CTA's contiguous range of work units may cover whole column tiles (written directly)
+    and K-slices of tiles (summed through scratch by the last contributor): shapes that hit each
+    mix, with alpha/beta, compared with the checker and run twice for determinism."""
+    rng = np.random.default_rng(M + N + K)
     A = rng.standard_normal((M, K)).astype(np.float32)
     W = (rng.standard_normal((K, N)) * 0.02).astype(np.float32)
     p, s = chk.q4_quantize_groupwise(W, G)
     C0 = rng.standard_normal((M, N)).astype(np.float32)
-    got = lb.gemm_w4a16_groupwise(dev(A), dev(p), dev(s), G, C=dev(C0), alpha=0.5, beta=2.0)
-    assert_close(host(got), chk.gemm_w4a16_groupwise(A, p, s, G, C0, alpha=0.5, beta=2.0), what=f"splits={splits}")
-    got2 = lb.gemm_w4a16_groupwise(dev(A), dev(p), dev(s), G, C=dev(C0), alpha=0.5, beta=2.0)
+    dA, dp, ds = dev(A), dev(p), dev(s)
+    assert lb._cabi.load().lhb_gemm_w4a16_fast_path(M, N, K, G) == 1
+    got = lb.gemm_w4a16_groupwise(dA, dp, ds, G, C=dev(C0), alpha=0.5, beta=2.0)
+    assert_close(host(got), chk.gemm_w4a16_groupwise(A, p, s, G, C0, alpha=0.5, beta=2.0), what=f"{M}x{N}x{K} G={G}")
+    got2 = lb.gemm_w4a16_groupwise(dA, dp, ds, G, C=dev(C0), alpha=0.5, beta=2.0)
     assert torch.equal(got, got2)
     poll_ok()
 
