@@ -66,6 +66,7 @@ constexpr int GV_CONSUMER_WARPS = 8;
 constexpr int GV_CONSUMERS = GV_CONSUMER_WARPS * 32;
 constexpr int GV_THREADS = GV_CONSUMERS + 32;     // + one producer warp
 constexpr int GV_MAX_M = 16;
+constexpr size_t GV_DIG_BYTES = size_t(2) << 20;   // head of the scratch arena: activation digits + 16 row factors
 constexpr int GV_PB = 8;           // activation float4 loads a thread keeps in flight in the prologue
 
 using ptx::smem_u32;
@@ -107,6 +108,91 @@ __device__ unsigned long long g_gv_trace[64][512][8];
 #define GV_STAMP(i) do { } while (0)
 #endif
 
+// Three signed 7-bit digits of four consecutive activations (k .. k+3, k % 4 == 0, `kin`
+// = k % 32), written into the operand fragment of their k32-block: `base` points at the 32
+// bytes of the row's first digit column, the other two follow at +32 and +64.
+template <int WBITS>
+__device__ __forceinline__ void write_digits(uint8_t* base, int kin, float4 v, float scl) {
+    const int half = kin >> 4, r = kin & 15;
+    // a = rint(v * scl) = d1*2^14 + d2*2^7 + d3 with every digit in [-64, 64], by
+    // exact fp32 arithmetic: adding 1.5*2^23 rounds to an integer and leaves its
+    // two's-complement low bits in the low mantissa bits.
+    const float x[4] = {v.x * scl, v.y * scl, v.z * scl, v.w * scl};
+    uint32_t b1[4], b2[4], b3[4];                     // low byte = digit
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float MG = 12582912.0f;
+        const float xi = (x[j] + MG) - MG;                         // rint(x), |xi| <= 2^20
+        const float t1 = fmaf(xi, 6.103515625e-05f, MG);           // + xi / 2^14
+        const float r1 = fmaf(t1 - MG, -16384.0f, xi);             // |r1| <= 2^13
+        const float t2 = fmaf(r1, 0.0078125f, MG);                 // + r1 / 2^7
+        const float t3 = fmaf(t2 - MG, -128.0f, r1) + MG;          // |.| <= 64
+        b1[j] = __float_as_uint(t1); b2[j] = __float_as_uint(t2); b3[j] = __float_as_uint(t3);
+    }
+    // d1/d2/d3: 4 digits each, one byte per element
+    const uint32_t d1 = __byte_perm(__byte_perm(b1[0], b1[1], 0x0040), __byte_perm(b1[2], b1[3], 0x0040), 0x5410);
+    const uint32_t d2 = __byte_perm(__byte_perm(b2[0], b2[1], 0x0040), __byte_perm(b2[2], b2[3], 0x0040), 0x5410);
+    const uint32_t d3 = __byte_perm(__byte_perm(b3[0], b3[1], 0x0040), __byte_perm(b3[2], b3[3], 0x0040), 0x5410);
+    if (WBITS == 4) {
+        // Operand slot order of a k32-block (see the main loop): thread slot t = r / 4,
+        // first word = even k {4t, 4t+2, 16+4t, 16+4t+2}, second word = the odd k beside them.
+        uint8_t* d = base + (r >> 2) * 8 + half * 2;
+        *reinterpret_cast<uint16_t*>(d) = static_cast<uint16_t>(__byte_perm(d1, 0, 0x4420));
+        *reinterpret_cast<uint16_t*>(d + 4) = static_cast<uint16_t>(__byte_perm(d1, 0, 0x4431));
+        *reinterpret_cast<uint16_t*>(d + 32) = static_cast<uint16_t>(__byte_perm(d2, 0, 0x4420));
+        *reinterpret_cast<uint16_t*>(d + 36) = static_cast<uint16_t>(__byte_perm(d2, 0, 0x4431));
+        *reinterpret_cast<uint16_t*>(d + 64) = static_cast<uint16_t>(__byte_perm(d3, 0, 0x4420));
+        *reinterpret_cast<uint16_t*>(d + 68) = static_cast<uint16_t>(__byte_perm(d3, 0, 0x4431));
+    } else {
+        // slot t holds k0 + {2t, 2t+1, 8+2t, 9+2t}: elements (k, k+1) -> slot t0,
+        // (k+2, k+3) -> slot t0 + 1, bytes 0-1 (r < 8) or 2-3 (r >= 8)
+        uint8_t* d = base + half * 4 + ((r & 7) >> 1) * 8 + ((r >> 3) << 1);
+        *reinterpret_cast<uint16_t*>(d) = static_cast<uint16_t>(d1);
+        *reinterpret_cast<uint16_t*>(d + 8) = static_cast<uint16_t>(d1 >> 16);
+        *reinterpret_cast<uint16_t*>(d + 32) = static_cast<uint16_t>(d2);
+        *reinterpret_cast<uint16_t*>(d + 40) = static_cast<uint16_t>(d2 >> 16);
+        *reinterpret_cast<uint16_t*>(d + 64) = static_cast<uint16_t>(d3);
+        *reinterpret_cast<uint16_t*>(d + 72) = static_cast<uint16_t>(d3 >> 16);
+    }
+}
+
+// Digits of the whole activation matrix, once per GEMM call with M > 2 (for M <= 2 every
+// GEMV CTA makes the digits of its own K-range, which costs less than a launch).  One CTA
+// per row: row maximum, power-of-two factor, then the three digit columns of the row in
+// the operand order of gemv_mma_kernel, [K/32 blocks][nj columns][32 bytes]; k >= K is
+// written as zero up to k_pad.
+template <int WBITS>
+__global__ void __launch_bounds__(1024)
+gemv_digits_kernel(const float* __restrict__ A, int K, int k_pad, int nj, uint8_t* __restrict__ digits,
+                   float* __restrict__ inv_scale) {
+    __shared__ unsigned s_max[32];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");      // A may come from the kernel before; so may readers of `digits`
+    const int m = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float* row = A + static_cast<int64_t>(m) * K;
+    float mx = 0.0f;
+    for (int k = threadIdx.x * 4; k < K; k += 4096) {
+        const float4 v = *reinterpret_cast<const float4*>(row + k);
+        mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+    }
+    mx = warp_max(mx);
+    if (lane == 0) s_max[warp] = __float_as_uint(mx);
+    __syncthreads();
+    unsigned mb = s_max[lane];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mb = max(mb, __shfl_xor_sync(0xffffffffu, mb, o));
+    // power-of-two factor taking max|a| into [2^19, 2^20); exponent clamped
+    int se = mb ? 273 - static_cast<int>((mb >> 23) & 0xff) : 127;
+    se = max(1, min(253, se));
+    const float scl = __uint_as_float(static_cast<uint32_t>(se) << 23);
+    if (threadIdx.x == 0) inv_scale[m] = __uint_as_float(static_cast<uint32_t>(254 - se) << 23);
+    for (int k = threadIdx.x * 4; k < k_pad; k += 4096) {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (k < K) v = *reinterpret_cast<const float4*>(row + k);
+        write_digits<WBITS>(digits + (static_cast<int64_t>(k >> 5) * nj + 3 * m) * 32, k & 31, v, scl);
+    }
+}
+
 struct GemvParams {
     const float* A;        // [M, K]
     const float* scales;   // W8: [N] (W4 scales arrive through their tensor map)
@@ -122,13 +208,15 @@ struct GemvParams {
     float* partial;        // scratch [column tile][max_contrib][M][256]
     int* counters;         // one per column tile, zero between calls
     int* status;
+    const uint8_t* digits; // M > 2: activation digits of all of K in operand order, from gemv_digits_kernel
+    const float* inv_scale;//        and the inverse of each row's power-of-two factor
     int trace_slot;        // development builds only
 };
 
 // WBITS: 4 or 8.  JB: number of 8-column activation blocks; 3 digit columns per
 // row of A, so M <= (8 * JB) / 3.
 template <int WBITS, int JB>
-__global__ void __launch_bounds__(GV_THREADS, (JB >= 6) ? 1 : (JB == 1 ? 3 : 2))
+__global__ void __launch_bounds__(GV_THREADS, (JB >= 6) ? 1 : 2)
 gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ TensorMap tmS, const GemvParams p) {
     constexpr int K_PER_ROW = (WBITS == 4) ? 2 : 1;
     constexpr int KPS = GV_ROWS * K_PER_ROW;              // k per stage: 128 (W4), 64 (W8)
@@ -145,7 +233,7 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ T
     float* inv_s = part + NJ * GV_COLS;                                // [16]
     unsigned* rowmax = reinterpret_cast<unsigned*>(inv_s + 16);        // [16] max|a| bits per row
     uint64_t* bars = reinterpret_cast<uint64_t*>(rowmax + 16);         // full[], empty[]
-    int* flags = reinterpret_cast<int*>(bars + 2 * GV_MAX_STAGE);      // [0] abort, [1] is-last
+    int* flags = reinterpret_cast<int*>(bars + 2 * GV_MAX_STAGE + 2);  // after the digit barrier; [0] abort, [1] is-last
     uint8_t* dfrag = reinterpret_cast<uint8_t*>(flags + 4);            // [digit stage][kb32][NJ][32]
     volatile int* abort_flag = flags;
 
@@ -160,6 +248,7 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ T
     const int n_dig = min(S, n_units);                     // distinct stages of K this CTA meets
 
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + GV_MAX_STAGE);
+    const uint32_t digbar = smem_u32(bars + 2 * GV_MAX_STAGE);        // M > 2: the digits have landed
     const uint32_t stage_tx = GV_STAGE_BYTES + ((WBITS == 4) ? p.srows * GV_COLS * 4 : 0);
     // one unit into ring slot `slot`: two weight boxes and, for W4, its rows of group scales
     auto issue = [&](int tile, int stage, int slot) {
@@ -182,6 +271,7 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ T
             ptx::mbar_init(full0 + 8 * s, 1);
             ptx::mbar_init(empty0 + 8 * s, GV_CONSUMER_WARPS);
         }
+        ptx::mbar_init(digbar, 1);
         flags[0] = 0;
         flags[1] = 0;
         ptx::fence_mbar_init();
@@ -202,6 +292,22 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ T
     __syncthreads();
 
     // ---- prologue, overlapped with the loads in flight ---------------------------
+    constexpr bool PRE = JB > 1;        // digits were made once for all CTAs by gemv_digits_kernel
+    if constexpr (PRE) {
+        // digit stage i = stage (s_first + i) mod S: one or two contiguous pieces of the global array
+        if (warp == GV_CONSUMER_WARPS && lane == 0) {
+            const uint32_t per_stage = KPS * NJ;
+            const int len_a = min(n_dig, S - s_first);
+            ptx::mbar_expect_tx(digbar, n_dig * per_stage);
+            ptx::bulk_load_1d(smem_u32(dfrag), p.digits + static_cast<int64_t>(s_first) * per_stage, len_a * per_stage,
+                              digbar);
+            if (n_dig > len_a)
+                ptx::bulk_load_1d(smem_u32(dfrag) + len_a * per_stage, p.digits, (n_dig - len_a) * per_stage, digbar);
+        }
+        if (threadIdx.x < p.M) inv_s[threadIdx.x] = p.inv_scale[threadIdx.x];
+        ptx::mbar_wait(digbar, 0, abort_flag, p.status);
+        __syncthreads();
+    } else {
     // Activations of the K stages this CTA meets (digit stage i = stage
     // (s_first + i) mod S): row maxima, then three 7-bit digits per element in
     // MMA-operand order.  Digit columns of rows m >= M are left as they are: an
@@ -274,51 +380,11 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ T
         const float scl = __uint_as_float(static_cast<uint32_t>(se) << 23);
         if (kl == 0) inv_s[m] = __uint_as_float(static_cast<uint32_t>(254 - se) << 23);
         const float4 v = vb[j];
-        // a = rint(v * scl) = d1*2^14 + d2*2^7 + d3 with every digit in [-64, 64], by
-        // exact fp32 arithmetic: adding 1.5*2^23 rounds to an integer and leaves its
-        // two's-complement low bits in the low mantissa bits.
-        const float x[4] = {v.x * scl, v.y * scl, v.z * scl, v.w * scl};
-        uint32_t b1[4], b2[4], b3[4];                     // low byte = digit
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const float MG = 12582912.0f;
-            const float xi = (x[j] + MG) - MG;                         // rint(x), |xi| <= 2^20
-            const float t1 = fmaf(xi, 6.103515625e-05f, MG);           // + xi / 2^14
-            const float r1 = fmaf(t1 - MG, -16384.0f, xi);             // |r1| <= 2^13
-            const float t2 = fmaf(r1, 0.0078125f, MG);                 // + r1 / 2^7
-            const float t3 = fmaf(t2 - MG, -128.0f, r1) + MG;          // |.| <= 64
-            b1[j] = __float_as_uint(t1); b2[j] = __float_as_uint(t2); b3[j] = __float_as_uint(t3);
-        }
-        // d1/d2/d3: 4 digits each, one byte per element
-        const uint32_t d1 = __byte_perm(__byte_perm(b1[0], b1[1], 0x0040), __byte_perm(b1[2], b1[3], 0x0040), 0x5410);
-        const uint32_t d2 = __byte_perm(__byte_perm(b2[0], b2[1], 0x0040), __byte_perm(b2[2], b2[3], 0x0040), 0x5410);
-        const uint32_t d3 = __byte_perm(__byte_perm(b3[0], b3[1], 0x0040), __byte_perm(b3[2], b3[3], 0x0040), 0x5410);
-        const int kb = kl >> 5, kin = kl & 31, half = kin >> 4, r = kin & 15;      // kb counts across digit stages
-        uint8_t* base = dfrag + (kb * NJ + 3 * m) * 32;
-        if (WBITS == 4) {
-            // Operand slot order of a k32-block (see the main loop): thread slot t = r / 4,
-            // first word = even k {4t, 4t+2, 16+4t, 16+4t+2}, second word = the odd k beside them.
-            uint8_t* d = base + (r >> 2) * 8 + half * 2;
-            *reinterpret_cast<uint16_t*>(d) = static_cast<uint16_t>(__byte_perm(d1, 0, 0x4420));
-            *reinterpret_cast<uint16_t*>(d + 4) = static_cast<uint16_t>(__byte_perm(d1, 0, 0x4431));
-            *reinterpret_cast<uint16_t*>(d + 32) = static_cast<uint16_t>(__byte_perm(d2, 0, 0x4420));
-            *reinterpret_cast<uint16_t*>(d + 36) = static_cast<uint16_t>(__byte_perm(d2, 0, 0x4431));
-            *reinterpret_cast<uint16_t*>(d + 64) = static_cast<uint16_t>(__byte_perm(d3, 0, 0x4420));
-            *reinterpret_cast<uint16_t*>(d + 68) = static_cast<uint16_t>(__byte_perm(d3, 0, 0x4431));
-        } else {
-            // slot t holds k0 + {2t, 2t+1, 8+2t, 9+2t}: elements (k, k+1) -> slot t0,
-            // (k+2, k+3) -> slot t0 + 1, bytes 0-1 (r < 8) or 2-3 (r >= 8)
-            uint8_t* d = base + half * 4 + ((r & 7) >> 1) * 8 + ((r >> 3) << 1);
-            *reinterpret_cast<uint16_t*>(d) = static_cast<uint16_t>(d1);
-            *reinterpret_cast<uint16_t*>(d + 8) = static_cast<uint16_t>(d1 >> 16);
-            *reinterpret_cast<uint16_t*>(d + 32) = static_cast<uint16_t>(d2);
-            *reinterpret_cast<uint16_t*>(d + 40) = static_cast<uint16_t>(d2 >> 16);
-            *reinterpret_cast<uint16_t*>(d + 64) = static_cast<uint16_t>(d3);
-            *reinterpret_cast<uint16_t*>(d + 72) = static_cast<uint16_t>(d3 >> 16);
-        }
+        write_digits<WBITS>(dfrag + ((kl >> 5) * NJ + 3 * m) * 32, kl & 31, v, scl);
       }
     }
     __syncthreads();
+    }   // !PRE
     GV_STAMP(2);
 
     if (warp < GV_CONSUMER_WARPS) {
@@ -595,11 +661,11 @@ static GemvPlan plan_gemv(int wbits, int jb, int N, int K, int G, int sm_count) 
     pl.units = static_cast<int>(units);
     pl.srows = wbits == 4 ? (G < 128 ? 128 / G : 1) : 0;
     pl.flush_mask = wbits == 4 ? (G == 32 ? 0xF : (G == 64 ? 0xA : 0x8)) : 0;
-    int per_sm = jb >= 6 ? 1 : (jb == 1 ? 3 : 2);          // what the kernel's launch bounds allow
+    int per_sm = jb >= 6 ? 1 : 2;                          // what the kernel's launch bounds allow
     if (const char* e = getenv("LHB_GEMV_CTAS_PER_SM")) per_sm = std::max(1, std::min(per_sm, atoi(e)));
     const size_t nj = 8 * jb;
     const size_t stage_bytes = GV_STAGE_BYTES + static_cast<size_t>(pl.srows) * GV_COLS * 4;
-    const size_t fixed = 1024 + nj * GV_COLS * 4 + 16 * 4 + 16 * 4 + 2 * GV_MAX_STAGE * 8 + 16;
+    const size_t fixed = 1024 + nj * GV_COLS * 4 + 16 * 4 + 16 * 4 + (2 * GV_MAX_STAGE + 2) * 8 + 16;
     const size_t dig_per_stage = static_cast<size_t>(kps) * nj;
     size_t budget = per_sm == 1 ? 227 * 1024 : (228 * 1024) / per_sm - 1024 - 512;
     if (const char* e = getenv("LHB_GEMV_SMEM_KB")) budget = std::min<size_t>(budget, static_cast<size_t>(atoi(e)) * 1024);
@@ -657,7 +723,9 @@ static int launch_gemv_t(lhb_ctx* ctx, const TensorMap& tm, const TensorMap& tms
     p.srows = pl.srows;
     p.flush_mask = pl.flush_mask;
     p.max_contrib = pl.max_contrib;
-    p.partial = reinterpret_cast<float*>(ctx->scratch);
+    p.partial = reinterpret_cast<float*>(static_cast<uint8_t*>(ctx->scratch) + GV_DIG_BYTES);
+    p.digits = static_cast<const uint8_t*>(ctx->scratch);
+    p.inv_scale = reinterpret_cast<const float*>(static_cast<uint8_t*>(ctx->scratch) + GV_DIG_BYTES - 256);
     p.counters = ctx->counters;
     p.status = ctx->status_word;
 #ifdef LHB_GEMV_TRACE
@@ -697,8 +765,28 @@ static int launch_gemv(lhb_ctx* ctx, const float* A, const void* B, const float*
         GemvPlan pl = plan_gemv(WBITS, jb, N, K, WBITS == 4 ? G : 1, ctx->sm_count);
         if (!pl.ok) return LHB_ERR_UNSUPPORTED;
         if (pl.col_tiles > static_cast<int>(ctx->counters_len)) return LHB_ERR_UNSUPPORTED;
-        if (static_cast<size_t>(pl.col_tiles) * pl.max_contrib * m * GV_COLS * sizeof(float) > ctx->scratch_bytes)
+        if (ctx->scratch_bytes < GV_DIG_BYTES ||
+            static_cast<size_t>(pl.col_tiles) * pl.max_contrib * m * GV_COLS * sizeof(float) >
+                ctx->scratch_bytes - GV_DIG_BYTES)
             return LHB_ERR_SCRATCH;
+        if (jb > 1) {
+            // digits of this slab's rows, once, for every CTA of the GEMV that follows
+            const int kps = GV_ROWS * (WBITS == 4 ? 2 : 1);
+            const int k_pad = pl.S * kps;
+            if (static_cast<size_t>(k_pad) * 8 * jb > GV_DIG_BYTES - 256) return LHB_ERR_SCRATCH;
+            cudaLaunchConfig_t dc = {};
+            dc.gridDim = dim3(m, 1, 1);
+            dc.blockDim = dim3(1024, 1, 1);
+            dc.stream = st;
+            cudaLaunchAttribute da[1];
+            da[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            da[0].val.programmaticStreamSerializationAllowed = 1;
+            dc.attrs = da;
+            dc.numAttrs = 1;
+            LHB_CUDA(cudaLaunchKernelEx(&dc, gemv_digits_kernel<WBITS>, A + static_cast<int64_t>(m0) * K, K, k_pad,
+                                        8 * jb, static_cast<uint8_t*>(ctx->scratch),
+                                        reinterpret_cast<float*>(static_cast<uint8_t*>(ctx->scratch) + GV_DIG_BYTES - 256)));
+        }
         if (WBITS == 4 && m0 == 0)
             if (int e = get_tensor_map_2d_f32(ctx, scales, K / G, N, static_cast<uint64_t>(N) * 4, pl.srows,
                                               GV_COLS, &tms))

@@ -76,6 +76,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int 
         ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar)
         : "memory");
 }
+// untiled bulk copy global -> this CTA's shared memory; both addresses and the size are multiples of 16
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+        : "memory");
+}
 __device__ __forceinline__ void prefetch_tmap(const void* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
