@@ -289,7 +289,62 @@ def bench_extra(torch, lb, steps, warmup, hbm_peak):
     out["paged_decode_q8"] = bench_paged_decode(torch, lb, steps, warmup, hbm_peak)
     torch.cuda.empty_cache()
     out["w8a8_prefill"] = bench_w8a8(torch, lb, min(steps, 5), 3)
+    torch.cuda.empty_cache()
+    out["decode_step_cfg4"] = bench_decode_step(torch, lb, min(steps, 5), 3, hbm_peak)
+    torch.cuda.empty_cache()
     return out
+
+
+def bench_decode_step(torch, lb, steps, warmup, hbm_peak, layers=32, batch=32, ctx_len=2048, seed=20244):
+    """Fourth BASELINE config: one decode step of a 32-layer Llama-3-8B-shaped stack (d 4096, 32/8 heads of
+    128, FFN 14336, RoPE base 500000, RMSNorm), all seven projections int4 group-128, int8 paged KV holding
+    `ctx_len` tokens per sequence, `batch` sequences; the whole step replayed as one CUDA graph."""
+    import numpy as np
+    from longhornai_b200 import decode_step as ds
+    cfg = ds.StepConfig(4096, 32, 8, 128, 14336, GROUP, 500000.0, False, 1e-5)
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+    bs = 16
+    blocks_per_req = (ctx_len + 1 + bs - 1) // bs
+    num_blocks = batch * blocks_per_req
+    L = lb.PagedLayout(num_blocks, bs, cfg.n_kv_heads, cfg.head_dim)
+    acfg = lb.PagedAttnCfg(cfg.n_q_heads, cfg.n_kv_heads, 1, cfg.head_dim, 1, 0.0, 0, 0)
+    rng = np.random.default_rng(seed)
+    perm = rng.permutation(num_blocks).astype(np.int32)
+    tables = torch.from_numpy(perm.reshape(batch, blocks_per_req).copy()).cuda()
+    past = torch.full((batch,), ctx_len, dtype=torch.int32, device="cuda")
+    cur = past + 1
+
+    def rnd(k, n):
+        return torch.randn(k, n, device="cuda", generator=gen) * 0.02
+    lw, pools = [], []
+    for _ in range(layers):
+        lw.append(ds.LayerWeights.quantize(cfg, rnd(4096, 4096), rnd(4096, 1024), rnd(4096, 1024), rnd(4096, 4096),
+                                           rnd(4096, 2 * 14336), rnd(14336, 4096),
+                                           torch.ones(4096, device="cuda"), torch.ones(4096, device="cuda")))
+        shape = (num_blocks, cfg.n_kv_heads, bs, cfg.head_dim)
+        pools.append(ds.KVPools(
+            torch.randint(-127, 128, shape, dtype=torch.int8, device="cuda", generator=gen),
+            torch.randint(-127, 128, shape, dtype=torch.int8, device="cuda", generator=gen),
+            torch.rand(shape[:3], device="cuda", generator=gen) * 0.02 + 0.005,
+            torch.rand(shape[:3], device="cuda", generator=gen) * 0.02 + 0.005))
+    x0 = torch.randn(batch, 4096, device="cuda", generator=gen)
+    x = x0.clone()
+    buf = ds.StepBuffers.allocate(cfg, batch, x.device)
+
+    def step():
+        x.copy_(x0)                  # every replay starts from the same hidden state
+        ds.decode_step(x, lw, pools, tables, past, cur, cfg, L, acfg, buf)
+    run, is_graph = graphed(step, torch, GRAPHS)
+    ms = timed(run, steps, warmup, None, torch)
+    per = ms / steps * 1e-3
+    wbytes = sum(w.weight_bytes() for w in lw)
+    kvbytes = layers * batch * (ctx_len + 1) * cfg.n_kv_heads * (2 * cfg.head_dim + 8)
+    b = wbytes + kvbytes
+    finite = bool(torch.isfinite(x).all().item())
+    return {"ms_per_step": per * 1e3, "tok_per_s": batch / per, "GBps": b / per / 1e9,
+            "hbm_frac": b / per / 1e9 / hbm_peak, "bytes": b, "layers": layers, "batch": batch,
+            "ctx_len": ctx_len, "launches_per_step": layers * ds.launches_per_layer(batch) + 1,
+            "graph": int(is_graph), "finite": int(finite)}
 
 
 def bench_w8a8(torch, lb, steps, warmup, M=8192, K=8192, N=28672):
@@ -493,7 +548,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary workloads")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--only", default=None, choices=["paged_decode", "w8a8"],
+    ap.add_argument("--only", default=None, choices=["paged_decode", "w8a8", "decode_step"],
                     help="run one secondary workload alone on one GPU (for profiling) and print its numbers")
     args = ap.parse_args()
     if args.warmup < 3:
@@ -509,6 +564,13 @@ def main():
         import longhornai_b200 as lb
         torch.cuda.set_device(0)
         print(json.dumps({"w8a8_prefill": bench_w8a8(torch, lb, args.steps, args.warmup, M=2048)}), flush=True)
+    elif args.only == "decode_step":
+        import torch
+        import longhornai_b200 as lb
+        torch.cuda.set_device(0)
+        layers = int(os.environ.get("LHB_BENCH_LAYERS", "32"))
+        print(json.dumps({"decode_step_cfg4": bench_decode_step(torch, lb, args.steps, args.warmup,
+                                                                 measured_peaks()[0], layers=layers)}), flush=True)
     elif args.impl == "reference":
         run_reference(args)
     else:

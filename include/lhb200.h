@@ -215,6 +215,25 @@ LHB_API int lhb_paged_attention_f32_batched(lhb_ctx* ctx, const float* Q, const 
                                             const lhb_paged_attn_cfg* cfg,
                                             const lhb_paged_layout* layout, void* stream);
 
+/* ---- decode-step glue between the quantised GEMMs -------------------------------- */
+
+/* lh::rmsnorm (src/kernels/normalization.hpp:21): y[r, :] = x[r, :] / rms(x[r, :]) * gamma. */
+LHB_API int lhb_rmsnorm(lhb_ctx* ctx, const float* x, const float* gamma, float* y, int rows,
+                        int dim, float eps, void* stream);
+/* lh::rope (src/kernels/rope.hpp:19-21), in place on x = [seq, n_heads, head_dim]; row s sits
+ * at position pos_offset + s.  interleaved != 0 rotates pairs (2i, 2i+1), else (i, i + d/2). */
+LHB_API int lhb_rope(lhb_ctx* ctx, float* x, int seq, int n_heads, int head_dim, float theta_base,
+                     float freq_scale, int interleaved, int pos_offset, void* stream);
+/* The same rotation for a decode batch: x = [n_requests, n_heads, head_dim], one token per
+ * request at positions[r] (a device array, e.g. the cache manager's seq_lens before the
+ * append).  Equals lh::rope(x_r, 1, ..., pos_offset = positions[r]) for every request. */
+LHB_API int lhb_rope_decode_batched(lhb_ctx* ctx, float* x, const int32_t* positions,
+                                    int n_requests, int n_heads, int head_dim, float theta_base,
+                                    float freq_scale, int interleaved, void* stream);
+/* lh::swiglu (src/kernels/activation.hpp:34): x = [rows, 2*dim] (gate || value),
+ * y[r, i] = gate * sigmoid(gate) * value. */
+LHB_API int lhb_swiglu(lhb_ctx* ctx, const float* x, float* y, int rows, int dim, void* stream);
+
 /* ---- device-resident cache manager ---------------------------------------------- */
 
 /* Host bookkeeping of lh::CacheManager (src/runtime/cache_manager.hpp:34-110:

@@ -50,6 +50,10 @@ SIGNATURES = {
     "lhb_q8_dequantize_per_col": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp]),
     "lhb_q4_quantize_groupwise": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "lhb_q4_dequantize_groupwise": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "lhb_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _vp]),
+    "lhb_rope": (_i, [_vp, _vp, _i, _i, _i, _f, _f, _i, _i, _vp]),
+    "lhb_rope_decode_batched": (_i, [_vp, _vp, _vp, _i, _i, _i, _f, _f, _i, _vp]),
+    "lhb_swiglu": (_i, [_vp, _vp, _vp, _i, _i, _vp]),
     "lhb_gemm_w8a8": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _f, _vp]),
     "lhb_gemm_w4a16_groupwise": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _f, _vp]),
     "lhb_gemm_w8a16_perchannel": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _f, _vp]),

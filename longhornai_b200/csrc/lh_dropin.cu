@@ -268,4 +268,27 @@ void paged_attention(const float* Q, const float* K_pool, const float* V_pool, c
     paged_attention_batched(Q, K_pool, V_pool, block_table, nb, sl.get(), 1, O, cfg, L);
 }
 
+void rmsnorm(const float* x, const float* gamma, float* y, int rows, int dim, float eps) {
+    bool any_host = false;
+    ARG(float, xi, x, sz(rows, dim), In); ARG(float, g, gamma, sz(dim), In); ARG(float, yo, y, sz(rows, dim), Out);
+    check(lhb_rmsnorm(context(), xi.get(), g.get(), yo.get(), rows, dim, eps, g_stream), "rmsnorm");
+    yo.writeback(); finish(any_host);
+}
+
+void rope(float* x, int seq, int n_heads, int head_dim, float theta_base, float freq_scale, bool interleaved,
+          int pos_offset) {
+    bool any_host = false;
+    ARG(float, xi, x, sz(seq, n_heads) * head_dim, InOut);
+    check(lhb_rope(context(), xi.get(), seq, n_heads, head_dim, theta_base, freq_scale, interleaved ? 1 : 0, pos_offset,
+                   g_stream), "rope");
+    xi.writeback(); finish(any_host);
+}
+
+void swiglu(const float* x, float* y, int rows, int dim) {
+    bool any_host = false;
+    ARG(float, xi, x, sz(rows, dim) * 2, In); ARG(float, yo, y, sz(rows, dim), Out);
+    check(lhb_swiglu(context(), xi.get(), yo.get(), rows, dim, g_stream), "swiglu");
+    yo.writeback(); finish(any_host);
+}
+
 }  // namespace lh

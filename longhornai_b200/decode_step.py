@@ -1,0 +1,149 @@
+"""One decode step of a Llama-style layer stack on the quantised path.
+
+This is host-side composition only: every arithmetic step is one of the
+library's C-ABI calls, in the order the reference's kernels would be called
+for a pre-norm decoder layer with grouped-query attention and a SwiGLU MLP:
+
+    h  = rmsnorm(x)                          src/kernels/normalization.hpp:21
+    q, k, v = h Wq, h Wk, h Wv               gemm_w4a16_groupwise (gemm_quant.hpp:54)
+    rope(q), rope(k) at each request's position          src/kernels/rope.hpp:19
+    append k, v to the int8 paged cache      paged_kv_append_q8 (kvcache_quant.hpp:41)
+    o  = paged attention over the cache      paged_attention_q8 (kvcache_quant.hpp:51)
+    x += o Wo                                the residual add is beta = 1 of the GEMM
+    h  = rmsnorm(x)
+    x += swiglu(h Wgu) Wdown                 src/kernels/activation.hpp:34; Wgu = gate || up
+
+`x` is fp32 [n_requests, dim], one new token per request.  All seven
+projections are int4 group-wise weights in the reference layout.  Nothing here
+allocates inside the step once `StepBuffers` exists, so a step can be captured
+into a CUDA graph after one eager run.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from . import kernels as K
+from ._cabi import PagedAttnCfg, PagedLayout
+
+
+@dataclass
+class StepConfig:
+    dim: int
+    n_q_heads: int
+    n_kv_heads: int
+    head_dim: int
+    ffn: int
+    group: int = 128
+    rope_theta: float = 500000.0
+    rope_interleaved: bool = False      # Llama checkpoints use the half-rotation layout
+    eps: float = 1e-5
+
+    @property
+    def q_dim(self) -> int:
+        return self.n_q_heads * self.head_dim
+
+    @property
+    def kv_dim(self) -> int:
+        return self.n_kv_heads * self.head_dim
+
+
+@dataclass
+class LayerWeights:
+    """(packed uint8 [K/2, N], fp32 scales [K/G, N]) per projection, plus the two norm gains."""
+    wq: tuple
+    wk: tuple
+    wv: tuple
+    wo: tuple
+    wgu: tuple          # [dim, 2*ffn]: gate columns first, then up ("value") columns
+    wdown: tuple
+    g_attn: torch.Tensor
+    g_ffn: torch.Tensor
+
+    @staticmethod
+    def quantize(cfg: StepConfig, wq, wk, wv, wo, wgu, wdown, g_attn, g_ffn) -> "LayerWeights":
+        q = lambda w: K.q4_quantize_groupwise(w, cfg.group)
+        return LayerWeights(q(wq), q(wk), q(wv), q(wo), q(wgu), q(wdown), g_attn, g_ffn)
+
+    def weight_bytes(self) -> int:
+        return sum(p.numel() + s.numel() * 4 for p, s in (self.wq, self.wk, self.wv, self.wo, self.wgu, self.wdown))
+
+
+@dataclass
+class KVPools:
+    """int8 pools [num_blocks, n_kv_heads, block_size, head_dim] and fp32 scale pools of one layer."""
+    k: torch.Tensor
+    v: torch.Tensor
+    ks: torch.Tensor
+    vs: torch.Tensor
+
+    @staticmethod
+    def empty(L: PagedLayout, device) -> "KVPools":
+        shape = (L.num_blocks, L.n_kv_heads, L.block_size, L.head_dim)
+        return KVPools(torch.zeros(shape, dtype=torch.int8, device=device),
+                       torch.zeros(shape, dtype=torch.int8, device=device),
+                       torch.zeros(shape[:3], dtype=torch.float32, device=device),
+                       torch.zeros(shape[:3], dtype=torch.float32, device=device))
+
+
+@dataclass
+class StepBuffers:
+    """Activations of one layer, reused by every layer of the step."""
+    h: torch.Tensor
+    q: torch.Tensor
+    k: torch.Tensor
+    v: torch.Tensor
+    o: torch.Tensor
+    gu: torch.Tensor
+    act: torch.Tensor
+
+    @staticmethod
+    def allocate(cfg: StepConfig, n_req: int, device) -> "StepBuffers":
+        f = lambda n: torch.empty((n_req, n), dtype=torch.float32, device=device)
+        return StepBuffers(f(cfg.dim), f(cfg.q_dim), f(cfg.kv_dim), f(cfg.kv_dim), f(cfg.q_dim),
+                           f(2 * cfg.ffn), f(cfg.ffn))
+
+
+def decode_layer(x, w: LayerWeights, pools: KVPools, block_tables, past_lens, cur_lens, cfg: StepConfig,
+                 L: PagedLayout, acfg: PagedAttnCfg, buf: StepBuffers, ctx=None):
+    """Updates `x` [n_req, dim] in place.  `past_lens` = tokens already cached per request (the new
+    token's position), `cur_lens` = past_lens + 1; both int32 device tensors."""
+    n_req = x.shape[0]
+    G = cfg.group
+    K.rmsnorm(x, w.g_attn, cfg.eps, out=buf.h, ctx=ctx)
+    K.gemm_w4a16_groupwise(buf.h, *w.wq, G, C=buf.q, ctx=ctx)
+    K.gemm_w4a16_groupwise(buf.h, *w.wk, G, C=buf.k, ctx=ctx)
+    K.gemm_w4a16_groupwise(buf.h, *w.wv, G, C=buf.v, ctx=ctx)
+    K.rope_decode_batched(buf.q.view(n_req, cfg.n_q_heads, cfg.head_dim), past_lens, cfg.rope_theta, 1.0,
+                          cfg.rope_interleaved, ctx=ctx)
+    K.rope_decode_batched(buf.k.view(n_req, cfg.n_kv_heads, cfg.head_dim), past_lens, cfg.rope_theta, 1.0,
+                          cfg.rope_interleaved, ctx=ctx)
+    K.paged_kv_append_q8_batched(pools.k, pools.v, pools.ks, pools.vs, buf.k, buf.v, block_tables, past_lens, L,
+                                 1, ctx=ctx)
+    K.paged_attention_q8_batched(buf.q.view(n_req, cfg.n_q_heads, 1, cfg.head_dim), pools.k, pools.v, pools.ks,
+                                 pools.vs, block_tables, cur_lens, acfg, L,
+                                 O=buf.o.view(n_req, cfg.n_q_heads, 1, cfg.head_dim), ctx=ctx)
+    K.gemm_w4a16_groupwise(buf.o, *w.wo, G, C=x, alpha=1.0, beta=1.0, ctx=ctx)
+    K.rmsnorm(x, w.g_ffn, cfg.eps, out=buf.h, ctx=ctx)
+    K.gemm_w4a16_groupwise(buf.h, *w.wgu, G, C=buf.gu, ctx=ctx)
+    K.swiglu(buf.gu, out=buf.act, ctx=ctx)
+    K.gemm_w4a16_groupwise(buf.act, *w.wdown, G, C=x, alpha=1.0, beta=1.0, ctx=ctx)
+    return x
+
+
+def decode_step(x, layers, pools, block_tables, past_lens, cur_lens, cfg: StepConfig, L: PagedLayout,
+                acfg: PagedAttnCfg, buf: StepBuffers, ctx=None):
+    """All layers in turn; `layers` and `pools` are per-layer lists."""
+    for w, kv in zip(layers, pools):
+        decode_layer(x, w, kv, block_tables, past_lens, cur_lens, cfg, L, acfg, buf, ctx=ctx)
+    return x
+
+
+def launches_per_layer(n_req: int) -> int:
+    """Kernel launches of one layer (for the bench's launch count): 2 norms, 2 rotations, append,
+    attention, SwiGLU, and 6 GEMMs each served in slabs of 16 rows, plus one digit pass per slab
+    when a slab has more than two rows."""
+    slabs = (n_req + 15) // 16
+    per_gemm = slabs * (2 if n_req > 2 else 1)
+    return 7 + 6 * per_gemm

@@ -315,3 +315,49 @@ def paged_attention_q8_batched_noalloc(Q, K_pool, V_pool, K_scales, V_scales, bl
         n_req, _t(O, torch.float32, "O"), C.byref(cfg), C.byref(L), _stream(dev)),
         "paged_attention_q8_batched_noalloc")
     return O
+
+
+# ---- decode-step glue -----------------------------------------------------------
+
+def rmsnorm(x, gamma, eps: float = 1e-5, out=None, ctx=None):
+    """lh::rmsnorm (src/kernels/normalization.hpp:21): fp32 [rows, dim] -> [rows, dim]."""
+    c = _ctx_for(x, ctx)
+    rows, dim = x.shape
+    y = torch.empty_like(x) if out is None else out
+    check(c.lib.lhb_rmsnorm(c.handle, _t(x, torch.float32, "x"), _t(gamma, torch.float32, "gamma"),
+                            _t(y, torch.float32, "out"), rows, dim, C.c_float(eps), _stream(c.device)),
+          "rmsnorm")
+    return y
+
+
+def rope(x, theta_base: float = 10000.0, freq_scale: float = 1.0, interleaved: bool = True,
+         pos_offset: int = 0, ctx=None):
+    """lh::rope (src/kernels/rope.hpp:19-21), in place on fp32 [seq, n_heads, head_dim]."""
+    c = _ctx_for(x, ctx)
+    seq, n_heads, head_dim = x.shape
+    check(c.lib.lhb_rope(c.handle, _t(x, torch.float32, "x"), seq, n_heads, head_dim,
+                         C.c_float(theta_base), C.c_float(freq_scale), int(bool(interleaved)),
+                         int(pos_offset), _stream(c.device)), "rope")
+    return x
+
+
+def rope_decode_batched(x, positions, theta_base: float = 10000.0, freq_scale: float = 1.0,
+                        interleaved: bool = True, ctx=None):
+    """One token per request: fp32 [n_req, n_heads, head_dim] rotated in place at positions[r]."""
+    c = _ctx_for(x, ctx)
+    n_req, n_heads, head_dim = x.shape
+    check(c.lib.lhb_rope_decode_batched(c.handle, _t(x, torch.float32, "x"),
+                                        _t(positions, torch.int32, "positions"), n_req, n_heads,
+                                        head_dim, C.c_float(theta_base), C.c_float(freq_scale),
+                                        int(bool(interleaved)), _stream(c.device)), "rope_decode_batched")
+    return x
+
+
+def swiglu(x, out=None, ctx=None):
+    """lh::swiglu (src/kernels/activation.hpp:34): fp32 [rows, 2*dim] (gate || value) -> [rows, dim]."""
+    c = _ctx_for(x, ctx)
+    rows, dim2 = x.shape
+    y = torch.empty((rows, dim2 // 2), dtype=torch.float32, device=x.device) if out is None else out
+    check(c.lib.lhb_swiglu(c.handle, _t(x, torch.float32, "x"), _t(y, torch.float32, "out"), rows,
+                           dim2 // 2, _stream(c.device)), "swiglu")
+    return y

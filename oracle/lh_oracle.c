@@ -511,6 +511,69 @@ LHO_API void lho_paged_attention_f32_batched(
 /* Bench harness: independent calls of the functions above spread over */
 /* host threads (the functions themselves stay single-threaded, as in  */
 /* the reference).  Compiled with -fopenmp.                            */
+/* ---------------------------------------------------------------------------
+ * Decode-step glue: RMSNorm, rotary embedding, SwiGLU.
+ * ------------------------------------------------------------------------- */
+
+/* src/kernels/normalization.cpp:58-76 (rmsnorm = rmsnorm_ref): sum of squares in
+ * index order, inv_rms = 1 / sqrt(sumsq / dim + eps), y = (x * inv_rms) * gamma. */
+LHO_API void lho_rmsnorm(const float* x, const float* gamma, float* y, int rows,
+                         int dim, float eps) {
+    for (int r = 0; r < rows; ++r) {
+        const float* xr = x + (int64_t)r * dim;
+        float* yr = y + (int64_t)r * dim;
+        float sumsq = 0.0f;
+        for (int i = 0; i < dim; ++i) sumsq += xr[i] * xr[i];
+        const float inv_rms = 1.0f / sqrtf(sumsq / (float)dim + eps);
+        for (int i = 0; i < dim; ++i) yr[i] = xr[i] * inv_rms * gamma[i];
+    }
+}
+
+/* src/kernels/rope.cpp:9-15 and 47-86 (the table-driven `rope`): pair i of a
+ * head rotates by angle = (pos_offset + s) * freq_scale / theta_base^(2i/head_dim);
+ * interleaved pairs are (2i, 2i+1), half-rotation pairs are (i, i + head_dim/2).
+ * x is [seq, n_heads, head_dim], rotated in place. */
+LHO_API void lho_rope(float* x, int seq, int n_heads, int head_dim,
+                      float theta_base, float freq_scale, int interleaved,
+                      int pos_offset) {
+    const int half = head_dim / 2;
+    for (int s = 0; s < seq; ++s) {
+        const float pos = (float)(pos_offset + s) * freq_scale;
+        for (int i = 0; i < half; ++i) {
+            const float exponent = (float)(2 * i) / (float)head_dim;
+            const float inv_freq = 1.0f / powf(theta_base, exponent);
+            const float angle = pos * inv_freq;
+            const float c = cosf(angle), sn = sinf(angle);
+            for (int h = 0; h < n_heads; ++h) {
+                float* v = x + ((int64_t)s * n_heads + h) * head_dim;
+                if (interleaved) {
+                    const float a = v[2 * i], b = v[2 * i + 1];
+                    v[2 * i] = a * c - b * sn;
+                    v[2 * i + 1] = a * sn + b * c;
+                } else {
+                    const float a = v[i], b = v[i + half];
+                    v[i] = a * c - b * sn;
+                    v[i + half] = b * c + a * sn;
+                }
+            }
+        }
+    }
+}
+
+/* src/kernels/activation.cpp:12 and 46-55: x is [rows, 2*dim] = gate || value,
+ * y[r, i] = (gate * sigmoid(gate)) * value with sigmoid(v) = 1 / (1 + exp(-v)). */
+LHO_API void lho_swiglu(const float* x, float* y, int rows, int dim) {
+    for (int r = 0; r < rows; ++r) {
+        const float* gate = x + (int64_t)r * 2 * dim;
+        const float* value = gate + dim;
+        float* yr = y + (int64_t)r * dim;
+        for (int i = 0; i < dim; ++i) {
+            const float sg = 1.0f / (1.0f + expf(-gate[i]));
+            yr[i] = (gate[i] * sg) * value[i];
+        }
+    }
+}
+
 /* ------------------------------------------------------------------ */
 
 /* N-sharded W4A16: shard s holds a compact [K/2, n_shard] packed slab, its

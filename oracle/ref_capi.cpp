@@ -9,13 +9,16 @@
 #include <cstdint>
 #include <cstring>
 
+#include "kernels/activation.hpp"
 #include "kernels/dtypes.hpp"
 #include "kernels/gemm.hpp"
 #include "kernels/gemm_quant.hpp"
 #include "kernels/kvcache.hpp"
 #include "kernels/kvcache_quant.hpp"
+#include "kernels/normalization.hpp"
 #include "kernels/paged_attention.hpp"
 #include "kernels/quant.hpp"
+#include "kernels/rope.hpp"
 #include "runtime/cache_manager.hpp"
 
 #ifdef _OPENMP
@@ -147,6 +150,15 @@ LHR_API void lhr_paged_attention_f32_batched(const float* Q, const float* kp, co
 
 // --- bench harness: independent calls of the unmodified functions spread over
 // --- host threads (the reference's kernels contain no parallel region).
+
+LHR_API void lhr_rmsnorm(const float* x, const float* gamma, float* y, int rows, int dim, float eps) {
+    lh::rmsnorm(x, gamma, y, rows, dim, eps);
+}
+LHR_API void lhr_rope(float* x, int seq, int n_heads, int head_dim, float theta_base, float freq_scale,
+                      int interleaved, int pos_offset) {
+    lh::rope(x, seq, n_heads, head_dim, theta_base, freq_scale, interleaved != 0, pos_offset);
+}
+LHR_API void lhr_swiglu(const float* x, float* y, int rows, int dim) { lh::swiglu(x, y, rows, dim); }
 
 LHR_API void lhr_par_gemm_w4a16_shards(const float* A, const uint8_t* const* Bp, const float* const* Bs,
                                        float* const* C, int M, int n_shard, int K, int G, float alpha,

@@ -1,7 +1,8 @@
 // The reference's unit tests for the quantized decode path, re-expressed
 // against the GPU drop-in (include/lh_dropin): same shapes, seeds, call
 // sequences and acceptance bounds as tests/test_quant.cpp,
-// tests/test_gemm_quant.cpp and tests/test_kvcache_quant.cpp of the reference,
+// tests/test_gemm_quant.cpp, tests/test_kvcache_quant.cpp and (RMSNorm, RoPE, SwiGLU cases)
+// tests/test_normalization.cpp, tests/test_rope.cpp, tests/test_activation.cpp of the reference,
 // with all-host buffers, exactly as code written for the reference calls them.
 // Own minimal harness (the reference uses GoogleTest).
 #include <cmath>
@@ -10,10 +11,13 @@
 #include <random>
 #include <vector>
 
+#include "kernels/activation.hpp"
 #include "kernels/gemm_quant.hpp"
 #include "kernels/kvcache_quant.hpp"
+#include "kernels/normalization.hpp"
 #include "kernels/paged_attention.hpp"
 #include "kernels/quant.hpp"
+#include "kernels/rope.hpp"
 
 static int g_fail = 0, g_checks = 0;
 #define EXPECT(cond)                                                        \
@@ -181,11 +185,76 @@ static void kv_quant() {
     }
 }
 
+// RmsNorm.MatchesReference (17 x 96), Rope.* (12x4x64 interleaved, 9x3x48 half rotation with
+// scale 0.5 and offset 2, norm preservation on 5x2x32) and Activation.SwiGLU (7 x 32), each
+// against the plain loop the reference's *_ref function or test body spells out.
+static void decode_glue() {
+    {
+        const int rows = 17, dim = 96;
+        auto x = random_vector(rows * dim, 121, -4.0f, 4.0f);
+        auto g = random_vector(dim, 122);
+        std::vector<float> y(rows * dim);
+        lh::rmsnorm(x.data(), g.data(), y.data(), rows, dim);
+        for (int r = 0; r < rows; ++r) {
+            float ss = 0.0f;
+            for (int i = 0; i < dim; ++i) ss += x[r * dim + i] * x[r * dim + i];
+            const float inv = 1.0f / std::sqrt(ss / dim + 1e-5f);
+            for (int i = 0; i < dim; ++i)
+                EXPECT(std::fabs(y[r * dim + i] - x[r * dim + i] * inv * g[i]) <= 1e-5f + 1e-5f * std::fabs(y[r * dim + i]));
+        }
+    }
+    auto rope_loop = [](std::vector<float>& v, int seq, int n_heads, int hd, float theta, float fs, bool inter, int off) {
+        const int half = hd / 2;
+        for (int s = 0; s < seq; ++s)
+            for (int h = 0; h < n_heads; ++h)
+                for (int i = 0; i < half; ++i) {
+                    const float ang = static_cast<float>(off + s) * fs * (1.0f / std::pow(theta, static_cast<float>(2 * i) / hd));
+                    const float c = std::cos(ang), sn = std::sin(ang);
+                    float* p = v.data() + (static_cast<size_t>(s) * n_heads + h) * hd;
+                    const int ia = inter ? 2 * i : i, ib = inter ? 2 * i + 1 : i + half;
+                    const float a = p[ia], b = p[ib];
+                    p[ia] = a * c - b * sn;
+                    p[ib] = inter ? a * sn + b * c : b * c + a * sn;
+                }
+    };
+    for (int variant = 0; variant < 2; ++variant) {
+        const int seq = variant ? 9 : 12, n_heads = variant ? 3 : 4, hd = variant ? 48 : 64;
+        auto base = random_vector(seq * n_heads * hd, 501 + variant);
+        auto x = base, want = base;
+        lh::rope(x.data(), seq, n_heads, hd, 10000.0f, variant ? 0.5f : 1.0f, variant == 0, variant ? 2 : 0);
+        rope_loop(want, seq, n_heads, hd, 10000.0f, variant ? 0.5f : 1.0f, variant == 0, variant ? 2 : 0);
+        for (size_t i = 0; i < x.size(); ++i) EXPECT(std::fabs(x[i] - want[i]) <= 1e-5f + 1e-5f * std::fabs(want[i]));
+    }
+    {
+        const int seq = 5, n_heads = 2, hd = 32;
+        auto base = random_vector(seq * n_heads * hd, 503);
+        auto x = base;
+        lh::rope(x.data(), seq, n_heads, hd);
+        for (size_t i = 0; i < base.size(); i += 2) {
+            const double n0 = base[i] * base[i] + base[i + 1] * base[i + 1];
+            const double n1 = x[i] * x[i] + x[i + 1] * x[i + 1];
+            EXPECT(std::fabs(n0 - n1) <= 1e-3);
+        }
+    }
+    {
+        const int rows = 7, dim = 32;
+        auto x = random_vector(rows * 2 * dim, 203, -4.0f, 4.0f);
+        std::vector<float> y(rows * dim);
+        lh::swiglu(x.data(), y.data(), rows, dim);
+        for (int r = 0; r < rows; ++r)
+            for (int i = 0; i < dim; ++i) {
+                const float gate = x[r * 2 * dim + i], val = x[r * 2 * dim + dim + i];
+                EXPECT(std::fabs(y[r * dim + i] - gate / (1.0f + std::exp(-gate)) * val) <= 1e-5f);
+            }
+    }
+}
+
 int main() {
     try {
         quant_round_trips();
         gemm_quant();
         kv_quant();
+        decode_glue();
     } catch (const std::exception& e) {
         std::printf("EXCEPTION: %s\n", e.what());
         return 2;

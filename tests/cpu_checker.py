@@ -165,6 +165,29 @@ class Checker:
                                          _p(out), M, N, K, C.c_float(alpha), C.c_float(beta))
         return out
 
+    # -- decode-step glue ---------------------------------------------------
+    def rmsnorm(self, x, gamma, eps=1e-5):
+        x = np.ascontiguousarray(x, np.float32)
+        rows, dim = x.shape
+        y = np.empty_like(x)
+        self.fn("rmsnorm")(_p(x), _p(gamma, np.float32), _p(y), rows, dim, C.c_float(eps))
+        return y
+
+    def rope(self, x, theta_base=10000.0, freq_scale=1.0, interleaved=True, pos_offset=0):
+        """x: [seq, n_heads, head_dim]; returns the rotated copy."""
+        y = np.ascontiguousarray(x, np.float32).copy()
+        seq, n_heads, head_dim = y.shape
+        self.fn("rope")(_p(y), seq, n_heads, head_dim, C.c_float(theta_base), C.c_float(freq_scale),
+                        int(bool(interleaved)), int(pos_offset))
+        return y
+
+    def swiglu(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        rows, dim2 = x.shape
+        y = np.empty((rows, dim2 // 2), np.float32)
+        self.fn("swiglu")(_p(x), _p(y), rows, dim2 // 2)
+        return y
+
     # -- paged KV -----------------------------------------------------------
     @staticmethod
     def empty_pools_q8(L: Layout) -> PagedPools:

@@ -192,5 +192,40 @@ def main():
     print("wrote cache_manager_trace", log)
 
 
+def glue_fixtures():
+    """RMSNorm / RoPE / SwiGLU (src/kernels/normalization.cpp, rope.cpp, activation.cpp); shapes
+    follow tests/test_normalization.cpp, tests/test_rope.cpp and tests/test_activation.cpp plus
+    the decode-step sizes (dim 4096, head_dim 128, theta 500000, position 2047)."""
+    if not ref_available():
+        raise SystemExit("oracle/_ref/liblh_ref.so missing: run `make -C oracle ref` first")
+    ref = Checker("lhr")
+    rng = np.random.default_rng(20244)
+    x = uniform(rng, (5, 96), -3, 3)
+    x[2] = 0.0                                   # zero row: y = 0, inv_rms = 1/sqrt(eps)
+    x[3] *= 1e3
+    g = uniform(rng, 96, 0.5, 1.5)
+    save("rmsnorm_r5d96", x=x, gamma=g, eps=np.float32(1e-5), y=ref.rmsnorm(x, g, 1e-5))
+    x = rng.standard_normal((3, 4096)).astype(np.float32)
+    g = uniform(rng, 4096, 0.5, 1.5)
+    save("rmsnorm_r3d4096", x=x, gamma=g, eps=np.float32(1e-6), y=ref.rmsnorm(x, g, 1e-6))
+    for name, inter, theta, fs, off, shape in [
+            ("rope_interleaved", True, 10000.0, 1.0, 0, (6, 2, 16)),
+            ("rope_half_offset", False, 10000.0, 1.0, 37, (4, 3, 32)),
+            ("rope_half_llama3", False, 500000.0, 1.0, 2047, (2, 8, 128)),
+            ("rope_scaled", True, 10000.0, 0.25, 5, (3, 2, 64))]:
+        x = rng.standard_normal(shape).astype(np.float32)
+        save(name, x=x, theta=np.float32(theta), freq_scale=np.float32(fs), interleaved=np.int32(inter),
+             pos_offset=np.int32(off), y=ref.rope(x, theta, fs, inter, off))
+    x = (rng.standard_normal((4, 2 * 50)) * 4).astype(np.float32)
+    x[0, :4] = [0.0, -30.0, 30.0, -100.0]        # sigmoid tails
+    save("swiglu_r4d50", x=x, y=ref.swiglu(x))
+    x = rng.standard_normal((2, 2 * 1024)).astype(np.float32)
+    save("swiglu_r2d1024", x=x, y=ref.swiglu(x))
+
+
 if __name__ == "__main__":
-    main()
+    if "--glue" in sys.argv:        # only the decode-step glue fixtures (the others stay as they are)
+        glue_fixtures()
+    else:
+        main()
+        glue_fixtures()

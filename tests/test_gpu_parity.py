@@ -408,3 +408,53 @@ def test_device_cache_manager_end_to_end(chk):
     torch.cuda.synchronize()
     assert (host(tables)[ids[1]] == -1).all() and host(seq_lens)[ids[1]] == 0
     cm.close()
+
+
+# --------------------------------------------------------------------------- decode-step glue
+
+@pytest.mark.parametrize("name", gio.names("rmsnorm_"))
+def test_rmsnorm_golden(name):
+    g = gio.load(name)
+    y = lb.rmsnorm(dev(g["x"]), dev(g["gamma"]), float(g["eps"]))
+    assert_close(host(y), g["y"], what=name)
+
+
+@pytest.mark.parametrize("rows,dim", [(1, 4096), (32, 4096), (7, 14336), (3, 1001)])
+def test_rmsnorm_against_checker(chk, rows, dim):
+    rng = np.random.default_rng(rows + dim)
+    x = (rng.standard_normal((rows, dim)) * rng.choice([1e-2, 1.0, 50.0])).astype(np.float32)
+    gamma = rng.uniform(0.5, 1.5, dim).astype(np.float32)
+    assert_close(host(lb.rmsnorm(dev(x), dev(gamma), 1e-5)), chk.rmsnorm(x, gamma, 1e-5), what=f"rmsnorm {rows}x{dim}")
+
+
+@pytest.mark.parametrize("name", gio.names("rope_"))
+def test_rope_golden(name):
+    g = gio.load(name)
+    y = lb.rope(dev(g["x"]), float(g["theta"]), float(g["freq_scale"]), bool(g["interleaved"]), int(g["pos_offset"]))
+    assert_close(host(y), g["y"], what=name)
+
+
+@pytest.mark.parametrize("interleaved", [True, False])
+def test_rope_decode_batch_equals_per_request_calls(chk, interleaved):
+    """One token per request at its own position = the reference called once per request with
+    seq = 1 and pos_offset = that position (Llama-3 sizes: 32 + 8 heads of 128, theta 500000)."""
+    rng = np.random.default_rng(17)
+    n_req, n_heads, hd = 9, 40, 128
+    x = rng.standard_normal((n_req, n_heads, hd)).astype(np.float32)
+    pos = rng.integers(0, 8192, n_req).astype(np.int32)
+    want = np.stack([chk.rope(x[r:r + 1], 500000.0, 1.0, interleaved, int(pos[r]))[0] for r in range(n_req)])
+    got = lb.rope_decode_batched(dev(x), dev(pos), 500000.0, 1.0, interleaved)
+    assert_close(host(got), want, what="rope decode batch")
+
+
+@pytest.mark.parametrize("name", gio.names("swiglu_"))
+def test_swiglu_golden(name):
+    g = gio.load(name)
+    assert_close(host(lb.swiglu(dev(g["x"]))), g["y"], what=name)
+
+
+@pytest.mark.parametrize("rows,dim", [(1, 14336), (32, 14336), (5, 1003)])
+def test_swiglu_against_checker(chk, rows, dim):
+    rng = np.random.default_rng(rows * 3 + dim)
+    x = (rng.standard_normal((rows, 2 * dim)) * 3).astype(np.float32)
+    assert_close(host(lb.swiglu(dev(x))), chk.swiglu(x), what=f"swiglu {rows}x{dim}")

@@ -108,6 +108,40 @@ def test_attention_golden(name):
 
 
 @pytest.mark.skipif(not ref_available(), reason="compiled reference not present")
+@pytest.mark.parametrize("name", gio.names("rmsnorm_"))
+def test_rmsnorm_golden(name):
+    g = gio.load(name)
+    y = port.rmsnorm(g["x"], g["gamma"], float(g["eps"]))
+    same(y, g["y"])
+    # invariant of the reference's own test: unit gamma gives rows of RMS one
+    u = port.rmsnorm(g["x"], np.ones_like(g["gamma"]), 0.0)
+    rms = np.sqrt((u.astype(np.float64) ** 2).mean(axis=1))
+    nz = np.abs(g["x"]).max(axis=1) > 0
+    assert np.allclose(rms[nz], 1.0, atol=1e-5)
+
+
+@pytest.mark.parametrize("name", gio.names("rope_"))
+def test_rope_golden(name):
+    g = gio.load(name)
+    args = (float(g["theta"]), float(g["freq_scale"]), bool(g["interleaved"]), int(g["pos_offset"]))
+    y = port.rope(g["x"], *args)
+    same(y, g["y"])
+    # a rotation keeps every pair's norm; position 0 without offset is the identity
+    assert np.allclose((y.astype(np.float64) ** 2).sum(-1), (g["x"].astype(np.float64) ** 2).sum(-1), rtol=1e-5)
+    if int(g["pos_offset"]) == 0:
+        assert np.array_equal(y[0], g["x"][0])
+    # one token at position p equals row p of the sequence call
+    seq = g["x"].shape[0]
+    one = port.rope(g["x"][seq - 1:seq], args[0], args[1], args[2], args[3] + seq - 1)
+    same(one[0], y[seq - 1])
+
+
+@pytest.mark.parametrize("name", gio.names("swiglu_"))
+def test_swiglu_golden(name):
+    g = gio.load(name)
+    same(port.swiglu(g["x"]), g["y"])
+
+
 def test_port_matches_compiled_reference_on_larger_inputs():
     ref = Checker("lhr")
     rng = np.random.default_rng(7)
