@@ -62,11 +62,15 @@ constexpr int GV_ROWS = 64;         // byte-rows per stage
 constexpr int GV_BOX_BYTES = GV_BOX_COLS * GV_ROWS;
 constexpr int GV_STAGE_BYTES = GV_BOX_BYTES * GV_BOXES;
 constexpr int GV_MAX_STAGE = 8;     // ring depth is chosen per launch (2..8) from the shared-memory budget
-constexpr int GV_CONSUMER_WARPS = 8;
-constexpr int GV_CONSUMERS = GV_CONSUMER_WARPS * 32;
-constexpr int GV_THREADS = GV_CONSUMERS + 32;     // + one producer warp
+constexpr int GV_COL_WARPS = 8;                   // consumer warps across the 256 columns of a tile
+// For M > 8 two groups of column warps share a tile: both unpack the same weights, each
+// feeds half of the activation digit columns (half the accumulators per warp, twice the
+// warps in flight).
+constexpr int gv_groups(int jb) { return jb >= 6 ? 2 : 1; }
+constexpr int gv_consumer_warps(int jb) { return GV_COL_WARPS * gv_groups(jb); }
+constexpr int gv_threads(int jb) { return (gv_consumer_warps(jb) + 1) * 32; }   // + one producer warp
 constexpr int GV_MAX_M = 16;
-constexpr size_t GV_DIG_BYTES = size_t(2) << 20;   // head of the scratch arena: activation digits + 16 row factors
+constexpr size_t GV_DIG_BYTES = size_t(4) << 20;   // head of the scratch arena: activation digits (four slabs) + 64 row factors
 constexpr int GV_PB = 8;           // activation float4 loads a thread keeps in flight in the prologue
 
 using ptx::smem_u32;
@@ -87,8 +91,9 @@ __device__ __forceinline__ void mma_s8_16832(int (&c)[4], uint32_t a0, uint32_t 
 }
 
 // barrier among the consumer warps only (the producer warp never joins it)
+template <int CONSUMERS>
 __device__ __forceinline__ void consumer_sync() {
-    asm volatile("bar.sync 1, %0;" ::"n"(GV_CONSUMERS) : "memory");
+    asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS) : "memory");
 }
 
 // exact int32 -> fp32 for |v| < 2^22 without the conversion pipe
@@ -156,20 +161,28 @@ __device__ __forceinline__ void write_digits(uint8_t* base, int kin, float4 v, f
     }
 }
 
+__host__ __device__ constexpr int gv_jb_for(int M) { return M <= 2 ? 1 : (M <= 5 ? 2 : (M <= 8 ? 3 : 6)); }
+
 // Digits of the whole activation matrix, once per GEMM call with M > 2 (for M <= 2 every
 // GEMV CTA makes the digits of its own K-range, which costs less than a launch).  One CTA
 // per row: row maximum, power-of-two factor, then the three digit columns of the row in
-// the operand order of gemv_mma_kernel, [K/32 blocks][nj columns][32 bytes]; k >= K is
-// written as zero up to k_pad.
+// the operand order of gemv_mma_kernel.  Rows are served in slabs of 16; slab s owns
+// `slab_bytes` of the array, laid out [K/32 blocks][nj columns][32 bytes] with nj = 8 * JB
+// of that slab's launch; k >= K is written as zero up to k_pad.
 template <int WBITS>
 __global__ void __launch_bounds__(1024)
-gemv_digits_kernel(const float* __restrict__ A, int K, int k_pad, int nj, uint8_t* __restrict__ digits,
-                   float* __restrict__ inv_scale) {
+gemv_digits_kernel(const float* __restrict__ A, int M, int K, int k_pad, size_t slab_bytes,
+                   uint8_t* __restrict__ digits, float* __restrict__ inv_scale) {
     __shared__ unsigned s_max[32];
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");      // A may come from the kernel before; so may readers of `digits`
-    const int m = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const float* row = A + static_cast<int64_t>(m) * K;
+    const int row_g = blockIdx.x, slab = row_g / GV_MAX_M, m = row_g % GV_MAX_M;
+    const int jb = gv_jb_for(min(GV_MAX_M, M - slab * GV_MAX_M));
+    if (jb == 1) return;                                    // a slab of one or two rows makes its own digits
+    const int nj = 8 * jb;
+    digits += slab * slab_bytes;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float* row = A + static_cast<int64_t>(row_g) * K;
     float mx = 0.0f;
     for (int k = threadIdx.x * 4; k < K; k += 4096) {
         const float4 v = *reinterpret_cast<const float4*>(row + k);
@@ -185,7 +198,7 @@ gemv_digits_kernel(const float* __restrict__ A, int K, int k_pad, int nj, uint8_
     int se = mb ? 273 - static_cast<int>((mb >> 23) & 0xff) : 127;
     se = max(1, min(253, se));
     const float scl = __uint_as_float(static_cast<uint32_t>(se) << 23);
-    if (threadIdx.x == 0) inv_scale[m] = __uint_as_float(static_cast<uint32_t>(254 - se) << 23);
+    if (threadIdx.x == 0) inv_scale[row_g] = __uint_as_float(static_cast<uint32_t>(254 - se) << 23);
     for (int k = threadIdx.x * 4; k < k_pad; k += 4096) {
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
         if (k < K) v = *reinterpret_cast<const float4*>(row + k);
@@ -216,13 +229,17 @@ struct GemvParams {
 // WBITS: 4 or 8.  JB: number of 8-column activation blocks; 3 digit columns per
 // row of A, so M <= (8 * JB) / 3.
 template <int WBITS, int JB>
-__global__ void __launch_bounds__(GV_THREADS, (JB >= 6) ? 1 : 2)
+__global__ void __launch_bounds__(gv_threads(JB), (JB >= 6) ? 1 : 2)
 gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ TensorMap tmS, const GemvParams p) {
     constexpr int K_PER_ROW = (WBITS == 4) ? 2 : 1;
     constexpr int KPS = GV_ROWS * K_PER_ROW;              // k per stage: 128 (W4), 64 (W8)
     constexpr int KPS_SHIFT = (WBITS == 4) ? 7 : 6;
     constexpr int KB = KPS / 32;                          // k32 blocks per stage: 4 (W4), 2 (W8)
     constexpr int NJ = 8 * JB;                            // digit columns
+    constexpr int GV_CONSUMER_WARPS = gv_consumer_warps(JB);
+    constexpr int GV_CONSUMERS = GV_CONSUMER_WARPS * 32;
+    constexpr int GV_THREADS = gv_threads(JB);
+    constexpr int JBL = JB / gv_groups(JB);               // digit blocks of one consumer warp
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -388,11 +405,13 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ T
     GV_STAMP(2);
 
     if (warp < GV_CONSUMER_WARPS) {
-        // A warp owns two 16-column fragments f = 0, 1: columns 32*warp + 16*f .. +15 of
-        // the tile, i.e. 16-byte chunks 2*(warp%4) + f of box warp/4.
+        // A warp owns two 16-column fragments f = 0, 1: columns 32*cw + 16*f .. +15 of the
+        // tile (cw = its column-warp index), i.e. 16-byte chunks 2*(cw%4) + f of box cw/4,
+        // and the digit blocks jb0 .. jb0 + JBL - 1 of its group.
         const int g = lane >> 2, t = lane & 3;
-        const int box = warp >> 2, chunk0 = (warp & 3) * 2;
-        const int wcol = warp * 32 + 2 * g;                 // + 16*f: this thread's column pair in the tile
+        const int cw = warp & (GV_COL_WARPS - 1), jb0 = (warp / GV_COL_WARPS) * JBL;
+        const int box = cw >> 2, chunk0 = (cw & 3) * 2;
+        const int wcol = cw * 32 + 2 * g;                   // + 16*f: this thread's column pair in the tile
         const int lrow = lane & 7, lmat = lane >> 3;
         // ldmatrix source of this lane inside a stage, per half (32 byte-rows) and fragment
         uint32_t ldoff[2][2];
@@ -403,16 +422,16 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ T
             for (int f = 0; f < 2; ++f)
                 ldoff[half][f] = box * GV_BOX_BYTES + row * 128 + (((chunk0 + f) ^ (row & 7)) << 4);
         }
-        const uint8_t* dlane = dfrag + g * 32 + t * 8;      // + ((digit stage * KB + kb) * NJ + jb * 8) * 32
+        const uint8_t* dlane = dfrag + (jb0 * 8 + g) * 32 + t * 8;     // + ((digit stage * KB + kb) * NJ + jb * 8) * 32
         const uint32_t tiles0 = smem_u32(tiles);
 
-        float out[2][JB][4];
-        int acc[2][JB][4];
+        float out[2][JBL][4];
+        int acc[2][JBL][4];
         auto clear = [&]() {
 #pragma unroll
             for (int f = 0; f < 2; ++f)
 #pragma unroll
-                for (int jb = 0; jb < JB; ++jb)
+                for (int jb = 0; jb < JBL; ++jb)
 #pragma unroll
                     for (int i = 0; i < 4; ++i) { out[f][jb][i] = 0.0f; acc[f][jb][i] = 0; }
         };
@@ -426,7 +445,7 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ T
                     s0 = sv.x; s1 = sv.y;
                 }
 #pragma unroll
-                for (int jb = 0; jb < JB; ++jb) {
+                for (int jb = 0; jb < JBL; ++jb) {
                     out[f][jb][0] = fmaf(s0, small_int_to_float(acc[f][jb][0]), out[f][jb][0]);
                     out[f][jb][1] = fmaf(s0, small_int_to_float(acc[f][jb][1]), out[f][jb][1]);
                     out[f][jb][2] = fmaf(s1, small_int_to_float(acc[f][jb][2]), out[f][jb][2]);
@@ -438,7 +457,7 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ T
         // one k32-block: the activation fragment is loaded once and feeds both column fragments
         auto mma_block = [&](const uint8_t* dblk, const uint32_t (&a)[2][4]) {
 #pragma unroll
-            for (int jb = 0; jb < JB; ++jb) {
+            for (int jb = 0; jb < JBL; ++jb) {
                 const uint2 b = *reinterpret_cast<const uint2*>(dblk + jb * 8 * 32);
                 mma_s8_16832(acc[0][jb], a[0][0], a[0][1], a[0][2], a[0][3], b.x, b.y);
                 mma_s8_16832(acc[1][jb], a[1][0], a[1][1], a[1][2], a[1][3], b.x, b.y);
@@ -522,13 +541,13 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ T
                     c1 = (n_a + 1 < p.N) ? p.scales[n_a + 1] : 0.0f;
                 }
 #pragma unroll
-                for (int jb = 0; jb < JB; ++jb) {
-                    float* d = part + (jb * 8 + 2 * t) * GV_COLS + wcol + 16 * f;
+                for (int jb = 0; jb < JBL; ++jb) {
+                    float* d = part + ((jb0 + jb) * 8 + 2 * t) * GV_COLS + wcol + 16 * f;
                     *reinterpret_cast<float2*>(d) = make_float2(c0 * out[f][jb][0], c1 * out[f][jb][2]);
                     *reinterpret_cast<float2*>(d + GV_COLS) = make_float2(c0 * out[f][jb][1], c1 * out[f][jb][3]);
                 }
             }
-            consumer_sync();
+            consumer_sync<GV_CONSUMERS>();
 
             const bool whole = (s_begin == 0 && s_end == S);       // this segment is all of K
             const int col0 = tile * GV_COLS;
@@ -572,7 +591,7 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ T
             }
             if (!whole) {
                 // the last contributor to arrive sums the partials in contributor order and writes C
-                consumer_sync();
+                consumer_sync<GV_CONSUMERS>();
                 GV_STAMP(4);
                 // One thread fences for the CTA on either side of the count (a fence per thread
                 // costs microseconds here): the barrier before orders every consumer's partial
@@ -585,7 +604,7 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ T
                     if (old == n_contrib - 1) p.counters[tile] = 0;    // ready for the next call
                     __threadfence();
                 }
-                consumer_sync();
+                consumer_sync<GV_CONSUMERS>();
                 GV_STAMP(5);
                 if (flags[1]) {
                     for (int i = threadIdx.x; i < p.M * (GV_COLS / 4); i += GV_CONSUMERS) {
@@ -608,7 +627,7 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ T
                     }
                 }
             }
-            consumer_sync();                                // `part` and flags[1] are free again
+            consumer_sync<GV_CONSUMERS>();                                // `part` and flags[1] are free again
             GV_STAMP(6);
             u += s_end - s_begin;
             s_begin = 0;
@@ -693,7 +712,7 @@ static GemvPlan plan_gemv(int wbits, int jb, int N, int K, int G, int sm_count) 
     return pl;
 }
 
-static int jb_for(int M) { return M <= 2 ? 1 : (M <= 5 ? 2 : (M <= 8 ? 3 : 6)); }
+static int jb_for(int M) { return gv_jb_for(M); }
 
 bool w4a16_fast_ok(int M, int N, int K, int G) {
     if (M < 1 || (N % 16) != 0 || (K % 32) != 0 || G <= 0 || (K % G) != 0) return false;
@@ -724,8 +743,6 @@ static int launch_gemv_t(lhb_ctx* ctx, const TensorMap& tm, const TensorMap& tms
     p.flush_mask = pl.flush_mask;
     p.max_contrib = pl.max_contrib;
     p.partial = reinterpret_cast<float*>(static_cast<uint8_t*>(ctx->scratch) + GV_DIG_BYTES);
-    p.digits = static_cast<const uint8_t*>(ctx->scratch);
-    p.inv_scale = reinterpret_cast<const float*>(static_cast<uint8_t*>(ctx->scratch) + GV_DIG_BYTES - 256);
     p.counters = ctx->counters;
     p.status = ctx->status_word;
 #ifdef LHB_GEMV_TRACE
@@ -734,7 +751,7 @@ static int launch_gemv_t(lhb_ctx* ctx, const TensorMap& tm, const TensorMap& tms
 #endif
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(pl.ctas, 1, 1);
-    cfg.blockDim = dim3(GV_THREADS, 1, 1);
+    cfg.blockDim = dim3(gv_threads(JB), 1, 1);
     cfg.dynamicSmemBytes = pl.smem;
     cfg.stream = st;
     static const bool pdl = !(getenv("LHB_PDL") && atoi(getenv("LHB_PDL")) == 0);
@@ -759,6 +776,26 @@ static int launch_gemv(lhb_ctx* ctx, const float* A, const void* B, const float*
     if (int e = get_tensor_map_2d_u8(ctx, B, rows, N, N, GV_ROWS, GV_BOX_COLS, true, &tm)) return e;
     tms = tm;                                     // W8 has no scale tiles; the kernel never uses the map
     // rows of A are independent: M > 16 is served in slabs of 16 rows
+    const int kps_d = GV_ROWS * (WBITS == 4 ? 2 : 1);
+    const int k_pad = ceil_div(K, kps_d) * kps_d;
+    const size_t slab_bytes = static_cast<size_t>(k_pad) * 8 * gv_jb_for(GV_MAX_M);
+    uint8_t* const dig = static_cast<uint8_t*>(ctx->scratch);
+    float* const inv = reinterpret_cast<float*>(dig + GV_DIG_BYTES - 256);
+    if (M > 2) {
+        // digits of every row, once, for all CTAs of the GEMV launches that follow
+        if (ctx->scratch_bytes < GV_DIG_BYTES || slab_bytes * ceil_div(M, GV_MAX_M) > GV_DIG_BYTES - 256)
+            return LHB_ERR_SCRATCH;
+        cudaLaunchConfig_t dc = {};
+        dc.gridDim = dim3(M, 1, 1);
+        dc.blockDim = dim3(1024, 1, 1);
+        dc.stream = st;
+        cudaLaunchAttribute da[1];
+        da[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        da[0].val.programmaticStreamSerializationAllowed = 1;
+        dc.attrs = da;
+        dc.numAttrs = 1;
+        LHB_CUDA(cudaLaunchKernelEx(&dc, gemv_digits_kernel<WBITS>, A, M, K, k_pad, slab_bytes, dig, inv));
+    }
     for (int m0 = 0; m0 < M; m0 += GV_MAX_M) {
         const int m = std::min(GV_MAX_M, M - m0);
         const int jb = jb_for(m);
@@ -769,24 +806,6 @@ static int launch_gemv(lhb_ctx* ctx, const float* A, const void* B, const float*
             static_cast<size_t>(pl.col_tiles) * pl.max_contrib * m * GV_COLS * sizeof(float) >
                 ctx->scratch_bytes - GV_DIG_BYTES)
             return LHB_ERR_SCRATCH;
-        if (jb > 1) {
-            // digits of this slab's rows, once, for every CTA of the GEMV that follows
-            const int kps = GV_ROWS * (WBITS == 4 ? 2 : 1);
-            const int k_pad = pl.S * kps;
-            if (static_cast<size_t>(k_pad) * 8 * jb > GV_DIG_BYTES - 256) return LHB_ERR_SCRATCH;
-            cudaLaunchConfig_t dc = {};
-            dc.gridDim = dim3(m, 1, 1);
-            dc.blockDim = dim3(1024, 1, 1);
-            dc.stream = st;
-            cudaLaunchAttribute da[1];
-            da[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-            da[0].val.programmaticStreamSerializationAllowed = 1;
-            dc.attrs = da;
-            dc.numAttrs = 1;
-            LHB_CUDA(cudaLaunchKernelEx(&dc, gemv_digits_kernel<WBITS>, A + static_cast<int64_t>(m0) * K, K, k_pad,
-                                        8 * jb, static_cast<uint8_t*>(ctx->scratch),
-                                        reinterpret_cast<float*>(static_cast<uint8_t*>(ctx->scratch) + GV_DIG_BYTES - 256)));
-        }
         if (WBITS == 4 && m0 == 0)
             if (int e = get_tensor_map_2d_f32(ctx, scales, K / G, N, static_cast<uint64_t>(N) * 4, pl.srows,
                                               GV_COLS, &tms))
@@ -796,6 +815,8 @@ static int launch_gemv(lhb_ctx* ctx, const float* A, const void* B, const float*
         p.scales = scales;
         p.C = C + static_cast<int64_t>(m0) * N;
         p.M = m; p.N = N; p.K = K; p.G = G; p.alpha = alpha; p.beta = beta;
+        p.digits = dig + (m0 / GV_MAX_M) * slab_bytes;
+        p.inv_scale = inv + m0;
         int e;
         if (jb == 1) e = launch_gemv_t<WBITS, 1>(ctx, tm, tms, p, pl, st);
         else if (jb == 2) e = launch_gemv_t<WBITS, 2>(ctx, tm, tms, p, pl, st);

@@ -5,7 +5,8 @@ library's C-ABI calls, in the order the reference's kernels would be called
 for a pre-norm decoder layer with grouped-query attention and a SwiGLU MLP:
 
     h  = rmsnorm(x)                          src/kernels/normalization.hpp:21
-    q, k, v = h Wq, h Wk, h Wv               gemm_w4a16_groupwise (gemm_quant.hpp:54)
+    q | k | v = h Wqkv                       gemm_w4a16_groupwise (gemm_quant.hpp:54), one GEMM over
+                                             the three projections' columns side by side
     rope(q), rope(k) at each request's position          src/kernels/rope.hpp:19
     append k, v to the int8 paged cache      paged_kv_append_q8 (kvcache_quant.hpp:41)
     o  = paged attention over the cache      paged_attention_q8 (kvcache_quant.hpp:51)
@@ -14,13 +15,16 @@ for a pre-norm decoder layer with grouped-query attention and a SwiGLU MLP:
     x += swiglu(h Wgu) Wdown                 src/kernels/activation.hpp:34; Wgu = gate || up
 
 `x` is fp32 [n_requests, dim], one new token per request.  All seven
-projections are int4 group-wise weights in the reference layout.  Nothing here
+projections are int4 group-wise weights in the reference layout; Wq, Wk, Wv
+are stored as one [dim, q_dim + 2 kv_dim] matrix and gate/up as one
+[dim, 2 ffn] matrix (any column slab of a packed int4 matrix is itself a valid
+weight, so this is only a choice of where the columns live).  Nothing here
 allocates inside the step once `StepBuffers` exists, so a step can be captured
 into a CUDA graph after one eager run.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 import torch
 
@@ -52,9 +56,7 @@ class StepConfig:
 @dataclass
 class LayerWeights:
     """(packed uint8 [K/2, N], fp32 scales [K/G, N]) per projection, plus the two norm gains."""
-    wq: tuple
-    wk: tuple
-    wv: tuple
+    wqkv: tuple         # [dim, q_dim + 2*kv_dim]: q columns, then k, then v
     wo: tuple
     wgu: tuple          # [dim, 2*ffn]: gate columns first, then up ("value") columns
     wdown: tuple
@@ -64,10 +66,17 @@ class LayerWeights:
     @staticmethod
     def quantize(cfg: StepConfig, wq, wk, wv, wo, wgu, wdown, g_attn, g_ffn) -> "LayerWeights":
         q = lambda w: K.q4_quantize_groupwise(w, cfg.group)
-        return LayerWeights(q(wq), q(wk), q(wv), q(wo), q(wgu), q(wdown), g_attn, g_ffn)
+        return LayerWeights(q(torch.cat([wq, wk, wv], dim=1)), q(wo), q(wgu), q(wdown), g_attn, g_ffn)
+
+    @staticmethod
+    def from_quantized(wq, wk, wv, wo, wgu, wdown, g_attn, g_ffn) -> "LayerWeights":
+        """From already quantised (packed, scales) pairs: q, k, v are joined along the columns."""
+        qkv = (torch.cat([wq[0], wk[0], wv[0]], dim=1).contiguous(),
+               torch.cat([wq[1], wk[1], wv[1]], dim=1).contiguous())
+        return LayerWeights(qkv, wo, wgu, wdown, g_attn, g_ffn)
 
     def weight_bytes(self) -> int:
-        return sum(p.numel() + s.numel() * 4 for p, s in (self.wq, self.wk, self.wv, self.wo, self.wgu, self.wdown))
+        return sum(p.numel() + s.numel() * 4 for p, s in (self.wqkv, self.wo, self.wgu, self.wdown))
 
 
 @dataclass
@@ -91,6 +100,7 @@ class KVPools:
 class StepBuffers:
     """Activations of one layer, reused by every layer of the step."""
     h: torch.Tensor
+    qkv: torch.Tensor
     q: torch.Tensor
     k: torch.Tensor
     v: torch.Tensor
@@ -101,7 +111,7 @@ class StepBuffers:
     @staticmethod
     def allocate(cfg: StepConfig, n_req: int, device) -> "StepBuffers":
         f = lambda n: torch.empty((n_req, n), dtype=torch.float32, device=device)
-        return StepBuffers(f(cfg.dim), f(cfg.q_dim), f(cfg.kv_dim), f(cfg.kv_dim), f(cfg.q_dim),
+        return StepBuffers(f(cfg.dim), f(cfg.q_dim + 2 * cfg.kv_dim), f(cfg.q_dim), f(cfg.kv_dim), f(cfg.kv_dim), f(cfg.q_dim),
                            f(2 * cfg.ffn), f(cfg.ffn))
 
 
@@ -112,9 +122,11 @@ def decode_layer(x, w: LayerWeights, pools: KVPools, block_tables, past_lens, cu
     n_req = x.shape[0]
     G = cfg.group
     K.rmsnorm(x, w.g_attn, cfg.eps, out=buf.h, ctx=ctx)
-    K.gemm_w4a16_groupwise(buf.h, *w.wq, G, C=buf.q, ctx=ctx)
-    K.gemm_w4a16_groupwise(buf.h, *w.wk, G, C=buf.k, ctx=ctx)
-    K.gemm_w4a16_groupwise(buf.h, *w.wv, G, C=buf.v, ctx=ctx)
+    K.gemm_w4a16_groupwise(buf.h, *w.wqkv, G, C=buf.qkv, ctx=ctx)
+    # split the row [q | k | v] into the three contiguous tensors the cache calls take (copies only)
+    buf.q.copy_(buf.qkv[:, :cfg.q_dim])
+    buf.k.copy_(buf.qkv[:, cfg.q_dim:cfg.q_dim + cfg.kv_dim])
+    buf.v.copy_(buf.qkv[:, cfg.q_dim + cfg.kv_dim:])
     K.rope_decode_batched(buf.q.view(n_req, cfg.n_q_heads, cfg.head_dim), past_lens, cfg.rope_theta, 1.0,
                           cfg.rope_interleaved, ctx=ctx)
     K.rope_decode_batched(buf.k.view(n_req, cfg.n_kv_heads, cfg.head_dim), past_lens, cfg.rope_theta, 1.0,
@@ -141,9 +153,9 @@ def decode_step(x, layers, pools, block_tables, past_lens, cur_lens, cfg: StepCo
 
 
 def launches_per_layer(n_req: int) -> int:
-    """Kernel launches of one layer (for the bench's launch count): 2 norms, 2 rotations, append,
-    attention, SwiGLU, and 6 GEMMs each served in slabs of 16 rows, plus one digit pass per slab
-    when a slab has more than two rows."""
+    """This library's kernel launches in one layer (for the bench's launch count): 2 norms,
+    2 rotations, append, attention, SwiGLU, and 4 GEMMs each served in slabs of 16 rows plus one
+    digit pass when there are more than two rows.  (The three q/k/v split copies are torch's.)"""
     slabs = (n_req + 15) // 16
-    per_gemm = slabs * (2 if n_req > 2 else 1)
-    return 7 + 6 * per_gemm
+    per_gemm = slabs + (1 if n_req > 2 else 0)
+    return 7 + 4 * per_gemm

@@ -75,8 +75,9 @@ def test_two_layer_decode_step_matches_cpu_composition():
     # ---- GPU ----
     scfg = ds.StepConfig(cfg["dim"], cfg["n_q_heads"], cfg["n_kv_heads"], cfg["head_dim"], cfg["ffn"], cfg["group"],
                          cfg["theta"], False, cfg["eps"])
-    layers_gpu = [ds.LayerWeights(*[(dev(w[k][0]), dev(w[k][1])) for k in ("wq", "wk", "wv", "wo", "wgu", "wdown")],
-                                  dev(w["g_attn"]), dev(w["g_ffn"])) for w in layers_cpu]
+    layers_gpu = [ds.LayerWeights.from_quantized(
+        *[(dev(w[k][0]), dev(w[k][1])) for k in ("wq", "wk", "wv", "wo", "wgu", "wdown")],
+        dev(w["g_attn"]), dev(w["g_ffn"])) for w in layers_cpu]
     pools_gpu = [ds.KVPools(dev(p.k), dev(p.v), dev(p.ks), dev(p.vs)) for p in pools_cpu]
     x = dev(x0.copy())
     buf = ds.StepBuffers.allocate(scfg, n_req, x.device)
