@@ -108,10 +108,15 @@ LH_DROPIN_API void paged_attention_batched(const float* Q, const float* K_pool, 
                                            const PagedAttnConfig& cfg, const PagedCacheLayout& L);
 
 // -- decode-step glue: src/kernels/normalization.hpp:21, rope.hpp:19-21, activation.hpp:34 ---------
+// Same arguments as lh::rmsnorm / lh::rope / lh::swiglu, in a namespace of their own: the
+// reference's normalization.cpp, rope.cpp and activation.cpp also hold functions outside
+// this path and stay in the build, so these names must not collide with theirs.
+namespace b200 {
 LH_DROPIN_API void rmsnorm(const float* x, const float* gamma, float* y, int rows, int dim, float eps = 1e-5f);
 LH_DROPIN_API void rope(float* x, int seq, int n_heads, int head_dim, float theta_base = 10000.0f,
                         float freq_scale = 1.0f, bool interleaved = true, int pos_offset = 0);
 LH_DROPIN_API void swiglu(const float* x, float* y, int rows, int dim);
+}  // namespace b200
 
 namespace dropin {
 // The CUDA stream device-pointer calls are enqueued on (default: the legacy

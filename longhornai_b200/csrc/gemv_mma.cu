@@ -530,8 +530,11 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ T
             if (WBITS == 8 && unflushed != 0) flush(nullptr);
             GV_STAMP(3);
 
-            // ---- end of a segment: digit columns -> shared memory -> [M, 256] tile ----
-            // per-column partial sums: column j of the operand = digit (j % 3) of row j / 3
+            // ---- end of a segment: digit columns -> [M, 256] tile ----
+            // per-column partial sums: column j of the operand = digit (j % 3) of row j / 3.
+            // M > 2: through shared memory.  M <= 2: the three digits of a row sit in two
+            // neighbouring lanes, so a shuffle brings them together (further down).
+            if constexpr (JB > 1) {
 #pragma unroll
             for (int f = 0; f < 2; ++f) {
                 float c0 = 1.0f, c1 = 1.0f;
@@ -548,6 +551,7 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ T
                 }
             }
             consumer_sync<GV_CONSUMERS>();
+            }
 
             const bool whole = (s_begin == 0 && s_end == S);       // this segment is all of K
             const int col0 = tile * GV_COLS;
@@ -574,6 +578,48 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ T
                 }
                 *cp = v;
             };
+            if constexpr (JB == 1) {
+                // lane t = 0 holds digits 0, 1 of row 0 and gets digit 2 from lane t = 1; lane t = 2
+                // holds digits 1, 2 of row 1 (operand columns 4, 5) and gets digit 0 (column 3)
+                // from lane t = 1.  Values: out[f][0][{0,1}] = column wcol, digit columns 2t, 2t+1;
+                // out[f][0][{2,3}] = column wcol + 1.
+#pragma unroll
+                for (int f = 0; f < 2; ++f) {
+                    float c0 = 1.0f, c1 = 1.0f;
+                    const int cc = wcol + 16 * f;
+                    if (WBITS == 8) {
+                        c0 = (col0 + cc < p.N) ? p.scales[col0 + cc] : 0.0f;
+                        c1 = (col0 + cc + 1 < p.N) ? p.scales[col0 + cc + 1] : 0.0f;
+                    }
+                    const float e0 = out[f][0][0], o0 = out[f][0][1], e1 = out[f][0][2], o1 = out[f][0][3];
+                    const float up_e0 = __shfl_down_sync(0xffffffffu, e0, 1), up_e1 = __shfl_down_sync(0xffffffffu, e1, 1);
+                    const float dn_o0 = __shfl_up_sync(0xffffffffu, o0, 1), dn_o1 = __shfl_up_sync(0xffffffffu, o1, 1);
+                    const int m = t >> 1;                          // t = 0 -> row 0, t = 2 -> row 1
+                    if ((t & 1) == 0 && m < p.M && cc < ncol) {
+                        const float is = inv_s[m] * digit_unit;
+                        float2 v;
+                        if (t == 0) {
+                            v.x = c0 * is * fmaf(16384.0f, e0, fmaf(128.0f, o0, up_e0));
+                            v.y = c1 * is * fmaf(16384.0f, e1, fmaf(128.0f, o1, up_e1));
+                        } else {
+                            v.x = c0 * is * fmaf(16384.0f, dn_o0, fmaf(128.0f, e0, o0));
+                            v.y = c1 * is * fmaf(16384.0f, dn_o1, fmaf(128.0f, e1, o1));
+                        }
+                        if (whole) {
+                            float2* cp = reinterpret_cast<float2*>(p.C + static_cast<int64_t>(m) * p.N + col0 + cc);
+                            if (p.beta == 0.0f) {
+                                v.x *= p.alpha; v.y *= p.alpha;
+                            } else {
+                                const float2 o = *cp;
+                                v.x = fmaf(p.beta, o.x, p.alpha * v.x); v.y = fmaf(p.beta, o.y, p.alpha * v.y);
+                            }
+                            *cp = v;
+                        } else {
+                            *reinterpret_cast<float2*>(my_slot + m * GV_COLS + cc) = v;
+                        }
+                    }
+                }
+            } else
             for (int i = threadIdx.x; i < p.M * (GV_COLS / 4); i += GV_CONSUMERS) {
                 const int m = i >> 6, c = (i & 63) * 4;
                 if (c >= ncol) continue;
@@ -601,8 +647,10 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ T
                     __threadfence();
                     const int old = atomicAdd(p.counters + tile, 1);
                     flags[1] = (old == n_contrib - 1);
-                    if (old == n_contrib - 1) p.counters[tile] = 0;    // ready for the next call
-                    __threadfence();
+                    if (old == n_contrib - 1) {
+                        p.counters[tile] = 0;                          // ready for the next call
+                        __threadfence();                               // only the summing CTA reads the others' stores
+                    }
                 }
                 consumer_sync<GV_CONSUMERS>();
                 GV_STAMP(5);
@@ -698,7 +746,12 @@ static GemvPlan plan_gemv(int wbits, int jb, int N, int K, int G, int sm_count) 
         if (fixed + 2 * stage_bytes + dig_per_stage > budget) return pl;
         const int r_max = static_cast<int>((budget - fixed - 2 * stage_bytes) / dig_per_stage);
         ctas = ceil_div(pl.units, r_max);
-        if (pl.col_tiles <= ctas) ctas = pl.col_tiles * ceil_div(ctas, pl.col_tiles);
+        // more CTAs than the device holds at once: whole waves of equal ranges, so that the
+        // last wave is not a handful of CTAs with everybody else idle
+        const int capacity = per_sm * sm_count;
+        if (ctas > capacity) ctas = static_cast<int>(std::min<int64_t>(units, static_cast<int64_t>(ceil_div(ctas, capacity)) * capacity));
+        else if (pl.col_tiles <= ctas && pl.col_tiles * ceil_div(ctas, pl.col_tiles) <= capacity)
+            ctas = pl.col_tiles * ceil_div(ctas, pl.col_tiles);
         range = ceil_div(pl.units, ctas);
     }
     const size_t dig = dig_per_stage * std::min(pl.S, range);

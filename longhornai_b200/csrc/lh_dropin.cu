@@ -268,6 +268,8 @@ void paged_attention(const float* Q, const float* K_pool, const float* V_pool, c
     paged_attention_batched(Q, K_pool, V_pool, block_table, nb, sl.get(), 1, O, cfg, L);
 }
 
+namespace b200 {
+
 void rmsnorm(const float* x, const float* gamma, float* y, int rows, int dim, float eps) {
     bool any_host = false;
     ARG(float, xi, x, sz(rows, dim), In); ARG(float, g, gamma, sz(dim), In); ARG(float, yo, y, sz(rows, dim), Out);
@@ -290,5 +292,7 @@ void swiglu(const float* x, float* y, int rows, int dim) {
     check(lhb_swiglu(context(), xi.get(), yo.get(), rows, dim, g_stream), "swiglu");
     yo.writeback(); finish(any_host);
 }
+
+}  // namespace b200
 
 }  // namespace lh

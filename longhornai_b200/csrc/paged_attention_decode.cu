@@ -483,8 +483,10 @@ paged_decode_q8_kernel(const DecodeParams p) {
         __threadfence();
         const int old = atomicAdd(p.counters + cidx, 1);
         s_last = (old == nsplit - 1);
-        if (s_last) p.counters[cidx] = 0;              // ready for the next call
-        __threadfence();
+        if (s_last) {
+            p.counters[cidx] = 0;                      // ready for the next call
+            __threadfence();                           // only the merging CTA reads the others' stores
+        }
     }
     __syncthreads();
     if (!s_last) return;

@@ -11,13 +11,10 @@
 #include <random>
 #include <vector>
 
-#include "kernels/activation.hpp"
 #include "kernels/gemm_quant.hpp"
 #include "kernels/kvcache_quant.hpp"
-#include "kernels/normalization.hpp"
 #include "kernels/paged_attention.hpp"
 #include "kernels/quant.hpp"
-#include "kernels/rope.hpp"
 
 static int g_fail = 0, g_checks = 0;
 #define EXPECT(cond)                                                        \
@@ -194,7 +191,7 @@ static void decode_glue() {
         auto x = random_vector(rows * dim, 121, -4.0f, 4.0f);
         auto g = random_vector(dim, 122);
         std::vector<float> y(rows * dim);
-        lh::rmsnorm(x.data(), g.data(), y.data(), rows, dim);
+        lh::b200::rmsnorm(x.data(), g.data(), y.data(), rows, dim);
         for (int r = 0; r < rows; ++r) {
             float ss = 0.0f;
             for (int i = 0; i < dim; ++i) ss += x[r * dim + i] * x[r * dim + i];
@@ -221,7 +218,7 @@ static void decode_glue() {
         const int seq = variant ? 9 : 12, n_heads = variant ? 3 : 4, hd = variant ? 48 : 64;
         auto base = random_vector(seq * n_heads * hd, 501 + variant);
         auto x = base, want = base;
-        lh::rope(x.data(), seq, n_heads, hd, 10000.0f, variant ? 0.5f : 1.0f, variant == 0, variant ? 2 : 0);
+        lh::b200::rope(x.data(), seq, n_heads, hd, 10000.0f, variant ? 0.5f : 1.0f, variant == 0, variant ? 2 : 0);
         rope_loop(want, seq, n_heads, hd, 10000.0f, variant ? 0.5f : 1.0f, variant == 0, variant ? 2 : 0);
         for (size_t i = 0; i < x.size(); ++i) EXPECT(std::fabs(x[i] - want[i]) <= 1e-5f + 1e-5f * std::fabs(want[i]));
     }
@@ -229,7 +226,7 @@ static void decode_glue() {
         const int seq = 5, n_heads = 2, hd = 32;
         auto base = random_vector(seq * n_heads * hd, 503);
         auto x = base;
-        lh::rope(x.data(), seq, n_heads, hd);
+        lh::b200::rope(x.data(), seq, n_heads, hd);
         for (size_t i = 0; i < base.size(); i += 2) {
             const double n0 = base[i] * base[i] + base[i + 1] * base[i + 1];
             const double n1 = x[i] * x[i] + x[i + 1] * x[i + 1];
@@ -240,7 +237,7 @@ static void decode_glue() {
         const int rows = 7, dim = 32;
         auto x = random_vector(rows * 2 * dim, 203, -4.0f, 4.0f);
         std::vector<float> y(rows * dim);
-        lh::swiglu(x.data(), y.data(), rows, dim);
+        lh::b200::swiglu(x.data(), y.data(), rows, dim);
         for (int r = 0; r < rows; ++r)
             for (int i = 0; i < dim; ++i) {
                 const float gate = x[r * 2 * dim + i], val = x[r * 2 * dim + dim + i];
