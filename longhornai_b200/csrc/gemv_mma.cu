@@ -90,6 +90,16 @@ __device__ __forceinline__ void mma_s8_16832(int (&c)[4], uint32_t a0, uint32_t 
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// the same with C = 0: starts a fresh sum without a separate clearing of the accumulators
+__device__ __forceinline__ void mma_s8_16832_first(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                   uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%10,%10,%10,%10};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
 // barrier among the consumer warps only (the producer warp never joins it)
 template <int CONSUMERS>
 __device__ __forceinline__ void consumer_sync() {
@@ -228,7 +238,9 @@ struct GemvParams {
 
 // WBITS: 4 or 8.  JB: number of 8-column activation blocks; 3 digit columns per
 // row of A, so M <= (8 * JB) / 3.
-template <int WBITS, int JB>
+// STAGE_FOLD: W4 with group_size >= 128: the int32 sums are folded exactly once per stage, after
+// its last k32-block, so the first block of a stage starts its sums from zero inside the MMA.
+template <int WBITS, int JB, bool STAGE_FOLD>
 __global__ void __launch_bounds__(gv_threads(JB), (JB >= 6) ? 1 : 2)
 gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ TensorMap tmS, const GemvParams p) {
     constexpr int K_PER_ROW = (WBITS == 4) ? 2 : 1;
@@ -450,17 +462,22 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ T
                     out[f][jb][1] = fmaf(s0, small_int_to_float(acc[f][jb][1]), out[f][jb][1]);
                     out[f][jb][2] = fmaf(s1, small_int_to_float(acc[f][jb][2]), out[f][jb][2]);
                     out[f][jb][3] = fmaf(s1, small_int_to_float(acc[f][jb][3]), out[f][jb][3]);
-                    acc[f][jb][0] = acc[f][jb][1] = acc[f][jb][2] = acc[f][jb][3] = 0;
+                    if (!STAGE_FOLD) acc[f][jb][0] = acc[f][jb][1] = acc[f][jb][2] = acc[f][jb][3] = 0;
                 }
             }
         };
         // one k32-block: the activation fragment is loaded once and feeds both column fragments
-        auto mma_block = [&](const uint8_t* dblk, const uint32_t (&a)[2][4]) {
+        auto mma_block = [&](const uint8_t* dblk, const uint32_t (&a)[2][4], bool first) {
 #pragma unroll
             for (int jb = 0; jb < JBL; ++jb) {
                 const uint2 b = *reinterpret_cast<const uint2*>(dblk + jb * 8 * 32);
-                mma_s8_16832(acc[0][jb], a[0][0], a[0][1], a[0][2], a[0][3], b.x, b.y);
-                mma_s8_16832(acc[1][jb], a[1][0], a[1][1], a[1][2], a[1][3], b.x, b.y);
+                if (first) {
+                    mma_s8_16832_first(acc[0][jb], a[0][0], a[0][1], a[0][2], a[0][3], b.x, b.y);
+                    mma_s8_16832_first(acc[1][jb], a[1][0], a[1][1], a[1][2], a[1][3], b.x, b.y);
+                } else {
+                    mma_s8_16832(acc[0][jb], a[0][0], a[0][1], a[0][2], a[0][3], b.x, b.y);
+                    mma_s8_16832(acc[1][jb], a[1][0], a[1][1], a[1][2], a[1][3], b.x, b.y);
+                }
             }
         };
 
@@ -501,8 +518,10 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ T
                                     a[f][3] = e1 & 0xf0f0f0f0u;
                                 }
                                 const int kb = 2 * half + q;
-                                mma_block(dst + kb * NJ * 32, a);
-                                if (p.flush_mask & (1 << kb)) {
+                                mma_block(dst + kb * NJ * 32, a, STAGE_FOLD && kb == 0);
+                                if (STAGE_FOLD) {
+                                    if (kb == KB - 1) flush(sstage);
+                                } else if (p.flush_mask & (1 << kb)) {
                                     flush(sstage + srow_i * GV_COLS);
                                     ++srow_i;
                                 }
@@ -517,7 +536,7 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ T
                                 a[f][2] = __byte_perm(x[f][2], x[f][3], 0x6420);
                                 a[f][3] = __byte_perm(x[f][2], x[f][3], 0x7531);
                             }
-                            mma_block(dst + half * NJ * 32, a);
+                            mma_block(dst + half * NJ * 32, a, false);
                         }
                     }
                     if (WBITS == 8 && ++unflushed == 4) { unflushed = 0; flush(nullptr); }
@@ -771,19 +790,21 @@ bool w4a16_fast_ok(int M, int N, int K, int G) {
     if (M < 1 || (N % 16) != 0 || (K % 32) != 0 || G <= 0 || (K % G) != 0) return false;
     if (!w4_group_ok(G)) return false;            // groups must tile a 128-k stage, or be whole stages
     if (M > 64) return false;                     // larger M: generic path (dense GEMM territory)
+    if (M > 2 && static_cast<size_t>(ceil_div(K, 128) * 128) * 48 > GV_DIG_BYTES - 256) return false;
     return plan_gemv(4, jb_for(std::min(M, GV_MAX_M)), N, K, G, 148).ok;
 }
 
 bool w8a16_fast_ok(int M, int N, int K) {
     if (M < 1 || (N % 16) != 0 || (K % 32) != 0) return false;
     if (M > 64) return false;
+    if (M > 2 && static_cast<size_t>(ceil_div(K, 64) * 64) * 48 > GV_DIG_BYTES - 256) return false;
     return plan_gemv(8, jb_for(std::min(M, GV_MAX_M)), N, K, 1, 148).ok;
 }
 
-template <int WBITS, int JB>
+template <int WBITS, int JB, bool STAGE_FOLD>
 static int launch_gemv_t(lhb_ctx* ctx, const TensorMap& tm, const TensorMap& tms, GemvParams p,
                          const GemvPlan& pl, cudaStream_t st) {
-    auto kern = gemv_mma_kernel<WBITS, JB>;
+    auto kern = gemv_mma_kernel<WBITS, JB, STAGE_FOLD>;
     static bool attr_set[64] = {};                // per instantiation and device
     if (!attr_set[ctx->device & 63]) {
         LHB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
@@ -834,30 +855,34 @@ static int launch_gemv(lhb_ctx* ctx, const float* A, const void* B, const float*
     const size_t slab_bytes = static_cast<size_t>(k_pad) * 8 * gv_jb_for(GV_MAX_M);
     uint8_t* const dig = static_cast<uint8_t*>(ctx->scratch);
     float* const inv = reinterpret_cast<float*>(dig + GV_DIG_BYTES - 256);
-    if (M > 2) {
-        // digits of every row, once, for all CTAs of the GEMV launches that follow
-        if (ctx->scratch_bytes < GV_DIG_BYTES || slab_bytes * ceil_div(M, GV_MAX_M) > GV_DIG_BYTES - 256)
-            return LHB_ERR_SCRATCH;
-        cudaLaunchConfig_t dc = {};
-        dc.gridDim = dim3(M, 1, 1);
-        dc.blockDim = dim3(1024, 1, 1);
-        dc.stream = st;
-        cudaLaunchAttribute da[1];
-        da[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        da[0].val.programmaticStreamSerializationAllowed = 1;
-        dc.attrs = da;
-        dc.numAttrs = 1;
-        LHB_CUDA(cudaLaunchKernelEx(&dc, gemv_digits_kernel<WBITS>, A, M, K, k_pad, slab_bytes, dig, inv));
-    }
+    // The digit array holds a few slabs at a time (all of them unless K is very long).
+    if (ctx->scratch_bytes < GV_DIG_BYTES || (M > 2 && slab_bytes > GV_DIG_BYTES - 256)) return LHB_ERR_SCRATCH;
+    const int rows_per_pass = M > 2 ? static_cast<int>((GV_DIG_BYTES - 256) / slab_bytes) * GV_MAX_M : M;
+    int pass0 = 0;                                  // first row of the current digit pass
     for (int m0 = 0; m0 < M; m0 += GV_MAX_M) {
+        if (M > 2 && (m0 == 0 || m0 - pass0 >= rows_per_pass)) {
+            // digits of the next rows, once, for all CTAs of the GEMV launches that follow
+            pass0 = m0;
+            const int rows = std::min(rows_per_pass, M - pass0);
+            cudaLaunchConfig_t dc = {};
+            dc.gridDim = dim3(rows, 1, 1);
+            dc.blockDim = dim3(1024, 1, 1);
+            dc.stream = st;
+            cudaLaunchAttribute da[1];
+            da[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            da[0].val.programmaticStreamSerializationAllowed = 1;
+            dc.attrs = da;
+            dc.numAttrs = 1;
+            LHB_CUDA(cudaLaunchKernelEx(&dc, gemv_digits_kernel<WBITS>, A + static_cast<int64_t>(pass0) * K, rows, K,
+                                        k_pad, slab_bytes, dig, inv));
+        }
         const int m = std::min(GV_MAX_M, M - m0);
         const int jb = jb_for(m);
         GemvPlan pl = plan_gemv(WBITS, jb, N, K, WBITS == 4 ? G : 1, ctx->sm_count);
         if (!pl.ok) return LHB_ERR_UNSUPPORTED;
         if (pl.col_tiles > static_cast<int>(ctx->counters_len)) return LHB_ERR_UNSUPPORTED;
-        if (ctx->scratch_bytes < GV_DIG_BYTES ||
-            static_cast<size_t>(pl.col_tiles) * pl.max_contrib * m * GV_COLS * sizeof(float) >
-                ctx->scratch_bytes - GV_DIG_BYTES)
+        if (static_cast<size_t>(pl.col_tiles) * pl.max_contrib * m * GV_COLS * sizeof(float) >
+            ctx->scratch_bytes - GV_DIG_BYTES)
             return LHB_ERR_SCRATCH;
         if (WBITS == 4 && m0 == 0)
             if (int e = get_tensor_map_2d_f32(ctx, scales, K / G, N, static_cast<uint64_t>(N) * 4, pl.srows,
@@ -868,13 +893,20 @@ static int launch_gemv(lhb_ctx* ctx, const float* A, const void* B, const float*
         p.scales = scales;
         p.C = C + static_cast<int64_t>(m0) * N;
         p.M = m; p.N = N; p.K = K; p.G = G; p.alpha = alpha; p.beta = beta;
-        p.digits = dig + (m0 / GV_MAX_M) * slab_bytes;
-        p.inv_scale = inv + m0;
+        p.digits = dig + ((m0 - pass0) / GV_MAX_M) * slab_bytes;
+        p.inv_scale = inv + (m0 - pass0);
         int e;
-        if (jb == 1) e = launch_gemv_t<WBITS, 1>(ctx, tm, tms, p, pl, st);
-        else if (jb == 2) e = launch_gemv_t<WBITS, 2>(ctx, tm, tms, p, pl, st);
-        else if (jb == 3) e = launch_gemv_t<WBITS, 3>(ctx, tm, tms, p, pl, st);
-        else e = launch_gemv_t<WBITS, 6>(ctx, tm, tms, p, pl, st);
+        if (WBITS == 4 && G >= 128) {
+            if (jb == 1) e = launch_gemv_t<WBITS, 1, WBITS == 4>(ctx, tm, tms, p, pl, st);
+            else if (jb == 2) e = launch_gemv_t<WBITS, 2, WBITS == 4>(ctx, tm, tms, p, pl, st);
+            else if (jb == 3) e = launch_gemv_t<WBITS, 3, WBITS == 4>(ctx, tm, tms, p, pl, st);
+            else e = launch_gemv_t<WBITS, 6, WBITS == 4>(ctx, tm, tms, p, pl, st);
+        } else {
+            if (jb == 1) e = launch_gemv_t<WBITS, 1, false>(ctx, tm, tms, p, pl, st);
+            else if (jb == 2) e = launch_gemv_t<WBITS, 2, false>(ctx, tm, tms, p, pl, st);
+            else if (jb == 3) e = launch_gemv_t<WBITS, 3, false>(ctx, tm, tms, p, pl, st);
+            else e = launch_gemv_t<WBITS, 6, false>(ctx, tm, tms, p, pl, st);
+        }
         if (e) return e;
     }
     return LHB_OK;

@@ -45,9 +45,16 @@
 
 namespace lhb {
 
+// Tuning points (overridable at compile time for experiments)
+#ifndef LHB_PD_STAGES
+#define LHB_PD_STAGES 3
+#endif
+#ifndef LHB_PD_MIN_CTAS
+#define LHB_PD_MIN_CTAS 4
+#endif
 constexpr int PD_WARPS = 4;
 constexpr int PD_THREADS = PD_WARPS * 32;
-constexpr int PD_STAGES = 3;
+constexpr int PD_STAGES = LHB_PD_STAGES;
 constexpr int PD_D = 128;
 constexpr int PD_BS = 16;
 constexpr int PD_STAGE_BYTES = 2048 + 2048 + 64 + 64;          // K, V, ks, vs
@@ -154,7 +161,7 @@ struct DecodeParams {
     float scale_log2e;
 };
 
-__global__ void __launch_bounds__(PD_THREADS, 4)
+__global__ void __launch_bounds__(PD_THREADS, LHB_PD_MIN_CTAS)
 paged_decode_q8_kernel(const DecodeParams p) {
     extern __shared__ __align__(128) uint8_t pd_smem[];
     __shared__ int s_last;
