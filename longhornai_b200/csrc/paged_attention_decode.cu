@@ -47,10 +47,10 @@ namespace lhb {
 
 // Tuning points (overridable at compile time for experiments)
 #ifndef LHB_PD_STAGES
-#define LHB_PD_STAGES 3
+#define LHB_PD_STAGES 4
 #endif
 #ifndef LHB_PD_MIN_CTAS
-#define LHB_PD_MIN_CTAS 4
+#define LHB_PD_MIN_CTAS 3
 #endif
 constexpr int PD_WARPS = 4;
 constexpr int PD_THREADS = PD_WARPS * 32;
@@ -542,15 +542,17 @@ paged_decode_q8_kernel(const DecodeParams p) {
     }
 }
 
-// How a request is cut: `pages` pages (16 tokens each) per CTA, hence at most
-// `splits` pieces for the longest request the table can describe.  Sized so that
-// about six CTAs per SM exist if requests are half as long as the table allows,
-// within 8..40 pages per CTA (fewer pages: the per-CTA set-up dominates; more:
-// the last CTAs to finish leave SMs idle).
+// How a request is cut: the longest request the table can describe is cut into `splits`
+// equal pieces of `pages` pages (16 tokens each); shorter requests use fewer pieces.  Sized
+// so that about four CTAs per SM (an SM holds three at a time) would exist if every
+// request were as long as the table, within 16..128 pages per CTA (fewer pages: the per-CTA
+// set-up dominates; more: the last CTAs to finish leave SMs idle).
 static void decode_split_plan(int sm_count, int64_t items, int max_blocks, size_t part_floats_avail, int group,
                               int* splits, int* pages) {
-    int64_t pp = items * max_blocks / (12LL * std::max(1, sm_count));
-    int pg = static_cast<int>(std::max<int64_t>(8, std::min<int64_t>(96, pp)));
+    int target = 4;                                          // CTAs per SM if every request were as long as the table
+    if (const char* e = getenv("LHB_DECODE_TARGET")) target = std::max(1, atoi(e));
+    int64_t pp = items * max_blocks / (static_cast<int64_t>(target) * std::max(1, sm_count));
+    int pg = static_cast<int>(std::max<int64_t>(16, std::min<int64_t>(128, pp)));
     if (const char* e = getenv("LHB_DECODE_PAGES")) pg = std::max(1, atoi(e));
     int sp = std::max(1, std::min(32, ceil_div(max_blocks, pg)));
     if (const char* e = getenv("LHB_DECODE_SPLITS")) sp = std::max(1, std::min(sp, atoi(e)));
@@ -558,7 +560,7 @@ static void decode_split_plan(int sm_count, int64_t items, int max_blocks, size_
     if (sp > 1 && per_split * sp > part_floats_avail)
         sp = static_cast<int>(std::max<size_t>(1, part_floats_avail / per_split));
     *splits = sp;
-    *pages = std::max(pg, ceil_div(max_blocks, sp));       // every page of the longest request is covered
+    *pages = ceil_div(max_blocks, sp);      // equal pieces of the longest request; covers every page of it
 }
 
 bool decode_fast_ok(const lhb_paged_attn_cfg& cfg, const lhb_paged_layout& L) {
