@@ -129,6 +129,8 @@ def cpu_gemv_baseline(budget_s=12.0, M=1):
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     from cpu_checker import best_checker
     chk = best_checker()
+    # all the host cores this process may use, whatever OMP_NUM_THREADS a launcher exported
+    chk.set_threads(len(os.sched_getaffinity(0)))
     threads = chk.max_threads()
     rng = np.random.default_rng(20242)
     W = (rng.standard_normal((K_DIM, N_DIM)) * 0.02).astype(np.float32)
@@ -295,56 +297,86 @@ def bench_extra(torch, lb, steps, warmup, hbm_peak):
     return out
 
 
-def bench_decode_step(torch, lb, steps, warmup, hbm_peak, layers=32, batch=32, ctx_len=2048, seed=20244):
+def bench_decode_step(torch, lb, steps, warmup, hbm_peak, layers=32, batch=32, ctx_len=2048, seed=20244,
+                      rank=0, world=1, dist=None):
     """Fourth BASELINE config: one decode step of a 32-layer Llama-3-8B-shaped stack (d 4096, 32/8 heads of
     128, FFN 14336, RoPE base 500000, RMSNorm), all seven projections int4 group-128, int8 paged KV holding
-    `ctx_len` tokens per sequence, `batch` sequences; the whole step replayed as one CUDA graph."""
+    `ctx_len` tokens per sequence, `batch` sequences; the whole step replayed as one CUDA graph.  With
+    world > 1 the projections are sharded along N and attention by KV head (decode_step.decode_step_tp):
+    every rank generates the same full-size weights from the seed and keeps its column slabs."""
     import numpy as np
     from longhornai_b200 import decode_step as ds
     cfg = ds.StepConfig(4096, 32, 8, 128, 14336, GROUP, 500000.0, False, 1e-5)
+    lc = ds.local_config(cfg, world)
     gen = torch.Generator(device="cuda").manual_seed(seed)
     bs = 16
     blocks_per_req = (ctx_len + 1 + bs - 1) // bs
     num_blocks = batch * blocks_per_req
-    L = lb.PagedLayout(num_blocks, bs, cfg.n_kv_heads, cfg.head_dim)
-    acfg = lb.PagedAttnCfg(cfg.n_q_heads, cfg.n_kv_heads, 1, cfg.head_dim, 1, 0.0, 0, 0)
+    L = lb.PagedLayout(num_blocks, bs, lc.n_kv_heads, cfg.head_dim)
+    acfg = lb.PagedAttnCfg(lc.n_q_heads, lc.n_kv_heads, 1, cfg.head_dim, 1, 0.0, 0, 0)
     rng = np.random.default_rng(seed)
     perm = rng.permutation(num_blocks).astype(np.int32)
     tables = torch.from_numpy(perm.reshape(batch, blocks_per_req).copy()).cuda()
     past = torch.full((batch,), ctx_len, dtype=torch.int32, device="cuda")
     cur = past + 1
+    from longhornai_b200 import sharding as sh
+    hd, grp = cfg.head_dim, cfg.n_q_heads // cfg.n_kv_heads
+    h_lo, h_hi = sh.kv_head_range(cfg.n_kv_heads, rank, world)
+    f_lo, f_hi = sh.column_range(cfg.ffn, rank, world)
+    d_lo, d_hi = sh.column_range(cfg.dim, rank, world)
 
-    def rnd(k, n):
-        return torch.randn(k, n, device="cuda", generator=gen) * 0.02
+    def rnd(k, n, lo, hi):
+        """Columns [lo, hi) of a seeded full [k, n] matrix (every rank draws the same full matrix)."""
+        w = torch.randn(k, n, device="cuda", generator=gen) * 0.02
+        return w[:, lo:hi].contiguous()
     lw, pools = [], []
+    ones = torch.ones(4096, device="cuda")
     for _ in range(layers):
-        lw.append(ds.LayerWeights.quantize(cfg, rnd(4096, 4096), rnd(4096, 1024), rnd(4096, 1024), rnd(4096, 4096),
-                                           rnd(4096, 2 * 14336), rnd(14336, 4096),
-                                           torch.ones(4096, device="cuda"), torch.ones(4096, device="cuda")))
-        shape = (num_blocks, cfg.n_kv_heads, bs, cfg.head_dim)
+        wq = rnd(4096, 4096, h_lo * grp * hd, h_hi * grp * hd)
+        wk = rnd(4096, 1024, h_lo * hd, h_hi * hd)
+        wv = rnd(4096, 1024, h_lo * hd, h_hi * hd)
+        wo = rnd(4096, 4096, d_lo, d_hi)
+        full_gu = torch.randn(4096, 2 * 14336, device="cuda", generator=gen) * 0.02
+        wgu = torch.cat([full_gu[:, f_lo:f_hi], full_gu[:, 14336 + f_lo:14336 + f_hi]], dim=1).contiguous()
+        del full_gu
+        wdown = rnd(14336, 4096, d_lo, d_hi)
+        lw.append(ds.LayerWeights.quantize(lc, wq, wk, wv, wo, wgu, wdown, ones, ones))
+        del wq, wk, wv, wo, wgu, wdown
+        shape = (num_blocks, lc.n_kv_heads, bs, cfg.head_dim)
         pools.append(ds.KVPools(
             torch.randint(-127, 128, shape, dtype=torch.int8, device="cuda", generator=gen),
             torch.randint(-127, 128, shape, dtype=torch.int8, device="cuda", generator=gen),
             torch.rand(shape[:3], device="cuda", generator=gen) * 0.02 + 0.005,
             torch.rand(shape[:3], device="cuda", generator=gen) * 0.02 + 0.005))
-    x0 = torch.randn(batch, 4096, device="cuda", generator=gen)
+    x0 = torch.randn(batch, 4096, device="cuda", generator=torch.Generator(device="cuda").manual_seed(seed + 1))
     x = x0.clone()
-    buf = ds.StepBuffers.allocate(cfg, batch, x.device)
+    if world == 1:
+        buf = ds.StepBuffers.allocate(cfg, batch, x.device)
 
-    def step():
-        x.copy_(x0)                  # every replay starts from the same hidden state
-        ds.decode_step(x, lw, pools, tables, past, cur, cfg, L, acfg, buf)
+        def step():
+            x.copy_(x0)                  # every replay starts from the same hidden state
+            ds.decode_step(x, lw, pools, tables, past, cur, cfg, L, acfg, buf)
+    else:
+        buf = ds.TPBuffers.allocate(cfg, world, batch, x.device)
+
+        def step():
+            x.copy_(x0)
+            ds.decode_step_tp(x, lw, pools, tables, past, cur, cfg, L, acfg, buf, rank, world, dist)
     run, is_graph = graphed(step, torch, GRAPHS)
-    ms = timed(run, steps, warmup, None, torch)
+    ms = timed(run, steps, warmup, dist, torch)
     per = ms / steps * 1e-3
-    wbytes = sum(w.weight_bytes() for w in lw)
+    wbytes = sum(w.weight_bytes() for w in lw) * world
     kvbytes = layers * batch * (ctx_len + 1) * cfg.n_kv_heads * (2 * cfg.head_dim + 8)
     b = wbytes + kvbytes
     finite = bool(torch.isfinite(x).all().item())
-    return {"ms_per_step": per * 1e3, "tok_per_s": batch / per, "GBps": b / per / 1e9,
-            "hbm_frac": b / per / 1e9 / hbm_peak, "bytes": b, "layers": layers, "batch": batch,
-            "ctx_len": ctx_len, "launches_per_step": layers * ds.launches_per_layer(batch) + 1,
-            "graph": int(is_graph), "finite": int(finite)}
+    out = {"ms_per_step": per * 1e3, "tok_per_s": batch / per, "GBps": b / per / 1e9,
+           "hbm_frac_per_gpu": b / per / 1e9 / hbm_peak / world, "bytes": b, "layers": layers, "batch": batch,
+           "ctx_len": ctx_len, "launches_per_step": layers * ds.launches_per_layer(batch) + 1,
+           "graph": int(is_graph), "finite": int(finite), "n_gpus": world}
+    if world > 1:
+        out["sharding"] = (f"projections N/{world}, attention {cfg.n_kv_heads // world} KV heads per rank, "
+                           f"4 all-gathers per layer")
+    return out
 
 
 def bench_w8a8(torch, lb, steps, warmup, M=8192, K=8192, N=28672):
@@ -508,6 +540,16 @@ def run_ours(args):
     if status != 0:
         raise SystemExit(f"device status word = {status}")
 
+    tp_step = None
+    if g > 1 and not args.no_extra:
+        # the fourth workload, tensor-parallel: every rank takes part, rank 0 reports
+        del packed, scales, run_gemvs, run_e2e
+        torch.cuda.empty_cache()
+        try:
+            tp_step = bench_decode_step(torch, lb, min(args.steps, 5), 3, hbm_peak, rank=rank, world=g, dist=dist)
+        except Exception as e:
+            tp_step = {"error": repr(e)}
+
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -549,6 +591,8 @@ def run_ours(args):
             line["extra"] = bench_extra(torch, lb, args.steps, args.warmup, hbm_peak)
         except Exception as e:      # the headline must still be printed
             line["extra"] = {"error": repr(e)}
+    if tp_step is not None:
+        line["extra"] = {"decode_step_cfg4": tp_step}
     if g == 1 and not args.no_cpu:
         try:
             line["cpu_baseline"] = cpu_gemv_baseline()

@@ -116,39 +116,41 @@ class StepBuffers:
 
 
 def decode_layer(x, w: LayerWeights, pools: KVPools, block_tables, past_lens, cur_lens, cfg: StepConfig,
-                 L: PagedLayout, acfg: PagedAttnCfg, buf: StepBuffers, ctx=None):
+                 L: PagedLayout, acfg: PagedAttnCfg, buf: StepBuffers, ctx=None, ops=K):
     """Updates `x` [n_req, dim] in place.  `past_lens` = tokens already cached per request (the new
-    token's position), `cur_lens` = past_lens + 1; both int32 device tensors."""
+    token's position), `cur_lens` = past_lens + 1; both int32 device tensors.  `ops` is the module
+    the kernels are taken from (this package's `kernels`; the CPU tests substitute a stand-in to
+    exercise the composition without a GPU)."""
     n_req = x.shape[0]
     G = cfg.group
-    K.rmsnorm(x, w.g_attn, cfg.eps, out=buf.h, ctx=ctx)
-    K.gemm_w4a16_groupwise(buf.h, *w.wqkv, G, C=buf.qkv, ctx=ctx)
+    ops.rmsnorm(x, w.g_attn, cfg.eps, out=buf.h, ctx=ctx)
+    ops.gemm_w4a16_groupwise(buf.h, *w.wqkv, G, C=buf.qkv, ctx=ctx)
     # split the row [q | k | v] into the three contiguous tensors the cache calls take (copies only)
     buf.q.copy_(buf.qkv[:, :cfg.q_dim])
     buf.k.copy_(buf.qkv[:, cfg.q_dim:cfg.q_dim + cfg.kv_dim])
     buf.v.copy_(buf.qkv[:, cfg.q_dim + cfg.kv_dim:])
-    K.rope_decode_batched(buf.q.view(n_req, cfg.n_q_heads, cfg.head_dim), past_lens, cfg.rope_theta, 1.0,
+    ops.rope_decode_batched(buf.q.view(n_req, cfg.n_q_heads, cfg.head_dim), past_lens, cfg.rope_theta, 1.0,
                           cfg.rope_interleaved, ctx=ctx)
-    K.rope_decode_batched(buf.k.view(n_req, cfg.n_kv_heads, cfg.head_dim), past_lens, cfg.rope_theta, 1.0,
+    ops.rope_decode_batched(buf.k.view(n_req, cfg.n_kv_heads, cfg.head_dim), past_lens, cfg.rope_theta, 1.0,
                           cfg.rope_interleaved, ctx=ctx)
-    K.paged_kv_append_q8_batched(pools.k, pools.v, pools.ks, pools.vs, buf.k, buf.v, block_tables, past_lens, L,
+    ops.paged_kv_append_q8_batched(pools.k, pools.v, pools.ks, pools.vs, buf.k, buf.v, block_tables, past_lens, L,
                                  1, ctx=ctx)
-    K.paged_attention_q8_batched(buf.q.view(n_req, cfg.n_q_heads, 1, cfg.head_dim), pools.k, pools.v, pools.ks,
+    ops.paged_attention_q8_batched(buf.q.view(n_req, cfg.n_q_heads, 1, cfg.head_dim), pools.k, pools.v, pools.ks,
                                  pools.vs, block_tables, cur_lens, acfg, L,
                                  O=buf.o.view(n_req, cfg.n_q_heads, 1, cfg.head_dim), ctx=ctx)
-    K.gemm_w4a16_groupwise(buf.o, *w.wo, G, C=x, alpha=1.0, beta=1.0, ctx=ctx)
-    K.rmsnorm(x, w.g_ffn, cfg.eps, out=buf.h, ctx=ctx)
-    K.gemm_w4a16_groupwise(buf.h, *w.wgu, G, C=buf.gu, ctx=ctx)
-    K.swiglu(buf.gu, out=buf.act, ctx=ctx)
-    K.gemm_w4a16_groupwise(buf.act, *w.wdown, G, C=x, alpha=1.0, beta=1.0, ctx=ctx)
+    ops.gemm_w4a16_groupwise(buf.o, *w.wo, G, C=x, alpha=1.0, beta=1.0, ctx=ctx)
+    ops.rmsnorm(x, w.g_ffn, cfg.eps, out=buf.h, ctx=ctx)
+    ops.gemm_w4a16_groupwise(buf.h, *w.wgu, G, C=buf.gu, ctx=ctx)
+    ops.swiglu(buf.gu, out=buf.act, ctx=ctx)
+    ops.gemm_w4a16_groupwise(buf.act, *w.wdown, G, C=x, alpha=1.0, beta=1.0, ctx=ctx)
     return x
 
 
 def decode_step(x, layers, pools, block_tables, past_lens, cur_lens, cfg: StepConfig, L: PagedLayout,
-                acfg: PagedAttnCfg, buf: StepBuffers, ctx=None):
+                acfg: PagedAttnCfg, buf: StepBuffers, ctx=None, ops=K):
     """All layers in turn; `layers` and `pools` are per-layer lists."""
     for w, kv in zip(layers, pools):
-        decode_layer(x, w, kv, block_tables, past_lens, cur_lens, cfg, L, acfg, buf, ctx=ctx)
+        decode_layer(x, w, kv, block_tables, past_lens, cur_lens, cfg, L, acfg, buf, ctx=ctx, ops=ops)
     return x
 
 
@@ -159,3 +161,114 @@ def launches_per_layer(n_req: int) -> int:
     slabs = (n_req + 15) // 16
     per_gemm = slabs + (1 if n_req > 2 else 0)
     return 7 + 4 * per_gemm
+
+
+# ---- tensor-parallel step: projections sharded along N, attention by KV head ----------------
+
+def shard_layer(w: LayerWeights, cfg: StepConfig, rank: int, world: int) -> LayerWeights:
+    """This rank's column slabs of every projection.  The fused QKV slab keeps the rank's query
+    heads, then its key heads, then its value heads; the gate||up slab keeps the rank's gate
+    columns, then its up columns; o and down keep a plain column slab.  Any 16-aligned column
+    slab of a packed int4 matrix and its scales is itself a valid weight."""
+    from . import sharding as sh
+    hd = cfg.head_dim
+    ql, qh = sh.kv_head_range(cfg.n_kv_heads, rank, world)
+    grp = cfg.n_q_heads // cfg.n_kv_heads
+
+    def cols(pair, ranges):
+        p, s = pair
+        return (torch.cat([p[:, a:b] for a, b in ranges], dim=1).contiguous(),
+                torch.cat([s[:, a:b] for a, b in ranges], dim=1).contiguous())
+    q0, k0, v0 = 0, cfg.q_dim, cfg.q_dim + cfg.kv_dim
+    wqkv = cols(w.wqkv, [(q0 + ql * grp * hd, q0 + qh * grp * hd), (k0 + ql * hd, k0 + qh * hd),
+                         (v0 + ql * hd, v0 + qh * hd)])
+    flo, fhi = sh.column_range(cfg.ffn, rank, world)
+    wgu = cols(w.wgu, [(flo, fhi), (cfg.ffn + flo, cfg.ffn + fhi)])
+    dlo, dhi = sh.column_range(cfg.dim, rank, world)
+    return LayerWeights(wqkv, cols(w.wo, [(dlo, dhi)]), wgu, cols(w.wdown, [(dlo, dhi)]), w.g_attn, w.g_ffn)
+
+
+def local_config(cfg: StepConfig, world: int) -> StepConfig:
+    """The per-rank view: 1/world of the heads and of the FFN columns, the full model width."""
+    return StepConfig(cfg.dim, cfg.n_q_heads // world, cfg.n_kv_heads // world, cfg.head_dim, cfg.ffn // world,
+                      cfg.group, cfg.rope_theta, cfg.rope_interleaved, cfg.eps)
+
+
+@dataclass
+class TPBuffers:
+    """Per-rank activations of the sharded step.  `x` is the replicated residual stream, `xs` this
+    rank's column slab of it; `g_*` receive all-gathers in rank-major layout [world, n_req, n/world]."""
+    local: StepBuffers
+    xs: torch.Tensor
+    o_full: torch.Tensor
+    act_full: torch.Tensor
+    g_o: torch.Tensor
+    g_x: torch.Tensor
+    g_act: torch.Tensor
+
+    @staticmethod
+    def allocate(cfg: StepConfig, world: int, n_req: int, device) -> "TPBuffers":
+        lc = local_config(cfg, world)
+        f = lambda *shape: torch.empty(shape, dtype=torch.float32, device=device)
+        return TPBuffers(StepBuffers.allocate(lc, n_req, device), f(n_req, cfg.dim // world), f(n_req, cfg.q_dim),
+                         f(n_req, cfg.ffn), f(world, n_req, cfg.q_dim // world), f(world, n_req, cfg.dim // world),
+                         f(world, n_req, cfg.ffn // world))
+
+
+def _gather_rows(dst_full, gathered, local, dist):
+    """All-gather `local` [n_req, n/world] into `gathered` [world, n_req, n/world], then lay the slabs
+    side by side in `dst_full` [n_req, n] (a strided copy: the next GEMM reads row-major activations)."""
+    world, n_req, w = gathered.shape
+    if world == 1:
+        dst_full.copy_(local)
+        return
+    if local.is_cuda:
+        dist.all_gather_into_tensor(gathered, local)
+    else:
+        dist.all_gather(list(gathered.unbind(0)), local)
+    dst_full.view(n_req, world, w).copy_(gathered.transpose(0, 1))
+
+
+def decode_layer_tp(x, w: LayerWeights, pools: KVPools, block_tables, past_lens, cur_lens, cfg: StepConfig,
+                    L: PagedLayout, acfg: PagedAttnCfg, buf: TPBuffers, rank: int, world: int, dist, ctx=None, ops=K):
+    """One layer on rank `rank` of `world`.  `w` is shard_layer(...), `pools`/`L`/`acfg` describe this rank's
+    KV heads, `x` [n_req, dim] is replicated and updated in place.  Exchanges: all-gathers of the attention
+    output, of the SwiGLU output and (twice) of the residual slabs; nothing else crosses ranks."""
+    lc = local_config(cfg, world)
+    b = buf.local
+    n_req = x.shape[0]
+    G = cfg.group
+    lo = rank * (cfg.dim // world)
+    ops.rmsnorm(x, w.g_attn, cfg.eps, out=b.h, ctx=ctx)
+    ops.gemm_w4a16_groupwise(b.h, *w.wqkv, G, C=b.qkv, ctx=ctx)
+    b.q.copy_(b.qkv[:, :lc.q_dim])
+    b.k.copy_(b.qkv[:, lc.q_dim:lc.q_dim + lc.kv_dim])
+    b.v.copy_(b.qkv[:, lc.q_dim + lc.kv_dim:])
+    ops.rope_decode_batched(b.q.view(n_req, lc.n_q_heads, lc.head_dim), past_lens, cfg.rope_theta, 1.0,
+                          cfg.rope_interleaved, ctx=ctx)
+    ops.rope_decode_batched(b.k.view(n_req, lc.n_kv_heads, lc.head_dim), past_lens, cfg.rope_theta, 1.0,
+                          cfg.rope_interleaved, ctx=ctx)
+    ops.paged_kv_append_q8_batched(pools.k, pools.v, pools.ks, pools.vs, b.k, b.v, block_tables, past_lens, L, 1,
+                                 ctx=ctx)
+    ops.paged_attention_q8_batched(b.q.view(n_req, lc.n_q_heads, 1, lc.head_dim), pools.k, pools.v, pools.ks,
+                                 pools.vs, block_tables, cur_lens, acfg, L,
+                                 O=b.o.view(n_req, lc.n_q_heads, 1, lc.head_dim), ctx=ctx)
+    _gather_rows(buf.o_full, buf.g_o, b.o, dist)
+    buf.xs.copy_(x[:, lo:lo + cfg.dim // world])
+    ops.gemm_w4a16_groupwise(buf.o_full, *w.wo, G, C=buf.xs, alpha=1.0, beta=1.0, ctx=ctx)
+    _gather_rows(x, buf.g_x, buf.xs, dist)
+    ops.rmsnorm(x, w.g_ffn, cfg.eps, out=b.h, ctx=ctx)
+    ops.gemm_w4a16_groupwise(b.h, *w.wgu, G, C=b.gu, ctx=ctx)
+    ops.swiglu(b.gu, out=b.act, ctx=ctx)
+    _gather_rows(buf.act_full, buf.g_act, b.act, dist)
+    ops.gemm_w4a16_groupwise(buf.act_full, *w.wdown, G, C=buf.xs, alpha=1.0, beta=1.0, ctx=ctx)
+    _gather_rows(x, buf.g_x, buf.xs, dist)
+    return x
+
+
+def decode_step_tp(x, layers, pools, block_tables, past_lens, cur_lens, cfg: StepConfig, L: PagedLayout,
+                   acfg: PagedAttnCfg, buf: TPBuffers, rank: int, world: int, dist, ctx=None, ops=K):
+    for w, kv in zip(layers, pools):
+        decode_layer_tp(x, w, kv, block_tables, past_lens, cur_lens, cfg, L, acfg, buf, rank, world, dist,
+                        ctx=ctx, ops=ops)
+    return x

@@ -652,3 +652,13 @@ LHO_API int lho_max_threads(void) {
     return 1;
 #endif
 }
+
+/* Thread count of the harness loops above (a launcher may have exported OMP_NUM_THREADS=1). */
+LHO_API void lho_set_threads(int n) {
+#ifdef _OPENMP
+    extern void omp_set_num_threads(int);
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}

@@ -216,6 +216,14 @@ LHR_API int lhr_max_threads(void) {
     return 1;
 #endif
 }
+// Thread count of the harness loops above (a launcher may have exported OMP_NUM_THREADS=1).
+LHR_API void lhr_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
 
 // --- the reference cache manager, for pinning the device cache manager's
 // --- allocation order (free list pops ascending ids, LIFO on release).

@@ -89,6 +89,10 @@ class Checker:
     def max_threads(self) -> int:
         return int(self.fn("max_threads", C.c_int)())
 
+    def set_threads(self, n: int) -> None:
+        """Thread count of the `par_*` harness loops (overrides OMP_NUM_THREADS)."""
+        self.fn("set_threads")(int(n))
+
     # -- quantisers -----------------------------------------------------
     def q8_quantize_per_row(self, x):
         rows, dim = x.shape
