@@ -270,6 +270,27 @@ def bench_extra(torch, lb, steps, warmup, hbm_peak):
         out[f"w4a16_m{M}"] = {"us_per_call": per * 1e6, "GBps": b / per / 1e9,
                               "hbm_frac": b / per / 1e9 / hbm_peak, "bytes": b}
     del packed, scales
+    # the second config's literal weight format: asymmetric int4, fp16 scale and zero-point per group
+    # (same bytes per group as the reference's fp32 scale), 16 weight sets = 500 MB, M = 1
+    asym = []
+    for _ in range(16):
+        W = torch.randn(K_DIM, N_DIM, device="cuda", generator=gen) * 0.02
+        asym.append(lb.q4a_quantize_groupwise(W, GROUP))
+        del W
+    A = torch.randn(1, K_DIM, device="cuda", generator=gen).bfloat16().float()
+    C = torch.empty(1, N_DIM, device="cuda")
+
+    def step_asym():
+        for p, s, z in asym:
+            lb.gemm_w4a16_asym(A, p, s, z, GROUP, C=C)
+    run_a, _ = graphed(step_asym, torch, GRAPHS)
+    ms = timed(run_a, steps, warmup, None, torch)
+    per = ms / (steps * len(asym)) * 1e-3
+    b = gemv_bytes(1, K_DIM, N_DIM, GROUP)
+    out["w4a16_asym_f16_m1"] = {"us_per_call": per * 1e6, "GBps": b / per / 1e9, "hbm_frac": b / per / 1e9 / hbm_peak,
+                                "bytes": b,
+                                "fast_path": int(lb._cabi.load().lhb_gemm_w4a16_asym_fast_path(1, N_DIM, K_DIM, GROUP))}
+    del asym
     # weight-only int8, M=16, K=N=4096 (first BASELINE config), 16 weight sets = 268 MB
     ws = []
     for _ in range(16):

@@ -234,6 +234,28 @@ LHB_API int lhb_rope_decode_batched(lhb_ctx* ctx, float* x, const int32_t* posit
  * y[r, i] = gate * sigmoid(gate) * value. */
 LHB_API int lhb_swiglu(lhb_ctx* ctx, const float* x, float* y, int rows, int dim, void* stream);
 
+/* ---- asymmetric int4 (extension; no counterpart in the reference) ------------------ */
+
+/* The reference's int4 is symmetric with fp32 scales (src/kernels/quant.hpp:52-57).  This
+ * variant keeps its packing - uint8 [K/2, N], low nibble = even k - with unsigned nibbles and
+ * an fp16 scale and fp16 integer-valued zero-point per (group, column), both [K/G, N]:
+ * lo = min(0, min w), hi = max(0, max w), s = fp16((hi - lo) / 15) (1 if 0),
+ * z = clamp(rint(-lo / s), 0, 15), u = clamp(rint(w / s) + z, 0, 15), w' = (u - z) * s. */
+LHB_API int lhb_q4a_quantize_groupwise(lhb_ctx* ctx, const float* src, uint8_t* packed,
+                                       uint16_t* scales_f16, uint16_t* zeros_f16, int K, int N,
+                                       int group_size, void* stream);
+LHB_API int lhb_q4a_dequantize_groupwise(lhb_ctx* ctx, const uint8_t* packed,
+                                         const uint16_t* scales_f16, const uint16_t* zeros_f16,
+                                         float* dst, int K, int N, int group_size, void* stream);
+/* C = beta*C + alpha * A @ dequant(B), the asymmetric counterpart of
+ * lh::gemm_w4a16_groupwise (src/kernels/gemm_quant.hpp:54-57). */
+LHB_API int lhb_gemm_w4a16_asym(lhb_ctx* ctx, const float* A, const uint8_t* B_packed,
+                                const uint16_t* scales_f16, const uint16_t* zeros_f16, float* C,
+                                int M, int N, int K, int group_size, float alpha, float beta,
+                                void* stream);
+/* 1 when the tensor-core decode kernel serves this shape. */
+LHB_API int lhb_gemm_w4a16_asym_fast_path(int M, int N, int K, int group_size);
+
 /* ---- device-resident cache manager ---------------------------------------------- */
 
 /* Host bookkeeping of lh::CacheManager (src/runtime/cache_manager.hpp:34-110:

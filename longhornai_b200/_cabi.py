@@ -54,6 +54,10 @@ SIGNATURES = {
     "lhb_rope": (_i, [_vp, _vp, _i, _i, _i, _f, _f, _i, _i, _vp]),
     "lhb_rope_decode_batched": (_i, [_vp, _vp, _vp, _i, _i, _i, _f, _f, _i, _vp]),
     "lhb_swiglu": (_i, [_vp, _vp, _vp, _i, _i, _vp]),
+    "lhb_q4a_quantize_groupwise": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "lhb_q4a_dequantize_groupwise": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "lhb_gemm_w4a16_asym": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _f, _vp]),
+    "lhb_gemm_w4a16_asym_fast_path": (_i, [_i, _i, _i, _i]),
     "lhb_gemm_w8a8": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _f, _vp]),
     "lhb_gemm_w4a16_groupwise": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _f, _vp]),
     "lhb_gemm_w8a16_perchannel": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _f, _vp]),

@@ -42,6 +42,14 @@ int launch_decode_fast(lhb_ctx* ctx, const float* Q, const int8_t* Kp, const int
                        const int32_t* seq_lens, int n_req, float* O, const lhb_paged_attn_cfg& cfg,
                        const lhb_paged_layout& L, cudaStream_t st);
 
+// asymmetric int4 (fp16 scale and zero-point per group): generic kernel in quant_asym.cu,
+// decode fast path in gemv_mma.cu
+int launch_w4a16_asym_generic(const float* A, const uint8_t* Bp, const uint16_t* Bs, const uint16_t* Bz, float* C,
+                              int M, int N, int K, int G, float alpha, float beta, cudaStream_t st);
+bool w4a16_asym_fast_ok(int M, int N, int K, int G);
+int launch_w4a16_asym_fast(lhb_ctx* ctx, const float* A, const uint8_t* Bp, const uint16_t* Bs, const uint16_t* Bz,
+                           float* C, int M, int N, int K, int G, float alpha, float beta, cudaStream_t st);
+
 // TMA tensor maps (tensor_map.cu): 2-D uint8 tensor [rows, cols] (cols
 // contiguous, row pitch in bytes), box [box_rows, box_cols], 128-byte swizzle
 // when swizzle128 is set.  Cached per context.
@@ -51,6 +59,9 @@ int get_tensor_map_2d_u8(lhb_ctx* ctx, const void* base, uint64_t rows, uint64_t
                          bool swizzle128, TensorMap* out);
 // the same for an fp32 tensor (cols and box_cols in elements), no swizzle
 int get_tensor_map_2d_f32(lhb_ctx* ctx, const void* base, uint64_t rows, uint64_t cols,
+                          uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols, TensorMap* out);
+// and for an fp16 tensor
+int get_tensor_map_2d_f16(lhb_ctx* ctx, const void* base, uint64_t rows, uint64_t cols,
                           uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols, TensorMap* out);
 
 }  // namespace lhb

@@ -33,10 +33,10 @@
 //       columns), activations the 8-column operand.
 //
 // Activations are fp32 in the API.  Each row of the K-range a CTA touches is
-// scaled by a power of two so that max|a| lands in [2^19, 2^20), rounded to an
-// integer and written as three signed 7-bit digits (a = d1*2^14 + d2*2^7 + d3),
+// scaled by a power of two so that max|a| lands in [2^21, 2^22), rounded to an
+// integer and written as three signed 8-bit digits (a = d1*2^16 + d2*2^8 + d3),
 // one MMA column per digit.  Integer products and sums are exact; the only error
-// is the rounding of a to 20 bits relative to the range maximum (2^-21), so any
+// is the rounding of a to 22 bits relative to the range maximum (2^-23), so any
 // fp32 input meets the 1e-3 / 1e-4 tolerance against the reference's fp32 loop
 // (src/kernels/gemm_quant.cpp:54-82).  int32 partial sums are converted to
 // fp32 at every quantisation group (at most every 128 k of int4, 256 k of
@@ -47,6 +47,8 @@
 // contributor to arrive for that column tile (a self-resetting counter) sums
 // the partials in contributor order and writes C: deterministic for a given SM
 // count, and C is written once, with alpha/beta applied.
+#include <cuda_fp16.h>
+
 #include <cstdlib>
 
 #include "common.cuh"
@@ -100,6 +102,24 @@ __device__ __forceinline__ void mma_s8_16832_first(int (&c)[4], uint32_t a0, uin
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 
+// unsigned weights (asymmetric int4 carried as 16*u in [0, 240]) x signed activation digits
+__device__ __forceinline__ void mma_u8s8_16832(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_u8s8_16832_first(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                     uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%10,%10,%10,%10};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
 // barrier among the consumer warps only (the producer warp never joins it)
 template <int CONSUMERS>
 __device__ __forceinline__ void consumer_sync() {
@@ -123,26 +143,26 @@ __device__ unsigned long long g_gv_trace[64][512][8];
 #define GV_STAMP(i) do { } while (0)
 #endif
 
-// Three signed 7-bit digits of four consecutive activations (k .. k+3, k % 4 == 0, `kin`
+// Three signed 8-bit digits of four consecutive activations (k .. k+3, k % 4 == 0, `kin`
 // = k % 32), written into the operand fragment of their k32-block: `base` points at the 32
 // bytes of the row's first digit column, the other two follow at +32 and +64.
 template <int WBITS>
 __device__ __forceinline__ void write_digits(uint8_t* base, int kin, float4 v, float scl) {
     const int half = kin >> 4, r = kin & 15;
-    // a = rint(v * scl) = d1*2^14 + d2*2^7 + d3 with every digit in [-64, 64], by
-    // exact fp32 arithmetic: adding 1.5*2^23 rounds to an integer and leaves its
-    // two's-complement low bits in the low mantissa bits.
+    // a = rint(v * scl) = d1*2^16 + d2*2^8 + d3 with d2, d3 in [-128, 127] and |d1| <= 64
+    // (|a| <= 2^22): the low byte of an integer, read as signed, is its balanced digit, and
+    // what remains is divisible by 256.
     const float x[4] = {v.x * scl, v.y * scl, v.z * scl, v.w * scl};
     uint32_t b1[4], b2[4], b3[4];                     // low byte = digit
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-        const float MG = 12582912.0f;
-        const float xi = (x[j] + MG) - MG;                         // rint(x), |xi| <= 2^20
-        const float t1 = fmaf(xi, 6.103515625e-05f, MG);           // + xi / 2^14
-        const float r1 = fmaf(t1 - MG, -16384.0f, xi);             // |r1| <= 2^13
-        const float t2 = fmaf(r1, 0.0078125f, MG);                 // + r1 / 2^7
-        const float t3 = fmaf(t2 - MG, -128.0f, r1) + MG;          // |.| <= 64
-        b1[j] = __float_as_uint(t1); b2[j] = __float_as_uint(t2); b3[j] = __float_as_uint(t3);
+        const int iv = __float2int_rn(x[j]);
+        const int lo = static_cast<int>(static_cast<int8_t>(iv));
+        const int iv2 = (iv - lo) >> 8;
+        const int mid = static_cast<int>(static_cast<int8_t>(iv2));
+        b3[j] = static_cast<uint32_t>(lo);
+        b2[j] = static_cast<uint32_t>(mid);
+        b1[j] = static_cast<uint32_t>((iv2 - mid) >> 8);
     }
     // d1/d2/d3: 4 digits each, one byte per element
     const uint32_t d1 = __byte_perm(__byte_perm(b1[0], b1[1], 0x0040), __byte_perm(b1[2], b1[3], 0x0040), 0x5410);
@@ -204,8 +224,8 @@ gemv_digits_kernel(const float* __restrict__ A, int M, int K, int k_pad, size_t 
     unsigned mb = s_max[lane];
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mb = max(mb, __shfl_xor_sync(0xffffffffu, mb, o));
-    // power-of-two factor taking max|a| into [2^19, 2^20); exponent clamped
-    int se = mb ? 273 - static_cast<int>((mb >> 23) & 0xff) : 127;
+    // power-of-two factor taking max|a| into [2^21, 2^22); exponent clamped
+    int se = mb ? 275 - static_cast<int>((mb >> 23) & 0xff) : 127;
     se = max(1, min(253, se));
     const float scl = __uint_as_float(static_cast<uint32_t>(se) << 23);
     if (threadIdx.x == 0) inv_scale[row_g] = __uint_as_float(static_cast<uint32_t>(254 - se) << 23);
@@ -240,9 +260,13 @@ struct GemvParams {
 // row of A, so M <= (8 * JB) / 3.
 // STAGE_FOLD: W4 with group_size >= 128: the int32 sums are folded exactly once per stage, after
 // its last k32-block, so the first block of a stage starts its sums from zero inside the MMA.
-template <int WBITS, int JB, bool STAGE_FOLD>
+// ASYM: asymmetric int4 (W4, group_size 128, STAGE_FOLD): unsigned nibbles, fp16 scale and
+// zero-point tiles (tmS, tmZ), and per stage  sum_k a_k (u_k - z) = sum_k a_k u_k - z * sum_k a_k,
+// the second term from per-stage sums of the activation digits.
+template <int WBITS, int JB, bool STAGE_FOLD, bool ASYM>
 __global__ void __launch_bounds__(gv_threads(JB), (JB >= 6) ? 1 : 2)
-gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ TensorMap tmS, const GemvParams p) {
+gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ TensorMap tmS,
+                const __grid_constant__ TensorMap tmZ, const GemvParams p) {
     constexpr int K_PER_ROW = (WBITS == 4) ? 2 : 1;
     constexpr int KPS = GV_ROWS * K_PER_ROW;              // k per stage: 128 (W4), 64 (W8)
     constexpr int KPS_SHIFT = (WBITS == 4) ? 7 : 6;
@@ -287,7 +311,11 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ T
         for (int b = 0; b < GV_BOXES; ++b)
             ptx::tma_load_2d(smem_u32(tiles + slot * GV_STAGE_BYTES + b * GV_BOX_BYTES), &tmB,
                              tile * GV_COLS + b * GV_BOX_COLS, stage * GV_ROWS, bar);
-        if (WBITS == 4) {
+        if (ASYM) {
+            // one group per stage: 256 fp16 scales, then 256 fp16 zero-points, in the stage's 1 KiB
+            ptx::tma_load_2d(smem_u32(sc + slot * GV_COLS), &tmS, tile * GV_COLS, stage, bar);
+            ptx::tma_load_2d(smem_u32(sc + slot * GV_COLS) + GV_COLS * 2, &tmZ, tile * GV_COLS, stage, bar);
+        } else if (WBITS == 4) {
             const int row = (p.G >= KPS) ? (stage * KPS) / p.G : stage * p.srows;
             ptx::tma_load_2d(smem_u32(sc + slot * p.srows * GV_COLS), &tmS, tile * GV_COLS, row, bar);
         }
@@ -338,7 +366,7 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ T
         __syncthreads();
     } else {
     // Activations of the K stages this CTA meets (digit stage i = stage
-    // (s_first + i) mod S): row maxima, then three 7-bit digits per element in
+    // (s_first + i) mod S): row maxima, then three 8-bit digits per element in
     // MMA-operand order.  Digit columns of rows m >= M are left as they are: an
     // MMA column only feeds its own output column, never read.
     const int q4 = n_dig * (KPS / 4);                      // float4 per row
@@ -402,9 +430,9 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ T
         if (i >= n4) break;
         const int m = min(p.M - 1, __float2int_rz((static_cast<float>(i) + 0.5f) * inv_q4));
         const int kl = (i - m * q4) * 4;
-        // power-of-two factor taking max|a| into [2^19, 2^20); exponent clamped
+        // power-of-two factor taking max|a| into [2^21, 2^22); exponent clamped
         const unsigned mb = rowmax[m];
-        int se = mb ? 273 - static_cast<int>((mb >> 23) & 0xff) : 127;     // 127 + 19 - (e - 127)
+        int se = mb ? 275 - static_cast<int>((mb >> 23) & 0xff) : 127;     // 127 + 21 - (e - 127)
         se = max(1, min(253, se));
         const float scl = __uint_as_float(static_cast<uint32_t>(se) << 23);
         if (kl == 0) inv_s[m] = __uint_as_float(static_cast<uint32_t>(254 - se) << 23);
@@ -414,6 +442,22 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ T
     }
     __syncthreads();
     }   // !PRE
+    // ASYM: sum of each digit column over each digit stage (= one quantisation group)
+    float* dsum = reinterpret_cast<float*>(dfrag + n_dig * (KPS * NJ));       // [digit stage][NJ]
+    if constexpr (ASYM) {
+        for (int i = threadIdx.x; i < n_dig * NJ; i += GV_THREADS) {
+            const int ds_i = i / NJ, j = i - ds_i * NJ;
+            int sum = 0;
+#pragma unroll
+            for (int kb = 0; kb < KB; ++kb) {
+                const uint32_t* w = reinterpret_cast<const uint32_t*>(dfrag + ((ds_i * KB + kb) * NJ + j) * 32);
+#pragma unroll
+                for (int q = 0; q < 8; ++q) sum = __dp4a(static_cast<int>(w[q]), 0x01010101, sum);
+            }
+            dsum[i] = static_cast<float>(sum);
+        }
+        __syncthreads();
+    }
     GV_STAMP(2);
 
     if (warp < GV_CONSUMER_WARPS) {
@@ -448,6 +492,24 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ T
                     for (int i = 0; i < 4; ++i) { out[f][jb][i] = 0.0f; acc[f][jb][i] = 0; }
         };
         // fold the int32 sums into fp32, times the scales at `srow` (W4) or 1 (W8)
+        auto flush_asym = [&](const float* stile, const float* dsum_stage) {
+            // stile: 256 fp16 scales, then 256 fp16 zero-points of this stage's group
+            const __half* sh = reinterpret_cast<const __half*>(stile);
+#pragma unroll
+            for (int f = 0; f < 2; ++f) {
+                const float2 sv = __half22float2(*reinterpret_cast<const __half2*>(sh + wcol + 16 * f));
+                const float2 zv = __half22float2(*reinterpret_cast<const __half2*>(sh + GV_COLS + wcol + 16 * f));
+                const float z0 = -16.0f * zv.x, z1 = -16.0f * zv.y;      // weights are carried as 16 * u
+#pragma unroll
+                for (int jb = 0; jb < JBL; ++jb) {
+                    const float2 sd = *reinterpret_cast<const float2*>(dsum_stage + (jb0 + jb) * 8 + 2 * t);
+                    out[f][jb][0] = fmaf(sv.x, fmaf(z0, sd.x, small_int_to_float(acc[f][jb][0])), out[f][jb][0]);
+                    out[f][jb][1] = fmaf(sv.x, fmaf(z0, sd.y, small_int_to_float(acc[f][jb][1])), out[f][jb][1]);
+                    out[f][jb][2] = fmaf(sv.y, fmaf(z1, sd.x, small_int_to_float(acc[f][jb][2])), out[f][jb][2]);
+                    out[f][jb][3] = fmaf(sv.y, fmaf(z1, sd.y, small_int_to_float(acc[f][jb][3])), out[f][jb][3]);
+                }
+            }
+        };
         auto flush = [&](const float* srow) {
 #pragma unroll
             for (int f = 0; f < 2; ++f) {
@@ -471,7 +533,15 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ T
 #pragma unroll
             for (int jb = 0; jb < JBL; ++jb) {
                 const uint2 b = *reinterpret_cast<const uint2*>(dblk + jb * 8 * 32);
-                if (first) {
+                if (ASYM) {
+                    if (first) {
+                        mma_u8s8_16832_first(acc[0][jb], a[0][0], a[0][1], a[0][2], a[0][3], b.x, b.y);
+                        mma_u8s8_16832_first(acc[1][jb], a[1][0], a[1][1], a[1][2], a[1][3], b.x, b.y);
+                    } else {
+                        mma_u8s8_16832(acc[0][jb], a[0][0], a[0][1], a[0][2], a[0][3], b.x, b.y);
+                        mma_u8s8_16832(acc[1][jb], a[1][0], a[1][1], a[1][2], a[1][3], b.x, b.y);
+                    }
+                } else if (first) {
                     mma_s8_16832_first(acc[0][jb], a[0][0], a[0][1], a[0][2], a[0][3], b.x, b.y);
                     mma_s8_16832_first(acc[1][jb], a[1][0], a[1][1], a[1][2], a[1][3], b.x, b.y);
                 } else {
@@ -520,7 +590,10 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ T
                                 const int kb = 2 * half + q;
                                 mma_block(dst + kb * NJ * 32, a, STAGE_FOLD && kb == 0);
                                 if (STAGE_FOLD) {
-                                    if (kb == KB - 1) flush(sstage);
+                                    if (kb == KB - 1) {
+                                        if (ASYM) flush_asym(sstage, dsum + didx * NJ);
+                                        else flush(sstage);
+                                    }
                                 } else if (p.flush_mask & (1 << kb)) {
                                     flush(sstage + srow_i * GV_COLS);
                                     ++srow_i;
@@ -618,11 +691,11 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ T
                         const float is = inv_s[m] * digit_unit;
                         float2 v;
                         if (t == 0) {
-                            v.x = c0 * is * fmaf(16384.0f, e0, fmaf(128.0f, o0, up_e0));
-                            v.y = c1 * is * fmaf(16384.0f, e1, fmaf(128.0f, o1, up_e1));
+                            v.x = c0 * is * fmaf(65536.0f, e0, fmaf(256.0f, o0, up_e0));
+                            v.y = c1 * is * fmaf(65536.0f, e1, fmaf(256.0f, o1, up_e1));
                         } else {
-                            v.x = c0 * is * fmaf(16384.0f, dn_o0, fmaf(128.0f, e0, o0));
-                            v.y = c1 * is * fmaf(16384.0f, dn_o1, fmaf(128.0f, e1, o1));
+                            v.x = c0 * is * fmaf(65536.0f, dn_o0, fmaf(256.0f, e0, o0));
+                            v.y = c1 * is * fmaf(65536.0f, dn_o1, fmaf(256.0f, e1, o1));
                         }
                         if (whole) {
                             float2* cp = reinterpret_cast<float2*>(p.C + static_cast<int64_t>(m) * p.N + col0 + cc);
@@ -647,10 +720,10 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ T
                 const float4 l = *reinterpret_cast<const float4*>(part + (3 * m + 2) * GV_COLS + c);
                 const float is = inv_s[m] * digit_unit;
                 float4 v;
-                v.x = is * fmaf(16384.0f, h.x, fmaf(128.0f, md.x, l.x));
-                v.y = is * fmaf(16384.0f, h.y, fmaf(128.0f, md.y, l.y));
-                v.z = is * fmaf(16384.0f, h.z, fmaf(128.0f, md.z, l.z));
-                v.w = is * fmaf(16384.0f, h.w, fmaf(128.0f, md.w, l.w));
+                v.x = is * fmaf(65536.0f, h.x, fmaf(256.0f, md.x, l.x));
+                v.y = is * fmaf(65536.0f, h.y, fmaf(256.0f, md.y, l.y));
+                v.z = is * fmaf(65536.0f, h.z, fmaf(256.0f, md.z, l.z));
+                v.w = is * fmaf(65536.0f, h.w, fmaf(256.0f, md.w, l.w));
                 if (whole) store_c(m, c, v);
                 else *reinterpret_cast<float4*>(my_slot + m * GV_COLS + c) = v;
             }
@@ -737,7 +810,7 @@ static bool w4_group_ok(int G) { return G == 32 || G == 64 || (G >= 128 && G % 1
 // hold (two per SM up to M = 8, one for M <= 16) unless a CTA's share of K needs
 // more shared memory for its activation digits than there is; then there are more,
 // smaller CTAs.  The ring takes what shared memory remains, up to GV_MAX_STAGE.
-static GemvPlan plan_gemv(int wbits, int jb, int N, int K, int G, int sm_count) {
+static GemvPlan plan_gemv(int wbits, int jb, int N, int K, int G, int sm_count, bool asym = false) {
     GemvPlan pl{};
     const int kps = GV_ROWS * (wbits == 4 ? 2 : 1);
     pl.S = ceil_div(K, kps);
@@ -752,7 +825,7 @@ static GemvPlan plan_gemv(int wbits, int jb, int N, int K, int G, int sm_count) 
     const size_t nj = 8 * jb;
     const size_t stage_bytes = GV_STAGE_BYTES + static_cast<size_t>(pl.srows) * GV_COLS * 4;
     const size_t fixed = 1024 + nj * GV_COLS * 4 + 16 * 4 + 16 * 4 + (2 * GV_MAX_STAGE + 2) * 8 + 16;
-    const size_t dig_per_stage = static_cast<size_t>(kps) * nj;
+    const size_t dig_per_stage = static_cast<size_t>(kps) * nj + (asym ? nj * 4 : 0);   // digits (+ their sums)
     size_t budget = per_sm == 1 ? 227 * 1024 : (228 * 1024) / per_sm - 1024 - 512;
     if (const char* e = getenv("LHB_GEMV_SMEM_KB")) budget = std::min<size_t>(budget, static_cast<size_t>(atoi(e)) * 1024);
     int ctas = static_cast<int>(std::min<int64_t>(units, static_cast<int64_t>(per_sm) * sm_count));
@@ -801,10 +874,10 @@ bool w8a16_fast_ok(int M, int N, int K) {
     return plan_gemv(8, jb_for(std::min(M, GV_MAX_M)), N, K, 1, 148).ok;
 }
 
-template <int WBITS, int JB, bool STAGE_FOLD>
-static int launch_gemv_t(lhb_ctx* ctx, const TensorMap& tm, const TensorMap& tms, GemvParams p,
+template <int WBITS, int JB, bool STAGE_FOLD, bool ASYM = false>
+static int launch_gemv_t(lhb_ctx* ctx, const TensorMap& tm, const TensorMap& tms, const TensorMap& tmz, GemvParams p,
                          const GemvPlan& pl, cudaStream_t st) {
-    auto kern = gemv_mma_kernel<WBITS, JB, STAGE_FOLD>;
+    auto kern = gemv_mma_kernel<WBITS, JB, STAGE_FOLD, ASYM>;
     static bool attr_set[64] = {};                // per instantiation and device
     if (!attr_set[ctx->device & 63]) {
         LHB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
@@ -838,17 +911,19 @@ static int launch_gemv_t(lhb_ctx* ctx, const TensorMap& tm, const TensorMap& tms
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    LHB_CUDA(cudaLaunchKernelEx(&cfg, kern, tm, tms, p));
+    LHB_CUDA(cudaLaunchKernelEx(&cfg, kern, tm, tms, tmz, p));
     return LHB_OK;
 }
 
-template <int WBITS>
-static int launch_gemv(lhb_ctx* ctx, const float* A, const void* B, const float* scales, float* C,
+template <int WBITS, bool ASYM = false>
+static int launch_gemv(lhb_ctx* ctx, const float* A, const void* B, const void* scales_v, const void* zeros, float* C,
                        int M, int N, int K, int G, float alpha, float beta, cudaStream_t st) {
+    const float* scales = ASYM ? nullptr : static_cast<const float*>(scales_v);
     const uint64_t rows = (WBITS == 4) ? K / 2 : K;
-    TensorMap tm, tms;
+    TensorMap tm, tms, tmz;
     if (int e = get_tensor_map_2d_u8(ctx, B, rows, N, N, GV_ROWS, GV_BOX_COLS, true, &tm)) return e;
     tms = tm;                                     // W8 has no scale tiles; the kernel never uses the map
+    tmz = tm;
     // rows of A are independent: M > 16 is served in slabs of 16 rows
     const int kps_d = GV_ROWS * (WBITS == 4 ? 2 : 1);
     const int k_pad = ceil_div(K, kps_d) * kps_d;
@@ -878,16 +953,23 @@ static int launch_gemv(lhb_ctx* ctx, const float* A, const void* B, const float*
         }
         const int m = std::min(GV_MAX_M, M - m0);
         const int jb = jb_for(m);
-        GemvPlan pl = plan_gemv(WBITS, jb, N, K, WBITS == 4 ? G : 1, ctx->sm_count);
+        GemvPlan pl = plan_gemv(WBITS, jb, N, K, WBITS == 4 ? G : 1, ctx->sm_count, ASYM);
         if (!pl.ok) return LHB_ERR_UNSUPPORTED;
         if (pl.col_tiles > static_cast<int>(ctx->counters_len)) return LHB_ERR_UNSUPPORTED;
         if (static_cast<size_t>(pl.col_tiles) * pl.max_contrib * m * GV_COLS * sizeof(float) >
             ctx->scratch_bytes - GV_DIG_BYTES)
             return LHB_ERR_SCRATCH;
-        if (WBITS == 4 && m0 == 0)
+        if (ASYM && m0 == 0) {
+            if (int e = get_tensor_map_2d_f16(ctx, scales_v, K / G, N, static_cast<uint64_t>(N) * 2, 1, GV_COLS, &tms))
+                return e;
+            if (int e = get_tensor_map_2d_f16(ctx, zeros, K / G, N, static_cast<uint64_t>(N) * 2, 1, GV_COLS, &tmz))
+                return e;
+        } else if (WBITS == 4 && m0 == 0) {
             if (int e = get_tensor_map_2d_f32(ctx, scales, K / G, N, static_cast<uint64_t>(N) * 4, pl.srows,
                                               GV_COLS, &tms))
                 return e;
+            tmz = tms;
+        }
         GemvParams p{};
         p.A = A + static_cast<int64_t>(m0) * K;
         p.scales = scales;
@@ -896,16 +978,21 @@ static int launch_gemv(lhb_ctx* ctx, const float* A, const void* B, const float*
         p.digits = dig + ((m0 - pass0) / GV_MAX_M) * slab_bytes;
         p.inv_scale = inv + (m0 - pass0);
         int e;
-        if (WBITS == 4 && G >= 128) {
-            if (jb == 1) e = launch_gemv_t<WBITS, 1, WBITS == 4>(ctx, tm, tms, p, pl, st);
-            else if (jb == 2) e = launch_gemv_t<WBITS, 2, WBITS == 4>(ctx, tm, tms, p, pl, st);
-            else if (jb == 3) e = launch_gemv_t<WBITS, 3, WBITS == 4>(ctx, tm, tms, p, pl, st);
-            else e = launch_gemv_t<WBITS, 6, WBITS == 4>(ctx, tm, tms, p, pl, st);
+        if (ASYM) {
+            if (jb == 1) e = launch_gemv_t<4, 1, true, ASYM>(ctx, tm, tms, tmz, p, pl, st);
+            else if (jb == 2) e = launch_gemv_t<4, 2, true, ASYM>(ctx, tm, tms, tmz, p, pl, st);
+            else if (jb == 3) e = launch_gemv_t<4, 3, true, ASYM>(ctx, tm, tms, tmz, p, pl, st);
+            else e = launch_gemv_t<4, 6, true, ASYM>(ctx, tm, tms, tmz, p, pl, st);
+        } else if (WBITS == 4 && G >= 128) {
+            if (jb == 1) e = launch_gemv_t<WBITS, 1, WBITS == 4>(ctx, tm, tms, tmz, p, pl, st);
+            else if (jb == 2) e = launch_gemv_t<WBITS, 2, WBITS == 4>(ctx, tm, tms, tmz, p, pl, st);
+            else if (jb == 3) e = launch_gemv_t<WBITS, 3, WBITS == 4>(ctx, tm, tms, tmz, p, pl, st);
+            else e = launch_gemv_t<WBITS, 6, WBITS == 4>(ctx, tm, tms, tmz, p, pl, st);
         } else {
-            if (jb == 1) e = launch_gemv_t<WBITS, 1, false>(ctx, tm, tms, p, pl, st);
-            else if (jb == 2) e = launch_gemv_t<WBITS, 2, false>(ctx, tm, tms, p, pl, st);
-            else if (jb == 3) e = launch_gemv_t<WBITS, 3, false>(ctx, tm, tms, p, pl, st);
-            else e = launch_gemv_t<WBITS, 6, false>(ctx, tm, tms, p, pl, st);
+            if (jb == 1) e = launch_gemv_t<WBITS, 1, false>(ctx, tm, tms, tmz, p, pl, st);
+            else if (jb == 2) e = launch_gemv_t<WBITS, 2, false>(ctx, tm, tms, tmz, p, pl, st);
+            else if (jb == 3) e = launch_gemv_t<WBITS, 3, false>(ctx, tm, tms, tmz, p, pl, st);
+            else e = launch_gemv_t<WBITS, 6, false>(ctx, tm, tms, tmz, p, pl, st);
         }
         if (e) return e;
     }
@@ -914,12 +1001,23 @@ static int launch_gemv(lhb_ctx* ctx, const float* A, const void* B, const float*
 
 int launch_w4a16_fast(lhb_ctx* ctx, const float* A, const uint8_t* Bp, const float* Bs, float* C,
                       int M, int N, int K, int G, float alpha, float beta, cudaStream_t st) {
-    return launch_gemv<4>(ctx, A, Bp, Bs, C, M, N, K, G, alpha, beta, st);
+    return launch_gemv<4>(ctx, A, Bp, Bs, nullptr, C, M, N, K, G, alpha, beta, st);
+}
+
+// asymmetric int4: the decode kernel serves group_size 128 (one group per 128-k stage)
+bool w4a16_asym_fast_ok(int M, int N, int K, int G) {
+    if (M < 1 || M > 64 || (N % 16) != 0 || (K % 128) != 0 || G != 128) return false;
+    if (M > 2 && static_cast<size_t>(K) * 48 > GV_DIG_BYTES - 256) return false;
+    return plan_gemv(4, jb_for(std::min(M, GV_MAX_M)), N, K, G, 148, true).ok;
+}
+int launch_w4a16_asym_fast(lhb_ctx* ctx, const float* A, const uint8_t* Bp, const uint16_t* Bs, const uint16_t* Bz,
+                           float* C, int M, int N, int K, int G, float alpha, float beta, cudaStream_t st) {
+    return launch_gemv<4, true>(ctx, A, Bp, Bs, Bz, C, M, N, K, G, alpha, beta, st);
 }
 
 int launch_w8a16_fast(lhb_ctx* ctx, const float* A, const int8_t* Bq, const float* Bs, float* C,
                       int M, int N, int K, float alpha, float beta, cudaStream_t st) {
-    return launch_gemv<8>(ctx, A, Bq, Bs, C, M, N, K, 0, alpha, beta, st);
+    return launch_gemv<8>(ctx, A, Bq, Bs, nullptr, C, M, N, K, 0, alpha, beta, st);
 }
 
 }  // namespace lhb

@@ -82,4 +82,10 @@ int get_tensor_map_2d_f32(lhb_ctx* ctx, const void* base, uint64_t rows, uint64_
                              box_cols, false, out);
 }
 
+int get_tensor_map_2d_f16(lhb_ctx* ctx, const void* base, uint64_t rows, uint64_t cols,
+                          uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols, TensorMap* out) {
+    return get_tensor_map_2d(ctx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, base, rows, cols, pitch_bytes, box_rows,
+                             box_cols, false, out);
+}
+
 }  // namespace lhb

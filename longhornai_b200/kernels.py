@@ -361,3 +361,45 @@ def swiglu(x, out=None, ctx=None):
     check(c.lib.lhb_swiglu(c.handle, _t(x, torch.float32, "x"), _t(y, torch.float32, "out"), rows,
                            dim2 // 2, _stream(c.device)), "swiglu")
     return y
+
+
+# ---- asymmetric int4 (fp16 scale and zero-point per group) ------------------------------
+
+def q4a_quantize_groupwise(src, group_size: int, ctx=None):
+    """fp32 [K, N] -> (uint8 packed [K/2, N], fp16 scales [K/G, N], fp16 zero-points [K/G, N])."""
+    c = _ctx_for(src, ctx)
+    K_, N = src.shape
+    packed = torch.empty((K_ // 2, N), dtype=torch.uint8, device=src.device)
+    scales = torch.empty((K_ // group_size, N), dtype=torch.float16, device=src.device)
+    zeros = torch.empty((K_ // group_size, N), dtype=torch.float16, device=src.device)
+    check(c.lib.lhb_q4a_quantize_groupwise(c.handle, _t(src, torch.float32, "src"), packed.data_ptr(),
+                                           scales.data_ptr(), zeros.data_ptr(), K_, N, group_size,
+                                           _stream(c.device)), "q4a_quantize_groupwise")
+    return packed, scales, zeros
+
+
+def q4a_dequantize_groupwise(packed, scales, zeros, group_size: int, ctx=None):
+    c = _ctx_for(packed, ctx)
+    K_, N = packed.shape[0] * 2, packed.shape[1]
+    dst = torch.empty((K_, N), dtype=torch.float32, device=packed.device)
+    check(c.lib.lhb_q4a_dequantize_groupwise(c.handle, _t(packed, torch.uint8, "packed"),
+                                             _t(scales, torch.float16, "scales"), _t(zeros, torch.float16, "zeros"),
+                                             dst.data_ptr(), K_, N, group_size, _stream(c.device)),
+          "q4a_dequantize_groupwise")
+    return dst
+
+
+def gemm_w4a16_asym(A, B_packed, B_scales, B_zeros, group_size: int, C=None, alpha: float = 1.0,
+                    beta: float = 0.0, ctx=None):
+    """C = beta*C + alpha * A @ ((u - zero) * scale); fp32 A [M, K], packed [K/2, N], fp16 parameters."""
+    c = _ctx_for(A, ctx)
+    M, K_ = A.shape
+    N = B_packed.shape[1]
+    if B_packed.shape[0] * 2 != K_:
+        raise ValueError("packed rows must be K/2")
+    out = _out(C, M, N, A, beta)
+    check(c.lib.lhb_gemm_w4a16_asym(c.handle, _t(A, torch.float32, "A"), _t(B_packed, torch.uint8, "B_packed"),
+                                    _t(B_scales, torch.float16, "B_scales"), _t(B_zeros, torch.float16, "B_zeros"),
+                                    _t(out, torch.float32, "C"), M, N, K_, group_size, alpha, beta,
+                                    _stream(c.device)), "gemm_w4a16_asym")
+    return out

@@ -574,6 +574,150 @@ LHO_API void lho_swiglu(const float* x, float* y, int rows, int dim) {
     }
 }
 
+/* ---------------------------------------------------------------------------
+ * Asymmetric int4 with fp16 scale and zero-point per group (an extension: the
+ * reference's int4 is symmetric with fp32 scales, src/kernels/quant.hpp:52-57).
+ * Same packing as the symmetric form - byte (k/2, n), low nibble = even k - but
+ * the nibble is unsigned, u in [0, 15]; parameters are fp16 [K/G, N] each.
+ * Parity of these three functions is NOT pinned by the reference (it has no such
+ * scheme); only the fp16 conversion is (against lh::half).
+ *   range   lo = min(0, min w), hi = max(0, max w) over the group
+ *   scale   s = fp16((hi - lo) / 15), 1 if that is 0
+ *   zero    z = clamp(rint(-lo / s), 0, 15)
+ *   weight  u = clamp(rint(w / s) + z, 0, 15),   w' = (u - z) * s
+ * The loop structure follows quant.cpp:128-171 and gemm_quant.cpp:54-82.
+ * ------------------------------------------------------------------------- */
+
+/* fp32 -> fp16 bits, round to nearest even, subnormals kept
+ * (src/kernels/dtypes.hpp:17-55 computes the same function). */
+LHO_API uint16_t lho_f32_to_f16_bits(float v) {
+    uint32_t x;
+    memcpy(&x, &v, sizeof x);
+    const uint32_t sign = (x >> 16) & 0x8000u;
+    const int e = (int)((x >> 23) & 0xff);
+    uint32_t m = x & 0x7fffffu;
+    if (e == 0xff) return (uint16_t)(sign | (m ? 0x7e00u : 0x7c00u));
+    int he = e - 127 + 15;
+    if (he >= 31) return (uint16_t)(sign | 0x7c00u);
+    uint32_t keep, rest, half_ulp;
+    if (he <= 0) {
+        if (he < -10) return (uint16_t)sign;
+        m |= 0x800000u;
+        const int sh = 14 - he;                 /* 14 .. 24 */
+        keep = m >> sh;
+        rest = m & ((1u << sh) - 1u);
+        half_ulp = 1u << (sh - 1);
+        he = 0;
+    } else {
+        keep = m >> 13;
+        rest = m & 0x1fffu;
+        half_ulp = 0x1000u;
+    }
+    uint32_t h = ((uint32_t)he << 10) + keep;  /* a mantissa carry runs into the exponent */
+    if (rest > half_ulp || (rest == half_ulp && (h & 1u))) ++h;
+    return (uint16_t)(sign | h);
+}
+
+LHO_API float lho_f16_bits_to_f32(uint16_t h) {
+    const uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+    const int e = (h >> 10) & 0x1f;
+    const uint32_t m = h & 0x3ffu;
+    float f;
+    if (e == 0) {
+        f = ldexpf((float)m, -24);             /* zero or subnormal */
+    } else if (e == 31) {
+        const uint32_t bits = 0x7f800000u | (m << 13);
+        memcpy(&f, &bits, sizeof f);
+    } else {
+        const uint32_t bits = ((uint32_t)(e - 15 + 127) << 23) | (m << 13);
+        memcpy(&f, &bits, sizeof f);
+    }
+    uint32_t b;
+    memcpy(&b, &f, sizeof b);
+    b |= sign;
+    memcpy(&f, &b, sizeof f);
+    return f;
+}
+
+LHO_API void lho_q4a_quantize_groupwise(const float* src, uint8_t* packed, uint16_t* scales_h,
+                                        uint16_t* zeros_h, int K, int N, int G) {
+    const int groups = K / G;
+    for (int g = 0; g < groups; ++g) {
+        for (int n = 0; n < N; ++n) {
+            float lo = 0.0f, hi = 0.0f;
+            for (int kk = 0; kk < G; ++kk) {
+                const float w = src[(int64_t)(g * G + kk) * N + n];
+                lo = fminf(lo, w);
+                hi = fmaxf(hi, w);
+            }
+            float s = lho_f16_bits_to_f32(lho_f32_to_f16_bits((hi - lo) / 15.0f));
+            if (!(s > 0.0f)) s = 1.0f;
+            long z = lrintf(-lo / s);
+            z = z < 0 ? 0 : (z > 15 ? 15 : z);
+            scales_h[(int64_t)g * N + n] = lho_f32_to_f16_bits(s);
+            zeros_h[(int64_t)g * N + n] = lho_f32_to_f16_bits((float)z);
+        }
+    }
+    for (int r = 0; r < K / 2; ++r) {
+        for (int n = 0; n < N; ++n) {
+            uint8_t byte = 0;
+            for (int half = 0; half < 2; ++half) {
+                const int k = 2 * r + half, g = k / G;
+                const float s = lho_f16_bits_to_f32(scales_h[(int64_t)g * N + n]);
+                const long z = (long)lho_f16_bits_to_f32(zeros_h[(int64_t)g * N + n]);
+                long u = lrintf(src[(int64_t)k * N + n] / s) + z;
+                u = u < 0 ? 0 : (u > 15 ? 15 : u);
+                byte |= (uint8_t)(u << (4 * half));
+            }
+            packed[(int64_t)r * N + n] = byte;
+        }
+    }
+}
+
+static inline int q4a_get(const uint8_t* packed, int k, int n, int N) {
+    const uint8_t b = packed[(int64_t)(k >> 1) * N + n];
+    return (k & 1) ? (b >> 4) : (b & 0xf);
+}
+
+LHO_API void lho_q4a_dequantize_groupwise(const uint8_t* packed, const uint16_t* scales_h,
+                                          const uint16_t* zeros_h, float* dst, int K, int N, int G) {
+    for (int k = 0; k < K; ++k)
+        for (int n = 0; n < N; ++n) {
+            const int g = k / G;
+            const int z = (int)lho_f16_bits_to_f32(zeros_h[(int64_t)g * N + n]);
+            dst[(int64_t)k * N + n] =
+                (float)(q4a_get(packed, k, n, N) - z) * lho_f16_bits_to_f32(scales_h[(int64_t)g * N + n]);
+        }
+}
+
+/* C = beta*C + alpha * A @ dequant(B): group panel first, then fp32 accumulation in k order,
+ * a = alpha * A[i, k] folded in before the product (gemm_quant.cpp:60-80). */
+LHO_API void lho_gemm_w4a16_asym(const float* A, const uint8_t* Bp, const uint16_t* scales_h,
+                                 const uint16_t* zeros_h, float* C, int M, int N, int K, int G,
+                                 float alpha, float beta) {
+    scale_c(C, M, N, beta);
+    float* panel = (float*)malloc(sizeof(float) * (size_t)G * N);
+    for (int k0 = 0; k0 < K; k0 += G) {
+        const int g = k0 / G;
+        for (int kk = 0; kk < G; ++kk)
+            for (int n = 0; n < N; ++n) {
+                const int z = (int)lho_f16_bits_to_f32(zeros_h[(int64_t)g * N + n]);
+                panel[(int64_t)kk * N + n] =
+                    (float)(q4a_get(Bp, k0 + kk, n, N) - z) * lho_f16_bits_to_f32(scales_h[(int64_t)g * N + n]);
+            }
+        for (int i = 0; i < M; ++i) {
+            const float* arow = A + (int64_t)i * K + k0;
+            float* crow = C + (int64_t)i * N;
+            for (int kk = 0; kk < G; ++kk) {
+                const float a = alpha * arow[kk];
+                const float* brow = panel + (int64_t)kk * N;
+                for (int j = 0; j < N; ++j) crow[j] += a * brow[j];
+            }
+        }
+    }
+    free(panel);
+}
+
 /* ------------------------------------------------------------------ */
 
 /* N-sharded W4A16: shard s holds a compact [K/2, n_shard] packed slab, its

@@ -64,6 +64,9 @@ LHR_API uint16_t lhr_f32_to_bf16_bits(float v) { return lh::bfloat16(v).bits; }
 LHR_API float lhr_bf16_bits_to_f32(uint16_t b) {
     return lh::detail::bf16_bits_to_float(b);
 }
+// fp16 conversion of the reference (src/kernels/dtypes.hpp:17-85), for pinning the restatement
+LHR_API uint16_t lhr_f32_to_f16_bits(float v) { return lh::detail::float_to_half_bits(v); }
+LHR_API float lhr_f16_bits_to_f32(uint16_t b) { return lh::detail::half_bits_to_float(b); }
 LHR_API void lhr_round_to_bf16(float* x, int64_t n) {
     for (int64_t i = 0; i < n; ++i)
         x[i] = static_cast<float>(lh::bfloat16(x[i]));

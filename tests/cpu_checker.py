@@ -169,6 +169,34 @@ class Checker:
                                          _p(out), M, N, K, C.c_float(alpha), C.c_float(beta))
         return out
 
+    # -- asymmetric int4 (extension; the compiled reference has no such scheme) ----------
+    def f32_to_f16_bits(self, x):
+        f = self.fn("f32_to_f16_bits", C.c_uint16)
+        return np.array([f(C.c_float(float(v))) for v in np.asarray(x, np.float32).ravel()], np.uint16)
+
+    def q4a_quantize_groupwise(self, w, G):
+        w = np.ascontiguousarray(w, np.float32)
+        K, N = w.shape
+        p = np.zeros((K // 2, N), np.uint8)
+        s = np.zeros((K // G, N), np.uint16)
+        z = np.zeros((K // G, N), np.uint16)
+        self.fn("q4a_quantize_groupwise")(_p(w), _p(p), _p(s), _p(z), K, N, G)
+        return p, s.view(np.float16), z.view(np.float16)
+
+    def q4a_dequantize_groupwise(self, p, s, z, G):
+        K, N = p.shape[0] * 2, p.shape[1]
+        d = np.zeros((K, N), np.float32)
+        self.fn("q4a_dequantize_groupwise")(_p(p, np.uint8), _p(s.view(np.uint16)), _p(z.view(np.uint16)), _p(d), K, N, G)
+        return d
+
+    def gemm_w4a16_asym(self, A, Bp, Bs, Bz, G, C0=None, alpha=1.0, beta=0.0):
+        M, K = A.shape
+        N = Bp.shape[1]
+        out = np.zeros((M, N), np.float32) if C0 is None else C0.copy()
+        self.fn("gemm_w4a16_asym")(_p(A, np.float32), _p(Bp, np.uint8), _p(Bs.view(np.uint16)),
+                                   _p(Bz.view(np.uint16)), _p(out), M, N, K, G, C.c_float(alpha), C.c_float(beta))
+        return out
+
     # -- decode-step glue ---------------------------------------------------
     def rmsnorm(self, x, gamma, eps=1e-5):
         x = np.ascontiguousarray(x, np.float32)

@@ -223,9 +223,41 @@ def glue_fixtures():
     save("swiglu_r2d1024", x=x, y=ref.swiglu(x))
 
 
+def asym_fixtures():
+    """Asymmetric int4 (fp16 scale and zero-point per group).  The reference has no such scheme, so
+    these vectors come from the C restatement of the rules written in include/lhb200.h (parity
+    unpinned); only the fp16 conversion inside them is pinned, against lh::half, here."""
+    port = Checker("lho")
+    rng = np.random.default_rng(20246)
+    if ref_available():
+        ref = Checker("lhr")
+        x = np.concatenate([rng.standard_normal(4096).astype(np.float32) *
+                            rng.choice([1e-8, 1e-5, 1e-3, 1.0, 100.0, 70000.0], 4096).astype(np.float32),
+                            np.array([0.0, -0.0, 65504.0, 65520.0, 6.1e-5, 5.96e-8, 2.98e-8, 1.0009765625,
+                                      1.00048828125, 1.00146484375, np.inf, -np.inf], np.float32)])
+        bits = ref.f32_to_f16_bits(x)
+        assert np.array_equal(bits, port.f32_to_f16_bits(x))
+        save("f16_round", x=x, bits=bits)
+    for name, K, N, G, M in [("q4a_k256n48g128", 256, 48, 128, 3), ("q4a_k128n32g32", 128, 32, 32, 5),
+                             ("q4a_k512n256g128", 512, 256, 128, 1)]:
+        w = (rng.standard_normal((K, N)) * 0.02).astype(np.float32)
+        w[: G, 1] = 0.0                          # an all-zero group: scale 1, zero-point 0
+        w[:, 2] = np.abs(w[:, 2])                # one-sided groups: zero-point 0 / 15
+        w[:, 3] = -np.abs(w[:, 3])
+        p, s, z = port.q4a_quantize_groupwise(w, G)
+        A = rng.standard_normal((M, K)).astype(np.float32)
+        C0 = rng.standard_normal((M, N)).astype(np.float32)
+        save(name, w=w, G=np.int32(G), p=p, s=s.view(np.uint16), z=z.view(np.uint16),
+             d=port.q4a_dequantize_groupwise(p, s, z, G), A=A, C=port.gemm_w4a16_asym(A, p, s, z, G),
+             C0=C0, C_ab=port.gemm_w4a16_asym(A, p, s, z, G, C0, alpha=0.5, beta=2.0))
+
+
 if __name__ == "__main__":
-    if "--glue" in sys.argv:        # only the decode-step glue fixtures (the others stay as they are)
+    if "--asym" in sys.argv:
+        asym_fixtures()
+    elif "--glue" in sys.argv:        # only the decode-step glue fixtures (the others stay as they are)
         glue_fixtures()
     else:
         main()
         glue_fixtures()
+        asym_fixtures()

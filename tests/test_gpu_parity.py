@@ -458,3 +458,45 @@ def test_swiglu_against_checker(chk, rows, dim):
     rng = np.random.default_rng(rows * 3 + dim)
     x = (rng.standard_normal((rows, 2 * dim)) * 3).astype(np.float32)
     assert_close(host(lb.swiglu(dev(x))), chk.swiglu(x), what=f"swiglu {rows}x{dim}")
+
+
+# --------------------------------------------------------------------------- asymmetric int4
+
+@pytest.mark.parametrize("name", gio.names("q4a_"))
+def test_q4a_golden_bits_and_gemm(name):
+    g = gio.load(name)
+    G = int(g["G"])
+    p, s, z = lb.q4a_quantize_groupwise(dev(g["w"]), G)
+    assert_same_bits(host(p), g["p"], "packed")
+    assert_same_bits(host(s).view(np.uint16), g["s"], "scales")
+    assert_same_bits(host(z).view(np.uint16), g["z"], "zero-points")
+    assert_same_bits(host(lb.q4a_dequantize_groupwise(p, s, z, G)), g["d"], "dequant")
+    assert_close(host(lb.gemm_w4a16_asym(dev(g["A"]), p, s, z, G)), g["C"], what=name)
+    got = lb.gemm_w4a16_asym(dev(g["A"]), p, s, z, G, C=dev(g["C0"]), alpha=0.5, beta=2.0)
+    assert_close(host(got), g["C_ab"], what=name + " alpha/beta")
+    poll_ok()
+
+
+@pytest.mark.parametrize("M", [1, 2, 8, 16, 32])
+@pytest.mark.parametrize("N,K,G", [(1040, 1024, 128), (14336, 4096, 128), (256, 384, 64)])
+def test_w4a16_asym_against_checker(lib, M, N, K, G):
+    from cpu_checker import Checker
+    chk = Checker("lho")            # the scheme is an extension: only the C statement of its rules has it
+    rng = np.random.default_rng(7000 + M + N + K)
+    A = chk.round_to_bf16((rng.standard_normal((M, K)) * rng.choice([1e-2, 1.0])).astype(np.float32))
+    W = (rng.standard_normal((K, N)) * 0.02 + 0.01).astype(np.float32)
+    p0, s0, z0 = chk.q4a_quantize_groupwise(W, G)
+    p, s, z = lb.q4a_quantize_groupwise(dev(W), G)
+    assert_same_bits(host(p), p0, "packed"); assert_same_bits(host(s).view(np.uint16), s0.view(np.uint16), "scales")
+    assert_same_bits(host(z).view(np.uint16), z0.view(np.uint16), "zero-points")
+    want = chk.gemm_w4a16_asym(A, p0, s0, z0, G)
+    got = lb.gemm_w4a16_asym(dev(A), p, s, z, G)
+    assert_close(host(got), want,
+                 what=f"w4a16 asym M={M} N={N} K={K} G={G} fast={lib.lhb_gemm_w4a16_asym_fast_path(M, N, K, G)}")
+    # activations a hundred times larger: the CPU loop's own fp32 rounding (partial sums of ~1e2) is then
+    # above 1e-4, so the yardstick is the fp64 product with the dequantised weights, absolute bound scaled
+    A100 = (A * 100.0).astype(np.float32)
+    d = chk.q4a_dequantize_groupwise(p0, s0, z0, G).astype(np.float64)
+    assert_close(host(lb.gemm_w4a16_asym(dev(A100), p, s, z, G)), A100.astype(np.float64) @ d, atol=1e-2,
+                 what="w4a16 asym, activations x100, vs fp64")
+    poll_ok()

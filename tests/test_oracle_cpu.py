@@ -142,6 +142,32 @@ def test_swiglu_golden(name):
     same(port.swiglu(g["x"]), g["y"])
 
 
+def test_f16_conversion_matches_reference_bits():
+    g = gio.load("f16_round")
+    assert np.array_equal(port.f32_to_f16_bits(g["x"]), g["bits"])
+
+
+@pytest.mark.parametrize("name", gio.names("q4a_"))
+def test_q4a_fixture_properties(name):
+    """Asymmetric int4: the fixture reproduces, zero-points are integers in [0, 15], zero is exactly
+    representable, the round trip is within half a step, and the GEMM equals A @ dequant."""
+    g = gio.load(name)
+    G = int(g["G"])
+    p, s, z = port.q4a_quantize_groupwise(g["w"], G)
+    same(p, g["p"]); same(s.view(np.uint16), g["s"]); same(z.view(np.uint16), g["z"])
+    zf, sf = z.astype(np.float32), s.astype(np.float32)
+    assert np.all(zf == np.round(zf)) and zf.min() >= 0 and zf.max() <= 15
+    d = port.q4a_dequantize_groupwise(p, s, z, G)
+    same(d, g["d"])
+    step = np.repeat(sf, G, axis=0)
+    assert np.all(np.abs(g["w"] - d) <= 0.5 * step * (1 + 1e-3) + 1e-12)
+    assert np.all(d[g["w"] == 0.0] == 0.0)
+    same(port.gemm_w4a16_asym(g["A"], p, s, z, G), g["C"])
+    same(port.gemm_w4a16_asym(g["A"], p, s, z, G, g["C0"], alpha=0.5, beta=2.0), g["C_ab"])
+    ref = g["A"].astype(np.float64) @ d.astype(np.float64)
+    assert np.allclose(g["C"], ref, rtol=1e-4, atol=1e-5)
+
+
 def test_port_matches_compiled_reference_on_larger_inputs():
     ref = Checker("lhr")
     rng = np.random.default_rng(7)
