@@ -301,6 +301,34 @@ LHB_API int32_t* lhb_cm_block_tables(lhb_cache_manager* cm);
 LHB_API int32_t* lhb_cm_seq_lens(lhb_cache_manager* cm);
 LHB_API int lhb_cm_max_blocks_per_req(const lhb_cache_manager* cm);
 
+/* ---- continuous-batching scheduler over the device cache manager ------------------- */
+
+/* lh::Scheduler (src/runtime/scheduler.hpp:47-105): FIFO admission gated by max_concurrent and by an
+ * all-or-nothing reservation of prompt + 1 tokens; commit_step counts one produced token per active
+ * request, retires it on its flag or at max_new_tokens, else reserves the next slot.  Request bodies
+ * are reduced to (prompt length, max_new_tokens): the scheduler never reads token values.
+ * prepare_step returns the number of active requests, writes their ids (prepare order) to ids_out
+ * when it is not NULL, and leaves the dense view of the reference's ActiveStep - block tables
+ * [n_active, max_blocks_per_req] padded with -1 and seq_lens [n_active] - in device buffers
+ * (lhb_sched_block_tables / lhb_sched_seq_lens), gathered on `stream` from the cache manager's
+ * resident rows: only the active ids cross PCIe.  The view's width is the cache manager's fixed
+ * max_blocks_per_req, not the step's maximum.  A scheduler over a detached cache manager keeps the
+ * bookkeeping only. */
+typedef struct lhb_scheduler lhb_scheduler;
+LHB_API int lhb_sched_create(lhb_cache_manager* cm, int max_concurrent, lhb_scheduler** out);
+LHB_API int lhb_sched_destroy(lhb_scheduler* s);
+LHB_API int lhb_sched_submit(lhb_scheduler* s, int prompt_len, int max_new_tokens);   /* request id */
+LHB_API int lhb_sched_has_work(const lhb_scheduler* s);
+LHB_API int lhb_sched_queue_depth(const lhb_scheduler* s);
+LHB_API int lhb_sched_active_size(const lhb_scheduler* s);
+LHB_API double lhb_sched_last_step_occupancy(const lhb_scheduler* s);
+LHB_API int lhb_sched_generated(const lhb_scheduler* s, int id);
+LHB_API int lhb_sched_prepare_step(lhb_scheduler* s, int32_t* ids_out, int cap, void* stream);
+LHB_API int lhb_sched_commit_step(lhb_scheduler* s, const uint8_t* completed, int n, void* stream);
+LHB_API int32_t* lhb_sched_block_tables(lhb_scheduler* s);
+LHB_API int32_t* lhb_sched_seq_lens(lhb_scheduler* s);
+LHB_API int lhb_sched_max_blocks_per_req(const lhb_scheduler* s);
+
 #ifdef __cplusplus
 }
 #endif

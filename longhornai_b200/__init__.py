@@ -17,6 +17,6 @@ from .kernels import (Context, default_context, gemm_w4a16_groupwise, gemm_w8a8,
                       q8_dequantize_per_col, q8_dequantize_per_row, q8_quantize_per_col,
                       q8_quantize_per_row, rmsnorm, rope, rope_decode_batched, swiglu,
                       gemm_w4a16_asym, q4a_dequantize_groupwise, q4a_quantize_groupwise)
-from .runtime import DeviceCacheManager
+from .runtime import ActiveStep, DeviceCacheManager, DeviceScheduler
 
 __all__ = [n for n in dir() if not n.startswith("_")]

@@ -90,6 +90,19 @@ SIGNATURES = {
     "lhb_cm_block_tables": (_vp, [_vp]),
     "lhb_cm_seq_lens": (_vp, [_vp]),
     "lhb_cm_max_blocks_per_req": (_i, [_vp]),
+    "lhb_sched_create": (_i, [_vp, _i, C.POINTER(_vp)]),
+    "lhb_sched_destroy": (_i, [_vp]),
+    "lhb_sched_submit": (_i, [_vp, _i, _i]),
+    "lhb_sched_has_work": (_i, [_vp]),
+    "lhb_sched_queue_depth": (_i, [_vp]),
+    "lhb_sched_active_size": (_i, [_vp]),
+    "lhb_sched_last_step_occupancy": (C.c_double, [_vp]),
+    "lhb_sched_generated": (_i, [_vp, _i]),
+    "lhb_sched_prepare_step": (_i, [_vp, _vp, _i, _vp]),
+    "lhb_sched_commit_step": (_i, [_vp, _vp, _i, _vp]),
+    "lhb_sched_block_tables": (_vp, [_vp]),
+    "lhb_sched_seq_lens": (_vp, [_vp]),
+    "lhb_sched_max_blocks_per_req": (_i, [_vp]),
 }
 
 _lib = None

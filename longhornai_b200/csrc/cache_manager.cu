@@ -226,3 +226,176 @@ int32_t* lhb_cm_seq_lens(lhb_cache_manager* cm) { return cm ? cm->d_seq_lens : n
 int lhb_cm_max_blocks_per_req(const lhb_cache_manager* cm) { return cm ? cm->max_blocks : 0; }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Continuous-batching scheduler over the device cache manager.
+//
+// Lifecycle rules are lh::Scheduler's (src/runtime/scheduler.cpp:11-102): FIFO
+// admission gated by the active-set cap and by all-or-nothing reservation of
+// prompt + 1 tokens, no admission past a blocked queue head; every committed
+// step counts one produced token, retires a request on its flag or on
+// max_new_tokens, otherwise reserves the next slot (retiring the request if the
+// pool is exhausted) and bumps its length.
+//
+// What differs is where the step view lives.  The reference rebuilds a dense
+// [n_active, max_blocks] table on the host every step (scheduler.cpp:41-58).
+// Here the per-request rows already sit in device memory (patched in place by
+// the cache manager), so prepare_step uploads only the active request ids
+// (4 bytes each) and a gather kernel writes the dense table and seq_lens of the
+// active set, in active order, into device buffers the batched kernels read.
+// Its width is the table's fixed max_blocks_per_req, not the step's maximum.
+// ---------------------------------------------------------------------------
+#include <deque>
+#include <unordered_map>
+
+struct lhb_scheduler {
+    lhb_cache_manager* cm = nullptr;
+    int max_concurrent = 0;
+    struct Req { int prompt_len; int max_new; };
+    std::deque<std::pair<int, Req>> queue;
+    struct Active { Req req; int produced; };
+    std::unordered_map<int, Active> active;
+    std::vector<int> order;                       // active ids in prepare_step order
+    std::unordered_map<int, int> generated;
+    double last_occ = 0.0;
+    int32_t* d_ids = nullptr;                     // [max_concurrent]
+    int32_t* d_tables = nullptr;                  // [max_concurrent, max_blocks]
+    int32_t* d_seq_lens = nullptr;                // [max_concurrent]
+    int32_t* h_ids = nullptr;                     // pinned staging for the id upload
+};
+
+namespace {
+
+__global__ void gather_active_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ all_tables,
+                                     const int32_t* __restrict__ all_lens, int32_t* __restrict__ tables,
+                                     int32_t* __restrict__ lens, int max_blocks) {
+    const int row = blockIdx.x, id = ids[row];
+    for (int b = threadIdx.x; b < max_blocks; b += blockDim.x)
+        tables[static_cast<int64_t>(row) * max_blocks + b] = all_tables[static_cast<int64_t>(id) * max_blocks + b];
+    if (threadIdx.x == 0) lens[row] = all_lens[id];
+}
+
+bool sched_try_admit(lhb_scheduler* s, int id, const lhb_scheduler::Req& r, void* stream) {
+    if (lhb_cm_ensure_capacity(s->cm, id, r.prompt_len + 1, stream) != 1) return false;
+    lhb_cm_set_seq_len(s->cm, id, r.prompt_len, stream);
+    s->active.emplace(id, lhb_scheduler::Active{r, 0});
+    s->order.push_back(id);
+    return true;
+}
+
+void sched_retire(lhb_scheduler* s, int id, int produced, void* stream) {
+    s->generated[id] = produced;
+    lhb_cm_release_request(s->cm, id, stream);
+    s->active.erase(id);
+}
+
+}  // namespace
+
+extern "C" {
+
+int lhb_sched_create(lhb_cache_manager* cm, int max_concurrent, lhb_scheduler** out) {
+    if (!cm || !out) return LHB_ERR_NULL;
+    if (max_concurrent < 0 || max_concurrent > cm->max_requests) return LHB_ERR_BAD_SHAPE;
+    auto* s = new lhb_scheduler();
+    s->cm = cm;
+    s->max_concurrent = max_concurrent;
+    if (cm->ctx && max_concurrent > 0) {
+        const size_t n = static_cast<size_t>(max_concurrent);
+        if (cudaMalloc(&s->d_ids, n * 4) != cudaSuccess || cudaMalloc(&s->d_seq_lens, n * 4) != cudaSuccess ||
+            cudaMalloc(&s->d_tables, n * cm->max_blocks * 4) != cudaSuccess ||
+            cudaMallocHost(&s->h_ids, n * 4) != cudaSuccess) {
+            cudaGetLastError();
+            lhb_sched_destroy(s);
+            return LHB_ERR_CUDA;
+        }
+    }
+    *out = s;
+    return LHB_OK;
+}
+
+int lhb_sched_destroy(lhb_scheduler* s) {
+    if (!s) return LHB_OK;
+    cudaFree(s->d_ids);
+    cudaFree(s->d_seq_lens);
+    cudaFree(s->d_tables);
+    cudaFreeHost(s->h_ids);
+    delete s;
+    return LHB_OK;
+}
+
+int lhb_sched_submit(lhb_scheduler* s, int prompt_len, int max_new_tokens) {
+    if (!s || prompt_len < 0) return -1;
+    const int id = lhb_cm_create_request(s->cm);
+    if (id < 0) return -1;
+    s->queue.emplace_back(id, lhb_scheduler::Req{prompt_len, max_new_tokens});
+    return id;
+}
+
+int lhb_sched_has_work(const lhb_scheduler* s) { return s && (!s->queue.empty() || !s->active.empty()) ? 1 : 0; }
+int lhb_sched_queue_depth(const lhb_scheduler* s) { return s ? static_cast<int>(s->queue.size()) : 0; }
+int lhb_sched_active_size(const lhb_scheduler* s) { return s ? static_cast<int>(s->active.size()) : 0; }
+double lhb_sched_last_step_occupancy(const lhb_scheduler* s) { return s ? s->last_occ : 0.0; }
+int lhb_sched_generated(const lhb_scheduler* s, int id) {
+    if (!s) return 0;
+    auto it = s->generated.find(id);
+    return it == s->generated.end() ? 0 : it->second;
+}
+
+int lhb_sched_prepare_step(lhb_scheduler* s, int32_t* ids_out, int cap, void* stream) {
+    if (!s) return LHB_ERR_NULL;
+    while (!s->queue.empty() && static_cast<int>(s->active.size()) < s->max_concurrent) {
+        auto& head = s->queue.front();
+        if (!sched_try_admit(s, head.first, head.second, stream)) break;
+        s->queue.pop_front();
+    }
+    const int n = static_cast<int>(s->order.size());
+    s->last_occ = s->max_concurrent > 0 ? static_cast<double>(s->active.size()) / s->max_concurrent : 0.0;
+    if (ids_out) {
+        if (cap < n) return LHB_ERR_BAD_SHAPE;
+        for (int i = 0; i < n; ++i) ids_out[i] = s->order[i];
+    }
+    if (s->cm->ctx && n > 0) {
+        cudaStream_t st = as_stream(stream);
+        // the staging buffer may still be in flight from the previous step on another stream
+        LHB_CUDA(cudaStreamSynchronize(st));
+        for (int i = 0; i < n; ++i) s->h_ids[i] = s->order[i];
+        LHB_CUDA(cudaMemcpyAsync(s->d_ids, s->h_ids, sizeof(int32_t) * n, cudaMemcpyHostToDevice, st));
+        gather_active_kernel<<<n, 128, 0, st>>>(s->d_ids, s->cm->d_tables, s->cm->d_seq_lens, s->d_tables,
+                                                s->d_seq_lens, s->cm->max_blocks);
+        LHB_LAUNCH_CHECK();
+    }
+    return n;
+}
+
+int lhb_sched_commit_step(lhb_scheduler* s, const uint8_t* completed, int n, void* stream) {
+    if (!s || (!completed && n > 0)) return LHB_ERR_NULL;
+    if (n != static_cast<int>(s->order.size())) return LHB_ERR_BAD_SHAPE;
+    std::vector<int> survivors;
+    survivors.reserve(s->order.size());
+    for (int i = 0; i < n; ++i) {
+        const int id = s->order[i];
+        auto it = s->active.find(id);
+        if (it == s->active.end()) continue;
+        auto& st = it->second;
+        ++st.produced;
+        if (completed[i] || st.produced >= st.req.max_new) {
+            sched_retire(s, id, st.produced, stream);
+            continue;
+        }
+        const int new_len = lhb_cm_seq_len(s->cm, id) + 1;
+        if (lhb_cm_ensure_capacity(s->cm, id, new_len + 1, stream) != 1) {   // pool exhausted: finish early
+            sched_retire(s, id, st.produced, stream);
+            continue;
+        }
+        lhb_cm_set_seq_len(s->cm, id, new_len, stream);
+        survivors.push_back(id);
+    }
+    s->order.swap(survivors);
+    return LHB_OK;
+}
+
+int32_t* lhb_sched_block_tables(lhb_scheduler* s) { return s ? s->d_tables : nullptr; }
+int32_t* lhb_sched_seq_lens(lhb_scheduler* s) { return s ? s->d_seq_lens : nullptr; }
+int lhb_sched_max_blocks_per_req(const lhb_scheduler* s) { return s ? s->cm->max_blocks : 0; }
+
+}  // extern "C"

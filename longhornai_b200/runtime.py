@@ -129,3 +129,89 @@ class DeviceCacheManager:
             self.close()
         except Exception:
             pass
+
+
+class ActiveStep:
+    """The view `Scheduler::prepare_step` returns (src/runtime/scheduler.hpp:38-45): ids in step order and,
+    on a device-backed scheduler, CUDA tensors `block_tables` [n_active, max_blocks_per_req] (padding -1)
+    and `seq_lens` [n_active] aliasing the scheduler's device buffers (valid until the next prepare_step)."""
+
+    def __init__(self, ids, block_tables=None, seq_lens=None, max_blocks_per_req=0):
+        self.ids = ids
+        self.block_tables = block_tables
+        self.seq_lens = seq_lens
+        self.max_blocks_per_req = max_blocks_per_req
+
+    def n_active(self) -> int:
+        return len(self.ids)
+
+
+class DeviceScheduler:
+    """lh::Scheduler (src/runtime/scheduler.hpp:47-105) over a DeviceCacheManager: same admission and
+    retirement rules, with the step's dense block tables gathered on the GPU from the manager's resident
+    rows instead of rebuilt on the host.  Requests are (prompt length, max_new_tokens)."""
+
+    def __init__(self, manager: DeviceCacheManager, max_concurrent: int):
+        self.lib = manager.lib
+        self.manager = manager
+        self.max_concurrent = max_concurrent
+        h = C.c_void_p()
+        check(self.lib.lhb_sched_create(manager.handle, max_concurrent, C.byref(h)), "lhb_sched_create")
+        self.handle = h
+        self._ids = np.zeros(max(1, max_concurrent), np.int32)
+
+    def submit(self, prompt_len: int, max_new_tokens: int) -> int:
+        rid = self.lib.lhb_sched_submit(self.handle, int(prompt_len), int(max_new_tokens))
+        if rid < 0:
+            raise RuntimeError("lhb_sched_submit failed (no free request row)")
+        return rid
+
+    def has_work(self) -> bool:
+        return bool(self.lib.lhb_sched_has_work(self.handle))
+
+    def queue_depth(self) -> int:
+        return self.lib.lhb_sched_queue_depth(self.handle)
+
+    def active_size(self) -> int:
+        return self.lib.lhb_sched_active_size(self.handle)
+
+    def last_step_occupancy(self) -> float:
+        return float(self.lib.lhb_sched_last_step_occupancy(self.handle))
+
+    def generated(self, rid: int) -> int:
+        return self.lib.lhb_sched_generated(self.handle, rid)
+
+    def prepare_step(self) -> ActiveStep:
+        n = self.lib.lhb_sched_prepare_step(self.handle, self._ids.ctypes.data_as(C.c_void_p), self._ids.size,
+                                            self.manager._stream())
+        if n < 0:
+            check(n, "lhb_sched_prepare_step")
+        ids = self._ids[:n].tolist()
+        mb = self.lib.lhb_sched_max_blocks_per_req(self.handle)
+        if self.manager.ctx is None or n == 0:
+            return ActiveStep(ids, None, None, mb)
+        import torch
+        dev = f"cuda:{self.manager.ctx.device}"
+
+        def view(ptr, count, shape):
+            iface = {"shape": (count * 4,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+            holder = type("_DevMem", (), {"__cuda_array_interface__": iface})()
+            return torch.as_tensor(holder, device=dev).view(torch.int32).view(shape)
+        return ActiveStep(ids, view(self.lib.lhb_sched_block_tables(self.handle), n * mb, (n, mb)),
+                          view(self.lib.lhb_sched_seq_lens(self.handle), n, (n,)), mb)
+
+    def commit_step(self, completed) -> None:
+        flags = np.ascontiguousarray(np.asarray(completed, dtype=np.uint8))
+        check(self.lib.lhb_sched_commit_step(self.handle, flags.ctypes.data_as(C.c_void_p), int(flags.size),
+                                             self.manager._stream()), "lhb_sched_commit_step")
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.lib.lhb_sched_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -20,6 +20,7 @@
 #include "kernels/quant.hpp"
 #include "kernels/rope.hpp"
 #include "runtime/cache_manager.hpp"
+#include "runtime/scheduler.hpp"
 
 #ifdef _OPENMP
 #include <omp.h>
@@ -254,3 +255,50 @@ LHR_API int lhr_cm_reference_block(void* m, int id, int logical, int physical) {
 }
 LHR_API int lhr_cm_allocate_block(void* m) { return static_cast<lh::CacheManager*>(m)->allocate_block(); }
 LHR_API void lhr_cm_release_block(void* m, int b) { static_cast<lh::CacheManager*>(m)->release_block(b); }
+
+// --- the reference scheduler, for pinning the device scheduler's lifecycle rules
+//     (src/runtime/scheduler.hpp).  Requests are (prompt length, max_new_tokens).
+struct RefSched {
+    lh::CacheManager* mgr;
+    lh::Scheduler* sched;
+    lh::ActiveStep last;
+};
+LHR_API void* lhr_sched_create(void* cm, int max_concurrent) {
+    auto* m = static_cast<lh::CacheManager*>(cm);
+    return new RefSched{m, new lh::Scheduler(*m, max_concurrent), {}};
+}
+LHR_API void lhr_sched_destroy(void* s) {
+    auto* r = static_cast<RefSched*>(s);
+    delete r->sched;
+    delete r;
+}
+LHR_API int lhr_sched_submit(void* s, int prompt_len, int max_new_tokens) {
+    lh::Request q;
+    q.prompt_tokens.assign(static_cast<size_t>(prompt_len), 0);
+    q.max_new_tokens = max_new_tokens;
+    return static_cast<RefSched*>(s)->sched->submit(std::move(q));
+}
+LHR_API int lhr_sched_has_work(void* s) { return static_cast<RefSched*>(s)->sched->has_work() ? 1 : 0; }
+LHR_API int lhr_sched_queue_depth(void* s) { return static_cast<int>(static_cast<RefSched*>(s)->sched->queue_depth()); }
+LHR_API int lhr_sched_active_size(void* s) { return static_cast<int>(static_cast<RefSched*>(s)->sched->active_size()); }
+LHR_API double lhr_sched_last_step_occupancy(void* s) { return static_cast<RefSched*>(s)->sched->last_step_occupancy(); }
+LHR_API int lhr_sched_generated(void* s, int id) { return static_cast<RefSched*>(s)->sched->generated(id); }
+// prepare_step; returns n_active and keeps the view for the getters below
+LHR_API int lhr_sched_prepare_step(void* s) {
+    auto* r = static_cast<RefSched*>(s);
+    r->last = r->sched->prepare_step();
+    return r->last.n_active();
+}
+LHR_API int lhr_sched_step_max_blocks(void* s) { return static_cast<RefSched*>(s)->last.max_blocks_per_req; }
+LHR_API void lhr_sched_step_view(void* s, int32_t* ids, int32_t* seq_lens, int32_t* tables) {
+    auto* r = static_cast<RefSched*>(s);
+    const auto& v = r->last;
+    for (size_t i = 0; i < v.ids.size(); ++i) { ids[i] = v.ids[i]; seq_lens[i] = v.seq_lens[i]; }
+    for (size_t i = 0; i < v.block_tables.size(); ++i) tables[i] = v.block_tables[i];
+}
+LHR_API void lhr_sched_commit_step(void* s, const uint8_t* completed, int n) {
+    std::vector<bool> c(static_cast<size_t>(n));
+    for (int i = 0; i < n; ++i) c[i] = completed[i] != 0;
+    static_cast<RefSched*>(s)->sched->commit_step(c, std::vector<int32_t>(static_cast<size_t>(n), 0));
+}
+

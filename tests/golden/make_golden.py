@@ -252,8 +252,53 @@ def asym_fixtures():
              C0=C0, C_ab=port.gemm_w4a16_asym(A, p, s, z, G, C0, alpha=0.5, beta=2.0))
 
 
+def scheduler_trace():
+    """Step-by-step record of the reference's own Scheduler (src/runtime/scheduler.cpp) on a mixed workload
+    in the style of tests/test_scheduler.cpp (MixedWorkloadHitsHighOccupancy, AdmissionStallsOnOOM): more
+    requests than the active set holds, a pool small enough to stall admission, random EOS flags."""
+    import json
+    if not ref_available():
+        raise SystemExit("oracle/_ref/liblh_ref.so missing: run `make -C oracle ref` first")
+    lib = Checker("lhr").lib
+    lib.lhr_cm_create.restype = C.c_void_p
+    lib.lhr_sched_create.restype = C.c_void_p
+    lib.lhr_sched_last_step_occupancy.restype = C.c_double
+    num_blocks, block_size, max_concurrent, n_requests = 24, 4, 6, 40
+    L = Layout(num_blocks, block_size, 2, 8)
+    m = C.c_void_p(lib.lhr_cm_create(C.byref(L)))
+    sch = C.c_void_p(lib.lhr_sched_create(m, max_concurrent))
+    rng = np.random.default_rng(4242)
+    reqs = [(int(rng.integers(1, 14)), int(rng.integers(1, 9))) for _ in range(n_requests)]
+    ids = [lib.lhr_sched_submit(sch, p, n) for p, n in reqs]
+    steps = []
+    while lib.lhr_sched_has_work(sch):
+        n = lib.lhr_sched_prepare_step(sch)
+        if n == 0:
+            break
+        mb = lib.lhr_sched_step_max_blocks(sch)
+        a_ids, lens, tab = np.zeros(n, np.int32), np.zeros(n, np.int32), np.zeros(n * mb, np.int32)
+        lib.lhr_sched_step_view(sch, a_ids.ctypes.data_as(C.c_void_p), lens.ctypes.data_as(C.c_void_p),
+                                tab.ctypes.data_as(C.c_void_p))
+        flags = (rng.random(n) < 0.08).astype(np.uint8)
+        steps.append({"ids": a_ids.tolist(), "seq_lens": lens.tolist(), "max_blocks": int(mb),
+                      "tables": tab.reshape(n, mb).tolist(), "queue": lib.lhr_sched_queue_depth(sch),
+                      "occupancy": lib.lhr_sched_last_step_occupancy(sch), "free": lib.lhr_cm_num_free(m),
+                      "completed": flags.tolist()})
+        lib.lhr_sched_commit_step(sch, flags.ctypes.data_as(C.c_void_p), n)
+    out = {"num_blocks": num_blocks, "block_size": block_size, "max_concurrent": max_concurrent,
+           "requests": reqs, "submitted_ids": ids, "steps": steps,
+           "generated": [lib.lhr_sched_generated(sch, i) for i in ids], "free_at_end": lib.lhr_cm_num_free(m)}
+    lib.lhr_sched_destroy(sch)
+    lib.lhr_cm_destroy(m)
+    with open(os.path.join(HERE, "scheduler_trace.json"), "w") as f:
+        json.dump(out, f)
+    print("wrote scheduler_trace:", len(steps), "steps,", sum(1 for s in steps if s["queue"]), "with a queue")
+
+
 if __name__ == "__main__":
-    if "--asym" in sys.argv:
+    if "--sched" in sys.argv:
+        scheduler_trace()
+    elif "--asym" in sys.argv:
         asym_fixtures()
     elif "--glue" in sys.argv:        # only the decode-step glue fixtures (the others stay as they are)
         glue_fixtures()
@@ -261,3 +306,4 @@ if __name__ == "__main__":
         main()
         glue_fixtures()
         asym_fixtures()
+        scheduler_trace()

@@ -104,3 +104,37 @@ def test_cache_manager_refcounts_and_release():
     cm.release_block(b)
     cm.release_block(b)                                # double release is ignored
     assert cm.num_free_blocks() == 4
+
+
+def _replay_scheduler(trace, manager, sched, check_step):
+    ids = [sched.submit(p, n) for p, n in trace["requests"]]
+    assert ids == trace["submitted_ids"]
+    for want in trace["steps"]:
+        assert sched.has_work()
+        step = sched.prepare_step()
+        assert step.ids == want["ids"]
+        assert sched.queue_depth() == want["queue"]
+        assert abs(sched.last_step_occupancy() - want["occupancy"]) < 1e-12
+        assert manager.num_free_blocks() == want["free"]
+        for rid, ln, row in zip(step.ids, want["seq_lens"], want["tables"]):
+            assert manager.seq_len(rid) == ln
+            assert manager.block_table(rid) == [b for b in row if b >= 0]
+        check_step(step, want)
+        sched.commit_step(want["completed"])
+    assert not sched.has_work() or sched.prepare_step().n_active() == 0
+    assert [sched.generated(i) for i in ids] == trace["generated"]
+    assert manager.num_free_blocks() == trace["free_at_end"]
+
+
+def test_scheduler_follows_the_reference_step_by_step():
+    """The scheduler over a detached (host-only) cache manager reproduces a recorded run of the reference's
+    own Scheduler: admissions, stalls on a full pool, retirements, per-step ids / lengths / block tables."""
+    import json
+    import longhornai_b200 as lb
+    trace = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "scheduler_trace.json")))
+    L = lb.PagedLayout(trace["num_blocks"], trace["block_size"], 2, 8)
+    mgr = lb.DeviceCacheManager(L, max_requests=64, max_blocks_per_req=8, detached=True)
+    sched = lb.DeviceScheduler(mgr, trace["max_concurrent"])
+    _replay_scheduler(trace, mgr, sched, lambda step, want: None)
+    sched.close()
+    mgr.close()

@@ -500,3 +500,31 @@ def test_w4a16_asym_against_checker(lib, M, N, K, G):
     assert_close(host(lb.gemm_w4a16_asym(dev(A100), p, s, z, G)), A100.astype(np.float64) @ d, atol=1e-2,
                  what="w4a16 asym, activations x100, vs fp64")
     poll_ok()
+
+
+# --------------------------------------------------------------------------- scheduler on the device tables
+
+def test_scheduler_device_view_matches_reference_trace():
+    """Device-backed scheduler: the dense block tables and seq_lens gathered on the GPU for every step equal
+    the view the reference's Scheduler built on the host (recorded trace), padded to the fixed table width."""
+    import json
+    import os
+    from test_cabi_cpu import _replay_scheduler
+    trace = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "scheduler_trace.json")))
+    L = lb.PagedLayout(trace["num_blocks"], trace["block_size"], 2, 8)
+    mgr = lb.DeviceCacheManager(L, max_requests=64, max_blocks_per_req=8)
+    sched = lb.DeviceScheduler(mgr, trace["max_concurrent"])
+
+    def check_step(step, want):
+        n, mb = len(want["ids"]), step.max_blocks_per_req
+        torch.cuda.synchronize()
+        tab = host(step.block_tables)
+        assert tab.shape == (n, mb)
+        ref = np.full((n, mb), -1, np.int32)
+        ref[:, :want["max_blocks"]] = np.asarray(want["tables"], np.int32).reshape(n, want["max_blocks"])
+        assert np.array_equal(tab, ref)
+        assert host(step.seq_lens).tolist() == want["seq_lens"]
+    _replay_scheduler(trace, mgr, sched, check_step)
+    sched.close()
+    mgr.close()
+    poll_ok()
