@@ -313,6 +313,8 @@ def bench_extra(torch, lb, steps, warmup, hbm_peak):
     torch.cuda.empty_cache()
     out["w8a8_prefill"] = bench_w8a8(torch, lb, min(steps, 5), 3)
     torch.cuda.empty_cache()
+    out["fp8_prefill"] = bench_fp8(torch, lb, min(steps, 5), 3)
+    torch.cuda.empty_cache()
     out["decode_step_cfg4"] = bench_decode_step(torch, lb, min(steps, 5), 3, hbm_peak)
     torch.cuda.empty_cache()
     return out
@@ -398,6 +400,26 @@ def bench_decode_step(torch, lb, steps, warmup, hbm_peak, layers=32, batch=32, c
         out["sharding"] = (f"projections N/{world}, attention {cfg.n_kv_heads // world} KV heads per rank, "
                            f"4 all-gathers per layer")
     return out
+
+
+def bench_fp8(torch, lb, steps, warmup, M=8192, K=8192, N=28672):
+    """The fifth config's shape with E4M3 operands and per-tensor scales (lh::gemm_fp8_e4m3) on tcgen05."""
+    gen = torch.Generator(device="cuda").manual_seed(20246)
+    A, sa = lb.fp8_quantize_per_tensor(torch.randn(M, K, device="cuda", generator=gen))
+    B, sb = lb.fp8_quantize_per_tensor(torch.randn(K, N, device="cuda", generator=gen) * 0.02)
+    sa, sb = float(sa.item()), float(sb.item())
+    Cout = torch.empty(M, N, device="cuda")
+
+    def step():
+        lb.gemm_fp8_e4m3(A, B, sa, sb, C=Cout)
+    ms = timed(step, steps, warmup, None, torch)
+    per = ms / steps * 1e-3
+    ops = 2.0 * M * N * K
+    _, bf16_peak, kind = measured_peaks()
+    return {"ms_per_call": per * 1e3, "TFLOPs": ops / per / 1e12,
+            "frac_of_2x_bf16_" + kind: ops / per / 1e12 / (2 * bf16_peak),
+            "frac_of_nominal_4500": ops / per / 1e12 / 4500.0,
+            "fast_path": int(lb._cabi.load().lhb_gemm_fp8_fast_path(M, N, K))}
 
 
 def bench_w8a8(torch, lb, steps, warmup, M=8192, K=8192, N=28672):

@@ -234,6 +234,30 @@ LHB_API int lhb_rope_decode_batched(lhb_ctx* ctx, float* x, const int32_t* posit
  * y[r, i] = gate * sigmoid(gate) * value. */
 LHB_API int lhb_swiglu(lhb_ctx* ctx, const float* x, float* y, int rows, int dim, void* stream);
 
+/* ---- FP8 E4M3 ------------------------------------------------------------------------ */
+
+/* lh::fp8_quantize_per_tensor / per_row / per_col (src/kernels/quant.hpp:81-94): E4M3 bytes
+ * (src/kernels/dtypes.hpp:111-159: RNE, saturating at +-448, NaN/inf -> 0x7f) and fp32 scales
+ * max|x| / 448 (1 if 0); one scale, one per row, one per column.  `scale_out` / `scales_out` are
+ * device pointers.  Bit-exact with the reference. */
+LHB_API int lhb_fp8_quantize_per_tensor(lhb_ctx* ctx, const float* src, uint8_t* dst, float* scale_out,
+                                        int64_t n, void* stream);
+LHB_API int lhb_fp8_quantize_per_row(lhb_ctx* ctx, const float* src, uint8_t* dst, float* scales_out,
+                                     int rows, int dim, void* stream);
+LHB_API int lhb_fp8_quantize_per_col(lhb_ctx* ctx, const float* src, uint8_t* dst, float* scales_out,
+                                     int rows, int cols, void* stream);
+/* lh::fp8_dequantize_per_tensor / per_row / per_col: dst = float(q) * scale; `mode` 0 = scales[0],
+ * 1 = scales[row], 2 = scales[col] (device array). */
+LHB_API int lhb_fp8_dequantize(lhb_ctx* ctx, const uint8_t* src, const float* scales, float* dst,
+                               int rows, int cols, int mode, void* stream);
+/* lh::gemm_fp8_e4m3 (src/kernels/gemm_quant.hpp:66-69): A [M, K] and B [K, N] E4M3 bytes, per-tensor
+ * scales by value, C = beta*C + (alpha * A_scale * B_scale) * sum_k a*b with fp32 accumulation.
+ * Shapes of lhb_gemm_w8a8_fast_path run on tcgen05 (kind::f8f6f4). */
+LHB_API int lhb_gemm_fp8_e4m3(lhb_ctx* ctx, const uint8_t* A, const uint8_t* B, float A_scale,
+                              float B_scale, float* C, int M, int N, int K, float alpha, float beta,
+                              void* stream);
+LHB_API int lhb_gemm_fp8_fast_path(int M, int N, int K);
+
 /* ---- asymmetric int4 (extension; no counterpart in the reference) ------------------ */
 
 /* The reference's int4 is symmetric with fp32 scales (src/kernels/quant.hpp:52-57).  This

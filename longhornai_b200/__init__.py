@@ -16,7 +16,9 @@ from .kernels import (Context, default_context, gemm_w4a16_groupwise, gemm_w8a8,
                       paged_kv_append_q8_batched, q4_dequantize_groupwise, q4_quantize_groupwise,
                       q8_dequantize_per_col, q8_dequantize_per_row, q8_quantize_per_col,
                       q8_quantize_per_row, rmsnorm, rope, rope_decode_batched, swiglu,
-                      gemm_w4a16_asym, q4a_dequantize_groupwise, q4a_quantize_groupwise)
+                      gemm_w4a16_asym, q4a_dequantize_groupwise, q4a_quantize_groupwise,
+                      fp8_dequantize, fp8_quantize_per_col, fp8_quantize_per_row, fp8_quantize_per_tensor,
+                      gemm_fp8_e4m3)
 from .runtime import ActiveStep, DeviceCacheManager, DeviceScheduler
 
 __all__ = [n for n in dir() if not n.startswith("_")]

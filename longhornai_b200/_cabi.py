@@ -54,6 +54,12 @@ SIGNATURES = {
     "lhb_rope": (_i, [_vp, _vp, _i, _i, _i, _f, _f, _i, _i, _vp]),
     "lhb_rope_decode_batched": (_i, [_vp, _vp, _vp, _i, _i, _i, _f, _f, _i, _vp]),
     "lhb_swiglu": (_i, [_vp, _vp, _vp, _i, _i, _vp]),
+    "lhb_fp8_quantize_per_tensor": (_i, [_vp, _vp, _vp, _vp, C.c_int64, _vp]),
+    "lhb_fp8_quantize_per_row": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp]),
+    "lhb_fp8_quantize_per_col": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp]),
+    "lhb_fp8_dequantize": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "lhb_gemm_fp8_e4m3": (_i, [_vp, _vp, _vp, _f, _f, _vp, _i, _i, _i, _f, _f, _vp]),
+    "lhb_gemm_fp8_fast_path": (_i, [_i, _i, _i]),
     "lhb_q4a_quantize_groupwise": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "lhb_q4a_dequantize_groupwise": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "lhb_gemm_w4a16_asym": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _f, _vp]),

@@ -42,6 +42,12 @@ int launch_decode_fast(lhb_ctx* ctx, const float* Q, const int8_t* Kp, const int
                        const int32_t* seq_lens, int n_req, float* O, const lhb_paged_attn_cfg& cfg,
                        const lhb_paged_layout& L, cudaStream_t st);
 
+// fp8 E4M3 GEMM: generic kernel in fp8.cu, tcgen05 path in gemm_w8a8_tc.cu (shapes of w8a8_fast_ok)
+int launch_fp8_generic(const uint8_t* A, const uint8_t* B, float combined, float* C, int M, int N, int K, float beta,
+                       cudaStream_t st);
+int launch_fp8_fast(lhb_ctx* ctx, const uint8_t* A, const uint8_t* B, float combined, float* C, int M, int N, int K,
+                    float beta, cudaStream_t st);
+
 // asymmetric int4 (fp16 scale and zero-point per group): generic kernel in quant_asym.cu,
 // decode fast path in gemv_mma.cu
 int launch_w4a16_asym_generic(const float* A, const uint8_t* Bp, const uint16_t* Bs, const uint16_t* Bz, float* C,

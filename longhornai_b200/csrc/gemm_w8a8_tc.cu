@@ -59,7 +59,39 @@ struct W8Params {
     float alpha, beta;
     int tiles_m, tiles_n;
     int* status;
+    float combined;        // fp8: alpha * A_scale * B_scale (a_scales / b_scales unused)
 };
+
+// fp8 (E4M3 x E4M3 -> fp32): same tiles, barriers and shared-memory descriptors; the
+// instruction descriptor names D = f32 (bits 4-5 = 1) and A = B = E4M3 (formats 0)
+constexpr uint32_t f8_idesc(int m, int n) {
+    return (1u << 4) | (1u << 16) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// One 32-column chunk of one output row of the fp8 GEMM: C = beta*C + combined * acc, with the
+// reference's separate roundings (src/kernels/gemm_quant.cpp:87-104).
+__device__ __forceinline__ void f8_store_chunk(float* crow, int nb, const uint32_t (&r)[32], const W8Params& p) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+        if (nb + j >= p.N) break;                      // N % 16 == 0: whole float4 in range
+        float4 v;
+        v.x = __fmul_rn(p.combined, __uint_as_float(r[j]));
+        v.y = __fmul_rn(p.combined, __uint_as_float(r[j + 1]));
+        v.z = __fmul_rn(p.combined, __uint_as_float(r[j + 2]));
+        v.w = __fmul_rn(p.combined, __uint_as_float(r[j + 3]));
+        float4* dst = reinterpret_cast<float4*>(crow + nb + j);
+        if (p.beta != 0.0f) {
+            const float4 o = *dst;
+            if (p.beta == 1.0f) {
+                v.x = __fadd_rn(o.x, v.x); v.y = __fadd_rn(o.y, v.y); v.z = __fadd_rn(o.z, v.z); v.w = __fadd_rn(o.w, v.w);
+            } else {
+                v.x = __fadd_rn(__fmul_rn(o.x, p.beta), v.x); v.y = __fadd_rn(__fmul_rn(o.y, p.beta), v.y);
+                v.z = __fadd_rn(__fmul_rn(o.z, p.beta), v.z); v.w = __fadd_rn(__fmul_rn(o.w, p.beta), v.w);
+            }
+        }
+        *dst = v;
+    }
+}
 
 
 // One 32-column chunk of one output row: C = beta*C + ((alpha*a_s)*b_s[n])*float(acc),
@@ -102,6 +134,7 @@ __device__ __forceinline__ void w8_store_chunk(float* crow, int nb, const uint32
     }
 }
 
+template <bool F8>
 __global__ void __launch_bounds__(W8_THREADS, 1)
 gemm_w8a8_tc_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ TensorMap tmB,
                     const W8Params p) {
@@ -186,7 +219,8 @@ gemm_w8a8_tc_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant
                         // B: MN-major, 128 columns per atom row, 8 k-rows = 1024 B, the second
                         // 128-column box lies W8_BK*128 bytes further; K advances 32 rows
                         const uint64_t db = ptx::smem_desc_sw128(sb + k4 * 32 * 128, W8_BK * 128, 1024);
-                        ptx::mma_i8_ss(d_tmem, da, db, W8_IDESC, (kb | k4) != 0 ? 1u : 0u);
+                        if (F8) ptx::mma_f8_ss(d_tmem, da, db, f8_idesc(W8_BM, W8_BN), (kb | k4) != 0 ? 1u : 0u);
+                        else ptx::mma_i8_ss(d_tmem, da, db, W8_IDESC, (kb | k4) != 0 ? 1u : 0u);
                     }
                     ptx::tc_commit(empty_bar(s));
                 }
@@ -204,7 +238,7 @@ gemm_w8a8_tc_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant
             ptx::tc_fence_after();
             const int row = m0 + 32 * q + lane;
             const bool row_ok = row < p.M;
-            const float sa = row_ok ? __fmul_rn(p.alpha, p.a_scales[row]) : 0.0f;
+            const float sa = (row_ok && !F8) ? __fmul_rn(p.alpha, p.a_scales[row]) : 0.0f;
             float* crow = p.C + static_cast<int64_t>(row_ok ? row : 0) * p.N;
 #pragma unroll 1
             for (int c = 0; c < W8_BN / 32; ++c) {
@@ -217,7 +251,8 @@ gemm_w8a8_tc_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant
                 }
                 const int nb = n0 + c * 32;
                 if (!row_ok || nb >= p.N) continue;
-                w8_store_chunk(crow, nb, r, sa, p);
+                if (F8) f8_store_chunk(crow, nb, r, p);
+                else w8_store_chunk(crow, nb, r, sa, p);
             }
         }
     }
@@ -249,6 +284,7 @@ constexpr size_t W8P_SMEM = 1024 + static_cast<size_t>(W8P_STAGES) * W8P_STAGE_B
 constexpr uint32_t W8P_IDESC = (2u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
                                (static_cast<uint32_t>(256 >> 3) << 17) | (static_cast<uint32_t>(256 >> 4) << 24);
 
+template <bool F8>
 __global__ void __launch_bounds__(W8_THREADS, 1)
 gemm_w8a8_tc_pair_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ TensorMap tmB,
                          const W8Params p) {
@@ -325,7 +361,8 @@ gemm_w8a8_tc_pair_kernel(const __grid_constant__ TensorMap tmA, const __grid_con
                     for (int k4 = 0; k4 < W8_BK / 32; ++k4) {
                         const uint64_t da = ptx::smem_desc_sw128(sa + k4 * 32, 16, 1024);
                         const uint64_t db = ptx::smem_desc_sw128(sb + k4 * 32 * 128, 16, 1024);
-                        ptx::mma_i8_ss_pair(d_tmem, da, db, W8P_IDESC, (kb | k4) != 0 ? 1u : 0u);
+                        if (F8) ptx::mma_f8_ss_pair(d_tmem, da, db, f8_idesc(256, 256), (kb | k4) != 0 ? 1u : 0u);
+                        else ptx::mma_i8_ss_pair(d_tmem, da, db, W8P_IDESC, (kb | k4) != 0 ? 1u : 0u);
                     }
                     ptx::tc_commit_pair(ptx::mapa_shared(empty_bar(s), 0));     // stage free in both CTAs
                     ptx::tc_commit_pair(ptx::mapa_shared(empty_bar(s), 1));
@@ -345,7 +382,7 @@ gemm_w8a8_tc_pair_kernel(const __grid_constant__ TensorMap tmA, const __grid_con
             ptx::tc_fence_after();
             const int row = m0 + 32 * q + lane;
             const bool row_ok = row < p.M;
-            const float sa = row_ok ? __fmul_rn(p.alpha, p.a_scales[row]) : 0.0f;
+            const float sa = (row_ok && !F8) ? __fmul_rn(p.alpha, p.a_scales[row]) : 0.0f;
             float* crow = p.C + static_cast<int64_t>(row_ok ? row : 0) * p.N;
             const uint32_t leader_tempty = ptx::mapa_shared(tempty_bar(buf), 0);
 #pragma unroll 1
@@ -359,7 +396,8 @@ gemm_w8a8_tc_pair_kernel(const __grid_constant__ TensorMap tmA, const __grid_con
                 }
                 const int nb = n0 + c * 32;
                 if (!row_ok || nb >= p.N) continue;
-                w8_store_chunk(crow, nb, r, sa, p);
+                if (F8) f8_store_chunk(crow, nb, r, p);
+                else w8_store_chunk(crow, nb, r, sa, p);
             }
         }
     }
@@ -377,32 +415,25 @@ bool w8a8_fast_ok(int M, int N, int K) {
     return M >= 64 && N >= 128 && K >= 128 && (N % 16) == 0 && (K % 16) == 0;
 }
 
-int launch_w8a8_fast(lhb_ctx* ctx, const int8_t* Aq, const int8_t* Bq, const float* as,
-                     const float* bs, float* C, int M, int N, int K, float alpha, float beta,
-                     cudaStream_t st) {
+template <bool F8>
+static int launch_tc(lhb_ctx* ctx, const void* Aq, const void* Bq, W8Params p, cudaStream_t st) {
+    const int M = p.M, N = p.N, K = p.K;
     TensorMap tmA, tmB;
     if (int e = get_tensor_map_2d_u8(ctx, Aq, M, K, K, W8_BM, W8_BK, true, &tmA)) return e;
     if (int e = get_tensor_map_2d_u8(ctx, Bq, K, N, N, W8_BK, 128, true, &tmB)) return e;
     static bool attr_set[64] = {};
     if (!attr_set[ctx->device & 63]) {
-        LHB_CUDA(cudaFuncSetAttribute(gemm_w8a8_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        LHB_CUDA(cudaFuncSetAttribute(gemm_w8a8_tc_kernel<F8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       static_cast<int>(W8_SMEM)));
+        LHB_CUDA(cudaFuncSetAttribute(gemm_w8a8_tc_pair_kernel<F8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(W8P_SMEM)));
         attr_set[ctx->device & 63] = true;
     }
-    W8Params p{};
-    p.a_scales = as; p.b_scales = bs; p.C = C; p.M = M; p.N = N; p.K = K;
-    p.alpha = alpha; p.beta = beta;
     p.tiles_m = ceil_div(M, W8_BM); p.tiles_n = ceil_div(N, W8_BN);
     p.status = ctx->status_word;
     const char* pair_env = getenv("LHB_W8A8_PAIR");          // 0 forces the single-CTA kernel
     const int use_pair = pair_env ? atoi(pair_env) : 1;
     if (use_pair && M >= 256) {
-        static bool attr2[64] = {};
-        if (!attr2[ctx->device & 63]) {
-            LHB_CUDA(cudaFuncSetAttribute(gemm_w8a8_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          static_cast<int>(W8P_SMEM)));
-            attr2[ctx->device & 63] = true;
-        }
         const int tiles = ceil_div(M, 256) * p.tiles_n;
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(2 * std::min(ctx->sm_count / 2, tiles), 1, 1);
@@ -416,13 +447,31 @@ int launch_w8a8_fast(lhb_ctx* ctx, const int8_t* Aq, const int8_t* Bq, const flo
         attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        LHB_CUDA(cudaLaunchKernelEx(&cfg, gemm_w8a8_tc_pair_kernel, tmA, tmB, p));
+        LHB_CUDA(cudaLaunchKernelEx(&cfg, gemm_w8a8_tc_pair_kernel<F8>, tmA, tmB, p));
         return LHB_OK;
     }
     const int grid = std::min(ctx->sm_count, p.tiles_m * p.tiles_n);
-    gemm_w8a8_tc_kernel<<<grid, W8_THREADS, W8_SMEM, st>>>(tmA, tmB, p);
+    gemm_w8a8_tc_kernel<F8><<<grid, W8_THREADS, W8_SMEM, st>>>(tmA, tmB, p);
     LHB_LAUNCH_CHECK();
     return LHB_OK;
+}
+
+int launch_w8a8_fast(lhb_ctx* ctx, const int8_t* Aq, const int8_t* Bq, const float* as,
+                     const float* bs, float* C, int M, int N, int K, float alpha, float beta,
+                     cudaStream_t st) {
+    W8Params p{};
+    p.a_scales = as; p.b_scales = bs; p.C = C; p.M = M; p.N = N; p.K = K;
+    p.alpha = alpha; p.beta = beta;
+    return launch_tc<false>(ctx, Aq, Bq, p, st);
+}
+
+// fp8 E4M3 GEMM with per-tensor scales folded into `combined` (same shapes as the int8 kernel)
+int launch_fp8_fast(lhb_ctx* ctx, const uint8_t* A, const uint8_t* B, float combined, float* C, int M, int N, int K,
+                    float beta, cudaStream_t st) {
+    W8Params p{};
+    p.C = C; p.M = M; p.N = N; p.K = K;
+    p.alpha = 1.0f; p.beta = beta; p.combined = combined;
+    return launch_tc<true>(ctx, A, B, p, st);
 }
 
 }  // namespace lhb

@@ -403,3 +403,58 @@ def gemm_w4a16_asym(A, B_packed, B_scales, B_zeros, group_size: int, C=None, alp
                                     _t(out, torch.float32, "C"), M, N, K_, group_size, alpha, beta,
                                     _stream(c.device)), "gemm_w4a16_asym")
     return out
+
+
+# ---- FP8 E4M3 ----------------------------------------------------------------------------
+
+def fp8_quantize_per_tensor(src, ctx=None):
+    """fp32 tensor -> (uint8 E4M3 bytes of the same shape, fp32 scale as a 1-element CUDA tensor)."""
+    c = _ctx_for(src, ctx)
+    dst = torch.empty(src.shape, dtype=torch.uint8, device=src.device)
+    scale = torch.empty(1, dtype=torch.float32, device=src.device)
+    check(c.lib.lhb_fp8_quantize_per_tensor(c.handle, _t(src, torch.float32, "src"), dst.data_ptr(),
+                                            scale.data_ptr(), src.numel(), _stream(c.device)),
+          "fp8_quantize_per_tensor")
+    return dst, scale
+
+
+def fp8_quantize_per_row(src, ctx=None):
+    c = _ctx_for(src, ctx)
+    rows, dim = src.shape
+    dst = torch.empty((rows, dim), dtype=torch.uint8, device=src.device)
+    scales = torch.empty(rows, dtype=torch.float32, device=src.device)
+    check(c.lib.lhb_fp8_quantize_per_row(c.handle, _t(src, torch.float32, "src"), dst.data_ptr(),
+                                         scales.data_ptr(), rows, dim, _stream(c.device)), "fp8_quantize_per_row")
+    return dst, scales
+
+
+def fp8_quantize_per_col(src, ctx=None):
+    c = _ctx_for(src, ctx)
+    rows, cols = src.shape
+    dst = torch.empty((rows, cols), dtype=torch.uint8, device=src.device)
+    scales = torch.empty(cols, dtype=torch.float32, device=src.device)
+    check(c.lib.lhb_fp8_quantize_per_col(c.handle, _t(src, torch.float32, "src"), dst.data_ptr(),
+                                         scales.data_ptr(), rows, cols, _stream(c.device)), "fp8_quantize_per_col")
+    return dst, scales
+
+
+def fp8_dequantize(src, scales, mode: int, ctx=None):
+    """mode 0: one scale (1-element tensor), 1: per row, 2: per column."""
+    c = _ctx_for(src, ctx)
+    rows, cols = src.shape
+    dst = torch.empty((rows, cols), dtype=torch.float32, device=src.device)
+    check(c.lib.lhb_fp8_dequantize(c.handle, _t(src, torch.uint8, "src"), _t(scales, torch.float32, "scales"),
+                                   dst.data_ptr(), rows, cols, int(mode), _stream(c.device)), "fp8_dequantize")
+    return dst
+
+
+def gemm_fp8_e4m3(A, B, A_scale: float, B_scale: float, C=None, alpha: float = 1.0, beta: float = 0.0, ctx=None):
+    """lh::gemm_fp8_e4m3: A [M, K], B [K, N] uint8 E4M3 bytes, per-tensor scales as Python floats."""
+    c = _ctx_for(A, ctx)
+    M, K_ = A.shape
+    N = B.shape[1]
+    out = _out(C, M, N, A, beta)
+    check(c.lib.lhb_gemm_fp8_e4m3(c.handle, _t(A, torch.uint8, "A"), _t(B, torch.uint8, "B"), float(A_scale),
+                                  float(B_scale), _t(out, torch.float32, "C"), M, N, K_, alpha, beta,
+                                  _stream(c.device)), "gemm_fp8_e4m3")
+    return out

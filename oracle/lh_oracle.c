@@ -718,6 +718,120 @@ LHO_API void lho_gemm_w4a16_asym(const float* A, const uint8_t* Bp, const uint16
     free(panel);
 }
 
+/* ---------------------------------------------------------------------------
+ * FP8 E4M3: conversion, quantisers and GEMM.
+ * ------------------------------------------------------------------------- */
+
+/* fp32 -> E4M3 bits (1 sign, 4 exponent bits with bias 7, 3 mantissa bits): round to
+ * nearest even, saturate at +-448 (0x7e), NaN and infinities become the one NaN code
+ * 0x7f, values below half the smallest subnormal (2^-10) flush to signed zero.
+ * Reference: src/kernels/dtypes.hpp:111-159. */
+LHO_API uint8_t lho_f32_to_e4m3_bits(float v) {
+    uint32_t x;
+    memcpy(&x, &v, sizeof x);
+    const uint32_t sign = (x >> 24) & 0x80u;
+    const int e = (int)((x >> 23) & 0xff);
+    uint32_t m = x & 0x7fffffu;
+    if (e == 0xff) return (uint8_t)(sign | 0x7fu);
+    const int ne = e - 127 + 7;
+    if (ne > 15 || (ne == 15 && m > 0x600000u)) return (uint8_t)(sign | 0x7eu);
+    uint32_t keep, rest, half_ulp, base;
+    if (ne >= 1) {
+        keep = m >> 20;
+        rest = m & 0xfffffu;
+        half_ulp = 0x80000u;
+        base = (uint32_t)ne << 3;
+    } else {
+        if (ne < -2) return (uint8_t)sign;
+        m |= 0x800000u;
+        const int sh = 21 - ne;                 /* 21 .. 23 */
+        keep = m >> sh;
+        rest = m & ((1u << sh) - 1u);
+        half_ulp = 1u << (sh - 1);
+        base = 0;
+    }
+    uint32_t out = base + keep;                 /* a mantissa carry runs into the exponent */
+    if (rest > half_ulp || (rest == half_ulp && (out & 1u))) ++out;
+    if (out > 0x7eu) out = 0x7eu;
+    return (uint8_t)(sign | out);
+}
+
+/* Reference: src/kernels/dtypes.hpp:161-196. */
+LHO_API float lho_e4m3_bits_to_f32(uint8_t b) {
+    const int e = (b >> 3) & 0xf, m = b & 7;
+    float mag;
+    if (e == 0xf && m == 7) {
+        const uint32_t bits = ((b & 0x80u) ? 0x80000000u : 0u) | 0x7fc00000u;
+        memcpy(&mag, &bits, sizeof mag);
+        return mag;
+    }
+    mag = (e == 0) ? ldexpf((float)m, -9) : ldexpf((float)(8 + m), e - 10);
+    return (b & 0x80u) ? -mag : mag;
+}
+
+/* src/kernels/quant.cpp:176-188: one scale = max|x| / 448 (1 if 0), q = e4m3(x * (1/scale)). */
+LHO_API void lho_fp8_quantize_per_tensor(const float* src, uint8_t* dst, float* scale_out, int64_t n) {
+    float mx = 0.0f;
+    for (int64_t i = 0; i < n; ++i) { const float a = fabsf(src[i]); if (a > mx) mx = a; }
+    const float scale = (mx > 0.0f) ? mx / 448.0f : 1.0f;
+    const float inv = 1.0f / scale;
+    for (int64_t i = 0; i < n; ++i) dst[i] = lho_f32_to_e4m3_bits(src[i] * inv);
+    *scale_out = scale;
+}
+
+/* src/kernels/quant.cpp:195-206: per row, reciprocal-multiply idiom. */
+LHO_API void lho_fp8_quantize_per_row(const float* src, uint8_t* dst, float* scales_out, int rows, int dim) {
+    for (int r = 0; r < rows; ++r) {
+        const float* row = src + (int64_t)r * dim;
+        float mx = 0.0f;
+        for (int i = 0; i < dim; ++i) { const float a = fabsf(row[i]); if (a > mx) mx = a; }
+        const float scale = (mx > 0.0f) ? mx / 448.0f : 1.0f;
+        const float inv = 1.0f / scale;
+        for (int i = 0; i < dim; ++i) dst[(int64_t)r * dim + i] = lho_f32_to_e4m3_bits(row[i] * inv);
+        scales_out[r] = scale;
+    }
+}
+
+/* src/kernels/quant.cpp:219-238: per column, true-division idiom. */
+LHO_API void lho_fp8_quantize_per_col(const float* src, uint8_t* dst, float* scales_out, int rows, int cols) {
+    for (int c = 0; c < cols; ++c) scales_out[c] = 0.0f;
+    for (int r = 0; r < rows; ++r)
+        for (int c = 0; c < cols; ++c) {
+            const float a = fabsf(src[(int64_t)r * cols + c]);
+            if (a > scales_out[c]) scales_out[c] = a;
+        }
+    for (int c = 0; c < cols; ++c) scales_out[c] = (scales_out[c] > 0.0f) ? scales_out[c] / 448.0f : 1.0f;
+    for (int r = 0; r < rows; ++r)
+        for (int c = 0; c < cols; ++c)
+            dst[(int64_t)r * cols + c] = lho_f32_to_e4m3_bits(src[(int64_t)r * cols + c] / scales_out[c]);
+}
+
+/* src/kernels/quant.cpp:190-193, 208-217, 240-249: q * scale (per tensor: one scale; per row;
+ * per column).  `mode` 0 / 1 / 2 selects which, `scales` has 1 / rows / cols entries. */
+LHO_API void lho_fp8_dequantize(const uint8_t* src, const float* scales, float* dst, int rows, int cols, int mode) {
+    for (int r = 0; r < rows; ++r)
+        for (int c = 0; c < cols; ++c) {
+            const float s = mode == 0 ? scales[0] : (mode == 1 ? scales[r] : scales[c]);
+            dst[(int64_t)r * cols + c] = lho_e4m3_bits_to_f32(src[(int64_t)r * cols + c]) * s;
+        }
+}
+
+/* src/kernels/gemm_quant.cpp:87-104: C = beta*C + (alpha * A_scale * B_scale) * sum_k a*b, the sum in
+ * fp32 in k order for each (i, j). */
+LHO_API void lho_gemm_fp8_e4m3(const uint8_t* A, const uint8_t* B, float A_scale, float B_scale, float* C,
+                               int M, int N, int K, float alpha, float beta) {
+    scale_c(C, M, N, beta);
+    const float combined = alpha * A_scale * B_scale;
+    float lut[256];
+    for (int i = 0; i < 256; ++i) lut[i] = lho_e4m3_bits_to_f32((uint8_t)i);
+    for (int i = 0; i < M; ++i)
+        for (int j = 0; j < N; ++j) {
+            float acc = 0.0f;
+            for (int k = 0; k < K; ++k) acc += lut[A[(int64_t)i * K + k]] * lut[B[(int64_t)k * N + j]];
+            C[(int64_t)i * N + j] += combined * acc;
+        }
+}
+
 /* ------------------------------------------------------------------ */
 
 /* N-sharded W4A16: shard s holds a compact [K/2, n_shard] packed slab, its

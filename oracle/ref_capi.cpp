@@ -65,6 +65,29 @@ LHR_API uint16_t lhr_f32_to_bf16_bits(float v) { return lh::bfloat16(v).bits; }
 LHR_API float lhr_bf16_bits_to_f32(uint16_t b) {
     return lh::detail::bf16_bits_to_float(b);
 }
+// FP8 E4M3 of the reference (src/kernels/dtypes.hpp:111-196, quant.cpp:176-249, gemm_quant.cpp:87-104)
+LHR_API uint8_t lhr_f32_to_e4m3_bits(float v) { return lh::detail::float_to_e4m3_bits(v); }
+LHR_API float lhr_e4m3_bits_to_f32(uint8_t b) { return lh::detail::e4m3_bits_to_float(b); }
+LHR_API void lhr_fp8_quantize_per_tensor(const float* s, uint8_t* d, float* sc, int64_t n) {
+    lh::fp8_quantize_per_tensor(s, reinterpret_cast<lh::fp8_e4m3*>(d), sc, n);
+}
+LHR_API void lhr_fp8_quantize_per_row(const float* s, uint8_t* d, float* sc, int rows, int dim) {
+    lh::fp8_quantize_per_row(s, reinterpret_cast<lh::fp8_e4m3*>(d), sc, rows, dim);
+}
+LHR_API void lhr_fp8_quantize_per_col(const float* s, uint8_t* d, float* sc, int rows, int cols) {
+    lh::fp8_quantize_per_col(s, reinterpret_cast<lh::fp8_e4m3*>(d), sc, rows, cols);
+}
+LHR_API void lhr_fp8_dequantize(const uint8_t* s, const float* sc, float* d, int rows, int cols, int mode) {
+    auto* q = reinterpret_cast<const lh::fp8_e4m3*>(s);
+    if (mode == 0) lh::fp8_dequantize_per_tensor(q, sc[0], d, static_cast<int64_t>(rows) * cols);
+    else if (mode == 1) lh::fp8_dequantize_per_row(q, sc, d, rows, cols);
+    else lh::fp8_dequantize_per_col(q, sc, d, rows, cols);
+}
+LHR_API void lhr_gemm_fp8_e4m3(const uint8_t* A, const uint8_t* B, float as, float bs, float* C, int M, int N, int K,
+                               float alpha, float beta) {
+    lh::gemm_fp8_e4m3(reinterpret_cast<const lh::fp8_e4m3*>(A), reinterpret_cast<const lh::fp8_e4m3*>(B), as, bs, C,
+                      M, N, K, alpha, beta);
+}
 // fp16 conversion of the reference (src/kernels/dtypes.hpp:17-85), for pinning the restatement
 LHR_API uint16_t lhr_f32_to_f16_bits(float v) { return lh::detail::float_to_half_bits(v); }
 LHR_API float lhr_f16_bits_to_f32(uint16_t b) { return lh::detail::half_bits_to_float(b); }

@@ -169,6 +169,52 @@ class Checker:
                                          _p(out), M, N, K, C.c_float(alpha), C.c_float(beta))
         return out
 
+    # -- FP8 E4M3 -----------------------------------------------------------
+    def f32_to_e4m3_bits(self, x):
+        f = self.fn("f32_to_e4m3_bits", C.c_uint8)
+        return np.array([f(C.c_float(float(v))) for v in np.asarray(x, np.float32).ravel()], np.uint8)
+
+    def e4m3_bits_to_f32(self, b):
+        f = self.fn("e4m3_bits_to_f32", C.c_float)
+        return np.array([f(C.c_uint8(int(v))) for v in np.asarray(b, np.uint8).ravel()], np.float32)
+
+    def fp8_quantize_per_tensor(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        q = np.zeros(x.shape, np.uint8)
+        s = np.zeros(1, np.float32)
+        self.fn("fp8_quantize_per_tensor")(_p(x), _p(q), _p(s), C.c_int64(x.size))
+        return q, float(s[0])
+
+    def fp8_quantize_per_row(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        q = np.zeros(x.shape, np.uint8)
+        s = np.zeros(x.shape[0], np.float32)
+        self.fn("fp8_quantize_per_row")(_p(x), _p(q), _p(s), x.shape[0], x.shape[1])
+        return q, s
+
+    def fp8_quantize_per_col(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        q = np.zeros(x.shape, np.uint8)
+        s = np.zeros(x.shape[1], np.float32)
+        self.fn("fp8_quantize_per_col")(_p(x), _p(q), _p(s), x.shape[0], x.shape[1])
+        return q, s
+
+    def fp8_dequantize(self, q, scales, mode):
+        """mode 0: one scale, 1: per row, 2: per column."""
+        q = np.ascontiguousarray(q, np.uint8)
+        d = np.zeros(q.shape, np.float32)
+        sc = np.ascontiguousarray(np.atleast_1d(np.asarray(scales, np.float32)))
+        self.fn("fp8_dequantize")(_p(q), _p(sc), _p(d), q.shape[0], q.shape[1], int(mode))
+        return d
+
+    def gemm_fp8_e4m3(self, A, B, a_scale, b_scale, C0=None, alpha=1.0, beta=0.0):
+        M, K = A.shape
+        N = B.shape[1]
+        out = np.zeros((M, N), np.float32) if C0 is None else C0.copy()
+        self.fn("gemm_fp8_e4m3")(_p(A, np.uint8), _p(B, np.uint8), C.c_float(a_scale), C.c_float(b_scale), _p(out),
+                                 M, N, K, C.c_float(alpha), C.c_float(beta))
+        return out
+
     # -- asymmetric int4 (extension; the compiled reference has no such scheme) ----------
     def f32_to_f16_bits(self, x):
         f = self.fn("f32_to_f16_bits", C.c_uint16)

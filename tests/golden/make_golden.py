@@ -252,6 +252,36 @@ def asym_fixtures():
              C0=C0, C_ab=port.gemm_w4a16_asym(A, p, s, z, G, C0, alpha=0.5, beta=2.0))
 
 
+def fp8_fixtures():
+    """FP8 E4M3 (src/kernels/dtypes.hpp:111-196, quant.cpp:176-249, gemm_quant.cpp:87-104), shapes after
+    tests/test_quant.cpp and tests/test_gemm_quant.cpp's fp8 cases, produced by the compiled reference."""
+    if not ref_available():
+        raise SystemExit("oracle/_ref/liblh_ref.so missing: run `make -C oracle ref` first")
+    ref = Checker("lhr")
+    rng = np.random.default_rng(20247)
+    x = np.concatenate([rng.standard_normal(2048).astype(np.float32) *
+                        rng.choice([1e-4, 1e-3, 1e-2, 0.1, 1.0, 30.0, 300.0, 1000.0], 2048).astype(np.float32),
+                        np.array([0.0, -0.0, 448.0, 449.0, 464.0, 465.0, 480.0, 1e9, -1e9, np.inf, -np.inf, np.nan,
+                                  2.0 ** -9, 2.0 ** -10, 2.0 ** -10 * 1.0001, 2.0 ** -11, 1.5 * 2.0 ** -9,
+                                  0.0146484375, 0.9375, 0.96875, 1.0625], np.float32)])
+    save("fp8_convert", x=x, bits=ref.f32_to_e4m3_bits(x), back=ref.e4m3_bits_to_f32(np.arange(256, dtype=np.uint8)))
+    X = uniform(rng, (9, 80), -3, 3)
+    X[2] = 0.0
+    X[5] *= 100.0
+    X[:, 7] = 0.0
+    qt, st = ref.fp8_quantize_per_tensor(X)
+    qr, sr = ref.fp8_quantize_per_row(X)
+    qc, sc = ref.fp8_quantize_per_col(X)
+    save("fp8_quant", x=X, qt=qt, st=np.float32(st), qr=qr, sr=sr, qc=qc, sc=sc,
+         dt=ref.fp8_dequantize(qt, [st], 0), dr=ref.fp8_dequantize(qr, sr, 1), dc=ref.fp8_dequantize(qc, sc, 2))
+    for name, M, N, K in [("fp8_gemm_m5n24k64", 5, 24, 64), ("fp8_gemm_m33n48k96", 33, 48, 96)]:
+        A, sa = ref.fp8_quantize_per_tensor(uniform(rng, (M, K)))
+        B, sb = ref.fp8_quantize_per_tensor(uniform(rng, (K, N)))
+        C0 = uniform(rng, (M, N))
+        save(name, A=A, B=B, sa=np.float32(sa), sb=np.float32(sb), C=ref.gemm_fp8_e4m3(A, B, sa, sb), C0=C0,
+             C_ab=ref.gemm_fp8_e4m3(A, B, sa, sb, C0, alpha=0.5, beta=2.0))
+
+
 def scheduler_trace():
     """Step-by-step record of the reference's own Scheduler (src/runtime/scheduler.cpp) on a mixed workload
     in the style of tests/test_scheduler.cpp (MixedWorkloadHitsHighOccupancy, AdmissionStallsOnOOM): more
@@ -296,7 +326,9 @@ def scheduler_trace():
 
 
 if __name__ == "__main__":
-    if "--sched" in sys.argv:
+    if "--fp8" in sys.argv:
+        fp8_fixtures()
+    elif "--sched" in sys.argv:
         scheduler_trace()
     elif "--asym" in sys.argv:
         asym_fixtures()
@@ -306,4 +338,5 @@ if __name__ == "__main__":
         main()
         glue_fixtures()
         asym_fixtures()
+        fp8_fixtures()
         scheduler_trace()

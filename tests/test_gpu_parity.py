@@ -528,3 +528,51 @@ def test_scheduler_device_view_matches_reference_trace():
     sched.close()
     mgr.close()
     poll_ok()
+
+
+# --------------------------------------------------------------------------- FP8 E4M3
+
+def test_fp8_quantisers_bit_exact():
+    g = gio.load("fp8_quant")
+    x = dev(g["x"])
+    qt, st = lb.fp8_quantize_per_tensor(x)
+    assert_same_bits(host(qt), g["qt"], "per tensor"); assert host(st)[0] == g["st"]
+    qr, sr = lb.fp8_quantize_per_row(x)
+    assert_same_bits(host(qr), g["qr"], "per row"); assert_same_bits(host(sr), g["sr"], "row scales")
+    qc, sc = lb.fp8_quantize_per_col(x)
+    assert_same_bits(host(qc), g["qc"], "per col"); assert_same_bits(host(sc), g["sc"], "col scales")
+    assert_same_bits(host(lb.fp8_dequantize(qt, st, 0)), g["dt"], "dequant tensor")
+    assert_same_bits(host(lb.fp8_dequantize(qr, sr, 1)), g["dr"], "dequant row")
+    assert_same_bits(host(lb.fp8_dequantize(qc, sc, 2)), g["dc"], "dequant col")
+    # every conversion case of the fixture, through the per-tensor quantiser with scale 1 (max = 448)
+    c = gio.load("fp8_convert")
+    keep = np.isfinite(c["x"]) & (np.abs(c["x"]) <= 448.0)
+    v = np.concatenate([c["x"][keep], np.array([448.0], np.float32)])
+    q, s = lb.fp8_quantize_per_tensor(dev(v))
+    assert host(s)[0] == 1.0
+    assert_same_bits(host(q)[:-1], c["bits"][keep], "conversion cases")
+    poll_ok()
+
+
+@pytest.mark.parametrize("name", gio.names("fp8_gemm_"))
+def test_fp8_gemm_golden(name):
+    g = gio.load(name)
+    got = lb.gemm_fp8_e4m3(dev(g["A"]), dev(g["B"]), float(g["sa"]), float(g["sb"]))
+    assert_close(host(got), g["C"], what=name)
+    got = lb.gemm_fp8_e4m3(dev(g["A"]), dev(g["B"]), float(g["sa"]), float(g["sb"]), C=dev(g["C0"]), alpha=0.5, beta=2.0)
+    assert_close(host(got), g["C_ab"], what=name + " alpha/beta")
+    poll_ok()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 512), (300, 1040, 768), (1024, 2048, 1024)])
+def test_fp8_gemm_tensor_core_path_against_checker(chk, lib, M, N, K):
+    """Shapes served by tcgen05 (kind::f8f6f4), single-CTA and CTA-pair tiles, against the reference loop."""
+    assert lib.lhb_gemm_fp8_fast_path(M, N, K) == 1
+    rng = np.random.default_rng(M + N + K)
+    A, sa = chk.fp8_quantize_per_tensor(rng.standard_normal((M, K)).astype(np.float32))
+    B, sb = chk.fp8_quantize_per_tensor((rng.standard_normal((K, N)) * 0.02).astype(np.float32))
+    C0 = rng.standard_normal((M, N)).astype(np.float32)
+    want = chk.gemm_fp8_e4m3(A, B, sa, sb, C0, alpha=0.75, beta=1.0)
+    got = lb.gemm_fp8_e4m3(dev(A), dev(B), sa, sb, C=dev(C0), alpha=0.75, beta=1.0)
+    assert_close(host(got), want, what=f"fp8 gemm {M}x{N}x{K}")
+    poll_ok()

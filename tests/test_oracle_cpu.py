@@ -168,6 +168,29 @@ def test_q4a_fixture_properties(name):
     assert np.allclose(g["C"], ref, rtol=1e-4, atol=1e-5)
 
 
+def test_fp8_conversion_and_quantisers_golden():
+    g = gio.load("fp8_convert")
+    assert np.array_equal(port.f32_to_e4m3_bits(g["x"]), g["bits"])
+    back = port.e4m3_bits_to_f32(np.arange(256, dtype=np.uint8))
+    assert np.array_equal(back.view(np.uint32), g["back"].view(np.uint32))
+    assert np.nanmax(np.abs(back)) == 448.0 and np.isnan(back[0x7f]) and np.isnan(back[0xff])
+    g = gio.load("fp8_quant")
+    qt, st = port.fp8_quantize_per_tensor(g["x"]); same(qt, g["qt"]); assert np.float32(st) == g["st"]
+    qr, sr = port.fp8_quantize_per_row(g["x"]); same(qr, g["qr"]); same(sr, g["sr"])
+    qc, sc = port.fp8_quantize_per_col(g["x"]); same(qc, g["qc"]); same(sc, g["sc"])
+    same(port.fp8_dequantize(qt, [st], 0), g["dt"]); same(port.fp8_dequantize(qr, sr, 1), g["dr"])
+    same(port.fp8_dequantize(qc, sc, 2), g["dc"])
+    # the reference's own bound: a round trip is within 2^-4 of the magnitude (3 mantissa bits) or of the step
+    assert np.all(np.abs(g["dr"] - g["x"]) <= np.maximum(np.abs(g["x"]) * 2.0 ** -4, sr[:, None] * 2.0 ** -9) + 1e-12)
+
+
+@pytest.mark.parametrize("name", gio.names("fp8_gemm_"))
+def test_fp8_gemm_golden(name):
+    g = gio.load(name)
+    same(port.gemm_fp8_e4m3(g["A"], g["B"], float(g["sa"]), float(g["sb"])), g["C"])
+    same(port.gemm_fp8_e4m3(g["A"], g["B"], float(g["sa"]), float(g["sb"]), g["C0"], alpha=0.5, beta=2.0), g["C_ab"])
+
+
 def test_port_matches_compiled_reference_on_larger_inputs():
     ref = Checker("lhr")
     rng = np.random.default_rng(7)
