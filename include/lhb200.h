@@ -234,6 +234,20 @@ LHB_API int lhb_rope_decode_batched(lhb_ctx* ctx, float* x, const int32_t* posit
  * y[r, i] = gate * sigmoid(gate) * value. */
 LHB_API int lhb_swiglu(lhb_ctx* ctx, const float* x, float* y, int rows, int dim, void* stream);
 
+/* Decode-step fusion (no counterpart in the reference): qkv = [n_requests rows, row_stride floats
+ * apart], each row = [n_q_heads | n_kv_heads | n_kv_heads] heads of head_dim, the output of a fused
+ * QKV projection.  Equals lhb_rope_decode_batched on the q and on the k heads followed by
+ * lhb_paged_kv_append_q8_batched(seq_new = 1) with the rotated k and the v heads, bit for bit:
+ * rotated q goes to q_out [n_requests, n_q_heads, head_dim], k and v rows into the pools at
+ * position positions[r] of request r. */
+LHB_API int lhb_qkv_rope_append_q8_decode(lhb_ctx* ctx, const float* qkv, int64_t row_stride, float* q_out,
+                                          int8_t* k_pool, int8_t* v_pool, float* k_scales,
+                                          float* v_scales, const int32_t* block_tables,
+                                          int max_blocks_per_req, const int32_t* positions,
+                                          int n_requests, int n_q_heads,
+                                          const lhb_paged_layout* layout, float theta_base,
+                                          float freq_scale, int interleaved, void* stream);
+
 /* ---- FP8 E4M3 ------------------------------------------------------------------------ */
 
 /* lh::fp8_quantize_per_tensor / per_row / per_col (src/kernels/quant.hpp:81-94): E4M3 bytes

@@ -94,4 +94,16 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
+// sin and cos of the rotary angle of pair i at position p: p * freq_scale / theta_base^(2i/head_dim)
+// (src/kernels/rope.cpp:9-15).  The power goes through double precision and is rounded once, as
+// the host's powf does: a few ulps in the frequency would become 1e-3 rad at position 8000.
+__device__ __forceinline__ void rope_sincos(int p, int i, int head_dim, float theta_base, float freq_scale,
+                                            float* sn, float* c) {
+    const float pos = __fmul_rn(static_cast<float>(p), freq_scale);
+    const float exponent = __fdiv_rn(static_cast<float>(2 * i), static_cast<float>(head_dim));
+    const float inv_freq = __fdiv_rn(1.0f, static_cast<float>(pow(static_cast<double>(theta_base),
+                                                                   static_cast<double>(exponent))));
+    sincosf(__fmul_rn(pos, inv_freq), sn, c);
+}
+
 }  // namespace lhb

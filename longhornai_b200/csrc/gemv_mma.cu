@@ -72,7 +72,8 @@ constexpr int gv_groups(int jb) { return jb >= 6 ? 2 : 1; }
 constexpr int gv_consumer_warps(int jb) { return GV_COL_WARPS * gv_groups(jb); }
 constexpr int gv_threads(int jb) { return (gv_consumer_warps(jb) + 1) * 32; }   // + one producer warp
 constexpr int GV_MAX_M = 16;
-constexpr size_t GV_DIG_BYTES = size_t(4) << 20;   // head of the scratch arena: activation digits (four slabs) + 64 row factors
+constexpr size_t GV_DIG_BYTES = size_t(4) << 20;   // head of the scratch arena: activation digits of a pass + its row factors
+constexpr size_t GV_INV_BYTES = 4096;              // the last 4 KiB of it: one fp32 factor per row, up to 1024 rows a pass
 constexpr int GV_PB = 8;           // activation float4 loads a thread keeps in flight in the prologue
 
 using ptx::smem_u32;
@@ -862,15 +863,15 @@ static int jb_for(int M) { return gv_jb_for(M); }
 bool w4a16_fast_ok(int M, int N, int K, int G) {
     if (M < 1 || (N % 16) != 0 || (K % 32) != 0 || G <= 0 || (K % G) != 0) return false;
     if (!w4_group_ok(G)) return false;            // groups must tile a 128-k stage, or be whole stages
-    if (M > 64) return false;                     // larger M: generic path (dense GEMM territory)
-    if (M > 2 && static_cast<size_t>(ceil_div(K, 128) * 128) * 48 > GV_DIG_BYTES - 256) return false;
+    if (M > 1024) return false;                   // rows are served in slabs of 16; beyond this the generic kernel
+    if (M > 2 && static_cast<size_t>(ceil_div(K, 128) * 128) * 48 > GV_DIG_BYTES - GV_INV_BYTES) return false;
     return plan_gemv(4, jb_for(std::min(M, GV_MAX_M)), N, K, G, 148).ok;
 }
 
 bool w8a16_fast_ok(int M, int N, int K) {
     if (M < 1 || (N % 16) != 0 || (K % 32) != 0) return false;
-    if (M > 64) return false;
-    if (M > 2 && static_cast<size_t>(ceil_div(K, 64) * 64) * 48 > GV_DIG_BYTES - 256) return false;
+    if (M > 1024) return false;
+    if (M > 2 && static_cast<size_t>(ceil_div(K, 64) * 64) * 48 > GV_DIG_BYTES - GV_INV_BYTES) return false;
     return plan_gemv(8, jb_for(std::min(M, GV_MAX_M)), N, K, 1, 148).ok;
 }
 
@@ -929,10 +930,11 @@ static int launch_gemv(lhb_ctx* ctx, const float* A, const void* B, const void* 
     const int k_pad = ceil_div(K, kps_d) * kps_d;
     const size_t slab_bytes = static_cast<size_t>(k_pad) * 8 * gv_jb_for(GV_MAX_M);
     uint8_t* const dig = static_cast<uint8_t*>(ctx->scratch);
-    float* const inv = reinterpret_cast<float*>(dig + GV_DIG_BYTES - 256);
+    float* const inv = reinterpret_cast<float*>(dig + GV_DIG_BYTES - GV_INV_BYTES);
     // The digit array holds a few slabs at a time (all of them unless K is very long).
-    if (ctx->scratch_bytes < GV_DIG_BYTES || (M > 2 && slab_bytes > GV_DIG_BYTES - 256)) return LHB_ERR_SCRATCH;
-    const int rows_per_pass = M > 2 ? static_cast<int>((GV_DIG_BYTES - 256) / slab_bytes) * GV_MAX_M : M;
+    if (ctx->scratch_bytes < GV_DIG_BYTES || (M > 2 && slab_bytes > GV_DIG_BYTES - GV_INV_BYTES)) return LHB_ERR_SCRATCH;
+    const int rows_per_pass =
+        M > 2 ? std::min<int>(GV_INV_BYTES / 4, static_cast<int>((GV_DIG_BYTES - GV_INV_BYTES) / slab_bytes) * GV_MAX_M) : M;
     int pass0 = 0;                                  // first row of the current digit pass
     for (int m0 = 0; m0 < M; m0 += GV_MAX_M) {
         if (M > 2 && (m0 == 0 || m0 - pass0 >= rows_per_pass)) {
@@ -1006,8 +1008,8 @@ int launch_w4a16_fast(lhb_ctx* ctx, const float* A, const uint8_t* Bp, const flo
 
 // asymmetric int4: the decode kernel serves group_size 128 (one group per 128-k stage)
 bool w4a16_asym_fast_ok(int M, int N, int K, int G) {
-    if (M < 1 || M > 64 || (N % 16) != 0 || (K % 128) != 0 || G != 128) return false;
-    if (M > 2 && static_cast<size_t>(K) * 48 > GV_DIG_BYTES - 256) return false;
+    if (M < 1 || M > 1024 || (N % 16) != 0 || (K % 128) != 0 || G != 128) return false;
+    if (M > 2 && static_cast<size_t>(K) * 48 > GV_DIG_BYTES - GV_INV_BYTES) return false;
     return plan_gemv(4, jb_for(std::min(M, GV_MAX_M)), N, K, G, 148, true).ok;
 }
 int launch_w4a16_asym_fast(lhb_ctx* ctx, const float* A, const uint8_t* Bp, const uint16_t* Bs, const uint16_t* Bz,

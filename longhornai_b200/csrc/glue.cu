@@ -69,15 +69,8 @@ rope_kernel(float* __restrict__ x, const int32_t* __restrict__ positions, int64_
     const int64_t rh = idx / half;                       // row * n_heads + head
     const int row = static_cast<int>(rh / n_heads);
     const int p = positions ? positions[row] + pos_offset : pos_offset + row;
-    const float pos = __fmul_rn(static_cast<float>(p), freq_scale);
-    const float exponent = __fdiv_rn(static_cast<float>(2 * i), static_cast<float>(head_dim));
-    // The power goes through double precision and is rounded once, as the host's powf does:
-    // a few ulps in inv_freq would become 1e-3 rad at position 8000.
-    const float inv_freq = __fdiv_rn(1.0f, static_cast<float>(pow(static_cast<double>(theta_base),
-                                                                   static_cast<double>(exponent))));
-    const float angle = __fmul_rn(pos, inv_freq);
     float sn, c;
-    sincosf(angle, &sn, &c);
+    rope_sincos(p, i, head_dim, theta_base, freq_scale, &sn, &c);
     float* v = x + rh * head_dim;
     if (interleaved) {
         const float2 ab = *reinterpret_cast<const float2*>(v + 2 * i);

@@ -63,6 +63,58 @@ paged_kv_append_q8_kernel(int8_t* __restrict__ k_pool, int8_t* __restrict__ v_po
     quantize_row_warp(v_new + src, v_pool + srow * L.head_dim, v_scales + srow, L.head_dim, lane);
 }
 
+// Decode-step fusion: the fused QKV projection's output row [q heads | k heads | v heads]
+// is split, the q and k heads are rotated (rotary embedding at the request's position), q goes
+// to a contiguous [n_req, n_q_heads, head_dim] tensor and the rotated k and the v rows are
+// quantised straight into the request's page.  One warp per (request, head); the result is
+// bit-identical to rope on q, rope on k and paged_kv_append_q8 run one after the other
+// (src/kernels/rope.cpp:47-86, src/kernels/kvcache_quant.cpp:58-80), without the three
+// intermediate tensors and five launches.
+constexpr int QKV_MAX_D = 256;
+
+__global__ void __launch_bounds__(128)
+qkv_rope_append_q8_kernel(const float* __restrict__ qkv, int64_t row_stride, float* __restrict__ q_out,
+                          int8_t* __restrict__ k_pool, int8_t* __restrict__ v_pool, float* __restrict__ k_scales,
+                          float* __restrict__ v_scales, const int32_t* __restrict__ block_tables, int max_blocks,
+                          const int32_t* __restrict__ positions, int n_req, int n_q_heads, lhb_paged_layout L,
+                          float theta_base, float freq_scale, int interleaved) {
+    __shared__ __align__(16) float rot[4][QKV_MAX_D];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int heads = n_q_heads + 2 * L.n_kv_heads;
+    const int64_t item = static_cast<int64_t>(blockIdx.x) * 4 + w;
+    if (item >= static_cast<int64_t>(n_req) * heads) return;
+    const int r = static_cast<int>(item / heads), j = static_cast<int>(item % heads);
+    const int d = L.head_dim, half = d >> 1;
+    const int pos = positions[r];
+    const float* src = qkv + r * row_stride + static_cast<int64_t>(j) * d;
+    const bool is_v = j >= n_q_heads + L.n_kv_heads;
+    const float* row = src;
+    if (!is_v) {
+        for (int i = lane; i < half; i += 32) {
+            float sn, c;
+            rope_sincos(pos, i, d, theta_base, freq_scale, &sn, &c);
+            const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
+            const float a = src[ia], b = src[ib];
+            rot[w][ia] = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, sn));
+            rot[w][ib] = interleaved ? __fadd_rn(__fmul_rn(a, sn), __fmul_rn(b, c))
+                                     : __fadd_rn(__fmul_rn(b, c), __fmul_rn(a, sn));
+        }
+        __syncwarp();
+        row = rot[w];
+    }
+    if (j < n_q_heads) {
+        float* dst = q_out + (static_cast<int64_t>(r) * n_q_heads + j) * d;
+        for (int i = lane; i < d; i += 32) dst[i] = row[i];
+        return;
+    }
+    const int h = is_v ? j - n_q_heads - L.n_kv_heads : j - n_q_heads;
+    const int blk = block_tables[static_cast<int64_t>(r) * max_blocks + pos / L.block_size];
+    if (blk < 0 || blk >= L.num_blocks) return;       // unallocated page: nothing to write
+    const int64_t srow = (static_cast<int64_t>(blk) * L.n_kv_heads + h) * L.block_size + pos % L.block_size;
+    if (is_v) quantize_row_warp(row, v_pool + srow * d, v_scales + srow, d, lane);
+    else quantize_row_warp(row, k_pool + srow * d, k_scales + srow, d, lane);
+}
+
 // fp32 append (src/kernels/kvcache.cpp:7-32): a row copy.
 __global__ void __launch_bounds__(128)
 paged_kv_append_f32_kernel(float* __restrict__ k_pool, float* __restrict__ v_pool,
@@ -150,6 +202,27 @@ int lhb_paged_kv_append_f32(lhb_ctx* ctx, float* k_pool, float* v_pool, const fl
     paged_kv_append_f32_kernel<<<static_cast<unsigned>(ceil_div64(rows, 4)), 128, 0,
                                  as_stream(stream)>>>(k_pool, v_pool, k_new, v_new, block_table,
                                                       past_len, seq_new, *layout);
+    LHB_LAUNCH_CHECK();
+    return LHB_OK;
+}
+
+int lhb_qkv_rope_append_q8_decode(lhb_ctx* ctx, const float* qkv, int64_t row_stride, float* q_out, int8_t* k_pool,
+                                  int8_t* v_pool, float* k_scales, float* v_scales, const int32_t* block_tables,
+                                  int max_blocks_per_req, const int32_t* positions, int n_requests, int n_q_heads,
+                                  const lhb_paged_layout* layout, float theta_base, float freq_scale,
+                                  int interleaved, void* stream) {
+    if (!ctx || !qkv || !q_out || !k_pool || !v_pool || !k_scales || !v_scales || !block_tables || !positions)
+        return LHB_ERR_NULL;
+    if (int e = check_layout(layout)) return e;
+    if (n_requests < 0 || n_q_heads <= 0 || max_blocks_per_req <= 0 || (layout->head_dim & 1)) return LHB_ERR_BAD_SHAPE;
+    if (layout->head_dim > QKV_MAX_D) return LHB_ERR_UNSUPPORTED;
+    const int heads = n_q_heads + 2 * layout->n_kv_heads;
+    if (row_stride < static_cast<int64_t>(heads) * layout->head_dim) return LHB_ERR_BAD_SHAPE;
+    if (n_requests == 0) return LHB_OK;
+    const int64_t items = static_cast<int64_t>(n_requests) * heads;
+    qkv_rope_append_q8_kernel<<<static_cast<unsigned>(ceil_div64(items, 4)), 128, 0, as_stream(stream)>>>(
+        qkv, row_stride, q_out, k_pool, v_pool, k_scales, v_scales, block_tables, max_blocks_per_req, positions,
+        n_requests, n_q_heads, *layout, theta_base, freq_scale, interleaved);
     LHB_LAUNCH_CHECK();
     return LHB_OK;
 }

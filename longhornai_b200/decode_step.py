@@ -7,8 +7,8 @@ for a pre-norm decoder layer with grouped-query attention and a SwiGLU MLP:
     h  = rmsnorm(x)                          src/kernels/normalization.hpp:21
     q | k | v = h Wqkv                       gemm_w4a16_groupwise (gemm_quant.hpp:54), one GEMM over
                                              the three projections' columns side by side
-    rope(q), rope(k) at each request's position          src/kernels/rope.hpp:19
-    append k, v to the int8 paged cache      paged_kv_append_q8 (kvcache_quant.hpp:41)
+    rope(q), rope(k) at each request's position          src/kernels/rope.hpp:19          } one fused
+    append k, v to the int8 paged cache      paged_kv_append_q8 (kvcache_quant.hpp:41)    } launch
     o  = paged attention over the cache      paged_attention_q8 (kvcache_quant.hpp:51)
     x += o Wo                                the residual add is beta = 1 of the GEMM
     h  = rmsnorm(x)
@@ -125,16 +125,10 @@ def decode_layer(x, w: LayerWeights, pools: KVPools, block_tables, past_lens, cu
     G = cfg.group
     ops.rmsnorm(x, w.g_attn, cfg.eps, out=buf.h, ctx=ctx)
     ops.gemm_w4a16_groupwise(buf.h, *w.wqkv, G, C=buf.qkv, ctx=ctx)
-    # split the row [q | k | v] into the three contiguous tensors the cache calls take (copies only)
-    buf.q.copy_(buf.qkv[:, :cfg.q_dim])
-    buf.k.copy_(buf.qkv[:, cfg.q_dim:cfg.q_dim + cfg.kv_dim])
-    buf.v.copy_(buf.qkv[:, cfg.q_dim + cfg.kv_dim:])
-    ops.rope_decode_batched(buf.q.view(n_req, cfg.n_q_heads, cfg.head_dim), past_lens, cfg.rope_theta, 1.0,
-                          cfg.rope_interleaved, ctx=ctx)
-    ops.rope_decode_batched(buf.k.view(n_req, cfg.n_kv_heads, cfg.head_dim), past_lens, cfg.rope_theta, 1.0,
-                          cfg.rope_interleaved, ctx=ctx)
-    ops.paged_kv_append_q8_batched(pools.k, pools.v, pools.ks, pools.vs, buf.k, buf.v, block_tables, past_lens, L,
-                                 1, ctx=ctx)
+    # one launch: split [q | k | v], rotate q and k at the request's position, q -> buf.q, k and v -> the cache
+    ops.qkv_rope_append_q8_decode(buf.qkv, buf.q.view(n_req, cfg.n_q_heads, cfg.head_dim), pools.k, pools.v,
+                                  pools.ks, pools.vs, block_tables, past_lens, cfg.n_q_heads, L, cfg.rope_theta,
+                                  1.0, cfg.rope_interleaved, ctx=ctx)
     ops.paged_attention_q8_batched(buf.q.view(n_req, cfg.n_q_heads, 1, cfg.head_dim), pools.k, pools.v, pools.ks,
                                  pools.vs, block_tables, cur_lens, acfg, L,
                                  O=buf.o.view(n_req, cfg.n_q_heads, 1, cfg.head_dim), ctx=ctx)
@@ -155,12 +149,12 @@ def decode_step(x, layers, pools, block_tables, past_lens, cur_lens, cfg: StepCo
 
 
 def launches_per_layer(n_req: int) -> int:
-    """This library's kernel launches in one layer (for the bench's launch count): 2 norms,
-    2 rotations, append, attention, SwiGLU, and 4 GEMMs each served in slabs of 16 rows plus one
-    digit pass when there are more than two rows.  (The three q/k/v split copies are torch's.)"""
+    """Kernel launches in one layer (for the bench's launch count): 2 norms, the fused
+    split + rotation + append, attention, SwiGLU, and 4 GEMMs each served in slabs of 16 rows plus
+    one digit pass when there are more than two rows."""
     slabs = (n_req + 15) // 16
     per_gemm = slabs + (1 if n_req > 2 else 0)
-    return 7 + 4 * per_gemm
+    return 5 + 4 * per_gemm
 
 
 # ---- tensor-parallel step: projections sharded along N, attention by KV head ----------------
@@ -241,15 +235,9 @@ def decode_layer_tp(x, w: LayerWeights, pools: KVPools, block_tables, past_lens,
     lo = rank * (cfg.dim // world)
     ops.rmsnorm(x, w.g_attn, cfg.eps, out=b.h, ctx=ctx)
     ops.gemm_w4a16_groupwise(b.h, *w.wqkv, G, C=b.qkv, ctx=ctx)
-    b.q.copy_(b.qkv[:, :lc.q_dim])
-    b.k.copy_(b.qkv[:, lc.q_dim:lc.q_dim + lc.kv_dim])
-    b.v.copy_(b.qkv[:, lc.q_dim + lc.kv_dim:])
-    ops.rope_decode_batched(b.q.view(n_req, lc.n_q_heads, lc.head_dim), past_lens, cfg.rope_theta, 1.0,
-                          cfg.rope_interleaved, ctx=ctx)
-    ops.rope_decode_batched(b.k.view(n_req, lc.n_kv_heads, lc.head_dim), past_lens, cfg.rope_theta, 1.0,
-                          cfg.rope_interleaved, ctx=ctx)
-    ops.paged_kv_append_q8_batched(pools.k, pools.v, pools.ks, pools.vs, b.k, b.v, block_tables, past_lens, L, 1,
-                                 ctx=ctx)
+    ops.qkv_rope_append_q8_decode(b.qkv, b.q.view(n_req, lc.n_q_heads, lc.head_dim), pools.k, pools.v, pools.ks,
+                                  pools.vs, block_tables, past_lens, lc.n_q_heads, L, cfg.rope_theta, 1.0,
+                                  cfg.rope_interleaved, ctx=ctx)
     ops.paged_attention_q8_batched(b.q.view(n_req, lc.n_q_heads, 1, lc.head_dim), pools.k, pools.v, pools.ks,
                                  pools.vs, block_tables, cur_lens, acfg, L,
                                  O=b.o.view(n_req, lc.n_q_heads, 1, lc.head_dim), ctx=ctx)

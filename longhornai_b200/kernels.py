@@ -353,6 +353,22 @@ def rope_decode_batched(x, positions, theta_base: float = 10000.0, freq_scale: f
     return x
 
 
+def qkv_rope_append_q8_decode(qkv, q_out, k_pool, v_pool, k_scales, v_scales, block_tables, positions,
+                              n_q_heads: int, L: PagedLayout, theta_base: float = 10000.0, freq_scale: float = 1.0,
+                              interleaved: bool = True, ctx=None):
+    """Split a fused QKV row, rotate q and k at positions[r], write q to `q_out` [n_req, n_q_heads, head_dim] and
+    quantise k, v into the paged int8 cache: rope + rope + append in one launch, same bits."""
+    c = _ctx_for(qkv, ctx)
+    n_req, max_blocks = block_tables.shape
+    check(c.lib.lhb_qkv_rope_append_q8_decode(
+        c.handle, _t(qkv, torch.float32, "qkv"), qkv.stride(0), _t(q_out, torch.float32, "q_out"),
+        _t(k_pool, torch.int8, "k_pool"), _t(v_pool, torch.int8, "v_pool"), _t(k_scales, torch.float32, "k_scales"),
+        _t(v_scales, torch.float32, "v_scales"), _t(block_tables, torch.int32, "block_tables"), max_blocks,
+        _t(positions, torch.int32, "positions"), n_req, n_q_heads, C.byref(L), C.c_float(theta_base),
+        C.c_float(freq_scale), int(bool(interleaved)), _stream(c.device)), "qkv_rope_append_q8_decode")
+    return q_out
+
+
 def swiglu(x, out=None, ctx=None):
     """lh::swiglu (src/kernels/activation.hpp:34): fp32 [rows, 2*dim] (gate || value) -> [rows, dim]."""
     c = _ctx_for(x, ctx)

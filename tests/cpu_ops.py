@@ -47,6 +47,20 @@ class CpuOps:
                                         vn[r].reshape(L.n_kv_heads, seq_new, L.head_dim), tb[r], Lc, int(past[r]),
                                         seq_new)
 
+    def qkv_rope_append_q8_decode(self, qkv, q_out, k_pool, v_pool, k_scales, v_scales, block_tables, positions,
+                                  n_q_heads, L, theta_base=10000.0, freq_scale=1.0, interleaved=True, ctx=None):
+        """The fused call as the three reference steps it stands for: rope(q), rope(k), append(k, v)."""
+        n_req, hd, hkv = qkv.shape[0], L.head_dim, L.n_kv_heads
+        qd, kd = n_q_heads * hd, hkv * hd
+        q = qkv[:, :qd].contiguous().view(n_req, n_q_heads, hd)
+        k = qkv[:, qd:qd + kd].contiguous().view(n_req, hkv, hd)
+        v = qkv[:, qd + kd:qd + 2 * kd].contiguous().view(n_req, hkv, hd)
+        self.rope_decode_batched(q, positions, theta_base, freq_scale, interleaved)
+        self.rope_decode_batched(k, positions, theta_base, freq_scale, interleaved)
+        q_out.copy_(q)
+        self.paged_kv_append_q8_batched(k_pool, v_pool, k_scales, v_scales, k, v, block_tables, positions, L, 1)
+        return q_out
+
     def paged_attention_q8_batched(self, Q, K_pool, V_pool, K_scales, V_scales, block_tables, seq_lens, cfg, L,
                                    O=None, ctx=None):
         pools = PagedPools(self._np(K_pool), self._np(V_pool), self._np(K_scales), self._np(V_scales))

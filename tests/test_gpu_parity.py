@@ -199,6 +199,21 @@ def test_w4a16_unit_ranges_and_partial_sums(chk, M, N, K, G):
     poll_ok()
 
 
+@pytest.mark.parametrize("M,N,K,G", [(100, 1040, 1024, 128), (300, 512, 2048, 64), (200, 256, 16384, 128)])
+def test_w4a16_many_rows_in_slabs(chk, lib, M, N, K, G):
+    """More than 64 rows: slabs of 16 rows over one digit pass, or several passes when K is long
+    (K = 16384: 80 rows per pass); the last slab is ragged."""
+    assert lib.lhb_gemm_w4a16_fast_path(M, N, K, G) == 1
+    rng = np.random.default_rng(M + N + K)
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    W = (rng.standard_normal((K, N)) * 0.02).astype(np.float32)
+    p, s = chk.q4_quantize_groupwise(W, G)
+    C0 = rng.standard_normal((M, N)).astype(np.float32)
+    got = lb.gemm_w4a16_groupwise(dev(A), dev(p), dev(s), G, C=dev(C0), alpha=0.5, beta=2.0)
+    assert_close(host(got), chk.gemm_w4a16_groupwise(A, p, s, G, C0, alpha=0.5, beta=2.0), what=f"{M}x{N}x{K}")
+    poll_ok()
+
+
 def test_w4a16_linearity_and_determinism():
     K, N, G = 2048, 2048, 128
     g = torch.Generator(device="cuda").manual_seed(5)
@@ -575,4 +590,34 @@ def test_fp8_gemm_tensor_core_path_against_checker(chk, lib, M, N, K):
     want = chk.gemm_fp8_e4m3(A, B, sa, sb, C0, alpha=0.75, beta=1.0)
     got = lb.gemm_fp8_e4m3(dev(A), dev(B), sa, sb, C=dev(C0), alpha=0.75, beta=1.0)
     assert_close(host(got), want, what=f"fp8 gemm {M}x{N}x{K}")
+    poll_ok()
+
+
+def test_fused_qkv_rope_append_equals_the_three_calls():
+    """lhb_qkv_rope_append_q8_decode = rope(q) + rope(k) + paged_kv_append_q8_batched, bit for bit."""
+    rng = np.random.default_rng(91)
+    n_req, hq, hkv, hd, bs, nb, mb = 6, 8, 2, 128, 16, 40, 6
+    L = lb.PagedLayout(nb, bs, hkv, hd)
+    pos = np.array([0, 5, 15, 16, 47, 80], np.int32)
+    perm = rng.permutation(nb).astype(np.int32)
+    tables = perm[:n_req * mb].reshape(n_req, mb).copy()
+    qkv = dev(rng.standard_normal((n_req, (hq + 2 * hkv) * hd)).astype(np.float32))
+
+    def pools():
+        shape = (nb, hkv, bs, hd)
+        return (torch.zeros(shape, dtype=torch.int8, device="cuda"), torch.zeros(shape, dtype=torch.int8, device="cuda"),
+                torch.zeros(shape[:3], device="cuda"), torch.zeros(shape[:3], device="cuda"))
+    for interleaved in (False, True):
+        k1, v1, ks1, vs1 = pools()
+        q1 = torch.empty(n_req, hq, hd, device="cuda")
+        lb.qkv_rope_append_q8_decode(qkv, q1, k1, v1, ks1, vs1, dev(tables), dev(pos), hq, L, 500000.0, 1.0, interleaved)
+        k2, v2, ks2, vs2 = pools()
+        q2 = qkv[:, :hq * hd].contiguous().view(n_req, hq, hd)
+        kk = qkv[:, hq * hd:(hq + hkv) * hd].contiguous().view(n_req, hkv, hd)
+        vv = qkv[:, (hq + hkv) * hd:].contiguous().view(n_req, hkv, hd)
+        lb.rope_decode_batched(q2, dev(pos), 500000.0, 1.0, interleaved)
+        lb.rope_decode_batched(kk, dev(pos), 500000.0, 1.0, interleaved)
+        lb.paged_kv_append_q8_batched(k2, v2, ks2, vs2, kk, vv, dev(tables), dev(pos), L, 1)
+        assert torch.equal(q1, q2) and torch.equal(k1, k2) and torch.equal(v1, v2)
+        assert torch.equal(ks1, ks2) and torch.equal(vs1, vs2)
     poll_ok()
