@@ -234,6 +234,17 @@ LHB_API int lhb_rope_decode_batched(lhb_ctx* ctx, float* x, const int32_t* posit
  * y[r, i] = gate * sigmoid(gate) * value. */
 LHB_API int lhb_swiglu(lhb_ctx* ctx, const float* x, float* y, int rows, int dim, void* stream);
 
+/* lhb_gemm_w4a16_groupwise with an operator of the decode step applied to the activations on the way
+ * in (no counterpart in the reference; equals the two calls one after the other up to the order of the
+ * sum of squares): prologue 1 = lh::rmsnorm(X [M, K], gamma [K], eps), 2 = lh::swiglu(X [M, 2K]).  The
+ * normalised / activated tensor is never written.  Served for shapes of the tensor-core kernel whose
+ * last slab of 16 rows has more than two rows; otherwise LHB_ERR_UNSUPPORTED, and the caller makes the
+ * two calls. */
+LHB_API int lhb_gemm_w4a16_groupwise_prologue(lhb_ctx* ctx, const float* X, int prologue,
+                                              const float* gamma, float eps, const uint8_t* B_packed,
+                                              const float* B_scales, float* C, int M, int N, int K,
+                                              int group_size, float alpha, float beta, void* stream);
+
 /* Decode-step fusion (no counterpart in the reference): qkv = [n_requests rows, row_stride floats
  * apart], each row = [n_q_heads | n_kv_heads | n_kv_heads] heads of head_dim, the output of a fused
  * QKV projection.  Equals lhb_rope_decode_batched on the q and on the k heads followed by

@@ -18,7 +18,7 @@ from .kernels import (Context, default_context, gemm_w4a16_groupwise, gemm_w8a8,
                       q8_quantize_per_row, rmsnorm, rope, rope_decode_batched, swiglu,
                       gemm_w4a16_asym, q4a_dequantize_groupwise, q4a_quantize_groupwise,
                       fp8_dequantize, fp8_quantize_per_col, fp8_quantize_per_row, fp8_quantize_per_tensor,
-                      gemm_fp8_e4m3, qkv_rope_append_q8_decode)
+                      gemm_fp8_e4m3, qkv_rope_append_q8_decode, gemm_w4a16_norm, gemm_w4a16_swiglu)
 from .runtime import ActiveStep, DeviceCacheManager, DeviceScheduler
 
 __all__ = [n for n in dir() if not n.startswith("_")]

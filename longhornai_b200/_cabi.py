@@ -54,6 +54,7 @@ SIGNATURES = {
     "lhb_rope": (_i, [_vp, _vp, _i, _i, _i, _f, _f, _i, _i, _vp]),
     "lhb_rope_decode_batched": (_i, [_vp, _vp, _vp, _i, _i, _i, _f, _f, _i, _vp]),
     "lhb_swiglu": (_i, [_vp, _vp, _vp, _i, _i, _vp]),
+    "lhb_gemm_w4a16_groupwise_prologue": (_i, [_vp, _vp, _i, _vp, _f, _vp, _vp, _vp, _i, _i, _i, _i, _f, _f, _vp]),
     "lhb_qkv_rope_append_q8_decode": (_i, [_vp, _vp, C.c_int64, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _LP,
                                            _f, _f, _i, _vp]),
     "lhb_fp8_quantize_per_tensor": (_i, [_vp, _vp, _vp, _vp, C.c_int64, _vp]),

@@ -126,6 +126,21 @@ int lhb_gemm_w8a16_perchannel(lhb_ctx* ctx, const float* A, const int8_t* Bq, co
     return launch_w8a16_generic(A, Bq, Bs, C, M, N, K, alpha, beta, st);
 }
 
+int lhb_gemm_w4a16_groupwise_prologue(lhb_ctx* ctx, const float* X, int prologue, const float* gamma, float eps,
+                                      const uint8_t* Bp, const float* Bs, float* C, int M, int N, int K, int G,
+                                      float alpha, float beta, void* stream) {
+    if (!ctx || !X || !Bp || !Bs || !C) return LHB_ERR_NULL;
+    if (prologue != 1 && prologue != 2) return LHB_ERR_BAD_SHAPE;
+    if (prologue == 1 && !gamma) return LHB_ERR_NULL;
+    if (M < 0 || N <= 0 || K <= 0 || G <= 0 || (K % 2) || (K % G)) return LHB_ERR_BAD_SHAPE;
+    if (M == 0) return LHB_OK;
+    if (!(w4a16_fast_ok(M, N, K, G) && aligned16(X) && aligned16(Bp) && aligned16(Bs) && aligned16(C) &&
+          (prologue != 1 || aligned16(gamma))))
+        return LHB_ERR_UNSUPPORTED;       // the caller runs lhb_rmsnorm / lhb_swiglu and the plain GEMM instead
+    return launch_w4a16_fast_prologue(ctx, X, prologue, gamma, eps, Bp, Bs, C, M, N, K, G, alpha, beta,
+                                      as_stream(stream));
+}
+
 int lhb_gemm_w8a8(lhb_ctx* ctx, const int8_t* Aq, const int8_t* Bq, const float* as,
                   const float* bs, float* C, int M, int N, int K, float alpha, float beta,
                   void* stream) {

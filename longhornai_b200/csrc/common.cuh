@@ -94,6 +94,13 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
+// SwiGLU of one element: (gate * sigmoid(gate)) * value with sigmoid(v) = 1 / (1 + exp(-v)), in the
+// reference's operation order (src/kernels/activation.cpp:12, 46-55).
+__device__ __forceinline__ float swiglu_one(float g, float v) {
+    const float sg = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-g)));
+    return __fmul_rn(__fmul_rn(g, sg), v);
+}
+
 // sin and cos of the rotary angle of pair i at position p: p * freq_scale / theta_base^(2i/head_dim)
 // (src/kernels/rope.cpp:9-15).  The power goes through double precision and is rounded once, as
 // the host's powf does: a few ulps in the frequency would become 1e-3 rad at position 8000.

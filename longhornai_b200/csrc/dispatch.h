@@ -42,6 +42,11 @@ int launch_decode_fast(lhb_ctx* ctx, const float* Q, const int8_t* Kp, const int
                        const int32_t* seq_lens, int n_req, float* O, const lhb_paged_attn_cfg& cfg,
                        const lhb_paged_layout& L, cudaStream_t st);
 
+// W4A16 with a prologue on the activations (1 = RMSNorm with gamma/eps, 2 = SwiGLU of [gate || value] rows)
+int launch_w4a16_fast_prologue(lhb_ctx* ctx, const float* X, int prologue, const float* gamma, float eps,
+                               const uint8_t* Bp, const float* Bs, float* C, int M, int N, int K, int G, float alpha,
+                               float beta, cudaStream_t st);
+
 // fp8 E4M3 GEMM: generic kernel in fp8.cu, tcgen05 path in gemm_w8a8_tc.cu (shapes of w8a8_fast_ok)
 int launch_fp8_generic(const uint8_t* A, const uint8_t* B, float combined, float* C, int M, int N, int K, float beta,
                        cudaStream_t st);

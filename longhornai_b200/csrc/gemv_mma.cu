@@ -200,11 +200,19 @@ __host__ __device__ constexpr int gv_jb_for(int M) { return M <= 2 ? 1 : (M <= 5
 // the operand order of gemv_mma_kernel.  Rows are served in slabs of 16; slab s owns
 // `slab_bytes` of the array, laid out [K/32 blocks][nj columns][32 bytes] with nj = 8 * JB
 // of that slab's launch; k >= K is written as zero up to k_pad.
+// What the digit pass does to its input before making digits: nothing, RMSNorm of the row
+// (src/kernels/normalization.cpp:58-76) or SwiGLU of a [gate || value] row
+// (src/kernels/activation.cpp:46-55).  With a prologue the GEMM consumes norm(x) / swiglu(x)
+// without that tensor ever being written.
+enum GemvPrologue { GV_PRO_NONE = 0, GV_PRO_RMSNORM = 1, GV_PRO_SWIGLU = 2 };
+
 template <int WBITS>
 __global__ void __launch_bounds__(1024)
 gemv_digits_kernel(const float* __restrict__ A, int M, int K, int k_pad, size_t slab_bytes,
-                   uint8_t* __restrict__ digits, float* __restrict__ inv_scale) {
+                   uint8_t* __restrict__ digits, float* __restrict__ inv_scale, int prologue,
+                   const float* __restrict__ gamma, float eps) {
     __shared__ unsigned s_max[32];
+    __shared__ float s_sum[32];
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");      // A may come from the kernel before; so may readers of `digits`
     const int row_g = blockIdx.x, slab = row_g / GV_MAX_M, m = row_g % GV_MAX_M;
@@ -213,11 +221,66 @@ gemv_digits_kernel(const float* __restrict__ A, int M, int K, int k_pad, size_t 
     const int nj = 8 * jb;
     digits += slab * slab_bytes;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const float* row = A + static_cast<int64_t>(row_g) * K;
+    const int64_t row_len = (prologue == GV_PRO_SWIGLU) ? 2 * static_cast<int64_t>(K) : K;
+    const float* row = A + static_cast<int64_t>(row_g) * row_len;
+    // Rows of up to 16384 elements stay in registers between the passes (one trip to memory, the
+    // prologue computed once); longer rows are re-read and the prologue recomputed.
+    constexpr int DC = 4;                                   // float4 per thread held in registers
+    const bool cached = K <= 4096 * DC;
+    float4 hv[DC];
+    if (cached) {
+#pragma unroll
+        for (int i = 0; i < DC; ++i) {
+            const int k = threadIdx.x * 4 + i * 4096;
+            hv[i] = (k < K) ? *reinterpret_cast<const float4*>(row + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    float inv_rms = 1.0f;
+    if (prologue == GV_PRO_RMSNORM) {
+        float ss = 0.0f;
+        if (cached) {
+#pragma unroll
+            for (int i = 0; i < DC; ++i) ss += hv[i].x * hv[i].x + hv[i].y * hv[i].y + hv[i].z * hv[i].z + hv[i].w * hv[i].w;
+        } else {
+            for (int k = threadIdx.x * 4; k < K; k += 4096) {
+                const float4 v = *reinterpret_cast<const float4*>(row + k);
+                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            }
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) s_sum[warp] = ss;
+        __syncthreads();
+        ss = s_sum[0];
+#pragma unroll
+        for (int w = 1; w < 32; ++w) ss += s_sum[w];        // same order in every thread
+        inv_rms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, static_cast<float>(K)), eps)));
+    }
+    // the prologue on four consecutive inputs at k (k < K), given their raw values
+    auto transform = [&](float4 v, int k) {
+        if (prologue == GV_PRO_RMSNORM) {
+            const float4 g = *reinterpret_cast<const float4*>(gamma + k);
+            v.x = __fmul_rn(__fmul_rn(v.x, inv_rms), g.x); v.y = __fmul_rn(__fmul_rn(v.y, inv_rms), g.y);
+            v.z = __fmul_rn(__fmul_rn(v.z, inv_rms), g.z); v.w = __fmul_rn(__fmul_rn(v.w, inv_rms), g.w);
+        } else if (prologue == GV_PRO_SWIGLU) {
+            const float4 u = *reinterpret_cast<const float4*>(row + K + k);
+            v.x = swiglu_one(v.x, u.x); v.y = swiglu_one(v.y, u.y);
+            v.z = swiglu_one(v.z, u.z); v.w = swiglu_one(v.w, u.w);
+        }
+        return v;
+    };
     float mx = 0.0f;
-    for (int k = threadIdx.x * 4; k < K; k += 4096) {
-        const float4 v = *reinterpret_cast<const float4*>(row + k);
-        mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+    if (cached) {
+#pragma unroll
+        for (int i = 0; i < DC; ++i) {
+            const int k = threadIdx.x * 4 + i * 4096;
+            if (k < K && prologue != GV_PRO_NONE) hv[i] = transform(hv[i], k);
+            mx = fmaxf(mx, fmaxf(fmaxf(fabsf(hv[i].x), fabsf(hv[i].y)), fmaxf(fabsf(hv[i].z), fabsf(hv[i].w))));
+        }
+    } else {
+        for (int k = threadIdx.x * 4; k < K; k += 4096) {
+            const float4 v = transform(*reinterpret_cast<const float4*>(row + k), k);
+            mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+        }
     }
     mx = warp_max(mx);
     if (lane == 0) s_max[warp] = __float_as_uint(mx);
@@ -230,10 +293,18 @@ gemv_digits_kernel(const float* __restrict__ A, int M, int K, int k_pad, size_t 
     se = max(1, min(253, se));
     const float scl = __uint_as_float(static_cast<uint32_t>(se) << 23);
     if (threadIdx.x == 0) inv_scale[row_g] = __uint_as_float(static_cast<uint32_t>(254 - se) << 23);
-    for (int k = threadIdx.x * 4; k < k_pad; k += 4096) {
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (k < K) v = *reinterpret_cast<const float4*>(row + k);
-        write_digits<WBITS>(digits + (static_cast<int64_t>(k >> 5) * nj + 3 * m) * 32, k & 31, v, scl);
+    if (cached) {
+#pragma unroll
+        for (int i = 0; i < DC; ++i) {
+            const int k = threadIdx.x * 4 + i * 4096;
+            if (k < k_pad) write_digits<WBITS>(digits + (static_cast<int64_t>(k >> 5) * nj + 3 * m) * 32, k & 31, hv[i], scl);
+        }
+    } else {
+        for (int k = threadIdx.x * 4; k < k_pad; k += 4096) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (k < K) v = transform(*reinterpret_cast<const float4*>(row + k), k);
+            write_digits<WBITS>(digits + (static_cast<int64_t>(k >> 5) * nj + 3 * m) * 32, k & 31, v, scl);
+        }
     }
 }
 
@@ -918,7 +989,8 @@ static int launch_gemv_t(lhb_ctx* ctx, const TensorMap& tm, const TensorMap& tms
 
 template <int WBITS, bool ASYM = false>
 static int launch_gemv(lhb_ctx* ctx, const float* A, const void* B, const void* scales_v, const void* zeros, float* C,
-                       int M, int N, int K, int G, float alpha, float beta, cudaStream_t st) {
+                       int M, int N, int K, int G, float alpha, float beta, cudaStream_t st,
+                       int prologue = GV_PRO_NONE, const float* gamma = nullptr, float eps = 0.0f) {
     const float* scales = ASYM ? nullptr : static_cast<const float*>(scales_v);
     const uint64_t rows = (WBITS == 4) ? K / 2 : K;
     TensorMap tm, tms, tmz;
@@ -931,6 +1003,9 @@ static int launch_gemv(lhb_ctx* ctx, const float* A, const void* B, const void* 
     const size_t slab_bytes = static_cast<size_t>(k_pad) * 8 * gv_jb_for(GV_MAX_M);
     uint8_t* const dig = static_cast<uint8_t*>(ctx->scratch);
     float* const inv = reinterpret_cast<float*>(dig + GV_DIG_BYTES - GV_INV_BYTES);
+    // A prologue is applied where the digits are made, by the digit pass; a slab of one or two rows
+    // makes its own digits inside the GEMV kernel and has no such hook.
+    if (prologue != GV_PRO_NONE && jb_for(M - ((M - 1) / GV_MAX_M) * GV_MAX_M) == 1) return LHB_ERR_UNSUPPORTED;
     // The digit array holds a few slabs at a time (all of them unless K is very long).
     if (ctx->scratch_bytes < GV_DIG_BYTES || (M > 2 && slab_bytes > GV_DIG_BYTES - GV_INV_BYTES)) return LHB_ERR_SCRATCH;
     const int rows_per_pass =
@@ -950,8 +1025,9 @@ static int launch_gemv(lhb_ctx* ctx, const float* A, const void* B, const void* 
             da[0].val.programmaticStreamSerializationAllowed = 1;
             dc.attrs = da;
             dc.numAttrs = 1;
-            LHB_CUDA(cudaLaunchKernelEx(&dc, gemv_digits_kernel<WBITS>, A + static_cast<int64_t>(pass0) * K, rows, K,
-                                        k_pad, slab_bytes, dig, inv));
+            const int64_t row_len = (prologue == GV_PRO_SWIGLU) ? 2 * static_cast<int64_t>(K) : K;
+            LHB_CUDA(cudaLaunchKernelEx(&dc, gemv_digits_kernel<WBITS>, A + pass0 * row_len, rows, K, k_pad,
+                                        slab_bytes, dig, inv, prologue, gamma, eps));
         }
         const int m = std::min(GV_MAX_M, M - m0);
         const int jb = jb_for(m);
@@ -1015,6 +1091,13 @@ bool w4a16_asym_fast_ok(int M, int N, int K, int G) {
 int launch_w4a16_asym_fast(lhb_ctx* ctx, const float* A, const uint8_t* Bp, const uint16_t* Bs, const uint16_t* Bz,
                            float* C, int M, int N, int K, int G, float alpha, float beta, cudaStream_t st) {
     return launch_gemv<4, true>(ctx, A, Bp, Bs, Bz, C, M, N, K, G, alpha, beta, st);
+}
+
+// gemm_w4a16_groupwise with RMSNorm or SwiGLU applied to the activations on the way in
+int launch_w4a16_fast_prologue(lhb_ctx* ctx, const float* X, int prologue, const float* gamma, float eps,
+                               const uint8_t* Bp, const float* Bs, float* C, int M, int N, int K, int G, float alpha,
+                               float beta, cudaStream_t st) {
+    return launch_gemv<4>(ctx, X, Bp, Bs, nullptr, C, M, N, K, G, alpha, beta, st, prologue, gamma, eps);
 }
 
 int launch_w8a16_fast(lhb_ctx* ctx, const float* A, const int8_t* Bq, const float* Bs, float* C,

@@ -93,10 +93,7 @@ swiglu_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t total,
     const int64_t r = idx / dim;
     const int i = static_cast<int>(idx - r * dim);
     const float* gate = x + r * 2 * dim + i;
-    auto one = [](float g, float v) {
-        const float sg = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-g)));
-        return __fmul_rn(__fmul_rn(g, sg), v);
-    };
+    auto one = [](float g, float v) { return swiglu_one(g, v); };
     if ((dim & 3) == 0) {
         const float4 g = *reinterpret_cast<const float4*>(gate);
         const float4 v = *reinterpret_cast<const float4*>(gate + dim);

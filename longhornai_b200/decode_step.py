@@ -4,7 +4,7 @@ This is host-side composition only: every arithmetic step is one of the
 library's C-ABI calls, in the order the reference's kernels would be called
 for a pre-norm decoder layer with grouped-query attention and a SwiGLU MLP:
 
-    h  = rmsnorm(x)                          src/kernels/normalization.hpp:21
+    h  = rmsnorm(x)                          src/kernels/normalization.hpp:21         } fused into the
     q | k | v = h Wqkv                       gemm_w4a16_groupwise (gemm_quant.hpp:54), one GEMM over
                                              the three projections' columns side by side
     rope(q), rope(k) at each request's position          src/kernels/rope.hpp:19          } one fused
@@ -123,8 +123,7 @@ def decode_layer(x, w: LayerWeights, pools: KVPools, block_tables, past_lens, cu
     exercise the composition without a GPU)."""
     n_req = x.shape[0]
     G = cfg.group
-    ops.rmsnorm(x, w.g_attn, cfg.eps, out=buf.h, ctx=ctx)
-    ops.gemm_w4a16_groupwise(buf.h, *w.wqkv, G, C=buf.qkv, ctx=ctx)
+    ops.gemm_w4a16_norm(x, w.g_attn, cfg.eps, *w.wqkv, G, C=buf.qkv, scratch=buf.h, ctx=ctx)
     # one launch: split [q | k | v], rotate q and k at the request's position, q -> buf.q, k and v -> the cache
     ops.qkv_rope_append_q8_decode(buf.qkv, buf.q.view(n_req, cfg.n_q_heads, cfg.head_dim), pools.k, pools.v,
                                   pools.ks, pools.vs, block_tables, past_lens, cfg.n_q_heads, L, cfg.rope_theta,
@@ -133,10 +132,8 @@ def decode_layer(x, w: LayerWeights, pools: KVPools, block_tables, past_lens, cu
                                  pools.vs, block_tables, cur_lens, acfg, L,
                                  O=buf.o.view(n_req, cfg.n_q_heads, 1, cfg.head_dim), ctx=ctx)
     ops.gemm_w4a16_groupwise(buf.o, *w.wo, G, C=x, alpha=1.0, beta=1.0, ctx=ctx)
-    ops.rmsnorm(x, w.g_ffn, cfg.eps, out=buf.h, ctx=ctx)
-    ops.gemm_w4a16_groupwise(buf.h, *w.wgu, G, C=buf.gu, ctx=ctx)
-    ops.swiglu(buf.gu, out=buf.act, ctx=ctx)
-    ops.gemm_w4a16_groupwise(buf.act, *w.wdown, G, C=x, alpha=1.0, beta=1.0, ctx=ctx)
+    ops.gemm_w4a16_norm(x, w.g_ffn, cfg.eps, *w.wgu, G, C=buf.gu, scratch=buf.h, ctx=ctx)
+    ops.gemm_w4a16_swiglu(buf.gu, *w.wdown, G, C=x, alpha=1.0, beta=1.0, scratch=buf.act, ctx=ctx)
     return x
 
 
@@ -149,12 +146,15 @@ def decode_step(x, layers, pools, block_tables, past_lens, cur_lens, cfg: StepCo
 
 
 def launches_per_layer(n_req: int) -> int:
-    """Kernel launches in one layer (for the bench's launch count): 2 norms, the fused
-    split + rotation + append, attention, SwiGLU, and 4 GEMMs each served in slabs of 16 rows plus
-    one digit pass when there are more than two rows."""
+    """Kernel launches in one layer (for the bench's launch count): the fused split + rotation +
+    append, attention, and 4 GEMMs each served in slabs of 16 rows plus one digit pass (which also
+    applies RMSNorm / SwiGLU) when there are more than two rows; with one or two rows the two norms
+    and SwiGLU are launches of their own."""
     slabs = (n_req + 15) // 16
-    per_gemm = slabs + (1 if n_req > 2 else 0)
-    return 5 + 4 * per_gemm
+    last = n_req - (slabs - 1) * 16
+    if last <= 2:
+        return 5 + 4 * (slabs + (1 if n_req > 2 else 0))
+    return 2 + 4 * (slabs + 1)
 
 
 # ---- tensor-parallel step: projections sharded along N, attention by KV head ----------------
@@ -233,8 +233,7 @@ def decode_layer_tp(x, w: LayerWeights, pools: KVPools, block_tables, past_lens,
     n_req = x.shape[0]
     G = cfg.group
     lo = rank * (cfg.dim // world)
-    ops.rmsnorm(x, w.g_attn, cfg.eps, out=b.h, ctx=ctx)
-    ops.gemm_w4a16_groupwise(b.h, *w.wqkv, G, C=b.qkv, ctx=ctx)
+    ops.gemm_w4a16_norm(x, w.g_attn, cfg.eps, *w.wqkv, G, C=b.qkv, scratch=b.h, ctx=ctx)
     ops.qkv_rope_append_q8_decode(b.qkv, b.q.view(n_req, lc.n_q_heads, lc.head_dim), pools.k, pools.v, pools.ks,
                                   pools.vs, block_tables, past_lens, lc.n_q_heads, L, cfg.rope_theta, 1.0,
                                   cfg.rope_interleaved, ctx=ctx)
@@ -245,9 +244,8 @@ def decode_layer_tp(x, w: LayerWeights, pools: KVPools, block_tables, past_lens,
     buf.xs.copy_(x[:, lo:lo + cfg.dim // world])
     ops.gemm_w4a16_groupwise(buf.o_full, *w.wo, G, C=buf.xs, alpha=1.0, beta=1.0, ctx=ctx)
     _gather_rows(x, buf.g_x, buf.xs, dist)
-    ops.rmsnorm(x, w.g_ffn, cfg.eps, out=b.h, ctx=ctx)
-    ops.gemm_w4a16_groupwise(b.h, *w.wgu, G, C=b.gu, ctx=ctx)
-    ops.swiglu(b.gu, out=b.act, ctx=ctx)
+    ops.gemm_w4a16_norm(x, w.g_ffn, cfg.eps, *w.wgu, G, C=b.gu, scratch=b.h, ctx=ctx)
+    ops.swiglu(b.gu, out=b.act, ctx=ctx)        # its output is what the ranks exchange
     _gather_rows(buf.act_full, buf.g_act, b.act, dist)
     ops.gemm_w4a16_groupwise(buf.act_full, *w.wdown, G, C=buf.xs, alpha=1.0, beta=1.0, ctx=ctx)
     _gather_rows(x, buf.g_x, buf.xs, dist)

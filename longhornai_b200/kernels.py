@@ -353,6 +353,44 @@ def rope_decode_batched(x, positions, theta_base: float = 10000.0, freq_scale: f
     return x
 
 
+def gemm_w4a16_norm(x, gamma, eps: float, B_packed, B_scales, group_size: int, C=None, alpha: float = 1.0,
+                    beta: float = 0.0, scratch=None, ctx=None):
+    """C = beta*C + alpha * rmsnorm(x, gamma, eps) @ dequant(B): one fused call where the library serves
+    the shape, else lhb_rmsnorm into `scratch` ([M, K], allocated if None) and the plain GEMM."""
+    c = _ctx_for(x, ctx)
+    M, K_ = x.shape
+    N = B_packed.shape[1]
+    out = _out(C, M, N, x, beta)
+    rc = c.lib.lhb_gemm_w4a16_groupwise_prologue(
+        c.handle, _t(x, torch.float32, "x"), 1, _t(gamma, torch.float32, "gamma"), float(eps),
+        _t(B_packed, torch.uint8, "B_packed"), _t(B_scales, torch.float32, "B_scales"), _t(out, torch.float32, "C"),
+        M, N, K_, group_size, alpha, beta, _stream(c.device))
+    if rc == _cabi.ERR_UNSUPPORTED:
+        h = rmsnorm(x, gamma, eps, out=scratch, ctx=ctx)
+        return gemm_w4a16_groupwise(h, B_packed, B_scales, group_size, C=out, alpha=alpha, beta=beta, ctx=ctx)
+    check(rc, "gemm_w4a16_groupwise_prologue")
+    return out
+
+
+def gemm_w4a16_swiglu(x, B_packed, B_scales, group_size: int, C=None, alpha: float = 1.0, beta: float = 0.0,
+                      scratch=None, ctx=None):
+    """C = beta*C + alpha * swiglu(x) @ dequant(B) for x = [M, 2K] (gate || value); fused where served."""
+    c = _ctx_for(x, ctx)
+    M, K2 = x.shape
+    K_ = K2 // 2
+    N = B_packed.shape[1]
+    out = _out(C, M, N, x, beta)
+    rc = c.lib.lhb_gemm_w4a16_groupwise_prologue(
+        c.handle, _t(x, torch.float32, "x"), 2, None, 0.0, _t(B_packed, torch.uint8, "B_packed"),
+        _t(B_scales, torch.float32, "B_scales"), _t(out, torch.float32, "C"), M, N, K_, group_size, alpha, beta,
+        _stream(c.device))
+    if rc == _cabi.ERR_UNSUPPORTED:
+        a = swiglu(x, out=scratch, ctx=ctx)
+        return gemm_w4a16_groupwise(a, B_packed, B_scales, group_size, C=out, alpha=alpha, beta=beta, ctx=ctx)
+    check(rc, "gemm_w4a16_groupwise_prologue")
+    return out
+
+
 def qkv_rope_append_q8_decode(qkv, q_out, k_pool, v_pool, k_scales, v_scales, block_tables, positions,
                               n_q_heads: int, L: PagedLayout, theta_base: float = 10000.0, freq_scale: float = 1.0,
                               interleaved: bool = True, ctx=None):

@@ -31,6 +31,14 @@ class CpuOps:
         C.copy_(torch.from_numpy(y))
         return C
 
+    def gemm_w4a16_norm(self, x, gamma, eps, Bp, Bs, G, C=None, alpha=1.0, beta=0.0, scratch=None, ctx=None):
+        self.rmsnorm(x, gamma, eps, out=scratch)
+        return self.gemm_w4a16_groupwise(scratch, Bp, Bs, G, C=C, alpha=alpha, beta=beta)
+
+    def gemm_w4a16_swiglu(self, x, Bp, Bs, G, C=None, alpha=1.0, beta=0.0, scratch=None, ctx=None):
+        self.swiglu(x, out=scratch)
+        return self.gemm_w4a16_groupwise(scratch, Bp, Bs, G, C=C, alpha=alpha, beta=beta)
+
     def rope_decode_batched(self, x, positions, theta_base=10000.0, freq_scale=1.0, interleaved=True, ctx=None):
         xn, pos = self._np(x), self._np(positions)
         for r in range(xn.shape[0]):

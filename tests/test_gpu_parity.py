@@ -621,3 +621,25 @@ def test_fused_qkv_rope_append_equals_the_three_calls():
         assert torch.equal(q1, q2) and torch.equal(k1, k2) and torch.equal(v1, v2)
         assert torch.equal(ks1, ks2) and torch.equal(vs1, vs2)
     poll_ok()
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 16, 18, 32, 40])
+def test_w4a16_with_rmsnorm_and_swiglu_prologue(chk, lib, M):
+    """RMSNorm / SwiGLU applied inside the GEMM's digit pass (or, for slabs of one or two rows, as
+    separate launches by the wrapper) against the CPU composition of the two reference functions."""
+    rng = np.random.default_rng(300 + M)
+    K, N, G = 1024, 1040, 128
+    W = (rng.standard_normal((K, N)) * 0.03).astype(np.float32)
+    p, s = chk.q4_quantize_groupwise(W, G)
+    dp, dsc = dev(p), dev(s)
+    x = (rng.standard_normal((M, K)) * 3).astype(np.float32)
+    gamma = rng.uniform(0.5, 1.5, K).astype(np.float32)
+    C0 = rng.standard_normal((M, N)).astype(np.float32)
+    want = chk.gemm_w4a16_groupwise(chk.rmsnorm(x, gamma, 1e-5), p, s, G, C0, alpha=1.0, beta=1.0)
+    got = lb.gemm_w4a16_norm(dev(x), dev(gamma), 1e-5, dp, dsc, G, C=dev(C0), alpha=1.0, beta=1.0)
+    assert_close(host(got), want, what=f"rmsnorm prologue M={M}")
+    gu = (rng.standard_normal((M, 2 * K)) * 2).astype(np.float32)
+    want = chk.gemm_w4a16_groupwise(chk.swiglu(gu), p, s, G)
+    got = lb.gemm_w4a16_swiglu(dev(gu), dp, dsc, G)
+    assert_close(host(got), want, what=f"swiglu prologue M={M}")
+    poll_ok()
