@@ -134,6 +134,7 @@ int lhb_gemm_w4a16_groupwise_prologue(lhb_ctx* ctx, const float* X, int prologue
     if (prologue == 1 && !gamma) return LHB_ERR_NULL;
     if (M < 0 || N <= 0 || K <= 0 || G <= 0 || (K % 2) || (K % G)) return LHB_ERR_BAD_SHAPE;
     if (M == 0) return LHB_OK;
+    if (M - ((M - 1) / 16) * 16 <= 2) return LHB_ERR_UNSUPPORTED;   // a last slab of one or two rows has no digit pass
     if (!(w4a16_fast_ok(M, N, K, G) && aligned16(X) && aligned16(Bp) && aligned16(Bs) && aligned16(C) &&
           (prologue != 1 || aligned16(gamma))))
         return LHB_ERR_UNSUPPORTED;       // the caller runs lhb_rmsnorm / lhb_swiglu and the plain GEMM instead

@@ -53,6 +53,27 @@ def test_argument_validation_comes_before_cuda(lib):
     assert lib.lhb_paged_attention_q8_batched(fake, fake, fake, fake, fake, fake, fake, 4, fake, 1, fake,
                                               C.byref(cfg), C.byref(L), None) == _cabi.ERR_BAD_SHAPE
     assert lib.lhb_status_string(_cabi.ERR_TIMEOUT) == b"device-side wait timed out"
+    # the entry points added around the decode step, fp8 and asymmetric int4
+    assert lib.lhb_rmsnorm(fake, fake, fake, fake, 2, 0, 1e-5, None) == _cabi.ERR_BAD_SHAPE
+    assert lib.lhb_rmsnorm(None, fake, fake, fake, 2, 8, 1e-5, None) == _cabi.ERR_NULL
+    assert lib.lhb_rope(fake, fake, 2, 2, 7, 1e4, 1.0, 1, 0, None) == _cabi.ERR_BAD_SHAPE        # odd head_dim
+    assert lib.lhb_rope_decode_batched(fake, fake, None, 2, 2, 8, 1e4, 1.0, 1, None) == _cabi.ERR_NULL
+    assert lib.lhb_swiglu(fake, fake, fake, 2, 0, None) == _cabi.ERR_BAD_SHAPE
+    assert lib.lhb_gemm_w4a16_groupwise_prologue(fake, fake, 3, fake, 1e-5, fake, fake, fake, 4, 16, 128, 128, 1.0, 0.0,
+                                                 None) == _cabi.ERR_BAD_SHAPE                     # unknown prologue
+    assert lib.lhb_gemm_w4a16_groupwise_prologue(fake, fake, 1, None, 1e-5, fake, fake, fake, 4, 16, 128, 128, 1.0, 0.0,
+                                                 None) == _cabi.ERR_NULL                          # rmsnorm needs gamma
+    assert lib.lhb_gemm_w4a16_groupwise_prologue(fake, fake, 2, None, 0.0, fake, fake, fake, 1, 16, 128, 128, 1.0, 0.0,
+                                                 None) == _cabi.ERR_UNSUPPORTED                   # one row: separate calls
+    assert lib.lhb_qkv_rope_append_q8_decode(fake, fake, 10, fake, fake, fake, fake, fake, fake, 4, fake, 1, 2, C.byref(L),
+                                             1e4, 1.0, 0, None) == _cabi.ERR_BAD_SHAPE            # row stride too small
+    assert lib.lhb_fp8_dequantize(fake, fake, fake, fake, 2, 8, 3, None) == _cabi.ERR_BAD_SHAPE   # mode out of range
+    assert lib.lhb_gemm_fp8_e4m3(fake, fake, fake, 1.0, 1.0, fake, 4, 0, 8, 1.0, 0.0, None) == _cabi.ERR_BAD_SHAPE
+    assert lib.lhb_q4a_quantize_groupwise(fake, fake, fake, fake, fake, 7, 4, 7, None) == _cabi.ERR_BAD_SHAPE
+    assert lib.lhb_gemm_w4a16_asym(fake, fake, fake, fake, fake, fake, 1, 16, 32, 12, 1.0, 0.0, None) == _cabi.ERR_BAD_SHAPE
+    assert lib.lhb_gemm_w4a16_asym_fast_path(1, 14336, 4096, 128) == 1 and lib.lhb_gemm_w4a16_asym_fast_path(1, 256, 256, 64) == 0
+    assert lib.lhb_gemm_fp8_fast_path(256, 256, 256) == 1 and lib.lhb_gemm_fp8_fast_path(8, 256, 256) == 0
+    assert lib.lhb_gemm_w4a16_fast_path(512, 14336, 4096, 128) == 1 and lib.lhb_gemm_w4a16_fast_path(2000, 14336, 4096, 128) == 0
 
 
 def test_fast_path_predicates(lib):
