@@ -380,11 +380,36 @@ def bench_decode_step(torch, lb, steps, warmup, hbm_peak, layers=32, batch=32, c
             x.copy_(x0)                  # every replay starts from the same hidden state
             ds.decode_step(x, lw, pools, tables, past, cur, cfg, L, acfg, buf)
     else:
-        buf = ds.TPBuffers.allocate(cfg, world, batch, x.device)
+        # exchanges: this library's push all-gather over peer memory; the NCCL composition is timed
+        # beside it (and is the fallback when the processes cannot map each other's memory)
+        from longhornai_b200 import peer as lpeer
+        nccl_buf = ds.TPBuffers.allocate(cfg, world, batch, x.device)
 
-        def step():
+        def nccl_step():
             x.copy_(x0)
-            ds.decode_step_tp(x, lw, pools, tables, past, cur, cfg, L, acfg, buf, rank, world, dist)
+            ds.decode_step_tp(x, lw, pools, tables, past, cur, cfg, L, acfg, nccl_buf, rank, world, dist)
+        pg, why = None, ""
+        if os.environ.get("LHB_TP_EXCHANGE", "peer") == "peer":
+            try:
+                pg = lpeer.PeerGather(ds.TPBuffers.peer_shapes(cfg, batch), rank, world, dist)
+            except Exception as e:      # noqa: BLE001 - reported in the JSON line
+                why = f"{type(e).__name__}: {e}"[:200]
+            ok = torch.tensor([1 if pg is not None else 0], device="cuda")
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if int(ok.item()) == 0 and pg is not None:
+                pg = None
+                why = "a peer could not map the buffers"
+        if pg is not None:
+            buf = ds.TPBuffers.allocate(cfg, world, batch, x.device, peer=pg)
+            x = buf.x
+
+            def step():
+                x.copy_(x0)
+                ds.decode_step_tp(x, lw, pools, tables, past, cur, cfg, L, acfg, buf, rank, world, dist)
+            run_n, _ = graphed(nccl_step, torch, GRAPHS)
+            nccl_ms = timed(run_n, steps, warmup, dist, torch) / steps
+        else:
+            step, nccl_ms = nccl_step, None
     run, is_graph = graphed(step, torch, GRAPHS)
     ms = timed(run, steps, warmup, dist, torch)
     per = ms / steps * 1e-3
@@ -399,6 +424,14 @@ def bench_decode_step(torch, lb, steps, warmup, hbm_peak, layers=32, batch=32, c
     if world > 1:
         out["sharding"] = (f"projections N/{world}, attention {cfg.n_kv_heads // world} KV heads per rank, "
                            f"4 all-gathers per layer")
+        out["exchange"] = "peer-memory push (own kernel)" if pg is not None else "nccl"
+        if pg is not None:
+            pg.check()                                  # raises if any bounded wait gave up
+            out["ms_per_step_nccl_exchange"] = nccl_ms
+            out["launches_per_step"] += layers * 4
+            pg.close(dist)
+        elif why:
+            out["peer_exchange_unavailable"] = why
     return out
 
 
@@ -673,10 +706,21 @@ def main():
     elif args.only == "decode_step":
         import torch
         import longhornai_b200 as lb
-        torch.cuda.set_device(0)
+        world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+        local = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(local)
+        dist = None
+        if world > 1:                       # under torch.distributed.run: the tensor-parallel step
+            import torch.distributed as dist
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
         layers = int(os.environ.get("LHB_BENCH_LAYERS", "32"))
-        print(json.dumps({"decode_step_cfg4": bench_decode_step(torch, lb, args.steps, args.warmup,
-                                                                 measured_peaks()[0], layers=layers)}), flush=True)
+        res = bench_decode_step(torch, lb, args.steps, args.warmup, measured_peaks()[0], layers=layers,
+                                rank=rank, world=world, dist=dist)
+        if rank == 0:
+            print(json.dumps({"decode_step_cfg4": res}), flush=True)
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
     elif args.impl == "reference":
         run_reference(args)
     else:

@@ -378,6 +378,39 @@ LHB_API int32_t* lhb_sched_block_tables(lhb_scheduler* s);
 LHB_API int32_t* lhb_sched_seq_lens(lhb_scheduler* s);
 LHB_API int lhb_sched_max_blocks_per_req(const lhb_scheduler* s);
 
+/* ---- exchange step of a tensor-parallel decode layer over NVLink peer memory ------- */
+
+/* No reference interface stands behind these: the reference runs one model on one device
+ * (src/runtime/scheduler.hpp:47).  They exist so that N processes, one per GPU, can run the decode
+ * step with the projections sharded along N without a library collective between the GEMMs.
+ *
+ * lhb_peer_alloc returns zero-filled device memory that other processes on the same machine can map:
+ * lhb_peer_export writes its 64-byte handle (send it to the peers by any means), lhb_peer_open maps a
+ * peer's handle into this process with peer access enabled, lhb_peer_close / lhb_peer_free undo them
+ * (close every mapping of a buffer before its owner frees it).
+ *
+ * lhb_peer_allgather_cols: this rank holds `local` [rows, width] fp32, columns
+ * [rank*width, (rank+1)*width) of a row-major [rows, world*width] matrix that every rank needs.  One
+ * launch stores the slab into its place in every rank's copy (dst_table[p] = base of rank p's copy as
+ * mapped in this process, this rank's own pointer at p == rank; a DEVICE array of `world` pointers),
+ * adds to rank p's arrival counters (flag_table[p] = rank p's uint32[world], peer-visible, zero at
+ * start; a device array of `world` pointers) and returns once all ranks' slabs have arrived here.
+ * `state` is this rank's own uint32[4], zero at start.  Rules: every rank issues the same sequence of
+ * calls with the same shapes; width % 4 == 0 and 16-byte aligned buffers; consecutive calls target
+ * different destination matrices, and a destination is not read between the call before it and the
+ * call that fills it.  The wait is bounded by timeout_ms: after that the kernel records the silent
+ * rank in `state` and returns; lhb_peer_status (synchronises `stream`) then gives LHB_ERR_TIMEOUT
+ * and the data is not valid.  The launch can be captured in a CUDA graph. */
+LHB_API int lhb_peer_alloc(void** out, size_t bytes);
+LHB_API int lhb_peer_free(void* ptr);
+LHB_API int lhb_peer_export(void* ptr, unsigned char* handle64);
+LHB_API int lhb_peer_open(const unsigned char* handle64, void** out);
+LHB_API int lhb_peer_close(void* mapped);
+LHB_API int lhb_peer_allgather_cols(const float* local, int rows, int width, void* const* dst_table,
+                                    uint32_t* const* flag_table, uint32_t* state, int rank, int world,
+                                    int timeout_ms, void* stream);
+LHB_API int lhb_peer_status(const uint32_t* state, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -112,6 +112,13 @@ SIGNATURES = {
     "lhb_sched_block_tables": (_vp, [_vp]),
     "lhb_sched_seq_lens": (_vp, [_vp]),
     "lhb_sched_max_blocks_per_req": (_i, [_vp]),
+    "lhb_peer_alloc": (_i, [C.POINTER(_vp), C.c_size_t]),
+    "lhb_peer_free": (_i, [_vp]),
+    "lhb_peer_export": (_i, [_vp, _vp]),
+    "lhb_peer_open": (_i, [_vp, C.POINTER(_vp)]),
+    "lhb_peer_close": (_i, [_vp]),
+    "lhb_peer_allgather_cols": (_i, [_vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "lhb_peer_status": (_i, [_vp, _vp]),
 }
 
 _lib = None

@@ -109,7 +109,10 @@ int lhb_gemm_w4a16_groupwise(lhb_ctx* ctx, const float* A, const uint8_t* Bp, co
     if ((K & 1) || (K % G) != 0) return LHB_ERR_BAD_SHAPE;
     if (M == 0) return LHB_OK;
     cudaStream_t st = as_stream(stream);
-    if (w4a16_fast_ok(M, N, K, G) && aligned16(A) && aligned16(Bp) && aligned16(Bs) && aligned16(C))
+    const bool al = aligned16(A) && aligned16(Bp) && aligned16(Bs) && aligned16(C);
+    if (al && M >= w4a16_tc_min_rows() && w4a16_tc_ok(M, N, K, G))
+        return launch_w4a16_tc(ctx, A, Bp, Bs, C, M, N, K, G, alpha, beta, st, 0, nullptr, 0.0f);
+    if (w4a16_fast_ok(M, N, K, G) && al)
         return launch_w4a16_fast(ctx, A, Bp, Bs, C, M, N, K, G, alpha, beta, st);
     return launch_w4a16_generic(A, Bp, Bs, C, M, N, K, G, alpha, beta, st);
 }
@@ -134,6 +137,9 @@ int lhb_gemm_w4a16_groupwise_prologue(lhb_ctx* ctx, const float* X, int prologue
     if (prologue == 1 && !gamma) return LHB_ERR_NULL;
     if (M < 0 || N <= 0 || K <= 0 || G <= 0 || (K % 2) || (K % G)) return LHB_ERR_BAD_SHAPE;
     if (M == 0) return LHB_OK;
+    if (M >= w4a16_tc_min_rows() && w4a16_tc_ok(M, N, K, G) && aligned16(X) && aligned16(Bp) && aligned16(Bs) &&
+        aligned16(C) && (prologue != 1 || aligned16(gamma)))
+        return launch_w4a16_tc(ctx, X, Bp, Bs, C, M, N, K, G, alpha, beta, as_stream(stream), prologue, gamma, eps);
     if (M - ((M - 1) / 16) * 16 <= 2) return LHB_ERR_UNSUPPORTED;   // a last slab of one or two rows has no digit pass
     if (!(w4a16_fast_ok(M, N, K, G) && aligned16(X) && aligned16(Bp) && aligned16(Bs) && aligned16(C) &&
           (prologue != 1 || aligned16(gamma))))

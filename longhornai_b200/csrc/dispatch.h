@@ -43,6 +43,13 @@ int launch_decode_fast(lhb_ctx* ctx, const float* Q, const int8_t* Kp, const int
                        const lhb_paged_layout& L, cudaStream_t st);
 
 // W4A16 with a prologue on the activations (1 = RMSNorm with gamma/eps, 2 = SwiGLU of [gate || value] rows)
+// tensor-core W4A16 for a few rows up to a few hundred (gemm_w4a16_tc.cu); prologue 0 = none,
+// 1 = RMSNorm (gamma, eps), 2 = SwiGLU of [gate || value] rows.  w4a16_tc_min_rows: the row count
+// from which it is preferred over the GEMV kernel (environment LHB_W4TC_MIN_M overrides).
+bool w4a16_tc_ok(int M, int N, int K, int G);
+int w4a16_tc_min_rows();
+int launch_w4a16_tc(lhb_ctx* ctx, const float* A, const uint8_t* Bp, const float* Bs, float* C, int M, int N, int K,
+                    int G, float alpha, float beta, cudaStream_t st, int prologue, const float* gamma, float eps);
 int launch_w4a16_fast_prologue(lhb_ctx* ctx, const float* X, int prologue, const float* gamma, float eps,
                                const uint8_t* Bp, const float* Bs, float* C, int M, int N, int K, int G, float alpha,
                                float beta, cudaStream_t st);

@@ -190,8 +190,11 @@ def local_config(cfg: StepConfig, world: int) -> StepConfig:
 
 @dataclass
 class TPBuffers:
-    """Per-rank activations of the sharded step.  `x` is the replicated residual stream, `xs` this
-    rank's column slab of it; `g_*` receive all-gathers in rank-major layout [world, n_req, n/world]."""
+    """Per-rank activations of the sharded step.  `xs` is this rank's column slab of the replicated
+    residual stream.  With `peer` (a peer.PeerGather) the full-width matrices live in peer-visible
+    memory, `x` is the residual stream the caller must use, and the exchanges are this library's
+    push all-gather; without it `g_*` receive library all-gathers in rank-major layout
+    [world, n_req, n/world] and a strided copy lays them out."""
     local: StepBuffers
     xs: torch.Tensor
     o_full: torch.Tensor
@@ -199,12 +202,23 @@ class TPBuffers:
     g_o: torch.Tensor
     g_x: torch.Tensor
     g_act: torch.Tensor
+    peer: object = None
+    x: torch.Tensor = None
 
     @staticmethod
-    def allocate(cfg: StepConfig, world: int, n_req: int, device) -> "TPBuffers":
+    def peer_shapes(cfg: StepConfig, n_req: int) -> dict:
+        """The matrices a peer.PeerGather must hold for this step."""
+        return {"o": (n_req, cfg.q_dim), "x": (n_req, cfg.dim), "act": (n_req, cfg.ffn)}
+
+    @staticmethod
+    def allocate(cfg: StepConfig, world: int, n_req: int, device, peer=None) -> "TPBuffers":
         lc = local_config(cfg, world)
         f = lambda *shape: torch.empty(shape, dtype=torch.float32, device=device)
-        return TPBuffers(StepBuffers.allocate(lc, n_req, device), f(n_req, cfg.dim // world), f(n_req, cfg.q_dim),
+        local = StepBuffers.allocate(lc, n_req, device)
+        if peer is not None:
+            return TPBuffers(local, f(n_req, cfg.dim // world), peer.tensor("o"), peer.tensor("act"), None, None, None,
+                             peer, peer.tensor("x"))
+        return TPBuffers(local, f(n_req, cfg.dim // world), f(n_req, cfg.q_dim),
                          f(n_req, cfg.ffn), f(world, n_req, cfg.q_dim // world), f(world, n_req, cfg.dim // world),
                          f(world, n_req, cfg.ffn // world))
 
@@ -224,15 +238,22 @@ def _gather_rows(dst_full, gathered, local, dist):
 
 
 def decode_layer_tp(x, w: LayerWeights, pools: KVPools, block_tables, past_lens, cur_lens, cfg: StepConfig,
-                    L: PagedLayout, acfg: PagedAttnCfg, buf: TPBuffers, rank: int, world: int, dist, ctx=None, ops=K):
+                    L: PagedLayout, acfg: PagedAttnCfg, buf: TPBuffers, rank: int, world: int, dist, ctx=None, ops=K,
+                    xs_in_sync: bool = False):
     """One layer on rank `rank` of `world`.  `w` is shard_layer(...), `pools`/`L`/`acfg` describe this rank's
     KV heads, `x` [n_req, dim] is replicated and updated in place.  Exchanges: all-gathers of the attention
-    output, of the SwiGLU output and (twice) of the residual slabs; nothing else crosses ranks."""
+    output, of the SwiGLU output and (twice) of the residual slabs; nothing else crosses ranks.  After a layer
+    `buf.xs` equals this rank's slab of `x`; `xs_in_sync` says that it already does on entry."""
     lc = local_config(cfg, world)
     b = buf.local
     n_req = x.shape[0]
     G = cfg.group
     lo = rank * (cfg.dim // world)
+    if buf.peer is not None:
+        assert x.data_ptr() == buf.x.data_ptr(), "with peer buffers the residual stream is buf.x"
+        gather = lambda dst, g, local, name: buf.peer.gather(local, name)
+    else:
+        gather = lambda dst, g, local, name: _gather_rows(dst, g, local, dist)
     ops.gemm_w4a16_norm(x, w.g_attn, cfg.eps, *w.wqkv, G, C=b.qkv, scratch=b.h, ctx=ctx)
     ops.qkv_rope_append_q8_decode(b.qkv, b.q.view(n_req, lc.n_q_heads, lc.head_dim), pools.k, pools.v, pools.ks,
                                   pools.vs, block_tables, past_lens, lc.n_q_heads, L, cfg.rope_theta, 1.0,
@@ -240,21 +261,22 @@ def decode_layer_tp(x, w: LayerWeights, pools: KVPools, block_tables, past_lens,
     ops.paged_attention_q8_batched(b.q.view(n_req, lc.n_q_heads, 1, lc.head_dim), pools.k, pools.v, pools.ks,
                                  pools.vs, block_tables, cur_lens, acfg, L,
                                  O=b.o.view(n_req, lc.n_q_heads, 1, lc.head_dim), ctx=ctx)
-    _gather_rows(buf.o_full, buf.g_o, b.o, dist)
-    buf.xs.copy_(x[:, lo:lo + cfg.dim // world])
+    gather(buf.o_full, buf.g_o, b.o, "o")
+    if not xs_in_sync:
+        buf.xs.copy_(x[:, lo:lo + cfg.dim // world])
     ops.gemm_w4a16_groupwise(buf.o_full, *w.wo, G, C=buf.xs, alpha=1.0, beta=1.0, ctx=ctx)
-    _gather_rows(x, buf.g_x, buf.xs, dist)
+    gather(x, buf.g_x, buf.xs, "x")
     ops.gemm_w4a16_norm(x, w.g_ffn, cfg.eps, *w.wgu, G, C=b.gu, scratch=b.h, ctx=ctx)
     ops.swiglu(b.gu, out=b.act, ctx=ctx)        # its output is what the ranks exchange
-    _gather_rows(buf.act_full, buf.g_act, b.act, dist)
+    gather(buf.act_full, buf.g_act, b.act, "act")
     ops.gemm_w4a16_groupwise(buf.act_full, *w.wdown, G, C=buf.xs, alpha=1.0, beta=1.0, ctx=ctx)
-    _gather_rows(x, buf.g_x, buf.xs, dist)
+    gather(x, buf.g_x, buf.xs, "x")
     return x
 
 
 def decode_step_tp(x, layers, pools, block_tables, past_lens, cur_lens, cfg: StepConfig, L: PagedLayout,
                    acfg: PagedAttnCfg, buf: TPBuffers, rank: int, world: int, dist, ctx=None, ops=K):
-    for w, kv in zip(layers, pools):
+    for i, (w, kv) in enumerate(zip(layers, pools)):
         decode_layer_tp(x, w, kv, block_tables, past_lens, cur_lens, cfg, L, acfg, buf, rank, world, dist,
-                        ctx=ctx, ops=ops)
+                        ctx=ctx, ops=ops, xs_in_sync=i > 0)
     return x
