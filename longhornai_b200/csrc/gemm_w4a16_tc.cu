@@ -222,6 +222,52 @@ __device__ __forceinline__ float tc_int_to_float(uint32_t v) {
     return __uint_as_float(v + 0x4B400000u) - 12582912.0f;
 }
 
+// The last contributor to a column tile adds the partial sums up and writes C.  The 256 epilogue
+// threads share the [M][256] outputs as float4s, whatever columns they held before: each takes up to
+// four of them at a time, reads one contributor's four float4s together (one round trip per contributor) and
+// adds in contributor order.
+__device__ __forceinline__ void tc_sum_partials(const W4TcParams& p, const float* tile_slots, int tile_col0,
+                                                int n_contrib, int et) {
+    const int n_out = p.M * (TC_COLS / 4);
+    for (int e0 = et; e0 < n_out; e0 += 4 * 256) {
+        float4 sum[4];
+#pragma unroll
+        for (int x = 0; x < 4; ++x) sum[x] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j = 0; j < n_contrib; ++j) {
+            const float* slot = tile_slots + static_cast<int64_t>(j) * p.M * TC_COLS;
+            float4 v[4];
+#pragma unroll
+            for (int x = 0; x < 4; ++x)           // clamped, unconditional: the loads overlap
+                v[x] = __ldcg(reinterpret_cast<const float4*>(slot) + min(e0 + 256 * x, n_out - 1));
+#pragma unroll
+            for (int x = 0; x < 4; ++x) { sum[x].x += v[x].x; sum[x].y += v[x].y; sum[x].z += v[x].z; sum[x].w += v[x].w; }
+        }
+        float4 old[4];
+        if (p.beta != 0.0f) {
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+                const int e = min(e0 + 256 * x, n_out - 1), m = e >> 6, c = (e & 63) * 4;
+                old[x] = (tile_col0 + c < p.N) ? *reinterpret_cast<const float4*>(p.C + m * p.N + tile_col0 + c)
+                                               : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+            const int e = e0 + 256 * x, m = e >> 6, c = (e & 63) * 4;
+            if (e < n_out && tile_col0 + c < p.N) {       // N % 16 == 0: whole float4 in range
+                float4 r;
+                if (p.beta == 0.0f) {
+                    r = make_float4(p.alpha * sum[x].x, p.alpha * sum[x].y, p.alpha * sum[x].z, p.alpha * sum[x].w);
+                } else {
+                    r.x = fmaf(p.beta, old[x].x, p.alpha * sum[x].x); r.y = fmaf(p.beta, old[x].y, p.alpha * sum[x].y);
+                    r.z = fmaf(p.beta, old[x].z, p.alpha * sum[x].z); r.w = fmaf(p.beta, old[x].w, p.alpha * sum[x].w);
+                }
+                *reinterpret_cast<float4*>(p.C + m * p.N + tile_col0 + c) = r;
+            }
+        }
+    }
+}
+
 __device__ __forceinline__ void tc_epi_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 template <int MP>
@@ -549,51 +595,7 @@ gemm_w4a16_tc_kernel(const __grid_constant__ TensorMap tmW, const __grid_constan
                     *epi_flag = last;
                 }
                 tc_epi_sync();
-                if (*epi_flag) {
-                    // The 256 epilogue threads share the [M][256] outputs as float4s, whatever column they
-                    // held before: each takes up to eight of them, reads one contributor's eight float4s
-                    // together (one round trip per contributor) and adds in contributor order.
-                    const float* tile_slots = p.partial + (static_cast<int64_t>(tile) * p.max_contrib) * p.M * TC_COLS;
-                    const int tile_col0 = tile * TC_COLS;
-                    const int n_out = p.M * (TC_COLS / 4);
-                    for (int e0 = et; e0 < n_out; e0 += 8 * 256) {
-                        float4 sum[8];
-#pragma unroll
-                        for (int x = 0; x < 8; ++x) sum[x] = make_float4(0.f, 0.f, 0.f, 0.f);
-                        for (int j = 0; j < n_contrib; ++j) {
-                            const float* slot = tile_slots + static_cast<int64_t>(j) * p.M * TC_COLS;
-                            float4 v[8];
-#pragma unroll
-                            for (int x = 0; x < 8; ++x)           // clamped, unconditional: the loads overlap
-                                v[x] = __ldcg(reinterpret_cast<const float4*>(slot) + min(e0 + 256 * x, n_out - 1));
-#pragma unroll
-                            for (int x = 0; x < 8; ++x) { sum[x].x += v[x].x; sum[x].y += v[x].y; sum[x].z += v[x].z; sum[x].w += v[x].w; }
-                        }
-                        float4 old[8];
-                        if (p.beta != 0.0f) {
-#pragma unroll
-                            for (int x = 0; x < 8; ++x) {
-                                const int e = min(e0 + 256 * x, n_out - 1), m = e >> 6, c = (e & 63) * 4;
-                                old[x] = (tile_col0 + c < p.N) ? *reinterpret_cast<const float4*>(p.C + m * p.N + tile_col0 + c)
-                                                               : make_float4(0.f, 0.f, 0.f, 0.f);
-                            }
-                        }
-#pragma unroll
-                        for (int x = 0; x < 8; ++x) {
-                            const int e = e0 + 256 * x, m = e >> 6, c = (e & 63) * 4;
-                            if (e < n_out && tile_col0 + c < p.N) {       // N % 16 == 0: whole float4 in range
-                                float4 r;
-                                if (p.beta == 0.0f) {
-                                    r = make_float4(p.alpha * sum[x].x, p.alpha * sum[x].y, p.alpha * sum[x].z, p.alpha * sum[x].w);
-                                } else {
-                                    r.x = fmaf(p.beta, old[x].x, p.alpha * sum[x].x); r.y = fmaf(p.beta, old[x].y, p.alpha * sum[x].y);
-                                    r.z = fmaf(p.beta, old[x].z, p.alpha * sum[x].z); r.w = fmaf(p.beta, old[x].w, p.alpha * sum[x].w);
-                                }
-                                *reinterpret_cast<float4*>(p.C + m * p.N + tile_col0 + c) = r;
-                            }
-                        }
-                    }
-                }
+                if (*epi_flag) tc_sum_partials(p, p.partial + (static_cast<int64_t>(tile) * p.max_contrib) * p.M * TC_COLS, tile * TC_COLS, n_contrib, et);
                 tc_epi_sync();                               // epi_flag is free again
             }
             if (et == 0) TC_STAMP(3, 3);
@@ -611,12 +613,13 @@ gemm_w4a16_tc_kernel(const __grid_constant__ TensorMap tmW, const __grid_constan
 
 // ---- host side --------------------------------------------------------------------------
 
-static int tc_slab_rows(int M) { return M <= 16 ? 16 : 32; }
+static int tc_slab_rows(int M) { return M > 16 ? 32 : 16; }
+static int tc_digit_rows(int mp) { return 3 * mp; }      // digit rows per slab
 
 bool w4a16_tc_ok(int M, int N, int K, int G) {
     if (M < 1 || M > 1024 || N < 16 || (N % 16) != 0 || G < 128 || (G % 128) != 0 || K < G || (K % G) != 0) return false;
     // the digits of one slab must fit the head of the scratch arena
-    return static_cast<size_t>(3 * tc_slab_rows(M)) * K <= TC_DIG_BYTES;
+    return static_cast<size_t>(tc_digit_rows(tc_slab_rows(M))) * K <= TC_DIG_BYTES;
 }
 
 int w4a16_tc_min_rows() {
@@ -656,8 +659,9 @@ int launch_w4a16_tc(lhb_ctx* ctx, const float* A, const uint8_t* Bp, const float
     if (ctx->scratch_bytes < TC_SCRATCH_HEAD) return LHB_ERR_SCRATCH;
     TensorMap tmW;
     if (int e = get_tensor_map_2d_u8(ctx, Bp, K / 2, N, N, TC_ROWS, TC_COLS, false, &tmW)) return e;
-    const int mp = tc_slab_rows(M);                         // rows per slab; digit rows per slab = 3 * mp
-    const size_t slab_bytes = static_cast<size_t>(3 * mp) * K;
+    const int mp = tc_slab_rows(M);                         // rows per slab
+    const int drows = tc_digit_rows(mp);                    // digit rows per slab
+    const size_t slab_bytes = static_cast<size_t>(drows) * K;
     const int slabs_per_pass = std::max<int>(1, std::min<size_t>(1024 / mp, TC_DIG_BYTES / slab_bytes));
     const int rows_per_pass = slabs_per_pass * mp;
     uint8_t* const dig = static_cast<uint8_t*>(ctx->scratch);
@@ -695,7 +699,7 @@ int launch_w4a16_tc(lhb_ctx* ctx, const float* A, const uint8_t* Bp, const float
         for (int sl = 0; sl < pass_slabs; ++sl) {
             const int m0 = pass0 + sl * mp, m = std::min(mp, M - m0);
             TensorMap tmD;
-            if (int e = get_tensor_map_2d_u8(ctx, dig, static_cast<uint64_t>(pass_slabs) * 3 * mp, K, K, 3 * mp, 128,
+            if (int e = get_tensor_map_2d_u8(ctx, dig, static_cast<uint64_t>(pass_slabs) * drows, K, K, drows, 128,
                                              true, &tmD))
                 return e;
             if (static_cast<size_t>(col_tiles) * max_contrib * m * TC_COLS * sizeof(float) >
@@ -712,9 +716,9 @@ int launch_w4a16_tc(lhb_ctx* ctx, const float* A, const uint8_t* Bp, const float
             p.counters = ctx->counters;
             p.status = ctx->status_word;
             p.inv_scale = inv + (m0 - pass0);
-            p.dig_row0 = sl * 3 * mp;
+            p.dig_row0 = sl * drows;
             const int e = mp == 16 ? launch_tc_slab<16>(ctx, tmW, tmD, p, ctas, st)
-                                    : launch_tc_slab<32>(ctx, tmW, tmD, p, ctas, st);
+                                   : launch_tc_slab<32>(ctx, tmW, tmD, p, ctas, st);
             if (e) return e;
         }
     }
