@@ -145,11 +145,14 @@ def decode_step(x, layers, pools, block_tables, past_lens, cur_lens, cfg: StepCo
     return x
 
 
-def launches_per_layer(n_req: int) -> int:
+def launches_per_layer(n_req: int, tc_min_rows: int = 17) -> int:
     """Kernel launches in one layer (for the bench's launch count): the fused split + rotation +
-    append, attention, and 4 GEMMs each served in slabs of 16 rows plus one digit pass (which also
-    applies RMSNorm / SwiGLU) when there are more than two rows; with one or two rows the two norms
-    and SwiGLU are launches of their own."""
+    append, attention, and 4 GEMMs.  From `tc_min_rows` rows on a GEMM is one digit pass (which also
+    applies RMSNorm / SwiGLU) plus one tensor-core launch per slab of 32 rows; below that it is served
+    in slabs of 16 rows plus one digit pass when there are more than two rows, and with one or two
+    rows the two norms and SwiGLU are launches of their own."""
+    if n_req >= tc_min_rows:
+        return 2 + 4 * (1 + (n_req + 31) // 32)
     slabs = (n_req + 15) // 16
     last = n_req - (slabs - 1) * 16
     if last <= 2:

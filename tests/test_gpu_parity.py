@@ -214,6 +214,51 @@ def test_w4a16_many_rows_in_slabs(chk, lib, M, N, K, G):
     poll_ok()
 
 
+@pytest.mark.parametrize("M,N,K,G", [
+    (17, 1040, 128, 128),       # one unit per column tile, ragged last tile: every segment whole
+    (32, 256, 4096, 128),       # one column tile shared by 32 CTAs: 32 partial slots summed
+    (33, 4096, 4096, 256),      # group of two units; second slab holds one row
+    (40, 16 * 37, 1024, 128),   # ragged N below three tiles, short second slab
+    (64, 6144, 4096, 128),      # two full slabs, whole number of CTAs per tile
+    (100, 28672, 512, 128),     # more tiles than three quarters of the SMs: one CTA per tile... or an even deal
+    (1024, 512, 256, 128),      # the row limit: 32 slabs over one digit pass
+])
+def test_w4a16_tensor_core_kernel_shapes(chk, M, N, K, G):
+    """From 17 rows on gemm_w4a16_groupwise runs on the tensor cores (int8 digits x int8 weights,
+    exact int32 sums per group, fp32 fold).  Shapes for each way its work is split, with
+    alpha / beta, against the checker, twice for run-to-run determinism."""
+    rng = np.random.default_rng(3 * M + N + K + G)
+    A = (rng.standard_normal((M, K)) * rng.choice([1e-2, 1.0, 50.0], size=(M, 1))).astype(np.float32)
+    W = (rng.standard_normal((K, N)) * 0.02).astype(np.float32)
+    p, s = chk.q4_quantize_groupwise(W, G)
+    C0 = rng.standard_normal((M, N)).astype(np.float32)
+    dA, dp, ds = dev(A), dev(p), dev(s)
+    got = lb.gemm_w4a16_groupwise(dA, dp, ds, G, C=dev(C0), alpha=0.5, beta=2.0)
+    want = chk.gemm_w4a16_groupwise(A, p, s, G, C0, alpha=0.5, beta=2.0)
+    scale = np.maximum(1.0, np.abs(A).max(axis=1, keepdims=True))     # the absolute term is stated for unit rows
+    assert_close(host(got) / scale, want / scale, what=f"tensor-core w4a16 {M}x{N}x{K} G={G}")
+    got2 = lb.gemm_w4a16_groupwise(dA, dp, ds, G, C=dev(C0), alpha=0.5, beta=2.0)
+    assert torch.equal(got, got2)
+    poll_ok()
+
+
+def test_w4a16_tensor_core_kernel_is_exact_on_integers():
+    """Small integer activations and unit scales: every product and sum is an integer below 2^22 that
+    the kernel carries exactly, so the result equals integer arithmetic bit for bit (no tolerance)."""
+    M, N, K, G = 32, 512, 512, 128
+    rng = np.random.default_rng(77)
+    q = rng.integers(-8, 8, size=(K, N)).astype(np.int64)
+    a = rng.integers(-1000, 1001, size=(M, K)).astype(np.int64)
+    a[:, 0] = 1024                                      # every row's factor is then the same power of two
+    packed = ((q[0::2] & 15) | ((q[1::2] & 15) << 4)).astype(np.uint8)
+    scales = np.ones((K // G, N), np.float32)
+    got = host(lb.gemm_w4a16_groupwise(dev(a.astype(np.float32)), dev(packed), dev(scales), G))
+    want = (a @ q).astype(np.float64)
+    assert np.abs(want).max() < 2 ** 22
+    np.testing.assert_array_equal(got.astype(np.float64), want.astype(np.float32).astype(np.float64))
+    poll_ok()
+
+
 def test_w4a16_linearity_and_determinism():
     K, N, G = 2048, 2048, 128
     g = torch.Generator(device="cuda").manual_seed(5)
