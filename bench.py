@@ -428,7 +428,7 @@ def bench_decode_step(torch, lb, steps, warmup, hbm_peak, layers=32, batch=32, c
         if pg is not None:
             pg.check()                                  # raises if any bounded wait gave up
             out["ms_per_step_nccl_exchange"] = nccl_ms
-            out["launches_per_step"] += layers * 4
+            out["launches_per_step"] += layers * 5 + 1        # four exchanges and a separate SwiGLU per layer, one slab copy
             pg.close(dist)
         elif why:
             out["peer_exchange_unavailable"] = why
