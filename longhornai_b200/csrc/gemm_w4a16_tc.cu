@@ -224,8 +224,7 @@ __device__ __forceinline__ float tc_int_to_float(uint32_t v) {
 
 // The last contributor to a column tile adds the partial sums up and writes C.  The 256 epilogue
 // threads share the [M][256] outputs as float4s, whatever columns they held before: each takes up to
-// four of them at a time, reads one contributor's four float4s together (one round trip per contributor) and
-// adds in contributor order.
+// four of them at a time and adds the contributors' float4s in contributor order.
 __device__ __forceinline__ void tc_sum_partials(const W4TcParams& p, const float* tile_slots, int tile_col0,
                                                 int n_contrib, int et) {
     const int n_out = p.M * (TC_COLS / 4);
@@ -233,14 +232,25 @@ __device__ __forceinline__ void tc_sum_partials(const W4TcParams& p, const float
         float4 sum[4];
 #pragma unroll
         for (int x = 0; x < 4; ++x) sum[x] = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int j = 0; j < n_contrib; ++j) {
-            const float* slot = tile_slots + static_cast<int64_t>(j) * p.M * TC_COLS;
-            float4 v[4];
+        // three contributors' loads in flight per round trip, added in contributor order
+        for (int j = 0; j < n_contrib; j += 3) {
+            float4 v[3][4];
 #pragma unroll
-            for (int x = 0; x < 4; ++x)           // clamped, unconditional: the loads overlap
-                v[x] = __ldcg(reinterpret_cast<const float4*>(slot) + min(e0 + 256 * x, n_out - 1));
+            for (int y = 0; y < 3; ++y) {
+                const float* slot = tile_slots + static_cast<int64_t>(min(j + y, n_contrib - 1)) * p.M * TC_COLS;
 #pragma unroll
-            for (int x = 0; x < 4; ++x) { sum[x].x += v[x].x; sum[x].y += v[x].y; sum[x].z += v[x].z; sum[x].w += v[x].w; }
+                for (int x = 0; x < 4; ++x)       // clamped, unconditional: the loads overlap
+                    v[y][x] = __ldcg(reinterpret_cast<const float4*>(slot) + min(e0 + 256 * x, n_out - 1));
+            }
+#pragma unroll
+            for (int y = 0; y < 3; ++y) {
+                if (j + y < n_contrib) {
+#pragma unroll
+                    for (int x = 0; x < 4; ++x) {
+                        sum[x].x += v[y][x].x; sum[x].y += v[y][x].y; sum[x].z += v[y][x].z; sum[x].w += v[y][x].w;
+                    }
+                }
+            }
         }
         float4 old[4];
         if (p.beta != 0.0f) {
