@@ -627,7 +627,7 @@ static int tc_slab_rows(int M) { return M > 16 ? 32 : 16; }
 static int tc_digit_rows(int mp) { return 3 * mp; }      // digit rows per slab
 
 bool w4a16_tc_ok(int M, int N, int K, int G) {
-    if (M < 1 || M > 1024 || N < 16 || (N % 16) != 0 || G < 128 || (G % 128) != 0 || K < G || (K % G) != 0) return false;
+    if (M < 1 || M > 65536 || N < 16 || (N % 16) != 0 || G < 128 || (G % 128) != 0 || K < G || (K % G) != 0) return false;
     // the digits of one slab must fit the head of the scratch arena
     return static_cast<size_t>(tc_digit_rows(tc_slab_rows(M))) * K <= TC_DIG_BYTES;
 }

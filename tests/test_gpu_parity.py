@@ -221,7 +221,8 @@ def test_w4a16_many_rows_in_slabs(chk, lib, M, N, K, G):
     (40, 16 * 37, 1024, 128),   # ragged N below three tiles, short second slab
     (64, 6144, 4096, 128),      # two full slabs, whole number of CTAs per tile
     (100, 28672, 512, 128),     # more tiles than three quarters of the SMs: one CTA per tile... or an even deal
-    (1024, 512, 256, 128),      # the row limit: 32 slabs over one digit pass
+    (1024, 512, 256, 128),      # 32 slabs over one digit pass
+    (2100, 256, 384, 128),      # three digit passes of up to 1024 rows, short last slab
 ])
 def test_w4a16_tensor_core_kernel_shapes(chk, M, N, K, G):
     """From 17 rows on gemm_w4a16_groupwise runs on the tensor cores (int8 digits x int8 weights,
