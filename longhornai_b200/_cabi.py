@@ -119,6 +119,8 @@ SIGNATURES = {
     "lhb_peer_close": (_i, [_vp]),
     "lhb_peer_allgather_cols": (_i, [_vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "lhb_peer_status": (_i, [_vp, _vp]),
+    "lhb_gemm_w4a16_groupwise_peer": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, C.c_float, C.c_float, _vp, _vp, _vp,
+                                           _i, _i, _i, _vp]),
 }
 
 _lib = None

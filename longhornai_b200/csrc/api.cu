@@ -117,6 +117,25 @@ int lhb_gemm_w4a16_groupwise(lhb_ctx* ctx, const float* A, const uint8_t* Bp, co
     return launch_w4a16_generic(A, Bp, Bs, C, M, N, K, G, alpha, beta, st);
 }
 
+int lhb_gemm_w4a16_groupwise_peer(lhb_ctx* ctx, const float* A, const uint8_t* Bp, const float* Bs, float* C, int M,
+                                  int N, int K, int G, float alpha, float beta, void* const* dst_table,
+                                  uint32_t* const* flag_table, uint32_t* state, int rank, int world, int timeout_ms,
+                                  void* stream) {
+    if (!ctx || !A || !Bp || !Bs || !C || !dst_table || !flag_table || !state) return LHB_ERR_NULL;
+    if (M <= 0 || N <= 0 || K <= 0 || G <= 0 || (K & 1) || (K % G) != 0) return LHB_ERR_BAD_SHAPE;
+    if (world < 1 || world > 64 || rank < 0 || rank >= world || timeout_ms <= 0) return LHB_ERR_BAD_SHAPE;
+    if (static_cast<int64_t>(M) * N * world >= (int64_t(1) << 31)) return LHB_ERR_BAD_SHAPE;
+    // only the tensor-core kernel pushes its results itself; other shapes: plain GEMM + lhb_peer_allgather_cols
+    if (!(M >= w4a16_tc_min_rows() && w4a16_tc_ok(M, N, K, G) && aligned16(A) && aligned16(Bp) && aligned16(Bs) &&
+          aligned16(C)))
+        return LHB_ERR_UNSUPPORTED;
+    cudaStream_t st = as_stream(stream);
+    const W4Peer peer{dst_table, flag_table, world, rank, N * world, rank * N};
+    uint32_t arrivals = 0;
+    if (int e = launch_w4a16_tc(ctx, A, Bp, Bs, C, M, N, K, G, alpha, beta, st, 0, nullptr, 0.0f, &peer, &arrivals)) return e;
+    return launch_peer_wait(flag_table, state, rank, world, arrivals, timeout_ms, st);
+}
+
 int lhb_gemm_w8a16_perchannel(lhb_ctx* ctx, const float* A, const int8_t* Bq, const float* Bs,
                               float* C, int M, int N, int K, float alpha, float beta,
                               void* stream) {

@@ -48,8 +48,19 @@ int launch_decode_fast(lhb_ctx* ctx, const float* Q, const int8_t* Kp, const int
 // from which it is preferred over the GEMV kernel (environment LHB_W4TC_MIN_M overrides).
 bool w4a16_tc_ok(int M, int N, int K, int G);
 int w4a16_tc_min_rows();
+// `peer` (optional): the result also goes to columns [col0, col0 + N) of every rank's [M, ld] matrix and each
+// completed column tile of each slab adds one arrival at every rank; *arrivals_out = arrivals per rank.
+struct W4Peer {
+    void* const* dst_table;          // device array of `world` matrix bases as mapped in this process
+    uint32_t* const* flag_table;     // device array of `world` arrival-counter arrays
+    int world, rank, ld, col0;
+};
 int launch_w4a16_tc(lhb_ctx* ctx, const float* A, const uint8_t* Bp, const float* Bs, float* C, int M, int N, int K,
-                    int G, float alpha, float beta, cudaStream_t st, int prologue, const float* gamma, float eps);
+                    int G, float alpha, float beta, cudaStream_t st, int prologue, const float* gamma, float eps,
+                    const W4Peer* peer = nullptr, uint32_t* arrivals_out = nullptr);
+// waits (bounded) until every rank's counter in this rank's arrival array has grown by `add` (peer_gather.cu)
+int launch_peer_wait(uint32_t* const* flag_table, uint32_t* state, int rank, int world, uint32_t add,
+                     int timeout_ms, cudaStream_t st);
 int launch_w4a16_fast_prologue(lhb_ctx* ctx, const float* X, int prologue, const float* gamma, float eps,
                                const uint8_t* Bp, const float* Bs, float* C, int M, int N, int K, int G, float alpha,
                                float beta, cudaStream_t st);

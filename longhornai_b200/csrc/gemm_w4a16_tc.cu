@@ -208,7 +208,20 @@ struct W4TcParams {
     int* status;
     const float* inv_scale;  // [M]
     int dig_row0;            // first row of this slab in the digit tensor
+    // Sharded use (peer_world > 0): the final values also go to columns [peer_col0, peer_col0 + N) of every
+    // rank's row-major [rows, peer_ld] matrix (peer_dst[w], this slab's first row added by the kernel), and
+    // the CTA that completes a column tile then adds one to counter `peer_rank` of every rank (peer_flags[w]).
+    float* const* peer_dst;
+    uint32_t* const* peer_flags;
+    int peer_world, peer_rank, peer_ld, peer_col0, peer_row0;
 };
+
+// one arrival at every rank of a sharded GEMM, by the thread that has fenced the CTA's stores
+__device__ __forceinline__ void tc_peer_signal(const W4TcParams& p) {
+    __threadfence_system();
+    for (int w = 0; w < p.peer_world; ++w)
+        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.peer_flags[w] + p.peer_rank) : "memory");
+}
 
 // int8 x int8 -> int32 (bits 4-5 = 2; formats at bits 7-9 and 10-12 = 1), A = weights MN-major
 // (bit 15), B = digits K-major, N >> 3 at bit 17, M = 128 >> 4 at bit 24
@@ -273,6 +286,9 @@ __device__ __forceinline__ void tc_sum_partials(const W4TcParams& p, const float
                     r.z = fmaf(p.beta, old[x].z, p.alpha * sum[x].z); r.w = fmaf(p.beta, old[x].w, p.alpha * sum[x].w);
                 }
                 *reinterpret_cast<float4*>(p.C + m * p.N + tile_col0 + c) = r;
+                for (int w = 0; w < p.peer_world; ++w)
+                    *reinterpret_cast<float4*>(p.peer_dst[w] + static_cast<int64_t>(p.peer_row0 + m) * p.peer_ld +
+                                               p.peer_col0 + tile_col0 + c) = r;
             }
         }
     }
@@ -573,9 +589,12 @@ gemm_w4a16_tc_kernel(const __grid_constant__ TensorMap tmW, const __grid_constan
                     }
 #pragma unroll
                     for (int m = 0; m < 8; ++m) {
-                        if (m0 + m < p.M)
-                            cp[(m0 + m) * p.N] =
-                                (p.beta == 0.0f) ? p.alpha * val[m0 + m] : fmaf(p.beta, old[m], p.alpha * val[m0 + m]);
+                        if (m0 + m < p.M) {
+                            const float r = (p.beta == 0.0f) ? p.alpha * val[m0 + m] : fmaf(p.beta, old[m], p.alpha * val[m0 + m]);
+                            cp[(m0 + m) * p.N] = r;
+                            for (int w = 0; w < p.peer_world; ++w)
+                                p.peer_dst[w][static_cast<int64_t>(p.peer_row0 + m0 + m) * p.peer_ld + p.peer_col0 + col0 + cl] = r;
+                        }
                     }
                 }
             };
@@ -589,6 +608,10 @@ gemm_w4a16_tc_kernel(const __grid_constant__ TensorMap tmW, const __grid_constan
                     for (int m = 0; m < MP; ++m)
                         if (m < p.M) my_slot[m * TC_COLS] = acc[m];
                 }
+            }
+            if (whole && p.peer_world > 0) {                 // the tile is complete: tell every rank
+                tc_epi_sync();
+                if (et == 0) tc_peer_signal(p);
             }
             if (!whole) {
                 // the last contributor to arrive adds the partials up in contributor order and writes C;
@@ -607,6 +630,7 @@ gemm_w4a16_tc_kernel(const __grid_constant__ TensorMap tmW, const __grid_constan
                 tc_epi_sync();
                 if (*epi_flag) tc_sum_partials(p, p.partial + (static_cast<int64_t>(tile) * p.max_contrib) * p.M * TC_COLS, tile * TC_COLS, n_contrib, et);
                 tc_epi_sync();                               // epi_flag is free again
+                if (p.peer_world > 0 && et == 0 && *epi_flag) tc_peer_signal(p);
             }
             if (et == 0) TC_STAMP(3, 3);
             u += s_end - s_begin;
@@ -664,8 +688,10 @@ static int launch_tc_slab(lhb_ctx* ctx, const TensorMap& tmW, const TensorMap& t
 }
 
 int launch_w4a16_tc(lhb_ctx* ctx, const float* A, const uint8_t* Bp, const float* Bs, float* C, int M, int N, int K,
-                    int G, float alpha, float beta, cudaStream_t st, int prologue, const float* gamma, float eps) {
+                    int G, float alpha, float beta, cudaStream_t st, int prologue, const float* gamma, float eps,
+                    const W4Peer* peer, uint32_t* arrivals_out) {
     if (!w4a16_tc_ok(M, N, K, G)) return LHB_ERR_UNSUPPORTED;
+    if (arrivals_out) *arrivals_out = 0;
     if (ctx->scratch_bytes < TC_SCRATCH_HEAD) return LHB_ERR_SCRATCH;
     TensorMap tmW;
     if (int e = get_tensor_map_2d_u8(ctx, Bp, K / 2, N, N, TC_ROWS, TC_COLS, false, &tmW)) return e;
@@ -727,6 +753,13 @@ int launch_w4a16_tc(lhb_ctx* ctx, const float* A, const uint8_t* Bp, const float
             p.status = ctx->status_word;
             p.inv_scale = inv + (m0 - pass0);
             p.dig_row0 = sl * drows;
+            if (peer) {
+                p.peer_dst = reinterpret_cast<float* const*>(peer->dst_table);
+                p.peer_flags = peer->flag_table;
+                p.peer_world = peer->world; p.peer_rank = peer->rank; p.peer_ld = peer->ld; p.peer_col0 = peer->col0;
+                p.peer_row0 = m0;
+                if (arrivals_out) *arrivals_out += static_cast<uint32_t>(col_tiles);
+            }
             const int e = mp == 16 ? launch_tc_slab<16>(ctx, tmW, tmD, p, ctas, st)
                                    : launch_tc_slab<32>(ctx, tmW, tmD, p, ctas, st);
             if (e) return e;

@@ -29,6 +29,7 @@
 // it with lhb_peer_status.  CTAs push before they wait and wait only on other
 // GPUs, so no scheduling order of the grid can deadlock it.
 #include "common.cuh"
+#include "dispatch.h"
 
 namespace lhb {
 
@@ -90,6 +91,37 @@ peer_allgather_cols_kernel(const float4* __restrict__ local, int rows, int w4, f
             state[0] = target;
         }
     }
+}
+
+// The waiting half alone, for producers that push their results themselves (the sharded GEMM): thread p
+// waits until rank p's counter here has grown by `add` over state[0], then state[0] advances.
+__global__ void __launch_bounds__(64)
+peer_wait_kernel(uint32_t* const* __restrict__ flag_table, uint32_t* __restrict__ state, int rank, int world,
+                 uint32_t add, unsigned long long timeout_ns) {
+    const uint32_t target = state[0] + add;
+    if (static_cast<int>(threadIdx.x) < world) {
+        const uint32_t* mine = flag_table[rank] + threadIdx.x;
+        const unsigned long long t0 = pg_now_ns();
+        bool ok = false;
+        for (;;) {
+            if (static_cast<int32_t>(pg_peek(mine) - target) >= 0) { ok = true; break; }
+            if (pg_now_ns() - t0 > timeout_ns) break;
+            __nanosleep(40);
+        }
+        if (!ok) atomicCAS(&state[2], 0u, static_cast<uint32_t>(1 + threadIdx.x));
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) state[0] = target;
+}
+
+int launch_peer_wait(uint32_t* const* flag_table, uint32_t* state, int rank, int world, uint32_t add,
+                     int timeout_ms, cudaStream_t st) {
+    if (!flag_table || !state) return LHB_ERR_NULL;
+    if (world < 1 || world > 64 || rank < 0 || rank >= world || timeout_ms <= 0) return LHB_ERR_BAD_SHAPE;
+    peer_wait_kernel<<<1, 64, 0, st>>>(flag_table, state, rank, world, add,
+                                       static_cast<unsigned long long>(timeout_ms) * 1000000ull);
+    LHB_LAUNCH_CHECK();
+    return LHB_OK;
 }
 
 inline int peer_ctas_per_peer(int rows, int width) {

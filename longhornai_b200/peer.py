@@ -91,6 +91,28 @@ class PeerGather:
                                                      self.world, self.timeout_ms, stream), "lhb_peer_allgather_cols")
         return self.tensor(name)
 
+    def gemm_w4a16_gather(self, A, packed, scales, group: int, C: torch.Tensor, name: str, alpha=1.0, beta=0.0, ctx=None):
+        """C [rows, cols/world] = alpha * A @ dequant(packed, scales) + beta * C on this rank's column shard of
+        the weight, and matrix `name` on every rank receives all ranks' results: the GEMM's own epilogue
+        stores over NVLink where the tensor-core kernel serves the shape, otherwise GEMM and gather()."""
+        from . import kernels as K
+        o, rows, cols = self._offsets[name]
+        w = cols // self.world
+        assert tuple(C.shape) == (rows, w) and C.is_contiguous() and C.dtype == torch.float32
+        assert name != self._last or self.world == 1, "consecutive gathers must fill different matrices"
+        h = (ctx or K.default_context()).handle
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        rc = self.lib.lhb_gemm_w4a16_groupwise_peer(h, A.data_ptr(), packed.data_ptr(), scales.data_ptr(), C.data_ptr(),
+                                                    rows, w, A.shape[1], group, float(alpha), float(beta),
+                                                    self._dst_tables[name].data_ptr(), self._flag_table.data_ptr(),
+                                                    self._state.data_ptr(), self.rank, self.world, self.timeout_ms, stream)
+        if rc == _cabi.ERR_UNSUPPORTED:
+            K.gemm_w4a16_groupwise(A, packed, scales, group, C=C, alpha=alpha, beta=beta, ctx=ctx)
+            return self.gather(C, name)
+        _cabi.check(rc, "lhb_gemm_w4a16_groupwise_peer")
+        self._last = name
+        return self.tensor(name)
+
     def check(self) -> None:
         """Synchronises the current stream and raises if a wait of any gather so far gave up."""
         stream = torch.cuda.current_stream(self.device).cuda_stream

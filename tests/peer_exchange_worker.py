@@ -42,15 +42,17 @@ def exchange_alone(rank, world):
     pg.close(dist)
 
 
-def sharded_step(rank, world):
+def sharded_step(rank, world, n_req=5):
+    """n_req = 5: the projections run on the GEMV kernel and the exchanges are separate launches;
+    n_req = 40: they run on the tensor-core kernel, whose epilogue pushes the residual slabs itself."""
     cfg = ds.StepConfig(1024, 8, 4, 128, 2048, 128, 500000.0, False, 1e-5)
-    n_layers, n_req, bs, bpr = 2, 5, 16, 8
+    n_layers, bs, bpr = 2, 16, 8
     nb = n_req * bpr
     L = lb.PagedLayout(nb, bs, cfg.n_kv_heads, cfg.head_dim)
     acfg = lb.PagedAttnCfg(cfg.n_q_heads, cfg.n_kv_heads, 1, cfg.head_dim, 1, 0.0, 0, 0)
     g = torch.Generator(device="cuda").manual_seed(3)
     tables = torch.from_numpy(np.random.default_rng(0).permutation(nb).astype(np.int32).reshape(n_req, bpr)).cuda()
-    past = torch.tensor([5, 16, 37, 100, 64], dtype=torch.int32, device="cuda")
+    past = torch.tensor([5, 16, 37, 100, 64] * (n_req // 5), dtype=torch.int32, device="cuda")
     cur = past + 1
 
     def rnd(k, n):
@@ -92,12 +94,20 @@ def sharded_step(rank, world):
     buf.x.copy_(x0)
     ds.decode_step_tp(buf.x, lw, pools3, tables, past, cur, cfg, Lr, ar, buf, rank, world, dist)
     torch.cuda.synchronize()
-    assert torch.equal(x2, x1), f"rank {rank}: library-gather step differs from the single-rank step"
-    assert torch.equal(buf.x, x1), f"rank {rank}: peer-gather step differs from the single-rank step"
+    # the GEMV kernel's result does not depend on how N is sharded; the tensor-core kernel deals its K
+    # ranges out by the shard's tile count, so its sharded sums may differ from the unsharded ones in the
+    # last place - the two sharded forms run the same GEMMs and must agree exactly either way
+    assert torch.equal(buf.x, x2), f"rank {rank}: peer-gather step differs from the library-gather step"
+    if n_req < 17:
+        assert torch.equal(x2, x1), f"rank {rank}: sharded step differs from the single-rank step"
+    else:
+        err = (x2 - x1).abs().max().item()
+        assert err <= 1e-4 + 1e-3 * x1.abs().max().item(), f"rank {rank}: sharded step off by {err}"
     lo, hi = sh.kv_head_range(cfg.n_kv_heads, rank, world)
     for a, b, c in zip(pools3, pools2, pools1):
         assert torch.equal(a.k, b.k) and torch.equal(a.v, b.v) and torch.equal(a.ks, b.ks) and torch.equal(a.vs, b.vs)
-        assert torch.equal(a.k, c.k[:, lo:hi]) and torch.equal(a.vs, c.vs[:, lo:hi])
+        if n_req < 17:
+            assert torch.equal(a.k, c.k[:, lo:hi]) and torch.equal(a.vs, c.vs[:, lo:hi])
     # the same step as a CUDA graph, replayed
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
@@ -110,7 +120,7 @@ def sharded_step(rank, world):
     for _ in range(5):
         graph.replay()
     torch.cuda.synchronize()
-    assert torch.equal(buf.x, x1), f"rank {rank}: graph replay of the peer-gather step differs"
+    assert torch.equal(buf.x, x2), f"rank {rank}: graph replay of the peer-gather step differs"
     pg.check()
     assert lb.default_context().poll() == 0
     del graph
@@ -123,6 +133,7 @@ def main():
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     exchange_alone(rank, world)
     sharded_step(rank, world)
+    sharded_step(rank, world, n_req=40)
     ok = torch.ones(1, device="cuda")
     dist.all_reduce(ok)
     if rank == 0 and int(ok.item()) == world:

@@ -73,6 +73,10 @@ def test_argument_validation_comes_before_cuda(lib):
     assert lib.lhb_gemm_w4a16_asym(fake, fake, fake, fake, fake, fake, 1, 16, 32, 12, 1.0, 0.0, None) == _cabi.ERR_BAD_SHAPE
     assert lib.lhb_gemm_w4a16_asym_fast_path(1, 14336, 4096, 128) == 1 and lib.lhb_gemm_w4a16_asym_fast_path(1, 256, 256, 64) == 0
     assert lib.lhb_gemm_fp8_fast_path(256, 256, 256) == 1 and lib.lhb_gemm_fp8_fast_path(8, 256, 256) == 0
+    assert lib.lhb_gemm_w4a16_groupwise_peer(fake, fake, fake, fake, fake, 32, 256, 128, 128, 1.0, 0.0, fake, fake, fake,
+                                             2, 2, 100, None) == _cabi.ERR_BAD_SHAPE              # rank out of range
+    assert lib.lhb_gemm_w4a16_groupwise_peer(fake, fake, fake, fake, fake, 4, 256, 128, 128, 1.0, 0.0, fake, fake, fake,
+                                             0, 2, 100, None) == _cabi.ERR_UNSUPPORTED            # too few rows
     assert lib.lhb_gemm_w4a16_fast_path(512, 14336, 4096, 128) == 1 and lib.lhb_gemm_w4a16_fast_path(2000, 14336, 4096, 128) == 0
 
 
