@@ -216,6 +216,9 @@ struct W4TcParams {
     int peer_world, peer_rank, peer_ld, peer_col0, peer_row0;
 };
 
+// PEER is a template parameter of the kernel: the unsharded instantiation carries none of this code
+#define TC_PW(p) (PEER ? (p).peer_world : 0)
+
 // one arrival at every rank of a sharded GEMM, by the thread that has fenced the CTA's stores
 __device__ __forceinline__ void tc_peer_signal(const W4TcParams& p) {
     __threadfence_system();
@@ -238,6 +241,7 @@ __device__ __forceinline__ float tc_int_to_float(uint32_t v) {
 // The last contributor to a column tile adds the partial sums up and writes C.  The 256 epilogue
 // threads share the [M][256] outputs as float4s, whatever columns they held before: each takes up to
 // four of them at a time and adds the contributors' float4s in contributor order.
+template <bool PEER>
 __device__ __forceinline__ void tc_sum_partials(const W4TcParams& p, const float* tile_slots, int tile_col0,
                                                 int n_contrib, int et) {
     const int n_out = p.M * (TC_COLS / 4);
@@ -286,7 +290,7 @@ __device__ __forceinline__ void tc_sum_partials(const W4TcParams& p, const float
                     r.z = fmaf(p.beta, old[x].z, p.alpha * sum[x].z); r.w = fmaf(p.beta, old[x].w, p.alpha * sum[x].w);
                 }
                 *reinterpret_cast<float4*>(p.C + m * p.N + tile_col0 + c) = r;
-                for (int w = 0; w < p.peer_world; ++w)
+                for (int w = 0; w < TC_PW(p); ++w)
                     *reinterpret_cast<float4*>(p.peer_dst[w] + static_cast<int64_t>(p.peer_row0 + m) * p.peer_ld +
                                                p.peer_col0 + tile_col0 + c) = r;
             }
@@ -296,7 +300,7 @@ __device__ __forceinline__ void tc_sum_partials(const W4TcParams& p, const float
 
 __device__ __forceinline__ void tc_epi_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
-template <int MP>
+template <int MP, bool PEER>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_w4a16_tc_kernel(const __grid_constant__ TensorMap tmW, const __grid_constant__ TensorMap tmD,
                      const W4TcParams p) {
@@ -592,7 +596,7 @@ gemm_w4a16_tc_kernel(const __grid_constant__ TensorMap tmW, const __grid_constan
                         if (m0 + m < p.M) {
                             const float r = (p.beta == 0.0f) ? p.alpha * val[m0 + m] : fmaf(p.beta, old[m], p.alpha * val[m0 + m]);
                             cp[(m0 + m) * p.N] = r;
-                            for (int w = 0; w < p.peer_world; ++w)
+                            for (int w = 0; w < TC_PW(p); ++w)
                                 p.peer_dst[w][static_cast<int64_t>(p.peer_row0 + m0 + m) * p.peer_ld + p.peer_col0 + col0 + cl] = r;
                         }
                     }
@@ -609,7 +613,7 @@ gemm_w4a16_tc_kernel(const __grid_constant__ TensorMap tmW, const __grid_constan
                         if (m < p.M) my_slot[m * TC_COLS] = acc[m];
                 }
             }
-            if (whole && p.peer_world > 0) {                 // the tile is complete: tell every rank
+            if (whole && TC_PW(p) > 0) {                 // the tile is complete: tell every rank
                 tc_epi_sync();
                 if (et == 0) tc_peer_signal(p);
             }
@@ -628,9 +632,9 @@ gemm_w4a16_tc_kernel(const __grid_constant__ TensorMap tmW, const __grid_constan
                     *epi_flag = last;
                 }
                 tc_epi_sync();
-                if (*epi_flag) tc_sum_partials(p, p.partial + (static_cast<int64_t>(tile) * p.max_contrib) * p.M * TC_COLS, tile * TC_COLS, n_contrib, et);
+                if (*epi_flag) tc_sum_partials<PEER>(p, p.partial + (static_cast<int64_t>(tile) * p.max_contrib) * p.M * TC_COLS, tile * TC_COLS, n_contrib, et);
                 tc_epi_sync();                               // epi_flag is free again
-                if (p.peer_world > 0 && et == 0 && *epi_flag) tc_peer_signal(p);
+                if (TC_PW(p) > 0 && et == 0 && *epi_flag) tc_peer_signal(p);
             }
             if (et == 0) TC_STAMP(3, 3);
             u += s_end - s_begin;
@@ -664,10 +668,10 @@ int w4a16_tc_min_rows() {
     return v;
 }
 
-template <int MP>
+template <int MP, bool PEER>
 static int launch_tc_slab(lhb_ctx* ctx, const TensorMap& tmW, const TensorMap& tmD, W4TcParams p, int ctas,
                           cudaStream_t st) {
-    auto kern = gemm_w4a16_tc_kernel<MP>;
+    auto kern = gemm_w4a16_tc_kernel<MP, PEER>;
     static bool attr_set[64] = {};
     if (!attr_set[ctx->device & 63]) {
         LHB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(tc_smem(MP))));
@@ -760,8 +764,10 @@ int launch_w4a16_tc(lhb_ctx* ctx, const float* A, const uint8_t* Bp, const float
                 p.peer_row0 = m0;
                 if (arrivals_out) *arrivals_out += static_cast<uint32_t>(col_tiles);
             }
-            const int e = mp == 16 ? launch_tc_slab<16>(ctx, tmW, tmD, p, ctas, st)
-                                   : launch_tc_slab<32>(ctx, tmW, tmD, p, ctas, st);
+            const int e = peer       ? (mp == 16 ? launch_tc_slab<16, true>(ctx, tmW, tmD, p, ctas, st)
+                                                 : launch_tc_slab<32, true>(ctx, tmW, tmD, p, ctas, st))
+                          : mp == 16 ? launch_tc_slab<16, false>(ctx, tmW, tmD, p, ctas, st)
+                                     : launch_tc_slab<32, false>(ctx, tmW, tmD, p, ctas, st);
             if (e) return e;
         }
     }
