@@ -401,6 +401,7 @@ def bench_decode_step(torch, lb, steps, warmup, hbm_peak, layers=32, batch=32, c
                 why = "a peer could not map the buffers"
         if pg is not None:
             buf = ds.TPBuffers.allocate(cfg, world, batch, x.device, peer=pg)
+            buf.fused_push = os.environ.get("LHB_TP_FUSED", "0") == "1"
             x = buf.x
 
             def step():

@@ -90,6 +90,7 @@ def sharded_step(rank, world, n_req=5):
     # sharded, push all-gather over peer memory
     pg = peer.PeerGather(ds.TPBuffers.peer_shapes(cfg, n_req), rank, world, dist)
     buf = ds.TPBuffers.allocate(cfg, world, n_req, x0.device, peer=pg)
+    buf.fused_push = n_req >= 17        # the fused form needs the tensor-core kernel
     pools3 = shard()
     buf.x.copy_(x0)
     ds.decode_step_tp(buf.x, lw, pools3, tables, past, cur, cfg, Lr, ar, buf, rank, world, dist)
