@@ -51,15 +51,22 @@ class PeerGather:
             dist.all_gather_object(handles, bytes(handle))
         self._mapped = []
         bases = []
-        for p in range(world):
-            if p == rank:
-                bases.append(self.base)
-                continue
-            ptr = C.c_void_p()
-            raw = (C.c_ubyte * 64).from_buffer_copy(handles[p])
-            _cabi.check(self.lib.lhb_peer_open(raw, C.byref(ptr)), "lhb_peer_open")
-            self._mapped.append(ptr.value)
-            bases.append(ptr.value)
+        try:
+            for p in range(world):
+                if p == rank:
+                    bases.append(self.base)
+                    continue
+                ptr = C.c_void_p()
+                raw = (C.c_ubyte * 64).from_buffer_copy(handles[p])
+                _cabi.check(self.lib.lhb_peer_open(raw, C.byref(ptr)), "lhb_peer_open")
+                self._mapped.append(ptr.value)
+                bases.append(ptr.value)
+        except Exception:
+            for ptr in self._mapped:                       # leave nothing mapped or allocated behind
+                self.lib.lhb_peer_close(ptr)
+            self.lib.lhb_peer_free(self.base)
+            self.base = None
+            raise
         self._keep = _DeviceView(self.base, off)
         self._bytes = torch.as_tensor(self._keep, device=self.device)
         self._flag_table = torch.tensor(bases, dtype=torch.int64, device=self.device)
