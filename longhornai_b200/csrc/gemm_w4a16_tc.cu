@@ -660,6 +660,12 @@ bool w4a16_tc_ok(int M, int N, int K, int G) {
     return static_cast<size_t>(tc_digit_rows(tc_slab_rows(M))) * K <= TC_DIG_BYTES;
 }
 
+// programmatic dependent launch between the digit pass and the GEMMs; LHB_PDL=0 turns it off
+static bool tc_pdl() {
+    static const bool v = !(getenv("LHB_PDL") && atoi(getenv("LHB_PDL")) == 0);
+    return v;
+}
+
 int w4a16_tc_min_rows() {
     static const int v = [] {
         const char* e = getenv("LHB_W4TC_MIN_M");
@@ -686,7 +692,7 @@ static int launch_tc_slab(lhb_ctx* ctx, const TensorMap& tmW, const TensorMap& t
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = tc_pdl() ? 1 : 0;
     LHB_CUDA(cudaLaunchKernelEx(&cfg, kern, tmW, tmD, p));
     return LHB_OK;
 }
@@ -732,7 +738,7 @@ int launch_w4a16_tc(lhb_ctx* ctx, const float* A, const uint8_t* Bp, const float
         da[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         da[0].val.programmaticStreamSerializationAllowed = 1;
         dc.attrs = da;
-        dc.numAttrs = 1;
+        dc.numAttrs = tc_pdl() ? 1 : 0;
         LHB_CUDA(cudaLaunchKernelEx(&dc, w4tc_digits_kernel, A + pass0 * row_len, K, mp, reinterpret_cast<int8_t*>(dig),
                                     inv, prologue, gamma, eps));
         const int pass_slabs = ceil_div(rows, mp);
