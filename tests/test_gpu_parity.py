@@ -223,6 +223,8 @@ def test_w4a16_many_rows_in_slabs(chk, lib, M, N, K, G):
     (100, 28672, 512, 128),     # more tiles than three quarters of the SMs: one CTA per tile... or an even deal
     (1024, 512, 256, 128),      # 32 slabs over one digit pass
     (2100, 256, 384, 128),      # three digit passes of up to 1024 rows, short last slab
+    (17, 256 * 300, 128, 128),  # more column tiles than CTAs: every CTA walks two whole tiles
+    (20, 256 * 200, 384, 128),  # ranges of four or five units over tiles of three: whole and partial segments mixed
 ])
 def test_w4a16_tensor_core_kernel_shapes(chk, M, N, K, G):
     """From 17 rows on gemm_w4a16_groupwise runs on the tensor cores (int8 digits x int8 weights,
