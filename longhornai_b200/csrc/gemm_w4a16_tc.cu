@@ -366,13 +366,16 @@ gemm_w4a16_tc_kernel(const __grid_constant__ TensorMap tmW, const __grid_constan
     }
     if (threadIdx.x == 0) TC_STAMP(3, 0);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");      // digits, C, scratch and counters belong to earlier kernels
-    if (threadIdx.x == 0) TC_STAMP(3, 1);
-    if (threadIdx.x < MP) inv_s[threadIdx.x] = threadIdx.x < p.M ? p.inv_scale[threadIdx.x] : 0.0f;
     ptx::tc_fence_before();
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Digits, C, scratch, counters and the row factors belong to earlier kernels of the stream: every role
+    // that touches them waits for the programmatic dependency here.  The weight producer and the converters
+    // touch only the weights and shared memory, so the first two units are converted while the previous
+    // kernel drains.
+    if (warp != 0 && warp < 12) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (threadIdx.x == 32) TC_STAMP(3, 1);
 
     if (warp == 0) {
         // ---- weight producer: refill ring slots as the converters release them ----
@@ -500,6 +503,8 @@ gemm_w4a16_tc_kernel(const __grid_constant__ TensorMap tmW, const __grid_constan
         const int cl = 32 * q + lane;                        // TMEM lane = column of the 128-column half
         const int et = threadIdx.x - 128;                    // 0..255
         const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(32 * q) << 16);
+        if (et < MP) inv_s[et] = et < p.M ? p.inv_scale[et] : 0.0f;
+        tc_epi_sync();
         float acc[MP];
         int i = 0, u = u0;
         bool alive = true;
