@@ -53,6 +53,74 @@ struct PagedAttnConfig {
     int chunk = 0;
 };
 
+// -- src/kernels/dtypes.hpp:305-318 -----------------------------------------------------------
+// E4M3 storage byte (4 exponent bits, bias 7; 3 mantissa bits; no infinities, 0x7f / 0xff = NaN;
+// largest finite value 448).  Same layout and members as the reference's type, so buffers of it
+// are interchangeable; the conversions are host-side helpers (round to nearest even, saturating at
+// +-448, NaN and infinities to the NaN code).
+namespace dropin {
+inline uint8_t float_to_e4m3_bits(float v) {
+    uint32_t x;
+    static_assert(sizeof(x) == sizeof(v), "float is 32 bits");
+    __builtin_memcpy(&x, &v, sizeof x);
+    const uint32_t sign = (x >> 24) & 0x80u;
+    const int e = static_cast<int>((x >> 23) & 0xff);
+    uint32_t m = x & 0x7fffffu;
+    if (e == 0xff) return static_cast<uint8_t>(sign | 0x7fu);
+    const int ne = e - 120;                               // exponent field of the result
+    if (ne > 15 || (ne == 15 && m > 0x600000u)) return static_cast<uint8_t>(sign | 0x7eu);
+    uint32_t keep, rest, half_ulp, base = 0;
+    if (ne >= 1) {
+        keep = m >> 20; rest = m & 0xfffffu; half_ulp = 0x80000u; base = static_cast<uint32_t>(ne) << 3;
+    } else {
+        if (ne < -2) return static_cast<uint8_t>(sign);
+        m |= 0x800000u;
+        const int sh = 21 - ne;
+        keep = m >> sh; rest = m & ((1u << sh) - 1u); half_ulp = 1u << (sh - 1);
+    }
+    uint32_t out = base + keep;                           // a mantissa carry runs into the exponent
+    if (rest > half_ulp || (rest == half_ulp && (out & 1u))) ++out;
+    if (out > 0x7eu) out = 0x7eu;
+    return static_cast<uint8_t>(sign | out);
+}
+inline float e4m3_bits_to_float(uint8_t b) {
+    const int e = (b >> 3) & 0xf, m = b & 7;
+    uint32_t bits;
+    if (e == 0xf && m == 7) bits = 0x7fc00000u;
+    else if (e == 0) {
+        const float mag = static_cast<float>(m) * 0.001953125f;      // m * 2^-9
+        return (b & 0x80u) ? -mag : mag;
+    } else bits = (static_cast<uint32_t>(e + 120) << 23) | (static_cast<uint32_t>(m) << 20);
+    bits |= (b & 0x80u) ? 0x80000000u : 0u;
+    float f;
+    __builtin_memcpy(&f, &bits, sizeof f);
+    return f;
+}
+}  // namespace dropin
+
+struct fp8_e4m3 {
+    uint8_t bits = 0;
+
+    fp8_e4m3() = default;
+    fp8_e4m3(float v) : bits(dropin::float_to_e4m3_bits(v)) {}
+    float to_float() const { return dropin::e4m3_bits_to_float(bits); }
+    operator float() const { return to_float(); }
+    static fp8_e4m3 from_bits(uint8_t b) { fp8_e4m3 v; v.bits = b; return v; }
+};
+static_assert(sizeof(fp8_e4m3) == 1, "fp8_e4m3 is one byte");
+
+// -- src/kernels/quant.hpp:31-34 --------------------------------------------------------------
+LH_DROPIN_API void q8_quantize_per_tensor(const float* src, int8_t* dst, float* scale_out, int64_t n);
+LH_DROPIN_API void q8_dequantize_per_tensor(const int8_t* src, float scale, float* dst, int64_t n);
+
+// -- src/kernels/quant.hpp:81-94 --------------------------------------------------------------
+LH_DROPIN_API void fp8_quantize_per_tensor(const float* src, fp8_e4m3* dst, float* scale_out, int64_t n);
+LH_DROPIN_API void fp8_dequantize_per_tensor(const fp8_e4m3* src, float scale, float* dst, int64_t n);
+LH_DROPIN_API void fp8_quantize_per_row(const float* src, fp8_e4m3* dst, float* scales_out, int rows, int dim);
+LH_DROPIN_API void fp8_dequantize_per_row(const fp8_e4m3* src, const float* scales, float* dst, int rows, int dim);
+LH_DROPIN_API void fp8_quantize_per_col(const float* src, fp8_e4m3* dst, float* scales_out, int rows, int cols);
+LH_DROPIN_API void fp8_dequantize_per_col(const fp8_e4m3* src, const float* scales, float* dst, int rows, int cols);
+
 // -- src/kernels/quant.hpp:38-75 ----------------------------------------------------------
 LH_DROPIN_API void q8_quantize_per_row(const float* src, int8_t* dst, float* scales_out, int rows, int dim);
 LH_DROPIN_API void q8_dequantize_per_row(const int8_t* src, const float* scales, float* dst, int rows, int dim);
@@ -75,6 +143,9 @@ LH_DROPIN_API void gemm_w8a8(const int8_t* A_q, const int8_t* B_q, const float* 
 LH_DROPIN_API void gemm_w4a16_groupwise(const float* A, const uint8_t* B_packed, const float* B_scales, float* C,
                                         int M, int N, int K, int group_size, float alpha = 1.0f,
                                         float beta = 0.0f);
+// -- src/kernels/gemm_quant.hpp:66-69 ----------------------------------------------------------
+LH_DROPIN_API void gemm_fp8_e4m3(const fp8_e4m3* A, const fp8_e4m3* B, float A_scale, float B_scale, float* C,
+                                 int M, int N, int K, float alpha = 1.0f, float beta = 0.0f);
 // Weight-only int8 per output channel (the reference composes
 // q8_dequantize_per_col + gemm; this is the fused call).
 LH_DROPIN_API void gemm_w8a16_perchannel(const float* A, const int8_t* B_q, const float* B_scales, float* C,

@@ -81,7 +81,9 @@ typedef struct lhb_paged_attn_cfg {
 LHB_API int lhb_ctx_create(int device, size_t scratch_bytes, lhb_ctx** out);
 LHB_API int lhb_ctx_destroy(lhb_ctx* ctx);
 /* Synchronise `stream` and return the device status word (0, or
- * LHB_ERR_TIMEOUT if a kernel's bounded wait expired); clears it. */
+ * LHB_ERR_TIMEOUT if a kernel's bounded wait expired); clears it.  After a
+ * non-zero report the context's arrival counters are zeroed as well, so the
+ * context stays usable (the results of the call that timed out are undefined). */
 LHB_API int lhb_ctx_poll(lhb_ctx* ctx, void* stream);
 LHB_API const char* lhb_status_string(int status);
 /* Text of the last failing CUDA call on this thread ("" if none). */
@@ -97,6 +99,14 @@ LHB_API int lhb_paged_attention_q8_fast_path(const lhb_paged_attn_cfg* cfg,
 
 /* ---- quantisers (bit-exact with the reference) ---------------------------- */
 
+/* lh::q8_quantize_per_tensor / q8_dequantize_per_tensor (src/kernels/quant.hpp:31-34,
+ * src/kernels/quant.cpp:33-54): one fp32 scale = max|x| / 127 (1 if 0) for the whole buffer,
+ * q = sat(x * (1 / scale)).  `scale_out` is a device pointer; the dequantiser takes the scale by
+ * value, as the reference does. */
+LHB_API int lhb_q8_quantize_per_tensor(lhb_ctx* ctx, const float* src, int8_t* dst, float* scale_out,
+                                       int64_t n, void* stream);
+LHB_API int lhb_q8_dequantize_per_tensor(lhb_ctx* ctx, const int8_t* src, float scale, float* dst,
+                                         int64_t n, void* stream);
 /* lh::q8_quantize_per_row / q8_dequantize_per_row (src/kernels/quant.hpp:38-41). */
 LHB_API int lhb_q8_quantize_per_row(lhb_ctx* ctx, const float* src, int8_t* dst,
                                     float* scales_out, int rows, int dim, void* stream);

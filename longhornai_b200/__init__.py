@@ -15,6 +15,7 @@ from .kernels import (Context, default_context, gemm_w4a16_groupwise, gemm_w8a8,
                       paged_attention_q8_batched, paged_attention_q8_batched_noalloc, paged_kv_append, paged_kv_append_q8,
                       paged_kv_append_q8_batched, q4_dequantize_groupwise, q4_quantize_groupwise,
                       q8_dequantize_per_col, q8_dequantize_per_row, q8_quantize_per_col,
+                      q8_dequantize_per_tensor, q8_quantize_per_tensor,
                       q8_quantize_per_row, rmsnorm, rope, rope_decode_batched, swiglu,
                       gemm_w4a16_asym, q4a_dequantize_groupwise, q4a_quantize_groupwise,
                       fp8_dequantize, fp8_quantize_per_col, fp8_quantize_per_row, fp8_quantize_per_tensor,

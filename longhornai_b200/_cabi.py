@@ -44,6 +44,8 @@ SIGNATURES = {
     "lhb_gemm_w8a16_fast_path": (_i, [_i, _i, _i]),
     "lhb_gemm_w8a8_fast_path": (_i, [_i, _i, _i]),
     "lhb_paged_attention_q8_fast_path": (_i, [_CP, _LP]),
+    "lhb_q8_quantize_per_tensor": (_i, [_vp, _vp, _vp, _vp, C.c_int64, _vp]),
+    "lhb_q8_dequantize_per_tensor": (_i, [_vp, _vp, _f, _vp, C.c_int64, _vp]),
     "lhb_q8_quantize_per_row": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp]),
     "lhb_q8_dequantize_per_row": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp]),
     "lhb_q8_quantize_per_col": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp]),

@@ -86,7 +86,12 @@ int lhb_ctx_poll(lhb_ctx* c, void* stream) {
     int v = 0;
     LHB_CUDA(cudaStreamSynchronize(as_stream(stream)));
     LHB_CUDA(cudaMemcpy(&v, c->status_word, sizeof(int), cudaMemcpyDeviceToHost));
-    if (v != 0) LHB_CUDA(cudaMemset(c->status_word, 0, sizeof(int)));
+    if (v != 0) {
+        // A wait that ran out may have left a split-K or split-KV arrival count short of its
+        // reset: zero the counters too, so that the context is usable again after the report.
+        LHB_CUDA(cudaMemset(c->status_word, 0, sizeof(int)));
+        LHB_CUDA(cudaMemset(c->counters, 0, c->counters_len * sizeof(int)));
+    }
     return v;
 }
 

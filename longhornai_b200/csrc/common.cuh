@@ -88,6 +88,19 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
+// Largest magnitude of four floats as raw bits (sign cleared).  Unlike fmaxf this keeps a NaN
+// (bits above 0x7f800000) or an infinity (0x7f800000): a non-finite input wins the maximum.
+__device__ __forceinline__ unsigned abs_bits_max4(float4 v) {
+    return max(max(__float_as_uint(v.x) & 0x7fffffffu, __float_as_uint(v.y) & 0x7fffffffu),
+               max(__float_as_uint(v.z) & 0x7fffffffu, __float_as_uint(v.w) & 0x7fffffffu));
+}
+// Inverse of the power-of-two digit factor 2^(se-127) for a row whose largest magnitude has the
+// bits `mb`; NaN when the row holds a NaN or an infinity, so that every output of the row is NaN
+// (the reference's fp32 sums would be NaN or Inf there; finite digits would hide the fault).
+__device__ __forceinline__ float digit_inv_scale(unsigned mb, int se) {
+    return mb >= 0x7f800000u ? __uint_as_float(0x7fc00000u) : __uint_as_float(static_cast<uint32_t>(254 - se) << 23);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -137,22 +137,22 @@ w4tc_digits_kernel(const float* __restrict__ A, int K, int mp, int8_t* __restric
         }
         return v;
     };
-    float mx = 0.0f;
+    unsigned mxb = 0u;                      // largest magnitude as bits: NaN and Inf survive the maximum
     if (cached) {
 #pragma unroll
         for (int i = 0; i < DC; ++i) {
             const int k = threadIdx.x * 4 + i * 4096;
             if (k < K && prologue != TC_PRO_NONE) hv[i] = transform(hv[i], k);
-            mx = fmaxf(mx, fmaxf(fmaxf(fabsf(hv[i].x), fabsf(hv[i].y)), fmaxf(fabsf(hv[i].z), fabsf(hv[i].w))));
+            mxb = max(mxb, abs_bits_max4(hv[i]));
         }
     } else {
         for (int k = threadIdx.x * 4; k < K; k += 4096) {
             const float4 v = transform(*reinterpret_cast<const float4*>(row + k), k);
-            mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+            mxb = max(mxb, abs_bits_max4(v));
         }
     }
-    mx = warp_max(mx);
-    if (lane == 0) s_max[warp] = __float_as_uint(mx);
+    mxb = __reduce_max_sync(0xffffffffu, mxb);
+    if (lane == 0) s_max[warp] = mxb;
     __syncthreads();
     unsigned mb = s_max[lane];
 #pragma unroll
@@ -161,7 +161,7 @@ w4tc_digits_kernel(const float* __restrict__ A, int K, int mp, int8_t* __restric
     int se = mb ? 275 - static_cast<int>((mb >> 23) & 0xff) : 127;
     se = max(1, min(253, se));
     const float scl = __uint_as_float(static_cast<uint32_t>(se) << 23);
-    if (threadIdx.x == 0) inv_scale[row_g] = __uint_as_float(static_cast<uint32_t>(254 - se) << 23);
+    if (threadIdx.x == 0) inv_scale[row_g] = digit_inv_scale(mb, se);
     auto put = [&](int k, float4 v) {
         // iv = rint(v * scl) = 65536*d2 + 256*d1 + d0 with d0, d1 in [-128, 127] and |d2| <= 64: the low
         // byte of an integer, read as signed, is its balanced digit, and what remains is divisible by 256

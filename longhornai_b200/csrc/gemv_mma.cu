@@ -268,22 +268,22 @@ gemv_digits_kernel(const float* __restrict__ A, int M, int K, int k_pad, size_t 
         }
         return v;
     };
-    float mx = 0.0f;
+    unsigned mxb = 0u;                      // largest magnitude as bits: NaN and Inf survive the maximum
     if (cached) {
 #pragma unroll
         for (int i = 0; i < DC; ++i) {
             const int k = threadIdx.x * 4 + i * 4096;
             if (k < K && prologue != GV_PRO_NONE) hv[i] = transform(hv[i], k);
-            mx = fmaxf(mx, fmaxf(fmaxf(fabsf(hv[i].x), fabsf(hv[i].y)), fmaxf(fabsf(hv[i].z), fabsf(hv[i].w))));
+            mxb = max(mxb, abs_bits_max4(hv[i]));
         }
     } else {
         for (int k = threadIdx.x * 4; k < K; k += 4096) {
             const float4 v = transform(*reinterpret_cast<const float4*>(row + k), k);
-            mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+            mxb = max(mxb, abs_bits_max4(v));
         }
     }
-    mx = warp_max(mx);
-    if (lane == 0) s_max[warp] = __float_as_uint(mx);
+    mxb = __reduce_max_sync(0xffffffffu, mxb);
+    if (lane == 0) s_max[warp] = mxb;
     __syncthreads();
     unsigned mb = s_max[lane];
 #pragma unroll
@@ -292,7 +292,7 @@ gemv_digits_kernel(const float* __restrict__ A, int M, int K, int k_pad, size_t 
     int se = mb ? 275 - static_cast<int>((mb >> 23) & 0xff) : 127;
     se = max(1, min(253, se));
     const float scl = __uint_as_float(static_cast<uint32_t>(se) << 23);
-    if (threadIdx.x == 0) inv_scale[row_g] = __uint_as_float(static_cast<uint32_t>(254 - se) << 23);
+    if (threadIdx.x == 0) inv_scale[row_g] = digit_inv_scale(mb, se);
     if (cached) {
 #pragma unroll
         for (int i = 0; i < DC; ++i) {
@@ -473,13 +473,13 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ T
         for (int j = 0; j < GV_PB; ++j) {
             if (base + j * GV_THREADS + (threadIdx.x & ~31) >= n4_pad) break;      // warp-uniform
             const int m = mrow[j];
-            float mx = fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w)));
+            unsigned mx = abs_bits_max4(v[j]);             // as bits: a NaN or an infinity wins the maximum
             const int m0 = __shfl_sync(0xffffffffu, m, 0);
             if (__all_sync(0xffffffffu, m == m0)) {        // the usual case: one row per warp step
-                mx = warp_max(mx);
-                if (lane == 0 && m0 >= 0 && mx > 0.0f) atomicMax(rowmax + m0, __float_as_uint(mx));
-            } else if (m >= 0 && mx > 0.0f) {
-                atomicMax(rowmax + m, __float_as_uint(mx));
+                mx = __reduce_max_sync(0xffffffffu, mx);
+                if (lane == 0 && m0 >= 0 && mx > 0u) atomicMax(rowmax + m0, mx);
+            } else if (m >= 0 && mx > 0u) {
+                atomicMax(rowmax + m, mx);
             }
         }
     }
@@ -507,7 +507,7 @@ gemv_mma_kernel(const __grid_constant__ TensorMap tmB, const __grid_constant__ T
         int se = mb ? 275 - static_cast<int>((mb >> 23) & 0xff) : 127;     // 127 + 21 - (e - 127)
         se = max(1, min(253, se));
         const float scl = __uint_as_float(static_cast<uint32_t>(se) << 23);
-        if (kl == 0) inv_s[m] = __uint_as_float(static_cast<uint32_t>(254 - se) << 23);
+        if (kl == 0) inv_s[m] = digit_inv_scale(mb, se);
         const float4 v = vb[j];
         write_digits<WBITS>(dfrag + ((kl >> 5) * NJ + 3 * m) * 32, kl & 31, v, scl);
       }

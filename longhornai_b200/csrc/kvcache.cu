@@ -54,6 +54,10 @@ paged_kv_append_q8_kernel(int8_t* __restrict__ k_pool, int8_t* __restrict__ v_po
     const int r = static_cast<int>(row / (static_cast<int64_t>(L.n_kv_heads) * seq_new));
     const int past = past_lens ? past_lens[r] : past_len_scalar;
     const int pos = past + s;
+    // A position the request's table row cannot describe (negative, or at or past max_blocks *
+    // block_size where the row width is known) writes nothing: the next table entry would be
+    // another request's page.
+    if (pos < 0 || (past_lens && pos / L.block_size >= max_blocks)) return;
     const int blk = block_tables[static_cast<int64_t>(r) * max_blocks + pos / L.block_size];
     if (blk < 0 || blk >= L.num_blocks) return;   // unallocated page: nothing to write
     const int slot = pos % L.block_size;
@@ -108,6 +112,7 @@ qkv_rope_append_q8_kernel(const float* __restrict__ qkv, int64_t row_stride, flo
         return;
     }
     const int h = is_v ? j - n_q_heads - L.n_kv_heads : j - n_q_heads;
+    if (pos < 0 || pos / L.block_size >= max_blocks) return;      // outside the request's table row: nothing to write
     const int blk = block_tables[static_cast<int64_t>(r) * max_blocks + pos / L.block_size];
     if (blk < 0 || blk >= L.num_blocks) return;       // unallocated page: nothing to write
     const int64_t srow = (static_cast<int64_t>(blk) * L.n_kv_heads + h) * L.block_size + pos % L.block_size;

@@ -1,6 +1,7 @@
 // The reference's `namespace lh` entry points for the quantized decode path,
 // implemented over the C ABI (see include/lh_dropin/lh_dropin.hpp).  Host
 // pointers are staged through device memory; device pointers pass through.
+#include <algorithm>
 #include <cstdio>
 #include <mutex>
 #include <stdexcept>
@@ -100,6 +101,95 @@ void synchronize() { cuda_ok(cudaStreamSynchronize(g_stream), "synchronize"); }
 }  // namespace dropin
 
 #define ARG(T, name, ptr, n, mode) Arg<T> name(ptr, n, Arg<T>::mode, any_host)
+
+void q8_quantize_per_tensor(const float* src, int8_t* dst, float* scale_out, int64_t n) {
+    bool any_host = false;
+    ARG(float, s, src, sz(n), In); ARG(int8_t, d, dst, sz(n), Out); ARG(float, sc, scale_out, 1, Out);
+    check(lhb_q8_quantize_per_tensor(context(), s.get(), d.get(), sc.get(), n, g_stream), "q8_quantize_per_tensor");
+    d.writeback(); sc.writeback(); finish(any_host);
+}
+
+void q8_dequantize_per_tensor(const int8_t* src, float scale, float* dst, int64_t n) {
+    bool any_host = false;
+    ARG(int8_t, s, src, sz(n), In); ARG(float, d, dst, sz(n), Out);
+    check(lhb_q8_dequantize_per_tensor(context(), s.get(), scale, d.get(), n, g_stream), "q8_dequantize_per_tensor");
+    d.writeback(); finish(any_host);
+}
+
+// E4M3 buffers are byte buffers of the storage codes
+static const uint8_t* bytes(const fp8_e4m3* p) { return reinterpret_cast<const uint8_t*>(p); }
+static uint8_t* bytes(fp8_e4m3* p) { return reinterpret_cast<uint8_t*>(p); }
+
+void fp8_quantize_per_tensor(const float* src, fp8_e4m3* dst, float* scale_out, int64_t n) {
+    bool any_host = false;
+    ARG(float, s, src, sz(n), In); ARG(uint8_t, d, bytes(dst), sz(n), Out); ARG(float, sc, scale_out, 1, Out);
+    check(lhb_fp8_quantize_per_tensor(context(), s.get(), d.get(), sc.get(), n, g_stream), "fp8_quantize_per_tensor");
+    d.writeback(); sc.writeback(); finish(any_host);
+}
+
+void fp8_quantize_per_row(const float* src, fp8_e4m3* dst, float* scales_out, int rows, int dim) {
+    bool any_host = false;
+    ARG(float, s, src, sz(rows, dim), In); ARG(uint8_t, d, bytes(dst), sz(rows, dim), Out); ARG(float, sc, scales_out, sz(rows), Out);
+    check(lhb_fp8_quantize_per_row(context(), s.get(), d.get(), sc.get(), rows, dim, g_stream), "fp8_quantize_per_row");
+    d.writeback(); sc.writeback(); finish(any_host);
+}
+
+void fp8_quantize_per_col(const float* src, fp8_e4m3* dst, float* scales_out, int rows, int cols) {
+    bool any_host = false;
+    ARG(float, s, src, sz(rows, cols), In); ARG(uint8_t, d, bytes(dst), sz(rows, cols), Out); ARG(float, sc, scales_out, sz(cols), Out);
+    check(lhb_fp8_quantize_per_col(context(), s.get(), d.get(), sc.get(), rows, cols, g_stream), "fp8_quantize_per_col");
+    d.writeback(); sc.writeback(); finish(any_host);
+}
+
+// dst = float(q) * scale with one scale (given by value), one per row or one per column
+static void fp8_dequantize_any(const fp8_e4m3* src, const float* scales, size_t n_scales, bool scales_by_value,
+                               float* dst, int rows, int cols, int mode, const char* where) {
+    bool any_host = false;
+    ARG(uint8_t, s, bytes(src), sz(rows, cols), In); ARG(float, d, dst, sz(rows, cols), Out);
+    if (scales_by_value) {
+        float* dsc = nullptr;                             // the C ABI reads the scale from device memory
+        cuda_ok(cudaMalloc(&dsc, sizeof(float)), "cudaMalloc(scale)");
+        cuda_ok(cudaMemcpyAsync(dsc, scales, sizeof(float), cudaMemcpyHostToDevice, g_stream), "H2D(scale)");
+        const int e = lhb_fp8_dequantize(context(), s.get(), dsc, d.get(), rows, cols, mode, g_stream);
+        cuda_ok(cudaStreamSynchronize(g_stream), "synchronize");
+        cudaFree(dsc);
+        check(e, where);
+    } else {
+        ARG(float, sc, scales, n_scales, In);
+        check(lhb_fp8_dequantize(context(), s.get(), sc.get(), d.get(), rows, cols, mode, g_stream), where);
+    }
+    d.writeback(); finish(any_host);
+}
+
+void fp8_dequantize_per_tensor(const fp8_e4m3* src, float scale, float* dst, int64_t n) {
+    // the C ABI takes rows x cols as ints: a long buffer is cut into rows of 2^20
+    int64_t done = 0;
+    while (done < n) {
+        const int64_t part = std::min<int64_t>(n - done, int64_t(1) << 30);
+        const int cols = static_cast<int>(std::min<int64_t>(part, 1 << 20));
+        const int rows = static_cast<int>(part / cols);
+        fp8_dequantize_any(src + done, &scale, 1, true, dst + done, rows, cols, 0, "fp8_dequantize_per_tensor");
+        done += static_cast<int64_t>(rows) * cols;
+    }
+}
+
+void fp8_dequantize_per_row(const fp8_e4m3* src, const float* scales, float* dst, int rows, int dim) {
+    fp8_dequantize_any(src, scales, sz(rows), false, dst, rows, dim, 1, "fp8_dequantize_per_row");
+}
+
+void fp8_dequantize_per_col(const fp8_e4m3* src, const float* scales, float* dst, int rows, int cols) {
+    fp8_dequantize_any(src, scales, sz(cols), false, dst, rows, cols, 2, "fp8_dequantize_per_col");
+}
+
+void gemm_fp8_e4m3(const fp8_e4m3* A, const fp8_e4m3* B, float A_scale, float B_scale, float* C, int M, int N, int K,
+                   float alpha, float beta) {
+    bool any_host = false;
+    ARG(uint8_t, a, bytes(A), sz(M, K), In); ARG(uint8_t, b, bytes(B), sz(K, N), In);
+    Arg<float> c(C, sz(M, N), beta == 0.0f ? Arg<float>::Out : Arg<float>::InOut, any_host);
+    check(lhb_gemm_fp8_e4m3(context(), a.get(), b.get(), A_scale, B_scale, c.get(), M, N, K, alpha, beta, g_stream),
+          "gemm_fp8_e4m3");
+    c.writeback(); finish(any_host);
+}
 
 void q8_quantize_per_row(const float* src, int8_t* dst, float* scales_out, int rows, int dim) {
     bool any_host = false;

@@ -72,8 +72,11 @@ paged_attention_generic_kernel(const float* __restrict__ Q, const void* __restri
     float mx = -INFINITY;
     for (int j = first + warp; j <= last; j += PAG_THREADS / 32) {
         float s = -INFINITY;
-        if (key_visible(cfg, i, j, shift)) {
-            const int blk = table[j / B];
+        // A table entry outside the pool (the cache manager's -1 for a page that was never
+        // allocated or has been released) masks its keys, as in the decode kernel: the key gets
+        // no weight and its page is never dereferenced, in this pass or in the third.
+        const int blk = table[j / B];
+        if (blk >= 0 && blk < L.num_blocks && key_visible(cfg, i, j, shift)) {
             const int64_t row = (static_cast<int64_t>(blk) * L.n_kv_heads + kvh) * B + j % B;
             float dot = 0.0f;
             if (Q8) {

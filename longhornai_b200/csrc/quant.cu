@@ -10,6 +10,8 @@
 //
 // All kernels here are HBM-bound streaming passes; they are offline (weights)
 // or small (activations) next to the GEMMs they feed.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace lhb {
@@ -45,6 +47,41 @@ __global__ void q8_dequantize_per_row_kernel(const int8_t* __restrict__ src,
                                              float* __restrict__ dst, int64_t total, int dim) {
     const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
     if (i < total) dst[i] = __fmul_rn(static_cast<float>(src[i]), scales[i / dim]);
+}
+
+// ---- int8 per tensor -----------------------------------------------------------
+// (src/kernels/quant.cpp:33-49: one scale = max|x| / 127, reciprocal-multiply idiom as per row.)
+// Three small passes: max|x| merged with atomicMax on the float bits into the scale word itself,
+// bits -> scale, quantise.
+
+__global__ void __launch_bounds__(256)
+tensor_absmax_kernel(const float* __restrict__ src, unsigned* __restrict__ maxbits, int64_t n) {
+    float m = 0.0f;
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+        m = fmaxf(m, fabsf(src[i]));
+    m = warp_max(m);
+    if ((threadIdx.x & 31) == 0 && m > 0.0f) atomicMax(maxbits, __float_as_uint(m));
+}
+
+__global__ void q8_max_to_scale_kernel(float* scale) {
+    const float m = *scale;                       // holds max|x| (its bits were merged as unsigned)
+    *scale = (m > 0.0f) ? __fdiv_rn(m, 127.0f) : 1.0f;
+}
+
+__global__ void __launch_bounds__(256)
+q8_quantize_tensor_kernel(const float* __restrict__ src, int8_t* __restrict__ dst, const float* __restrict__ scale,
+                          int64_t n) {
+    const float inv = __fdiv_rn(1.0f, *scale);
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+        dst[i] = static_cast<int8_t>(sat_rne(__fmul_rn(src[i], inv), 127));
+}
+
+__global__ void q8_dequantize_tensor_kernel(const int8_t* __restrict__ src, float scale, float* __restrict__ dst,
+                                            int64_t n) {
+    const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (i < n) dst[i] = __fmul_rn(static_cast<float>(src[i]), scale);
 }
 
 // ---- int8 per column ---------------------------------------------------------
@@ -142,6 +179,36 @@ using namespace lhb;
     } while (0)
 
 extern "C" {
+
+int lhb_q8_quantize_per_tensor(lhb_ctx* ctx, const float* src, int8_t* dst, float* scale_out, int64_t n,
+                               void* stream) {
+    REQUIRE(ctx && src && dst && scale_out, LHB_ERR_NULL);
+    REQUIRE(n >= 0, LHB_ERR_BAD_SHAPE);
+    cudaStream_t st = as_stream(stream);
+    LHB_CUDA(cudaMemsetAsync(scale_out, 0, sizeof(float), st));          // doubles as the max|x| accumulator
+    const unsigned grid = static_cast<unsigned>(std::min<int64_t>(std::max<int64_t>(1, ceil_div64(n, 1024)), 2368));
+    if (n > 0) {
+        tensor_absmax_kernel<<<grid, 256, 0, st>>>(src, reinterpret_cast<unsigned*>(scale_out), n);
+        LHB_LAUNCH_CHECK();
+    }
+    q8_max_to_scale_kernel<<<1, 1, 0, st>>>(scale_out);
+    LHB_LAUNCH_CHECK();
+    if (n > 0) {
+        q8_quantize_tensor_kernel<<<grid, 256, 0, st>>>(src, dst, scale_out, n);
+        LHB_LAUNCH_CHECK();
+    }
+    return LHB_OK;
+}
+
+int lhb_q8_dequantize_per_tensor(lhb_ctx* ctx, const int8_t* src, float scale, float* dst, int64_t n, void* stream) {
+    REQUIRE(ctx && src && dst, LHB_ERR_NULL);
+    REQUIRE(n >= 0, LHB_ERR_BAD_SHAPE);
+    if (n == 0) return LHB_OK;
+    q8_dequantize_tensor_kernel<<<static_cast<unsigned>(ceil_div64(n, 256)), 256, 0, as_stream(stream)>>>(src, scale,
+                                                                                                          dst, n);
+    LHB_LAUNCH_CHECK();
+    return LHB_OK;
+}
 
 int lhb_q8_quantize_per_row(lhb_ctx* ctx, const float* src, int8_t* dst, float* scales_out,
                             int rows, int dim, void* stream) {

@@ -82,6 +82,27 @@ def _ctx_for(x: torch.Tensor, ctx: Context | None) -> Context:
 # quantisers  (src/kernels/quant.hpp:38-63)
 # ---------------------------------------------------------------------------
 
+def q8_quantize_per_tensor(src: torch.Tensor, ctx: Context | None = None):
+    """lh::q8_quantize_per_tensor (src/kernels/quant.hpp:31): fp32 tensor -> (int8 of the same shape,
+    fp32 scale [1] on the device); bit-exact."""
+    c = _ctx_for(src, ctx)
+    dst = torch.empty(src.shape, dtype=torch.int8, device=src.device)
+    scale = torch.empty(1, dtype=torch.float32, device=src.device)
+    check(c.lib.lhb_q8_quantize_per_tensor(c.handle, _t(src, torch.float32, "src"), dst.data_ptr(),
+                                           scale.data_ptr(), src.numel(), _stream(c.device)),
+          "q8_quantize_per_tensor")
+    return dst, scale
+
+
+def q8_dequantize_per_tensor(src, scale: float, ctx=None):
+    c = _ctx_for(src, ctx)
+    dst = torch.empty(src.shape, dtype=torch.float32, device=src.device)
+    check(c.lib.lhb_q8_dequantize_per_tensor(c.handle, _t(src, torch.int8, "src"), C.c_float(float(scale)),
+                                             dst.data_ptr(), src.numel(), _stream(c.device)),
+          "q8_dequantize_per_tensor")
+    return dst
+
+
 def q8_quantize_per_row(src: torch.Tensor, ctx: Context | None = None):
     """fp32 [rows, dim] -> (int8 [rows, dim], fp32 scales [rows]); bit-exact."""
     c = _ctx_for(src, ctx)

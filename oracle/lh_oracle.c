@@ -83,6 +83,21 @@ static inline float absmax_f32(const float* x, int64_t n, int64_t stride) {
 /* int8 quantisers                                                     */
 /* ------------------------------------------------------------------ */
 
+/* Per-tensor symmetric int8: one scale = max|x|/127 (1 when all zero),
+ * q = sat_rne(x * (1/scale)).  Reference: src/kernels/quant.cpp:33-49. */
+LHO_API void lho_q8_quantize_per_tensor(const float* src, int8_t* dst, float* scale_out, int64_t n) {
+    float m = absmax_f32(src, n, 1);
+    float s = (m > 0.0f) ? m / 127.0f : 1.0f;
+    float inv = 1.0f / s;
+    for (int64_t i = 0; i < n; ++i) dst[i] = (int8_t)sat_rne(src[i] * inv, 127);
+    *scale_out = s;
+}
+
+/* Reference: src/kernels/quant.cpp:51-54. */
+LHO_API void lho_q8_dequantize_per_tensor(const int8_t* src, float scale, float* dst, int64_t n) {
+    for (int64_t i = 0; i < n; ++i) dst[i] = src[i] * scale;
+}
+
 /* Per-row (per-token) symmetric int8: scale = max|row|/127 (1 when the row
  * is all zero), q = sat_rne(x * (1/scale)) -- note the reciprocal multiply.
  * Reference: src/kernels/quant.cpp:52-63. */

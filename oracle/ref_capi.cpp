@@ -96,6 +96,12 @@ LHR_API void lhr_round_to_bf16(float* x, int64_t n) {
         x[i] = static_cast<float>(lh::bfloat16(x[i]));
 }
 
+LHR_API void lhr_q8_quantize_per_tensor(const float* s, int8_t* d, float* sc, int64_t n) {
+    lh::q8_quantize_per_tensor(s, d, sc, n);
+}
+LHR_API void lhr_q8_dequantize_per_tensor(const int8_t* s, float sc, float* d, int64_t n) {
+    lh::q8_dequantize_per_tensor(s, sc, d, n);
+}
 LHR_API void lhr_q8_quantize_per_row(const float* s, int8_t* d, float* sc, int rows, int dim) {
     lh::q8_quantize_per_row(s, d, sc, rows, dim);
 }

@@ -98,6 +98,75 @@ static void quant_round_trips() {
     }
 }
 
+// tests/test_quant.cpp:10-22 and :100-140 of the reference
+static void per_tensor_and_fp8() {
+    {   // Q8PerTensorRoundTrip
+        auto x = random_vector(1024, 4000, -3.0f, 3.0f);
+        std::vector<int8_t> q(x.size());
+        float scale = 0.0f;
+        lh::q8_quantize_per_tensor(x.data(), q.data(), &scale, x.size());
+        std::vector<float> d(x.size());
+        lh::q8_dequantize_per_tensor(q.data(), scale, d.data(), x.size());
+        EXPECT(scale > 0.0f);
+        for (size_t i = 0; i < x.size(); ++i) EXPECT(std::fabs(d[i] - x[i]) < scale + 1e-6f);
+    }
+    {   // Fp8PerTensorRoundTrip
+        auto x = random_vector(1024, 4500, -2.0f, 2.0f);
+        std::vector<lh::fp8_e4m3> q(x.size());
+        float scale = 0.0f;
+        lh::fp8_quantize_per_tensor(x.data(), q.data(), &scale, x.size());
+        std::vector<float> d(x.size());
+        lh::fp8_dequantize_per_tensor(q.data(), scale, d.data(), x.size());
+        for (size_t i = 0; i < x.size(); ++i) EXPECT(std::fabs(d[i] - x[i]) < 0.13f * std::fabs(x[i]) + scale);
+        // the host-side conversion of the storage type agrees with what the device dequantised
+        for (size_t i = 0; i < x.size(); i += 37) EXPECT(d[i] == q[i].to_float() * scale);
+    }
+    {   // Fp8PerRowFollowsRowScale
+        constexpr int rows = 4, dim = 32;
+        std::vector<float> x(rows * dim);
+        for (int r = 0; r < rows; ++r) {
+            const float mag = (r == 0) ? 0.001f : 50.0f;
+            auto row = random_vector(dim, static_cast<uint32_t>(4600 + r), -mag, mag);
+            for (int i = 0; i < dim; ++i) x[r * dim + i] = row[i];
+        }
+        std::vector<lh::fp8_e4m3> q(x.size());
+        std::vector<float> scales(rows), d(x.size());
+        lh::fp8_quantize_per_row(x.data(), q.data(), scales.data(), rows, dim);
+        lh::fp8_dequantize_per_row(q.data(), scales.data(), d.data(), rows, dim);
+        for (int r = 0; r < rows; ++r)
+            for (int i = 0; i < dim; ++i)
+                EXPECT(std::fabs(d[r * dim + i] - x[r * dim + i]) < 0.13f * std::fabs(x[r * dim + i]) + scales[r]);
+    }
+    {   // per column, same bound
+        constexpr int rows = 16, cols = 24;
+        auto x = random_vector(rows * cols, 4700, -4.0f, 4.0f);
+        std::vector<lh::fp8_e4m3> q(x.size());
+        std::vector<float> scales(cols), d(x.size());
+        lh::fp8_quantize_per_col(x.data(), q.data(), scales.data(), rows, cols);
+        lh::fp8_dequantize_per_col(q.data(), scales.data(), d.data(), rows, cols);
+        for (int r = 0; r < rows; ++r)
+            for (int c = 0; c < cols; ++c)
+                EXPECT(std::fabs(d[r * cols + c] - x[r * cols + c]) < 0.13f * std::fabs(x[r * cols + c]) + scales[c]);
+    }
+    {   // storage type: conversion round trip of exactly representable values, saturation, NaN code
+        EXPECT(lh::fp8_e4m3(1.0f).to_float() == 1.0f && lh::fp8_e4m3(-0.375f).to_float() == -0.375f);
+        EXPECT(lh::fp8_e4m3(448.0f).bits == 0x7e && lh::fp8_e4m3(1e9f).bits == 0x7e);
+        EXPECT(lh::fp8_e4m3(std::nanf("")).bits == 0x7f && std::isnan(lh::fp8_e4m3::from_bits(0xff).to_float()));
+    }
+    {   // GemmQuant.Fp8MatchesFp32WithinTolerance (tests/test_gemm_quant.cpp:77-95)
+        constexpr int M = 16, N = 32, K = 64;
+        auto A = random_vector(M * K, 5200), B = random_vector(K * N, 5201);
+        std::vector<float> C_fp32(M * N, 0.0f), C_q(M * N, 0.0f);
+        gemm_f32(A.data(), B.data(), C_fp32.data(), M, N, K);
+        std::vector<lh::fp8_e4m3> A8(M * K), B8(K * N);
+        float a_s = 0.0f, b_s = 0.0f;
+        lh::fp8_quantize_per_tensor(A.data(), A8.data(), &a_s, M * K);
+        lh::fp8_quantize_per_tensor(B.data(), B8.data(), &b_s, K * N);
+        lh::gemm_fp8_e4m3(A8.data(), B8.data(), a_s, b_s, C_q.data(), M, N, K);
+        EXPECT(rms(C_q, C_fp32) / rms(C_fp32) < 0.10);
+    }
+}
+
 static void gemm_quant() {
     {   // W8A8MatchesFp32WithinTolerance
         constexpr int M = 32, N = 48, K = 64;
@@ -249,6 +318,7 @@ static void decode_glue() {
 int main() {
     try {
         quant_round_trips();
+        per_tensor_and_fp8();
         gemm_quant();
         kv_quant();
         decode_glue();

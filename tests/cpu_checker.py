@@ -94,6 +94,17 @@ class Checker:
         self.fn("set_threads")(int(n))
 
     # -- quantisers -----------------------------------------------------
+    def q8_quantize_per_tensor(self, x):
+        q = np.empty(x.shape, np.int8)
+        s = np.empty(1, np.float32)
+        self.fn("q8_quantize_per_tensor")(_p(x, np.float32), _p(q), _p(s), C.c_int64(x.size))
+        return q, s
+
+    def q8_dequantize_per_tensor(self, q, scale):
+        d = np.empty(q.shape, np.float32)
+        self.fn("q8_dequantize_per_tensor")(_p(q, np.int8), C.c_float(float(scale)), _p(d), C.c_int64(q.size))
+        return d
+
     def q8_quantize_per_row(self, x):
         rows, dim = x.shape
         q = np.empty((rows, dim), np.int8)

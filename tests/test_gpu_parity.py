@@ -57,6 +57,20 @@ def test_q4_groupwise_golden_bits(name):
     assert_same_bits(host(lb.q4_dequantize_groupwise(p, s, G)), g["d"], "dequant")
 
 
+def test_q8_per_tensor_bit_exact(chk):
+    """lh::q8_quantize_per_tensor / q8_dequantize_per_tensor (src/kernels/quant.cpp:33-54), incl. the
+    all-zero tensor (scale 1) and a size that is no multiple of the block."""
+    rng = np.random.default_rng(31)
+    for n, mag in ((4000, 3.0), (1, 0.5), (100003, 1e-3), (7, 0.0)):
+        x = (rng.uniform(-1, 1, n) * mag).astype(np.float32)
+        q, s = lb.q8_quantize_per_tensor(dev(x))
+        q0, s0 = chk.q8_quantize_per_tensor(x)
+        assert_same_bits(host(q), q0, f"per-tensor q n={n}"); assert_same_bits(host(s), s0, f"per-tensor scale n={n}")
+        assert_same_bits(host(lb.q8_dequantize_per_tensor(q, float(s0[0]))), chk.q8_dequantize_per_tensor(q0, s0[0]),
+                         f"per-tensor dequant n={n}")
+    poll_ok()
+
+
 def test_quantisers_bit_exact_on_seeded_matrices(chk):
     rng = np.random.default_rng(11)
     x = rng.standard_normal((300, 1000)).astype(np.float32)
@@ -262,6 +276,32 @@ def test_w4a16_tensor_core_kernel_is_exact_on_integers():
     poll_ok()
 
 
+@pytest.mark.parametrize("M", [1, 2, 5, 16, 32])
+def test_w4a16_non_finite_activations_are_not_hidden(chk, M):
+    """A NaN or an infinity in an activation row makes that row's outputs non-finite, as the
+    reference's fp32 accumulation does (src/kernels/gemm_quant.cpp:54-82); the other rows are
+    untouched.  (The digit decomposition would otherwise turn NaN into 0 and Inf into a large
+    finite number.)"""
+    K, N, G = 1024, 1040, 128
+    rng = np.random.default_rng(M)
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    W = (rng.standard_normal((K, N)) * 0.02).astype(np.float32)
+    p, s = chk.q4_quantize_groupwise(W, G)
+    clean = chk.gemm_w4a16_groupwise(A, p, s, G)
+    bad = A.copy()
+    bad[0, 17] = np.nan
+    if M > 1:
+        bad[M - 1, 900] = np.inf
+    got = host(lb.gemm_w4a16_groupwise(dev(bad), dev(p), dev(s), G))
+    want = chk.gemm_w4a16_groupwise(bad, p, s, G)
+    assert not np.isfinite(want[0]).any() and not np.isfinite(got[0]).any()
+    if M > 1:
+        assert not np.isfinite(got[M - 1]).any()
+    if M > 2:
+        assert_close(got[1:M - 1], clean[1:M - 1], what="rows without a fault")
+    poll_ok()
+
+
 def test_w4a16_linearity_and_determinism():
     K, N, G = 2048, 2048, 128
     g = torch.Generator(device="cuda").manual_seed(5)
@@ -431,6 +471,75 @@ def test_attention_ignores_table_padding_and_is_deterministic(chk):
     assert_close(host(b), host(a), rtol=1e-4, atol=1e-5, what="padding")
     a2 = lb.paged_attention_q8_batched(Q, k, v, ks, vs, dev(tables), sl, cfg, lb_layout(L))
     assert torch.equal(a, a2), "run-to-run determinism"
+    poll_ok()
+
+
+@pytest.mark.parametrize("d", [16, 128])
+def test_attention_masks_a_released_page_inside_the_sequence(chk, d):
+    """A table entry of -1 (or any id outside the pool) inside seq_len - what the cache manager
+    leaves behind for a released page - masks that page's keys instead of being dereferenced: the
+    result equals softmax attention over the remaining keys.  head_dim 16 takes the generic kernel,
+    128 the decode kernel."""
+    rng = np.random.default_rng(11 + d)
+    qh, kvh, bs, nblk = 4, 2, 16, 12
+    lens = [70, 40]
+    L, tables, pools, (k, v, ks, vs) = build_paged_case(chk, rng, 2, lens, qh, kvh, d, bs, nblk)
+    holed = tables.copy()
+    holed[0, 1] = -1                     # tokens 16..31 of request 0
+    holed[1, 2] = nblk + 5               # tokens 32..39 of request 1: beyond the pool
+    Q = rng.standard_normal((2, qh, 1, d)).astype(np.float32)
+    cfg = AttnCfg(qh, kvh, 1, d, 1, 0.0, 0, 0)
+    got = host(lb.paged_attention_q8_batched(dev(Q), k, v, ks, vs, dev(holed), dev(np.array(lens, np.int32)),
+                                              lb_cfg(cfg), lb_layout(L)))
+    kq, vq = pools.k.reshape(nblk, kvh, bs, d).astype(np.float64), pools.v.reshape(nblk, kvh, bs, d).astype(np.float64)
+    ksc, vsc = pools.ks.reshape(nblk, kvh, bs).astype(np.float64), pools.vs.reshape(nblk, kvh, bs).astype(np.float64)
+    want = np.zeros_like(got, dtype=np.float64)
+    for r, l in enumerate(lens):
+        for h in range(qh):
+            kvh_i = h // (qh // kvh)
+            keys = [j for j in range(l) if 0 <= holed[r, j // bs] < nblk]
+            blk = np.array([holed[r, j // bs] for j in keys]); slot = np.array([j % bs for j in keys])
+            kk = kq[blk, kvh_i, slot] * ksc[blk, kvh_i, slot][:, None]
+            vv = vq[blk, kvh_i, slot] * vsc[blk, kvh_i, slot][:, None]
+            s = kk @ Q[r, h, 0].astype(np.float64) / np.sqrt(d)
+            w = np.exp(s - s.max()); w /= w.sum()
+            want[r, h, 0] = w @ vv
+    assert_close(got, want, what=f"masked pages d={d}")
+    poll_ok()
+
+
+def test_batched_append_outside_the_table_row_writes_nothing(chk):
+    """A request whose position lies at or past max_blocks * block_size (or is negative) has no
+    table entry: the append must not fall through to the next request's row and quantise into its
+    page.  The other requests' rows are written as usual, bit for bit."""
+    rng = np.random.default_rng(5)
+    kvh, d, bs, nblk, max_blocks = 2, 128, 16, 8, 2
+    L = Layout(nblk, bs, kvh, d)
+    tables = np.array([[0, 1], [2, 3], [4, 5]], np.int32)
+    past = np.array([max_blocks * bs, 5, -3], np.int32)          # request 0: one past its row; request 2: negative
+    shp = (nblk, kvh, bs, d)
+    k = torch.full(shp, 7, dtype=torch.int8, device="cuda"); v = torch.full(shp, 9, dtype=torch.int8, device="cuda")
+    ks = torch.full(shp[:3], 0.5, device="cuda"); vs = torch.full(shp[:3], 0.25, device="cuda")
+    kn = rng.standard_normal((3, kvh, 1, d)).astype(np.float32)
+    vn = rng.standard_normal((3, kvh, 1, d)).astype(np.float32)
+    lb.paged_kv_append_q8_batched(k, v, ks, vs, dev(kn), dev(vn), dev(tables), dev(past), lb_layout(L), 1)
+    pools = chk.empty_pools_q8(L)
+    pools.k[:] = 7; pools.v[:] = 9; pools.ks[:] = 0.5; pools.vs[:] = 0.25
+    chk.paged_kv_append_q8(pools, kn[1].copy(), vn[1].copy(), tables[1], L, 5, 1)      # only request 1 has a place
+    assert_same_bits(host(k).reshape(-1), pools.k.reshape(-1), "k pool")
+    assert_same_bits(host(v).reshape(-1), pools.v.reshape(-1), "v pool")
+    assert_same_bits(host(ks).reshape(-1), pools.ks.reshape(-1), "k scales")
+    assert_same_bits(host(vs).reshape(-1), pools.vs.reshape(-1), "v scales")
+    # the fused QKV + rotary + append form applies the same rule
+    qh = 4
+    qkv = rng.standard_normal((3, (qh + 2 * kvh) * d)).astype(np.float32)
+    k2 = torch.full(shp, 7, dtype=torch.int8, device="cuda"); v2 = torch.full(shp, 9, dtype=torch.int8, device="cuda")
+    ks2 = torch.full(shp[:3], 0.5, device="cuda"); vs2 = torch.full(shp[:3], 0.25, device="cuda")
+    q_out = torch.empty(3, qh, d, device="cuda")
+    lb.qkv_rope_append_q8_decode(dev(qkv), q_out, k2, v2, ks2, vs2, dev(tables), dev(past), qh, lb_layout(L),
+                                 theta_base=500000.0, interleaved=False)
+    touched = (host(k2) != 7).reshape(nblk, -1).any(axis=1)
+    assert touched.tolist() == [False, False, True, False, False, False, False, False], touched
     poll_ok()
 
 

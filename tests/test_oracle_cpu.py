@@ -199,6 +199,11 @@ def test_port_matches_compiled_reference_on_larger_inputs():
     for f in ("q8_quantize_per_row", "q8_quantize_per_col"):
         a, b = getattr(port, f)(x), getattr(ref, f)(x)
         same(a[0], b[0]); same(a[1], b[1])
+    (qt, st), (qt2, st2) = port.q8_quantize_per_tensor(x), ref.q8_quantize_per_tensor(x)
+    same(qt, qt2); same(st, st2)
+    same(port.q8_dequantize_per_tensor(qt, st[0]), ref.q8_dequantize_per_tensor(qt, st[0]))
+    zq, zs = port.q8_quantize_per_tensor(np.zeros(5, np.float32))
+    assert float(zs[0]) == 1.0 and not zq.any()           # all-zero input: scale 1
     w = (rng.standard_normal((512, 96)) * 0.02).astype(np.float32)
     (p, s), (p2, s2) = port.q4_quantize_groupwise(w, 128), ref.q4_quantize_groupwise(w, 128)
     same(p, p2); same(s, s2)
