@@ -3,8 +3,8 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
 Headline workload (N=1): int4 group-128 decode GEMV at the Llama-3-8B MLP
-up-projection shape (A 1x4096 bf16-stored, W 4096x14336), the second BASELINE
-config.  One step = one pass of the GEMV over LAYERS distinct quantised weight
+up-projection shape (A 1x4096 bf16-stored, W 4096x14336).  One step = one pass
+of the GEMV over LAYERS distinct quantised weight
 matrices (a 32-layer model's worth, 1 GB of packed weights, so the 126 MB L2
 cannot serve the traffic).  value = algorithmic bytes moved per second, summed
 over ranks.  At N>1 every weight is sharded along N (output columns), each
@@ -15,10 +15,13 @@ The same JSON line carries: the roofline of the dominant kernel against the
 measured HBM copy bandwidth, the end-to-end number through the host-buffer API
 (activations in from pinned host memory, outputs back out, every call), the
 reference's CPU implementation timed on this box's host cores on a bounded
-sample, clocks sampled during the timed region, and the other BASELINE
-workloads (M=8/32, weight-only int8 M=16, paged int8-KV decode attention,
-W8A8) as `extra`.  All inputs are seeded synthetic data of the stated shapes
-and distributions.
+sample (one thread as shipped, and every core through a harness loop), clocks
+sampled during the timed region, per-step percentiles, and the other workloads
+(M=8/32, weight-only int8 M=16, paged int8-KV decode attention, W8A8, the
+32-layer decode step) as `extra`.  At N>1 `extra` holds the sharded forms: the
+tensor-parallel decode step, KV-head-sharded paged decode and N-sharded W8A8
+with its outputs pushed to every rank from the GEMM's epilogue.  All inputs are
+seeded synthetic data of the stated shapes and distributions.
 """
 from __future__ import annotations
 
@@ -157,10 +160,93 @@ def cpu_gemv_baseline(budget_s=12.0, M=1):
         times.append(time.perf_counter() - t0)
     times.sort()
     p50 = times[len(times) // 2]
-    return {"value": gemv_bytes(M, K_DIM, N_DIM, GROUP) / p50 / 1e12, "unit": UNIT, "cores": threads,
+    # as shipped: the reference function has no parallel region, one call runs on one thread
+    one = []
+    Cfull = np.zeros((M, N_DIM), np.float32)
+    for _ in range(2):
+        t0 = time.perf_counter()
+        chk.gemm_w4a16_groupwise(A, p, s, GROUP, Cfull)
+        one.append(time.perf_counter() - t0)
+    b = gemv_bytes(M, K_DIM, N_DIM, GROUP)
+    return {"value": b / p50 / 1e12, "unit": UNIT, "cores": threads,
             "kind": chk.kind, "ms_per_call": p50 * 1e3,
+            "one_thread": {"value": b / min(one) / 1e12, "unit": UNIT, "ms_per_call": min(one) * 1e3,
+                           "sample": "the unmodified function as shipped (no parallel region): best of 2 calls"},
             "sample": f"{len(times)} calls of one {K_DIM}x{N_DIM} GEMV (M={M}), N split into "
                       f"{shards} compact shards, one per host thread, {copies} weight copies cycled; p50"}
+
+
+def cpu_other_baselines():
+    """The other workloads on the host cores, each on a bounded sample: the reference's functions as
+    shipped (one thread) and through the harness loop over independent calls (all cores)."""
+    import numpy as np
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from cpu_checker import AttnCfg, Layout, best_checker
+    chk = best_checker()
+    chk.set_threads(len(os.sched_getaffinity(0)))
+    threads = chk.max_threads()
+    rng = np.random.default_rng(20241)
+    out = {}
+
+    def best(f, n=2):
+        ts = []
+        for _ in range(n):
+            t0 = time.perf_counter(); f(); ts.append(time.perf_counter() - t0)
+        return min(ts)
+    # weight-only int8, M=16, K=N=4096: dequantise + fp32 GEMM (the reference has no fused function)
+    W = (rng.standard_normal((4096, 4096)) * 0.02).astype(np.float32)
+    q, s = chk.q8_quantize_per_col(W)
+    A = rng.standard_normal((16, 4096)).astype(np.float32)
+    b1 = gemv_bytes(16, 4096, 4096, 0, wbits=8)
+    t_one = best(lambda: chk.gemm_w8a16_perchannel(A, q, s))
+    shards = threads
+    while 4096 % (shards * 16):
+        shards -= 1
+    ns = 4096 // shards
+    Bq = [np.ascontiguousarray(q[:, i * ns:(i + 1) * ns]) for i in range(shards)]
+    Bs = [np.ascontiguousarray(s[i * ns:(i + 1) * ns]) for i in range(shards)]
+    Cs = [np.zeros((16, ns), np.float32) for _ in range(shards)]
+    t_par = best(lambda: chk.par_gemm_w8a16_shards(A, Bq, Bs, Cs), 3)
+    out["w8a16_m16"] = {"value": b1 / t_par / 1e12, "unit": "TB/s", "cores": threads, "ms_per_call": t_par * 1e3,
+                        "one_thread": {"value": b1 / t_one / 1e12, "ms_per_call": t_one * 1e3},
+                        "sample": f"full size (M=16, K=N=4096); harness: {shards} column shards, one per thread"}
+    # paged int8-KV decode: 8 of the 64 sequences (requests are independent; tok/s scales with the count)
+    n_s, hq, hkv, d, bs, pages = 8, 32, 8, 128, 16, 65536
+    lens = rng.integers(512, 4097, size=n_s).astype(np.int32)
+    perm = rng.permutation(pages).astype(np.int32)
+    tables = np.full((n_s, 4096 // bs), -1, np.int32)
+    used = 0
+    L = Layout(pages, bs, hkv, d)
+    pools = chk.empty_pools_q8(L)
+    for r, l in enumerate(lens):
+        nb = (int(l) + bs - 1) // bs
+        tables[r, :nb] = perm[used:used + nb]; used += nb
+        kn = rng.standard_normal((hkv, int(l), d), dtype=np.float32)
+        chk.paged_kv_append_q8(pools, kn, kn[:, ::-1].copy(), tables[r], L, 0, int(l))
+    Q = rng.standard_normal((n_s, hq, 1, d)).astype(np.float32)
+    cfg = AttnCfg(hq, hkv, 1, d, 1, 0.0, 0, 0)
+    t_one = best(lambda: chk.paged_attention_q8_batched(Q, pools, tables, lens, cfg, L), 1)
+    t_par = best(lambda: chk.paged_attention_q8_batched(Q, pools, tables, lens, cfg, L, parallel=True), 2)
+    out["paged_decode_q8"] = {"value": n_s / t_par, "unit": "tok/s", "cores": min(threads, n_s),
+                              "one_thread": {"value": n_s / t_one},
+                              "sample": f"{n_s} of the 64 sequences ({int(lens.sum())} cached tokens), one request per "
+                                        f"thread in the harness loop; requests are independent, so tok/s is per call of this size"}
+    del pools
+    # W8A8 8192 x 8192 x 28672: one row of M per thread (the function is exactly linear in M), extrapolated
+    K5, N5, M5 = 8192, 28672, 8192
+    Bq5 = rng.integers(-127, 128, size=(K5, N5), dtype=np.int8)
+    rows = max(1, min(threads, 32))
+    Aq5 = rng.integers(-127, 128, size=(rows, K5), dtype=np.int8)
+    a_s, b_s = np.ones(rows, np.float32), np.ones(N5, np.float32)
+    t_one = best(lambda: chk.gemm_w8a8(Aq5[:1], Bq5, a_s[:1], b_s), 1)
+    t_par = best(lambda: chk.par_gemm_w8a8_mslabs(Aq5, Bq5, a_s, b_s, 1), 1)
+    ops_row = 2.0 * K5 * N5
+    out["w8a8_prefill"] = {"value": ops_row * rows / t_par / 1e12, "unit": "TOP/s", "cores": min(threads, rows),
+                           "one_thread": {"value": ops_row / t_one / 1e12, "s_per_row": t_one},
+                           "extrapolated_s_full_size": t_par / rows * M5,
+                           "sample": f"{rows} of the {M5} rows of M, one per thread; time scales linearly with M "
+                                     f"(extrapolated, not run at full size)"}
+    return {"kind": chk.kind, "cores": threads, "workloads": out}
 
 
 def run_reference(args):
@@ -183,31 +269,52 @@ def run_reference(args):
 
 # ----------------------------------------------------------------------------- our arm
 
-def timed(fn, steps, warmup, dist, torch, sampler=None):
+def timed(fn, steps, warmup, dist, torch, sampler=None, stats=None, min_region_s=0.0):
     """W untimed steps, then exactly `steps` steps between CUDA events on the
-    launching stream, bracketed by barrier + synchronize; max over ranks."""
+    launching stream, bracketed by barrier + synchronize; max over ranks.
+
+    With `stats` (a dict) the region is repeated until at least `min_region_s` seconds of
+    timed steps have run (each repeat bracketed the same way); the returned time is the median
+    region, and `stats` receives the percentiles of the single steps (an event pair per step,
+    mirroring bench/bench_util.hpp:98-123 of the reference: p50 / p90 / p99 beside the mean)."""
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
-    if dist is not None:
-        dist.barrier()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    regions, step_ms = [], []
     ctx = sampler if sampler is not None else _Null()
     with ctx:
-        e0.record()
-        for _ in range(steps):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-    if dist is not None:
-        dist.barrier()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1)
-    if dist is not None:
-        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+        while True:
+            if dist is not None:
+                dist.barrier()
+            torch.cuda.synchronize()
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+            ev[0].record()
+            for i in range(steps):
+                fn()
+                ev[i + 1].record()
+            torch.cuda.synchronize()
+            if dist is not None:
+                dist.barrier()
+            torch.cuda.synchronize()
+            ms = ev[0].elapsed_time(ev[steps])
+            if dist is not None:
+                t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t.item())
+            regions.append(ms)
+            if stats is not None:
+                step_ms += [ev[i].elapsed_time(ev[i + 1]) for i in range(steps)]
+            # every rank sees the same (max-reduced) times, so every rank stops at the same repeat
+            if stats is None or sum(regions) * 1e-3 >= min_region_s or len(regions) >= 200:
+                break
+    regions.sort()
+    ms = regions[len(regions) // 2]
+    if stats is not None:
+        s = sorted(step_ms)
+        pick = lambda q: s[min(len(s) - 1, int(q * len(s)))]
+        stats.update({"regions": len(regions), "steps_sampled": len(s), "mean_ms": sum(s) / len(s),
+                      "p50_ms": pick(0.50), "p90_ms": pick(0.90), "p99_ms": pick(0.99), "min_ms": s[0], "max_ms": s[-1],
+                      "region_ms_min": regions[0], "region_ms_max": regions[-1]})
     return ms
 
 
@@ -270,7 +377,7 @@ def bench_extra(torch, lb, steps, warmup, hbm_peak):
         out[f"w4a16_m{M}"] = {"us_per_call": per * 1e6, "GBps": b / per / 1e9,
                               "hbm_frac": b / per / 1e9 / hbm_peak, "bytes": b}
     del packed, scales
-    # the second config's literal weight format: asymmetric int4, fp16 scale and zero-point per group
+    # the same GEMV with asymmetric int4 weights: fp16 scale and zero-point per group
     # (same bytes per group as the reference's fp32 scale), 16 weight sets = 500 MB, M = 1
     asym = []
     for _ in range(16):
@@ -291,7 +398,7 @@ def bench_extra(torch, lb, steps, warmup, hbm_peak):
                                 "bytes": b,
                                 "fast_path": int(lb._cabi.load().lhb_gemm_w4a16_asym_fast_path(1, N_DIM, K_DIM, GROUP))}
     del asym
-    # weight-only int8, M=16, K=N=4096 (first BASELINE config), 16 weight sets = 268 MB
+    # weight-only int8, M=16, K=N=4096, 16 weight sets = 268 MB
     ws = []
     for _ in range(16):
         W = torch.randn(4096, 4096, device="cuda", generator=gen) * 0.02
@@ -322,7 +429,7 @@ def bench_extra(torch, lb, steps, warmup, hbm_peak):
 
 def bench_decode_step(torch, lb, steps, warmup, hbm_peak, layers=32, batch=32, ctx_len=2048, seed=20244,
                       rank=0, world=1, dist=None):
-    """Fourth BASELINE config: one decode step of a 32-layer Llama-3-8B-shaped stack (d 4096, 32/8 heads of
+    """One decode step of a 32-layer Llama-3-8B-shaped stack (d 4096, 32/8 heads of
     128, FFN 14336, RoPE base 500000, RMSNorm), all seven projections int4 group-128, int8 paged KV holding
     `ctx_len` tokens per sequence, `batch` sequences; the whole step replayed as one CUDA graph.  With
     world > 1 the projections are sharded along N and attention by KV head (decode_step.decode_step_tp):
@@ -409,6 +516,10 @@ def bench_decode_step(torch, lb, steps, warmup, hbm_peak, layers=32, batch=32, c
                 ds.decode_step_tp(x, lw, pools, tables, past, cur, cfg, L, acfg, buf, rank, world, dist)
             run_n, _ = graphed(nccl_step, torch, GRAPHS)
             nccl_ms = timed(run_n, steps, warmup, dist, torch) / steps
+            # the two exchanges must give the same hidden state, bit for bit, on every rank
+            nccl_step()
+            torch.cuda.synchronize()
+            x_nccl = x.clone()
         else:
             step, nccl_ms = nccl_step, None
     run, is_graph = graphed(step, torch, GRAPHS)
@@ -429,6 +540,12 @@ def bench_decode_step(torch, lb, steps, warmup, hbm_peak, layers=32, batch=32, c
         if pg is not None:
             pg.check()                                  # raises if any bounded wait gave up
             out["ms_per_step_nccl_exchange"] = nccl_ms
+            step()
+            torch.cuda.synchronize()
+            same = torch.tensor([1 if torch.equal(x, x_nccl) else 0], device="cuda")
+            dist.all_reduce(same, op=dist.ReduceOp.MIN)
+            out["tp_parity"] = ("bit-identical" if int(same.item()) == 1 else "MISMATCH") + \
+                               " (hidden state after the step: peer-memory exchange against NCCL all-gathers, every rank)"
             out["launches_per_step"] += layers * 5 + 1        # four exchanges and a separate SwiGLU per layer, one slab copy
             pg.close(dist)
         elif why:
@@ -437,7 +554,7 @@ def bench_decode_step(torch, lb, steps, warmup, hbm_peak, layers=32, batch=32, c
 
 
 def bench_fp8(torch, lb, steps, warmup, M=8192, K=8192, N=28672):
-    """The fifth config's shape with E4M3 operands and per-tensor scales (lh::gemm_fp8_e4m3) on tcgen05."""
+    """The prefill-sized GEMM shape (8192 x 8192 x 28672) with E4M3 operands and per-tensor scales (lh::gemm_fp8_e4m3) on tcgen05."""
     gen = torch.Generator(device="cuda").manual_seed(20246)
     A, sa = lb.fp8_quantize_per_tensor(torch.randn(M, K, device="cuda", generator=gen))
     B, sb = lb.fp8_quantize_per_tensor(torch.randn(K, N, device="cuda", generator=gen) * 0.02)
@@ -457,7 +574,7 @@ def bench_fp8(torch, lb, steps, warmup, M=8192, K=8192, N=28672):
 
 
 def bench_w8a8(torch, lb, steps, warmup, M=8192, K=8192, N=28672):
-    """Fifth BASELINE config: per-token int8 activations x per-channel int8 weights,
+    """Prefill-sized W8A8 GEMM: per-token int8 activations x per-channel int8 weights,
     int32 accumulate, fp32 rescale (Llama-3-70B MLP shape)."""
     import ctypes as C
     gen = torch.Generator(device="cuda").manual_seed(20245)
@@ -484,7 +601,7 @@ def bench_w8a8(torch, lb, steps, warmup, M=8192, K=8192, N=28672):
 
 def bench_paged_decode(torch, lb, steps, warmup, hbm_peak, n_req=64, hq=32, hkv=8, d=128, bs=16,
                        pool_pages=65536, seed=20243):
-    """Third BASELINE config: 64 sequences, lengths U[512,4096], page 16, random
+    """Paged int8-KV decode attention: 64 sequences, lengths U[512,4096], page 16, random
     block tables over a 64k-page pool, int8 KV with per-row fp32 scales."""
     import numpy as np
     rng = np.random.default_rng(seed)
@@ -529,6 +646,193 @@ def bench_paged_decode(torch, lb, steps, warmup, hbm_peak, n_req=64, hq=32, hkv=
             "note": "KV working set 313 MB > L2; one kernel launch per step"}
 
 
+def bench_paged_decode_sharded(torch, lb, steps, warmup, hbm_peak, rank, world, dist, n_req=64, hq=32, hkv=8, d=128,
+                               bs=16, pool_pages=65536, seed=20243):
+    """Paged int8-KV decode attention sharded by KV head: rank r holds the pools of heads
+    [r * Hkv/g, (r + 1) * Hkv/g) (a GQA group stays on one rank), the replicated block tables and the
+    query heads of its KV heads; there is no exchange inside the op.  Timed alone and with the
+    all-gather that reassembles O [n_req, Hq, d] on every rank."""
+    import numpy as np
+    from longhornai_b200 import sharding as sh
+    rng = np.random.default_rng(seed)
+    lens = rng.integers(512, 4097, size=n_req).astype(np.int32)
+    perm = rng.permutation(pool_pages).astype(np.int32)
+    max_blocks = 4096 // bs
+    tables = np.full((n_req, max_blocks), -1, np.int32)
+    used = 0
+    for r, l in enumerate(lens):
+        nb = (int(l) + bs - 1) // bs
+        tables[r, :nb] = perm[used:used + nb]
+        used += nb
+    h_lo, h_hi = sh.kv_head_range(hkv, rank, world)
+    hk, grp = h_hi - h_lo, hq // hkv
+    L = lb.PagedLayout(pool_pages, bs, hk, d)
+    shp = (pool_pages, hk, bs, d)
+    k = torch.zeros(shp, dtype=torch.int8, device="cuda")
+    v = torch.zeros_like(k)
+    ks = torch.zeros(shp[:3], device="cuda")
+    vs = torch.zeros_like(ks)
+    td = torch.from_numpy(tables).cuda()
+    gen = torch.Generator(device="cuda").manual_seed(seed)         # every rank draws the same full tensors
+    for r, l in enumerate(lens):
+        kn = torch.randn(hkv, int(l), d, device="cuda", generator=gen)
+        vn = torch.randn(hkv, int(l), d, device="cuda", generator=gen)
+        lb.paged_kv_append_q8(k, v, ks, vs, kn[h_lo:h_hi].contiguous(), vn[h_lo:h_hi].contiguous(), td[r], L, 0, int(l))
+    Qfull = torch.randn(n_req, hq, 1, d, device="cuda", generator=gen)
+    Q = Qfull[:, h_lo * grp:h_hi * grp].contiguous()
+    O = torch.empty_like(Q)
+    sl = torch.from_numpy(lens).cuda()
+    cfg = lb.PagedAttnCfg(hk * grp, hk, 1, d, 1, 0.0, 0, 0)
+
+    def op():
+        lb.paged_attention_q8_batched(Q, k, v, ks, vs, td, sl, cfg, L, O=O)
+    run, _ = graphed(op, torch, GRAPHS)
+    gathered = torch.empty((world,) + tuple(O.shape), device="cuda")
+
+    def op_gather():
+        run()
+        dist.all_gather_into_tensor(gathered, O)
+    ms_op = timed(run, steps, warmup, dist, torch)
+    ms_g = timed(op_gather, steps, warmup, dist, torch)
+    per, per_g = ms_op / steps * 1e-3, ms_g / steps * 1e-3
+    total = int(lens.sum())
+    pages = int(sum((int(l) + bs - 1) // bs for l in lens))
+    b_rank = total * hk * (2 * d + 8) + 2 * Q.numel() * 4 + 4 * pages + 4 * n_req
+    # parity across the sharding: rank 0 also runs the unsharded problem and compares the reassembled heads
+    parity = None
+    op_gather()
+    torch.cuda.synchronize()
+    if rank == 0:
+        Lf = lb.PagedLayout(pool_pages, bs, hkv, d)
+        shf = (pool_pages, hkv, bs, d)
+        kf = torch.zeros(shf, dtype=torch.int8, device="cuda"); vf = torch.zeros_like(kf)
+        ksf = torch.zeros(shf[:3], device="cuda"); vsf = torch.zeros_like(ksf)
+        gen = torch.Generator(device="cuda").manual_seed(seed)
+        for r, l in enumerate(lens):
+            kn = torch.randn(hkv, int(l), d, device="cuda", generator=gen)
+            vn = torch.randn(hkv, int(l), d, device="cuda", generator=gen)
+            lb.paged_kv_append_q8(kf, vf, ksf, vsf, kn, vn, td[r], Lf, 0, int(l))
+        cf = lb.PagedAttnCfg(hq, hkv, 1, d, 1, 0.0, 0, 0)
+        Of = lb.paged_attention_q8_batched(Qfull, kf, vf, ksf, vsf, td, sl, cf, Lf)
+        whole = sh.assemble_heads(gathered)
+        err = (whole - Of).abs()
+        tol = 1e-4 + 1e-3 * Of.abs()
+        parity = {"max_abs_err_vs_one_gpu": float(err.max().item()), "within_1e-3_1e-4": bool((err <= tol).all().item())}
+        del kf, vf, ksf, vsf
+    return {"tok_per_s": n_req / per, "us_per_step": per * 1e6, "tok_per_s_with_gather": n_req / per_g,
+            "us_per_step_with_gather": per_g * 1e6, "GBps_per_rank": b_rank / per / 1e9,
+            "hbm_frac_per_rank": b_rank / per / 1e9 / hbm_peak, "bytes_per_rank": b_rank, "sum_len": total,
+            "kv_heads_per_rank": hk, "gather_bytes_per_rank": O.numel() * 4, "n_gpus": world, "parity": parity,
+            "sharding": f"{hk} of {hkv} KV heads (and their {hk * grp} query heads) per rank, tables replicated, "
+                        f"no exchange inside the op; optional NCCL all-gather of O"}
+
+
+def bench_w8a8_sharded(torch, lb, steps, warmup, rank, world, dist, M=8192, K=8192, N=28672):
+    """W8A8 8192 x 8192 x 28672 with N sharded over the ranks.  Three forms of the same step:
+    the GEMM on the local slab alone (no exchange); the GEMM whose epilogue stores every finished
+    tile into every rank's full-width C over NVLink while the main loop runs on (this library's
+    kernel, lhb_gemm_w8a8_sharded), followed by a one-element all-reduce as the completion signal;
+    and the composition local GEMM + NCCL all-gather of the [M, N/g] slabs."""
+    from longhornai_b200 import peer as lpeer
+    from longhornai_b200 import sharding as sh
+    gen = torch.Generator(device="cuda").manual_seed(20245)       # the same full tensors on every rank
+    X = torch.randn(M, K, device="cuda", generator=gen)
+    Aq, a_s = lb.q8_quantize_per_row(X)
+    del X
+    Wt = torch.randn(K, N, device="cuda", generator=gen) * 0.02
+    Bq_full, bs_full = lb.q8_quantize_per_col(Wt)
+    del Wt
+    Bq, b_s = sh.shard_w8(Bq_full, bs_full, rank, world)
+    del Bq_full, bs_full
+    w = N // world
+    C_local = torch.empty(M, w, device="cuda")
+    ops = 2.0 * M * N * K
+    _, bf16_peak, kind = measured_peaks()
+    out = {"n_gpus": world, "sharding": f"N/{world} = {w} columns of B per rank, A replicated"}
+
+    def gemm_only():
+        lb.gemm_w8a8(Aq, Bq, a_s, b_s, C=C_local)
+    ms = timed(gemm_only, steps, warmup, dist, torch)
+    t_gemm = ms / steps * 1e-3
+    out["gemm_only"] = {"ms_per_call": t_gemm * 1e3, "TOPs": ops / t_gemm / 1e12}
+    gathered = torch.empty(world, M, w, device="cuda")
+
+    def gemm_nccl():
+        lb.gemm_w8a8(Aq, Bq, a_s, b_s, C=C_local)
+        dist.all_gather_into_tensor(gathered, C_local)
+    ms = timed(gemm_nccl, steps, warmup, dist, torch)
+    t_nccl = ms / steps * 1e-3
+    out["gemm_then_nccl_allgather"] = {"ms_per_call": t_nccl * 1e3, "TOPs": ops / t_nccl / 1e12,
+                                       "layout": "[g, M, N/g] (a re-layout would still be needed for row-major C)"}
+    nvlink_s = (world - 1) / world * M * N * 4 / 770e9            # bytes every rank must receive / measured peer-copy rate
+    out["nvlink_floor_ms"] = nvlink_s * 1e3
+    pg, why = None, ""
+    try:
+        pg = lpeer.PeerGather({"C": (M, N)}, rank, world, dist)
+    except Exception as e:      # noqa: BLE001 - reported in the JSON line
+        why = f"{type(e).__name__}: {e}"[:200]
+    ok = torch.tensor([1 if pg is not None else 0], device="cuda")
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if int(ok.item()) == 0:
+        if pg is not None:
+            pg.close(dist)
+        out["fused_push_unavailable"] = why or "a peer could not map the buffers"
+        return out
+    token = torch.zeros(1, device="cuda")
+
+    def fused():
+        pg.gemm_w8a8_sharded(Aq, Bq, a_s, b_s, "C")
+        dist.all_reduce(token)                                      # every rank's stream has passed its GEMM
+    ms = timed(fused, steps, warmup, dist, torch)
+    t_fused = ms / steps * 1e-3
+    roof = max(t_gemm, nvlink_s)
+    out["gemm_with_epilogue_push"] = {"ms_per_call": t_fused * 1e3, "TOPs": ops / t_fused / 1e12,
+                                      "exposed_exchange_ms": (t_fused - t_gemm) * 1e3,
+                                      "frac_of_roof": roof / t_fused,
+                                      "roof": "max(local GEMM time, (g-1)/g * M*N*4 B / 770 GB/s measured peer-copy rate)",
+                                      "layout": "row-major [M, N] on every rank, no re-layout"}
+    out["TOPs"] = ops / min(t_fused, t_nccl) / 1e12
+    out["ms_per_call"] = min(t_fused, t_nccl) * 1e3
+    out["frac_of_2x_bf16_" + kind + "_per_gpu"] = ops / min(t_fused, t_nccl) / 1e12 / (2 * bf16_peak) / world
+    # parity: this rank's columns of the pushed matrix are the local GEMM's bits; every other slab matches
+    # its producer's checksum
+    fused()
+    torch.cuda.synchronize()
+    dist.barrier()
+    full = pg.tensor("C")
+    gemm_only()
+    own = torch.equal(full[:, rank * w:(rank + 1) * w], C_local)
+    sums = torch.stack([full[:, r * w:(r + 1) * w].double().sum() for r in range(world)])
+    mine = C_local.double().sum().reshape(1)
+    theirs = torch.empty(world, dtype=torch.float64, device="cuda")
+    dist.all_gather_into_tensor(theirs, mine)
+    good = torch.tensor([1 if (own and bool(torch.equal(sums, theirs))) else 0], device="cuda")
+    dist.all_reduce(good, op=dist.ReduceOp.MIN)
+    out["parity"] = "bit-identical" if int(good.item()) == 1 else "MISMATCH"
+    pg.check()
+    pg.close(dist)
+    return out
+
+
+def profile_traffic(name):
+    """dram__bytes_read.sum + dram__bytes_write.sum of one launch, read from the committed ncu summary
+    of that kernel (the markdown table under the repository's profile summaries); None when the summary is absent or has no such rows."""
+    import re
+    path = os.path.join(ROOT, "profiles", name + ".md")
+    try:
+        text = open(path).read()
+    except OSError:
+        return None
+    unit = {"byte": 1.0, "Kbyte": 1e3, "Mbyte": 1e6, "Gbyte": 1e9}
+    total, seen = 0.0, 0
+    for metric in ("dram__bytes_read.sum", "dram__bytes_write.sum"):
+        m = re.search(r"\|\s*" + re.escape(metric) + r"\s*\|\s*([0-9.eE+-]+)\s*\|\s*(\w+)\s*\|", text)
+        if m and m.group(2) in unit:
+            total += float(m.group(1)) * unit[m.group(2)]
+            seen += 1
+    return int(total) if seen == 2 else None
+
+
 def run_ours(args):
     import torch
     import longhornai_b200 as lb
@@ -568,7 +872,8 @@ def run_ours(args):
             sharding.all_gather_columns(outs, g, dist)     # [g, layers, M, N/g]
 
     sampler = ClockSampler(physical_gpu_index(local)) if rank == 0 else None
-    ms = timed(step, args.steps, args.warmup, dist, torch, sampler)
+    stats = {}
+    ms = timed(step, args.steps, args.warmup, dist, torch, sampler, stats=stats, min_region_s=0.5)
     launches = args.steps * LAYERS
     bytes_call_local = gemv_bytes(M, K_DIM, n_local, GROUP)
     bytes_step_total = LAYERS * (g * (bytes_call_local - 4 * M * K_DIM) + 4 * M * K_DIM)
@@ -610,22 +915,34 @@ def run_ours(args):
         if g > 1:
             sharding.all_gather_columns(outs, g, dist)     # [g, layers, M, N/g]
         torch.cuda.current_stream().synchronize()      # the caller reads the results on the host
-    ms_e2e = timed(step_e2e, args.steps, args.warmup, dist, torch)
+    stats_e2e = {}
+    ms_e2e = timed(step_e2e, args.steps, args.warmup, dist, torch, stats=stats_e2e, min_region_s=0.3)
     e2e_value = bytes_step_total * args.steps / (ms_e2e * 1e-3) / 1e12
 
     status = lb.default_context().poll()
     if status != 0:
         raise SystemExit(f"device status word = {status}")
 
-    tp_step = None
+    tp_step, sharded = None, {}
     if g > 1 and not args.no_extra:
-        # the fourth workload, tensor-parallel: every rank takes part, rank 0 reports
+        # the sharded forms of the other workloads: every rank takes part, rank 0 reports
         del packed, scales, run_gemvs, run_e2e
         torch.cuda.empty_cache()
         try:
             tp_step = bench_decode_step(torch, lb, min(args.steps, 5), 3, hbm_peak, rank=rank, world=g, dist=dist)
         except Exception as e:
             tp_step = {"error": repr(e)}
+        torch.cuda.empty_cache()
+        try:
+            sharded["paged_decode_q8"] = bench_paged_decode_sharded(torch, lb, args.steps, args.warmup, hbm_peak, rank, g, dist)
+        except Exception as e:
+            sharded["paged_decode_q8"] = {"error": repr(e)}
+        torch.cuda.empty_cache()
+        try:
+            sharded["w8a8_prefill"] = bench_w8a8_sharded(torch, lb, min(args.steps, 5), 3, rank, g, dist)
+        except Exception as e:
+            sharded["w8a8_prefill"] = {"error": repr(e)}
+        torch.cuda.empty_cache()
 
     if rank != 0:
         if dist is not None:
@@ -648,7 +965,9 @@ def run_ours(args):
                                                  " (NOT larger than L2 at this shard size)"),
                    "launch": "CUDA graph replay of the step" if is_graph else "eager launches",
                    "fast_path": int(lb._cabi.load().lhb_gemm_w4a16_fast_path(M, n_local, K_DIM, GROUP))},
-        "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
+        "step_stats": dict(stats, note="per-step CUDA-event times over all timed regions; ms_per_step and value "
+                                       "come from the median region of exactly `steps` steps"),
+        "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e / args.steps, "step_stats": stats_e2e,
                 "h2d_bytes_per_step": LAYERS * M * K_DIM * 4, "d2h_bytes_per_step": LAYERS * M * n_local * 4,
                 "note": "every call's activations H2D from pinned memory and its outputs D2H to pinned memory, "
                         "input copies / GEMVs / result copies on three streams, host sync every step; "
@@ -658,9 +977,9 @@ def run_ours(args):
                      "unit": "GB/s", "frac": achieved / hbm_peak, "peak_kind": f"of {peak_kind}",
                      "frac_of_nominal_8TBps": achieved / 8000.0, "bytes_per_launch": bytes_call_local,
                      "us_per_launch": per_launch_s * 1e6,
-                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at the
-                     # full N (profiles/gemv_w4a16_m1_cfg2.md); scales with the shard width
-                     "traffic": int(31_274_496 * (n_local / N_DIM)) if M == 1 else None},
+                     # dram bytes of one launch of this kernel at the full N, read from the committed
+                     # profiler summary of the kernel; scaled by the shard width
+                     "traffic": (lambda tr: int(tr * (n_local / N_DIM)) if tr else None)(profile_traffic("gemv_w4a16_m1_cfg2"))},
         "clocks": sampler.summary() if sampler else None,
     }
     if g == 1 and not args.no_extra:
@@ -669,12 +988,16 @@ def run_ours(args):
         except Exception as e:      # the headline must still be printed
             line["extra"] = {"error": repr(e)}
     if tp_step is not None:
-        line["extra"] = {"decode_step_cfg4": tp_step}
+        line["extra"] = dict({"decode_step_cfg4": tp_step}, **sharded)
     if g == 1 and not args.no_cpu:
         try:
-            line["cpu_baseline"] = cpu_gemv_baseline()
+            line["cpu_baseline"] = cpu_gemv_baseline(budget_s=8.0)
         except Exception as e:
             line["cpu_baseline"] = {"error": repr(e)}
+        try:
+            line["cpu_baseline"]["other_workloads"] = cpu_other_baselines()
+        except Exception as e:
+            line["cpu_baseline"]["other_workloads"] = {"error": repr(e)}
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
@@ -688,7 +1011,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary workloads")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--only", default=None, choices=["paged_decode", "w8a8", "decode_step"],
+    ap.add_argument("--only", default=None, choices=["paged_decode", "w8a8", "decode_step", "sharded"],
                     help="run one secondary workload alone on one GPU (for profiling) and print its numbers")
     args = ap.parse_args()
     if args.warmup < 3:
@@ -704,6 +1027,23 @@ def main():
         import longhornai_b200 as lb
         torch.cuda.set_device(0)
         print(json.dumps({"w8a8_prefill": bench_w8a8(torch, lb, args.steps, args.warmup, M=2048)}), flush=True)
+    elif args.only == "sharded":
+        # under torch.distributed.run: the KV-head-sharded paged decode and the N-sharded W8A8 alone
+        import torch
+        import torch.distributed as dist
+        import longhornai_b200 as lb
+        world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+        local = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        res = {"paged_decode_q8": bench_paged_decode_sharded(torch, lb, args.steps, args.warmup, measured_peaks()[0],
+                                                             rank, world, dist)}
+        torch.cuda.empty_cache()
+        res["w8a8_prefill"] = bench_w8a8_sharded(torch, lb, min(args.steps, 5), 3, rank, world, dist)
+        if rank == 0:
+            print(json.dumps(res), flush=True)
+        dist.barrier()
+        dist.destroy_process_group()
     elif args.only == "decode_step":
         import torch
         import longhornai_b200 as lb

@@ -80,6 +80,10 @@ typedef struct lhb_paged_attn_cfg {
  * src/kernels/kvcache_quant.cpp:93). */
 LHB_API int lhb_ctx_create(int device, size_t scratch_bytes, lhb_ctx** out);
 LHB_API int lhb_ctx_destroy(lhb_ctx* ctx);
+/* Persistent kernels of this context (the tensor-core GEMMs) use at most `sm_limit` SMs (0 = all):
+ * a caller that runs its own communication kernels beside them keeps SMs free for those.  No
+ * counterpart in the reference. */
+LHB_API int lhb_ctx_set_sm_limit(lhb_ctx* ctx, int sm_limit);
 /* Synchronise `stream` and return the device status word (0, or
  * LHB_ERR_TIMEOUT if a kernel's bounded wait expired); clears it.  After a
  * non-zero report the context's arrival counters are zeroed as well, so the
@@ -133,6 +137,23 @@ LHB_API int lhb_q4_dequantize_groupwise(lhb_ctx* ctx, const uint8_t* packed, con
 LHB_API int lhb_gemm_w8a8(lhb_ctx* ctx, const int8_t* A_q, const int8_t* B_q,
                           const float* A_scales, const float* B_scales, float* C, int M, int N,
                           int K, float alpha, float beta, void* stream);
+
+/* N-sharded form of gemm_w8a8 across the GPUs of one machine (no counterpart in the reference,
+ * which has no multi-device path; the arithmetic is src/kernels/gemm_quant.cpp:29-49 on a column
+ * slab, which is self-contained: src/kernels/gemm_quant.hpp:35-45).  This rank holds B_q
+ * [K, N_local] and B_scales [N_local]; full_C is a HOST array of `world` device pointers, entry r
+ * the base of rank r's full-width fp32 matrix [M, N_local * world] as mapped in THIS process
+ * (entry `rank` this rank's own, the others peer memory: cudaIpc / lhb_peer_open).  The kernel's
+ * epilogue stores every finished tile into columns [rank * N_local, (rank + 1) * N_local) of all
+ * `world` matrices with plain stores while its main loop continues, so the transfer over NVLink
+ * overlaps the arithmetic tile by tile and every rank ends up with the row-major [M, N] result
+ * without a gather or a re-layout.  beta is 0 (the slab is overwritten).  The stores of a rank are
+ * complete when its stream has passed the call; a rank may read its matrix once every rank's
+ * stream has (a stream-ordered collective, or a barrier after synchronising).  Only shapes of
+ * lhb_gemm_w8a8_fast_path; others return LHB_ERR_UNSUPPORTED (run lhb_gemm_w8a8 and gather). */
+LHB_API int lhb_gemm_w8a8_sharded(lhb_ctx* ctx, const int8_t* A_q, const int8_t* B_q, const float* A_scales,
+                                  const float* B_scales, void* const* full_C, int rank, int world, int M,
+                                  int N_local, int K, float alpha, void* stream);
 /* lh::gemm_w4a16_groupwise (src/kernels/gemm_quant.hpp:54-57): fp32 A [M,K],
  * packed int4 B [K/2,N] with fp32 scales [K/G,N], fp32 C [M,N]. */
 LHB_API int lhb_gemm_w4a16_groupwise(lhb_ctx* ctx, const float* A, const uint8_t* B_packed,

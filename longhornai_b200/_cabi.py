@@ -38,6 +38,8 @@ SIGNATURES = {
     "lhb_ctx_create": (_i, [_i, _sz, C.POINTER(_vp)]),
     "lhb_ctx_destroy": (_i, [_vp]),
     "lhb_ctx_poll": (_i, [_vp, _vp]),
+    "lhb_ctx_set_sm_limit": (_i, [_vp, _i]),
+    "lhb_gemm_w8a8_sharded": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp]),
     "lhb_status_string": (C.c_char_p, [_i]),
     "lhb_last_error": (C.c_char_p, []),
     "lhb_gemm_w4a16_fast_path": (_i, [_i, _i, _i, _i]),

@@ -184,6 +184,35 @@ int lhb_gemm_w8a8(lhb_ctx* ctx, const int8_t* Aq, const int8_t* Bq, const float*
     return launch_w8a8_generic(Aq, Bq, as, bs, C, M, N, K, alpha, beta, st);
 }
 
+int lhb_gemm_w8a8_sharded(lhb_ctx* ctx, const int8_t* Aq, const int8_t* Bq, const float* as, const float* bs,
+                          void* const* full_C, int rank, int world, int M, int N_local, int K, float alpha,
+                          void* stream) {
+    if (!ctx || !Aq || !Bq || !as || !bs || !full_C) return LHB_ERR_NULL;
+    if (M <= 0 || N_local <= 0 || K <= 0) return LHB_ERR_BAD_SHAPE;
+    if (world < 1 || world > 8 || rank < 0 || rank >= world) return LHB_ERR_BAD_SHAPE;
+    if (static_cast<int64_t>(N_local) * world >= (int64_t(1) << 31)) return LHB_ERR_BAD_SHAPE;
+    for (int r = 0; r < world; ++r)
+        if (!full_C[r]) return LHB_ERR_NULL;
+    // only the tensor-core kernel pushes its tiles itself
+    if (!(w8a8_fast_ok(M, N_local, K) && aligned16(Aq) && aligned16(Bq) && aligned16(bs) && (N_local % 4) == 0))
+        return LHB_ERR_UNSUPPORTED;
+    float* dst[8];
+    dst[0] = static_cast<float*>(full_C[rank]);              // this rank's own copy first (p.C)
+    int n = 1;
+    for (int d = 1; d < world; ++d) dst[n++] = static_cast<float*>(full_C[(rank + d) % world]);
+    for (int d = 0; d < n; ++d)
+        if (!aligned16(dst[d])) return LHB_ERR_MISALIGNED;
+    return launch_w8a8_sharded(ctx, Aq, Bq, as, bs, dst, n, M, N_local, K, static_cast<int64_t>(N_local) * world,
+                               rank * N_local, alpha, as_stream(stream));
+}
+
+int lhb_ctx_set_sm_limit(lhb_ctx* ctx, int sm_limit) {
+    if (!ctx) return LHB_ERR_NULL;
+    if (sm_limit < 0) return LHB_ERR_BAD_SHAPE;
+    ctx->sm_limit = sm_limit;
+    return LHB_OK;
+}
+
 // ---- paged attention ------------------------------------------------------------
 
 static int check_attn(const lhb_paged_attn_cfg* cfg, const lhb_paged_layout* L) {

@@ -51,6 +51,7 @@ struct alignas(64) TensorMap { unsigned char bytes[128]; };
 struct lhb_ctx {
     int device = 0;
     int sm_count = 0;
+    int sm_limit = 0;                   // > 0: persistent kernels use at most this many SMs (lhb_ctx_set_sm_limit)
     size_t scratch_bytes = 0;
     unsigned char* scratch = nullptr;   // device
     int* status_word = nullptr;         // device, 0 = ok

@@ -35,6 +35,10 @@ int launch_w8a8_fast(lhb_ctx* ctx, const int8_t* Aq, const int8_t* Bq, const flo
                      const float* bs, float* C, int M, int N, int K, float alpha, float beta,
                      cudaStream_t st);
 
+int launch_w8a8_sharded(lhb_ctx* ctx, const int8_t* Aq, const int8_t* Bq, const float* as, const float* bs,
+                        float* const* dst, int n_dst, int M, int N, int K, int64_t ldc, int col0, float alpha,
+                        cudaStream_t st);
+
 // split-KV decode attention (paged_attention_decode.cu)
 bool decode_fast_ok(const lhb_paged_attn_cfg& cfg, const lhb_paged_layout& L);
 int launch_decode_fast(lhb_ctx* ctx, const float* Q, const int8_t* Kp, const int8_t* Vp,

@@ -51,10 +51,19 @@ constexpr uint32_t W8_IDESC = (2u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
                               (static_cast<uint32_t>(W8_BN >> 3) << 17) |
                               (static_cast<uint32_t>(W8_BM >> 4) << 24);
 
+constexpr int W8_MAX_DST = 8;
+
 struct W8Params {
     const float* a_scales;
     const float* b_scales;
-    float* C;
+    float* C;              // == dst[0]
+    // The result tile goes to n_dst matrices (row pitch ldc, first column col0): one for a plain call;
+    // for the N-sharded call the same place in every rank's full-width matrix, dst[1..] being peer
+    // memory written with plain stores from the epilogue while the main loop runs on.
+    float* dst[W8_MAX_DST];
+    int n_dst;
+    int64_t ldc;
+    int col0;
     int M, N, K;
     float alpha, beta;
     int tiles_m, tiles_n;
@@ -70,7 +79,8 @@ constexpr uint32_t f8_idesc(int m, int n) {
 
 // One 32-column chunk of one output row of the fp8 GEMM: C = beta*C + combined * acc, with the
 // reference's separate roundings (src/kernels/gemm_quant.cpp:87-104).
-__device__ __forceinline__ void f8_store_chunk(float* crow, int nb, const uint32_t (&r)[32], const W8Params& p) {
+__device__ __forceinline__ void f8_store_chunk(int64_t row_off, int nb, const uint32_t (&r)[32], const W8Params& p) {
+    float* crow = p.C + row_off;
 #pragma unroll
     for (int j = 0; j < 32; j += 4) {
         if (nb + j >= p.N) break;                      // N % 16 == 0: whole float4 in range
@@ -96,8 +106,9 @@ __device__ __forceinline__ void f8_store_chunk(float* crow, int nb, const uint32
 
 // One 32-column chunk of one output row: C = beta*C + ((alpha*a_s)*b_s[n])*float(acc),
 // multiplied in the reference's order with single roundings.
-__device__ __forceinline__ void w8_store_chunk(float* crow, int nb, const uint32_t (&r)[32], float sa,
+__device__ __forceinline__ void w8_store_chunk(int64_t row_off, int nb, const uint32_t (&r)[32], float sa,
                                                const W8Params& p) {
+    float* crow = p.C + row_off;
     if (nb + 32 <= p.N) {
 #pragma unroll
         for (int j = 0; j < 32; j += 4) {
@@ -119,6 +130,8 @@ __device__ __forceinline__ void w8_store_chunk(float* crow, int nb, const uint32
                 }
             }
             *dst = v;
+            for (int d = 1; d < p.n_dst; ++d)              // the other ranks' copies (beta == 0 there)
+                *reinterpret_cast<float4*>(p.dst[d] + row_off + nb + j) = v;
         }
     } else {
 #pragma unroll
@@ -129,6 +142,7 @@ __device__ __forceinline__ void w8_store_chunk(float* crow, int nb, const uint32
                 if (p.beta == 1.0f) v = __fadd_rn(*dst, v);
                 else if (p.beta != 0.0f) v = __fadd_rn(__fmul_rn(*dst, p.beta), v);
                 *dst = v;
+                for (int d = 1; d < p.n_dst; ++d) p.dst[d][row_off + nb + j] = v;
             }
         }
     }
@@ -239,7 +253,7 @@ gemm_w8a8_tc_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant
             const int row = m0 + 32 * q + lane;
             const bool row_ok = row < p.M;
             const float sa = (row_ok && !F8) ? __fmul_rn(p.alpha, p.a_scales[row]) : 0.0f;
-            float* crow = p.C + static_cast<int64_t>(row_ok ? row : 0) * p.N;
+            const int64_t crow = static_cast<int64_t>(row_ok ? row : 0) * p.ldc + p.col0;
 #pragma unroll 1
             for (int c = 0; c < W8_BN / 32; ++c) {
                 uint32_t r[32];
@@ -383,7 +397,7 @@ gemm_w8a8_tc_pair_kernel(const __grid_constant__ TensorMap tmA, const __grid_con
             const int row = m0 + 32 * q + lane;
             const bool row_ok = row < p.M;
             const float sa = (row_ok && !F8) ? __fmul_rn(p.alpha, p.a_scales[row]) : 0.0f;
-            float* crow = p.C + static_cast<int64_t>(row_ok ? row : 0) * p.N;
+            const int64_t crow = static_cast<int64_t>(row_ok ? row : 0) * p.ldc + p.col0;
             const uint32_t leader_tempty = ptx::mapa_shared(tempty_bar(buf), 0);
 #pragma unroll 1
             for (int c = 0; c < W8_BN / 32; ++c) {
@@ -431,12 +445,19 @@ static int launch_tc(lhb_ctx* ctx, const void* Aq, const void* Bq, W8Params p, c
     }
     p.tiles_m = ceil_div(M, W8_BM); p.tiles_n = ceil_div(N, W8_BN);
     p.status = ctx->status_word;
-    const char* pair_env = getenv("LHB_W8A8_PAIR");          // 0 forces the single-CTA kernel
-    const int use_pair = pair_env ? atoi(pair_env) : 1;
+    if (p.n_dst == 0) {                                      // a plain call: one row-major [M, N] result
+        p.n_dst = 1; p.dst[0] = p.C; p.ldc = N; p.col0 = 0;
+    }
+    static const int use_pair = [] {                         // LHB_W8A8_PAIR=0 forces the single-CTA kernel
+        const char* e = getenv("LHB_W8A8_PAIR");
+        return e ? atoi(e) : 1;
+    }();
+    // a caller that overlaps its own communication kernels keeps some SMs out of the persistent grid
+    const int sms = ctx->sm_limit > 0 ? std::min(ctx->sm_count, ctx->sm_limit) : ctx->sm_count;
     if (use_pair && M >= 256) {
         const int tiles = ceil_div(M, 256) * p.tiles_n;
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(2 * std::min(ctx->sm_count / 2, tiles), 1, 1);
+        cfg.gridDim = dim3(2 * std::min(sms / 2, tiles), 1, 1);
         cfg.blockDim = dim3(W8_THREADS, 1, 1);
         cfg.dynamicSmemBytes = W8P_SMEM;
         cfg.stream = st;
@@ -450,7 +471,7 @@ static int launch_tc(lhb_ctx* ctx, const void* Aq, const void* Bq, W8Params p, c
         LHB_CUDA(cudaLaunchKernelEx(&cfg, gemm_w8a8_tc_pair_kernel<F8>, tmA, tmB, p));
         return LHB_OK;
     }
-    const int grid = std::min(ctx->sm_count, p.tiles_m * p.tiles_n);
+    const int grid = std::min(sms, p.tiles_m * p.tiles_n);
     gemm_w8a8_tc_kernel<F8><<<grid, W8_THREADS, W8_SMEM, st>>>(tmA, tmB, p);
     LHB_LAUNCH_CHECK();
     return LHB_OK;
@@ -462,6 +483,20 @@ int launch_w8a8_fast(lhb_ctx* ctx, const int8_t* Aq, const int8_t* Bq, const flo
     W8Params p{};
     p.a_scales = as; p.b_scales = bs; p.C = C; p.M = M; p.N = N; p.K = K;
     p.alpha = alpha; p.beta = beta;
+    return launch_tc<false>(ctx, Aq, Bq, p, st);
+}
+
+// N-sharded form: the [M, N] result of this rank's weight slab lands in columns [col0, col0 + N) of the
+// [M, ldc] matrix of every rank (dst[0] this rank's own, the others peer memory).
+int launch_w8a8_sharded(lhb_ctx* ctx, const int8_t* Aq, const int8_t* Bq, const float* as, const float* bs,
+                        float* const* dst, int n_dst, int M, int N, int K, int64_t ldc, int col0, float alpha,
+                        cudaStream_t st) {
+    if (n_dst < 1 || n_dst > W8_MAX_DST) return LHB_ERR_BAD_SHAPE;
+    W8Params p{};
+    p.a_scales = as; p.b_scales = bs; p.C = dst[0]; p.M = M; p.N = N; p.K = K;
+    p.alpha = alpha; p.beta = 0.0f;
+    for (int d = 0; d < n_dst; ++d) p.dst[d] = dst[d];
+    p.n_dst = n_dst; p.ldc = ldc; p.col0 = col0;
     return launch_tc<false>(ctx, Aq, Bq, p, st);
 }
 

@@ -67,6 +67,7 @@ class PeerGather:
             self.lib.lhb_peer_free(self.base)
             self.base = None
             raise
+        self._bases = list(bases)                          # host copy: rank -> base of that rank's allocation here
         self._keep = _DeviceView(self.base, off)
         self._bytes = torch.as_tensor(self._keep, device=self.device)
         self._flag_table = torch.tensor(bases, dtype=torch.int64, device=self.device)
@@ -117,6 +118,25 @@ class PeerGather:
             K.gemm_w4a16_groupwise(A, packed, scales, group, C=C, alpha=alpha, beta=beta, ctx=ctx)
             return self.gather(C, name)
         _cabi.check(rc, "lhb_gemm_w4a16_groupwise_peer")
+        self._last = name
+        return self.tensor(name)
+
+    def gemm_w8a8_sharded(self, Aq, Bq, a_scales, b_scales, name: str, alpha: float = 1.0, ctx=None) -> torch.Tensor:
+        """N-sharded gemm_w8a8 (lhb_gemm_w8a8_sharded): this rank's weight slab Bq [K, cols/world] against the
+        replicated activations Aq [rows, K]; the tensor-core kernel's epilogue stores each finished tile into
+        columns [rank * w, (rank + 1) * w) of matrix `name` on every rank while its main loop runs on.  Returns
+        this rank's copy of the matrix; it is complete once every rank's stream has passed its own call (follow
+        it with a stream-ordered collective, or synchronise and barrier)."""
+        from . import kernels as K
+        o, rows, cols = self._offsets[name]
+        w = cols // self.world
+        assert tuple(Aq.shape)[0] == rows and tuple(Bq.shape) == (Aq.shape[1], w), (tuple(Aq.shape), tuple(Bq.shape))
+        full = (C.c_void_p * self.world)(*[b + o for b in self._bases])
+        h = (ctx or K.default_context()).handle
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        _cabi.check(self.lib.lhb_gemm_w8a8_sharded(h, Aq.data_ptr(), Bq.data_ptr(), a_scales.data_ptr(),
+                                                   b_scales.data_ptr(), full, self.rank, self.world, rows, w,
+                                                   Aq.shape[1], float(alpha), stream), "lhb_gemm_w8a8_sharded")
         self._last = name
         return self.tensor(name)
 

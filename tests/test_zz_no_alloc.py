@@ -6,7 +6,8 @@ they have no context to pass.  lhb_paged_attention_q8_batched_noalloc serves
 them from fixed scratch arrays inside the library image.  This test calls it
 through the C ABI twice in a row (the second call finds the first call's
 leftovers in the shared arrays) and compares each result with the
-context-based entry point on the same inputs, within the library tolerance;
+context-based entry point and with the CPU checker on the same inputs, within
+the library tolerance;
 it also checks that sizes beyond the fixed arrays are refused with a message.
 
 Collected last on purpose, so a run that stops at the first failure has already
@@ -19,6 +20,7 @@ import pytest
 import torch
 
 import longhornai_b200 as lb
+from cpu_checker import AttnCfg, Layout, PagedPools, best_checker
 from gpu_util import assert_close, host
 
 pytestmark = pytest.mark.gpu
@@ -57,6 +59,13 @@ def test_noalloc_entry_point_matches_context_entry_point_twice():
     for seed, lens in ((1, [1500, 33, 700, 16, 2049]), (2, [260, 4000, 5])):
         Q, k, v, ks, vs, td, sl, cfg, L = make_case(seed, lens)
         want = lb.paged_attention_q8_batched(Q, k, v, ks, vs, td, sl, cfg, L)
+        # and the CPU restatement of the reference on the same pools, so that a fault shared by both
+        # entry points (they run the same kernel) cannot pass unnoticed
+        chk = best_checker()
+        Lc, cc = Layout(L.num_blocks, L.block_size, L.n_kv_heads, L.head_dim), AttnCfg(cfg.n_q_heads, cfg.n_kv_heads, 1,
+                                                                                       cfg.head_dim, 1, 0.0, 0, 0)
+        want_cpu = chk.paged_attention_q8_batched(host(Q), PagedPools(host(k), host(v), host(ks), host(vs)), host(td),
+                                                  host(sl), cc, Lc)
         for call in (1, 2):                              # two calls in a row share the fixed arrays
             got = torch.full_like(Q, float("nan"))      # caller-owned output, poisoned
             torch.cuda.synchronize()
@@ -66,6 +75,7 @@ def test_noalloc_entry_point_matches_context_entry_point_twice():
             assert torch.cuda.mem_get_info()[0] >= free_before, "the call took device memory"
             assert torch.isfinite(got).all()
             assert_close(host(got), host(want), what=f"no-alloc entry point, case {seed}, call {call}")
+            assert_close(host(got), want_cpu, what=f"no-alloc entry point against the CPU checker, case {seed}, call {call}")
 
 
 def test_noalloc_entry_point_rejects_sizes_beyond_its_fixed_arrays():
