@@ -42,7 +42,8 @@ constexpr int W8_B_BYTES = W8_BK * W8_BN;            // 32 KiB, two 128-column b
 constexpr int W8_STAGE_BYTES = W8_A_BYTES + W8_B_BYTES;
 constexpr int W8_THREADS = 256;
 constexpr int W8_TMEM_COLS = 512;
-constexpr size_t W8_SMEM = 1024 + static_cast<size_t>(W8_STAGES) * W8_STAGE_BYTES + 256;
+constexpr int W8_OUT_STAGE = 4 * 4096;               // per epilogue warp: a 32 x 32 fp32 chunk on its way to peer memory
+constexpr size_t W8_SMEM = 1024 + static_cast<size_t>(W8_STAGES) * W8_STAGE_BYTES + 256 + W8_OUT_STAGE;
 
 // instruction descriptor: D = s32 (bits 4-5 = 2), A = B = signed int8 (bits 7-9,
 // 10-12 = 1), A K-major (bit 15 = 0), B MN-major (bit 16 = 1), N >> 3 at bit 17,
@@ -104,6 +105,35 @@ __device__ __forceinline__ void f8_store_chunk(int64_t row_off, int nb, const ui
 }
 
 
+// The same chunk for the other ranks of an N-sharded call: a warp holds 32 rows x 32 columns, one row
+// per lane.  Stored as they are, every 16-byte piece of a lane would cross NVLink as a request of
+// its own; staged through 4 KiB of shared memory (XOR-swizzled against bank conflicts) the warp
+// writes whole 128-byte row pieces, four rows per instruction.  Rows >= M are not written.
+__device__ __forceinline__ void w8_push_chunk(float4* stg, int lane, int row0, int nb, const uint32_t (&r)[32], float sa,
+                                              const W8Params& p) {
+#pragma unroll
+    for (int j4 = 0; j4 < 8; ++j4) {
+        const float4 bs = __ldg(reinterpret_cast<const float4*>(p.b_scales + nb + 4 * j4));
+        float4 v;
+        v.x = __fmul_rn(__fmul_rn(sa, bs.x), static_cast<float>(static_cast<int>(r[4 * j4])));
+        v.y = __fmul_rn(__fmul_rn(sa, bs.y), static_cast<float>(static_cast<int>(r[4 * j4 + 1])));
+        v.z = __fmul_rn(__fmul_rn(sa, bs.z), static_cast<float>(static_cast<int>(r[4 * j4 + 2])));
+        v.w = __fmul_rn(__fmul_rn(sa, bs.w), static_cast<float>(static_cast<int>(r[4 * j4 + 3])));
+        stg[lane * 8 + (j4 ^ (lane & 7))] = v;
+    }
+    __syncwarp();
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+        const int idx = it * 32 + lane, rr = idx >> 3, j4 = idx & 7;
+        const float4 v = stg[rr * 8 + (j4 ^ (rr & 7))];
+        if (row0 + rr < p.M) {
+            const int64_t off = static_cast<int64_t>(row0 + rr) * p.ldc + p.col0 + nb + 4 * j4;
+            for (int d = 1; d < p.n_dst; ++d) *reinterpret_cast<float4*>(p.dst[d] + off) = v;
+        }
+    }
+    __syncwarp();                                         // the tile is free for the next chunk
+}
+
 // One 32-column chunk of one output row: C = beta*C + ((alpha*a_s)*b_s[n])*float(acc),
 // multiplied in the reference's order with single roundings.
 __device__ __forceinline__ void w8_store_chunk(int64_t row_off, int nb, const uint32_t (&r)[32], float sa,
@@ -130,8 +160,6 @@ __device__ __forceinline__ void w8_store_chunk(int64_t row_off, int nb, const ui
                 }
             }
             *dst = v;
-            for (int d = 1; d < p.n_dst; ++d)              // the other ranks' copies (beta == 0 there)
-                *reinterpret_cast<float4*>(p.dst[d] + row_off + nb + j) = v;
         }
     } else {
 #pragma unroll
@@ -142,7 +170,6 @@ __device__ __forceinline__ void w8_store_chunk(int64_t row_off, int nb, const ui
                 if (p.beta == 1.0f) v = __fadd_rn(*dst, v);
                 else if (p.beta != 0.0f) v = __fadd_rn(__fmul_rn(*dst, p.beta), v);
                 *dst = v;
-                for (int d = 1; d < p.n_dst; ++d) p.dst[d][row_off + nb + j] = v;
             }
         }
     }
@@ -155,6 +182,7 @@ gemm_w8a8_tc_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant
     extern __shared__ uint8_t w8_smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(w8_smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + W8_STAGES * W8_STAGE_BYTES);
+    float4* stage_out = reinterpret_cast<float4*>(smem + W8_STAGES * W8_STAGE_BYTES + 256);
     // bars[0..3] full, [4..7] empty, [8..9] tmem_full, [10..11] tmem_empty
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -264,7 +292,10 @@ gemm_w8a8_tc_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant
                     ptx::mbar_arrive(tempty_bar(buf));
                 }
                 const int nb = n0 + c * 32;
-                if (!row_ok || nb >= p.N) continue;
+                if (nb >= p.N) continue;
+                if (!F8 && p.n_dst > 1 && nb + 32 <= p.N)      // warp-uniform: all 32 lanes take part
+                    w8_push_chunk(stage_out + q * 256, lane, row - lane, nb, r, sa, p);
+                if (!row_ok) continue;
                 if (F8) f8_store_chunk(crow, nb, r, p);
                 else w8_store_chunk(crow, nb, r, sa, p);
             }
@@ -294,7 +325,7 @@ constexpr int W8P_STAGES = 6;
 constexpr int W8P_A_BYTES = 128 * W8_BK;             // this CTA's 128 rows
 constexpr int W8P_B_BYTES = W8_BK * 128;             // this CTA's 128 columns
 constexpr int W8P_STAGE_BYTES = W8P_A_BYTES + W8P_B_BYTES;
-constexpr size_t W8P_SMEM = 1024 + static_cast<size_t>(W8P_STAGES) * W8P_STAGE_BYTES + 256;
+constexpr size_t W8P_SMEM = 1024 + static_cast<size_t>(W8P_STAGES) * W8P_STAGE_BYTES + 256 + W8_OUT_STAGE;
 constexpr uint32_t W8P_IDESC = (2u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
                                (static_cast<uint32_t>(256 >> 3) << 17) | (static_cast<uint32_t>(256 >> 4) << 24);
 
@@ -305,6 +336,7 @@ gemm_w8a8_tc_pair_kernel(const __grid_constant__ TensorMap tmA, const __grid_con
     extern __shared__ uint8_t w8_smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(w8_smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + W8P_STAGES * W8P_STAGE_BYTES);
+    float4* stage_out = reinterpret_cast<float4*>(smem + W8P_STAGES * W8P_STAGE_BYTES + 256);
     // bars[0..5] full, [6..11] empty, [12..13] tmem_full, [14..15] tmem_empty
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -409,7 +441,10 @@ gemm_w8a8_tc_pair_kernel(const __grid_constant__ TensorMap tmA, const __grid_con
                     ptx::mbar_arrive_cluster(leader_tempty);
                 }
                 const int nb = n0 + c * 32;
-                if (!row_ok || nb >= p.N) continue;
+                if (nb >= p.N) continue;
+                if (!F8 && p.n_dst > 1 && nb + 32 <= p.N)      // warp-uniform: all 32 lanes take part
+                    w8_push_chunk(stage_out + q * 256, lane, row - lane, nb, r, sa, p);
+                if (!row_ok) continue;
                 if (F8) f8_store_chunk(crow, nb, r, p);
                 else w8_store_chunk(crow, nb, r, sa, p);
             }
