@@ -790,7 +790,10 @@ def bench_w8a8_sharded(torch, lb, steps, warmup, rank, world, dist, M=8192, K=81
                                       "exposed_exchange_ms": (t_fused - t_gemm) * 1e3,
                                       "frac_of_roof": roof / t_fused,
                                       "roof": "max(local GEMM time, (g-1)/g * M*N*4 B / 770 GB/s measured peer-copy rate)",
-                                      "layout": "row-major [M, N] on every rank, no re-layout"}
+                                      "layout": "row-major [M, N] on every rank, no re-layout",
+                                      "peer_mapping": pg.mapping}
+    if pg.mapping_note:
+        out["gemm_with_epilogue_push"]["peer_mapping_note"] = pg.mapping_note[:300]
     out["TOPs"] = ops / min(t_fused, t_nccl) / 1e12
     out["ms_per_call"] = min(t_fused, t_nccl) * 1e3
     out["frac_of_2x_bf16_" + kind + "_per_gpu"] = ops / min(t_fused, t_nccl) / 1e12 / (2 * bf16_peak) / world

@@ -145,12 +145,15 @@ LHB_API int lhb_gemm_w8a8(lhb_ctx* ctx, const int8_t* A_q, const int8_t* B_q,
  * the base of rank r's full-width fp32 matrix [M, N_local * world] as mapped in THIS process
  * (entry `rank` this rank's own, the others peer memory: cudaIpc / lhb_peer_open).  The kernel's
  * epilogue stores every finished tile into columns [rank * N_local, (rank + 1) * N_local) of all
- * `world` matrices with plain stores while its main loop continues, so the transfer over NVLink
+ * `world` matrices (its own with plain stores, the peers' as TMA bulk stores of staged 32 x 32
+ * pieces; LHB_W8A8_PUSH=st in the environment selects plain stores there too) while its main loop
+ * continues, so the transfer over NVLink
  * overlaps the arithmetic tile by tile and every rank ends up with the row-major [M, N] result
  * without a gather or a re-layout.  beta is 0 (the slab is overwritten).  The stores of a rank are
  * complete when its stream has passed the call; a rank may read its matrix once every rank's
  * stream has (a stream-ordered collective, or a barrier after synchronising).  Only shapes of
- * lhb_gemm_w8a8_fast_path; others return LHB_ERR_UNSUPPORTED (run lhb_gemm_w8a8 and gather). */
+ * lhb_gemm_w8a8_fast_path with N_local a multiple of 32; others return LHB_ERR_UNSUPPORTED (run
+ * lhb_gemm_w8a8 and gather). */
 LHB_API int lhb_gemm_w8a8_sharded(lhb_ctx* ctx, const int8_t* A_q, const int8_t* B_q, const float* A_scales,
                                   const float* B_scales, void* const* full_C, int rank, int world, int M,
                                   int N_local, int K, float alpha, void* stream);
@@ -433,6 +436,19 @@ LHB_API int lhb_sched_max_blocks_per_req(const lhb_scheduler* s);
  * rank in `state` and returns; lhb_peer_status (synchronises `stream`) then gives LHB_ERR_TIMEOUT
  * and the data is not valid.  The launch can be captured in a CUDA graph. */
 LHB_API int lhb_peer_alloc(void** out, size_t bytes);
+/* The same service through the driver's virtual-memory-management calls, for buffers that kernels
+ * stream into (the matrices of lhb_gemm_w8a8_sharded): lhb_peer_alloc_shareable creates zero-filled
+ * device memory mapped with large pages, returns its address, the mapped size (`bytes` rounded up
+ * to the allocation granularity) and a POSIX file descriptor for it; pass the descriptor to the
+ * peer processes over a Unix socket (SCM_RIGHTS) and close it.  lhb_peer_open_fd maps a received
+ * descriptor for the calling thread's current device; lhb_peer_unmap undoes either mapping (the
+ * memory is freed when its owner and every peer have unmapped it and closed the descriptor).
+ * Stores into these mappings run at the NVLink rate where stores into lhb_peer_open mappings of
+ * several hundred megabytes did not (640 against 310 GB/s per GPU, four B200s).
+ * LHB_ERR_UNSUPPORTED when the driver lacks the calls. */
+LHB_API int lhb_peer_alloc_shareable(void** out, size_t bytes, int* fd_out, size_t* mapped_bytes);
+LHB_API int lhb_peer_open_fd(int fd, size_t mapped_bytes, void** out);
+LHB_API int lhb_peer_unmap(void* ptr, size_t mapped_bytes);
 LHB_API int lhb_peer_free(void* ptr);
 LHB_API int lhb_peer_export(void* ptr, unsigned char* handle64);
 LHB_API int lhb_peer_open(const unsigned char* handle64, void** out);

@@ -118,6 +118,9 @@ SIGNATURES = {
     "lhb_sched_max_blocks_per_req": (_i, [_vp]),
     "lhb_peer_alloc": (_i, [C.POINTER(_vp), C.c_size_t]),
     "lhb_peer_free": (_i, [_vp]),
+    "lhb_peer_alloc_shareable": (_i, [C.POINTER(_vp), C.c_size_t, C.POINTER(_i), C.POINTER(C.c_size_t)]),
+    "lhb_peer_open_fd": (_i, [_i, C.c_size_t, C.POINTER(_vp)]),
+    "lhb_peer_unmap": (_i, [_vp, C.c_size_t]),
     "lhb_peer_export": (_i, [_vp, _vp]),
     "lhb_peer_open": (_i, [_vp, C.POINTER(_vp)]),
     "lhb_peer_close": (_i, [_vp]),
@@ -155,6 +158,11 @@ class LhbError(RuntimeError):
         detail = lib.lhb_last_error().decode()
         super().__init__(f"{where}: {msg} ({status})" + (f": {detail}" if status == ERR_CUDA and detail else ""))
         self.status = status
+
+
+def last_error() -> str:
+    """Text of the last failed CUDA / driver call on this thread (empty when there was none)."""
+    return load().lhb_last_error().decode()
 
 
 def check(status: int, where: str) -> None:

@@ -21,7 +21,7 @@ LIB = os.path.join(PKG, "lib", "liblhb200.so")
 
 SOURCES = ["api.cu", "quant.cu", "gemm_generic.cu", "kvcache.cu", "paged_attention_generic.cu",
            "tensor_map.cu", "gemv_mma.cu", "gemm_w4a16_tc.cu", "gemm_w8a8_tc.cu", "paged_attention_decode.cu",
-           "cache_manager.cu", "glue.cu", "quant_asym.cu", "fp8.cu", "peer_gather.cu", "lh_dropin.cu"]
+           "cache_manager.cu", "glue.cu", "quant_asym.cu", "fp8.cu", "peer_gather.cu", "peer_vmm.cu", "lh_dropin.cu"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr",

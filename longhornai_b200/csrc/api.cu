@@ -194,7 +194,7 @@ int lhb_gemm_w8a8_sharded(lhb_ctx* ctx, const int8_t* Aq, const int8_t* Bq, cons
     for (int r = 0; r < world; ++r)
         if (!full_C[r]) return LHB_ERR_NULL;
     // only the tensor-core kernel pushes its tiles itself
-    if (!(w8a8_fast_ok(M, N_local, K) && aligned16(Aq) && aligned16(Bq) && aligned16(bs) && (N_local % 4) == 0))
+    if (!(w8a8_fast_ok(M, N_local, K) && aligned16(Aq) && aligned16(Bq) && aligned16(bs) && (N_local % 32) == 0))   // whole 32-column chunks reach the peers
         return LHB_ERR_UNSUPPORTED;
     float* dst[8];
     dst[0] = static_cast<float*>(full_C[rank]);              // this rank's own copy first (p.C)

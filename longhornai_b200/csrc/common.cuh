@@ -64,6 +64,22 @@ struct lhb_ctx {
 
 namespace lhb {
 
+// Tuning overrides from the environment (LHB_*), read once per process on first use; 0 / -1 = not set.
+struct Knobs {
+    bool pdl = true;             // LHB_PDL=0: no programmatic dependent launch
+    int w4tc_min_m = 17;         // LHB_W4TC_MIN_M: fewest rows that take the W4A16 tensor-core kernel
+    bool w4tc_stream_k = false;  // LHB_W4TC_SPLIT=1: even deal of units instead of whole CTAs per column tile
+    int w4tc_ctas = 0;           // LHB_W4TC_CTAS: cap on its grid
+    bool w8a8_pair = true;       // LHB_W8A8_PAIR=0: single-CTA W8A8 kernel for every M
+    bool w8a8_push_tma = true;   // LHB_W8A8_PUSH=st: sharded W8A8 pushes with plain stores instead of bulk stores
+    int gemv_ctas_per_sm = 0;    // LHB_GEMV_CTAS_PER_SM
+    int gemv_smem_kb = 0;        // LHB_GEMV_SMEM_KB
+    int decode_target = 0;       // LHB_DECODE_TARGET: CTAs per SM the split-KV plan aims at
+    int decode_pages = 0;        // LHB_DECODE_PAGES: pages per CTA
+    int decode_splits = 0;       // LHB_DECODE_SPLITS: cap on the KV splits
+};
+const Knobs& knobs();
+
 // ---------------------------------------------------------------------------
 // device helpers
 // ---------------------------------------------------------------------------

@@ -93,6 +93,9 @@ int get_tensor_map_2d_u8(lhb_ctx* ctx, const void* base, uint64_t rows, uint64_t
 // the same for an fp32 tensor (cols and box_cols in elements), no swizzle
 int get_tensor_map_2d_f32(lhb_ctx* ctx, const void* base, uint64_t rows, uint64_t cols,
                           uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols, TensorMap* out);
+// fp32 with the 128-byte swizzle (box_cols * 4 == 128): the target of bulk stores from swizzled staging tiles
+int get_tensor_map_2d_f32_sw128(lhb_ctx* ctx, const void* base, uint64_t rows, uint64_t cols,
+                                uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols, TensorMap* out);
 // and for an fp16 tensor
 int get_tensor_map_2d_f16(lhb_ctx* ctx, const void* base, uint64_t rows, uint64_t cols,
                           uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols, TensorMap* out);

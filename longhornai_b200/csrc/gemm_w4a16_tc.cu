@@ -666,18 +666,9 @@ bool w4a16_tc_ok(int M, int N, int K, int G) {
 }
 
 // programmatic dependent launch between the digit pass and the GEMMs; LHB_PDL=0 turns it off
-static bool tc_pdl() {
-    static const bool v = !(getenv("LHB_PDL") && atoi(getenv("LHB_PDL")) == 0);
-    return v;
-}
+static bool tc_pdl() { return knobs().pdl; }
 
-int w4a16_tc_min_rows() {
-    static const int v = [] {
-        const char* e = getenv("LHB_W4TC_MIN_M");
-        return e ? std::max(1, atoi(e)) : 17;
-    }();
-    return v;
-}
+int w4a16_tc_min_rows() { return knobs().w4tc_min_m; }
 
 template <int MP, bool PEER>
 static int launch_tc_slab(lhb_ctx* ctx, const TensorMap& tmW, const TensorMap& tmD, W4TcParams p, int ctas,
@@ -726,10 +717,9 @@ int launch_w4a16_tc(lhb_ctx* ctx, const float* A, const uint8_t* Bp, const float
     // that still occupies at least three quarters of the SMs; otherwise an even deal of the units.
     if (col_tiles <= ctas) {
         const int aligned = col_tiles * std::min(S, ctas / col_tiles);
-        static const bool stream_k = getenv("LHB_W4TC_SPLIT") && atoi(getenv("LHB_W4TC_SPLIT")) == 1;
-        if (!stream_k && 4 * aligned >= 3 * ctas) ctas = aligned;
+        if (!knobs().w4tc_stream_k && 4 * aligned >= 3 * ctas) ctas = aligned;
     }
-    if (const char* e = getenv("LHB_W4TC_CTAS")) ctas = std::max(1, std::min<int>(ctas, atoi(e)));
+    if (knobs().w4tc_ctas > 0) ctas = std::min(ctas, knobs().w4tc_ctas);
     const int r_min = std::max<int>(1, static_cast<int>(units / ctas));
     const int max_contrib = std::min(ctas, S / r_min + 2);
     const int64_t row_len = (prologue == TC_PRO_SWIGLU) ? 2 * static_cast<int64_t>(K) : K;

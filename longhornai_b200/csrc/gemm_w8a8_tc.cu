@@ -42,7 +42,9 @@ constexpr int W8_B_BYTES = W8_BK * W8_BN;            // 32 KiB, two 128-column b
 constexpr int W8_STAGE_BYTES = W8_A_BYTES + W8_B_BYTES;
 constexpr int W8_THREADS = 256;
 constexpr int W8_TMEM_COLS = 512;
-constexpr int W8_OUT_STAGE = 4 * 4096;               // per epilogue warp: a 32 x 32 fp32 chunk on its way to peer memory
+// per epilogue warp: two 32 x 32 fp32 chunks on their way to peer memory (one being filled while the
+// bulk stores of the other are still reading it); 1 KiB aligned for the 128-byte TMA swizzle
+constexpr int W8_OUT_STAGE = 4 * 2 * 4096;
 constexpr size_t W8_SMEM = 1024 + static_cast<size_t>(W8_STAGES) * W8_STAGE_BYTES + 256 + W8_OUT_STAGE;
 
 // instruction descriptor: D = s32 (bits 4-5 = 2), A = B = signed int8 (bits 7-9,
@@ -63,6 +65,7 @@ struct W8Params {
     // memory written with plain stores from the epilogue while the main loop runs on.
     float* dst[W8_MAX_DST];
     int n_dst;
+    int push_tma;          // 1: peer copies leave as TMA bulk stores (one per destination per chunk), 0: as plain stores
     int64_t ldc;
     int col0;
     int M, N, K;
@@ -70,6 +73,12 @@ struct W8Params {
     int tiles_m, tiles_n;
     int* status;
     float combined;        // fp8: alpha * A_scale * B_scale (a_scales / b_scales unused)
+};
+
+// Tensor maps of dst[1..] (fp32 [M, ldc], boxes of 32 rows x 32 columns, 128-byte swizzle) for the
+// bulk-store form of the peer push; unused by a plain call.
+struct W8DstMaps {
+    TensorMap m[W8_MAX_DST - 1];
 };
 
 // fp8 (E4M3 x E4M3 -> fp32): same tiles, barriers and shared-memory descriptors; the
@@ -105,6 +114,16 @@ __device__ __forceinline__ void f8_store_chunk(int64_t row_off, int nb, const ui
 }
 
 
+// Tile index -> (row block, column block).  Row blocks run fastest for a plain call (consecutive
+// CTAs share a weight tile in L2).  The N-sharded call runs column blocks fastest: its epilogues
+// store into every rank's matrix, and the tiles in flight then touch a band of rows - a few
+// hundred pages of each peer mapping - instead of every row of every matrix, which is more pages
+// than the translation caches for peer memory hold (measured: 9 ms instead of 1 ms on 4 GPUs).
+__device__ __forceinline__ void w8_tile_blocks(int tile, int tiles_m, int tiles_n, bool n_fastest, int& mb, int& nb) {
+    if (n_fastest) { mb = tile / tiles_n; nb = tile - mb * tiles_n; }
+    else { nb = tile / tiles_m; mb = tile - nb * tiles_m; }
+}
+
 // The same chunk for the other ranks of an N-sharded call: a warp holds 32 rows x 32 columns, one row
 // per lane.  Stored as they are, every 16-byte piece of a lane would cross NVLink as a request of
 // its own; staged through 4 KiB of shared memory (XOR-swizzled against bank conflicts) the warp
@@ -132,6 +151,36 @@ __device__ __forceinline__ void w8_push_chunk(float4* stg, int lane, int row0, i
         }
     }
     __syncwarp();                                         // the tile is free for the next chunk
+}
+
+// The bulk-store form of the same push: the staged chunk (the XOR pattern above is exactly the TMA
+// 128-byte swizzle) leaves as one cp.async.bulk.tensor store per destination, issued by lane 0.  The
+// copy engine of the SM then feeds NVLink with whole rows of the box and the warp goes back to the
+// accumulator at once; `use` alternates between the warp's two staging tiles, and a tile is refilled
+// only after the stores issued from it two chunks earlier have read it.  Rows >= M are clipped by
+// the tensor map.
+__device__ __forceinline__ void w8_push_chunk_tma(float4* stg2, int use, int lane, int row0, int nb, const uint32_t (&r)[32],
+                                                  float sa, const W8Params& p, const W8DstMaps& maps) {
+    float4* stg = stg2 + (use & 1) * 256;
+    if (lane == 0) ptx::bulk_wait_group_read<1>();
+    __syncwarp();
+#pragma unroll
+    for (int j4 = 0; j4 < 8; ++j4) {
+        const float4 bs = __ldg(reinterpret_cast<const float4*>(p.b_scales + nb + 4 * j4));
+        float4 v;
+        v.x = __fmul_rn(__fmul_rn(sa, bs.x), static_cast<float>(static_cast<int>(r[4 * j4])));
+        v.y = __fmul_rn(__fmul_rn(sa, bs.y), static_cast<float>(static_cast<int>(r[4 * j4 + 1])));
+        v.z = __fmul_rn(__fmul_rn(sa, bs.z), static_cast<float>(static_cast<int>(r[4 * j4 + 2])));
+        v.w = __fmul_rn(__fmul_rn(sa, bs.w), static_cast<float>(static_cast<int>(r[4 * j4 + 3])));
+        stg[lane * 8 + (j4 ^ (lane & 7))] = v;
+    }
+    ptx::fence_proxy_async_shared();                      // the bulk copy reads what this thread just wrote
+    __syncwarp();
+    if (lane == 0 && row0 < p.M) {
+        const uint32_t src = ptx::smem_u32(stg);
+        for (int d = 1; d < p.n_dst; ++d) ptx::tma_store_2d(&maps.m[d - 1], src, p.col0 + nb, row0);
+    }
+    if (lane == 0) ptx::bulk_commit_group();
 }
 
 // One 32-column chunk of one output row: C = beta*C + ((alpha*a_s)*b_s[n])*float(acc),
@@ -178,11 +227,11 @@ __device__ __forceinline__ void w8_store_chunk(int64_t row_off, int nb, const ui
 template <bool F8>
 __global__ void __launch_bounds__(W8_THREADS, 1)
 gemm_w8a8_tc_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ TensorMap tmB,
-                    const W8Params p) {
+                    const W8Params p, const __grid_constant__ W8DstMaps dmaps) {
     extern __shared__ uint8_t w8_smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(w8_smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + W8_STAGES * W8_STAGE_BYTES);
-    float4* stage_out = reinterpret_cast<float4*>(smem + W8_STAGES * W8_STAGE_BYTES + 256);
+    float4* stage_out = reinterpret_cast<float4*>(smem + W8_STAGES * W8_STAGE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + W8_STAGES * W8_STAGE_BYTES + W8_OUT_STAGE);
     // bars[0..3] full, [4..7] empty, [8..9] tmem_full, [10..11] tmem_empty
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -218,7 +267,9 @@ gemm_w8a8_tc_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant
         if (lane == 0) {
             int it = 0;
             for (int tile = blockIdx.x; tile < n_tiles && !*abort_flag; tile += gridDim.x) {
-                const int m0 = (tile % p.tiles_m) * W8_BM, n0 = (tile / p.tiles_m) * W8_BN;
+                int mb_, nb_;
+                w8_tile_blocks(tile, p.tiles_m, p.tiles_n, p.n_dst > 1, mb_, nb_);
+                const int m0 = mb_ * W8_BM, n0 = nb_ * W8_BN;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % W8_STAGES;
                     if (!ptx::mbar_wait(empty_bar(s), ((it / W8_STAGES) & 1) ^ 1, abort_flag, p.status)) break;
@@ -273,9 +324,12 @@ gemm_w8a8_tc_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant
     } else if (warp >= 4) {
         const int q = warp - 4;                            // TMEM lane quarter this warp may read
         int ti = 0;
+        int n_push = 0;
         for (int tile = blockIdx.x; tile < n_tiles && !*abort_flag; tile += gridDim.x, ++ti) {
             const int buf = ti & 1;
-            const int m0 = (tile % p.tiles_m) * W8_BM, n0 = (tile / p.tiles_m) * W8_BN;
+            int mb_, nb_;
+            w8_tile_blocks(tile, p.tiles_m, p.tiles_n, p.n_dst > 1, mb_, nb_);
+            const int m0 = mb_ * W8_BM, n0 = nb_ * W8_BN;
             if (!ptx::mbar_wait(tfull_bar(buf), (ti >> 1) & 1, abort_flag, p.status)) break;
             ptx::tc_fence_after();
             const int row = m0 + 32 * q + lane;
@@ -293,13 +347,16 @@ gemm_w8a8_tc_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant
                 }
                 const int nb = n0 + c * 32;
                 if (nb >= p.N) continue;
-                if (!F8 && p.n_dst > 1 && nb + 32 <= p.N)      // warp-uniform: all 32 lanes take part
-                    w8_push_chunk(stage_out + q * 256, lane, row - lane, nb, r, sa, p);
+                if (!F8 && p.n_dst > 1 && nb + 32 <= p.N) {    // warp-uniform: all 32 lanes take part
+                    if (p.push_tma) w8_push_chunk_tma(stage_out + q * 512, n_push++, lane, row - lane, nb, r, sa, p, dmaps);
+                    else w8_push_chunk(stage_out + q * 512, lane, row - lane, nb, r, sa, p);
+                }
                 if (!row_ok) continue;
                 if (F8) f8_store_chunk(crow, nb, r, p);
                 else w8_store_chunk(crow, nb, r, sa, p);
             }
         }
+        if (lane == 0) ptx::bulk_wait_group<0>();          // this warp's bulk stores have left shared memory and landed
     }
 
     ptx::tc_fence_before();
@@ -332,11 +389,11 @@ constexpr uint32_t W8P_IDESC = (2u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
 template <bool F8>
 __global__ void __launch_bounds__(W8_THREADS, 1)
 gemm_w8a8_tc_pair_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ TensorMap tmB,
-                         const W8Params p) {
+                         const W8Params p, const __grid_constant__ W8DstMaps dmaps) {
     extern __shared__ uint8_t w8_smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(w8_smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + W8P_STAGES * W8P_STAGE_BYTES);
-    float4* stage_out = reinterpret_cast<float4*>(smem + W8P_STAGES * W8P_STAGE_BYTES + 256);
+    float4* stage_out = reinterpret_cast<float4*>(smem + W8P_STAGES * W8P_STAGE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + W8P_STAGES * W8P_STAGE_BYTES + W8_OUT_STAGE);
     // bars[0..5] full, [6..11] empty, [12..13] tmem_full, [14..15] tmem_empty
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -376,7 +433,9 @@ gemm_w8a8_tc_pair_kernel(const __grid_constant__ TensorMap tmA, const __grid_con
         if (lane == 0) {
             int it = 0;
             for (int tile = pair; tile < n_tiles && !*abort_flag; tile += n_pairs) {
-                const int m0 = (tile % tiles_m) * 256 + 128 * rank, n0 = (tile / tiles_m) * W8_BN + 128 * rank;
+                int mb_, nb_;
+                w8_tile_blocks(tile, tiles_m, p.tiles_n, p.n_dst > 1, mb_, nb_);
+                const int m0 = mb_ * 256 + 128 * rank, n0 = nb_ * W8_BN + 128 * rank;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % W8P_STAGES;
                     if (!ptx::mbar_wait(empty_bar(s), ((it / W8P_STAGES) & 1) ^ 1, abort_flag, p.status)) break;
@@ -420,10 +479,12 @@ gemm_w8a8_tc_pair_kernel(const __grid_constant__ TensorMap tmA, const __grid_con
         }
     } else if (warp >= 4) {
         const int q = warp - 4;
-        int ti = 0;
+        int ti = 0, n_push = 0;
         for (int tile = pair; tile < n_tiles && !*abort_flag; tile += n_pairs, ++ti) {
             const int buf = ti & 1;
-            const int m0 = (tile % tiles_m) * 256 + 128 * rank, n0 = (tile / tiles_m) * W8_BN;
+            int mb_, nb_;
+            w8_tile_blocks(tile, tiles_m, p.tiles_n, p.n_dst > 1, mb_, nb_);
+            const int m0 = mb_ * 256 + 128 * rank, n0 = nb_ * W8_BN;
             if (!ptx::mbar_wait(tfull_bar(buf), (ti >> 1) & 1, abort_flag, p.status)) break;
             ptx::tc_fence_after();
             const int row = m0 + 32 * q + lane;
@@ -442,13 +503,16 @@ gemm_w8a8_tc_pair_kernel(const __grid_constant__ TensorMap tmA, const __grid_con
                 }
                 const int nb = n0 + c * 32;
                 if (nb >= p.N) continue;
-                if (!F8 && p.n_dst > 1 && nb + 32 <= p.N)      // warp-uniform: all 32 lanes take part
-                    w8_push_chunk(stage_out + q * 256, lane, row - lane, nb, r, sa, p);
+                if (!F8 && p.n_dst > 1 && nb + 32 <= p.N) {    // warp-uniform: all 32 lanes take part
+                    if (p.push_tma) w8_push_chunk_tma(stage_out + q * 512, n_push++, lane, row - lane, nb, r, sa, p, dmaps);
+                    else w8_push_chunk(stage_out + q * 512, lane, row - lane, nb, r, sa, p);
+                }
                 if (!row_ok) continue;
                 if (F8) f8_store_chunk(crow, nb, r, p);
                 else w8_store_chunk(crow, nb, r, sa, p);
             }
         }
+        if (lane == 0) ptx::bulk_wait_group<0>();          // this warp's bulk stores have left shared memory and landed
     }
 
     ptx::tc_fence_before();
@@ -483,10 +547,19 @@ static int launch_tc(lhb_ctx* ctx, const void* Aq, const void* Bq, W8Params p, c
     if (p.n_dst == 0) {                                      // a plain call: one row-major [M, N] result
         p.n_dst = 1; p.dst[0] = p.C; p.ldc = N; p.col0 = 0;
     }
-    static const int use_pair = [] {                         // LHB_W8A8_PAIR=0 forces the single-CTA kernel
-        const char* e = getenv("LHB_W8A8_PAIR");
-        return e ? atoi(e) : 1;
-    }();
+    static W8DstMaps no_maps = {};
+    W8DstMaps pushed;
+    const W8DstMaps* dmaps = &no_maps;
+    if (p.n_dst > 1) {
+        p.push_tma = knobs().w8a8_push_tma ? 1 : 0;
+        if (p.push_tma) {
+            for (int d = 1; d < p.n_dst; ++d)
+                if (int e = get_tensor_map_2d_f32_sw128(ctx, p.dst[d], M, p.ldc, p.ldc * 4, 32, 32, &pushed.m[d - 1])) return e;
+            for (int d = p.n_dst; d < W8_MAX_DST; ++d) pushed.m[d - 1] = pushed.m[0];
+            dmaps = &pushed;
+        }
+    }
+    const bool use_pair = knobs().w8a8_pair;
     // a caller that overlaps its own communication kernels keeps some SMs out of the persistent grid
     const int sms = ctx->sm_limit > 0 ? std::min(ctx->sm_count, ctx->sm_limit) : ctx->sm_count;
     if (use_pair && M >= 256) {
@@ -503,11 +576,11 @@ static int launch_tc(lhb_ctx* ctx, const void* Aq, const void* Bq, W8Params p, c
         attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        LHB_CUDA(cudaLaunchKernelEx(&cfg, gemm_w8a8_tc_pair_kernel<F8>, tmA, tmB, p));
+        LHB_CUDA(cudaLaunchKernelEx(&cfg, gemm_w8a8_tc_pair_kernel<F8>, tmA, tmB, p, *dmaps));
         return LHB_OK;
     }
     const int grid = std::min(sms, p.tiles_m * p.tiles_n);
-    gemm_w8a8_tc_kernel<F8><<<grid, W8_THREADS, W8_SMEM, st>>>(tmA, tmB, p);
+    gemm_w8a8_tc_kernel<F8><<<grid, W8_THREADS, W8_SMEM, st>>>(tmA, tmB, p, *dmaps);
     LHB_LAUNCH_CHECK();
     return LHB_OK;
 }

@@ -893,13 +893,13 @@ static GemvPlan plan_gemv(int wbits, int jb, int N, int K, int G, int sm_count, 
     pl.srows = wbits == 4 ? (G < 128 ? 128 / G : 1) : 0;
     pl.flush_mask = wbits == 4 ? (G == 32 ? 0xF : (G == 64 ? 0xA : 0x8)) : 0;
     int per_sm = jb >= 6 ? 1 : 2;                          // what the kernel's launch bounds allow
-    if (const char* e = getenv("LHB_GEMV_CTAS_PER_SM")) per_sm = std::max(1, std::min(per_sm, atoi(e)));
+    if (knobs().gemv_ctas_per_sm > 0) per_sm = std::min(per_sm, knobs().gemv_ctas_per_sm);
     const size_t nj = 8 * jb;
     const size_t stage_bytes = GV_STAGE_BYTES + static_cast<size_t>(pl.srows) * GV_COLS * 4;
     const size_t fixed = 1024 + nj * GV_COLS * 4 + 16 * 4 + 16 * 4 + (2 * GV_MAX_STAGE + 2) * 8 + 16;
     const size_t dig_per_stage = static_cast<size_t>(kps) * nj + (asym ? nj * 4 : 0);   // digits (+ their sums)
     size_t budget = per_sm == 1 ? 227 * 1024 : (228 * 1024) / per_sm - 1024 - 512;
-    if (const char* e = getenv("LHB_GEMV_SMEM_KB")) budget = std::min<size_t>(budget, static_cast<size_t>(atoi(e)) * 1024);
+    if (knobs().gemv_smem_kb > 0) budget = std::min<size_t>(budget, static_cast<size_t>(knobs().gemv_smem_kb) * 1024);
     int ctas = static_cast<int>(std::min<int64_t>(units, static_cast<int64_t>(per_sm) * sm_count));
     // with fewer column tiles than CTAs, a whole number of CTAs per tile: no CTA then
     // straddles two tiles and pays for two hand-offs
@@ -973,7 +973,7 @@ static int launch_gemv_t(lhb_ctx* ctx, const TensorMap& tm, const TensorMap& tms
     cfg.blockDim = dim3(gv_threads(JB), 1, 1);
     cfg.dynamicSmemBytes = pl.smem;
     cfg.stream = st;
-    static const bool pdl = !(getenv("LHB_PDL") && atoi(getenv("LHB_PDL")) == 0);
+    const bool pdl = knobs().pdl;
     cudaLaunchAttribute attr[1];
     int na = 0;
     if (pdl) {

@@ -550,12 +550,12 @@ paged_decode_q8_kernel(const DecodeParams p) {
 static void decode_split_plan(int sm_count, int64_t items, int max_blocks, size_t part_floats_avail, int group,
                               int* splits, int* pages) {
     int target = 4;                                          // CTAs per SM if every request were as long as the table
-    if (const char* e = getenv("LHB_DECODE_TARGET")) target = std::max(1, atoi(e));
+    if (knobs().decode_target > 0) target = knobs().decode_target;
     int64_t pp = items * max_blocks / (static_cast<int64_t>(target) * std::max(1, sm_count));
     int pg = static_cast<int>(std::max<int64_t>(16, std::min<int64_t>(128, pp)));
-    if (const char* e = getenv("LHB_DECODE_PAGES")) pg = std::max(1, atoi(e));
+    if (knobs().decode_pages > 0) pg = knobs().decode_pages;
     int sp = std::max(1, std::min(32, ceil_div(max_blocks, pg)));
-    if (const char* e = getenv("LHB_DECODE_SPLITS")) sp = std::max(1, std::min(sp, atoi(e)));
+    if (knobs().decode_splits > 0) sp = std::min(sp, knobs().decode_splits);
     const size_t per_split = static_cast<size_t>(items) * group * PD_PART;
     if (sp > 1 && per_split * sp > part_floats_avail)
         sp = static_cast<int>(std::max<size_t>(1, part_floats_avail / per_split));

@@ -4,6 +4,8 @@
 // driver (where every compute call reports LHB_ERR_CUDA).
 #include <cuda.h>
 
+#include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 
@@ -82,10 +84,42 @@ int get_tensor_map_2d_f32(lhb_ctx* ctx, const void* base, uint64_t rows, uint64_
                              box_cols, false, out);
 }
 
+int get_tensor_map_2d_f32_sw128(lhb_ctx* ctx, const void* base, uint64_t rows, uint64_t cols,
+                                uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols, TensorMap* out) {
+    return get_tensor_map_2d(ctx, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, base, rows, cols, pitch_bytes, box_rows,
+                             box_cols, true, out);
+}
+
 int get_tensor_map_2d_f16(lhb_ctx* ctx, const void* base, uint64_t rows, uint64_t cols,
                           uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols, TensorMap* out) {
     return get_tensor_map_2d(ctx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, base, rows, cols, pitch_bytes, box_rows,
                              box_cols, false, out);
 }
 
+}  // namespace lhb
+
+namespace lhb {
+const Knobs& knobs() {
+    static const Knobs k = [] {
+        Knobs v;
+        auto num = [](const char* name, int unset) {
+            const char* e = getenv(name);
+            return e ? atoi(e) : unset;
+        };
+        v.pdl = num("LHB_PDL", 1) != 0;
+        v.w4tc_min_m = std::max(1, num("LHB_W4TC_MIN_M", 17));
+        v.w4tc_stream_k = num("LHB_W4TC_SPLIT", 0) == 1;
+        v.w4tc_ctas = std::max(0, num("LHB_W4TC_CTAS", 0));
+        v.w8a8_pair = num("LHB_W8A8_PAIR", 1) != 0;
+        const char* push = getenv("LHB_W8A8_PUSH");
+        v.w8a8_push_tma = !(push && push[0] == 's');
+        v.gemv_ctas_per_sm = std::max(0, num("LHB_GEMV_CTAS_PER_SM", 0));
+        v.gemv_smem_kb = std::max(0, num("LHB_GEMV_SMEM_KB", 0));
+        v.decode_target = std::max(0, num("LHB_DECODE_TARGET", 0));
+        v.decode_pages = std::max(0, num("LHB_DECODE_PAGES", 0));
+        v.decode_splits = std::max(0, num("LHB_DECODE_SPLITS", 0));
+        return v;
+    }();
+    return k;
+}
 }  // namespace lhb

@@ -1,7 +1,9 @@
 """Peer-memory buffers and the push all-gather of the tensor-parallel decode step
-(csrc/peer_gather.cu).  One process per GPU on one machine; `torch.distributed` is used once, at
-set-up, to pass the buffers' 64-byte handles around - the exchange itself is one kernel launch per
-rank that stores into the peers' memory over NVLink and waits (bounded) for their stores.
+(csrc/peer_gather.cu, csrc/peer_vmm.cu).  One process per GPU on one machine; `torch.distributed` is
+used once, at set-up, to agree on how the buffers are shared - file descriptors of driver-managed
+allocations sent over Unix sockets (mapped with large pages everywhere, which kernels that stream
+into several peers need), else 64-byte cudaIpc handles - the exchange itself is one kernel launch
+per rank that stores into the peers' memory over NVLink and waits (bounded) for their stores.
 
 The reference has no multi-device path (src/runtime/scheduler.hpp:47 drives one model on one
 device); this file serves only this library's sharded step.
@@ -13,6 +15,37 @@ import ctypes as C
 import torch
 
 from . import _cabi
+
+
+def _use_vmm() -> bool:
+    """LHB_PEER_VMM=0 keeps every buffer on the 64-byte-handle mappings."""
+    import os
+    return os.environ.get("LHB_PEER_VMM", "1") != "0"
+
+
+def pass_descriptors(sock, fd: int, rank: int, addresses: list) -> dict:
+    """Sends file descriptor `fd` to every other rank's datagram socket (`addresses[p]`, this rank's
+    own being the bound `sock`) and receives theirs: {rank: descriptor}.  One SCM_RIGHTS datagram per
+    pair and direction, the sender's rank as payload; nothing blocks on a peer being ready because
+    datagrams queue at the receiver."""
+    import array
+    import socket
+    import struct
+
+    for p, addr in enumerate(addresses):
+        if p != rank:
+            sock.sendmsg([struct.pack("i", rank)], [(socket.SOL_SOCKET, socket.SCM_RIGHTS, array.array("i", [fd]))], 0, addr)
+    got = {}
+    while len(got) < len(addresses) - 1:
+        msg, anc, _, _ = sock.recvmsg(16, socket.CMSG_SPACE(array.array("i").itemsize))
+        fds = array.array("i")
+        for level, kind, data in anc:
+            if level == socket.SOL_SOCKET and kind == socket.SCM_RIGHTS:
+                fds.frombytes(data[:len(data) - len(data) % fds.itemsize])
+        if len(msg) != 4 or len(fds) != 1:
+            raise OSError("a descriptor datagram arrived without its descriptor")
+        got[struct.unpack("i", msg)[0]] = fds[0]
+    return got
 
 
 class _DeviceView:
@@ -41,32 +74,13 @@ class PeerGather:
             self._offsets[name] = (off, rows, cols)
             off += (rows * cols * 4 + 255) // 256 * 256
         self.n_bytes = off
-        base = C.c_void_p()
-        _cabi.check(self.lib.lhb_peer_alloc(C.byref(base), off), "lhb_peer_alloc")
-        self.base = base.value
-        handle = (C.c_ubyte * 64)()
-        _cabi.check(self.lib.lhb_peer_export(self.base, handle), "lhb_peer_export")
-        handles = [bytes(handle)] * world
-        if world > 1:
-            dist.all_gather_object(handles, bytes(handle))
-        self._mapped = []
-        bases = []
-        try:
-            for p in range(world):
-                if p == rank:
-                    bases.append(self.base)
-                    continue
-                ptr = C.c_void_p()
-                raw = (C.c_ubyte * 64).from_buffer_copy(handles[p])
-                _cabi.check(self.lib.lhb_peer_open(raw, C.byref(ptr)), "lhb_peer_open")
-                self._mapped.append(ptr.value)
-                bases.append(ptr.value)
-        except Exception:
-            for ptr in self._mapped:                       # leave nothing mapped or allocated behind
-                self.lib.lhb_peer_close(ptr)
-            self.lib.lhb_peer_free(self.base)
-            self.base = None
-            raise
+        self._mapped = []                                  # (address, mapped bytes or None) of the peers' buffers here
+        self.base, self._own_bytes = None, None
+        self.mapping_note = ""                             # why the large-page mappings were not used, if they were not
+        bases = self._map_shareable(dist) if world > 1 and _use_vmm() else None
+        self.mapping = "vmm" if bases is not None else "cudaIpc"
+        if bases is None:
+            bases = self._map_handles(dist)
         self._bases = list(bases)                          # host copy: rank -> base of that rank's allocation here
         self._keep = _DeviceView(self.base, off)
         self._bytes = torch.as_tensor(self._keep, device=self.device)
@@ -78,6 +92,104 @@ class PeerGather:
         torch.cuda.synchronize(self.device)
         if world > 1:
             dist.barrier()                                 # every rank has mapped every buffer
+
+    def _map_handles(self, dist) -> list:
+        """This rank's buffer from cudaMalloc, the peers' through their 64-byte handles."""
+        rank, world = self.rank, self.world
+        base = C.c_void_p()
+        _cabi.check(self.lib.lhb_peer_alloc(C.byref(base), self.n_bytes), "lhb_peer_alloc")
+        self.base, self._own_bytes = base.value, None
+        handle = (C.c_ubyte * 64)()
+        _cabi.check(self.lib.lhb_peer_export(self.base, handle), "lhb_peer_export")
+        handles = [bytes(handle)] * world
+        if world > 1:
+            dist.all_gather_object(handles, bytes(handle))
+        bases = []
+        try:
+            for p in range(world):
+                if p == rank:
+                    bases.append(self.base)
+                    continue
+                ptr = C.c_void_p()
+                raw = (C.c_ubyte * 64).from_buffer_copy(handles[p])
+                _cabi.check(self.lib.lhb_peer_open(raw, C.byref(ptr)), "lhb_peer_open")
+                self._mapped.append((ptr.value, None))
+                bases.append(ptr.value)
+        except Exception:
+            self._release()                                # leave nothing mapped or allocated behind
+            raise
+        return bases
+
+    def _map_shareable(self, dist):
+        """This rank's buffer from the virtual-memory-management calls, mapped with large pages in every
+        process: the file descriptors travel over Unix datagram sockets in the abstract namespace (one
+        datagram from every rank to every other).  Returns None - with nothing left mapped, on every rank
+        alike - when some rank could not do it; the caller then uses the 64-byte handles."""
+        import os
+        import socket
+
+        rank, world = self.rank, self.world
+        base, fd, mapped = C.c_void_p(), C.c_int(-1), C.c_size_t(0)
+        rc = self.lib.lhb_peer_alloc_shareable(C.byref(base), self.n_bytes, C.byref(fd), C.byref(mapped))
+        sock, addr = None, None
+        why = "" if rc == _cabi.OK else f"rank {rank}: lhb_peer_alloc_shareable: {_cabi.last_error()}"
+        if rc == _cabi.OK:
+            try:
+                sock = socket.socket(socket.AF_UNIX, socket.SOCK_DGRAM)
+                addr = f"\0lhb-peer-{os.getpid()}-{rank}-{id(self):x}"
+                sock.bind(addr)
+                sock.settimeout(60.0)
+            except OSError as e:
+                rc, why = _cabi.ERR_UNSUPPORTED, f"rank {rank}: Unix socket: {e}"
+        mine = (rc, addr, int(mapped.value), why)
+        everyone = [mine] * world
+        dist.all_gather_object(everyone, mine)
+        got, ok = {}, all(e[0] == _cabi.OK for e in everyone)
+        if ok:
+            self.base, self._own_bytes = base.value, int(mapped.value)
+            try:
+                got = pass_descriptors(sock, fd.value, rank, [e[1] for e in everyone])
+            except OSError as e:
+                ok, why = False, f"rank {rank}: passing descriptors: {e}"
+        bases = []
+        if ok:
+            for p in range(world):
+                if p == rank:
+                    bases.append(self.base)
+                    continue
+                ptr = C.c_void_p()
+                if self.lib.lhb_peer_open_fd(got[p], everyone[p][2], C.byref(ptr)) != _cabi.OK:
+                    ok, why = False, f"rank {rank}: lhb_peer_open_fd: {_cabi.last_error()}"
+                    break
+                self._mapped.append((ptr.value, everyone[p][2]))
+                bases.append(ptr.value)
+        for f in list(got.values()) + ([fd.value] if fd.value >= 0 else []):
+            os.close(f)                                    # the mappings keep the memory; the descriptors are done
+        if sock is not None:
+            sock.close()
+        flags = [(ok, why)] * world
+        dist.all_gather_object(flags, (ok, why))
+        if all(f[0] for f in flags):
+            return bases
+        self.mapping_note = "; ".join(w for _, w in flags if w) or "; ".join(e[3] for e in everyone if e[3])
+        if self.base is None and rc == _cabi.OK:
+            self.base, self._own_bytes = base.value, int(mapped.value)
+        self._release()
+        return None
+
+    def _release(self) -> None:
+        for ptr, n in self._mapped:
+            if n is None:
+                self.lib.lhb_peer_close(ptr)
+            else:
+                self.lib.lhb_peer_unmap(ptr, n)
+        self._mapped = []
+        if self.base is not None:
+            if self._own_bytes is None:
+                self.lib.lhb_peer_free(self.base)
+            else:
+                self.lib.lhb_peer_unmap(self.base, self._own_bytes)
+        self.base = None
 
     def tensor(self, name: str) -> torch.Tensor:
         """This rank's copy of matrix `name` (a view of the peer-visible allocation)."""
@@ -153,11 +265,10 @@ class PeerGather:
         torch.cuda.synchronize(self.device)
         if dist is not None:
             dist.barrier()
-        for ptr in self._mapped:
-            self.lib.lhb_peer_close(ptr)
-        self._mapped = []
+        mine, self.base = self.base, None
+        self._release()                                    # the peers' buffers first
+        self.base = mine
         if dist is not None:
             dist.barrier()
         self._bytes = None
-        self.lib.lhb_peer_free(self.base)
-        self.base = None
+        self._release()

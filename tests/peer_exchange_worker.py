@@ -5,7 +5,9 @@ test_gpu_peer_exchange.py with torch.distributed.run, one process per GPU.
     rank's copy must equal the concatenation of all ranks' slabs;
 (b) the sharded decode step with the push all-gather against the same step with library
     all-gathers and against the single-rank step: residual stream and KV pools bit-identical,
-    eager and replayed from a CUDA graph.
+    eager and replayed from a CUDA graph;
+(c) the N-sharded W8A8 GEMM whose epilogue stores its tiles into every rank's matrix: each rank's
+    copy bit-identical to the unsharded product computed locally.
 Prints PEER_EXCHANGE_OK on rank 0 when every rank passed."""
 import os
 import sys
@@ -128,6 +130,31 @@ def sharded_step(rank, world, n_req=5):
     pg.close(dist)
 
 
+def w8a8_sharded(rank, world):
+    M, K, n_local = 640, 1024, 512                  # M ends inside a tile
+    N = n_local * world
+    g = torch.Generator(device="cuda").manual_seed(77)      # every rank draws the same operands
+    Aq, a_s = lb.q8_quantize_per_row(torch.randn(M, K, device="cuda", generator=g))
+    Bq, b_s = lb.q8_quantize_per_col(torch.randn(K, N, device="cuda", generator=g) * 0.02)
+    want = lb.gemm_w8a8(Aq, Bq, a_s, b_s, alpha=0.75)
+    pg = peer.PeerGather({"c": (M, N), "d": (M, N)}, rank, world, dist)
+    if rank == 0:
+        print(f"PEER_MAPPING {pg.mapping}", flush=True)
+    lo = rank * n_local
+    Bl, bl = Bq[:, lo:lo + n_local].contiguous(), b_s[lo:lo + n_local].contiguous()
+    for call in range(6):
+        name = "cd"[call % 2]
+        pg.tensor(name).fill_(-3.0)
+        torch.cuda.synchronize()
+        dist.barrier()                              # nobody's fill lands on top of a peer's tiles
+        out = pg.gemm_w8a8_sharded(Aq, Bl, a_s, bl, name, alpha=0.75)
+        torch.cuda.synchronize()
+        dist.barrier()                              # every rank's stores are complete
+        assert torch.equal(out, want), f"rank {rank}: sharded W8A8 call {call} differs from the unsharded product"
+    assert lb.default_context().poll() == 0
+    pg.close(dist)
+
+
 def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -135,6 +162,7 @@ def main():
     exchange_alone(rank, world)
     sharded_step(rank, world)
     sharded_step(rank, world, n_req=40)
+    w8a8_sharded(rank, world)
     ok = torch.ones(1, device="cuda")
     dist.all_reduce(ok)
     if rank == 0 and int(ok.item()) == world:

@@ -5,6 +5,7 @@
 Integer outputs and scales must be bit-identical; fp32 outputs must satisfy
 |x - y| <= 1e-4 + 1e-3 |y| (the library tolerance)."""
 import ctypes as C
+import os
 
 import numpy as np
 import pytest
@@ -12,7 +13,7 @@ import torch
 
 import golden_io as gio
 import longhornai_b200 as lb
-from cpu_checker import AttnCfg, Layout, PagedPools, best_checker
+from cpu_checker import AttnCfg, Checker, Layout, PagedPools, best_checker
 from gpu_util import assert_close, assert_same_bits, dev, host, lb_cfg, lb_layout
 
 pytestmark = pytest.mark.gpu
@@ -116,25 +117,94 @@ def test_w8a8_bit_exact_against_checker(chk, lib, M, N, K):
     poll_ok()
 
 
-@pytest.mark.parametrize("M,N,K", [(256, 256, 256), (300, 1040, 768), (1024, 2048, 1024), (2048, 4096 + 16, 4096)])
-def test_w8a8_cta_pair_path_bit_exact(chk, lib, monkeypatch, M, N, K):
-    """The CTA-pair kernel (two CTAs share a 256 x 256 tile, used for M >= 256) gives the same bits
-    as the single-CTA kernel and as the reference arithmetic."""
+@pytest.mark.parametrize("M,N,K", [(256, 256, 256), (1024, 2048, 1024), (2048, 4096 + 16, 4096)])
+def test_w8a8_cta_pair_path_bit_exact(lib, M, N, K):
+    """The CTA-pair kernel (two CTAs share a 256 x 256 tile, used for M >= 256) against the reference
+    arithmetic at sizes with many tiles per CTA pair, a ragged last column tile and alpha / beta."""
+    port = Checker("lho")
+    port.set_threads(len(os.sched_getaffinity(0)))
     rng = np.random.default_rng(7 * M + N + K)
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    W = (rng.standard_normal((K, N)) * 0.02).astype(np.float32)
+    Aq, a_s = port.q8_quantize_per_row(A)
+    Bq, b_s = port.q8_quantize_per_col(W)
+    C0 = rng.standard_normal((M, N)).astype(np.float32)
+    assert lib.lhb_gemm_w8a8_fast_path(M, N, K) == 1
+    got = host(lb.gemm_w8a8(dev(Aq), dev(Bq), dev(a_s), dev(b_s), C=dev(C0), alpha=0.5, beta=2.0))
+    poll_ok()
+    # the reference's result is C = beta*C0 + (alpha*a_s*b_s)*acc with single roundings: rebuild it from
+    # the beta = 0 product of the row-parallel CPU harness
+    prod = port.par_gemm_w8a8_mslabs(Aq, Bq, a_s, b_s, 8, alpha=0.5)
+    want = (C0 * np.float32(2.0) + prod).astype(np.float32)
+    assert_same_bits(got, want, f"pair kernel {M}x{N}x{K}")
+
+
+@pytest.mark.parametrize("world,M,N_local,K", [(2, 256, 256, 256), (3, 300, 288, 512), (4, 1024, 512, 1024), (8, 640, 160, 384)])
+def test_w8a8_sharded_call_fills_every_ranks_matrix(chk, lib, world, M, N_local, K):
+    """lhb_gemm_w8a8_sharded, every rank's call issued in turn from one process with all `world`
+    full-width matrices in this GPU's memory (the kernel does not know whose memory a destination
+    is): afterwards each matrix holds the unsharded product bit for bit, and the guard rows around
+    the matrices are untouched (M = 300 and 640 end inside a tile)."""
+    rng = np.random.default_rng(world * 1000 + M)
+    N = N_local * world
     A = rng.standard_normal((M, K)).astype(np.float32)
     W = (rng.standard_normal((K, N)) * 0.02).astype(np.float32)
     Aq, a_s = chk.q8_quantize_per_row(A)
     Bq, b_s = chk.q8_quantize_per_col(W)
-    C0 = rng.standard_normal((M, N)).astype(np.float32)
-    dAq, dBq, das, dbs = dev(Aq), dev(Bq), dev(a_s), dev(b_s)
-    monkeypatch.setenv("LHB_W8A8_PAIR", "0")
-    base = host(lb.gemm_w8a8(dAq, dBq, das, dbs, C=dev(C0), alpha=0.5, beta=2.0))
-    monkeypatch.setenv("LHB_W8A8_PAIR", "1")
-    got = host(lb.gemm_w8a8(dAq, dBq, das, dbs, C=dev(C0), alpha=0.5, beta=2.0))
+    want = chk.gemm_w8a8(Aq, Bq, a_s, b_s, alpha=0.75)
+    pad = 64                                                  # guard rows before and after every matrix
+    mats = [torch.full((M + 2 * pad, N), -7.0, device="cuda") for _ in range(world)]
+    full = (C.c_void_p * world)(*[m[pad:].data_ptr() for m in mats])
+    dAq, das = dev(Aq), dev(a_s)
+    ctx = lb.default_context().handle
+    st = torch.cuda.current_stream().cuda_stream
+    keep = []
+    for rank in range(world):
+        Bl = dev(np.ascontiguousarray(Bq[:, rank * N_local:(rank + 1) * N_local]))
+        bl = dev(np.ascontiguousarray(b_s[rank * N_local:(rank + 1) * N_local]))
+        keep += [Bl, bl]
+        rc = lib.lhb_gemm_w8a8_sharded(ctx, dAq.data_ptr(), Bl.data_ptr(), das.data_ptr(), bl.data_ptr(), full, rank,
+                                       world, M, N_local, K, 0.75, st)
+        assert rc == 0, lib.lhb_status_string(rc)
     poll_ok()
-    assert_same_bits(got, base, f"pair vs single-CTA {M}x{N}x{K}")
-    if M * N * K <= 1024 * 2048 * 1024:
-        assert_same_bits(got, chk.gemm_w8a8(Aq, Bq, a_s, b_s, C0, alpha=0.5, beta=2.0), "pair vs checker")
+    for r, m in enumerate(mats):
+        h = host(m)
+        assert_same_bits(h[pad:pad + M], want, f"matrix of rank {r}, world {world}")
+        assert (h[:pad] == -7.0).all() and (h[pad + M:] == -7.0).all(), f"rank {r}: rows outside the matrix were written"
+
+
+def test_w8a8_sharded_call_with_plain_store_push():
+    """The same cases with the peer copies written by plain stores instead of bulk stores.  The
+    library reads LHB_W8A8_PUSH once per process, so this variant runs in a child process."""
+    import subprocess
+    import sys
+    env = dict(os.environ, LHB_W8A8_PUSH="st")
+    r = subprocess.run([sys.executable, "-m", "pytest", "-q", "-x", "-p", "no:cacheprovider", os.path.abspath(__file__), "-k",
+                        "test_w8a8_sharded_call_fills_every_ranks_matrix"], env=env, capture_output=True, text=True,
+                       timeout=900, cwd=os.path.dirname(os.path.abspath(__file__)))
+    assert r.returncode == 0 and "4 passed" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def test_w8a8_sharded_call_rejects_what_it_cannot_push(lib):
+    M, K, world = 256, 256, 2
+    a = torch.zeros(M, K, dtype=torch.int8, device="cuda")
+    s = torch.ones(M, device="cuda")
+    ctx = lb.default_context().handle
+    for n_local in (144, 48):                                 # fast-path N, but not whole 32-column chunks
+        b = torch.zeros(K, n_local, dtype=torch.int8, device="cuda")
+        bs = torch.ones(n_local, device="cuda")
+        mats = [torch.zeros(M, n_local * world, device="cuda") for _ in range(world)]
+        full = (C.c_void_p * world)(*[m.data_ptr() for m in mats])
+        rc = lib.lhb_gemm_w8a8_sharded(ctx, a.data_ptr(), b.data_ptr(), s.data_ptr(), bs.data_ptr(), full, 0, world, M,
+                                       n_local, K, 1.0, None)
+        assert rc != 0 and b"unsupported" in lib.lhb_status_string(rc).lower()
+    full = (C.c_void_p * world)(mats[0].data_ptr(), None)
+    b = torch.zeros(K, 256, dtype=torch.int8, device="cuda"); bs = torch.ones(256, device="cuda")
+    assert lib.lhb_gemm_w8a8_sharded(ctx, a.data_ptr(), b.data_ptr(), s.data_ptr(), bs.data_ptr(), full, 0, world, M, 256, K,
+                                     1.0, None) != 0
+    assert lib.lhb_gemm_w8a8_sharded(ctx, a.data_ptr(), b.data_ptr(), s.data_ptr(), bs.data_ptr(), full, 2, world, M, 256, K,
+                                     1.0, None) != 0
+    poll_ok()
 
 
 # --------------------------------------------------------------------------- W4A16

@@ -36,6 +36,34 @@ def test_single_rank_gather_is_a_copy(rows, cols):
     pg.close()
 
 
+def test_shareable_allocation_maps_twice_and_unmaps():
+    """lhb_peer_alloc_shareable / lhb_peer_open_fd / lhb_peer_unmap inside one process: the descriptor
+    maps the same memory a second time, stores through one mapping are read through the other."""
+    lib = _cabi.load()
+    from longhornai_b200.peer import _DeviceView
+    base, fd, mapped = C.c_void_p(), C.c_int(-1), C.c_size_t(0)
+    n = 3 * 1024 * 1024 + 512
+    assert lib.lhb_peer_alloc_shareable(C.byref(base), n, C.byref(fd), C.byref(mapped)) == _cabi.OK, lib.lhb_last_error()
+    assert mapped.value >= n and fd.value >= 0 and base.value % (2 << 20) == 0
+    second = C.c_void_p()
+    assert lib.lhb_peer_open_fd(fd.value, mapped.value, C.byref(second)) == _cabi.OK, lib.lhb_last_error()
+    os.close(fd.value)
+    assert second.value not in (None, base.value)
+    a = torch.as_tensor(_DeviceView(base.value, n), device="cuda")
+    b = torch.as_tensor(_DeviceView(second.value, n), device="cuda")
+    assert int(a.count_nonzero().item()) == 0                  # zero-filled
+    pattern = torch.arange(n, device="cuda", dtype=torch.int64).mul_(2654435761).bitwise_and_(255).to(torch.uint8)
+    a.copy_(pattern)
+    torch.cuda.synchronize()
+    assert torch.equal(b, pattern)
+    del a, b
+    torch.cuda.synchronize()
+    assert lib.lhb_peer_unmap(second, mapped.value) == _cabi.OK
+    assert lib.lhb_peer_unmap(base, mapped.value) == _cabi.OK
+    assert lib.lhb_peer_open_fd(-1, mapped.value, C.byref(second)) != _cabi.OK
+    assert lib.lhb_peer_alloc_shareable(C.byref(base), 0, C.byref(fd), C.byref(mapped)) != _cabi.OK
+
+
 def _tables(bufs, flags):
     dev = bufs[0].device
     return (torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device=dev),
@@ -85,12 +113,16 @@ def test_argument_validation():
 
 
 @pytest.mark.timeout(600)
-def test_two_processes_two_gpus():
+@pytest.mark.parametrize("mapping", ["vmm", "cudaIpc"])
+def test_two_processes_two_gpus(mapping):
+    """Both ways of sharing the buffers: driver-managed allocations passed as file descriptors (the
+    default) and cudaIpc handles (LHB_PEER_VMM=0, also what a failed descriptor exchange falls back to)."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0", LHB_PEER_VMM="1" if mapping == "vmm" else "0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
-           "127.0.0.1", "--master-port", "29731", os.path.join(ROOT, "tests", "peer_exchange_worker.py")]
+           "127.0.0.1", "--master-port", "29731" if mapping == "vmm" else "29732", os.path.join(ROOT, "tests", "peer_exchange_worker.py")]
     res = subprocess.run(cmd, env=env, cwd=ROOT, capture_output=True, text=True, timeout=540)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert "PEER_EXCHANGE_OK" in res.stdout
+    assert f"PEER_MAPPING {mapping}" in res.stdout, res.stdout[-2000:]

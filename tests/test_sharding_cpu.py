@@ -82,3 +82,42 @@ def test_shard_ranges_and_alignment():
         sh.column_range(100, 0, 8)
     with pytest.raises(ValueError):
         sh.kv_head_range(8, 0, 3)
+
+
+def _fd_worker(rank, world, port, ret):
+    sys.path.insert(0, os.path.dirname(HERE))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import socket
+    import tempfile
+    from longhornai_b200.peer import pass_descriptors
+    # every rank owns a file with its own content; the peers must end up reading that content through
+    # the descriptor they were sent (a descriptor number means nothing in another process)
+    f = tempfile.TemporaryFile()
+    f.write(f"owned by rank {rank}".encode())
+    f.flush()
+    sock = socket.socket(socket.AF_UNIX, socket.SOCK_DGRAM)
+    addr = f"\0lhb-test-{os.getpid()}-{rank}"
+    sock.bind(addr)
+    sock.settimeout(30.0)
+    addrs = [None] * world
+    dist.all_gather_object(addrs, addr)
+    got = pass_descriptors(sock, f.fileno(), rank, addrs)
+    ok = sorted(got) == [p for p in range(world) if p != rank]
+    for p, fd in got.items():
+        ok = ok and os.pread(fd, 64, 0) == f"owned by rank {p}".encode()
+        os.close(fd)
+    sock.close()
+    ret[rank] = ok
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_descriptors_reach_every_other_rank():
+    """The exchange that shares driver-managed GPU allocations between the ranks' processes, with
+    ordinary files standing in for the allocations: three ranks, one datagram per pair and direction."""
+    world = 3
+    with mp.Manager() as m:
+        ret = m.dict()
+        mp.spawn(_fd_worker, args=(world, 31500 + os.getpid() % 2000, ret), nprocs=world, join=True)
+        assert all(ret[r] for r in range(world)), dict(ret)
