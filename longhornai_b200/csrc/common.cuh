@@ -70,6 +70,7 @@ struct Knobs {
     int w4tc_min_m = 17;         // LHB_W4TC_MIN_M: fewest rows that take the W4A16 tensor-core kernel
     bool w4tc_stream_k = false;  // LHB_W4TC_SPLIT=1: even deal of units instead of whole CTAs per column tile
     int w4tc_ctas = 0;           // LHB_W4TC_CTAS: cap on its grid
+    bool w4tc_coop = true;       // LHB_W4TC_COOP=0: the last CTA to reach a column tile adds its partial sums up alone
     bool w8a8_pair = true;       // LHB_W8A8_PAIR=0: single-CTA W8A8 kernel for every M
     bool w8a8_push_tma = true;   // LHB_W8A8_PUSH=st: sharded W8A8 pushes with plain stores instead of bulk stores
     int gemv_ctas_per_sm = 0;    // LHB_GEMV_CTAS_PER_SM

@@ -29,8 +29,13 @@
 // Work is split as in the GEMV kernel: a unit is 128 k x 256 columns (16 KiB of nibbles, two
 // 128-column MMA tiles that share one digit tile); the units, ordered column tile by column
 // tile, are dealt out to one CTA per SM; a CTA that holds only part of a column tile's K
-// leaves its partial sums in scratch and the last one to arrive adds them up in a fixed
-// order (same counters and scratch region as the GEMV kernel).
+// leaves its partial sums in scratch (same counters and scratch region as the GEMV kernel).
+// When the grid is a whole number of CTAs per column tile - the usual case: the host picks
+// such a grid whenever it keeps three quarters of the SMs busy - the contributors of a tile
+// wait (bounded) until all of their partials are in memory and each adds up its share of the
+// [M][256] outputs, in contributor order; all of them are resident, the grid being at most
+// one CTA per SM.  Otherwise the last CTA to arrive at a tile adds everything up alone.
+// Either way the order of the additions is fixed, so results do not vary from run to run.
 //
 // Warp roles (512 threads): 0 weight TMA producer, 1 MMA issuer, 2 TMEM allocator, 3 digit-tile
 // TMA producer, 4-7 and 8-11 epilogue of the first / second 128-column half (TMEM lane quarter =
@@ -205,6 +210,8 @@ struct W4TcParams {
     int max_contrib;         // partial slots per column tile in scratch
     float* partial;          // scratch [column tile][max_contrib][M][256]
     int* counters;           // one per column tile, zero between calls
+    int coop_sum;            // every CTA's units lie in one column tile (a whole number of CTAs per tile): the
+                             // contributors of a tile wait for each other and each adds up its share of the outputs
     int* status;
     const float* inv_scale;  // [M]
     int dig_row0;            // first row of this slab in the digit tensor
@@ -238,29 +245,32 @@ __device__ __forceinline__ float tc_int_to_float(uint32_t v) {
     return __uint_as_float(v + 0x4B400000u) - 12582912.0f;
 }
 
-// The last contributor to a column tile adds the partial sums up and writes C.  The 256 epilogue
-// threads share the [M][256] outputs as float4s, whatever columns they held before: each takes up to
-// four of them at a time and adds the contributors' float4s in contributor order.
-template <bool PEER>
+// The last contributor to a column tile adds the partial sums up and writes C.  NT threads share the
+// [M][256] outputs as float4s, whatever columns they held before: each takes up to four of them at a
+// time and adds the contributors' float4s in contributor order, Y contributors' loads in flight per
+// round trip to L2.  A CTA's last segment is summed by all of its 512 threads after the role loops
+// (the other roles have nothing left to do), five contributors per round trip: with nine CTAs per
+// column tile the sum costs two round trips instead of six, which is what the end of a short GEMM
+// (the o and QKV projections of a decode step: 3-5 units per CTA) spends its time on.
+template <bool PEER, int NT, int Y>
 __device__ __forceinline__ void tc_sum_partials(const W4TcParams& p, const float* tile_slots, int tile_col0,
                                                 int n_contrib, int et) {
     const int n_out = p.M * (TC_COLS / 4);
-    for (int e0 = et; e0 < n_out; e0 += 4 * 256) {
+    for (int e0 = et; e0 < n_out; e0 += 4 * NT) {
         float4 sum[4];
 #pragma unroll
         for (int x = 0; x < 4; ++x) sum[x] = make_float4(0.f, 0.f, 0.f, 0.f);
-        // three contributors' loads in flight per round trip, added in contributor order
-        for (int j = 0; j < n_contrib; j += 3) {
-            float4 v[3][4];
+        for (int j = 0; j < n_contrib; j += Y) {
+            float4 v[Y][4];
 #pragma unroll
-            for (int y = 0; y < 3; ++y) {
+            for (int y = 0; y < Y; ++y) {
                 const float* slot = tile_slots + static_cast<int64_t>(min(j + y, n_contrib - 1)) * p.M * TC_COLS;
 #pragma unroll
                 for (int x = 0; x < 4; ++x)       // clamped, unconditional: the loads overlap
-                    v[y][x] = __ldcg(reinterpret_cast<const float4*>(slot) + min(e0 + 256 * x, n_out - 1));
+                    v[y][x] = __ldcg(reinterpret_cast<const float4*>(slot) + min(e0 + NT * x, n_out - 1));
             }
 #pragma unroll
-            for (int y = 0; y < 3; ++y) {
+            for (int y = 0; y < Y; ++y) {
                 if (j + y < n_contrib) {
 #pragma unroll
                     for (int x = 0; x < 4; ++x) {
@@ -273,14 +283,14 @@ __device__ __forceinline__ void tc_sum_partials(const W4TcParams& p, const float
         if (p.beta != 0.0f) {
 #pragma unroll
             for (int x = 0; x < 4; ++x) {
-                const int e = min(e0 + 256 * x, n_out - 1), m = e >> 6, c = (e & 63) * 4;
+                const int e = min(e0 + NT * x, n_out - 1), m = e >> 6, c = (e & 63) * 4;
                 old[x] = (tile_col0 + c < p.N) ? *reinterpret_cast<const float4*>(p.C + m * p.N + tile_col0 + c)
                                                : make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
-            const int e = e0 + 256 * x, m = e >> 6, c = (e & 63) * 4;
+            const int e = e0 + NT * x, m = e >> 6, c = (e & 63) * 4;
             if (e < n_out && tile_col0 + c < p.N) {       // N % 16 == 0: whole float4 in range
                 float4 r;
                 if (p.beta == 0.0f) {
@@ -295,6 +305,44 @@ __device__ __forceinline__ void tc_sum_partials(const W4TcParams& p, const float
                                                p.peer_col0 + tile_col0 + c) = r;
             }
         }
+    }
+}
+
+// The shared form of that sum: contributor `ci` of `n_contrib` adds up outputs [ci, ci + 1) * n_out / n_contrib
+// of the tile once every contributor's partial is in memory - a few kilobytes per CTA instead of
+// n_contrib * 32 KiB into one SM, which is a bandwidth limit of that SM (2.4 us for nine contributors),
+// not a latency.  Same order of additions as tc_sum_partials.
+template <bool PEER>
+__device__ __forceinline__ void tc_sum_slice(const W4TcParams& p, const float* tile_slots, int tile_col0, int n_contrib,
+                                             int ci, int tid) {
+    const int n_out = p.M * (TC_COLS / 4);
+    const int lo = static_cast<int>(static_cast<int64_t>(ci) * n_out / n_contrib);
+    const int hi = static_cast<int>(static_cast<int64_t>(ci + 1) * n_out / n_contrib);
+    for (int e = lo + tid; e < hi; e += TC_THREADS) {
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j = 0; j < n_contrib; j += 8) {
+            float4 v[8];
+#pragma unroll
+            for (int y = 0; y < 8; ++y)
+                v[y] = __ldcg(reinterpret_cast<const float4*>(tile_slots + static_cast<int64_t>(min(j + y, n_contrib - 1)) * p.M * TC_COLS) + e);
+#pragma unroll
+            for (int y = 0; y < 8; ++y)
+                if (j + y < n_contrib) { sum.x += v[y].x; sum.y += v[y].y; sum.z += v[y].z; sum.w += v[y].w; }
+        }
+        const int m = e >> 6, c = (e & 63) * 4;
+        if (tile_col0 + c >= p.N) continue;               // N % 16 == 0: whole float4 in range
+        float4 r;
+        if (p.beta == 0.0f) {
+            r = make_float4(p.alpha * sum.x, p.alpha * sum.y, p.alpha * sum.z, p.alpha * sum.w);
+        } else {
+            const float4 old = *reinterpret_cast<const float4*>(p.C + m * p.N + tile_col0 + c);
+            r.x = fmaf(p.beta, old.x, p.alpha * sum.x); r.y = fmaf(p.beta, old.y, p.alpha * sum.y);
+            r.z = fmaf(p.beta, old.z, p.alpha * sum.z); r.w = fmaf(p.beta, old.w, p.alpha * sum.w);
+        }
+        *reinterpret_cast<float4*>(p.C + m * p.N + tile_col0 + c) = r;
+        for (int w = 0; w < TC_PW(p); ++w)
+            *reinterpret_cast<float4*>(p.peer_dst[w] + static_cast<int64_t>(p.peer_row0 + m) * p.peer_ld + p.peer_col0 +
+                                       tile_col0 + c) = r;
     }
 }
 
@@ -322,6 +370,7 @@ gemm_w4a16_tc_kernel(const __grid_constant__ TensorMap tmW, const __grid_constan
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NBARS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* epi_flag = const_cast<int*>(reinterpret_cast<volatile int*>(tmem_slot + 2));
+    int* final_tile = const_cast<int*>(reinterpret_cast<volatile int*>(tmem_slot + 3));   // column tile this CTA sums at its end, or -1
     float* inv_s = reinterpret_cast<float*>(tmem_slot + 4);          // [MP]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -348,6 +397,7 @@ gemm_w4a16_tc_kernel(const __grid_constant__ TensorMap tmW, const __grid_constan
         for (int s = 0; s < 4; ++s) { ptx::mbar_init(t_full(s), 1); ptx::mbar_init(t_empty(s), 128); }
         *abort_flag = 0;
         *epi_flag = 0;
+        *final_tile = -1;
         ptx::fence_mbar_init();
         ptx::prefetch_tmap(&tmW);
         ptx::prefetch_tmap(&tmD);
@@ -622,9 +672,18 @@ gemm_w4a16_tc_kernel(const __grid_constant__ TensorMap tmW, const __grid_constan
                 tc_epi_sync();
                 if (et == 0) tc_peer_signal(p);
             }
-            if (!whole) {
+            if (!whole && p.coop_sum) {
+                // this CTA's only segment: count the arrival; the wait for the others and the sum follow the role loops
+                tc_epi_sync();
+                if (et == 0) {
+                    __threadfence();
+                    atomicAdd(p.counters + tile, 1);
+                    *final_tile = tile;
+                }
+            } else if (!whole) {
                 // the last contributor to arrive adds the partials up in contributor order and writes C;
                 // one thread fences for the CTA on either side of the count
+                const bool final_seg = (u + (s_end - s_begin) >= u1);   // nothing follows: the whole CTA sums, below
                 tc_epi_sync();
                 if (et == 0) {
                     __threadfence();
@@ -634,10 +693,15 @@ gemm_w4a16_tc_kernel(const __grid_constant__ TensorMap tmW, const __grid_constan
                         p.counters[tile] = 0;                // ready for the next call
                         __threadfence();
                     }
-                    *epi_flag = last;
+                    if (final_seg) {
+                        *final_tile = last ? tile : -1;
+                        *epi_flag = 0;
+                    } else {
+                        *epi_flag = last;
+                    }
                 }
                 tc_epi_sync();
-                if (*epi_flag) tc_sum_partials<PEER>(p, p.partial + (static_cast<int64_t>(tile) * p.max_contrib) * p.M * TC_COLS, tile * TC_COLS, n_contrib, et);
+                if (*epi_flag) tc_sum_partials<PEER, 256, 3>(p, p.partial + (static_cast<int64_t>(tile) * p.max_contrib) * p.M * TC_COLS, tile * TC_COLS, n_contrib, et);
                 tc_epi_sync();                               // epi_flag is free again
                 if (TC_PW(p) > 0 && et == 0 && *epi_flag) tc_peer_signal(p);
             }
@@ -651,6 +715,48 @@ gemm_w4a16_tc_kernel(const __grid_constant__ TensorMap tmW, const __grid_constan
     if (warp == 2) {
         ptx::tc_fence_after();
         ptx::tmem_dealloc(tmem_base, TCOLS);
+    }
+    // this CTA arrived last at the column tile its units ended in: all 512 threads add the partials up
+    const int ft = *final_tile;
+    if (ft >= 0 && !*abort_flag) {
+        const int64_t P = gridDim.x;
+        const int cf = static_cast<int>(((static_cast<int64_t>(ft) * S + 1) * P - 1) / p.units);
+        const int cz = static_cast<int>(((static_cast<int64_t>(ft + 1) * S) * P - 1) / p.units);
+        const int n_contrib = cz - cf + 1;
+        const float* slots = p.partial + (static_cast<int64_t>(ft) * p.max_contrib) * p.M * TC_COLS;
+        if (p.coop_sum) {
+            // low half of the counter: arrivals (partials in memory); high half: departures (sums written)
+            if (threadIdx.x == 0) {
+                const uint64_t t0 = ptx::global_timer_ns();
+                while ((ptx::ld_acquire_gpu(p.counters + ft) & 0xffff) < n_contrib) {
+                    if (ptx::global_timer_ns() - t0 > 1000000000ull) {      // a contributor never ran: report, do not hang
+                        *abort_flag = 1;
+                        atomicExch(p.status, static_cast<int>(LHB_ERR_TIMEOUT));
+                        break;
+                    }
+                }
+                TC_STAMP(3, 4);
+            }
+            __syncthreads();
+            if (!*abort_flag) tc_sum_slice<PEER>(p, slots, ft * TC_COLS, n_contrib, static_cast<int>(blockIdx.x) - cf, threadIdx.x);
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                if (TC_PW(p) > 0) __threadfence_system(); else __threadfence();
+                const int old = atomicAdd(p.counters + ft, 0x10000);
+                if ((old >> 16) == n_contrib - 1) {          // the last to leave: the tile is complete
+                    p.counters[ft] = 0;                      // ready for the next call
+                    __threadfence();
+                    if (TC_PW(p) > 0 && !*abort_flag) tc_peer_signal(p);
+                }
+            }
+        } else {
+            tc_sum_partials<PEER, TC_THREADS, 5>(p, slots, ft * TC_COLS, n_contrib, threadIdx.x);
+            if (TC_PW(p) > 0) {
+                __syncthreads();
+                if (threadIdx.x == 0) tc_peer_signal(p);
+            }
+        }
+        if (threadIdx.x == 0) TC_STAMP(3, 3);
     }
 }
 
@@ -720,6 +826,8 @@ int launch_w4a16_tc(lhb_ctx* ctx, const float* A, const uint8_t* Bp, const float
         if (!knobs().w4tc_stream_k && 4 * aligned >= 3 * ctas) ctas = aligned;
     }
     if (knobs().w4tc_ctas > 0) ctas = std::min(ctas, knobs().w4tc_ctas);
+    // a whole number (two or more) of CTAs per column tile: the contributors of a tile share its final sum
+    const int coop_sum = (knobs().w4tc_coop && ctas % col_tiles == 0 && ctas / col_tiles >= 2 && ctas <= ctx->sm_count) ? 1 : 0;
     const int r_min = std::max<int>(1, static_cast<int>(units / ctas));
     const int max_contrib = std::min(ctas, S / r_min + 2);
     const int64_t row_len = (prologue == TC_PRO_SWIGLU) ? 2 * static_cast<int64_t>(K) : K;
@@ -755,6 +863,7 @@ int launch_w4a16_tc(lhb_ctx* ctx, const float* A, const uint8_t* Bp, const float
             p.max_contrib = max_contrib;
             p.partial = reinterpret_cast<float*>(dig + TC_SCRATCH_HEAD);
             p.counters = ctx->counters;
+            p.coop_sum = coop_sum;
             p.status = ctx->status_word;
             p.inv_scale = inv + (m0 - pass0);
             p.dig_row0 = sl * drows;

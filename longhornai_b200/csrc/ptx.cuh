@@ -67,6 +67,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     return true;
 }
 
+// a global load that later loads of this thread (and, after a barrier, of its CTA) cannot overtake
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
 // ---- TMA (tiled, 2-D, this CTA only) ---------------------------------------------
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int x, int y, uint32_t bar) {

@@ -110,6 +110,7 @@ const Knobs& knobs() {
         v.w4tc_min_m = std::max(1, num("LHB_W4TC_MIN_M", 17));
         v.w4tc_stream_k = num("LHB_W4TC_SPLIT", 0) == 1;
         v.w4tc_ctas = std::max(0, num("LHB_W4TC_CTAS", 0));
+        v.w4tc_coop = num("LHB_W4TC_COOP", 1) != 0;
         v.w8a8_pair = num("LHB_W8A8_PAIR", 1) != 0;
         const char* push = getenv("LHB_W8A8_PUSH");
         v.w8a8_push_tma = !(push && push[0] == 's');
