@@ -329,6 +329,21 @@ def test_w4a16_tensor_core_kernel_shapes(chk, M, N, K, G):
     poll_ok()
 
 
+@pytest.mark.parametrize("knob", ["LHB_W4TC_COOP=0", "LHB_W4TC_SPLIT=1"])
+def test_w4a16_tensor_core_kernel_other_hand_offs(knob):
+    """The same shapes with the other ways a column tile's partial sums are added up: the last CTA to
+    arrive alone (LHB_W4TC_COOP=0) and an even deal of units whatever the tile boundaries
+    (LHB_W4TC_SPLIT=1).  The library reads its knobs once per process: child processes."""
+    import subprocess
+    import sys
+    name, value = knob.split("=")
+    r = subprocess.run([sys.executable, "-m", "pytest", "-q", "-x", "-p", "no:cacheprovider", os.path.abspath(__file__), "-k",
+                        "test_w4a16_tensor_core_kernel_shapes or test_w4a16_with_rmsnorm_and_swiglu_prologue"],
+                       env=dict(os.environ, **{name: value}), capture_output=True, text=True, timeout=900,
+                       cwd=os.path.dirname(os.path.abspath(__file__)))
+    assert r.returncode == 0 and " passed" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
 def test_w4a16_tensor_core_kernel_is_exact_on_integers():
     """Small integer activations and unit scales: every product and sum is an integer below 2^22 that
     the kernel carries exactly, so the result equals integer arithmetic bit for bit (no tolerance)."""
