@@ -137,8 +137,13 @@ int lhb_gemm_w4a16_groupwise_peer(lhb_ctx* ctx, const float* A, const uint8_t* B
     cudaStream_t st = as_stream(stream);
     const W4Peer peer{dst_table, flag_table, world, rank, N * world, rank * N};
     uint32_t arrivals = 0;
-    if (int e = launch_w4a16_tc(ctx, A, Bp, Bs, C, M, N, K, G, alpha, beta, st, 0, nullptr, 0.0f, &peer, &arrivals)) return e;
-    return launch_peer_wait(flag_table, state, rank, world, arrivals, timeout_ms, st);
+    const int e = launch_w4a16_tc(ctx, A, Bp, Bs, C, M, N, K, G, alpha, beta, st, 0, nullptr, 0.0f, &peer, &arrivals);
+    if (e != LHB_OK && arrivals == 0) return e;              // nothing that signals was launched
+    // A failure after some slabs were launched: their tiles still raise every rank's counters, so the wait for
+    // exactly those arrivals is issued all the same - the ranks' expected counts stay in step - and the error
+    // is what the caller gets.
+    const int w = launch_peer_wait(flag_table, state, rank, world, arrivals, timeout_ms, st);
+    return e != LHB_OK ? e : w;
 }
 
 int lhb_gemm_w8a16_perchannel(lhb_ctx* ctx, const float* A, const int8_t* Bq, const float* Bs,

@@ -872,13 +872,13 @@ int launch_w4a16_tc(lhb_ctx* ctx, const float* A, const uint8_t* Bp, const float
                 p.peer_flags = peer->flag_table;
                 p.peer_world = peer->world; p.peer_rank = peer->rank; p.peer_ld = peer->ld; p.peer_col0 = peer->col0;
                 p.peer_row0 = m0;
-                if (arrivals_out) *arrivals_out += static_cast<uint32_t>(col_tiles);
             }
             const int e = peer       ? (mp == 16 ? launch_tc_slab<16, true>(ctx, tmW, tmD, p, ctas, st)
                                                  : launch_tc_slab<32, true>(ctx, tmW, tmD, p, ctas, st))
                           : mp == 16 ? launch_tc_slab<16, false>(ctx, tmW, tmD, p, ctas, st)
                                      : launch_tc_slab<32, false>(ctx, tmW, tmD, p, ctas, st);
             if (e) return e;
+            if (peer && arrivals_out) *arrivals_out += static_cast<uint32_t>(col_tiles);   // only launches that will signal
         }
     }
     return LHB_OK;

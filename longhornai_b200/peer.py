@@ -253,7 +253,9 @@ class PeerGather:
         return self.tensor(name)
 
     def check(self) -> None:
-        """Synchronises the current stream and raises if a wait of any gather so far gave up."""
+        """Synchronises the current stream and raises if a wait of any gather so far gave up.  After such
+        a timeout the ranks' arrival counters no longer agree: close() this object on every rank and
+        create a new one before exchanging again."""
         stream = torch.cuda.current_stream(self.device).cuda_stream
         _cabi.check(self.lib.lhb_peer_status(self._state.data_ptr(), stream), "lhb_peer_status")
 
