@@ -566,7 +566,7 @@ static int launch_tc(lhb_ctx* ctx, const void* Aq, const void* Bq, W8Params p, c
     if (use_pair && M >= 256) {
         const int tiles = ceil_div(M, 256) * p.tiles_n;
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(2 * std::min(sms / 2, tiles), 1, 1);
+        cfg.gridDim = dim3(2 * std::max(1, std::min(sms / 2, tiles)), 1, 1);   // at least one pair, whatever the SM limit
         cfg.blockDim = dim3(W8_THREADS, 1, 1);
         cfg.dynamicSmemBytes = W8P_SMEM;
         cfg.stream = st;

@@ -36,6 +36,11 @@ class Context:
         """Synchronise the current stream and return (and clear) the device status word."""
         return int(self.lib.lhb_ctx_poll(self.handle, _stream(self.device)))
 
+    def set_sm_limit(self, n: int) -> None:
+        """The persistent tensor-core grids of this context use at most `n` SMs (0 = all), leaving the
+        rest to kernels the caller runs beside them."""
+        check(self.lib.lhb_ctx_set_sm_limit(self.handle, int(n)), "lhb_ctx_set_sm_limit")
+
     def close(self):
         if getattr(self, "handle", None):
             self.lib.lhb_ctx_destroy(self.handle)

@@ -139,6 +139,27 @@ def test_w8a8_cta_pair_path_bit_exact(lib, M, N, K):
     assert_same_bits(got, want, f"pair kernel {M}x{N}x{K}")
 
 
+def test_w8a8_on_a_limited_number_of_sms_gives_the_same_bits(lib):
+    """lhb_ctx_set_sm_limit shrinks the persistent grids (both tcgen05 kernels walk their tiles with a
+    stride of the grid size): same result from 148, 37 and 2 SMs; a negative limit is refused."""
+    M, N, K = 512, 2048, 1024
+    g = torch.Generator(device="cuda").manual_seed(3)
+    Aq, a_s = lb.q8_quantize_per_row(torch.randn(M, K, device="cuda", generator=g))
+    Bq, b_s = lb.q8_quantize_per_col(torch.randn(K, N, device="cuda", generator=g) * 0.02)
+    ctx = lb.default_context()
+    full = lb.gemm_w8a8(Aq, Bq, a_s, b_s)
+    small = lb.gemm_w8a8(Aq[:100], Bq, a_s[:100], b_s)       # M < 256: the single-CTA kernel
+    try:
+        for n in (37, 2):
+            ctx.set_sm_limit(n)
+            assert torch.equal(lb.gemm_w8a8(Aq, Bq, a_s, b_s), full), f"{n} SMs"
+            assert torch.equal(lb.gemm_w8a8(Aq[:100], Bq, a_s[:100], b_s), small), f"{n} SMs, single-CTA kernel"
+        assert lib.lhb_ctx_set_sm_limit(ctx.handle, -1) != 0
+    finally:
+        ctx.set_sm_limit(0)
+    poll_ok()
+
+
 @pytest.mark.parametrize("world,M,N_local,K", [(2, 256, 256, 256), (3, 300, 288, 512), (4, 1024, 512, 1024), (8, 640, 160, 384)])
 def test_w8a8_sharded_call_fills_every_ranks_matrix(chk, lib, world, M, N_local, K):
     """lhb_gemm_w8a8_sharded, every rank's call issued in turn from one process with all `world`
