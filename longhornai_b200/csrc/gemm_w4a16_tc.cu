@@ -725,10 +725,14 @@ gemm_w4a16_tc_kernel(const __grid_constant__ TensorMap tmW, const __grid_constan
         const int n_contrib = cz - cf + 1;
         const float* slots = p.partial + (static_cast<int64_t>(ft) * p.max_contrib) * p.M * TC_COLS;
         if (p.coop_sum) {
-            // low half of the counter: arrivals (partials in memory); high half: departures (sums written)
+            // The counter counts arrivals (partials in memory) up to n_contrib and then departures; the
+            // departures increment with wrap-around at 2 * n_contrib - 1, so the last one leaves zero behind
+            // for the next call and nobody has to wait for the value it read (only the sharded form does:
+            // the last to leave tells the other ranks).
+            const unsigned wrap = 2u * static_cast<unsigned>(n_contrib) - 1u;
             if (threadIdx.x == 0) {
                 const uint64_t t0 = ptx::global_timer_ns();
-                while ((ptx::ld_acquire_gpu(p.counters + ft) & 0xffff) < n_contrib) {
+                while (ptx::ld_acquire_gpu(p.counters + ft) < n_contrib) {
                     if (ptx::global_timer_ns() - t0 > 1000000000ull) {      // a contributor never ran: report, do not hang
                         *abort_flag = 1;
                         atomicExch(p.status, static_cast<int>(LHB_ERR_TIMEOUT));
@@ -739,15 +743,16 @@ gemm_w4a16_tc_kernel(const __grid_constant__ TensorMap tmW, const __grid_constan
             }
             __syncthreads();
             if (!*abort_flag) tc_sum_slice<PEER>(p, slots, ft * TC_COLS, n_contrib, static_cast<int>(blockIdx.x) - cf, threadIdx.x);
-            __syncthreads();
-            if (threadIdx.x == 0) {
-                if (TC_PW(p) > 0) __threadfence_system(); else __threadfence();
-                const int old = atomicAdd(p.counters + ft, 0x10000);
-                if ((old >> 16) == n_contrib - 1) {          // the last to leave: the tile is complete
-                    p.counters[ft] = 0;                      // ready for the next call
-                    __threadfence();
-                    if (TC_PW(p) > 0 && !*abort_flag) tc_peer_signal(p);
+            if (TC_PW(p) > 0) {
+                __syncthreads();
+                if (threadIdx.x == 0) {
+                    __threadfence_system();
+                    const unsigned old = atomicInc(reinterpret_cast<unsigned*>(p.counters + ft), wrap);
+                    if (old == wrap && !*abort_flag) tc_peer_signal(p);   // the last to leave: the tile is complete everywhere
                 }
+            } else if (threadIdx.x == 0) {
+                // this thread's own outputs need no ordering against the count: the kernel's end publishes them
+                asm volatile("red.relaxed.gpu.global.inc.u32 [%0], %1;" ::"l"(p.counters + ft), "r"(wrap) : "memory");
             }
         } else {
             tc_sum_partials<PEER, TC_THREADS, 5>(p, slots, ft * TC_COLS, n_contrib, threadIdx.x);
