@@ -359,7 +359,7 @@ def make_w4_layers(torch, lb, layers, K, n_local, G, seed):
 
 
 def bench_extra(torch, lb, steps, warmup, hbm_peak):
-    """The other BASELINE workloads on one GPU (kernel-only, inputs resident)."""
+    """The other benchmark workloads on one GPU (kernel-only, inputs resident)."""
     out = {}
     gen = torch.Generator(device="cuda").manual_seed(20241)
     packed, scales = make_w4_layers(torch, lb, 8, K_DIM, N_DIM, GROUP, 20243)
