@@ -884,32 +884,41 @@ def run_ours(args):
 
     # end to end through the host-buffer path: activations come from pinned host
     # memory and results go back to pinned host memory on every call
-    h_act = [a.cpu().pin_memory() for a in acts]
+    h_act_all = torch.stack([a.cpu() for a in acts]).pin_memory()       # the step's activations, one pinned buffer
+    h_act = [h_act_all[i] for i in range(LAYERS)]
     h_out = torch.empty(LAYERS, M, n_local).pin_memory()
-    d_acts = [torch.empty(M, K_DIM, device="cuda") for _ in range(LAYERS)]
+    d_act_all = torch.empty(LAYERS, M, K_DIM, device="cuda")
+    d_acts = [d_act_all[i] for i in range(LAYERS)]
     s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    e2e_mode = os.environ.get("LHB_BENCH_E2E", "batched")
 
     def e2e_body():
-        # Three streams, as a serving loop would run it: input copies run ahead on one, the
-        # GEMVs follow on the launching stream as their inputs land, result copies trail on a
-        # third.  Every call still gets its activations from the host and returns its
-        # result to the host.
+        # As a serving loop would run it.  "batched": the step's activations arrive in one copy, the GEMVs
+        # follow back to back on the launching stream (programmatic dependent launch between them stays
+        # intact), each call's result copy trails on a second stream.  "percall": one input copy per
+        # call on a third stream, every GEMV waiting for its own.  Either way every call's activations
+        # come from the host and its result returns to the host inside the step.
         main = torch.cuda.current_stream()
-        s_in.wait_stream(main)
         s_out.wait_stream(main)
+        if e2e_mode == "batched":
+            d_act_all.copy_(h_act_all, non_blocking=True)
+        else:
+            s_in.wait_stream(main)
         for i in range(LAYERS):
-            with torch.cuda.stream(s_in):
-                d_acts[i].copy_(h_act[i], non_blocking=True)
-                landed = torch.cuda.Event()
-                landed.record(s_in)
-            main.wait_event(landed)
+            if e2e_mode != "batched":
+                with torch.cuda.stream(s_in):
+                    d_acts[i].copy_(h_act[i], non_blocking=True)
+                    landed = torch.cuda.Event()
+                    landed.record(s_in)
+                main.wait_event(landed)
             lb.gemm_w4a16_groupwise(d_acts[i], packed[i], scales[i], GROUP, C=outs[i])
             done = torch.cuda.Event()
             done.record(main)
             s_out.wait_event(done)
             with torch.cuda.stream(s_out):
                 h_out[i].copy_(outs[i], non_blocking=True)
-        main.wait_stream(s_in)
+        if e2e_mode != "batched":
+            main.wait_stream(s_in)
         main.wait_stream(s_out)
     run_e2e, e2e_graph = graphed(e2e_body, torch, GRAPHS)
 
@@ -972,8 +981,12 @@ def run_ours(args):
                                        "come from the median region of exactly `steps` steps"),
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e / args.steps, "step_stats": stats_e2e,
                 "h2d_bytes_per_step": LAYERS * M * K_DIM * 4, "d2h_bytes_per_step": LAYERS * M * n_local * 4,
-                "note": "every call's activations H2D from pinned memory and its outputs D2H to pinned memory, "
-                        "input copies / GEMVs / result copies on three streams, host sync every step; "
+                "mode": e2e_mode,
+                "note": ("the step's activations H2D from one pinned buffer at the start of the step, the GEMVs back to back, "
+                         "every call's output D2H to pinned memory on a second stream, host sync every step; "
+                         if e2e_mode == "batched" else
+                         "every call's activations H2D from pinned memory and its outputs D2H to pinned memory, "
+                         "input copies / GEMVs / result copies on three streams, host sync every step; ") +
                         "weights resident" + ("; the step replayed as one CUDA graph" if e2e_graph else "")},
         "gpu_launches": launches,
         "roofline": {"bound": "hbm", "kernel": "gemv_mma_kernel<4,1>", "achieved": achieved, "peak": hbm_peak,
