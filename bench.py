@@ -269,14 +269,22 @@ def run_reference(args):
 
 # ----------------------------------------------------------------------------- our arm
 
-def timed(fn, steps, warmup, dist, torch, sampler=None, stats=None, min_region_s=0.0):
+# rows of the per-workload table (`--csv`): name, calls per step, operations and bytes per call, step statistics
+ROWS = []
+
+
+def timed(fn, steps, warmup, dist, torch, sampler=None, stats=None, min_region_s=0.0, row=None):
     """W untimed steps, then exactly `steps` steps between CUDA events on the
     launching stream, bracketed by barrier + synchronize; max over ranks.
 
     With `stats` (a dict) the region is repeated until at least `min_region_s` seconds of
     timed steps have run (each repeat bracketed the same way); the returned time is the median
     region, and `stats` receives the percentiles of the single steps (an event pair per step,
-    mirroring bench/bench_util.hpp:98-123 of the reference: p50 / p90 / p99 beside the mean)."""
+    mirroring bench/bench_util.hpp:98-123 of the reference: p50 / p90 / p99 beside the mean).
+    `row` = (name, calls per step, operations per call, bytes per call) adds the workload to the table
+    that `--csv` writes in the reference's format (bench/bench_util.hpp:142-154)."""
+    if row is not None and stats is None:
+        stats = {}
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
@@ -315,7 +323,21 @@ def timed(fn, steps, warmup, dist, torch, sampler=None, stats=None, min_region_s
         stats.update({"regions": len(regions), "steps_sampled": len(s), "mean_ms": sum(s) / len(s),
                       "p50_ms": pick(0.50), "p90_ms": pick(0.90), "p99_ms": pick(0.99), "min_ms": s[0], "max_ms": s[-1],
                       "region_ms_min": regions[0], "region_ms_max": regions[-1]})
+    if row is not None:
+        ROWS.append((row, dict(stats)))
     return ms
+
+
+def write_csv(path):
+    """name,p50_us,p90_us,p99_us,min_us,max_us,mean_us,gflops,gbps per call; throughput from the p50, as the
+    reference's harness derives it (bench/bench_util.hpp:119-123, :142-154)."""
+    with open(path, "w") as f:
+        f.write("name,p50_us,p90_us,p99_us,min_us,max_us,mean_us,gflops,gbps\n")
+        for (name, calls, ops, nbytes), s in ROWS:
+            us = {k: s[k + "_ms"] * 1e3 / calls for k in ("p50", "p90", "p99", "min", "max", "mean")}
+            secs = us["p50"] * 1e-6
+            f.write(f"{name},{us['p50']:.3f},{us['p90']:.3f},{us['p99']:.3f},{us['min']:.3f},{us['max']:.3f},{us['mean']:.3f},"
+                    f"{(ops / secs / 1e9) if secs > 0 else 0:.2f},{(nbytes / secs / 1e9) if secs > 0 else 0:.2f}\n")
 
 
 def graphed(fn, torch, enabled=True):
@@ -371,9 +393,9 @@ def bench_extra(torch, lb, steps, warmup, hbm_peak):
             for p, s in zip(packed, scales):
                 lb.gemm_w4a16_groupwise(A, p, s, GROUP, C=C)
         run, _ = graphed(step, torch, GRAPHS)
-        ms = timed(run, steps, warmup, None, torch)
-        per = ms / (steps * len(packed)) * 1e-3
         b = gemv_bytes(M, K_DIM, N_DIM, GROUP)
+        ms = timed(run, steps, warmup, None, torch, row=(f"gemm_w4a16_groupwise_m{M}", len(packed), 2.0 * M * N_DIM * K_DIM, b))
+        per = ms / (steps * len(packed)) * 1e-3
         out[f"w4a16_m{M}"] = {"us_per_call": per * 1e6, "GBps": b / per / 1e9,
                               "hbm_frac": b / per / 1e9 / hbm_peak, "bytes": b}
     del packed, scales
@@ -391,9 +413,9 @@ def bench_extra(torch, lb, steps, warmup, hbm_peak):
         for p, s, z in asym:
             lb.gemm_w4a16_asym(A, p, s, z, GROUP, C=C)
     run_a, _ = graphed(step_asym, torch, GRAPHS)
-    ms = timed(run_a, steps, warmup, None, torch)
-    per = ms / (steps * len(asym)) * 1e-3
     b = gemv_bytes(1, K_DIM, N_DIM, GROUP)
+    ms = timed(run_a, steps, warmup, None, torch, row=("gemm_w4a16_asym_f16_m1", len(asym), 2.0 * N_DIM * K_DIM, b))
+    per = ms / (steps * len(asym)) * 1e-3
     out["w4a16_asym_f16_m1"] = {"us_per_call": per * 1e6, "GBps": b / per / 1e9, "hbm_frac": b / per / 1e9 / hbm_peak,
                                 "bytes": b,
                                 "fast_path": int(lb._cabi.load().lhb_gemm_w4a16_asym_fast_path(1, N_DIM, K_DIM, GROUP))}
@@ -410,9 +432,9 @@ def bench_extra(torch, lb, steps, warmup, hbm_peak):
         for q, s in ws:
             lb.gemm_w8a16_perchannel(A, q, s, C=C)
     run8, _ = graphed(step8, torch, GRAPHS)
-    ms = timed(run8, steps, warmup, None, torch)
-    per = ms / (steps * len(ws)) * 1e-3
     b = gemv_bytes(16, 4096, 4096, 0, wbits=8)
+    ms = timed(run8, steps, warmup, None, torch, row=("gemm_w8a16_perchannel_m16", len(ws), 2.0 * 16 * 4096 * 4096, b))
+    per = ms / (steps * len(ws)) * 1e-3
     out["w8a16_m16"] = {"us_per_call": per * 1e6, "GBps": b / per / 1e9, "hbm_frac": b / per / 1e9 / hbm_peak,
                         "bytes": b}
     del ws
@@ -563,7 +585,7 @@ def bench_fp8(torch, lb, steps, warmup, M=8192, K=8192, N=28672):
 
     def step():
         lb.gemm_fp8_e4m3(A, B, sa, sb, C=Cout)
-    ms = timed(step, steps, warmup, None, torch)
+    ms = timed(step, steps, warmup, None, torch, row=(f"gemm_fp8_e4m3_{M}x{N}x{K}", 1, 2.0 * M * N * K, M * K + K * N + 4.0 * M * N))
     per = ms / steps * 1e-3
     ops = 2.0 * M * N * K
     _, bf16_peak, kind = measured_peaks()
@@ -588,7 +610,7 @@ def bench_w8a8(torch, lb, steps, warmup, M=8192, K=8192, N=28672):
 
     def step():
         lb.gemm_w8a8(Aq, Bq, a_s, b_s, C=Cout)
-    ms = timed(step, steps, warmup, None, torch)
+    ms = timed(step, steps, warmup, None, torch, row=(f"gemm_w8a8_{M}x{N}x{K}", 1, 2.0 * M * N * K, M * K + K * N + 4.0 * M * N))
     per = ms / steps * 1e-3
     ops = 2.0 * M * N * K
     _, bf16_peak, kind = measured_peaks()
@@ -634,11 +656,11 @@ def bench_paged_decode(torch, lb, steps, warmup, hbm_peak, n_req=64, hq=32, hkv=
     def step():
         lb.paged_attention_q8_batched(Q, k, v, ks, vs, td, sl, cfg, L, O=O)
     run, _ = graphed(step, torch, GRAPHS)
-    ms = timed(run, steps, warmup, None, torch)
-    per = ms / steps * 1e-3
     total = int(lens.sum())
     pages = int(sum((int(l) + bs - 1) // bs for l in lens))
     b = total * hkv * (2 * d + 8) + 2 * Q.numel() * 4 + 4 * pages + 4 * n_req
+    ms = timed(run, steps, warmup, None, torch, row=("paged_attention_q8_batched_decode", 1, 4.0 * total * hq * d, b))
+    per = ms / steps * 1e-3
     import ctypes as C
     fast = lb._cabi.load().lhb_paged_attention_q8_fast_path(C.byref(cfg), C.byref(L))
     return {"tok_per_s": n_req / per, "us_per_step": per * 1e6, "GBps": b / per / 1e9,
@@ -876,7 +898,9 @@ def run_ours(args):
 
     sampler = ClockSampler(physical_gpu_index(local)) if rank == 0 else None
     stats = {}
-    ms = timed(step, args.steps, args.warmup, dist, torch, sampler, stats=stats, min_region_s=0.5)
+    ms = timed(step, args.steps, args.warmup, dist, torch, sampler, stats=stats, min_region_s=0.5,
+               row=("gemm_w4a16_groupwise_m1 (headline, per launch)", LAYERS, 2.0 * M * N_DIM * K_DIM,
+                    g * (gemv_bytes(M, K_DIM, n_local, GROUP) - 4 * M * K_DIM) + 4 * M * K_DIM))
     launches = args.steps * LAYERS
     bytes_call_local = gemv_bytes(M, K_DIM, n_local, GROUP)
     bytes_step_total = LAYERS * (g * (bytes_call_local - 4 * M * K_DIM) + 4 * M * K_DIM)
@@ -928,7 +952,9 @@ def run_ours(args):
             sharding.all_gather_columns(outs, g, dist)     # [g, layers, M, N/g]
         torch.cuda.current_stream().synchronize()      # the caller reads the results on the host
     stats_e2e = {}
-    ms_e2e = timed(step_e2e, args.steps, args.warmup, dist, torch, stats=stats_e2e, min_region_s=0.3)
+    ms_e2e = timed(step_e2e, args.steps, args.warmup, dist, torch, stats=stats_e2e, min_region_s=0.3,
+                   row=("gemm_w4a16_groupwise_m1 from host buffers (per launch)", LAYERS, 2.0 * M * N_DIM * K_DIM,
+                        g * (gemv_bytes(M, K_DIM, n_local, GROUP) - 4 * M * K_DIM) + 4 * M * K_DIM))
     e2e_value = bytes_step_total * args.steps / (ms_e2e * 1e-3) / 1e12
 
     status = lb.default_context().poll()
@@ -1014,6 +1040,8 @@ def run_ours(args):
             line["cpu_baseline"]["other_workloads"] = cpu_other_baselines()
         except Exception as e:
             line["cpu_baseline"]["other_workloads"] = {"error": repr(e)}
+    if args.csv:
+        write_csv(args.csv)
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
@@ -1027,6 +1055,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary workloads")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--csv", default=None, metavar="PATH",
+                    help="also write the per-workload table (p50/p90/p99/min/max/mean per call, GFLOP/s and GB/s "
+                         "from the p50) in the reference harness's CSV format")
     ap.add_argument("--only", default=None, choices=["paged_decode", "w8a8", "decode_step", "sharded"],
                     help="run one secondary workload alone on one GPU (for profiling) and print its numbers")
     args = ap.parse_args()
@@ -1082,6 +1113,8 @@ def main():
         run_reference(args)
     else:
         run_ours(args)
+    if args.csv and args.only and int(os.environ.get("RANK", "0")) == 0:
+        write_csv(args.csv)
 
 
 if __name__ == "__main__":
