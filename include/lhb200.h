@@ -463,7 +463,7 @@ LHB_API int lhb_peer_status(const uint32_t* state, void* stream);
  * by the GEMM's own epilogue over NVLink; every completed column tile raises the arrival counters, and a
  * one-CTA launch that follows waits (bounded) until all ranks' tiles have arrived.  Same tables, state and
  * rules as lhb_peer_allgather_cols, and it counts as one call of that sequence.  Served by the tensor-core
- * kernel only (17 rows or more, group a multiple of 128); otherwise LHB_ERR_UNSUPPORTED and the caller runs
+ * kernel only (9 rows or more, group a multiple of 128); otherwise LHB_ERR_UNSUPPORTED and the caller runs
  * the GEMM and lhb_peer_allgather_cols separately. */
 LHB_API int lhb_gemm_w4a16_groupwise_peer(lhb_ctx* ctx, const float* A, const uint8_t* B_packed, const float* B_scales,
                                           float* C, int M, int N, int K, int group_size, float alpha, float beta,

@@ -67,7 +67,8 @@ namespace lhb {
 // Tuning overrides from the environment (LHB_*), read once per process on first use; 0 / -1 = not set.
 struct Knobs {
     bool pdl = true;             // LHB_PDL=0: no programmatic dependent launch
-    int w4tc_min_m = 17;         // LHB_W4TC_MIN_M: fewest rows that take the W4A16 tensor-core kernel
+    int w4tc_min_m = 9;          // LHB_W4TC_MIN_M: fewest rows that take the W4A16 tensor-core kernel (measured: the GEMV
+                                 // kernel needs 31-32 us for 9-16 rows of the 4096 x 14336 shape, this kernel 24 us)
     bool w4tc_stream_k = false;  // LHB_W4TC_SPLIT=1: even deal of units instead of whole CTAs per column tile
     int w4tc_ctas = 0;           // LHB_W4TC_CTAS: cap on its grid
     bool w4tc_coop = true;       // LHB_W4TC_COOP=0: the last CTA to reach a column tile adds its partial sums up alone

@@ -107,7 +107,7 @@ const Knobs& knobs() {
             return e ? atoi(e) : unset;
         };
         v.pdl = num("LHB_PDL", 1) != 0;
-        v.w4tc_min_m = std::max(1, num("LHB_W4TC_MIN_M", 17));
+        v.w4tc_min_m = std::max(1, num("LHB_W4TC_MIN_M", 9));
         v.w4tc_stream_k = num("LHB_W4TC_SPLIT", 0) == 1;
         v.w4tc_ctas = std::max(0, num("LHB_W4TC_CTAS", 0));
         v.w4tc_coop = num("LHB_W4TC_COOP", 1) != 0;

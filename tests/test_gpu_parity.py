@@ -332,7 +332,7 @@ def test_w4a16_many_rows_in_slabs(chk, lib, M, N, K, G):
     (20, 256 * 200, 384, 128),  # ranges of four or five units over tiles of three: whole and partial segments mixed
 ])
 def test_w4a16_tensor_core_kernel_shapes(chk, M, N, K, G):
-    """From 17 rows on gemm_w4a16_groupwise runs on the tensor cores (int8 digits x int8 weights,
+    """From 9 rows on gemm_w4a16_groupwise runs on the tensor cores (int8 digits x int8 weights,
     exact int32 sums per group, fp32 fold).  Shapes for each way its work is split, with
     alpha / beta, against the checker, twice for run-to-run determinism."""
     rng = np.random.default_rng(3 * M + N + K + G)
