@@ -79,6 +79,7 @@ struct Knobs {
     int decode_target = 0;       // LHB_DECODE_TARGET: CTAs per SM the split-KV plan aims at
     int decode_pages = 0;        // LHB_DECODE_PAGES: pages per CTA
     int decode_splits = 0;       // LHB_DECODE_SPLITS: cap on the KV splits
+    bool decode_one_wave = true; // LHB_DECODE_ONE_WAVE=0: always aim at four CTAs per SM, also when one wave would hold all items
 };
 const Knobs& knobs();
 

@@ -555,6 +555,12 @@ static void decode_split_plan(int sm_count, int64_t items, int max_blocks, size_
     int pg = static_cast<int>(std::max<int64_t>(16, std::min<int64_t>(128, pp)));
     if (knobs().decode_pages > 0) pg = knobs().decode_pages;
     int sp = std::max(1, std::min(32, ceil_div(max_blocks, pg)));
+    // When all (request, KV head) items fit the resident CTA slots, one wave of the longest pieces that still
+    // fills the slots beats more, shorter pieces in a second wave (32 requests x 8 heads x 129 pages: 31.4 us as
+    // 256 CTAs, 37.5 us as 768, 44.7 us as 512).
+    const int64_t slots = static_cast<int64_t>(LHB_PD_MIN_CTAS) * std::max(1, sm_count);
+    if (knobs().decode_one_wave && knobs().decode_pages == 0 && knobs().decode_target == 0 && items <= slots)
+        sp = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(32, slots / items), max_blocks / 16)));
     if (knobs().decode_splits > 0) sp = std::min(sp, knobs().decode_splits);
     const size_t per_split = static_cast<size_t>(items) * group * PD_PART;
     if (sp > 1 && per_split * sp > part_floats_avail)

@@ -119,6 +119,7 @@ const Knobs& knobs() {
         v.decode_target = std::max(0, num("LHB_DECODE_TARGET", 0));
         v.decode_pages = std::max(0, num("LHB_DECODE_PAGES", 0));
         v.decode_splits = std::max(0, num("LHB_DECODE_SPLITS", 0));
+        v.decode_one_wave = num("LHB_DECODE_ONE_WAVE", 1) != 0;
         return v;
     }();
     return k;
